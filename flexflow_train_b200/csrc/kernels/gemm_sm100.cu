@@ -1,0 +1,617 @@
+// gemm_sm100.cu -- Blackwell (sm_100a) GEMM: TMA -> shared memory -> tcgen05.mma
+// with fp32 accumulators in tensor memory (TMEM), persistent over output tiles.
+//
+// Replaces the cuBLAS GemmEx calls the reference makes for Linear forward /
+// dgrad / wgrad (lib/kernels/src/cuda/ops/linear_kernels.cu:121-341) and supplies
+// the BatchMatmul the reference only declares
+// (lib/pcg/include/pcg/computation_graph_builder.h:129).
+//
+//   D[b][m][n] = epilogue( alpha * sum_k A[b][m][k] * B[b][n][k] )
+//
+// Operand layouts.  A is logically [M,K], B is logically [N,K] (so a Linear's
+// weight [out,in] is used as stored).  Either operand may be "K-major" (k is the
+// contiguous index) or "MN-major" (m resp. n is the contiguous index); this is
+// what lets forward, dgrad (dX = dY * W) and wgrad (dW = dY^T * X) all run
+// without a transpose pass.  Two batch dimensions (inner `nh`, outer `nb`)
+// with independent strides cover attention's [batch, seq, head, dim] views.
+//
+// CTA layout (192 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and
+// issues tcgen05.mma from one thread, warps 2..5 are the epilogue (TMEM ->
+// registers -> bias/activation/addend -> global).  Two TMEM accumulator stages
+// let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Every mbarrier wait is bounded: after ~2 s without progress the waiting thread
+// records an error code, raises a CTA-wide abort flag and every role leaves its
+// loop; TMEM is then freed and the kernel returns normally.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int GEMM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct GemmArgs {
+  int M, N, K;
+  int nh, nb;  // inner / outer batch extents
+  void *C;
+  long long ldc, c_sh, c_sb;
+  void *C2;  // optional second output: pre-activation value, bf16, same layout as C
+  const bf16 *bias;    // [N] or null
+  const bf16 *addend;  // optional, added after activation (residual), layout of C (bf16)
+  long long ld_add, add_sh, add_sb;
+  float alpha;
+  int act;
+  int out_fp32;    // C is float instead of bf16
+  int accumulate;  // C += result
+  int tiles_m, tiles_n;
+  long long num_tiles;
+  int *err;
+};
+
+// ----------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *err, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = ffk_globaltimer();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (err) atomicCAS(err, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint64_t *bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+template <bool TF32>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1 (Blackwell)
+//   bits [61,64) layout type: 2 = SWIZZLE_128B
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// ----------------------------------------------------------------------------
+// Kernel
+// ----------------------------------------------------------------------------
+// ES = operand element size (2: bf16 via kind::f16, 4: fp32 storage via kind::tf32).
+// A 128-byte swizzle row holds 128/ES elements, which is also the K extent of a
+// pipeline stage for K-major operands and the MN extent of one TMA box for
+// MN-major operands.
+template <int ES, int BN, bool A_MN, bool B_MN>
+struct GemmCfg {
+  static constexpr int ROW_ELEMS = 128 / ES;       // elements per 128-byte row
+  static constexpr int BK = ROW_ELEMS;             // k extent per stage
+  static constexpr int UMMA_K = 32 / ES;           // k per tcgen05.mma
+  static constexpr int A_BYTES = BM * BK * ES;     // 16 KB
+  static constexpr int B_BYTES = BN * BK * ES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (STAGE_BYTES <= 32768) ? 6 : (STAGE_BYTES <= 49152 ? 4 : 3);
+  static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  // K-major: one 8-row group is 8*128 B apart (SBO), LBO is the fixed 16 B.
+  // MN-major: 8 k-rows of one 64-wide chunk are 128 B apart, 8-row groups are
+  // 1024 B apart (SBO) and the next MN chunk starts BK*128 B later (LBO).
+  static constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16;
+  static constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16;
+  static constexpr uint32_t SBO = 1024;
+  static constexpr uint32_t A_KADV = A_MN ? UMMA_K * 128 : UMMA_K * ES;  // bytes per UMMA k-step
+  static constexpr uint32_t B_KADV = B_MN ? UMMA_K * 128 : UMMA_K * ES;
+  static constexpr uint32_t IDESC = (1u << 4)                                  // D = f32
+                                    | ((ES == 2 ? 1u : 2u) << 7)               // A: bf16 / tf32
+                                    | ((ES == 2 ? 1u : 2u) << 10)              // B
+                                    | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16)
+                                    | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
+
+__device__ __forceinline__ void tile_coords(long long tile, const GemmArgs &p, int &mb, int &nb_, int &bh, int &bb) {
+  long long per_batch = (long long)p.tiles_m * p.tiles_n;
+  long long batch = tile / per_batch;
+  int t = (int)(tile - batch * per_batch);
+  bh = (int)(batch % p.nh);
+  bb = (int)(batch / p.nh);
+  // grouped rasterisation: 8 m-blocks share the same B panel while it is hot in L2
+  const int GROUP = 8;
+  int per_group = GROUP * p.tiles_n;
+  int g = t / per_group;
+  int first_m = g * GROUP;
+  int gsize = min(p.tiles_m - first_m, GROUP);
+  int r = t - g * per_group;
+  mb = first_m + (r % gsize);
+  nb_ = r / gsize;
+}
+
+template <int ES, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                  const GemmArgs p) {
+  using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to.
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t *tiles = smem;
+  uint64_t *bars = (uint64_t *)(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t *full_bar = bars;                 // [STAGES]
+  uint64_t *empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t *tmem_full = bars + 2 * STAGES;   // [2]
+  uint64_t *tmem_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full[s], 1);
+      mbar_init(&tmem_empty[s], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        int mb, nb_, bh, bb;
+        tile_coords(tile, p, mb, nb_, bh, bb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+          uint32_t sb = sa + Cfg::A_BYTES;
+          int k0 = kb * Cfg::BK;
+          if constexpr (!A_MN) {
+            tma_load_4d(sa, &tmapA, &full_bar[stage], k0, mb * BM, bh, bb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / Cfg::ROW_ELEMS; ++c)
+              tma_load_4d(sa + c * Cfg::BK * 128, &tmapA, &full_bar[stage], mb * BM + c * Cfg::ROW_ELEMS, k0, bh, bb);
+          }
+          if constexpr (!B_MN) {
+            tma_load_4d(sb, &tmapB, &full_bar[stage], k0, nb_ * BN, bh, bb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / Cfg::ROW_ELEMS; ++c)
+              tma_load_4d(sb + c * Cfg::BK * 128, &tmapB, &full_bar[stage], nb_ * BN + c * Cfg::ROW_ELEMS, k0, bh, bb);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Drain: every load that was issued must land before the CTA may exit.
+      // The consumer releases each stage only after using it, so waiting for all
+      // stages to be empty again covers every load in flight.
+      for (int s = 0; s < STAGES && ok; ++s) {
+        ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+          uint32_t sb = sa + Cfg::A_BYTES;
+          uint64_t adesc = make_smem_desc(sa, Cfg::A_LBO, Cfg::SBO);
+          uint64_t bdesc = make_smem_desc(sb, Cfg::B_LBO, Cfg::SBO);
+#pragma unroll
+          for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
+            tc_mma<ES == 4>(d_tmem, adesc + (uint64_t)((k * Cfg::A_KADV) >> 4), bdesc + (uint64_t)((k * Cfg::B_KADV) >> 4),
+                            Cfg::IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tmem_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      int mb, nb_, bh, bb;
+      tile_coords(tile, p, mb, nb_, bh, bb);
+      ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = mb * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const long long coff = (long long)bh * p.c_sh + (long long)bb * p.c_sb + (long long)row * p.ldc;
+      const long long aoff = (long long)bh * p.add_sh + (long long)bb * p.add_sb + (long long)row * p.ld_add;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0);
+        tmem_ld32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = nb_ * BN + c0;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          const bool full = (col0 + 32 <= p.N);
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += bf2f(p.bias[col0 + j]);
+          }
+          if (p.C2) {
+            bf16 *c2 = (bf16 *)p.C2 + coff + col0;
+            if (full && ((((uintptr_t)c2) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u = make_uint4(pack_bf162(v[j], v[j + 1]), pack_bf162(v[j + 2], v[j + 3]),
+                                     pack_bf162(v[j + 4], v[j + 5]), pack_bf162(v[j + 6], v[j + 7]));
+                *reinterpret_cast<uint4 *>(c2 + j) = u;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) c2[j] = f2bf(v[j]);
+            }
+          }
+          if (p.act != ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_fwd(v[j], p.act);
+          }
+          if (p.addend) {
+            const bf16 *ad = p.addend + aoff + col0;
+            if (full && ((((uintptr_t)ad) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u = *reinterpret_cast<const uint4 *>(ad + j);
+                float2 f0 = unpack_bf162(u.x), f1 = unpack_bf162(u.y), f2 = unpack_bf162(u.z), f3 = unpack_bf162(u.w);
+                v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
+                v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += bf2f(ad[j]);
+            }
+          }
+          if (p.out_fp32) {
+            float *c = (float *)p.C + coff + col0;
+            if (full && ((((uintptr_t)c) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (p.accumulate) {
+                  float4 old = *reinterpret_cast<float4 *>(c + j);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4 *>(c + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) c[j] = p.accumulate ? c[j] + v[j] : v[j];
+            }
+          } else {
+            bf16 *c = (bf16 *)p.C + coff + col0;
+            if (full && ((((uintptr_t)c) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (p.accumulate) {
+                  uint4 u = *reinterpret_cast<uint4 *>(c + j);
+                  float2 f0 = unpack_bf162(u.x), f1 = unpack_bf162(u.y), f2 = unpack_bf162(u.z), f3 = unpack_bf162(u.w);
+                  v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
+                  v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+                }
+                uint4 o = make_uint4(pack_bf162(v[j], v[j + 1]), pack_bf162(v[j + 2], v[j + 3]),
+                                     pack_bf162(v[j + 4], v[j + 5]), pack_bf162(v[j + 6], v[j + 7]));
+                *reinterpret_cast<uint4 *>(c + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) c[j] = f2bf(p.accumulate ? bf2f(c[j]) + v[j] : v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Host side
+// ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// Build the 4-D map {contiguous, rows, inner batch, outer batch} of one operand.
+// K-major operand: contiguous = k, rows = m|n, box {128/ES, box_rows}.
+// MN-major operand: contiguous = m|n, rows = k, box {128/ES, BK}.
+int make_operand_map(CUtensorMap *map, const void *ptr, int es, long long contiguous, long long rows, long long ld,
+                     int nh, long long sh, int nb, long long sb, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)contiguous, (cuuint64_t)rows, (cuuint64_t)nh, (cuuint64_t)nb};
+  // a batch extent of 1 still needs a legal (multiple of 16 B, non-zero) stride
+  long long sh_b = (nh > 1 ? sh : ld * rows) * es, sb_b = (nb > 1 ? sb : (nh > 1 ? sh * nh : ld * rows)) * es;
+  if (sh_b <= 0) sh_b = 16;
+  if (sb_b <= 0) sb_b = 16;
+  cuuint64_t strides[3] = {(cuuint64_t)(ld * es), (cuuint64_t)sh_b, (cuuint64_t)sb_b};
+  cuuint32_t box[4] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)ptr,
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+__device__ int g_gemm_err = 0;
+
+template <int ES, int BN, bool A_MN, bool B_MN>
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
+  static bool attr_done = false;
+  auto kern = gemm_sm100_kernel<ES, BN, A_MN, B_MN>;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  args.tiles_m = (args.M + BM - 1) / BM;
+  args.tiles_n = (args.N + BN - 1) / BN;
+  args.num_tiles = (long long)args.tiles_m * args.tiles_n * args.nh * args.nb;
+  long long grid = args.num_tiles < max_ctas ? args.num_tiles : max_ctas;
+  if (grid < 1) return 0;
+  kern<<<(unsigned)grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+  return (int)cudaGetLastError();
+}
+
+template <int ES, int BN>
+int launch_major(bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int max_ctas,
+                 cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_cfg<ES, BN, false, false>(ta, tb, args, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_cfg<ES, BN, false, true>(ta, tb, args, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_cfg<ES, BN, true, false>(ta, tb, args, max_ctas, stream);
+  return launch_cfg<ES, BN, true, true>(ta, tb, args, max_ctas, stream);
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+// Descriptor of one GEMM call.  Plain C struct so ctypes can fill it.
+struct FfkGemmDesc {
+  int M, N, K;
+  int nh, nb;             // batch extents (1,1 for a plain GEMM)
+  int es;                 // operand element size: 2 = bf16, 4 = fp32 storage run as tf32
+  int a_mn, b_mn;         // 1 = operand is MN-major (m resp. n contiguous)
+  const void *A;
+  long long lda, a_sh, a_sb;  // leading dimension and batch strides, in elements
+  const void *B;
+  long long ldb, b_sh, b_sb;
+  void *C;
+  long long ldc, c_sh, c_sb;
+  void *C2;
+  const void *bias;
+  const void *addend;
+  long long ld_add, add_sh, add_sb;
+  float alpha;
+  int act;
+  int out_fp32;
+  int accumulate;
+  int bn;                 // tile N: 0 = choose, else 64/128/256
+  int max_ctas;           // 0 = one per SM
+};
+
+// Returns 0 on success, a CUDA/driver error code otherwise, -2 for an
+// argument the TMA path cannot express (unaligned base or stride).
+FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
+  const int es = d->es;
+  if (es != 2 && es != 4) return -2;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
+  if (((uintptr_t)d->A & 15) || ((uintptr_t)d->B & 15)) return -2;
+  if ((d->lda * es) % 16 || (d->ldb * es) % 16) return -2;
+  if ((d->nh > 1 && ((d->a_sh * es) % 16 || (d->b_sh * es) % 16)) ||
+      (d->nb > 1 && ((d->a_sb * es) % 16 || (d->b_sb * es) % 16)))
+    return -2;
+  int bn = d->bn;
+  if (bn == 0) {
+    // Prefer the widest tile that still gives every SM work.
+    long long t256 = (long long)((d->M + 127) / 128) * ((d->N + 255) / 256) * d->nh * d->nb;
+    if (d->N > 128 && t256 >= sm_count()) bn = 256;
+    else if (d->N > 64) bn = 128;
+    else bn = 64;
+    if (es == 4 && bn == 256) bn = 128;
+  }
+  const int BK = 128 / es;
+  CUtensorMap ta, tb;
+  int r;
+  if (!d->a_mn) r = make_operand_map(&ta, d->A, es, d->K, d->M, d->lda, d->nh, d->a_sh, d->nb, d->a_sb, BM);
+  else r = make_operand_map(&ta, d->A, es, d->M, d->K, d->lda, d->nh, d->a_sh, d->nb, d->a_sb, BK);
+  if (r) return r;
+  if (!d->b_mn) r = make_operand_map(&tb, d->B, es, d->K, d->N, d->ldb, d->nh, d->b_sh, d->nb, d->b_sb, bn);
+  else r = make_operand_map(&tb, d->B, es, d->N, d->K, d->ldb, d->nh, d->b_sh, d->nb, d->b_sb, BK);
+  if (r) return r;
+
+  GemmArgs a;
+  a.M = d->M; a.N = d->N; a.K = d->K; a.nh = d->nh < 1 ? 1 : d->nh; a.nb = d->nb < 1 ? 1 : d->nb;
+  a.C = d->C; a.ldc = d->ldc; a.c_sh = d->c_sh; a.c_sb = d->c_sb;
+  a.C2 = d->C2; a.bias = (const bf16 *)d->bias; a.addend = (const bf16 *)d->addend;
+  a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
+  a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate;
+  void *errp = nullptr;
+  cudaGetSymbolAddress(&errp, g_gemm_err);
+  a.err = (int *)errp;
+  int max_ctas = d->max_ctas > 0 ? d->max_ctas : sm_count();
+  if (es == 2) {
+    if (bn == 256) return launch_major<2, 256>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+    if (bn == 128) return launch_major<2, 128>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+    return launch_major<2, 64>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+  } else {
+    if (bn == 128) return launch_major<4, 128>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+    return launch_major<4, 64>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+  }
+}
+
+// Reads (and clears) the device-side error word written by a bounded wait that
+// ran out.  Synchronises the device.
+FFK_API int ffk_gemm_last_error() {
+  int v = 0, z = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  cudaMemcpyFromSymbol(&v, g_gemm_err, sizeof(int));
+  cudaMemcpyToSymbol(g_gemm_err, &z, sizeof(int));
+  return v;
+}

@@ -1,0 +1,352 @@
+// norm_softmax.cu -- row-wise kernels: LayerNorm fwd/bwd (with the dX pass the
+// reference defines but never launches, lib/kernels/src/cuda/ops/layer_norm_kernels.cu:163),
+// softmax fwd/bwd (replaces cudnnSoftmaxForward, softmax_kernels.cu:57), fused
+// softmax + sparse categorical cross-entropy, and the loss-gradient kernels of
+// lib/kernels/src/cuda/loss_function_kernels.cu:21-51.
+//
+// All kernels take bf16 or fp32 activations (dt: 0 = fp32, 1 = bf16) and keep
+// statistics in fp32.
+#include "common.cuh"
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T *p);
+template <> __device__ __forceinline__ float ldf<float>(const float *p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16 *p) { return bf2f(*p); }
+template <typename T> __device__ __forceinline__ void stf(T *p, float v);
+template <> __device__ __forceinline__ void stf<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16 *p, float v) { *p = f2bf(v); }
+
+// ------------------------------------------------------------------ LayerNorm
+// y = LN(a + b) * gamma + beta ; b optional (fused residual add); when b is
+// given and xsum is non-null the sum a + b is written too (backward needs it).
+template <typename T>
+__global__ void layernorm_fwd_kernel(const T *__restrict__ a, const T *__restrict__ b, const T *__restrict__ gamma,
+                                     const T *__restrict__ beta, T *__restrict__ xsum, T *__restrict__ y,
+                                     float *__restrict__ mean, float *__restrict__ rstd, int rows, int cols,
+                                     float eps) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *pa = a + (long long)row * cols;
+    const T *pb = b ? b + (long long)row * cols : nullptr;
+    float s = 0.f, ss = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float v = ldf(pa + c) + (pb ? ldf(pb + c) : 0.f);
+      if (pb && xsum) {
+        stf(xsum + (long long)row * cols + c, v);
+        v = ldf(xsum + (long long)row * cols + c);  // statistics of the rounded value backward will see
+      }
+      s += v;
+      ss += v * v;
+    }
+    s = block_sum(s, red);
+    ss = block_sum(ss, red);
+    float mu = s / cols;
+    float var = fmaxf(ss / cols - mu * mu, 0.f);
+    float rs = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (rstd) rstd[row] = rs;
+    }
+    const T *px = (pb && xsum) ? xsum + (long long)row * cols : pa;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float v = (pb && !xsum) ? ldf(pa + c) + ldf(pb + c) : ldf(px + c);
+      float o = (v - mu) * rs;
+      if (gamma) o = o * ldf(gamma + c) + (beta ? ldf(beta + c) : 0.f);
+      stf(y + (long long)row * cols + c, o);
+    }
+  }
+}
+
+// One pass over (dy, x): writes dx and per-block partial column sums of
+// dgamma / dbeta into scratch `partial` laid out [2][gridDim.x][cols].
+// Thread t owns columns t, t+blockDim, ... (at most KMAX of them).
+template <typename T, int KMAX>
+__global__ void layernorm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const T *__restrict__ gamma,
+                                     const float *__restrict__ mean, const float *__restrict__ rstd,
+                                     T *__restrict__ dx, float *__restrict__ partial, int rows, int cols,
+                                     int accumulate_dx) {
+  __shared__ float red[32];
+  float dg[KMAX], db[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) { dg[k] = 0.f; db[k] = 0.f; }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *pdy = dy + (long long)row * cols;
+    const T *px = x + (long long)row * cols;
+    float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    float vg[KMAX], vx[KMAX];
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      int c = threadIdx.x + k * blockDim.x;
+      if (c < cols) {
+        float g = ldf(pdy + c);
+        float xh = (ldf(px + c) - mu) * rs;
+        dg[k] += g * xh;
+        db[k] += g;
+        float gg = gamma ? g * ldf(gamma + c) : g;
+        vg[k] = gg;
+        vx[k] = xh;
+        s1 += gg;
+        s2 += gg * xh;
+      }
+    }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    float m1 = s1 / cols, m2 = s2 / cols;
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      int c = threadIdx.x + k * blockDim.x;
+      if (c < cols) {
+        float o = rs * (vg[k] - m1 - vx[k] * m2);
+        T *pdx = dx + (long long)row * cols + c;
+        stf(pdx, accumulate_dx ? ldf(pdx) + o : o);
+      }
+    }
+  }
+  if (partial) {
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      int c = threadIdx.x + k * blockDim.x;
+      if (c < cols) {
+        partial[(long long)blockIdx.x * cols + c] = dg[k];
+        partial[((long long)gridDim.x + blockIdx.x) * cols + c] = db[k];
+      }
+    }
+  }
+}
+template <typename T>
+__global__ void layernorm_bwd_finish_kernel(const float *__restrict__ partial, int nparts, int cols, T *dgamma,
+                                            T *dbeta, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float g = 0.f, b = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    g += partial[(long long)p * cols + c];
+    b += partial[((long long)nparts + p) * cols + c];
+  }
+  if (dgamma) stf(dgamma + c, accumulate ? ldf(dgamma + c) + g : g);
+  if (dbeta) stf(dbeta + c, accumulate ? ldf(dbeta + c) + b : b);
+}
+
+// ------------------------------------------------------------------ Softmax
+// y = softmax(scale * x) over the last dim.  causal_q > 0: row r is query
+// position (r % causal_q) and keys past it are masked out.
+template <typename T>
+__global__ void softmax_fwd_kernel(const T *__restrict__ x, T *__restrict__ y, int rows, int cols, float scale,
+                                   int causal_q) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *px = x + (long long)row * cols;
+    int limit = causal_q > 0 ? min(cols, (row % causal_q) + 1) : cols;
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < limit; c += blockDim.x) mx = fmaxf(mx, ldf(px + c) * scale);
+    mx = block_max(mx, red);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < limit; c += blockDim.x) s += __expf(ldf(px + c) * scale - mx);
+    s = block_sum(s, red);
+    float inv = 1.f / s;
+    T *py = y + (long long)row * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x)
+      stf(py + c, c < limit ? __expf(ldf(px + c) * scale - mx) * inv : 0.f);
+  }
+}
+// dx = scale * y * (dy - sum(dy * y))
+template <typename T>
+__global__ void softmax_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ y, T *__restrict__ dx, int rows,
+                                   int cols, float scale) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *pdy = dy + (long long)row * cols;
+    const T *py = y + (long long)row * cols;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) s += ldf(pdy + c) * ldf(py + c);
+    s = block_sum(s, red);
+    T *pdx = dx + (long long)row * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) stf(pdx + c, scale * ldf(py + c) * (ldf(pdy + c) - s));
+  }
+}
+
+// Fused softmax + sparse categorical cross-entropy: per-row loss, optional
+// probabilities, and dlogits = (p - onehot(label)) * grad_scale.  Rows whose
+// label is negative contribute no loss and no gradient.
+template <typename T, typename L>
+__global__ void softmax_ce_kernel(const T *__restrict__ logits, const L *__restrict__ labels, T *__restrict__ probs,
+                                  T *__restrict__ dlogits, float *__restrict__ loss, int rows, int cols,
+                                  float grad_scale) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *px = logits + (long long)row * cols;
+    long long label = (long long)labels[row];
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) mx = fmaxf(mx, ldf(px + c));
+    mx = block_max(mx, red);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) s += __expf(ldf(px + c) - mx);
+    s = block_sum(s, red);
+    float inv = 1.f / s;
+    bool valid = label >= 0 && label < cols;
+    if (threadIdx.x == 0 && loss) loss[row] = valid ? (__logf(s) + mx - ldf(px + label)) : 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float p = __expf(ldf(px + c) - mx) * inv;
+      if (probs) stf(probs + (long long)row * cols + c, p);
+      if (dlogits) stf(dlogits + (long long)row * cols + c, valid ? (p - (c == label ? 1.f : 0.f)) * grad_scale : 0.f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ loss gradients
+enum { LOSS_SPARSE_CCE = 0, LOSS_CCE = 1, LOSS_MSE_AVG = 2, LOSS_IDENTITY = 3, LOSS_MSE_SUM = 4 };
+// dlogit for losses whose input is already a probability / prediction tensor.
+template <typename T, typename L>
+__global__ void loss_bwd_kernel(int kind, const T *__restrict__ pred, const void *__restrict__ target,
+                                T *__restrict__ dpred, long long rows, int cols, float scale) {
+  long long n = rows * cols;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float p = ldf(pred + i), g;
+    if (kind == LOSS_SPARSE_CCE) {
+      long long lab = (long long)((const L *)target)[i / cols];
+      g = p - ((i % cols) == lab ? 1.f : 0.f);
+    } else if (kind == LOSS_CCE) {
+      g = p - ldf((const T *)target + i);
+    } else if (kind == LOSS_MSE_AVG || kind == LOSS_MSE_SUM) {
+      g = 2.f * (p - ldf((const T *)target + i));
+    } else {
+      g = 1.f;
+    }
+    stf(dpred + i, g * scale);
+  }
+}
+// per-row loss values for reporting
+template <typename T, typename L>
+__global__ void loss_fwd_kernel(int kind, const T *__restrict__ pred, const void *__restrict__ target,
+                                float *__restrict__ loss, int rows, int cols) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T *pp = pred + (long long)row * cols;
+    float acc = 0.f;
+    if (kind == LOSS_SPARSE_CCE) {
+      long long lab = (long long)((const L *)target)[row];
+      if (threadIdx.x == 0 && lab >= 0 && lab < cols) acc = -__logf(fmaxf(ldf(pp + lab), 1e-30f));
+    } else {
+      const T *pt = (const T *)target + (long long)row * cols;
+      for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float p = ldf(pp + c);
+        if (kind == LOSS_CCE) acc += -ldf(pt + c) * __logf(fmaxf(p, 1e-30f));
+        else if (kind == LOSS_IDENTITY) acc += p;
+        else { float d = p - ldf(pt + c); acc += d * d; }
+      }
+    }
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) loss[row] = acc;
+  }
+}
+
+}  // namespace
+
+#define DISPATCH_FLOAT(dt, ...)                                   \
+  if ((dt) == 0) { typedef float T; __VA_ARGS__; }                \
+  else if ((dt) == 1) { typedef bf16 T; __VA_ARGS__; }            \
+  else return -2;
+
+static int rows_grid(int rows) { return rows < 148 * 8 ? rows : 148 * 8; }
+
+FFK_API int ffk_layernorm_fwd(const void *a, const void *b, const void *gamma, const void *beta, void *xsum, void *y,
+                              float *mean, float *rstd, int rows, int cols, float eps, int dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  int threads = cols >= 2048 ? 512 : 256;
+  DISPATCH_FLOAT(dt, (layernorm_fwd_kernel<T><<<rows_grid(rows), threads, 0, st>>>(
+                         (const T *)a, (const T *)b, (const T *)gamma, (const T *)beta, (T *)xsum, (T *)y, mean, rstd,
+                         rows, cols, eps)));
+  return (int)cudaGetLastError();
+}
+
+static int ln_bwd_grid(int rows) { return rows < 296 ? rows : 296; }
+// floats of scratch needed by ffk_layernorm_bwd
+FFK_API long long ffk_layernorm_bwd_scratch(int rows, int cols) { return 2ll * ln_bwd_grid(rows) * cols; }
+
+// dx (+)= LN backward; dgamma/dbeta (+)= column sums.  `partial` is scratch of
+// ffk_layernorm_bwd_scratch(rows, cols) floats.  cols <= 16384.
+FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, const float *mean, const float *rstd,
+                              void *dx, void *dgamma, void *dbeta, float *partial, int rows, int cols, int dt,
+                              int accumulate_dx, int accumulate_params, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (cols > 16384) return -2;
+  int grid = ln_bwd_grid(rows);
+  float *part = (dgamma || dbeta) ? partial : nullptr;
+  DISPATCH_FLOAT(dt, {
+    if (cols <= 512 * 4)
+      layernorm_bwd_kernel<T, 4><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
+                                                        (T *)dx, part, rows, cols, accumulate_dx);
+    else if (cols <= 512 * 16)
+      layernorm_bwd_kernel<T, 16><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
+                                                         (T *)dx, part, rows, cols, accumulate_dx);
+    else
+      layernorm_bwd_kernel<T, 32><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
+                                                         (T *)dx, part, rows, cols, accumulate_dx);
+    if (part)
+      layernorm_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(part, grid, cols, (T *)dgamma, (T *)dbeta,
+                                                                          accumulate_params);
+  });
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_softmax_fwd(const void *x, void *y, int rows, int cols, float scale, int causal_q, int dt,
+                            cudaStream_t st) {
+  if (rows <= 0) return 0;
+  int threads = cols >= 1024 ? 256 : 128;
+  DISPATCH_FLOAT(dt, (softmax_fwd_kernel<T><<<rows < 148 * 16 ? rows : 148 * 16, threads, 0, st>>>(
+                         (const T *)x, (T *)y, rows, cols, scale, causal_q)));
+  return (int)cudaGetLastError();
+}
+FFK_API int ffk_softmax_bwd(const void *dy, const void *y, void *dx, int rows, int cols, float scale, int dt,
+                            cudaStream_t st) {
+  if (rows <= 0) return 0;
+  int threads = cols >= 1024 ? 256 : 128;
+  DISPATCH_FLOAT(dt, (softmax_bwd_kernel<T><<<rows < 148 * 16 ? rows : 148 * 16, threads, 0, st>>>(
+                         (const T *)dy, (const T *)y, (T *)dx, rows, cols, scale)));
+  return (int)cudaGetLastError();
+}
+// label_dt: 2 = int32, 3 = int64
+FFK_API int ffk_softmax_ce(const void *logits, const void *labels, void *probs, void *dlogits, float *loss, int rows,
+                           int cols, float grad_scale, int dt, int label_dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  int threads = cols >= 4096 ? 1024 : 256;
+  int grid = rows < 148 * 4 ? rows : 148 * 4;
+  DISPATCH_FLOAT(dt, {
+    if (label_dt == 3)
+      softmax_ce_kernel<T, long long><<<grid, threads, 0, st>>>((const T *)logits, (const long long *)labels,
+                                                                 (T *)probs, (T *)dlogits, loss, rows, cols, grad_scale);
+    else
+      softmax_ce_kernel<T, int><<<grid, threads, 0, st>>>((const T *)logits, (const int *)labels, (T *)probs,
+                                                           (T *)dlogits, loss, rows, cols, grad_scale);
+  });
+  return (int)cudaGetLastError();
+}
+FFK_API int ffk_loss_bwd(int kind, const void *pred, const void *target, void *dpred, long long rows, int cols,
+                         float scale, int dt, int label_dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  DISPATCH_FLOAT(dt, {
+    if (label_dt == 3)
+      loss_bwd_kernel<T, long long><<<ffk_blocks(rows * cols, 256), 256, 0, st>>>(kind, (const T *)pred, target,
+                                                                                   (T *)dpred, rows, cols, scale);
+    else
+      loss_bwd_kernel<T, int><<<ffk_blocks(rows * cols, 256), 256, 0, st>>>(kind, (const T *)pred, target, (T *)dpred,
+                                                                             rows, cols, scale);
+  });
+  return (int)cudaGetLastError();
+}
+FFK_API int ffk_loss_fwd(int kind, const void *pred, const void *target, float *loss, int rows, int cols, int dt,
+                         int label_dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  DISPATCH_FLOAT(dt, {
+    if (label_dt == 3)
+      loss_fwd_kernel<T, long long><<<rows < 2368 ? rows : 2368, 128, 0, st>>>(kind, (const T *)pred, target, loss,
+                                                                                rows, cols);
+    else
+      loss_fwd_kernel<T, int><<<rows < 2368 ? rows : 2368, 128, 0, st>>>(kind, (const T *)pred, target, loss, rows,
+                                                                          cols);
+  });
+  return (int)cudaGetLastError();
+}

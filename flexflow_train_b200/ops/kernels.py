@@ -1,0 +1,385 @@
+"""ctypes bindings of the sm_100a kernel library (``libffk.so``).
+
+Every function here takes torch CUDA tensors, checks what the kernel cannot
+check for itself (dtype, contiguity, device) and launches on the current torch
+stream.  Nothing falls back to a torch op: if the shared object is missing the
+import of the library raises, so a GPU run can never silently use another path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB_PATH = os.path.join(_PKG_DIR, "libffk.so")
+_lib = None
+
+# dtype codes of the C API
+DT_F32, DT_BF16, DT_I32, DT_I64, DT_F16, DT_BOOL, DT_F64 = range(7)
+_DT = {
+    torch.float32: DT_F32, torch.bfloat16: DT_BF16, torch.int32: DT_I32, torch.int64: DT_I64,
+    torch.float16: DT_F16, torch.bool: DT_BOOL, torch.float64: DT_F64,
+}
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_SIGMOID, ACT_TANH = range(5)
+ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4}
+
+UNARY_OPS = {
+    "identity": 0, "relu": 1, "sigmoid": 2, "tanh": 3, "elu": 4, "gelu": 5, "exp": 6, "rsqrt": 7, "sin": 8,
+    "cos": 9, "scalar_multiply": 10, "scalar_add": 11, "scalar_sub": 12, "scalar_truediv": 13, "pow": 14,
+    "log": 15, "sqrt": 16, "neg": 17,
+}
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "max": 4, "min": 5}
+LOSS_KINDS = {"sparse_categorical_crossentropy": 0, "categorical_crossentropy": 1,
+              "mean_squared_error_avg_reduce": 2, "identity": 3, "mean_squared_error_sum_reduce": 4}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class GemmDesc(ctypes.Structure):
+    _fields_ = [
+        ("M", c_int), ("N", c_int), ("K", c_int), ("nh", c_int), ("nb", c_int), ("es", c_int),
+        ("a_mn", c_int), ("b_mn", c_int),
+        ("A", c_void_p), ("lda", c_longlong), ("a_sh", c_longlong), ("a_sb", c_longlong),
+        ("B", c_void_p), ("ldb", c_longlong), ("b_sh", c_longlong), ("b_sb", c_longlong),
+        ("C", c_void_p), ("ldc", c_longlong), ("c_sh", c_longlong), ("c_sb", c_longlong),
+        ("C2", c_void_p), ("bias", c_void_p), ("addend", c_void_p),
+        ("ld_add", c_longlong), ("add_sh", c_longlong), ("add_sb", c_longlong),
+        ("alpha", c_float), ("act", c_int), ("out_fp32", c_int), ("accumulate", c_int),
+        ("bn", c_int), ("max_ctas", c_int),
+    ]
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def lib():
+    """The loaded kernel library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise KernelError(
+                f"{_LIB_PATH} is missing: run `python build.py` (nvcc, sm_100a) before using the GPU path")
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l):
+    P, I, L, F, S = c_void_p, c_int, c_longlong, c_float, c_void_p
+    sig = {
+        "ffk_gemm": [ctypes.POINTER(GemmDesc), S],
+        "ffk_gemm_last_error": [],
+        "ffk_unary_fwd": [I, P, P, L, F, I, S],
+        "ffk_unary_bwd": [I, P, P, P, P, L, F, I, I, S],
+        "ffk_binary_fwd": [I, P, P, P, L, L, I, S],
+        "ffk_binary_bwd": [I, P, P, P, P, P, L, I, I, S],
+        "ffk_dropout": [P, P, P, L, F, c_ulonglong, I, S],
+        "ffk_axpby": [P, P, L, F, F, I, S],
+        "ffk_fill": [P, L, F, I, S],
+        "ffk_cast": [P, I, P, I, L, I, S],
+        "ffk_bias_act_bwd": [P, P, P, P, P, I, I, I, I, I, S],
+        "ffk_layernorm_fwd": [P, P, P, P, P, P, P, P, I, I, F, I, S],
+        "ffk_layernorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, S],
+        "ffk_softmax_fwd": [P, P, I, I, F, I, I, S],
+        "ffk_softmax_bwd": [P, P, P, I, I, F, I, S],
+        "ffk_softmax_ce": [P, P, P, P, P, I, I, F, I, I, S],
+        "ffk_loss_bwd": [I, P, P, P, L, I, F, I, I, S],
+        "ffk_loss_fwd": [I, P, P, P, I, I, I, I, S],
+        "ffk_adam_update": [P, P, P, P, P, L, F, F, F, F, F, F, I, S],
+        "ffk_sgd_update": [P, P, P, P, L, F, F, I, F, F, I, S],
+        "ffk_embedding_fwd": [P, P, P, L, I, I, L, I, I, I, I, S],
+        "ffk_embedding_bwd": [P, P, P, L, I, I, L, I, I, I, I, S],
+        "ffk_embedding_sgd": [P, P, P, L, I, I, L, F, I, I, S],
+    }
+    for name, args in sig.items():
+        if hasattr(l, name):
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = c_int
+    for name in ("ffk_bias_act_bwd_scratch", "ffk_layernorm_bwd_scratch"):
+        if hasattr(l, name):
+            fn = getattr(l, name)
+            fn.argtypes = [c_int, c_int]
+            fn.restype = c_longlong
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        raise KernelError(f"{what} failed with code {code}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}")
+
+
+def _cuda_contig(*ts):
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("kernel called with a CPU tensor")
+        if not t.is_contiguous():
+            raise KernelError("kernel called with a non-contiguous tensor")
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, nh=1, nb=1,
+             a_sh=0, a_sb=0, b_sh=0, b_sb=0, c_sh=0, c_sb=0, C2=None, bias=None, addend=None,
+             ld_add=0, add_sh=0, add_sb=0, alpha=1.0, act=0, out_fp32=False, accumulate=False,
+             bn=0, max_ctas=0):
+    """D = epilogue(alpha * A[M,K] . B[N,K]^T) on raw pointers; see gemm_sm100.cu."""
+    d = GemmDesc(M, N, K, nh, nb, es, int(a_mn), int(b_mn), A, lda, a_sh, a_sb, B, ldb, b_sh, b_sb,
+                 C, ldc, c_sh, c_sb, C2, bias, addend, ld_add, add_sh, add_sb, alpha, act, int(out_fp32),
+                 int(accumulate), bn, max_ctas)
+    _check(lib().ffk_gemm(ctypes.byref(d), _stream()), "ffk_gemm")
+
+
+def gemm_last_error() -> int:
+    return lib().ffk_gemm_last_error()
+
+
+def _es(t):
+    if t.dtype == torch.bfloat16:
+        return 2
+    if t.dtype == torch.float32:
+        return 4
+    raise KernelError(f"gemm operands must be bf16 or fp32, got {t.dtype}")
+
+
+def matmul_nt(a, b, out=None, *, bias=None, act=None, addend=None, pre_act_out=None, alpha=1.0,
+              accumulate=False, out_dtype=None, bn=0):
+    """out[M,N] = a[M,K] @ b[N,K]^T (+bias, activation, +addend).  Linear forward."""
+    M, K = a.shape
+    N = b.shape[0]
+    out = _gemm_out(out, M, N, a, out_dtype)
+    _cuda_contig(a, b, out, bias, addend, pre_act_out)
+    gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=K, B=b.data_ptr(), ldb=K, C=out.data_ptr(), ldc=N,
+             es=_es(a), C2=_p(pre_act_out), bias=_p(bias), addend=_p(addend), ld_add=N, alpha=alpha,
+             act=ACT_CODES[act] if not isinstance(act, int) else act, out_fp32=out.dtype == torch.float32,
+             accumulate=accumulate, bn=bn)
+    return out
+
+
+def matmul_nn(a, b, out=None, *, alpha=1.0, accumulate=False, out_dtype=None, bn=0):
+    """out[M,N] = a[M,K] @ b[K,N].  Linear dgrad (a = dY, b = W[out,in])."""
+    M, K = a.shape
+    N = b.shape[1]
+    out = _gemm_out(out, M, N, a, out_dtype)
+    _cuda_contig(a, b, out)
+    gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=K, B=b.data_ptr(), ldb=N, b_mn=True, C=out.data_ptr(), ldc=N,
+             es=_es(a), alpha=alpha, out_fp32=out.dtype == torch.float32, accumulate=accumulate, bn=bn)
+    return out
+
+
+def matmul_tn(a, b, out=None, *, alpha=1.0, accumulate=False, out_dtype=None, bn=0):
+    """out[M,N] = a[K,M]^T @ b[K,N].  Linear wgrad (a = dY[tokens,out], b = X[tokens,in])."""
+    K, M = a.shape
+    N = b.shape[1]
+    out = _gemm_out(out, M, N, a, out_dtype)
+    _cuda_contig(a, b, out)
+    gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=M, a_mn=True, B=b.data_ptr(), ldb=N, b_mn=True,
+             C=out.data_ptr(), ldc=N, es=_es(a), alpha=alpha, out_fp32=out.dtype == torch.float32,
+             accumulate=accumulate, bn=bn)
+    return out
+
+
+def _gemm_out(out, M, N, like, out_dtype):
+    if out is None:
+        out = torch.empty((M, N), device=like.device, dtype=out_dtype or like.dtype)
+    return out
+
+
+# --------------------------------------------------------------------------- elementwise
+def unary_fwd(op: str, x, out=None, scalar: float = 0.0):
+    out = torch.empty_like(x) if out is None else out
+    _cuda_contig(x, out)
+    _check(lib().ffk_unary_fwd(UNARY_OPS[op], x.data_ptr(), out.data_ptr(), x.numel(), scalar, _dt(x), _stream()),
+           "ffk_unary_fwd")
+    return out
+
+
+def unary_bwd(op: str, x, y, dy, dx=None, scalar: float = 0.0, accumulate=False):
+    dx = torch.empty_like(x) if dx is None else dx
+    _cuda_contig(x, y, dy, dx)
+    _check(lib().ffk_unary_bwd(UNARY_OPS[op], x.data_ptr(), y.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(),
+                               scalar, _dt(x), int(accumulate), _stream()), "ffk_unary_bwd")
+    return dx
+
+
+def binary_fwd(op: str, a, b, out=None):
+    out = torch.empty_like(a) if out is None else out
+    _cuda_contig(a, b, out)
+    if a.dtype != b.dtype:
+        raise KernelError("binary op operands must share a dtype")
+    if a.numel() % b.numel() != 0:
+        raise KernelError("second operand must broadcast over trailing dims")
+    _check(lib().ffk_binary_fwd(BINARY_OPS[op], a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), b.numel(),
+                                _dt(a), _stream()), "ffk_binary_fwd")
+    return out
+
+
+def binary_bwd(op: str, a, b, dy, da=None, db=None, accumulate=False):
+    _cuda_contig(a, b, dy, da, db)
+    _check(lib().ffk_binary_bwd(BINARY_OPS[op], a.data_ptr(), b.data_ptr(), dy.data_ptr(), _p(da), _p(db),
+                                dy.numel(), _dt(dy), int(accumulate), _stream()), "ffk_binary_bwd")
+
+
+def dropout(x, p: float, seed: int, residual=None, out=None):
+    out = torch.empty_like(x) if out is None else out
+    _cuda_contig(x, residual, out)
+    _check(lib().ffk_dropout(x.data_ptr(), _p(residual), out.data_ptr(), x.numel(), p, seed & (2**64 - 1), _dt(x),
+                             _stream()), "ffk_dropout")
+    return out
+
+
+def axpby(x, y, a: float = 1.0, b: float = 1.0):
+    """y = a*x + b*y in place."""
+    _cuda_contig(x, y)
+    _check(lib().ffk_axpby(x.data_ptr(), y.data_ptr(), x.numel(), a, b, _dt(x), _stream()), "ffk_axpby")
+    return y
+
+
+def fill(y, v: float):
+    _cuda_contig(y)
+    _check(lib().ffk_fill(y.data_ptr(), y.numel(), v, _dt(y), _stream()), "ffk_fill")
+    return y
+
+
+def cast(src, dst, accumulate=False):
+    _cuda_contig(src, dst)
+    _check(lib().ffk_cast(src.data_ptr(), _dt(src), dst.data_ptr(), _dt(dst), src.numel(), int(accumulate),
+                          _stream()), "ffk_cast")
+    return dst
+
+
+def bias_act_bwd_scratch(rows, cols) -> int:
+    return lib().ffk_bias_act_bwd_scratch(rows, cols)
+
+
+def bias_act_bwd(dy, saved, dz, dbias, scratch, act, accumulate=False):
+    """dz = dy * act'(saved); dbias (+)= column sums of dz."""
+    rows, cols = dy.shape
+    _cuda_contig(dy, saved, dz, dbias, scratch)
+    _check(lib().ffk_bias_act_bwd(dy.data_ptr(), _p(saved), _p(dz), _p(dbias), _p(scratch), rows, cols,
+                                  ACT_CODES[act] if not isinstance(act, int) else act, _dt(dy), int(accumulate),
+                                  _stream()), "ffk_bias_act_bwd")
+
+
+# --------------------------------------------------------------------------- row-wise
+def layernorm_fwd(a, gamma, beta, eps, residual=None, xsum=None, out=None, mean=None, rstd=None):
+    rows, cols = a.shape
+    out = torch.empty_like(a) if out is None else out
+    _cuda_contig(a, residual, gamma, beta, xsum, out, mean, rstd)
+    _check(lib().ffk_layernorm_fwd(a.data_ptr(), _p(residual), _p(gamma), _p(beta), _p(xsum), out.data_ptr(),
+                                   _p(mean), _p(rstd), rows, cols, eps, _dt(a), _stream()), "ffk_layernorm_fwd")
+    return out
+
+
+def layernorm_bwd_scratch(rows, cols) -> int:
+    return lib().ffk_layernorm_bwd_scratch(rows, cols)
+
+
+def layernorm_bwd(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, scratch, accumulate_dx=False,
+                  accumulate_params=False):
+    rows, cols = dy.shape
+    _cuda_contig(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, scratch)
+    _check(lib().ffk_layernorm_bwd(dy.data_ptr(), x.data_ptr(), _p(gamma), mean.data_ptr(), rstd.data_ptr(),
+                                   dx.data_ptr(), _p(dgamma), _p(dbeta), _p(scratch), rows, cols, _dt(dy),
+                                   int(accumulate_dx), int(accumulate_params), _stream()), "ffk_layernorm_bwd")
+
+
+def softmax_fwd(x, out=None, scale=1.0, causal_q=0):
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    out = torch.empty_like(x) if out is None else out
+    _cuda_contig(x, out)
+    _check(lib().ffk_softmax_fwd(x.data_ptr(), out.data_ptr(), rows, cols, scale, causal_q, _dt(x), _stream()),
+           "ffk_softmax_fwd")
+    return out
+
+
+def softmax_bwd(dy, y, dx=None, scale=1.0):
+    cols = y.shape[-1]
+    rows = y.numel() // cols
+    dx = torch.empty_like(y) if dx is None else dx
+    _cuda_contig(dy, y, dx)
+    _check(lib().ffk_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, scale, _dt(y), _stream()),
+           "ffk_softmax_bwd")
+    return dx
+
+
+def softmax_ce(logits, labels, loss, dlogits=None, probs=None, grad_scale=1.0):
+    rows, cols = logits.shape
+    _cuda_contig(logits, labels, loss, dlogits, probs)
+    _check(lib().ffk_softmax_ce(logits.data_ptr(), labels.data_ptr(), _p(probs), _p(dlogits), _p(loss), rows, cols,
+                                grad_scale, _dt(logits), _dt(labels), _stream()), "ffk_softmax_ce")
+
+
+def loss_bwd(kind: str, pred, target, dpred, scale):
+    cols = pred.shape[-1]
+    rows = pred.numel() // cols
+    _cuda_contig(pred, target, dpred)
+    ldt = _dt(target) if target is not None and target.dtype in (torch.int32, torch.int64) else DT_I32
+    _check(lib().ffk_loss_bwd(LOSS_KINDS[kind], pred.data_ptr(), _p(target), dpred.data_ptr(), rows, cols, scale,
+                              _dt(pred), ldt, _stream()), "ffk_loss_bwd")
+
+
+def loss_fwd(kind: str, pred, target, loss_rows):
+    cols = pred.shape[-1]
+    rows = pred.numel() // cols
+    _cuda_contig(pred, target, loss_rows)
+    ldt = _dt(target) if target is not None and target.dtype in (torch.int32, torch.int64) else DT_I32
+    _check(lib().ffk_loss_fwd(LOSS_KINDS[kind], pred.data_ptr(), _p(target), loss_rows.data_ptr(), rows, cols,
+                              _dt(pred), ldt, _stream()), "ffk_loss_fwd")
+
+
+# --------------------------------------------------------------------------- optimizers / embedding
+def adam_update(w, m, v, g, shadow, alpha_t, beta1, beta2, eps, weight_decay=0.0, grad_scale=1.0):
+    _cuda_contig(w, m, v, g, shadow)
+    _check(lib().ffk_adam_update(w.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), _p(shadow), w.numel(),
+                                 alpha_t, beta1, beta2, eps, weight_decay, grad_scale, _dt(g), _stream()),
+           "ffk_adam_update")
+
+
+def sgd_update(w, mom, g, shadow, lr, momentum=0.0, nesterov=False, weight_decay=0.0, grad_scale=1.0):
+    _cuda_contig(w, mom, g, shadow)
+    _check(lib().ffk_sgd_update(w.data_ptr(), _p(mom), g.data_ptr(), _p(shadow), w.numel(), lr, momentum,
+                                int(nesterov), weight_decay, grad_scale, _dt(g), _stream()), "ffk_sgd_update")
+
+
+def embedding_fwd(idx, table, out, aggr="sum"):
+    bag = idx.shape[-1] if out.dim() == idx.dim() else 1
+    tokens = idx.numel() // bag
+    _cuda_contig(idx, table, out)
+    _check(lib().ffk_embedding_fwd(idx.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, bag, table.shape[1],
+                                   table.shape[0], int(aggr == "avg"), _dt(table), _dt(idx), _dt(out), _stream()),
+           "ffk_embedding_fwd")
+    return out
+
+
+def embedding_bwd(idx, dout, dtable, aggr="sum"):
+    bag = idx.shape[-1] if dout.dim() == idx.dim() else 1
+    tokens = idx.numel() // bag
+    _cuda_contig(idx, dout, dtable)
+    _check(lib().ffk_embedding_bwd(idx.data_ptr(), dout.data_ptr(), dtable.data_ptr(), tokens, bag,
+                                   dtable.shape[1], dtable.shape[0], int(aggr == "avg"), _dt(dtable), _dt(idx),
+                                   _dt(dout), _stream()), "ffk_embedding_bwd")
+    return dtable
