@@ -1,0 +1,223 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput (samples/s) of the large lib/models-style Transformer
+(24 decoder-only layers, d_model 2048, 16 heads, FFN 8192, vocab 32000, seq 1024, global batch 32,
+bf16 compute with fp32 master weights, Adam) on N GPUs of one node.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+Prints one JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with the batch
+already on the device; `e2e` times the public API (`CompiledModel.train_step`) including the
+host->device copy of every step's batch from pinned memory and the device->host read of the loss.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL_CONFIGS = {
+    "transformer_large": ("transformer_lm", {"num_features": 2048, "sequence_length": 1024, "batch_size": 32,
+                                             "dim_feedforward": 8192, "num_heads": 16, "num_decoder_layers": 24,
+                                             "dropout": 0.1, "vocab_size": 32000, "init_std": 0.02}),
+    "transformer_small": ("transformer_lm", {"num_features": 512, "sequence_length": 256, "batch_size": 8,
+                                             "dim_feedforward": 2048, "num_heads": 8, "num_decoder_layers": 2,
+                                             "dropout": 0.1, "vocab_size": 4096}),
+    "bert_base": ("bert", {"token_ids": True, "batch_size": 64, "sequence_length": 512, "vocab_size": 30528}),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.proc = None
+        self.lines = []
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    # The reference is C++/CMake with no Python project at its root; the one offline pip install that is
+    # allowed fails before any build starts (no setup.py / pyproject.toml; its legacy bindings need the
+    # absent cmake_build_extension package and a Legion runtime).  Nothing of it can be run here.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "pip install of /root/reference fails offline: no setup.py/pyproject.toml at the root; "
+                      "bindings/python/old needs cmake_build_extension + Legion/Realm, not in the wheelhouse"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
+    ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--strategy", default="search", help="search | dp | tp | <path to strategy json>")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from flexflow_train_b200 import api
+    from flexflow_train_b200.ops import kernels as K
+    from flexflow_train_b200.runtime.executor import OptimizerConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dctx = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from flexflow_train_b200.parallel.context import DistContext
+        dctx = DistContext(rank, world, local_rank)
+
+    model_name, mcfg = MODEL_CONFIGS[args.model]
+    mcfg = dict(mcfg)
+    global_batch, seq = mcfg["batch_size"], mcfg["sequence_length"]
+    ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
+                         search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel"}.get(args.strategy, "unity"),
+                         import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
+    lr = 1e-4
+    model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind="adam", lr=lr), dist=dctx)
+    ex = model.executable
+    vocab = mcfg["vocab_size"]
+    local_batch = ex.local_batch if hasattr(ex, "local_batch") else global_batch
+
+    # synthetic data of the named shape: token ids uniform over the vocabulary, next-token labels
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_host = 4
+    if model_name == "bert":
+        host_batches = [({"input_ids": torch.randint(0, 30522, (local_batch, seq, 1), generator=gen, dtype=torch.int32).pin_memory(),
+                          "position_ids": torch.arange(seq, dtype=torch.int32).repeat(local_batch, 1).reshape(local_batch, seq, 1).pin_memory()},
+                         torch.where(torch.rand(local_batch, seq, generator=gen) < 0.15,
+                                     torch.randint(0, 30522, (local_batch, seq), generator=gen), torch.tensor(-1)).to(torch.int32).pin_memory())
+                        for _ in range(n_host)]
+    else:
+        host_batches = [({"input_ids": torch.randint(0, vocab, (local_batch, seq, 1), generator=gen, dtype=torch.int32).pin_memory()},
+                         torch.randint(0, vocab, (local_batch, seq), generator=gen, dtype=torch.int32).pin_memory())
+                        for _ in range(n_host)]
+    dev_batches = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host_batches]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed: batch resident on the device
+    for i in range(args.warmup):
+        ex.train_step(*dev_batches[i % n_host])
+    barrier()
+    l0 = K.launch_count()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        ex.train_step(*dev_batches[i % n_host])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    launches = K.launch_count() - l0
+    if ex.cfg.use_cuda_graph:
+        launches = getattr(ex, "launches_per_step", 0) * args.steps + launches
+    final_loss = ex.mean_loss()
+
+    # ---- end to end through the public API: pinned host batch -> device, loss -> host, every step
+    for i in range(2):
+        model.train_step(*host_batches[i % n_host])
+    barrier()
+    t0 = time.perf_counter()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for i in range(args.steps):
+        model.train_step(*host_batches[i % n_host])
+    e3.record()
+    barrier()
+    e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3) / args.steps
+    h2d, d2h = model.h2d_bytes_last_step, model.d2h_bytes_last_step
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        value = global_batch / (ms / 1e3)
+        out = {
+            "metric": "train samples/s (searched strategy)", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq,
+                       "parallelism": getattr(ex, "parallelism", "single"), "layers": mcfg.get("num_decoder_layers", 12),
+                       "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768)), "optimizer": "adam", "lr": lr,
+                       "l2": "activations and weights per step (>100 GB) exceed the 126 MB L2; no flush needed",
+                       "cuda_graph": bool(ex.cfg.use_cuda_graph), "tokens_per_s": value * seq},
+            "clocks": clocks,
+            "e2e": {"value": global_batch / (e2e_ms / 1e3), "unit": "samples/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "final_loss": final_loss,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,139 @@
+"""Public entry points: ``compile`` a model into a trainable object and drive it.
+
+This is the new-design flow of the reference (docs/plantuml/figures/pytorch-tracing.puml):
+model -> ComputationGraph -> optimize (strategy search) -> CompiledModel -> forward/backward/update,
+with the reference's ``FFConfig`` search flags (lib/task-spec/include/task-spec/ff_config.dtg.toml).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional, Union
+
+import torch
+
+from . import _ffcore as core
+from .runtime.executor import ExecConfig, Executable, OptimizerConfig
+
+
+@dataclass
+class FFConfig:
+    """Run configuration; field names follow the reference's FFConfig / CLI flags (README.md:58-81)."""
+    epochs: int = 1
+    batch_size: int = 64
+    num_nodes: int = 1
+    gpus_per_node: int = 0  # 0 = use WORLD_SIZE / visible devices
+    learning_rate: float = 0.01
+    weight_decay: float = 0.0001
+    workspace_size: int = 1 << 30
+    enable_profiling: bool = False
+    search_budget: int = 0
+    search_alpha: float = 1.05
+    search_algorithm: str = "unity"  # "unity" | "mcmc" | "data_parallel" | "none"
+    only_data_parallel: bool = False
+    enable_parameter_parallel: bool = True
+    enable_attribute_parallel: bool = True
+    substitution_json_path: Optional[str] = None
+    export_strategy_file: Optional[str] = None
+    import_strategy_file: Optional[str] = None
+    export_strategy_computation_graph_file: Optional[str] = None
+    compute_dtype: str = "bf16"
+    use_cuda_graph: bool = True
+    seed: int = 0
+
+
+class CompiledModel:
+    """A computation graph bound to a strategy and an executor."""
+
+    def __init__(self, graph, executable: Executable, strategy=None, search_stats: Optional[dict] = None):
+        self.graph = graph
+        self.executable = executable
+        self.strategy = strategy
+        self.search_stats = search_stats or {}
+        self._pinned: Dict[str, torch.Tensor] = {}
+        self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory() if torch.cuda.is_available() else torch.zeros(1)
+        self.h2d_bytes_last_step = 0
+        self.d2h_bytes_last_step = 0
+
+    # ---- training
+    def train_step(self, inputs: Dict[str, torch.Tensor], labels: Optional[torch.Tensor] = None, return_loss: bool = True):
+        """One optimisation step on a batch given as host (ideally pinned) or device tensors.
+        Returns the mean loss as a Python float when ``return_loss`` (one device->host read)."""
+        ex = self.executable
+        h2d = 0
+        for t in list(inputs.values()) + ([labels] if labels is not None else []):
+            if t is not None and not t.is_cuda:
+                h2d += t.numel() * t.element_size()
+        self.h2d_bytes_last_step = h2d
+        ex.train_step(inputs, labels)
+        if not return_loss:
+            self.d2h_bytes_last_step = 0
+            return None
+        mean = ex.loss_rows.mean(dtype=torch.float32).reshape(1)
+        self._loss_host.copy_(mean, non_blocking=False)
+        self.d2h_bytes_last_step = 4
+        return float(self._loss_host[0])
+
+    def forward(self, inputs: Dict[str, torch.Tensor]):
+        return self.executable.infer(inputs)
+
+    def fit(self, data_loader, epochs: int = 1, log_every: int = 0):
+        """Legacy ``FFModel.fit`` loop (bindings/python/old/flexflow/core/flexflow_cffi.py:2058-2100)."""
+        history = []
+        for _ in range(epochs):
+            for step, (inputs, labels) in enumerate(data_loader):
+                loss = self.train_step(inputs, labels)
+                history.append(loss)
+                if log_every and step % log_every == 0:
+                    print(f"step {step}: loss {loss:.4f}")
+        return history
+
+    def state_dict(self):
+        return self.executable.state_dict()
+
+    def load_state_dict(self, sd):
+        self.executable.load_state_dict(sd)
+
+    def export_strategy(self, path: str):
+        with open(path, "w") as f:
+            f.write(self.graph.to_v1_string(parallel=True, indent=1))
+
+
+def _as_graph(model, model_config):
+    if isinstance(model, str):
+        return core.build_model(model, model_config)
+    return model
+
+
+def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None, *, config: Optional[FFConfig] = None,
+            optimizer: Optional[OptimizerConfig] = None, loss: Optional[str] = "sparse_categorical_crossentropy",
+            dist=None, training: bool = True, device: str = "cuda") -> CompiledModel:
+    """Build (or take) a computation graph, choose a parallelisation strategy and lower it to an executor.
+
+    With one device the graph runs as is.  With a ``dist`` context the strategy comes from the
+    search (``config.search_algorithm``) or from ``config.import_strategy_file``.
+    """
+    config = config or FFConfig()
+    cg = _as_graph(model, model_config)
+    exec_cfg = ExecConfig(compute_dtype=config.compute_dtype, loss=loss,
+                          optimizer=optimizer or OptimizerConfig(kind="sgd", lr=config.learning_rate),
+                          seed=config.seed, use_cuda_graph=config.use_cuda_graph, device=device, training=training,
+                          profile_layers=config.enable_profiling)
+    world = dist.world_size if dist is not None else 1
+    strategy, stats = cg, {}
+    if world > 1:
+        from .compiler.strategy import choose_strategy
+        strategy, stats = choose_strategy(cg, world, config)
+        from .parallel.dist_executor import DistExecutable
+        ex = DistExecutable(strategy, exec_cfg, dist)
+    else:
+        if config.import_strategy_file:
+            with open(config.import_strategy_file) as f:
+                strategy = core.Graph.from_v1(f.read())
+        ex = Executable(strategy, exec_cfg)
+    cm = CompiledModel(cg, ex, strategy, stats)
+    if config.export_strategy_file and (dist is None or dist.rank == 0):
+        with open(config.export_strategy_file, "w") as f:
+            f.write(strategy.to_v1_string(parallel=True, indent=1))
+    return cm

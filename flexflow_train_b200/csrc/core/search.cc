@@ -1,2 +1,758 @@
+#include "search.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <functional>
+#include <limits>
+#include <queue>
+#include <set>
+
 #include "pyjson.h"
-namespace ff { void bind_search(py::module &m) {} }
+
+namespace ff {
+
+// ---------------------------------------------------------------- cost model
+Json CostParams::to_json() const {
+  Json j = Json::object();
+  j["matmul_tflops"] = matmul_tflops; j["matmul_efficiency"] = matmul_efficiency; j["hbm_gbs"] = hbm_gbs;
+  j["nvlink_gbs"] = nvlink_gbs; j["allreduce_bus_gbs"] = allreduce_bus_gbs; j["launch_us"] = launch_us;
+  j["collective_latency_us"] = collective_latency_us; j["inter_node_gbs"] = inter_node_gbs;
+  j["fused_overlap"] = fused_overlap; j["bytes_per_float"] = bytes_per_float;
+  return j;
+}
+CostParams CostParams::from_json(const Json &j) {
+  CostParams p;
+  p.matmul_tflops = j.get_float("matmul_tflops", p.matmul_tflops);
+  p.matmul_efficiency = j.get_float("matmul_efficiency", p.matmul_efficiency);
+  p.hbm_gbs = j.get_float("hbm_gbs", p.hbm_gbs);
+  p.nvlink_gbs = j.get_float("nvlink_gbs", p.nvlink_gbs);
+  p.allreduce_bus_gbs = j.get_float("allreduce_bus_gbs", p.allreduce_bus_gbs);
+  p.launch_us = j.get_float("launch_us", p.launch_us);
+  p.collective_latency_us = j.get_float("collective_latency_us", p.collective_latency_us);
+  p.inter_node_gbs = j.get_float("inter_node_gbs", p.inter_node_gbs);
+  p.fused_overlap = j.get_float("fused_overlap", p.fused_overlap);
+  p.bytes_per_float = (int)j.get_int("bytes_per_float", p.bytes_per_float);
+  return p;
+}
+
+static double elem_bytes(const PShape &s, const CostParams &p) {
+  if (s.dtype == DataType::FLOAT || s.dtype == DataType::HALF || s.dtype == DataType::BFLOAT16) return p.bytes_per_float;
+  return dtype_bytes(s.dtype);
+}
+static double piece_bytes(const PShape &s, const CostParams &p) { return (double)s.piece_elements() * elem_bytes(s, p); }
+
+std::string CostEstimator::op_cost_key(const Node &n, const Graph &g) {
+  std::string k = to_string(n.type) + n.attrs.canonical();
+  for (auto &e : n.inputs) k += "|" + to_string(e.dst_slot) + ":" + g.shape(e.src).str();
+  return k;
+}
+
+double CostEstimator::movement_cost_ms(double bytes, bool inter_node) const {
+  double bw = inter_node ? params.inter_node_gbs : params.nvlink_gbs;
+  return params.collective_latency_us * 1e-3 + bytes / (bw * 1e9) * 1e3;
+}
+
+OpCost CostEstimator::op_cost(const Node &n, const Graph &g) const {
+  const_cast<CostEstimator *>(this)->num_queries++;
+  if (!measured.empty()) {
+    auto it = measured.find(op_cost_key(n, g));
+    if (it != measured.end()) return it->second;
+  }
+  const CostParams &p = params;
+  OpCost c;
+  double in_bytes = 0, out_bytes = 0, weight_bytes = 0;
+  for (auto &e : n.inputs) {
+    double b = piece_bytes(g.shape(e.src), p);
+    if (is_weight_slot(n.type, e.dst_slot)) weight_bytes += b;
+    else in_bytes += b;
+  }
+  for (auto &o : n.outputs) out_bytes += piece_bytes(o.shape, p);
+  c.memory_bytes = out_bytes;
+  const double flops_per_ms = p.matmul_tflops * p.matmul_efficiency * 1e9;
+  const double bytes_per_ms = p.hbm_gbs * 1e6;
+  const double launch = p.launch_us * 1e-3;
+  auto mem_time = [&](double bytes) { return bytes / bytes_per_ms; };
+  auto coll_lat = p.collective_latency_us * 1e-3;
+  switch (n.type) {
+    case OpType::INPUT:
+      return c;
+    case OpType::WEIGHT:
+      // parameters plus gradient plus fp32 master and Adam moments (2 + 2 + 4 + 4 + 4 bytes per element)
+      c.memory_bytes = (double)n.outputs[0].shape.piece_elements() * 16.0;
+      return c;
+    case OpType::NOOP:
+      c.memory_bytes = 0;
+      return c;
+    case OpType::LINEAR: {
+      const PShape &x = g.shape(n.in(Slot::INPUT)->src);
+      const PShape &y = n.outputs[0].shape;
+      double rows = (double)x.piece_elements() / ((double)x.dims.back().size / x.dims.back().degree);
+      double k = (double)x.dims.back().size / x.dims.back().degree;
+      double nn = (double)y.dims.back().size / y.dims.back().degree;
+      double flops = 2.0 * rows * k * nn;
+      c.fwd_ms = std::max(flops / flops_per_ms, mem_time(in_bytes + out_bytes + weight_bytes)) + launch;
+      c.bwd_ms = std::max(2.0 * flops / flops_per_ms, mem_time(2 * (in_bytes + out_bytes) + 2 * weight_bytes)) + 2 * launch;
+      return c;
+    }
+    case OpType::BATCHMATMUL: {
+      const PShape &a = g.shape(n.in(Slot::LHS_INPUT)->src);
+      const PShape &y = n.outputs[0].shape;
+      double m = (double)a.dims.back().size / a.dims.back().degree;
+      double flops = 2.0 * (double)y.piece_elements() * m;
+      c.fwd_ms = std::max(flops / flops_per_ms, mem_time(in_bytes + out_bytes)) + launch;
+      c.bwd_ms = 2 * c.fwd_ms;
+      return c;
+    }
+    case OpType::MULTIHEAD_ATTENTION: {
+      const PShape &q = g.shape(n.in(Slot::QUERY)->src);
+      const PShape &k = g.shape(n.in(Slot::KEY)->src);
+      double heads = (double)n.attrs.at("num_heads").as_int() / std::max(1, q.discard_copy_degree);
+      double kd = (double)n.attrs.at("kdim").as_int(), vd = (double)n.attrs.at("vdim").as_int();
+      double e = (double)n.attrs.at("embed_dim").as_int();
+      double b = (double)q.dims[0].size / q.dims[0].degree, sq = (double)q.dims[1].size, sk = (double)k.dims[1].size;
+      double dq = (double)q.dims[2].size;
+      double proj = 2.0 * b * (sq * dq * heads * kd + 2.0 * sk * dq * heads * (kd + vd) / 2.0 + sq * heads * vd * e);
+      double core = 2.0 * b * heads * sq * sk * (kd + vd);
+      double score_bytes = b * heads * sq * sk * p.bytes_per_float;
+      c.fwd_ms = std::max((proj + core) / flops_per_ms, mem_time(in_bytes + out_bytes + weight_bytes + 4.0 * score_bytes)) + 6 * launch;
+      c.bwd_ms = std::max(2.0 * (proj + core) / flops_per_ms, mem_time(2 * (in_bytes + out_bytes) + 2 * weight_bytes + 8.0 * score_bytes)) + 12 * launch;
+      c.memory_bytes = out_bytes + score_bytes + b * sq * heads * (2 * kd + 2 * vd) * p.bytes_per_float;
+      return c;
+    }
+    case OpType::CONV2D: {
+      const PShape &x = g.shape(n.in(Slot::INPUT)->src);
+      const PShape &y = n.outputs[0].shape;
+      double ic = (double)x.dims[1].size / x.dims[1].degree;
+      double flops = 2.0 * (double)y.piece_elements() * ic * (double)n.attrs.at("kernel_h").as_int() * (double)n.attrs.at("kernel_w").as_int();
+      // implicit GEMM on small, odd channel counts reaches a smaller share of the tensor-core peak than Linear
+      c.fwd_ms = std::max(flops / (0.5 * flops_per_ms), mem_time(in_bytes + out_bytes + weight_bytes)) + launch;
+      c.bwd_ms = 2 * c.fwd_ms;
+      return c;
+    }
+    case OpType::EMBEDDING:
+      c.fwd_ms = mem_time(2 * out_bytes) + launch;
+      c.bwd_ms = mem_time(3 * out_bytes) + launch;
+      return c;
+    // ---- parallel operators: collectives over NVLink (degree within one node) ----
+    case OpType::REPARTITION: {
+      int k = (int)n.attrs.at("repartition_degree").as_int();
+      // forward: every rank keeps its slice of data it already holds; backward: all-gather of the gradient
+      c.fwd_ms = launch;
+      c.bwd_ms = coll_lat + in_bytes * (k - 1.0) / k / (p.nvlink_gbs * 1e6);
+      c.memory_bytes = out_bytes;
+      return c;
+    }
+    case OpType::COMBINE: {
+      int k = (int)n.attrs.at("combine_degree").as_int();
+      c.fwd_ms = coll_lat + out_bytes * (k - 1.0) / k / (p.nvlink_gbs * 1e6);
+      c.bwd_ms = launch;
+      return c;
+    }
+    case OpType::REPLICATE: {
+      int k = (int)n.attrs.at("replicate_degree").as_int();
+      // forward is free in SPMD execution (the tensor already lives on every rank); backward sums the
+      // replicas' gradients: an all-reduce, overlapped with the rest of backward when it is a weight gradient
+      double ar = coll_lat + 2.0 * in_bytes * (k - 1.0) / k / (p.allreduce_bus_gbs * 1e6);
+      bool weight_grad = g.node(n.inputs[0].src.node).type == OpType::WEIGHT ||
+                         (is_parallel_op(g.node(n.inputs[0].src.node).type) && !g.node(n.inputs[0].src.node).inputs.empty() &&
+                          g.node(g.node(n.inputs[0].src.node).inputs[0].src.node).type == OpType::WEIGHT);
+      c.fwd_ms = 0;
+      c.bwd_ms = weight_grad ? ar * (1.0 - p.fused_overlap) : ar;
+      c.memory_bytes = 0;
+      return c;
+    }
+    case OpType::REDUCTION: {
+      int k = (int)n.attrs.at("reduction_degree").as_int();
+      double ar = coll_lat + 2.0 * out_bytes * (k - 1.0) / k / (p.allreduce_bus_gbs * 1e6);
+      // fused with the producing GEMM (GEMM -> reduce-scatter kernel) most of the transfer hides under the math
+      const Node &prod = g.node(n.inputs[0].src.node);
+      bool fused = prod.type == OpType::LINEAR || prod.type == OpType::BATCHMATMUL || prod.type == OpType::MULTIHEAD_ATTENTION;
+      c.fwd_ms = fused ? ar * (1.0 - p.fused_overlap) + coll_lat : ar;
+      c.bwd_ms = 0;
+      return c;
+    }
+    default: {
+      // bandwidth-bound operators: forward reads inputs and writes outputs, backward about twice that
+      c.fwd_ms = mem_time(in_bytes + out_bytes + weight_bytes) + launch;
+      c.bwd_ms = mem_time(2 * in_bytes + 2 * out_bytes) + launch;
+      if (n.type == OpType::RESHAPE || n.type == OpType::FLAT) { c.fwd_ms = 0; c.bwd_ms = 0; c.memory_bytes = 0; }
+      return c;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- machine views
+std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m) {
+  int count = 1;
+  for (int d : task_degrees) count *= d;
+  std::vector<MachineView> out;
+  if (count > r.count) return out;
+  const int per_node = m.num_gpus_per_node;
+  for (int start = r.start; start + count <= r.start + r.count; start += count) {
+    MachineView v;
+    v.start_node = start / per_node;
+    v.start_device = start % per_node;
+    int stride = 1;
+    std::vector<MachineViewDim> dims(task_degrees.size());
+    for (int i = (int)task_degrees.size() - 1; i >= 0; --i) {
+      // contiguous layout: the last task dim varies fastest; a dim whose stride reaches the node size crosses nodes
+      bool inter = stride >= per_node;
+      dims[i] = {inter ? stride / per_node : stride, inter};
+      stride *= task_degrees[i];
+    }
+    v.dims = dims;
+    out.push_back(v);
+  }
+  return out;
+}
+std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task_degrees, const MachineSpec &m) {
+  std::vector<int> devs;
+  int n = 1;
+  for (int d : task_degrees) n *= d;
+  int base = v.start_node * m.num_gpus_per_node + v.start_device;
+  for (int t = 0; t < n; ++t) {
+    int rem = t, dev = base;
+    for (int i = (int)task_degrees.size() - 1; i >= 0; --i) {
+      int c = rem % task_degrees[i];
+      rem /= task_degrees[i];
+      int stride = i < (int)v.dims.size() ? v.dims[i].stride * (v.dims[i].inter_node ? m.num_gpus_per_node : 1) : 1;
+      dev += c * stride;
+    }
+    devs.push_back(dev);
+  }
+  return devs;
+}
+
+// ---------------------------------------------------------------- SP decomposition of a graph
+static DiGraph graph_digraph(const Graph &g) {
+  DiGraph d;
+  for (auto &kv : g.nodes()) {
+    d.add_node(kv.first);
+    for (auto &e : kv.second.inputs) d.add_edge(e.src.node, kv.first);
+  }
+  return d;
+}
+SPTree get_graph_sp_decomposition(const Graph &g, bool *exact) {
+  DiGraph d = graph_digraph(g);
+  if (exact) *exact = true;
+  if (auto t = get_series_parallel_decomposition(d)) return *t;
+  // weights and inputs, each with its trailing chain of parallel ops, are connected all-to-all to the
+  // successors of those chains: this hoists them in front of the computation
+  std::set<int> sources, chain_nodes;
+  for (auto &kv : g.nodes())
+    if (kv.second.type == OpType::WEIGHT || kv.second.type == OpType::INPUT) sources.insert(kv.first);
+  std::map<int, int> chain_end;  // source -> last node of its parallel-op chain
+  for (int s : sources) {
+    int cur = s;
+    while (true) {
+      auto succ = g.successors(cur);
+      if (succ.size() == 1 && is_parallel_op(g.node(succ[0]).type) && g.predecessors(succ[0]).size() == 1) cur = succ[0];
+      else break;
+    }
+    chain_end[s] = cur;
+  }
+  std::set<int> targets;
+  for (auto &kv : chain_end)
+    for (int t : g.successors(kv.second)) targets.insert(t);
+  DiGraph d2 = d;
+  for (auto &kv : chain_end)
+    for (int t : targets) d2.add_edge(kv.second, t);
+  if (is_acyclic(d2))
+    if (auto t = get_series_parallel_decomposition(d2)) return *t;
+  if (exact) *exact = false;
+  return escribano_sp_ization(is_acyclic(d2) ? d2 : d);
+}
+
+// ---------------------------------------------------------------- machine-mapping DP
+const MappingPoint &MachineMappingResult::best_runtime() const {
+  if (front.empty()) throw Error("machine mapping is infeasible");
+  size_t b = 0;
+  for (size_t i = 1; i < front.size(); ++i) if (front[i].runtime_ms < front[b].runtime_ms) b = i;
+  return front[b];
+}
+
+namespace {
+using Front = std::vector<MappingPoint>;
+
+void prune(Front &f, int max_front) {
+  if (f.empty()) return;
+  std::sort(f.begin(), f.end(), [](const MappingPoint &a, const MappingPoint &b) {
+    return a.runtime_ms < b.runtime_ms || (a.runtime_ms == b.runtime_ms && a.memory_bytes < b.memory_bytes);
+  });
+  Front out;
+  double best_mem = std::numeric_limits<double>::infinity();
+  for (auto &p : f) {
+    if (max_front == 1) { out.push_back(p); break; }
+    if (p.memory_bytes < best_mem) { out.push_back(p); best_mem = p.memory_bytes; }
+    if ((int)out.size() >= max_front) break;
+  }
+  f.swap(out);
+}
+
+struct DP {
+  const Graph &g;
+  const MachineSpec &m;
+  const CostEstimator &est;
+  int max_front;
+  std::map<NodeId, OpCost> cost_cache;
+  std::map<NodeId, std::vector<int>> task_cache;
+  // memo key: (tree node pointer, resources, fixed views of leaves inside the subtree)
+  std::map<std::string, Front> memo;
+
+  const OpCost &cost(NodeId n) {
+    auto it = cost_cache.find(n);
+    if (it == cost_cache.end()) it = cost_cache.emplace(n, est.op_cost(g.node(n), g)).first;
+    return it->second;
+  }
+  const std::vector<int> &tasks(NodeId n) {
+    auto it = task_cache.find(n);
+    if (it == task_cache.end()) it = task_cache.emplace(n, operator_task_space(g.node(n), g)).first;
+    return it->second;
+  }
+  static void leaves(const SPTree &t, std::set<int> &out) {
+    if (t.kind == SPTree::Leaf) out.insert(t.node);
+    else for (auto &c : t.children) leaves(c, out);
+  }
+  // cost of moving the tensors on edges a->b when the two operators sit on different device sets
+  double movement(NodeId a, const MachineView &va, NodeId b, const MachineView &vb) {
+    std::vector<int> da = view_devices(va, tasks(a), m), db = view_devices(vb, tasks(b), m);
+    std::sort(da.begin(), da.end());
+    std::sort(db.begin(), db.end());
+    // an unsharded tensor is present on every device of the (single-node) job: no movement
+    if (da == db) return 0.0;
+    if (std::includes(da.begin(), da.end(), db.begin(), db.end())) return 0.0;
+    double bytes = 0;
+    for (auto &e : g.node(b).inputs)
+      if (e.src.node == a) bytes += (double)g.shape(e.src).piece_bytes();
+    bool inter = (da.front() / m.num_gpus_per_node) != (db.front() / m.num_gpus_per_node);
+    return 2.0 * est.movement_cost_ms(bytes, inter);  // forward activation + backward gradient
+  }
+
+  Front solve(const SPTree &t, Resources r, const std::map<NodeId, MachineView> &fixed) {
+    std::set<int> ls;
+    leaves(t, ls);
+    std::string key = std::to_string((uintptr_t)&t) + "@" + std::to_string(r.start) + "+" + std::to_string(r.count);
+    for (auto &kv : fixed)
+      if (ls.count(kv.first)) key += ";" + std::to_string(kv.first) + kv.second.str();
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+    Front res;
+    if (t.kind == SPTree::Leaf) {
+      const OpCost &c = cost(t.node);
+      auto fit = fixed.find(t.node);
+      std::vector<MachineView> views;
+      if (fit != fixed.end()) {
+        // a fixed view must lie inside the resources of this subproblem
+        auto devs = view_devices(fit->second, tasks(t.node), m);
+        bool inside = true;
+        for (int d : devs) if (d < r.start || d >= r.start + r.count) inside = false;
+        if (inside) views.push_back(fit->second);
+      } else views = allowed_machine_views(tasks(t.node), r, m);
+      // on a uniform machine every allowed view costs the same: keep the first (lowest start) only
+      if (!views.empty()) {
+        MappingPoint p;
+        p.runtime_ms = c.total_ms();
+        p.memory_bytes = c.memory_bytes;
+        p.views[t.node] = views.front();
+        res.push_back(p);
+      }
+    } else if (t.kind == SPTree::Series) {
+      const SPTree &l = t.children[0], &rt = t.children[1];
+      std::set<int> ll, rl;
+      leaves(l, ll);
+      leaves(rt, rl);
+      // boundary: producers in the left subtree with consumers in the right subtree
+      std::vector<std::pair<NodeId, NodeId>> edges;
+      for (int b : rl)
+        for (auto &e : g.node(b).inputs)
+          if (ll.count(e.src.node)) edges.push_back({e.src.node, b});
+      Front fl = solve(l, r, fixed), fr = solve(rt, r, fixed);
+      for (auto &a : fl)
+        for (auto &b : fr) {
+          MappingPoint p;
+          double move = 0;
+          for (auto &e : edges) move = std::max(move, movement(e.first, a.views.at(e.first), e.second, b.views.at(e.second)));
+          p.runtime_ms = a.runtime_ms + b.runtime_ms + move;
+          p.memory_bytes = a.memory_bytes + b.memory_bytes;
+          p.views = a.views;
+          p.views.insert(b.views.begin(), b.views.end());
+          res.push_back(p);
+        }
+    } else {
+      const SPTree &l = t.children[0], &rt = t.children[1];
+      // (a) run the branches one after the other on all resources
+      Front fl = solve(l, r, fixed), fr = solve(rt, r, fixed);
+      for (auto &a : fl)
+        for (auto &b : fr) {
+          MappingPoint p;
+          p.runtime_ms = a.runtime_ms + b.runtime_ms;
+          p.memory_bytes = a.memory_bytes + b.memory_bytes;
+          p.views = a.views;
+          p.views.insert(b.views.begin(), b.views.end());
+          res.push_back(p);
+        }
+      // (b) split the resources (power-of-two halves) and run the branches side by side
+      if (r.count >= 2 && r.count % 2 == 0) {
+        Resources r1{r.start, r.count / 2}, r2{r.start + r.count / 2, r.count / 2};
+        for (int swap = 0; swap < 2; ++swap) {
+          Front a_ = solve(l, swap ? r2 : r1, fixed), b_ = solve(rt, swap ? r1 : r2, fixed);
+          for (auto &a : a_)
+            for (auto &b : b_) {
+              MappingPoint p;
+              p.runtime_ms = std::max(a.runtime_ms, b.runtime_ms);
+              p.memory_bytes = std::max(a.memory_bytes, b.memory_bytes);
+              p.views = a.views;
+              p.views.insert(b.views.begin(), b.views.end());
+              res.push_back(p);
+            }
+        }
+      }
+    }
+    prune(res, max_front);
+    memo[key] = res;
+    return res;
+  }
+};
+}  // namespace
+
+MachineMappingResult get_optimal_machine_mapping(const Graph &pcg, const SPTree &binary_tree, const MachineSpec &m, const CostEstimator &est,
+                                                 int max_front) {
+  if (!sp_is_binary(binary_tree)) throw Error("machine mapping needs a binary SP tree");
+  DP dp{pcg, m, est, std::max(1, max_front)};
+  MachineMappingResult r;
+  r.front = dp.solve(binary_tree, Resources{0, m.num_devices()}, {});
+  return r;
+}
+
+Graph mapped_pcg_from_pcg_and_mapping(const Graph &pcg, const std::map<NodeId, MachineView> &mapping) {
+  Graph g = pcg;
+  for (auto &kv : mapping)
+    if (g.has_node(kv.first)) g.node(kv.first).view = kv.second;
+  return g;
+}
+
+SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est) {
+  SearchResult r;
+  r.pcg = pcg;
+  SPTree tree = balanced_binary_sp_tree(get_graph_sp_decomposition(pcg));
+  MachineMappingResult mm = get_optimal_machine_mapping(pcg, tree, m, est, 1);
+  if (!mm.feasible()) {
+    r.runtime_ms = std::numeric_limits<double>::infinity();
+    return r;
+  }
+  r.mapping = mm.best_runtime().views;
+  r.runtime_ms = mm.best_runtime().runtime_ms;
+  r.memory_bytes = mm.best_runtime().memory_bytes;
+  return r;
+}
+
+static bool within_degree(const Graph &g, int max_total_degree) {
+  if (max_total_degree <= 0) return true;
+  for (auto &kv : g.nodes())
+    for (auto &o : kv.second.outputs)
+      if (o.shape.total_degree() > max_total_degree) return false;
+  return true;
+}
+Graph apply_rules_exhaustively(const Graph &g0, const std::vector<Substitution> &rules, int max_applications, int max_total_degree) {
+  Graph g = g0;
+  int applied = 0;
+  bool progress = true;
+  while (progress && applied < max_applications) {
+    progress = false;
+    for (auto &rule : rules) {
+      bool again = true;
+      while (again && applied < max_applications) {
+        again = false;
+        for (auto &mt : find_pattern_matches(rule.pattern, g)) {
+          auto ng = apply_substitution(g, rule, mt);
+          if (ng && within_degree(*ng, max_total_degree)) {
+            g = *ng;
+            ++applied;
+            again = true;
+            progress = true;
+            break;  // matches are stale after an application
+          }
+        }
+      }
+    }
+  }
+  return g;
+}
+
+SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
+                          const UnityConfig &cfg) {
+  auto t0 = std::chrono::steady_clock::now();
+  auto elapsed = [&] { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); };
+  struct State {
+    double cost;
+    Graph g;
+    bool operator<(const State &o) const { return cost > o.cost; }  // min-heap
+  };
+  std::priority_queue<State> queue;
+  std::set<std::string> seen;
+  SearchResult best = evaluate_pcg(start, m, est);
+  queue.push({best.runtime_ms, start});
+  seen.insert(start.signature());
+  long long evaluated = 1, generated = 0;
+  int iterations = 0;
+  for (; iterations < cfg.budget && !queue.empty(); ++iterations) {
+    if (elapsed() > cfg.time_limit_s) break;
+    State cur = queue.top();
+    queue.pop();
+    if (cur.cost > cfg.alpha * best.runtime_ms) continue;
+    int candidates = 0;
+    for (auto &rule : rules) {
+      if (candidates >= cfg.max_candidates_per_step || elapsed() > cfg.time_limit_s) break;
+      for (auto &mt : find_pattern_matches(rule.pattern, cur.g)) {
+        if (candidates >= cfg.max_candidates_per_step) break;
+        auto ng = apply_substitution(cur.g, rule, mt);
+        if (!ng) continue;
+        ++generated;
+        if ((int)ng->num_nodes() > cfg.max_num_ops) continue;
+        std::string sig = ng->signature();
+        if (!seen.insert(sig).second) continue;
+        ++candidates;
+        SearchResult r = evaluate_pcg(*ng, m, est);
+        ++evaluated;
+        if (r.runtime_ms < best.runtime_ms) best = r;
+        if (r.runtime_ms <= cfg.alpha * best.runtime_ms) queue.push({r.runtime_ms, *ng});
+      }
+    }
+  }
+  best.stats = Json::object();
+  best.stats["iterations"] = iterations;
+  best.stats["evaluated"] = evaluated;
+  best.stats["generated"] = generated;
+  best.stats["seconds"] = elapsed();
+  best.stats["cost_queries"] = est.num_queries;
+  return best;
+}
+
+// ---------------------------------------------------------------- simulator
+double simulate_task_graph(const Graph &g, const MachineSpec &m, const CostEstimator &est, bool include_backward) {
+  // forward tasks in topological order; list scheduling: a task starts when its producers (plus the
+  // transfers between differing device sets) are done and all of its devices are free
+  std::map<NodeId, double> finish;
+  std::map<int, double> device_free;
+  auto devices_of = [&](NodeId n) {
+    const Node &nd = g.node(n);
+    auto ts = operator_task_space(nd, g);
+    MachineView v = nd.view ? *nd.view : MachineView{};
+    if (!nd.view) {
+      auto vs = allowed_machine_views(ts, Resources{0, m.num_devices()}, m);
+      if (!vs.empty()) v = vs.front();
+    }
+    return view_devices(v, ts, m);
+  };
+  auto order = g.topological_order();
+  std::map<NodeId, std::vector<int>> devs;
+  for (NodeId n : order) devs[n] = devices_of(n);
+  auto run = [&](NodeId n, double ready, double dur) {
+    double start = ready;
+    for (int d : devs[n]) start = std::max(start, device_free[d]);
+    double end = start + dur;
+    for (int d : devs[n]) device_free[d] = end;
+    return end;
+  };
+  auto comm = [&](NodeId a, NodeId b) {
+    auto da = devs[a], db = devs[b];
+    std::sort(da.begin(), da.end());
+    std::sort(db.begin(), db.end());
+    if (da == db || std::includes(da.begin(), da.end(), db.begin(), db.end())) return 0.0;
+    double bytes = 0;
+    for (auto &e : g.node(b).inputs) if (e.src.node == a) bytes += (double)g.shape(e.src).piece_bytes();
+    return est.movement_cost_ms(bytes, da.front() / m.num_gpus_per_node != db.front() / m.num_gpus_per_node);
+  };
+  for (NodeId n : order) {
+    double ready = 0;
+    for (auto &e : g.node(n).inputs) ready = std::max(ready, finish[e.src.node] + comm(e.src.node, n));
+    finish[n] = run(n, ready, est.op_cost(g.node(n), g).fwd_ms);
+  }
+  double makespan = 0;
+  for (auto &kv : finish) makespan = std::max(makespan, kv.second);
+  if (!include_backward) return makespan;
+  std::map<NodeId, double> bfinish;
+  for (auto it = order.rbegin(); it != order.rend(); ++it) {
+    NodeId n = *it;
+    double ready = makespan;
+    for (NodeId s : g.successors(n)) ready = std::max(ready, bfinish[s] + comm(n, s));
+    bfinish[n] = run(n, ready, est.op_cost(g.node(n), g).bwd_ms);
+  }
+  double total = makespan;
+  for (auto &kv : bfinish) total = std::max(total, kv.second);
+  return total;
+}
+
+// ---------------------------------------------------------------- MCMC
+SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
+                         const MCMCConfig &cfg) {
+  std::mt19937 rng(cfg.seed);
+  std::uniform_real_distribution<double> uni(0.0, 1.0);
+  auto random_views = [&](const Graph &g) {
+    std::map<NodeId, MachineView> mv;
+    for (auto &kv : g.nodes()) {
+      auto vs = allowed_machine_views(operator_task_space(kv.second, g), Resources{0, m.num_devices()}, m);
+      if (vs.empty()) continue;
+      mv[kv.first] = vs[rng() % vs.size()];
+    }
+    return mv;
+  };
+  auto score = [&](const Graph &g, const std::map<NodeId, MachineView> &mv) {
+    return simulate_task_graph(mapped_pcg_from_pcg_and_mapping(g, mv), m, est, true);
+  };
+  Graph cur = start;
+  auto cur_map = random_views(cur);
+  double cur_cost = score(cur, cur_map);
+  SearchResult best;
+  best.pcg = cur;
+  best.mapping = cur_map;
+  best.runtime_ms = cur_cost;
+  int accepted = 0, substitutions = 0;
+  for (int it = 0; it < cfg.num_iterations; ++it) {
+    Graph cand = cur;
+    auto cand_map = cur_map;
+    bool changed = false;
+    if (uni(rng) < cfg.substitution_frequency && !rules.empty()) {
+      // a random rule at a random match; new layers take a random allowed view
+      for (int attempt = 0; attempt < 8 && !changed; ++attempt) {
+        const Substitution &rule = rules[rng() % rules.size()];
+        auto ms = find_pattern_matches(rule.pattern, cur);
+        if (ms.empty()) continue;
+        auto ng = apply_substitution(cur, rule, ms[rng() % ms.size()]);
+        if (!ng) continue;
+        cand = *ng;
+        for (auto &kv : cand.nodes())
+          if (!cand_map.count(kv.first)) {
+            auto vs = allowed_machine_views(operator_task_space(kv.second, cand), Resources{0, m.num_devices()}, m);
+            if (!vs.empty()) cand_map[kv.first] = vs[rng() % vs.size()];
+          }
+        for (auto itv = cand_map.begin(); itv != cand_map.end();)
+          itv = cand.has_node(itv->first) ? std::next(itv) : cand_map.erase(itv);
+        changed = true;
+        ++substitutions;
+      }
+    }
+    if (!changed) {
+      // mutate the view of one layer
+      auto ids = cand.node_ids();
+      NodeId n = ids[rng() % ids.size()];
+      auto vs = allowed_machine_views(operator_task_space(cand.node(n), cand), Resources{0, m.num_devices()}, m);
+      if (vs.empty()) continue;
+      cand_map[n] = vs[rng() % vs.size()];
+    }
+    double c = score(cand, cand_map);
+    double accept_p = c <= cur_cost ? 1.0 : std::exp(-(c - cur_cost) / std::max(1e-9, cfg.temperature));
+    if (uni(rng) < accept_p) {
+      cur = cand;
+      cur_map = cand_map;
+      cur_cost = c;
+      ++accepted;
+      if (c < best.runtime_ms) {
+        best.pcg = cur;
+        best.mapping = cur_map;
+        best.runtime_ms = c;
+      }
+    }
+  }
+  best.stats = Json::object();
+  best.stats["iterations"] = cfg.num_iterations;
+  best.stats["accepted"] = accepted;
+  best.stats["substitutions"] = substitutions;
+  return best;
+}
+
+// ---------------------------------------------------------------- python bindings
+static py::dict result_to_py(const SearchResult &r) {
+  py::dict d;
+  d["pcg"] = r.pcg;
+  d["mapped_pcg"] = mapped_pcg_from_pcg_and_mapping(r.pcg, r.mapping);
+  py::dict mv;
+  for (auto &kv : r.mapping) mv[py::int_(kv.first)] = json_to_py(kv.second.to_json());
+  d["mapping"] = mv;
+  d["runtime_ms"] = r.runtime_ms;
+  d["memory_bytes"] = r.memory_bytes;
+  d["stats"] = json_to_py(r.stats);
+  return d;
+}
+
+void bind_search(py::module &m) {
+  py::class_<CostEstimator>(m, "CostEstimator")
+      .def(py::init([](const MachineSpec &ms, py::object params) {
+             CostParams p = params.is_none() ? CostParams() : CostParams::from_json(json_from_py(params));
+             p.nvlink_gbs = params.is_none() ? ms.intra_node_bandwidth : p.nvlink_gbs;
+             return CostEstimator(p, ms);
+           }),
+           py::arg("machine"), py::arg("params") = py::none())
+      .def("params", [](const CostEstimator &e) { return json_to_py(e.params.to_json()); })
+      .def("op_cost", [](const CostEstimator &e, const Graph &g, NodeId n) {
+        OpCost c = e.op_cost(g.node(n), g);
+        py::dict d;
+        d["fwd_ms"] = c.fwd_ms; d["bwd_ms"] = c.bwd_ms; d["memory_bytes"] = c.memory_bytes;
+        return d;
+      })
+      .def("op_cost_key", [](const CostEstimator &, const Graph &g, NodeId n) { return CostEstimator::op_cost_key(g.node(n), g); })
+      .def("set_measured", [](CostEstimator &e, const std::string &key, double fwd, double bwd, double mem) { e.measured[key] = OpCost{fwd, bwd, mem}; })
+      .def("num_measured", [](const CostEstimator &e) { return e.measured.size(); })
+      .def("movement_cost_ms", &CostEstimator::movement_cost_ms)
+      .def_readonly("num_queries", &CostEstimator::num_queries);
+  m.def("allowed_machine_views", [](std::vector<int> task, int start, int count, const MachineSpec &ms) {
+    py::list l;
+    for (auto &v : allowed_machine_views(task, Resources{start, count}, ms)) l.append(json_to_py(v.to_json()));
+    return l;
+  });
+  m.def("view_devices", [](py::object view, std::vector<int> task, const MachineSpec &ms) {
+    return view_devices(MachineView::from_json(json_from_py(view)), task, ms);
+  });
+  m.def("get_graph_sp_decomposition", [](const Graph &g) {
+    bool exact = true;
+    SPTree t = get_graph_sp_decomposition(g, &exact);
+    return py::make_tuple(sp_to_py(t), exact);
+  });
+  m.def("get_optimal_machine_mapping", [](const Graph &g, py::object tree, const MachineSpec &ms, const CostEstimator &est, int max_front) {
+    SPTree t = tree.is_none() ? balanced_binary_sp_tree(get_graph_sp_decomposition(g)) : sp_from_py(tree);
+    auto r = get_optimal_machine_mapping(g, t, ms, est, max_front);
+    py::list pts;
+    for (auto &p : r.front) {
+      py::dict d;
+      d["runtime_ms"] = p.runtime_ms;
+      d["memory_bytes"] = p.memory_bytes;
+      py::dict mv;
+      for (auto &kv : p.views) mv[py::int_(kv.first)] = json_to_py(kv.second.to_json());
+      d["views"] = mv;
+      pts.append(d);
+    }
+    return pts;
+  }, py::arg("pcg"), py::arg("tree") = py::none(), py::arg("machine") = MachineSpec(), py::arg("estimator") = CostEstimator(),
+        py::arg("max_front") = 1);
+  m.def("evaluate_pcg", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est) { return result_to_py(evaluate_pcg(g, ms, est)); });
+  m.def("apply_rules_exhaustively", [](const Graph &g, std::vector<Substitution> rules, int max_app, int max_deg) {
+    return apply_rules_exhaustively(g, rules, max_app, max_deg);
+  }, py::arg("graph"), py::arg("rules"), py::arg("max_applications") = 100000, py::arg("max_total_degree") = 0);
+  m.def("unity_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double alpha,
+                           int budget, int max_num_ops, double time_limit_s) {
+    UnityConfig c;
+    c.alpha = alpha; c.budget = budget; c.max_num_ops = max_num_ops; c.time_limit_s = time_limit_s;
+    py::gil_scoped_release rel;
+    SearchResult r = unity_search(g, ms, est, rules, c);
+    py::gil_scoped_acquire acq;
+    return result_to_py(r);
+  }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("alpha") = 1.05, py::arg("budget") = 10,
+        py::arg("max_num_ops") = 100000, py::arg("time_limit_s") = 120.0);
+  m.def("mcmc_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double temperature,
+                          int iters, double sub_freq, unsigned seed) {
+    MCMCConfig c;
+    c.temperature = temperature; c.num_iterations = iters; c.substitution_frequency = sub_freq; c.seed = seed;
+    return result_to_py(mcmc_search(g, ms, est, rules, c));
+  }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("temperature") = 1.0, py::arg("num_iterations") = 100,
+        py::arg("substitution_frequency") = 0.2, py::arg("seed") = 0);
+  m.def("simulate_task_graph", &simulate_task_graph, py::arg("mapped_pcg"), py::arg("machine"), py::arg("estimator"),
+        py::arg("include_backward") = false);
+  m.def("mapped_pcg_from_pcg_and_mapping", [](const Graph &g, py::dict mapping) {
+    std::map<NodeId, MachineView> mv;
+    for (auto kv : mapping) mv[kv.first.cast<int>()] = MachineView::from_json(json_from_py(kv.second));
+    return mapped_pcg_from_pcg_and_mapping(g, mv);
+  });
+}
+
+}  // namespace ff

@@ -1,0 +1,124 @@
+// search.h -- strategy search: cost model, machine views, machine-mapping DP (with a runtime/memory Pareto
+// variant), Unity best-first search over substitutions, MCMC search and the task-graph simulator.
+//
+// Reference counterparts: lib/compiler/src/compiler/machine_mapping/get_optimal_machine_mapping.cc:36-294,
+// memory_optimization/get_optimal_machine_mapping_with_memory.cc, allowed_machine_views.cc:51-162,
+// unity_algorithm/unity_algorithm.cc:51-146, mcmc/mcmc_over_mapped_pcg.cc:18-66,
+// task_graph_simulator/task_simulator.cc:23-75, cost_estimator/cost_estimator.h:14-41.
+#pragma once
+#include <map>
+#include <memory>
+#include <optional>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "graph_algos.h"
+#include "ir.h"
+#include "substitutions.h"
+
+namespace ff {
+
+struct OpCost {
+  double fwd_ms = 0, bwd_ms = 0;
+  double memory_bytes = 0;  // per device
+  double total_ms() const { return fwd_ms + bwd_ms; }
+};
+
+// Hardware constants of the analytical model.  Defaults are measurements of one B200 of an 8-GPU NVSwitch
+// box: bf16 GEMM throughput sustained under the power cap, stream-copy HBM bandwidth, peer-copy NVLink
+// bandwidth per direction and the 8-rank all-reduce bus bandwidth.
+struct CostParams {
+  double matmul_tflops = 1400.0;
+  double matmul_efficiency = 0.8;   // fraction of the above a real GEMM kernel reaches
+  double hbm_gbs = 6450.0;
+  double nvlink_gbs = 770.0;
+  double allreduce_bus_gbs = 725.0;
+  double launch_us = 4.0;
+  double collective_latency_us = 12.0;
+  double inter_node_gbs = 25.0;
+  double fused_overlap = 0.85;      // fraction of a collective hidden when it is fused with its GEMM
+  int bytes_per_float = 2;          // activations/weights are bf16 at run time
+  Json to_json() const;
+  static CostParams from_json(const Json &);
+};
+
+class CostEstimator {
+public:
+  explicit CostEstimator(CostParams p = CostParams(), MachineSpec m = MachineSpec()) : params(p), machine(m) {}
+  virtual ~CostEstimator() = default;
+  CostParams params;
+  MachineSpec machine;
+  // measured costs override the analytical model; key = op_cost_key(node, graph)
+  std::map<std::string, OpCost> measured;
+  virtual OpCost op_cost(const Node &n, const Graph &g) const;
+  // cost of moving `bytes` between two (different) device sets of the same node / across nodes
+  virtual double movement_cost_ms(double bytes, bool inter_node) const;
+  static std::string op_cost_key(const Node &n, const Graph &g);
+  long long num_queries = 0;
+};
+
+// contiguous, start-aligned machine views of an operator with `task_degrees` on `resources`
+struct Resources {
+  int start = 0;
+  int count = 1;
+  bool operator<(const Resources &o) const { return std::tie(start, count) < std::tie(o.start, o.count); }
+};
+std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m);
+std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task_degrees, const MachineSpec &m);
+
+struct MappingPoint {
+  double runtime_ms = 0;
+  double memory_bytes = 0;
+  std::map<NodeId, MachineView> views;
+};
+struct MachineMappingResult {
+  std::vector<MappingPoint> front;  // Pareto front (size 1 when memory is not tracked); empty = infeasible
+  bool feasible() const { return !front.empty(); }
+  const MappingPoint &best_runtime() const;
+};
+
+// SP decomposition of a (parallel) computation graph with the weight/input pre-processing of the reference
+// (get_pcg_series_parallel_decomposition.cc:12-78); falls back to SP-ization when the graph is not SP.
+SPTree get_graph_sp_decomposition(const Graph &g, bool *exact = nullptr);
+
+MachineMappingResult get_optimal_machine_mapping(const Graph &pcg, const SPTree &binary_tree, const MachineSpec &m,
+                                                 const CostEstimator &est, int max_front = 1);
+
+struct SearchResult {
+  Graph pcg;
+  std::map<NodeId, MachineView> mapping;
+  double runtime_ms = 0;
+  double memory_bytes = 0;
+  Json stats;
+};
+Graph mapped_pcg_from_pcg_and_mapping(const Graph &pcg, const std::map<NodeId, MachineView> &mapping);
+
+struct UnityConfig {
+  double alpha = 1.05;
+  int budget = 10;
+  int max_num_ops = 100000;
+  int max_candidates_per_step = 4000;
+  double time_limit_s = 120.0;
+};
+SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est);
+SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
+                          const UnityConfig &cfg);
+// apply every rule whose name passes `filter` wherever it matches, repeatedly, until nothing applies
+Graph apply_rules_exhaustively(const Graph &g, const std::vector<Substitution> &rules, int max_applications = 100000,
+                               int max_total_degree = 0);
+
+struct MCMCConfig {
+  double temperature = 1.0;
+  int num_iterations = 100;
+  double substitution_frequency = 0.2;
+  unsigned seed = 0;
+};
+SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
+                         const MCMCConfig &cfg);
+
+// Event-driven simulation of a mapped PCG: operator tasks occupy their devices exclusively, communication
+// tasks run unconstrained.  include_backward also schedules the mirrored backward tasks and the weight updates.
+double simulate_task_graph(const Graph &mapped_pcg, const MachineSpec &m, const CostEstimator &est, bool include_backward = false);
+
+}  // namespace ff

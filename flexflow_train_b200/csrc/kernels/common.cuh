@@ -91,6 +91,24 @@ __device__ __forceinline__ uint32_t ffk_hash_rng(uint64_t seed, uint64_t idx) {
 __device__ __forceinline__ float ffk_uniform01(uint64_t seed, uint64_t idx) {
   return (ffk_hash_rng(seed, idx) >> 8) * (1.0f / 16777216.0f);
 }
+// Dropout masks draw 16 random bits per element, four elements per 64-bit hash: element i uses bits
+// [16*(i&3), +16) of hash(seed, i>>2) and is kept when they are >= p * 65536.
+__device__ __forceinline__ uint64_t ffk_rand16x4(uint64_t seed, uint64_t group) {
+  uint64_t z = group * 0x9E3779B97F4A7C15ull + seed;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ uint32_t ffk_drop_threshold(float p) { return (uint32_t)(p * 65536.0f); }
+__device__ __forceinline__ bool ffk_keep(uint64_t seed, uint64_t idx, uint32_t thr) {
+  return ((ffk_rand16x4(seed, idx >> 2) >> (16 * (idx & 3))) & 0xFFFFu) >= thr;
+}
+// keep flags of the aligned group of four elements starting at idx4*4, one per bit of the result
+__device__ __forceinline__ uint32_t ffk_keep4(uint64_t seed, uint64_t idx4, uint32_t thr) {
+  uint64_t z = ffk_rand16x4(seed, idx4);
+  return ((uint32_t)(z & 0xFFFFu) >= thr ? 1u : 0u) | ((uint32_t)((z >> 16) & 0xFFFFu) >= thr ? 2u : 0u) |
+         ((uint32_t)((z >> 32) & 0xFFFFu) >= thr ? 4u : 0u) | ((uint32_t)(z >> 48) >= thr ? 8u : 0u);
+}
 
 static inline int ffk_blocks(long long n, int per_block, int max_blocks = 148 * 16) {
   long long b = (n + per_block - 1) / per_block;

@@ -5,6 +5,7 @@
 // element_binary_kernels.cu:27-412, dropout_kernels.cu:73-89, cast_kernels.cu:25-32,
 // cuda_helper.cu:145-195) without any cuDNN call.
 #include "common.cuh"
+#include "rowwise_vec.cuh"
 
 namespace {
 
@@ -197,23 +198,28 @@ __global__ void binary_bwd_kernel(int op, const T *__restrict__ a, const T *__re
 // y = dropout(x) [+ r]; the keep mask is a pure function of (seed, index).
 template <typename T>
 __global__ void dropout_kernel(const T *__restrict__ x, const T *__restrict__ r, T *__restrict__ y, long long n,
-                               float p, float scale, unsigned long long seed) {
+                               float p, float scale, unsigned long long seed, const unsigned long long *seed_ptr) {
+  // seed_ptr (optional) points at a per-step seed in device memory, so a captured CUDA graph draws a new
+  // mask on every replay; `seed` then acts as the per-operator salt.
+  if (seed_ptr) seed = seed * 0x9E3779B97F4A7C15ull + *seed_ptr;
   constexpr int N = V16<T>::N;
   long long nv = n / N;
   long long stride = (long long)gridDim.x * blockDim.x;
+  const uint32_t thr = ffk_drop_threshold(p);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
     float v[N], rv[N];
     V16<T>::load(x + i * N, v);
     if (r) V16<T>::load(r + i * N, rv);
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-      float keep = ffk_uniform01(seed, (unsigned long long)(i * N + j)) >= p ? scale : 0.f;
-      v[j] = v[j] * keep + (r ? rv[j] : 0.f);
+    for (int g4 = 0; g4 < N / 4; ++g4) {
+      uint32_t keep = ffk_keep4(seed, (unsigned long long)(i * (N / 4) + g4), thr);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[g4 * 4 + j] = ((keep >> j) & 1u ? v[g4 * 4 + j] * scale : 0.f) + (r ? rv[g4 * 4 + j] : 0.f);
     }
     V16<T>::store(y + i * N, v);
   }
   for (long long i = nv * N + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    float keep = ffk_uniform01(seed, (unsigned long long)i) >= p ? scale : 0.f;
+    float keep = ffk_keep(seed, (unsigned long long)i, thr) ? scale : 0.f;
     V16<T>::st1(y + i, V16<T>::ld1(x + i) * keep + (r ? V16<T>::ld1(r + i) : 0.f));
   }
 }
@@ -355,12 +361,12 @@ FFK_API int ffk_binary_bwd(int op, const void *a, const void *b, const void *dy,
   return (int)cudaGetLastError();
 }
 // y = dropout(x, p; seed) + r   (r optional).  Backward is the same call on dy with r = null.
-FFK_API int ffk_dropout(const void *x, const void *r, void *y, long long n, float p, unsigned long long seed, int dt,
-                        cudaStream_t st) {
+FFK_API int ffk_dropout(const void *x, const void *r, void *y, long long n, float p, unsigned long long seed,
+                        const unsigned long long *seed_ptr, int dt, cudaStream_t st) {
   if (n <= 0) return 0;
   float scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
   DISPATCH_FLOAT(dt, (dropout_kernel<T><<<ffk_blocks(n / V16<T>::N + 1, 256), 256, 0, st>>>(
-                         (const T *)x, (const T *)r, (T *)y, n, p, scale, seed)));
+                         (const T *)x, (const T *)r, (T *)y, n, p, scale, seed, seed_ptr)));
   return (int)cudaGetLastError();
 }
 // y = a*x + b*y
@@ -393,6 +399,13 @@ FFK_API int ffk_bias_act_bwd(const void *dy, const void *saved, void *dz, void *
                              int cols, int act, int dt, int accumulate, cudaStream_t st) {
   if (rows <= 0 || cols <= 0) return 0;
   int gy = rows / 64; if (gy < 1) gy = 1; if (gy > 64) gy = 64;
+  if (dt == DT_BF16 && cols % 8 == 0 && (((uintptr_t)dy | (uintptr_t)saved | (uintptr_t)dz) & 15) == 0) {
+    dim3 vgrid((cols + 255) / 256, gy), vblock(32, 8);
+    vec::bias_act_bwd_vec_kernel<<<vgrid, vblock, 0, st>>>((const bf16 *)dy, (const bf16 *)saved, (bf16 *)dz, dbias ? partial : nullptr, rows,
+                                                          cols, act);
+    if (dbias) colsum_finish_kernel<bf16><<<(cols + 255) / 256, 256, 0, st>>>(partial, gy, cols, (bf16 *)dbias, accumulate);
+    return (int)cudaGetLastError();
+  }
   dim3 grid((cols + 31) / 32, gy), block(32, 8);
   DISPATCH_FLOAT(dt, {
     bias_act_bwd_kernel<T><<<grid, block, 0, st>>>((const T *)dy, (const T *)saved, (T *)dz, dbias ? partial : nullptr,

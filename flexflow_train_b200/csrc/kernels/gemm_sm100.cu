@@ -15,8 +15,8 @@
 // without a transpose pass.  Two batch dimensions (inner `nh`, outer `nb`)
 // with independent strides cover attention's [batch, seq, head, dim] views.
 //
-// CTA layout (192 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and
-// issues tcgen05.mma from one thread, warps 2..5 are the epilogue (TMEM ->
+// CTA layout (320 threads): warp 0 issues TMA loads, warp 1 allocates TMEM and
+// issues tcgen05.mma from one thread, warps 2..9 are the epilogue (TMEM ->
 // registers -> bias/activation/addend -> global).  Two TMEM accumulator stages
 // let the epilogue of tile i overlap the main loop of tile i+1.
 //
@@ -28,7 +28,7 @@
 namespace {
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 struct GemmArgs {
@@ -37,13 +37,14 @@ struct GemmArgs {
   void *C;
   long long ldc, c_sh, c_sb;
   void *C2;  // optional second output: pre-activation value, bf16, same layout as C
-  const bf16 *bias;    // [N] or null
-  const bf16 *addend;  // optional, added after activation (residual), layout of C (bf16)
+  const void *bias;    // [N] or null
+  const void *addend;  // optional, added after activation (residual), layout of C
   long long ld_add, add_sh, add_sb;
   float alpha;
   int act;
   int out_fp32;    // C is float instead of bf16
   int accumulate;  // C += result
+  int aux_fp32;    // bias / addend / C2 are float (fp32 activations) instead of bf16
   int tiles_m, tiles_n;
   long long num_tiles;
   int *err;
@@ -173,7 +174,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (STAGE_BYTES <= 32768) ? 6 : (STAGE_BYTES <= 49152 ? 4 : 3);
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 8 * 32 * 32 * 4 /*epilogue staging*/;
   // K-major: one 8-row group is 8*128 B apart (SBO), LBO is the fixed 16 B.
   // MN-major: 8 k-rows of one 64-wide chunk are 128 B apart, 8-row groups are
   // 1024 B apart (SBO) and the next MN chunk starts BK*128 B later (LBO).
@@ -189,6 +190,13 @@ struct GemmCfg {
                                     | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
 
+__device__ __forceinline__ float ld_aux(const void *p, long long i, int fp32) {
+  return fp32 ? ((const float *)p)[i] : bf2f(((const bf16 *)p)[i]);
+}
+__device__ __forceinline__ void st_aux(void *p, long long i, int fp32, float v) {
+  if (fp32) ((float *)p)[i] = v;
+  else ((bf16 *)p)[i] = f2bf(v);
+}
 __device__ __forceinline__ void tile_coords(long long tile, const GemmArgs &p, int &mb, int &nb_, int &bh, int &bb) {
   long long per_batch = (long long)p.tiles_m * p.tiles_n;
   long long batch = tile / per_batch;
@@ -223,6 +231,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
   uint64_t *tmem_empty = bars + 2 * STAGES + 2;  // [2]
   uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  float *epi_stage = (float *)(smem + STAGES * Cfg::STAGE_BYTES + 256);  // 8 epilogue warps x 32x32 fp32
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -235,7 +244,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tmem_full[s], 1);
-      mbar_init(&tmem_empty[s], 4);
+      mbar_init(&tmem_empty[s], 8);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -328,8 +337,25 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int row_in_tile = q * 32 + lane;
+    // Eight warps: warp w reads TMEM lane quarter (w & 3) -- the hardware ties a warp to the lanes
+    // 32*(warp%4)..+31 -- and column half (w - 2) / 4 of the accumulator.  The epilogue of a tile must fit
+    // under the main loop of the next one, and with so few warps per SM it is bound by instruction latency,
+    // not bandwidth: the common case (bf16 output, bias + ReLU/none) therefore takes a branch-free path with
+    // all address arithmetic hoisted out of the inner loops.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HALF_COLS = BN / 2;
+    const int unit = lane & 7;
+    const int rsub = lane >> 3;
+    float *stg = epi_stage + (warp - 2) * (32 * 32);
+    // staging offsets: write = my row, 8 units; read = rows rsub, rsub+4, ... of unit `unit`
+    const uint32_t wr_base = smem_u32(stg + lane * 32);
+    const uint32_t rd_even = smem_u32(stg + rsub * 32 + ((unit ^ rsub) << 2));            // rows with (rr & 7) == rsub
+    const uint32_t rd_odd = smem_u32(stg + (rsub + 4) * 32 + ((unit ^ (rsub + 4)) << 2));  // rows with (rr & 7) == rsub + 4
+    const bool simple = !p.out_fp32 && !p.accumulate && !p.C2 && !p.addend && !p.aux_fp32 &&
+                        (p.act == ACT_NONE || p.act == ACT_RELU) && (p.ldc % 4 == 0) && (((uintptr_t)p.C) & 7) == 0 &&
+                        (p.c_sh % 4 == 0) && (p.c_sb % 4 == 0);
+    const float relu_floor = p.act == ACT_RELU ? 0.f : -INFINITY;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -340,97 +366,110 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = mb * BM + row_in_tile;
-      const bool row_ok = row < p.M;
-      const long long coff = (long long)bh * p.c_sh + (long long)bb * p.c_sb + (long long)row * p.ldc;
-      const long long aoff = (long long)bh * p.add_sh + (long long)bb * p.add_sb + (long long)row * p.ld_add;
+      const long long c_base = (long long)bh * p.c_sh + (long long)bb * p.c_sb;
+      const long long a_base = (long long)bh * p.add_sh + (long long)bb * p.add_sb;
+      const int row0 = mb * BM + q * 32;          // first row of this warp's quarter
+      const int rows_left = p.M - row0 - rsub;     // iteration i is valid iff 4*i < rows_left
+      const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * HALF_COLS);
+      uint32_t r[32];
+      tmem_ld32(t_base, r);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0);
-        tmem_ld32(taddr, r);
+      for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
         tmem_ld_wait();
-        const int col0 = nb_ * BN + c0;
-        if (row_ok && col0 < p.N) {
-          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-          const bool full = (col0 + 32 <= p.N);
-          if (p.bias) {
+        for (int u = 0; u < 8; ++u)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wr_base + (uint32_t)(((u ^ (lane & 7)) << 4))), "r"(r[4 * u]),
+                       "r"(r[4 * u + 1]), "r"(r[4 * u + 2]), "r"(r[4 * u + 3])
+                       : "memory");
+        __syncwarp();
+        if (c0 + 32 < HALF_COLS) tmem_ld32(t_base + (uint32_t)(c0 + 32), r);  // overlaps the stores below
+        const int col = nb_ * BN + half * HALF_COLS + c0 + unit * 4;
+        const bool col_ok = col < p.N;
+        const bool vec4 = col + 4 <= p.N;
+        float b4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.bias && col_ok) {
+          if (vec4 && !p.aux_fp32 && ((((uintptr_t)p.bias) & 7) == 0)) {
+            uint2 u = *reinterpret_cast<const uint2 *>((const bf16 *)p.bias + col);
+            float2 x0 = unpack_bf162(u.x), x1 = unpack_bf162(u.y);
+            b4[0] = x0.x; b4[1] = x0.y; b4[2] = x1.x; b4[3] = x1.y;
+          } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < p.N) v[j] += bf2f(p.bias[col0 + j]);
+            for (int j = 0; j < 4; ++j)
+              if (col + j < p.N) b4[j] = ld_aux(p.bias, col + j, p.aux_fp32);
           }
-          if (p.C2) {
-            bf16 *c2 = (bf16 *)p.C2 + coff + col0;
-            if (full && ((((uintptr_t)c2) & 15) == 0)) {
+        }
+        if (simple && vec4) {
+          bf16 *cp = (bf16 *)p.C + c_base + (long long)(row0 + rsub) * p.ldc + col;
+          const long long step = 4 * p.ldc;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 u = make_uint4(pack_bf162(v[j], v[j + 1]), pack_bf162(v[j + 2], v[j + 3]),
-                                     pack_bf162(v[j + 4], v[j + 5]), pack_bf162(v[j + 6], v[j + 7]));
-                *reinterpret_cast<uint4 *>(c2 + j) = u;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) c2[j] = f2bf(v[j]);
+          for (int i = 0; i < 8; ++i) {
+            float4 f;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w)
+                         : "r"(((i & 1) ? rd_odd : rd_even) + (uint32_t)((i >> 1) * 8 * 32 * 4)));
+            if (4 * i < rows_left) {
+              float v0 = fmaxf(fmaf(f.x, p.alpha, b4[0]), relu_floor), v1 = fmaxf(fmaf(f.y, p.alpha, b4[1]), relu_floor);
+              float v2 = fmaxf(fmaf(f.z, p.alpha, b4[2]), relu_floor), v3 = fmaxf(fmaf(f.w, p.alpha, b4[3]), relu_floor);
+              *reinterpret_cast<uint2 *>(cp) = make_uint2(pack_bf162(v0, v1), pack_bf162(v2, v3));
             }
+            cp += step;
           }
-          if (p.act != ACT_NONE) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = act_fwd(v[j], p.act);
-          }
-          if (p.addend) {
-            const bf16 *ad = p.addend + aoff + col0;
-            if (full && ((((uintptr_t)ad) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 u = *reinterpret_cast<const uint4 *>(ad + j);
-                float2 f0 = unpack_bf162(u.x), f1 = unpack_bf162(u.y), f2 = unpack_bf162(u.z), f3 = unpack_bf162(u.w);
-                v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
-                v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) v[j] += bf2f(ad[j]);
+        } else {
+#pragma unroll 1
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + rsub;
+            const int row = row0 + rr;
+            float4 f = *reinterpret_cast<const float4 *>(stg + rr * 32 + ((unit ^ (rr & 7)) << 2));
+            if (row >= p.M || !col_ok) continue;
+            float v[4] = {f.x * p.alpha + b4[0], f.y * p.alpha + b4[1], f.z * p.alpha + b4[2], f.w * p.alpha + b4[3]};
+            const long long coff = c_base + (long long)row * p.ldc + col;
+            if (p.C2) {
+              if (!p.aux_fp32 && vec4 && (((uintptr_t)((bf16 *)p.C2 + coff)) & 7) == 0)
+                *reinterpret_cast<uint2 *>((bf16 *)p.C2 + coff) = make_uint2(pack_bf162(v[0], v[1]), pack_bf162(v[2], v[3]));
+              else
+                for (int j = 0; j < 4; ++j) if (col + j < p.N) st_aux(p.C2, coff + j, p.aux_fp32, v[j]);
             }
-          }
-          if (p.out_fp32) {
-            float *c = (float *)p.C + coff + col0;
-            if (full && ((((uintptr_t)c) & 15) == 0)) {
+            if (p.act != ACT_NONE) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              for (int j = 0; j < 4; ++j) v[j] = act_fwd(v[j], p.act);
+            }
+            if (p.addend) {
+              const long long aoff = a_base + (long long)row * p.ld_add + col;
+              if (!p.aux_fp32 && vec4 && (((uintptr_t)((const bf16 *)p.addend + aoff)) & 7) == 0) {
+                uint2 u = *reinterpret_cast<const uint2 *>((const bf16 *)p.addend + aoff);
+                float2 a0 = unpack_bf162(u.x), a1 = unpack_bf162(u.y);
+                v[0] += a0.x; v[1] += a0.y; v[2] += a1.x; v[3] += a1.y;
+              } else {
+                for (int j = 0; j < 4; ++j) if (col + j < p.N) v[j] += ld_aux(p.addend, aoff + j, p.aux_fp32);
+              }
+            }
+            if (p.out_fp32) {
+              float *c = (float *)p.C + coff;
+              if (vec4 && (((uintptr_t)c) & 15) == 0) {
+                float4 o = make_float4(v[0], v[1], v[2], v[3]);
                 if (p.accumulate) {
-                  float4 old = *reinterpret_cast<float4 *>(c + j);
+                  float4 old = *reinterpret_cast<float4 *>(c);
                   o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                 }
-                *reinterpret_cast<float4 *>(c + j) = o;
+                *reinterpret_cast<float4 *>(c) = o;
+              } else {
+                for (int j = 0; j < 4; ++j) if (col + j < p.N) c[j] = p.accumulate ? c[j] + v[j] : v[j];
               }
             } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) c[j] = p.accumulate ? c[j] + v[j] : v[j];
-            }
-          } else {
-            bf16 *c = (bf16 *)p.C + coff + col0;
-            if (full && ((((uintptr_t)c) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
+              bf16 *c = (bf16 *)p.C + coff;
+              if (vec4 && (((uintptr_t)c) & 7) == 0) {
                 if (p.accumulate) {
-                  uint4 u = *reinterpret_cast<uint4 *>(c + j);
-                  float2 f0 = unpack_bf162(u.x), f1 = unpack_bf162(u.y), f2 = unpack_bf162(u.z), f3 = unpack_bf162(u.w);
-                  v[j] += f0.x; v[j + 1] += f0.y; v[j + 2] += f1.x; v[j + 3] += f1.y;
-                  v[j + 4] += f2.x; v[j + 5] += f2.y; v[j + 6] += f3.x; v[j + 7] += f3.y;
+                  uint2 u = *reinterpret_cast<uint2 *>(c);
+                  float2 o0 = unpack_bf162(u.x), o1 = unpack_bf162(u.y);
+                  v[0] += o0.x; v[1] += o0.y; v[2] += o1.x; v[3] += o1.y;
                 }
-                uint4 o = make_uint4(pack_bf162(v[j], v[j + 1]), pack_bf162(v[j + 2], v[j + 3]),
-                                     pack_bf162(v[j + 4], v[j + 5]), pack_bf162(v[j + 6], v[j + 7]));
-                *reinterpret_cast<uint4 *>(c + j) = o;
+                *reinterpret_cast<uint2 *>(c) = make_uint2(pack_bf162(v[0], v[1]), pack_bf162(v[2], v[3]));
+              } else {
+                for (int j = 0; j < 4; ++j) if (col + j < p.N) c[j] = f2bf(p.accumulate ? bf2f(c[j]) + v[j] : v[j]);
               }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) c[j] = f2bf(p.accumulate ? bf2f(c[j]) + v[j] : v[j]);
             }
           }
         }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -445,6 +484,51 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
                  : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------
+// General-shape fallback.  TMA needs 16-byte aligned bases and row pitches; operands that cannot offer
+// that (a 10-class classifier head, odd feature counts) take this plain shared-memory-tiled kernel.
+// Same semantics and epilogue as the tensor-core kernel; it is not a hot path.
+// ----------------------------------------------------------------------------
+struct SimtOperands {
+  const void *A, *B;
+  long long lda, a_sh, a_sb, ldb, b_sh, b_sb;
+  int a_mn, b_mn;
+};
+template <typename T>
+__global__ void gemm_simt_kernel(SimtOperands o, GemmArgs p) {
+  __shared__ float sa[16][17], sb[16][17];
+  const int batch = blockIdx.z, bh = batch % p.nh, bb = batch / p.nh;
+  const T *A = (const T *)o.A + (long long)bh * o.a_sh + (long long)bb * o.a_sb;
+  const T *B = (const T *)o.B + (long long)bh * o.b_sh + (long long)bb * o.b_sb;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int m = blockIdx.y * 16 + ty, n = blockIdx.x * 16 + tx;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += 16) {
+    int am = blockIdx.y * 16 + ty, ak = k0 + tx;
+    sa[ty][tx] = (am < p.M && ak < p.K) ? (float)(o.a_mn ? A[(long long)ak * o.lda + am] : A[(long long)am * o.lda + ak]) : 0.f;
+    int bn_ = blockIdx.x * 16 + ty, bk = k0 + tx;
+    sb[ty][tx] = (bn_ < p.N && bk < p.K) ? (float)(o.b_mn ? B[(long long)bk * o.ldb + bn_] : B[(long long)bn_ * o.ldb + bk]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc += sa[ty][k] * sb[tx][k];
+    __syncthreads();
+  }
+  if (m >= p.M || n >= p.N) return;
+  float v = acc * p.alpha;
+  if (p.bias) v += ld_aux(p.bias, n, p.aux_fp32);
+  const long long coff = (long long)bh * p.c_sh + (long long)bb * p.c_sb + (long long)m * p.ldc + n;
+  if (p.C2) st_aux(p.C2, coff, p.aux_fp32, v);
+  v = act_fwd(v, p.act);
+  if (p.addend) v += ld_aux(p.addend, (long long)bh * p.add_sh + (long long)bb * p.add_sb + (long long)m * p.ld_add + n, p.aux_fp32);
+  if (p.out_fp32) {
+    float *c = (float *)p.C + coff;
+    *c = p.accumulate ? *c + v : v;
+  } else {
+    bf16 *c = (bf16 *)p.C + coff;
+    *c = f2bf(p.accumulate ? bf2f(*c) + v : v);
   }
 }
 
@@ -562,11 +646,23 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   const int es = d->es;
   if (es != 2 && es != 4) return -2;
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
-  if (((uintptr_t)d->A & 15) || ((uintptr_t)d->B & 15)) return -2;
-  if ((d->lda * es) % 16 || (d->ldb * es) % 16) return -2;
-  if ((d->nh > 1 && ((d->a_sh * es) % 16 || (d->b_sh * es) % 16)) ||
-      (d->nb > 1 && ((d->a_sb * es) % 16 || (d->b_sb * es) % 16)))
-    return -2;
+  bool tma_ok = !(((uintptr_t)d->A & 15) || ((uintptr_t)d->B & 15)) && !((d->lda * es) % 16 || (d->ldb * es) % 16) &&
+                !((d->nh > 1 && ((d->a_sh * es) % 16 || (d->b_sh * es) % 16)) || (d->nb > 1 && ((d->a_sb * es) % 16 || (d->b_sb * es) % 16))) &&
+                !(es == 4 && (d->a_mn || d->b_mn));  // tf32 operands must be K-major
+  if (!tma_ok) {
+    GemmArgs a;
+    a.M = d->M; a.N = d->N; a.K = d->K; a.nh = d->nh < 1 ? 1 : d->nh; a.nb = d->nb < 1 ? 1 : d->nb;
+    a.C = d->C; a.ldc = d->ldc; a.c_sh = d->c_sh; a.c_sb = d->c_sb;
+    a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
+    a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
+    a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
+    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr;
+    SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
+    dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
+    if (es == 2) gemm_simt_kernel<bf16><<<grid, block, 0, stream>>>(o, a);
+    else gemm_simt_kernel<float><<<grid, block, 0, stream>>>(o, a);
+    return (int)cudaGetLastError();
+  }
   int bn = d->bn;
   if (bn == 0) {
     // Prefer the widest tile that still gives every SM work.
@@ -589,9 +685,9 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   GemmArgs a;
   a.M = d->M; a.N = d->N; a.K = d->K; a.nh = d->nh < 1 ? 1 : d->nh; a.nb = d->nb < 1 ? 1 : d->nb;
   a.C = d->C; a.ldc = d->ldc; a.c_sh = d->c_sh; a.c_sb = d->c_sb;
-  a.C2 = d->C2; a.bias = (const bf16 *)d->bias; a.addend = (const bf16 *)d->addend;
+  a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
   a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
-  a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate;
+  a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_gemm_err);
   a.err = (int *)errp;

@@ -7,6 +7,7 @@
 // All kernels take bf16 or fp32 activations (dt: 0 = fp32, 1 = bf16) and keep
 // statistics in fp32.
 #include "common.cuh"
+#include "rowwise_vec.cuh"
 
 namespace {
 
@@ -64,8 +65,8 @@ __global__ void layernorm_fwd_kernel(const T *__restrict__ a, const T *__restric
 template <typename T, int KMAX>
 __global__ void layernorm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const T *__restrict__ gamma,
                                      const float *__restrict__ mean, const float *__restrict__ rstd,
-                                     T *__restrict__ dx, float *__restrict__ partial, int rows, int cols,
-                                     int accumulate_dx) {
+                                     T *__restrict__ dx, T *__restrict__ dx2, float *__restrict__ partial, int rows,
+                                     int cols, int accumulate_dx, int accumulate_dx2) {
   __shared__ float red[32];
   float dg[KMAX], db[KMAX];
 #pragma unroll
@@ -101,6 +102,10 @@ __global__ void layernorm_bwd_kernel(const T *__restrict__ dy, const T *__restri
         float o = rs * (vg[k] - m1 - vx[k] * m2);
         T *pdx = dx + (long long)row * cols + c;
         stf(pdx, accumulate_dx ? ldf(pdx) + o : o);
+        if (dx2) {  // second consumer of the same gradient (the other operand of a fused residual add)
+          T *pdx2 = dx2 + (long long)row * cols + c;
+          stf(pdx2, accumulate_dx2 ? ldf(pdx2) + o : o);
+        }
       }
     }
   }
@@ -251,10 +256,31 @@ __global__ void loss_fwd_kernel(int kind, const T *__restrict__ pred, const void
   else return -2;
 
 static int rows_grid(int rows) { return rows < 148 * 8 ? rows : 148 * 8; }
+static bool aligned16(const void *p) { return (((uintptr_t)p) & 15) == 0; }
+// vectors per thread for the vectorised LayerNorm kernels: the smallest of 1/2/4 that gives a block of
+// whole warps with at most 512 threads; 0 = not expressible
+static int ln_vpt(int cols) {
+  if (cols % 8) return 0;
+  int nv = cols / 8;
+  for (int v = 1; v <= 4; v *= 2)
+    if (nv % v == 0 && (nv / v) % 32 == 0 && nv / v <= 512) return v;
+  return 0;
+}
+static bool ln_vec_ok(int cols, const void *a, const void *b, const void *c, const void *d, const void *e, const void *f) {
+  return ln_vpt(cols) > 0 && aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d) && aligned16(e) && aligned16(f);
+}
 
 FFK_API int ffk_layernorm_fwd(const void *a, const void *b, const void *gamma, const void *beta, void *xsum, void *y,
                               float *mean, float *rstd, int rows, int cols, float eps, int dt, cudaStream_t st) {
   if (rows <= 0) return 0;
+  if (dt == 1 && ln_vec_ok(cols, a, b, gamma, beta, xsum, y)) {
+    int vpt = ln_vpt(cols), threads = cols / 8 / vpt;
+    const bf16 *A = (const bf16 *)a, *B = (const bf16 *)b, *G = (const bf16 *)gamma, *Bt = (const bf16 *)beta;
+    if (vpt == 1) vec::layernorm_fwd_vec_kernel<1><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);
+    else if (vpt == 2) vec::layernorm_fwd_vec_kernel<2><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);
+    else vec::layernorm_fwd_vec_kernel<4><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);
+    return (int)cudaGetLastError();
+  }
   int threads = cols >= 2048 ? 512 : 256;
   DISPATCH_FLOAT(dt, (layernorm_fwd_kernel<T><<<rows_grid(rows), threads, 0, st>>>(
                          (const T *)a, (const T *)b, (const T *)gamma, (const T *)beta, (T *)xsum, (T *)y, mean, rstd,
@@ -269,22 +295,32 @@ FFK_API long long ffk_layernorm_bwd_scratch(int rows, int cols) { return 2ll * l
 // dx (+)= LN backward; dgamma/dbeta (+)= column sums.  `partial` is scratch of
 // ffk_layernorm_bwd_scratch(rows, cols) floats.  cols <= 16384.
 FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, const float *mean, const float *rstd,
-                              void *dx, void *dgamma, void *dbeta, float *partial, int rows, int cols, int dt,
-                              int accumulate_dx, int accumulate_params, cudaStream_t st) {
+                              void *dx, void *dx2, void *dgamma, void *dbeta, float *partial, int rows, int cols, int dt,
+                              int accumulate_dx, int accumulate_dx2, int accumulate_params, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols > 16384) return -2;
   int grid = ln_bwd_grid(rows);
   float *part = (dgamma || dbeta) ? partial : nullptr;
+  if (dt == 1 && ln_vec_ok(cols, dy, x, gamma, dx, dx2, nullptr)) {
+    int vpt = ln_vpt(cols), threads = cols / 8 / vpt;
+    const bf16 *DY = (const bf16 *)dy, *X = (const bf16 *)x, *G = (const bf16 *)gamma;
+    if (vpt == 1) vec::layernorm_bwd_vec_kernel<1><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
+    else if (vpt == 2) vec::layernorm_bwd_vec_kernel<2><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
+    else vec::layernorm_bwd_vec_kernel<4><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
+    if (part)
+      layernorm_bwd_finish_kernel<bf16><<<(cols + 255) / 256, 256, 0, st>>>(part, grid, cols, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_params);
+    return (int)cudaGetLastError();
+  }
   DISPATCH_FLOAT(dt, {
     if (cols <= 512 * 4)
       layernorm_bwd_kernel<T, 4><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
-                                                        (T *)dx, part, rows, cols, accumulate_dx);
+                                                        (T *)dx, (T *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     else if (cols <= 512 * 16)
       layernorm_bwd_kernel<T, 16><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
-                                                         (T *)dx, part, rows, cols, accumulate_dx);
+                                                         (T *)dx, (T *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     else
       layernorm_bwd_kernel<T, 32><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
-                                                         (T *)dx, part, rows, cols, accumulate_dx);
+                                                         (T *)dx, (T *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     if (part)
       layernorm_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(part, grid, cols, (T *)dgamma, (T *)dbeta,
                                                                           accumulate_params);
@@ -292,9 +328,59 @@ FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, 
   return (int)cudaGetLastError();
 }
 
+template <int VPT>
+static void launch_softmax_fwd_warp(const void *x, void *y, void *yd, int rows, float scale, int causal_q, float p, unsigned long long salt,
+                                    const unsigned long long *seed_ptr, cudaStream_t st) {
+  int blocks = (rows + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  vec::softmax_fwd_warp_kernel<VPT><<<blocks, 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (bf16 *)yd, rows, scale, causal_q, p, salt, seed_ptr);
+}
+template <int VPT>
+static void launch_softmax_bwd_warp(const void *dy, const void *y, void *dx, int rows, float scale, float p, unsigned long long salt,
+                                    const unsigned long long *seed_ptr, cudaStream_t st) {
+  int blocks = (rows + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  vec::softmax_bwd_warp_kernel<VPT><<<blocks, 256, 0, st>>>((const bf16 *)dy, (const bf16 *)y, (bf16 *)dx, rows, scale, p, salt, seed_ptr);
+}
+static bool softmax_vec_ok(int cols, int dt, const void *a, const void *b, const void *c) {
+  return dt == 1 && cols % 256 == 0 && cols <= 4096 && (cols / 256 == 1 || cols / 256 == 2 || cols / 256 == 4 || cols / 256 == 8 || cols / 256 == 16) &&
+         aligned16(a) && aligned16(b) && aligned16(c);
+}
+// y = softmax(scale * x); yd (optional, bf16 rows of 256*k columns only) = dropout(y, p) with the mask
+// hash(salt, *seed_ptr, element index).  Returns -3 when yd is requested for a shape the fused path cannot take.
+FFK_API int ffk_softmax_dropout_fwd(const void *x, void *y, void *yd, int rows, int cols, float scale, int causal_q, float p,
+                                    unsigned long long salt, const unsigned long long *seed_ptr, int dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (!softmax_vec_ok(cols, dt, x, y, yd)) return -3;
+  switch (cols / 256) {
+    case 1: launch_softmax_fwd_warp<1>(x, y, yd, rows, scale, causal_q, p, salt, seed_ptr, st); break;
+    case 2: launch_softmax_fwd_warp<2>(x, y, yd, rows, scale, causal_q, p, salt, seed_ptr, st); break;
+    case 4: launch_softmax_fwd_warp<4>(x, y, yd, rows, scale, causal_q, p, salt, seed_ptr, st); break;
+    case 8: launch_softmax_fwd_warp<8>(x, y, yd, rows, scale, causal_q, p, salt, seed_ptr, st); break;
+    default: launch_softmax_fwd_warp<16>(x, y, yd, rows, scale, causal_q, p, salt, seed_ptr, st); break;
+  }
+  return (int)cudaGetLastError();
+}
+// dx = scale * y * (g - sum(g*y)) with g = dropout_backward(dy) (p = 0: g = dy).  Same shape limits as above.
+FFK_API int ffk_softmax_dropout_bwd(const void *dy, const void *y, void *dx, int rows, int cols, float scale, float p,
+                                    unsigned long long salt, const unsigned long long *seed_ptr, int dt, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (!softmax_vec_ok(cols, dt, dy, y, dx)) return -3;
+  switch (cols / 256) {
+    case 1: launch_softmax_bwd_warp<1>(dy, y, dx, rows, scale, p, salt, seed_ptr, st); break;
+    case 2: launch_softmax_bwd_warp<2>(dy, y, dx, rows, scale, p, salt, seed_ptr, st); break;
+    case 4: launch_softmax_bwd_warp<4>(dy, y, dx, rows, scale, p, salt, seed_ptr, st); break;
+    case 8: launch_softmax_bwd_warp<8>(dy, y, dx, rows, scale, p, salt, seed_ptr, st); break;
+    default: launch_softmax_bwd_warp<16>(dy, y, dx, rows, scale, p, salt, seed_ptr, st); break;
+  }
+  return (int)cudaGetLastError();
+}
+
 FFK_API int ffk_softmax_fwd(const void *x, void *y, int rows, int cols, float scale, int causal_q, int dt,
                             cudaStream_t st) {
   if (rows <= 0) return 0;
+  if (softmax_vec_ok(cols, dt, x, y, nullptr))
+    return ffk_softmax_dropout_fwd(x, y, nullptr, rows, cols, scale, causal_q, 0.f, 0, nullptr, dt, st);
   int threads = cols >= 1024 ? 256 : 128;
   DISPATCH_FLOAT(dt, (softmax_fwd_kernel<T><<<rows < 148 * 16 ? rows : 148 * 16, threads, 0, st>>>(
                          (const T *)x, (T *)y, rows, cols, scale, causal_q)));
@@ -303,6 +389,8 @@ FFK_API int ffk_softmax_fwd(const void *x, void *y, int rows, int cols, float sc
 FFK_API int ffk_softmax_bwd(const void *dy, const void *y, void *dx, int rows, int cols, float scale, int dt,
                             cudaStream_t st) {
   if (rows <= 0) return 0;
+  if (softmax_vec_ok(cols, dt, dy, y, dx))
+    return ffk_softmax_dropout_bwd(dy, y, dx, rows, cols, scale, 0.f, 0, nullptr, dt, st);
   int threads = cols >= 1024 ? 256 : 128;
   DISPATCH_FLOAT(dt, (softmax_bwd_kernel<T><<<rows < 148 * 16 ? rows : 148 * 16, threads, 0, st>>>(
                          (const T *)dy, (const T *)y, (T *)dx, rows, cols, scale)));

@@ -19,7 +19,11 @@ template <> __device__ __forceinline__ float ldg<bf16>(const bf16 *p, long long 
 template <typename G>
 __global__ void adam_kernel(float *__restrict__ w, float *__restrict__ m, float *__restrict__ v,
                             const G *__restrict__ g, bf16 *__restrict__ shadow, long long n, float alpha_t,
-                            float beta1, float beta2, float eps, float wd, float gscale) {
+                            float beta1, float beta2, float eps, float wd, float gscale,
+                            const float *__restrict__ alpha_ptr) {
+  // alpha_ptr (optional): bias-corrected step size kept in device memory so that a captured CUDA graph
+  // sees the value of the current step.
+  if (alpha_ptr) alpha_t = *alpha_ptr;
   long long stride = (long long)gridDim.x * blockDim.x * 4;
   for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
     if (i + 4 <= n) {
@@ -134,14 +138,14 @@ __global__ void embedding_sgd_kernel(const I *__restrict__ idx, const O *__restr
 
 // grad_dt: 0 = fp32, 1 = bf16.  shadow may be null.
 FFK_API int ffk_adam_update(float *w, float *m, float *v, const void *g, void *shadow, long long n, float alpha_t,
-                            float beta1, float beta2, float eps, float wd, float gscale, int grad_dt,
-                            cudaStream_t st) {
+                            float beta1, float beta2, float eps, float wd, float gscale, const float *alpha_ptr,
+                            int grad_dt, cudaStream_t st) {
   if (n <= 0) return 0;
   int grid = ffk_blocks(n / 4 + 1, 256, 148 * 8);
   if (grad_dt == 1)
-    adam_kernel<bf16><<<grid, 256, 0, st>>>(w, m, v, (const bf16 *)g, (bf16 *)shadow, n, alpha_t, beta1, beta2, eps, wd, gscale);
+    adam_kernel<bf16><<<grid, 256, 0, st>>>(w, m, v, (const bf16 *)g, (bf16 *)shadow, n, alpha_t, beta1, beta2, eps, wd, gscale, alpha_ptr);
   else
-    adam_kernel<float><<<grid, 256, 0, st>>>(w, m, v, (const float *)g, (bf16 *)shadow, n, alpha_t, beta1, beta2, eps, wd, gscale);
+    adam_kernel<float><<<grid, 256, 0, st>>>(w, m, v, (const float *)g, (bf16 *)shadow, n, alpha_t, beta1, beta2, eps, wd, gscale, alpha_ptr);
   return (int)cudaGetLastError();
 }
 FFK_API int ffk_sgd_update(float *w, float *mom, const void *g, void *shadow, long long n, float lr, float momentum,

@@ -1,0 +1,287 @@
+// rowwise_vec.cuh -- 128-bit vectorised fast paths of the row-wise kernels for bf16 rows whose length
+// is a multiple of 8: softmax fwd/bwd (optionally fused with dropout of the probabilities), LayerNorm
+// fwd/bwd (fused residual add) and the bias/activation backward with its column reduction.
+//
+// Each thread owns whole 8-element vectors of a row and keeps them in registers, so a row is read once
+// and written once; HBM traffic is the algorithmic minimum.  The scalar kernels in norm_softmax.cu and
+// elementwise.cu remain the general path (fp32, odd lengths).
+#pragma once
+#include "common.cuh"
+
+namespace vec {
+
+__device__ __forceinline__ void ld8(const bf16 *p, float *v) {
+  uint4 u = *reinterpret_cast<const uint4 *>(p);
+  float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void st8(bf16 *p, const float *v) {
+  *reinterpret_cast<uint4 *>(p) = make_uint4(pack_bf162(v[0], v[1]), pack_bf162(v[2], v[3]), pack_bf162(v[4], v[5]), pack_bf162(v[6], v[7]));
+}
+
+// ---------------------------------------------------------------- softmax: one warp per row
+// cols = 256 * VPT.  y = softmax(scale * x); yd (optional) = dropout(y) with keep mask hash(seed, element index).
+template <int VPT>
+__global__ void softmax_fwd_warp_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, bf16 *__restrict__ yd, int rows, float scale,
+                                        int causal_q, float p_drop, unsigned long long salt, const unsigned long long *seed_ptr) {
+  constexpr int COLS = 256 * VPT;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  unsigned long long seed = salt;
+  if (seed_ptr) seed = salt * 0x9E3779B97F4A7C15ull + *seed_ptr;
+  const float keep_scale = p_drop < 1.f ? 1.f / (1.f - p_drop) : 0.f;
+  const uint32_t thr = ffk_drop_threshold(p_drop);
+  for (long long row = (long long)blockIdx.x * wpb + wib; row < rows; row += (long long)gridDim.x * wpb) {
+    const bf16 *px = x + row * COLS;
+    float v[VPT][8];
+    const int limit = causal_q > 0 ? (int)(row % causal_q) + 1 : COLS;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c0 = (i * 32 + lane) * 8;
+      ld8(px + c0, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = (c0 + j < limit) ? v[i][j] * scale : -INFINITY;
+        mx = fmaxf(mx, v[i][j]);
+      }
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = __expf(v[i][j] - mx);
+        s += v[i][j];
+      }
+    s = warp_sum(s);
+    const float inv = 1.f / s;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c0 = (i * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] *= inv;
+      st8(y + row * COLS + c0, v[i]);
+      if (yd) {
+        float d[8];
+        const unsigned long long g4 = (unsigned long long)(row * COLS + c0) >> 2;
+        const uint32_t keep = ffk_keep4(seed, g4, thr) | (ffk_keep4(seed, g4 + 1, thr) << 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d[j] = (keep >> j) & 1u ? v[i][j] * keep_scale : 0.f;
+        st8(yd + row * COLS + c0, d);
+      }
+    }
+  }
+}
+// dx = scale * y * (g - sum(g * y)), g = dy (optionally first passed back through the dropout mask)
+template <int VPT>
+__global__ void softmax_bwd_warp_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ y, bf16 *__restrict__ dx, int rows,
+                                        float scale, float p_drop, unsigned long long salt, const unsigned long long *seed_ptr) {
+  constexpr int COLS = 256 * VPT;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  unsigned long long seed = salt;
+  if (seed_ptr) seed = salt * 0x9E3779B97F4A7C15ull + *seed_ptr;
+  const float keep_scale = p_drop < 1.f ? 1.f / (1.f - p_drop) : 0.f;
+  const uint32_t thr = ffk_drop_threshold(p_drop);
+  for (long long row = (long long)blockIdx.x * wpb + wib; row < rows; row += (long long)gridDim.x * wpb) {
+    float g[VPT][8], p[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c0 = (i * 32 + lane) * 8;
+      ld8(dy + row * COLS + c0, g[i]);
+      ld8(y + row * COLS + c0, p[i]);
+      uint32_t keep = 0xFFu;
+      if (p_drop > 0.f) {
+        const unsigned long long g4 = (unsigned long long)(row * COLS + c0) >> 2;
+        keep = ffk_keep4(seed, g4, thr) | (ffk_keep4(seed, g4 + 1, thr) << 4);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (p_drop > 0.f) g[i][j] = (keep >> j) & 1u ? g[i][j] * keep_scale : 0.f;
+        s += g[i][j] * p[i][j];
+      }
+    }
+    s = warp_sum(s);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c0 = (i * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[i][j] = scale * p[i][j] * (g[i][j] - s);
+      st8(dx + row * COLS + c0, g[i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- LayerNorm: one block per row
+// cols = 8 * blockDim.x * VPT.  y = LN(a + b) * gamma + beta, xsum = a + b (when b is given).
+template <int VPT>
+__global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ b, const bf16 *__restrict__ gamma,
+                                         const bf16 *__restrict__ beta, bf16 *__restrict__ xsum, bf16 *__restrict__ y,
+                                         float *__restrict__ mean, float *__restrict__ rstd, int rows, int cols, float eps) {
+  __shared__ float red[32];
+  float gm[VPT][8], bt[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int c0 = (i * blockDim.x + threadIdx.x) * 8;
+    if (gamma) ld8(gamma + c0, gm[i]);
+    if (beta) ld8(beta + c0, bt[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
+      ld8(a + off, v[i]);
+      if (b) {
+        float w[8];
+        ld8(b + off, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += w[j];
+        if (xsum) {
+          st8(xsum + off, v[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = bf2f(f2bf(v[i][j]));  // statistics of the value backward will read
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+    const float mu = block_sum(s, red) / cols;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; ss += d * d; }
+    const float rs = rsqrtf(block_sum(ss, red) / cols + eps);
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o = (v[i][j] - mu) * rs;
+        v[i][j] = gamma ? o * gm[i][j] + (beta ? bt[i][j] : 0.f) : o;
+      }
+      st8(y + off, v[i]);
+    }
+  }
+}
+// dx (and optionally dx2) (+)= LN backward; per-block partial sums of dgamma/dbeta -> partial[2][grid][cols]
+template <int VPT>
+__global__ void layernorm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x, const bf16 *__restrict__ gamma,
+                                         const float *__restrict__ mean, const float *__restrict__ rstd, bf16 *__restrict__ dx,
+                                         bf16 *__restrict__ dx2, float *__restrict__ partial, int rows, int cols, int acc1, int acc2) {
+  __shared__ float red[32];
+  float gm[VPT][8], dg[VPT][8], db[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int c0 = (i * blockDim.x + threadIdx.x) * 8;
+    if (gamma) ld8(gamma + c0, gm[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; if (!gamma) gm[i][j] = 1.f; }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mu = mean[row], rs = rstd[row];
+    float g[VPT][8], xh[VPT][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
+      ld8(dy + off, g[i]);
+      ld8(x + off, xh[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[i][j] = (xh[i][j] - mu) * rs;
+        dg[i][j] += g[i][j] * xh[i][j];
+        db[i][j] += g[i][j];
+        g[i][j] *= gm[i][j];
+        s1 += g[i][j];
+        s2 += g[i][j] * xh[i][j];
+      }
+    }
+    const float m1 = block_sum(s1, red) / cols;
+    const float m2 = block_sum(s2, red) / cols;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - m1 - xh[i][j] * m2);
+      if (dx2) {
+        float t[8];
+        if (acc2) {
+          ld8(dx2 + off, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[j] += o[j];
+          st8(dx2 + off, t);
+        } else st8(dx2 + off, o);
+      }
+      if (acc1) {
+        float t[8];
+        ld8(dx + off, t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += t[j];
+      }
+      st8(dx + off, o);
+    }
+  }
+  if (partial) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c0 = (i * blockDim.x + threadIdx.x) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        partial[(long long)blockIdx.x * cols + c0 + j] = dg[i][j];
+        partial[((long long)gridDim.x + blockIdx.x) * cols + c0 + j] = db[i][j];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- bias / activation backward
+// block (32, 8): thread (tx, ty) owns columns [blockIdx.x*256 + tx*8, +8) of rows ty, ty+8*gridDim.y, ...
+// dz = dy * act'(saved); partial[blockIdx.y][col] = column sums over this block's rows.
+static __global__ void bias_act_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ saved, bf16 *__restrict__ dz,
+                                        float *__restrict__ partial, int rows, int cols, int act) {
+  __shared__ float red[8][32][9];
+  const int c0 = blockIdx.x * 256 + threadIdx.x * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (c0 < cols) {
+    for (int r = blockIdx.y * 8 + threadIdx.y; r < rows; r += gridDim.y * 8) {
+      long long off = (long long)r * cols + c0;
+      float g[8];
+      ld8(dy + off, g);
+      if (act != ACT_NONE) {
+        float sv[8];
+        ld8(saved + off, sv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] *= act_bwd(sv[j], act);
+      }
+      if (dz) st8(dz + off, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += g[j];
+    }
+  }
+  if (!partial) return;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && c0 < cols) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += red[k][threadIdx.x][j];
+      partial[(long long)blockIdx.y * cols + c0 + j] = s;
+    }
+  }
+}
+
+}  // namespace vec

@@ -80,19 +80,19 @@ def _declare(l):
         "ffk_unary_bwd": [I, P, P, P, P, L, F, I, I, S],
         "ffk_binary_fwd": [I, P, P, P, L, L, I, S],
         "ffk_binary_bwd": [I, P, P, P, P, P, L, I, I, S],
-        "ffk_dropout": [P, P, P, L, F, c_ulonglong, I, S],
+        "ffk_dropout": [P, P, P, L, F, c_ulonglong, P, I, S],
         "ffk_axpby": [P, P, L, F, F, I, S],
         "ffk_fill": [P, L, F, I, S],
         "ffk_cast": [P, I, P, I, L, I, S],
         "ffk_bias_act_bwd": [P, P, P, P, P, I, I, I, I, I, S],
         "ffk_layernorm_fwd": [P, P, P, P, P, P, P, P, I, I, F, I, S],
-        "ffk_layernorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, S],
+        "ffk_layernorm_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, S],
         "ffk_softmax_fwd": [P, P, I, I, F, I, I, S],
         "ffk_softmax_bwd": [P, P, P, I, I, F, I, S],
         "ffk_softmax_ce": [P, P, P, P, P, I, I, F, I, I, S],
         "ffk_loss_bwd": [I, P, P, P, L, I, F, I, I, S],
         "ffk_loss_fwd": [I, P, P, P, I, I, I, I, S],
-        "ffk_adam_update": [P, P, P, P, P, L, F, F, F, F, F, F, I, S],
+        "ffk_adam_update": [P, P, P, P, P, L, F, F, F, F, F, F, P, I, S],
         "ffk_sgd_update": [P, P, P, P, L, F, F, I, F, F, I, S],
         "ffk_embedding_fwd": [P, P, P, L, I, I, L, I, I, I, I, S],
         "ffk_embedding_bwd": [P, P, P, L, I, I, L, I, I, I, I, S],
@@ -118,7 +118,16 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+    """Number of kernel-library calls issued so far by this process (each is at least one launch)."""
+    return _LAUNCHES[0]
+
+
 def _check(code: int, what: str):
+    _LAUNCHES[0] += 1
     if code != 0:
         raise KernelError(f"{what} failed with code {code}")
 
@@ -184,6 +193,9 @@ def matmul_nn(a, b, out=None, *, alpha=1.0, accumulate=False, out_dtype=None, bn
     N = b.shape[1]
     out = _gemm_out(out, M, N, a, out_dtype)
     _cuda_contig(a, b, out)
+    if a.dtype == torch.float32:
+        # fp32 storage runs on the tf32 path, whose operands must be K-major: transpose b once
+        return matmul_nt(a, transpose2d(b), out=out, alpha=alpha, accumulate=accumulate, bn=bn)
     gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=K, B=b.data_ptr(), ldb=N, b_mn=True, C=out.data_ptr(), ldc=N,
              es=_es(a), alpha=alpha, out_fp32=out.dtype == torch.float32, accumulate=accumulate, bn=bn)
     return out
@@ -195,6 +207,8 @@ def matmul_tn(a, b, out=None, *, alpha=1.0, accumulate=False, out_dtype=None, bn
     N = b.shape[1]
     out = _gemm_out(out, M, N, a, out_dtype)
     _cuda_contig(a, b, out)
+    if a.dtype == torch.float32:
+        return matmul_nt(transpose2d(a), transpose2d(b), out=out, alpha=alpha, accumulate=accumulate, bn=bn)
     gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=M, a_mn=True, B=b.data_ptr(), ldb=N, b_mn=True,
              C=out.data_ptr(), ldc=N, es=_es(a), alpha=alpha, out_fp32=out.dtype == torch.float32,
              accumulate=accumulate, bn=bn)
@@ -242,11 +256,12 @@ def binary_bwd(op: str, a, b, dy, da=None, db=None, accumulate=False):
                                 dy.numel(), _dt(dy), int(accumulate), _stream()), "ffk_binary_bwd")
 
 
-def dropout(x, p: float, seed: int, residual=None, out=None):
+def dropout(x, p: float, seed: int, residual=None, out=None, seed_tensor=None):
+    """out = dropout(x) [+ residual]; the mask is a function of (seed, *seed_tensor, element index)."""
     out = torch.empty_like(x) if out is None else out
-    _cuda_contig(x, residual, out)
-    _check(lib().ffk_dropout(x.data_ptr(), _p(residual), out.data_ptr(), x.numel(), p, seed & (2**64 - 1), _dt(x),
-                             _stream()), "ffk_dropout")
+    _cuda_contig(x, residual, out, seed_tensor)
+    _check(lib().ffk_dropout(x.data_ptr(), _p(residual), out.data_ptr(), x.numel(), p, seed & (2**64 - 1),
+                             _p(seed_tensor), _dt(x), _stream()), "ffk_dropout")
     return out
 
 
@@ -298,12 +313,13 @@ def layernorm_bwd_scratch(rows, cols) -> int:
 
 
 def layernorm_bwd(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, scratch, accumulate_dx=False,
-                  accumulate_params=False):
+                  accumulate_params=False, dx2=None, accumulate_dx2=False):
     rows, cols = dy.shape
-    _cuda_contig(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, scratch)
+    _cuda_contig(dy, x, gamma, mean, rstd, dx, dx2, dgamma, dbeta, scratch)
     _check(lib().ffk_layernorm_bwd(dy.data_ptr(), x.data_ptr(), _p(gamma), mean.data_ptr(), rstd.data_ptr(),
-                                   dx.data_ptr(), _p(dgamma), _p(dbeta), _p(scratch), rows, cols, _dt(dy),
-                                   int(accumulate_dx), int(accumulate_params), _stream()), "ffk_layernorm_bwd")
+                                   dx.data_ptr(), _p(dx2), _p(dgamma), _p(dbeta), _p(scratch), rows, cols, _dt(dy),
+                                   int(accumulate_dx), int(accumulate_dx2), int(accumulate_params), _stream()),
+           "ffk_layernorm_bwd")
 
 
 def softmax_fwd(x, out=None, scale=1.0, causal_q=0):
@@ -352,11 +368,12 @@ def loss_fwd(kind: str, pred, target, loss_rows):
 
 
 # --------------------------------------------------------------------------- optimizers / embedding
-def adam_update(w, m, v, g, shadow, alpha_t, beta1, beta2, eps, weight_decay=0.0, grad_scale=1.0):
-    _cuda_contig(w, m, v, g, shadow)
+def adam_update(w, m, v, g, shadow, alpha_t, beta1, beta2, eps, weight_decay=0.0, grad_scale=1.0, alpha_tensor=None):
+    """One Adam step over an arena; alpha_tensor (1-element fp32 device tensor) overrides alpha_t when given."""
+    _cuda_contig(w, m, v, g, shadow, alpha_tensor)
     _check(lib().ffk_adam_update(w.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), _p(shadow), w.numel(),
-                                 alpha_t, beta1, beta2, eps, weight_decay, grad_scale, _dt(g), _stream()),
-           "ffk_adam_update")
+                                 alpha_t, beta1, beta2, eps, weight_decay, grad_scale, _p(alpha_tensor), _dt(g),
+                                 _stream()), "ffk_adam_update")
 
 
 def sgd_update(w, mom, g, shadow, lr, momentum=0.0, nesterov=False, weight_decay=0.0, grad_scale=1.0):
@@ -383,3 +400,187 @@ def embedding_bwd(idx, dout, dtable, aggr="sum"):
                                    dtable.shape[1], dtable.shape[0], int(aggr == "avg"), _dt(dtable), _dt(idx),
                                    _dt(dout), _stream()), "ffk_embedding_bwd")
     return dtable
+
+
+# --------------------------------------------------------------------------- data movement
+def _decl_tensor_ops(l):
+    P, I, L, F, S = c_void_p, c_int, c_longlong, c_float, c_void_p
+    LP = ctypes.POINTER(c_longlong)
+    sig = {
+        "ffk_permute": [P, P, I, LP, LP, I, I, S],
+        "ffk_transpose2d": [P, P, I, I, I, I, S],
+        "ffk_block_copy": [P, L, P, L, L, L, I, I, I, S],
+        "ffk_reduce": [P, P, L, L, L, I, I, S],
+        "ffk_reduce_bwd": [P, P, L, L, L, F, I, I, S],
+        "ffk_gather": [P, P, P, L, L, L, L, I, I, S],
+        "ffk_gather_bwd": [P, P, P, L, L, L, L, I, I, S],
+        "ffk_topk": [P, P, P, I, I, I, I, S],
+        "ffk_topk_bwd": [P, P, P, I, I, I, I, I, S],
+        "ffk_reverse": [P, P, L, L, L, I, S],
+    }
+    for name, args in sig.items():
+        fn = getattr(l, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+_tensor_ops_declared = [False]
+
+
+def _tlib():
+    l = lib()
+    if not _tensor_ops_declared[0]:
+        _decl_tensor_ops(l)
+        _tensor_ops_declared[0] = True
+    return l
+
+
+def permute(src, perm, out=None, accumulate=False):
+    """out = src.permute(perm), materialised contiguously (accumulate: out += ...)."""
+    _cuda_contig(src, out)
+    sizes = [src.shape[p] for p in perm]
+    strides = [src.stride(p) for p in perm]
+    out = torch.empty(sizes, dtype=src.dtype, device=src.device) if out is None else out
+    n = len(sizes)
+    arr = (c_longlong * n)
+    acc = 0
+    if accumulate:
+        acc = 1 if src.dtype == torch.float32 else 2
+    _check(_tlib().ffk_permute(src.data_ptr(), out.data_ptr(), n, arr(*sizes), arr(*strides), src.element_size(), acc,
+                               _stream()), "ffk_permute")
+    return out
+
+
+def transpose2d(src, out=None):
+    """[..., r, c] -> [..., c, r] through shared-memory tiles."""
+    _cuda_contig(src, out)
+    r, c = src.shape[-2], src.shape[-1]
+    batch = src.numel() // (r * c)
+    out = torch.empty(*src.shape[:-2], c, r, dtype=src.dtype, device=src.device) if out is None else out
+    _check(_tlib().ffk_transpose2d(src.data_ptr(), out.data_ptr(), batch, r, c, src.element_size(), _stream()),
+           "ffk_transpose2d")
+    return out
+
+
+def block_copy(src, src_off, src_ld, dst, dst_off, dst_ld, outer, block, accumulate=False):
+    """dst[o*dst_ld + dst_off + b] (+)= src[o*src_ld + src_off + b] for o < outer, b < block (flat element offsets)."""
+    _cuda_contig(src, dst)
+    es = src.element_size()
+    _check(_tlib().ffk_block_copy(src.data_ptr() + src_off * es, src_ld, dst.data_ptr() + dst_off * es, dst_ld, outer, block, es,
+                                  _DT.get(src.dtype, 0), int(accumulate), _stream()), "ffk_block_copy")
+
+
+REDUCE_OPS = {"sum": 0, "mean": 1, "max": 2, "min": 3, "prod": 4}
+
+
+def reduce(x, out, outer, red, inner, op="sum"):
+    _cuda_contig(x, out)
+    _check(_tlib().ffk_reduce(x.data_ptr(), out.data_ptr(), outer, red, inner, REDUCE_OPS[op], _dt(x), _stream()), "ffk_reduce")
+    return out
+
+
+def reduce_bwd(dy, dx, outer, red, inner, scale=1.0, accumulate=False):
+    _cuda_contig(dy, dx)
+    _check(_tlib().ffk_reduce_bwd(dy.data_ptr(), dx.data_ptr(), outer, red, inner, scale, _dt(dy), int(accumulate), _stream()),
+           "ffk_reduce_bwd")
+
+
+def gather(x, idx, out, dim):
+    _cuda_contig(x, idx, out)
+    outer = 1
+    for s in x.shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in x.shape[dim + 1:]:
+        inner *= s
+    if list(idx.shape[:dim]) != list(x.shape[:dim]) or list(idx.shape[dim + 1:]) != list(x.shape[dim + 1:]):
+        raise KernelError("gather: index must match the input outside the gather dim")
+    _check(_tlib().ffk_gather(x.data_ptr(), idx.data_ptr(), out.data_ptr(), outer, x.shape[dim], idx.shape[dim], inner,
+                              x.element_size(), _dt(idx), _stream()), "ffk_gather")
+    return out
+
+
+def gather_bwd(dy, idx, dx, dim):
+    _cuda_contig(dy, idx, dx)
+    outer = 1
+    for s in dx.shape[:dim]:
+        outer *= s
+    inner = 1
+    for s in dx.shape[dim + 1:]:
+        inner *= s
+    _check(_tlib().ffk_gather_bwd(dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), outer, dx.shape[dim], idx.shape[dim], inner,
+                                  _dt(dy), _dt(idx), _stream()), "ffk_gather_bwd")
+
+
+def topk(x, k, vals=None, idxs=None):
+    _cuda_contig(x, vals, idxs)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    vals = torch.empty(*x.shape[:-1], k, dtype=x.dtype, device=x.device) if vals is None else vals
+    idxs = torch.empty(*x.shape[:-1], k, dtype=torch.int32, device=x.device) if idxs is None else idxs
+    _check(_tlib().ffk_topk(x.data_ptr(), vals.data_ptr(), idxs.data_ptr(), rows, cols, k, _dt(x), _stream()), "ffk_topk")
+    return vals, idxs
+
+
+def topk_bwd(dvals, idxs, dx, accumulate=False):
+    _cuda_contig(dvals, idxs, dx)
+    cols, k = dx.shape[-1], idxs.shape[-1]
+    rows = dx.numel() // cols
+    _check(_tlib().ffk_topk_bwd(dvals.data_ptr(), idxs.data_ptr(), dx.data_ptr(), rows, cols, k, _dt(dx), int(accumulate),
+                                _stream()), "ffk_topk_bwd")
+
+
+def reverse(x, out, axis):
+    _cuda_contig(x, out)
+    outer = 1
+    for s in x.shape[:axis]:
+        outer *= s
+    inner = 1
+    for s in x.shape[axis + 1:]:
+        inner *= s
+    _check(_tlib().ffk_reverse(x.data_ptr(), out.data_ptr(), outer, x.shape[axis], inner, x.element_size(), _stream()),
+           "ffk_reverse")
+    return out
+
+
+# --------------------------------------------------------------------------- fused softmax + dropout (attention probabilities)
+def softmax_dropout_supported(t) -> bool:
+    cols = t.shape[-1]
+    return t.dtype == torch.bfloat16 and cols % 256 == 0 and cols // 256 in (1, 2, 4, 8, 16)
+
+
+def _decl_softmax_dropout(l):
+    P, I, F, S = c_void_p, c_int, c_float, c_void_p
+    l.ffk_softmax_dropout_fwd.argtypes = [P, P, P, I, I, F, I, F, c_ulonglong, P, I, S]
+    l.ffk_softmax_dropout_fwd.restype = c_int
+    l.ffk_softmax_dropout_bwd.argtypes = [P, P, P, I, I, F, F, c_ulonglong, P, I, S]
+    l.ffk_softmax_dropout_bwd.restype = c_int
+
+
+_sd_declared = [False]
+
+
+def _sdlib():
+    l = lib()
+    if not _sd_declared[0]:
+        _decl_softmax_dropout(l)
+        _sd_declared[0] = True
+    return l
+
+
+def softmax_dropout_fwd(x, y, y_dropped, p, salt, seed_tensor=None, scale=1.0, causal_q=0):
+    """y = softmax(scale*x) and, in the same pass, y_dropped = dropout(y, p) (y_dropped may be None)."""
+    _cuda_contig(x, y, y_dropped, seed_tensor)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    _check(_sdlib().ffk_softmax_dropout_fwd(x.data_ptr(), y.data_ptr(), _p(y_dropped), rows, cols, scale, causal_q, p,
+                                            salt & (2**64 - 1), _p(seed_tensor), _dt(x), _stream()), "ffk_softmax_dropout_fwd")
+
+
+def softmax_dropout_bwd(dy, y, dx, p, salt, seed_tensor=None, scale=1.0):
+    """dx = softmax backward of the gradient that first goes back through the same dropout mask."""
+    _cuda_contig(dy, y, dx, seed_tensor)
+    cols = y.shape[-1]
+    rows = y.numel() // cols
+    _check(_sdlib().ffk_softmax_dropout_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, scale, p,
+                                            salt & (2**64 - 1), _p(seed_tensor), _dt(y), _stream()), "ffk_softmax_dropout_bwd")

@@ -1,0 +1,1160 @@
+"""GPU executor: runs a (parallel) computation graph with the sm_100a kernel library.
+
+Counterpart of the reference's local executor
+(lib/local-execution/src/local-execution/computation_graph_instance.cc:61-155) and, with a
+``DistContext``, of its distributed executor (lib/realm-execution/src/realm-execution/pcg_instance.cc):
+the graph is lowered once into a static plan -- per operator a forward and a backward closure over
+pre-allocated tensors -- and a training step replays the plan (optionally as one CUDA graph).
+
+Differences from the reference that matter for speed:
+  * every rank runs the same program on its own shard (SPMD) instead of one controller that
+    serialises task arguments to JSON for each launch;
+  * parameters, gradients and optimizer state live in flat arenas, so the optimizer is one launch;
+  * gradients are written, not accumulated, by their first producer, so no buffer is zeroed per step
+    (the reference accumulates with beta = 1 everywhere and zeroes all gradients each iteration);
+  * pointwise neighbours are fused into the producing kernel (bias/activation in the GEMM epilogue,
+    residual add in LayerNorm, softmax in the cross-entropy loss).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from .. import _ffcore as core
+from ..ops import kernels as K
+from .initializers import initialize
+
+Value = Tuple[int, str]
+
+_TORCH_DT = {"FLOAT": torch.float32, "DOUBLE": torch.float64, "HALF": torch.float16, "BFLOAT16": torch.bfloat16,
+             "INT32": torch.int32, "INT64": torch.int64, "BOOL": torch.bool}
+
+
+@dataclass
+class OptimizerConfig:
+    """SGDOptimizerAttrs / AdamOptimizerAttrs of the reference (lib/pcg/src/pcg/optimizer_attrs.cc:7-45)."""
+    kind: str = "adam"  # "adam" | "sgd"
+    lr: float = 1e-3
+    momentum: float = 0.0
+    nesterov: bool = False
+    weight_decay: float = 0.0
+    beta1: float = 0.9
+    beta2: float = 0.999
+    epsilon: float = 1e-8
+
+
+@dataclass
+class ExecConfig:
+    compute_dtype: str = "bf16"          # "bf16" (fp32 master weights) or "fp32" (tf32 tensor cores)
+    loss: Optional[str] = "sparse_categorical_crossentropy"
+    optimizer: OptimizerConfig = field(default_factory=OptimizerConfig)
+    seed: int = 0
+    use_cuda_graph: bool = False
+    device: str = "cuda"
+    training: bool = True
+    causal_attention: bool = False
+    profile_layers: bool = False
+
+
+class _Buf:
+    """A tensor slot of the plan: data plus (optionally) gradient."""
+    __slots__ = ("data", "grad", "requires_grad", "shape")
+
+    def __init__(self, data=None, requires_grad=False):
+        self.data = data
+        self.grad = None
+        self.requires_grad = requires_grad
+
+
+class _GradPool:
+    """Reuses gradient buffers whose lifetimes do not overlap (plan-time, so addresses stay static)."""
+
+    def __init__(self, device):
+        self.free: Dict[Tuple[int, torch.dtype], List[torch.Tensor]] = {}
+        self.device = device
+        self.total_bytes = 0
+
+    def take(self, numel, dtype):
+        key = (numel, dtype)
+        lst = self.free.get(key)
+        if lst:
+            return lst.pop()
+        self.total_bytes += numel * torch.empty((), dtype=dtype).element_size()
+        return torch.empty(numel, dtype=dtype, device=self.device)
+
+    def give(self, t):
+        self.free.setdefault((t.numel(), t.dtype), []).append(t)
+
+
+class OpImpl:
+    """Base class of operator implementations.  ``setup`` allocates outputs; ``forward`` /
+    ``backward`` launch kernels only."""
+
+    def __init__(self, ex: "Executable", nid: int, node: dict):
+        self.ex = ex
+        self.nid = nid
+        self.node = node
+        self.attrs = node["attrs"]
+        self.type = node["type"]
+        self.inputs: Dict[str, Value] = {s: tuple(v) for s, v in node["inputs"]}
+        self.outputs = [(s, sh) for s, sh, _ in node["outputs"]]
+        self.acc: Dict[str, bool] = {}  # per input slot: accumulate into its grad?
+
+    # helpers
+    def buf(self, slot) -> _Buf:
+        return self.ex.values[self.inputs[slot]]
+
+    def x(self, slot="INPUT"):
+        return self.buf(slot).data
+
+    def out(self, slot="OUTPUT") -> _Buf:
+        return self.ex.values[(self.nid, slot)]
+
+    def alloc_out(self, slot="OUTPUT", dtype=None, shape=None):
+        sh = dict(self.outputs)[slot]
+        shape = list(sh.piece_sizes) if shape is None else shape
+        dt = self.ex.torch_dtype(sh.dtype) if dtype is None else dtype
+        t = torch.empty(shape, dtype=dt, device=self.ex.device)
+        self.out(slot).data = t
+        return t
+
+    def setup(self):
+        raise NotImplementedError
+
+    def forward(self):
+        raise NotImplementedError
+
+    def backward(self):
+        pass
+
+    def grad_inputs(self) -> List[str]:
+        """input slots that receive a gradient from this op"""
+        return [s for s, v in self.inputs.items() if self.ex.values[v].requires_grad]
+
+
+_REGISTRY: Dict[str, type] = {}
+
+
+def register(*types):
+    def deco(cls):
+        for t in types:
+            _REGISTRY[t] = cls
+        return cls
+    return deco
+
+
+# ------------------------------------------------------------------------------------------ leaf ops
+@register("INPUT")
+class InputOp(OpImpl):
+    def setup(self):
+        self.alloc_out()
+
+    def forward(self):
+        pass
+
+
+@register("WEIGHT")
+class WeightOp(OpImpl):
+    def setup(self):
+        pass  # bound to the parameter arena by the executable
+
+    def forward(self):
+        pass
+
+
+@register("NOOP", "IDENTITY")
+class NoopOp(OpImpl):
+    def setup(self):
+        self.out().data = self.x()
+
+    def forward(self):
+        pass
+
+    def backward(self):
+        g = self.out().grad
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            self.ex.write_grad(b, g, self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ Linear
+_ACT = {None: None, "RELU": "relu", "GELU": "gelu", "SIGMOID": "sigmoid", "TANH": "tanh"}
+
+
+@register("LINEAR")
+class LinearOp(OpImpl):
+    def setup(self):
+        self.act = _ACT[self.attrs.get("activation")]
+        y = self.alloc_out()
+        self.y2d = y.view(-1, y.shape[-1])
+        x = self.x()
+        self.x2d = x.view(-1, x.shape[-1])
+        self.w = self.x("WEIGHT")
+        self.bias = self.x("BIAS") if "BIAS" in self.inputs else None
+        self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
+        rows, cols = self.y2d.shape
+        self.ex.need_scratch(4 * K.bias_act_bwd_scratch(rows, cols) if K.available() and self.ex.on_gpu else 0)
+
+    def forward(self):
+        K.matmul_nt(self.x2d, self.w, out=self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
+
+    def backward(self):
+        dy = self.out().grad.view_as(self.y2d)
+        if self.act is not None or self.bias is not None:
+            saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
+            bb = self.buf("BIAS") if self.bias is not None else None
+            K.bias_act_bwd(dy, saved, dy if self.act else None, bb.grad if bb is not None else None,
+                           self.ex.scratch_f32(), self.act, accumulate=self.acc.get("BIAS", False))
+        wb = self.buf("WEIGHT")
+        if wb.requires_grad:
+            K.matmul_tn(dy, self.x2d, out=wb.grad, accumulate=self.acc["WEIGHT"])
+        xb = self.buf("INPUT")
+        if xb.requires_grad:
+            K.matmul_nn(dy, self.w, out=xb.grad.view_as(self.x2d), accumulate=self.acc["INPUT"])
+
+
+@register("BATCHMATMUL")
+class BatchMatmulOp(OpImpl):
+    """out[b, n, p] = lhs[b, n, m] @ rhs[b, m, p] (declared but unimplemented in the reference)."""
+
+    def setup(self):
+        self.a, self.b = self.x("LHS_INPUT"), self.x("RHS_INPUT")
+        self.c = self.alloc_out()
+        *batch, self.n, self.m = self.a.shape
+        self.p = self.b.shape[-1]
+        self.nb = 1
+        for s in batch:
+            self.nb *= s
+
+    def _gemm(self, A, a_mn, lda, a_sb, B, b_mn, ldb, b_sb, C, ldc, c_sb, M, N, Kd, acc):
+        if A.dtype == torch.float32:  # MN-major operands need 16-bit storage: run the product in bf16
+            A16, B16 = torch.empty_like(A, dtype=torch.bfloat16), torch.empty_like(B, dtype=torch.bfloat16)
+            K.cast(A, A16)
+            K.cast(B, B16)
+            A, B = A16, B16
+        K.gemm_raw(M=M, N=N, K=Kd, A=A.data_ptr(), lda=lda, a_mn=a_mn, a_sb=a_sb, B=B.data_ptr(), ldb=ldb, b_mn=b_mn,
+                   b_sb=b_sb, C=C.data_ptr(), ldc=ldc, c_sb=c_sb, nb=self.nb, es=A.element_size(),
+                   out_fp32=C.dtype == torch.float32, accumulate=acc)
+
+    def forward(self):
+        n, m, p = self.n, self.m, self.p
+        self._gemm(self.a, False, m, n * m, self.b, True, p, m * p, self.c, p, n * p, n, p, m, False)
+
+    def backward(self):
+        n, m, p = self.n, self.m, self.p
+        dc = self.out().grad
+        ab, bb = self.buf("LHS_INPUT"), self.buf("RHS_INPUT")
+        if ab.requires_grad:  # dA[n, m] = dC[n, p] . B[m, p]^T
+            self._gemm(dc, False, p, n * p, self.b, False, p, m * p, ab.grad, m, n * m, n, m, p, self.acc["LHS_INPUT"])
+        if bb.requires_grad:  # dB[m, p] = A[n, m]^T . dC[n, p]
+            self._gemm(self.a, True, m, n * m, dc, True, p, n * p, bb.grad, p, m * p, m, p, n, self.acc["RHS_INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ attention
+@register("MULTIHEAD_ATTENTION")
+class AttentionOp(OpImpl):
+    """Multi-head attention with packed projections.
+
+    The WEIGHT tensor has the reference's element count
+    ((q_in*kdim + k_in*kdim + v_in*vdim + vdim*embed) * heads, lib/op-attrs/src/op-attrs/ops/attention.cc:97-112)
+    and is laid out here as four row-major blocks Wq [H*kdim, q_in], Wk [H*kdim, k_in], Wv [H*vdim, v_in],
+    Wo [embed, H*vdim], so that self-attention runs one fused QKV GEMM.  Scores are scaled by 1/sqrt(kdim).
+    """
+
+    def setup(self):
+        a = self.attrs
+        ex = self.ex
+        self.H = int(a["num_heads"]) // ex.head_shards(self)
+        self.kd, self.vd, self.embed = int(a["kdim"]), int(a["vdim"]), int(a["embed_dim"])
+        self.p_drop = float(a.get("dropout", 0.0)) if ex.cfg.training else 0.0
+        q, k, v = self.x("QUERY"), self.x("KEY"), self.x("VALUE")
+        self.B, self.Sq, self.dq = q.shape
+        self.Sk, self.dk, self.dv = k.shape[1], k.shape[2], v.shape[2]
+        self.self_attn = self.inputs["QUERY"] == self.inputs["KEY"] == self.inputs["VALUE"]
+        H, kd, vd = self.H, self.kd, self.vd
+        w = self.x("WEIGHT").view(-1)
+        o0 = 0
+        self.wq = w[o0:o0 + H * kd * self.dq].view(H * kd, self.dq); o0 += H * kd * self.dq
+        self.wk = w[o0:o0 + H * kd * self.dk].view(H * kd, self.dk); o0 += H * kd * self.dk
+        self.wv = w[o0:o0 + H * vd * self.dv].view(H * vd, self.dv); o0 += H * vd * self.dv
+        self.wo = w[o0:o0 + self.embed * H * vd].view(self.embed, H * vd)
+        dt = q.dtype
+        dev = ex.device
+        self.ldqkv = H * (2 * kd + vd)
+        if self.self_attn:
+            self.wqkv = w[:self.ldqkv * self.dq].view(self.ldqkv, self.dq)
+            self.qkv = torch.empty(self.B * self.Sq, self.ldqkv, dtype=dt, device=dev)
+            self.qv = self.qkv[:, :H * kd]
+            self.kv = self.qkv[:, H * kd:2 * H * kd]
+            self.vv = self.qkv[:, 2 * H * kd:]
+            self.ldq = self.ldk = self.ldv = self.ldqkv
+        else:
+            self.qv = torch.empty(self.B * self.Sq, H * kd, dtype=dt, device=dev)
+            self.kv = torch.empty(self.B * self.Sk, H * kd, dtype=dt, device=dev)
+            self.vv = torch.empty(self.B * self.Sk, H * vd, dtype=dt, device=dev)
+            self.ldq, self.ldk, self.ldv = H * kd, H * kd, H * vd
+        # The batched core (scores, probabilities, context) always runs on bf16 tensor cores; with fp32
+        # activations the projections stay fp32/tf32 and q, k, v, ctx are cast at the boundary.
+        self.core16 = dt != torch.bfloat16
+        cdt = torch.bfloat16
+        if self.core16:
+            if self.self_attn:
+                self.c_qkv = torch.empty_like(self.qkv, dtype=cdt)
+                self.c_q, self.c_k, self.c_v = self.c_qkv[:, :H * kd], self.c_qkv[:, H * kd:2 * H * kd], self.c_qkv[:, 2 * H * kd:]
+            else:
+                self.c_q, self.c_k, self.c_v = (torch.empty_like(t, dtype=cdt) for t in (self.qv, self.kv, self.vv))
+            self.c_ctx = torch.empty(self.B * self.Sq, H * vd, dtype=cdt, device=dev)
+        else:
+            self.c_q, self.c_k, self.c_v = self.qv, self.kv, self.vv
+        self.probs = torch.empty(self.B, H, self.Sq, self.Sk, dtype=cdt, device=dev)
+        self.ctx = torch.empty(self.B * self.Sq, H * vd, dtype=dt, device=dev)
+        if not self.core16:
+            self.c_ctx = self.ctx
+        self.alloc_out()
+        self.bias_in = self.x("INPUT_BIAS") if "INPUT_BIAS" in self.inputs else None
+        self.bias_out = self.x("OUTPUT_BIAS") if "OUTPUT_BIAS" in self.inputs else None
+        self.alpha = 1.0 / math.sqrt(kd)
+        nbytes = self.probs.numel() * self.probs.element_size()
+        ex.need_big_scratch(nbytes, 2 if self.p_drop > 0 else 1)
+        ex.need_scratch(4 * K.bias_act_bwd_scratch(self.B * self.Sq, max(self.ldqkv, self.embed)) if ex.on_gpu else 0)
+        self.salt = ex.next_salt()
+        self.es = 2
+        if self.ex.cfg.training:
+            if self.self_attn:
+                self.dqkv = torch.empty_like(self.qkv)
+                self.dq_, self.dk_, self.dv_ = (self.dqkv[:, :H * kd], self.dqkv[:, H * kd:2 * H * kd], self.dqkv[:, 2 * H * kd:])
+            else:
+                self.dq_, self.dk_, self.dv_ = torch.empty_like(self.qv), torch.empty_like(self.kv), torch.empty_like(self.vv)
+            self.dctx = torch.empty_like(self.ctx)
+            if self.core16:
+                if self.self_attn:
+                    self.c_dqkv = torch.empty_like(self.c_qkv)
+                    self.c_dq, self.c_dk, self.c_dv = (self.c_dqkv[:, :H * kd], self.c_dqkv[:, H * kd:2 * H * kd], self.c_dqkv[:, 2 * H * kd:])
+                else:
+                    self.c_dq, self.c_dk, self.c_dv = (torch.empty_like(t) for t in (self.c_q, self.c_k, self.c_v))
+                self.c_dctx = torch.empty_like(self.c_ctx)
+            else:
+                self.c_dq, self.c_dk, self.c_dv, self.c_dctx = self.dq_, self.dk_, self.dv_, self.dctx
+
+    # batched GEMM over (head, batch) on strided [tokens, H*d] views
+    def _bg(self, M, N, Kd, A, lda, a_sh, a_sb, a_mn, Bm, ldb, b_sh, b_sb, b_mn, C, ldc, c_sh, c_sb, alpha=1.0):
+        K.gemm_raw(M=M, N=N, K=Kd, A=A.data_ptr(), lda=lda, a_sh=a_sh, a_sb=a_sb, a_mn=a_mn, B=Bm.data_ptr(), ldb=ldb,
+                   b_sh=b_sh, b_sb=b_sb, b_mn=b_mn, C=C.data_ptr(), ldc=ldc, c_sh=c_sh, c_sb=c_sb, nh=self.H,
+                   nb=self.B, alpha=alpha, es=self.es, out_fp32=C.dtype == torch.float32)
+
+    def forward(self):
+        H, kd, vd, Sq, Sk = self.H, self.kd, self.vd, self.Sq, self.Sk
+        q2 = self.x("QUERY").view(-1, self.dq)
+        if self.self_attn:
+            K.matmul_nt(q2, self.wqkv, out=self.qkv, bias=self.bias_in)
+        else:
+            K.matmul_nt(q2, self.wq, out=self.qv)
+            K.matmul_nt(self.x("KEY").view(-1, self.dk), self.wk, out=self.kv)
+            K.matmul_nt(self.x("VALUE").view(-1, self.dv), self.wv, out=self.vv)
+        if self.core16:
+            if self.self_attn:
+                K.cast(self.qkv, self.c_qkv)
+            else:
+                K.cast(self.qv, self.c_q); K.cast(self.kv, self.c_k); K.cast(self.vv, self.c_v)
+        # scores[b,h,sq,sk] = alpha * q . k^T
+        self._bg(Sq, Sk, kd, self.c_q, self.ldq, kd, Sq * self.ldq, False, self.c_k, self.ldk, kd, Sk * self.ldk, False,
+                 self.probs, Sk, Sq * Sk, H * Sq * Sk, alpha=self.alpha)
+        causal_q = Sq if self.ex.cfg.causal_attention else 0
+        p = self.probs
+        if self.p_drop > 0 and K.softmax_dropout_supported(self.probs):
+            p = self.ex.big_scratch(1, self.probs)  # probabilities and their dropped copy in one pass
+            K.softmax_dropout_fwd(self.probs, self.probs, p, self.p_drop, self.salt, self.ex.seed_tensor, causal_q=causal_q)
+        else:
+            K.softmax_fwd(self.probs, out=self.probs, causal_q=causal_q)
+            if self.p_drop > 0:
+                p = self.ex.big_scratch(1, self.probs)
+                K.dropout(self.probs, self.p_drop, self.salt, out=p, seed_tensor=self.ex.seed_tensor)
+        # ctx[b,sq,h,:] = p . v
+        self._bg(Sq, vd, Sk, p, Sk, Sq * Sk, H * Sq * Sk, False, self.c_v, self.ldv, vd, Sk * self.ldv, True,
+                 self.c_ctx, H * vd, vd, Sq * H * vd)
+        if self.core16:
+            K.cast(self.c_ctx, self.ctx)
+        y = self.out().data
+        K.matmul_nt(self.ctx, self.wo, out=y.view(-1, self.embed), bias=self.bias_out)
+
+    def backward(self):
+        H, kd, vd, Sq, Sk = self.H, self.kd, self.vd, self.Sq, self.Sk
+        ex = self.ex
+        dy = self.out().grad.view(-1, self.embed)
+        wbuf = self.buf("WEIGHT")
+        wg = wbuf.grad.view(-1)
+        accw = self.acc["WEIGHT"]
+        n_q, n_k, n_v = H * kd * self.dq, H * kd * self.dk, H * vd * self.dv
+        g_wo = wg[n_q + n_k + n_v:].view(self.embed, H * vd)
+        if self.bias_out is not None:
+            K.bias_act_bwd(dy, None, None, self.buf("OUTPUT_BIAS").grad, ex.scratch_f32(), None,
+                           accumulate=self.acc.get("OUTPUT_BIAS", False))
+        K.matmul_tn(dy, self.ctx, out=g_wo, accumulate=accw)
+        K.matmul_nn(dy, self.wo, out=self.dctx)
+        p = self.probs
+        if self.p_drop > 0:  # regenerate the dropped probabilities (mask is a function of the step seed)
+            p = ex.big_scratch(1, self.probs)
+            K.dropout(self.probs, self.p_drop, self.salt, out=p, seed_tensor=ex.seed_tensor)
+        dP = ex.big_scratch(0, self.probs)
+        if self.core16:
+            K.cast(self.dctx, self.c_dctx)
+        # dP[b,h,sq,sk] = dctx[b,sq,h,:] . v[b,sk,h,:]^T
+        self._bg(Sq, Sk, vd, self.c_dctx, H * vd, vd, Sq * H * vd, False, self.c_v, self.ldv, vd, Sk * self.ldv, False,
+                 dP, Sk, Sq * Sk, H * Sq * Sk)
+        # dV[b,sk,h,:] = p^T . dctx
+        self._bg(Sk, vd, Sq, p, Sk, Sq * Sk, H * Sq * Sk, True, self.c_dctx, H * vd, vd, Sq * H * vd, True,
+                 self.c_dv, self.ldv, vd, Sk * self.ldv)
+        if K.softmax_dropout_supported(self.probs):
+            K.softmax_dropout_bwd(dP, self.probs, dP, self.p_drop, self.salt, ex.seed_tensor, scale=self.alpha)
+        else:
+            if self.p_drop > 0:
+                K.dropout(dP, self.p_drop, self.salt, out=dP, seed_tensor=ex.seed_tensor)
+            K.softmax_bwd(dP, self.probs, dx=dP, scale=self.alpha)
+        # dQ = dS . K ; dK = dS^T . Q
+        self._bg(Sq, kd, Sk, dP, Sk, Sq * Sk, H * Sq * Sk, False, self.c_k, self.ldk, kd, Sk * self.ldk, True,
+                 self.c_dq, self.ldq, kd, Sq * self.ldq)
+        self._bg(Sk, kd, Sq, dP, Sk, Sq * Sk, H * Sq * Sk, True, self.c_q, self.ldq, kd, Sq * self.ldq, True,
+                 self.c_dk, self.ldk, kd, Sk * self.ldk)
+        if self.core16:
+            if self.self_attn:
+                K.cast(self.c_dqkv, self.dqkv)
+            else:
+                K.cast(self.c_dq, self.dq_); K.cast(self.c_dk, self.dk_); K.cast(self.c_dv, self.dv_)
+        qb, kb, vb = self.buf("QUERY"), self.buf("KEY"), self.buf("VALUE")
+        q2 = self.x("QUERY").view(-1, self.dq)
+        if self.self_attn:
+            if self.bias_in is not None:
+                K.bias_act_bwd(self.dqkv, None, None, self.buf("INPUT_BIAS").grad, ex.scratch_f32(), None,
+                               accumulate=self.acc.get("INPUT_BIAS", False))
+            K.matmul_tn(self.dqkv, q2, out=wg[:n_q + n_k + n_v].view(self.ldqkv, self.dq), accumulate=accw)
+            if qb.requires_grad:
+                K.matmul_nn(self.dqkv, self.wqkv, out=qb.grad.view(-1, self.dq), accumulate=self.acc["QUERY"])
+        else:
+            k2, v2 = self.x("KEY").view(-1, self.dk), self.x("VALUE").view(-1, self.dv)
+            K.matmul_tn(self.dq_, q2, out=wg[:n_q].view(H * kd, self.dq), accumulate=accw)
+            K.matmul_tn(self.dk_, k2, out=wg[n_q:n_q + n_k].view(H * kd, self.dk), accumulate=accw)
+            K.matmul_tn(self.dv_, v2, out=wg[n_q + n_k:n_q + n_k + n_v].view(H * vd, self.dv), accumulate=accw)
+            if qb.requires_grad:
+                K.matmul_nn(self.dq_, self.wq, out=qb.grad.view(-1, self.dq), accumulate=self.acc["QUERY"])
+            if kb.requires_grad:
+                K.matmul_nn(self.dk_, self.wk, out=kb.grad.view(-1, self.dk), accumulate=self.acc["KEY"])
+            if vb.requires_grad:
+                same = self.inputs["KEY"] == self.inputs["VALUE"]
+                K.matmul_nn(self.dv_, self.wv, out=vb.grad.view(-1, self.dv), accumulate=self.acc["VALUE"] or same)
+
+
+# ------------------------------------------------------------------------------------------ normalisation
+@register("LAYERNORM")
+class LayerNormOp(OpImpl):
+    """LayerNorm over the trailing dims; absorbs a preceding residual add when it is the add's only consumer."""
+    fused_add: Optional[OpImpl] = None
+
+    def setup(self):
+        x = self.x()
+        axes = sorted(int(a) for a in self.attrs["axes"])
+        nd = x.dim()
+        if axes != list(range(nd - len(axes), nd)):
+            raise NotImplementedError("layer_norm over non-trailing dims")
+        self.cols = 1
+        for a in axes:
+            self.cols *= x.shape[a]
+        self.rows = x.numel() // self.cols
+        self.eps = float(self.attrs.get("eps", 1e-5))
+        self.gamma = self.x("GAMMA").view(-1) if "GAMMA" in self.inputs else None
+        self.beta = self.x("BETA").view(-1) if "BETA" in self.inputs else None
+        y = self.alloc_out()
+        self.y2d = y.view(self.rows, self.cols)
+        self.mean = torch.empty(self.rows, dtype=torch.float32, device=self.ex.device)
+        self.rstd = torch.empty_like(self.mean)
+        self.ex.need_scratch(4 * K.layernorm_bwd_scratch(self.rows, self.cols) if self.ex.on_gpu else 0)
+
+    def forward(self):
+        if self.fused_add is not None:
+            add = self.fused_add
+            a, b = add.x("LHS_INPUT").view(self.rows, self.cols), add.x("RHS_INPUT").view(self.rows, self.cols)
+            K.layernorm_fwd(a, self.gamma, self.beta, self.eps, residual=b, xsum=self.x().view(self.rows, self.cols),
+                            out=self.y2d, mean=self.mean, rstd=self.rstd)
+        else:
+            K.layernorm_fwd(self.x().view(self.rows, self.cols), self.gamma, self.beta, self.eps, out=self.y2d,
+                            mean=self.mean, rstd=self.rstd)
+
+    def backward(self):
+        dy = self.out().grad.view(self.rows, self.cols)
+        x2d = self.x().view(self.rows, self.cols)
+        gb = self.buf("GAMMA") if self.gamma is not None else None
+        bb = self.buf("BETA") if self.beta is not None else None
+        dg = gb.grad.view(-1) if gb is not None and gb.requires_grad else None
+        db = bb.grad.view(-1) if bb is not None and bb.requires_grad else None
+        accp = self.acc.get("GAMMA", False)
+        if self.fused_add is not None:
+            add = self.fused_add
+            lb, rb = add.buf("LHS_INPUT"), add.buf("RHS_INPUT")
+            targets = [(b.grad.view(self.rows, self.cols), add.acc[s]) for s, b in (("LHS_INPUT", lb), ("RHS_INPUT", rb))
+                       if b.requires_grad]
+            if not targets:
+                targets = [(torch.empty_like(x2d), False)]
+            dx, a1 = targets[0]
+            dx2, a2 = targets[1] if len(targets) > 1 else (None, False)
+            if dx2 is not None and dx2.data_ptr() == dx.data_ptr():  # x + x: one buffer receives both
+                dx2, a2 = None, False
+            K.layernorm_bwd(dy, x2d, self.gamma, self.mean, self.rstd, dx, dg, db, self.ex.scratch_f32(),
+                            accumulate_dx=a1, accumulate_params=accp, dx2=dx2, accumulate_dx2=a2)
+        else:
+            xb = self.buf("INPUT")
+            dx = xb.grad.view(self.rows, self.cols) if xb.requires_grad else torch.empty_like(x2d)
+            K.layernorm_bwd(dy, x2d, self.gamma, self.mean, self.rstd, dx, dg, db, self.ex.scratch_f32(),
+                            accumulate_dx=self.acc.get("INPUT", False) and xb.requires_grad, accumulate_params=accp)
+
+
+# ------------------------------------------------------------------------------------------ pointwise
+_UNARY = {"RELU": "relu", "SIGMOID": "sigmoid", "TANH": "tanh", "ELU": "elu", "GELU": "gelu", "EXP": "exp",
+          "RSQRT": "rsqrt", "SIN": "sin", "COS": "cos", "SCALAR_MULTIPLY": "scalar_multiply", "SCALAR_ADD": "scalar_add",
+          "SCALAR_SUB": "scalar_sub", "SCALAR_TRUE_DIV": "scalar_truediv", "POW": "pow", "LOG": "log", "SQRT": "sqrt"}
+
+
+@register(*_UNARY.keys())
+class UnaryOp(OpImpl):
+    def setup(self):
+        self.op = _UNARY[self.type]
+        self.scalar = float(self.attrs.get("scalar") or 0.0)
+        self.alloc_out()
+
+    def forward(self):
+        K.unary_fwd(self.op, self.x(), out=self.out().data, scalar=self.scalar)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            K.unary_bwd(self.op, self.x(), self.out().data, self.out().grad.view_as(self.x()), dx=b.grad.view_as(self.x()),
+                        scalar=self.scalar, accumulate=self.acc["INPUT"])
+
+
+_BINARY = {"EW_ADD": "add", "EW_SUB": "sub", "EW_MUL": "mul", "EW_DIV": "div", "EW_MAX": "max", "EW_MIN": "min"}
+
+
+@register(*_BINARY.keys())
+class BinaryOp(OpImpl):
+    fused_into_ln = False
+
+    def setup(self):
+        self.op = _BINARY[self.type]
+        self.alloc_out()
+
+    def forward(self):
+        if self.fused_into_ln:
+            return  # the consuming LayerNorm writes this sum
+        K.binary_fwd(self.op, self.x("LHS_INPUT"), self.x("RHS_INPUT"), out=self.out().data)
+
+    def backward(self):
+        if self.fused_into_ln:
+            return
+        lb, rb = self.buf("LHS_INPUT"), self.buf("RHS_INPUT")
+        dy = self.out().grad
+        a, b = lb.data, rb.data
+        if a.shape != b.shape:
+            if lb.requires_grad:
+                self.ex.write_grad(lb, dy, self.acc["LHS_INPUT"]) if self.op in ("add", "sub") else self._bcast_unsupported()
+            if rb.requires_grad:
+                red = dy.float().reshape(-1, b.numel()).sum(0).to(dy.dtype) if self.op in ("add", "sub") else self._bcast_unsupported()
+                if self.op == "sub":
+                    red = -red
+                self.ex.write_grad(rb, red.view_as(b), self.acc["RHS_INPUT"])
+            return
+        if self.op == "add":
+            if lb.requires_grad:
+                self.ex.write_grad(lb, dy, self.acc["LHS_INPUT"])
+            if rb.requires_grad:
+                self.ex.write_grad(rb, dy, self.acc["RHS_INPUT"])
+            return
+        da = lb.grad.view_as(a) if lb.requires_grad else None
+        db = rb.grad.view_as(b) if rb.requires_grad else None
+        acc = self.acc.get("LHS_INPUT", False) or self.acc.get("RHS_INPUT", False)
+        if acc and da is not None and db is not None and self.acc["LHS_INPUT"] != self.acc["RHS_INPUT"]:
+            ta = torch.empty_like(a)
+            tb = torch.empty_like(b)
+            K.binary_bwd(self.op, a, b, dy, ta, tb)
+            self.ex.write_grad(lb, ta, self.acc["LHS_INPUT"])
+            self.ex.write_grad(rb, tb, self.acc["RHS_INPUT"])
+        else:
+            K.binary_bwd(self.op, a, b, dy, da, db, accumulate=acc)
+
+    def _bcast_unsupported(self):
+        raise NotImplementedError("backward of a broadcasting mul/div/max/min")
+
+
+@register("DROPOUT")
+class DropoutOp(OpImpl):
+    def setup(self):
+        self.p = float(self.attrs["rate"]) if self.ex.cfg.training else 0.0
+        self.salt = self.ex.next_salt() + int(self.attrs.get("seed", 0))
+        if self.p > 0:
+            self.alloc_out()
+        else:
+            self.out().data = self.x()
+
+    def forward(self):
+        if self.p > 0:
+            K.dropout(self.x(), self.p, self.salt, out=self.out().data, seed_tensor=self.ex.seed_tensor)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        dy = self.out().grad
+        if self.p > 0:
+            if self.acc["INPUT"]:
+                K.dropout(dy, self.p, self.salt, residual=b.grad.view_as(dy), out=b.grad.view_as(dy),
+                          seed_tensor=self.ex.seed_tensor)
+            else:
+                K.dropout(dy, self.p, self.salt, out=b.grad.view_as(dy), seed_tensor=self.ex.seed_tensor)
+        else:
+            self.ex.write_grad(b, dy, self.acc["INPUT"])
+
+
+@register("CAST")
+class CastOp(OpImpl):
+    def setup(self):
+        src = self.x()
+        want = self.ex.torch_dtype(self.attrs["dtype"])
+        if want == src.dtype:
+            self.out().data = src
+            self.alias = True
+        else:
+            self.alloc_out(dtype=want)
+            self.alias = False
+
+    def forward(self):
+        if not self.alias:
+            K.cast(self.x(), self.out().data)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        if self.alias:
+            self.ex.write_grad(b, self.out().grad, self.acc["INPUT"])
+        else:
+            K.cast(self.out().grad.view_as(self.x()), b.grad.view_as(self.x()), accumulate=self.acc["INPUT"])
+
+
+@register("EMBEDDING")
+class EmbeddingOp(OpImpl):
+    def setup(self):
+        self.aggr = "avg" if self.attrs.get("aggr") == "AVG" else "sum"
+        self.alloc_out()
+        self.table = self.x("WEIGHT")
+
+    def forward(self):
+        K.embedding_fwd(self.x(), self.table, self.out().data, aggr=self.aggr)
+
+    def backward(self):
+        wb = self.buf("WEIGHT")
+        if wb.requires_grad:
+            if not self.acc["WEIGHT"]:
+                wb.grad.zero_()
+            K.embedding_bwd(self.x(), self.out().grad.view_as(self.out().data), wb.grad, aggr=self.aggr)
+
+
+@register("SOFTMAX")
+class SoftmaxOp(OpImpl):
+    fused_loss = False  # set when this softmax feeds the loss: probabilities are then not materialised
+
+    def setup(self):
+        x = self.x()
+        d = int(self.attrs.get("dim", -1)) % x.dim()
+        if d != x.dim() - 1:
+            raise NotImplementedError("softmax over a non-trailing dim")
+        if self.fused_loss:
+            self.out().data = None
+        else:
+            self.alloc_out()
+
+    def forward(self):
+        if not self.fused_loss:
+            K.softmax_fwd(self.x(), out=self.out().data)
+
+    def probabilities(self):
+        if self.fused_loss:
+            return K.softmax_fwd(self.x())
+        return self.out().data
+
+    def backward(self):
+        if self.fused_loss:
+            return  # the loss wrote d(logits) directly
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            if self.acc["INPUT"]:
+                t = K.softmax_bwd(self.out().grad.view_as(self.x()), self.out().data)
+                self.ex.write_grad(b, t, True)
+            else:
+                K.softmax_bwd(self.out().grad.view_as(self.x()), self.out().data, dx=b.grad.view_as(self.x()))
+
+
+# ------------------------------------------------------------------------------------------ shape ops
+@register("FLAT", "RESHAPE")
+class ReshapeOp(OpImpl):
+    def setup(self):
+        sh = dict(self.outputs)["OUTPUT"]
+        self.out().data = self.x().view(list(sh.piece_sizes))
+
+    def forward(self):
+        pass
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            self.ex.write_grad(b, self.out().grad, self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ the executable
+class Executable:
+    """A computation graph lowered onto one device (one rank's shard of a parallel graph)."""
+
+    def __init__(self, graph, cfg: Optional[ExecConfig] = None, dist=None):
+        self.graph = graph
+        self.cfg = cfg or ExecConfig()
+        self.dist = dist
+        self.device = torch.device(self.cfg.device)
+        self.on_gpu = self.device.type == "cuda"
+        if self.on_gpu:
+            K.lib()  # fail loudly if the kernel library is missing
+        self.values: Dict[Value, _Buf] = {}
+        self.ops: Dict[int, OpImpl] = {}
+        self.order: List[int] = list(graph.topological_order())
+        self._scratch_bytes = 0
+        self._big_scratch_bytes = 0
+        self._big_scratch_slots = 0
+        self._salt = 0
+        self.step_count = 0
+        self.seed_tensor = torch.zeros(1, dtype=torch.int64, device=self.device) if self.on_gpu else None
+        self.alpha_tensor = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.layer_ms: Dict[int, float] = {}
+        self._graph = None
+        self._build()
+
+    # ---- dtype policy: FLOAT tensors run in the compute dtype
+    def torch_dtype(self, name: str):
+        if name == "FLOAT" and self.cfg.compute_dtype == "bf16":
+            return torch.bfloat16
+        if name == "HALF" and self.cfg.compute_dtype == "bf16":
+            return torch.bfloat16
+        return _TORCH_DT[name]
+
+    def head_shards(self, op) -> int:
+        w = self.values[op.inputs["WEIGHT"]]
+        return getattr(w, "head_shards", 1)
+
+    def next_salt(self) -> int:
+        self._salt += 1
+        return self._salt * 0x1000003
+
+    def need_scratch(self, nbytes: int):
+        self._scratch_bytes = max(self._scratch_bytes, int(nbytes))
+
+    def need_big_scratch(self, nbytes: int, slots: int):
+        self._big_scratch_bytes = max(self._big_scratch_bytes, int(nbytes))
+        self._big_scratch_slots = max(self._big_scratch_slots, slots)
+
+    def scratch_f32(self):
+        return self._scratch
+
+    def big_scratch(self, slot: int, like: torch.Tensor):
+        n = like.numel() * like.element_size()
+        return self._big[slot][:n].view(like.dtype).view(like.shape)
+
+    def write_grad(self, buf: _Buf, g: torch.Tensor, accumulate: bool):
+        tgt = buf.grad.view(-1)
+        src = g.reshape(-1)
+        if tgt.data_ptr() == src.data_ptr():
+            return
+        if accumulate:
+            K.axpby(src, tgt, 1.0, 1.0)
+        else:
+            tgt.copy_(src)
+
+    # ---- plan construction
+    def _build(self):
+        g = self.graph
+        nodes = {n["id"]: n for n in g.nodes()}
+        self.nodes = nodes
+        # 1. which values need gradients
+        req: Dict[Value, bool] = {}
+        for nid in self.order:
+            n = nodes[nid]
+            if n["type"] == "WEIGHT":
+                r = self.cfg.training
+            elif n["type"] == "INPUT":
+                r = False
+            else:
+                r = any(req[tuple(v)] for _, v in n["inputs"])
+            for s, sh, _ in n["outputs"]:
+                req[(nid, s)] = r and sh.dtype in ("FLOAT", "HALF", "DOUBLE", "BFLOAT16")
+                self.values[(nid, s)] = _Buf(None, req[(nid, s)])
+        # 2. parameters: flat arenas
+        self._build_params()
+        # 3. operator objects + fusion decisions
+        for nid in self.order:
+            n = nodes[nid]
+            cls = _REGISTRY.get(n["type"])
+            if cls is None:
+                raise NotImplementedError(f"no kernel implementation registered for operator {n['type']}")
+            self.ops[nid] = cls(self, nid, n)
+        self._fuse()
+        for nid in self.order:
+            self.ops[nid].setup()
+        # 4. loss
+        self._build_loss()
+        # 5. gradient buffers + accumulate flags
+        if self.cfg.training:
+            self._plan_gradients()
+        self._scratch = torch.empty(max(self._scratch_bytes // 4, 1), dtype=torch.float32, device=self.device)
+        self._big = [torch.empty(max(self._big_scratch_bytes, 1), dtype=torch.uint8, device=self.device)
+                     for _ in range(max(self._big_scratch_slots, 1))]
+
+    def _build_params(self):
+        nodes, dev = self.nodes, self.device
+        self.param_nodes = [nid for nid in self.order if nodes[nid]["type"] == "WEIGHT"]
+        offs, total = {}, 0
+        for nid in self.param_nodes:
+            sh = nodes[nid]["outputs"][0][1]
+            n = 1
+            for s in self.local_weight_shape(nid):
+                n *= s
+            offs[nid] = (total, n)
+            total += (n + 63) // 64 * 64  # keep every parameter 256-byte aligned in the arena
+        self.param_offsets = offs
+        self.num_params = total
+        mixed = self.cfg.compute_dtype == "bf16"
+        self.master = torch.zeros(max(total, 1), dtype=torch.float32, device=dev)
+        self.shadow = torch.zeros(max(total, 1), dtype=torch.bfloat16, device=dev) if mixed else None
+        if self.cfg.training:
+            self.grads = torch.zeros(max(total, 1), dtype=torch.bfloat16 if mixed else torch.float32, device=dev)
+            self.opt_m = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) \
+                if (self.cfg.optimizer.kind == "adam" or self.cfg.optimizer.momentum > 0) else None
+            self.opt_v = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) if self.cfg.optimizer.kind == "adam" else None
+        for i, nid in enumerate(self.param_nodes):
+            o, n = offs[nid]
+            shape = self.local_weight_shape(nid)
+            full = initialize(list(nodes[nid]["outputs"][0][1].sizes), nodes[nid]["attrs"].get("initializer"),
+                              base_seed=self.cfg.seed, ordinal=i)
+            self.master[o:o + n].copy_(self.shard_weight(nid, full).reshape(-1))
+            b = self.values[(nid, "OUTPUT")]
+            b.data = (self.shadow if mixed else self.master)[o:o + n].view(shape)
+            if self.cfg.training:
+                b.grad = self.grads[o:o + n].view(shape)
+        if mixed:
+            self.shadow.copy_(self.master)
+
+    # single-device: a weight's local shape is its full shape; the distributed executable overrides both
+    def local_weight_shape(self, nid):
+        return list(self.nodes[nid]["outputs"][0][1].sizes)
+
+    def shard_weight(self, nid, full):
+        return full
+
+    def _fuse(self):
+        g = self.graph
+        for nid in self.order:
+            op = self.ops[nid]
+            if isinstance(op, LayerNormOp):
+                src = op.inputs["INPUT"]
+                prod = self.ops[src[0]]
+                if (isinstance(prod, BinaryOp) and prod.type == "EW_ADD" and len(g.consumers(src)) == 1
+                        and self._same_shape(prod.inputs["LHS_INPUT"], prod.inputs["RHS_INPUT"])):
+                    op.fused_add = prod
+                    prod.fused_into_ln = True
+        # a trailing softmax that only feeds the loss is fused into it
+        self.loss_value: Optional[Value] = None
+        if self.cfg.loss:
+            sinks = [tuple(v) for v in g.sink_values() if self.nodes[v[0]]["type"] not in ("WEIGHT", "INPUT")]
+            named = [v for v in sinks if self.nodes[v[0]]["name"] == "out_prob"]
+            self.loss_value = (named or sinks)[-1] if sinks else None
+            if self.loss_value is not None:
+                op = self.ops[self.loss_value[0]]
+                if isinstance(op, SoftmaxOp) and self.cfg.loss == "sparse_categorical_crossentropy":
+                    op.fused_loss = True
+
+    def _same_shape(self, a: Value, b: Value) -> bool:
+        return list(self.graph.shape(a).piece_sizes) == list(self.graph.shape(b).piece_sizes)
+
+    def _build_loss(self):
+        self.loss_rows = None
+        self.labels = None
+        if self.loss_value is None:
+            return
+        op = self.ops[self.loss_value[0]]
+        sh = self.graph.shape(self.loss_value)
+        sizes = list(sh.piece_sizes)
+        cols = sizes[-1]
+        rows = 1
+        for s in sizes[:-1]:
+            rows *= s
+        self.loss_shape = (rows, cols)
+        self.loss_rows = torch.zeros(rows, dtype=torch.float32, device=self.device)
+        if self.cfg.loss == "sparse_categorical_crossentropy":
+            self.labels = torch.zeros(rows, dtype=torch.int32, device=self.device)
+        else:
+            self.labels = torch.zeros(rows, cols, dtype=self.torch_dtype(sh.dtype), device=self.device)
+        self.loss_scale = 1.0 / rows
+
+    def _plan_gradients(self):
+        pool = _GradPool(self.device)
+        written: Dict[Value, bool] = {}
+        # the loss seeds the gradient of its input
+        seeds: List[Value] = []
+        if self.loss_value is not None:
+            op = self.ops[self.loss_value[0]]
+            tgt = op.inputs["INPUT"] if (isinstance(op, SoftmaxOp) and op.fused_loss) else self.loss_value
+            seeds.append(tgt)
+        live: Dict[Value, torch.Tensor] = {}
+
+        def ensure(v: Value):
+            b = self.values[v]
+            if b.grad is None and b.requires_grad:
+                ref = b.data if b.data is not None else None
+                sizes = list(self.graph.shape(v).piece_sizes)
+                n = 1
+                for s in sizes:
+                    n *= s
+                dt = ref.dtype if ref is not None else self.torch_dtype(self.graph.shape(v).dtype)
+                flat = pool.take(n, dt)
+                b.grad = flat.view(sizes)
+                live[v] = flat
+
+        for v in seeds:
+            ensure(v)
+            written[v] = True
+        for nid in reversed(self.order):
+            op = self.ops[nid]
+            if op.type in ("WEIGHT", "INPUT"):
+                continue
+            # an op whose outputs received no gradient has nothing to propagate
+            outs = [(nid, s) for s, _ in op.outputs]
+            op.has_grad = any(written.get(o, False) for o in outs)
+            if isinstance(op, BinaryOp) and op.fused_into_ln:
+                op.has_grad = False
+            if op.has_grad or (isinstance(op, SoftmaxOp) and op.fused_loss):
+                targets = list(op.inputs.items())
+                if isinstance(op, LayerNormOp) and op.fused_add is not None:
+                    # the LayerNorm writes straight into the add's operands
+                    add = op.fused_add
+                    for s, v in add.inputs.items():
+                        if self.values[v].requires_grad:
+                            ensure(v)
+                            add.acc[s] = written.get(v, False)
+                            written[v] = True
+                    targets = [(s, v) for s, v in targets if s != "INPUT"]
+                if isinstance(op, SoftmaxOp) and op.fused_loss:
+                    targets = []
+                seen_here = set()
+                for s, v in targets:
+                    if not self.values[v].requires_grad:
+                        continue
+                    ensure(v)
+                    op.acc[s] = written.get(v, False) or (v in seen_here)
+                    seen_here.add(v)
+                for v in seen_here:
+                    written[v] = True
+            # outputs of this node are dead once its backward ran
+            for o in outs:
+                if o in live:
+                    pool.give(live.pop(o))
+        self.grad_pool_bytes = pool.total_bytes
+
+    # ---- execution
+    def set_inputs(self, inputs: Dict[str, torch.Tensor], labels: Optional[torch.Tensor] = None):
+        for nid in self.order:
+            n = self.nodes[nid]
+            if n["type"] != "INPUT":
+                continue
+            name = n["name"] or f"input{nid}"
+            if name in inputs:
+                dst = self.values[(nid, "OUTPUT")].data
+                src = inputs[name]
+                dst.copy_(src.reshape(dst.shape), non_blocking=True)
+        if labels is not None and self.labels is not None:
+            self.labels.copy_(labels.reshape(self.labels.shape), non_blocking=True)
+
+    def forward(self):
+        if self.cfg.profile_layers:
+            return self._forward_profiled()
+        for nid in self.order:
+            self.ops[nid].forward()
+
+    def _forward_profiled(self):
+        for nid in self.order:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.ops[nid].forward()
+            e1.record()
+            e1.synchronize()
+            self.layer_ms[nid] = e0.elapsed_time(e1)
+
+    def compute_loss(self):
+        """Loss forward (per-row values) and, in training, the gradient of the loss input."""
+        if self.loss_value is None:
+            return None
+        op = self.ops[self.loss_value[0]]
+        rows, cols = self.loss_shape
+        kind = self.cfg.loss
+        if isinstance(op, SoftmaxOp) and op.fused_loss:
+            logits = op.x().view(rows, cols)
+            dl = self.values[op.inputs["INPUT"]].grad.view(rows, cols) if self.cfg.training else None
+            K.softmax_ce(logits, self.labels, self.loss_rows, dlogits=dl, grad_scale=self.loss_scale)
+        else:
+            pred = self.values[self.loss_value].data.view(rows, cols)
+            K.loss_fwd(kind, pred, self.labels, self.loss_rows)
+            if self.cfg.training:
+                K.loss_bwd(kind, pred, self.labels, self.values[self.loss_value].grad.view(rows, cols), self.loss_scale)
+        return self.loss_rows
+
+    def backward(self):
+        for nid in reversed(self.order):
+            op = self.ops[nid]
+            if getattr(op, "has_grad", False):
+                op.backward()
+
+    def profile_step(self):
+        """Run one eager step with CUDA events around every operator's forward and backward.
+
+        Returns ``{"by_type": {(op type, phase): ms}, "by_node": {(node id, phase): ms}, "total_ms": ms}``.
+        This is the per-layer timing the reference collects through its ``profile(...)`` wrapper
+        (lib/task-spec/include/task-spec/profiling.h:11-24) and the source of measured operator costs."""
+        self._pre_step()
+        recs = []
+
+        def timed(key, fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            recs.append((key, e0, e1))
+
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for nid in self.order:
+            timed((nid, "fwd"), self.ops[nid].forward)
+        timed((-1, "loss"), self.compute_loss)
+        for nid in reversed(self.order):
+            op = self.ops[nid]
+            if getattr(op, "has_grad", False):
+                timed((nid, "bwd"), op.backward)
+        timed((-2, "sync_gradients"), self.sync_gradients)
+        timed((-3, "update"), self.update)
+        t1.record()
+        torch.cuda.synchronize()
+        by_type, by_node = {}, {}
+        for (nid, phase), e0, e1 in recs:
+            ms = e0.elapsed_time(e1)
+            typ = self.nodes[nid]["type"] if nid >= 0 else phase
+            by_type[(typ, phase)] = by_type.get((typ, phase), 0.0) + ms
+            by_node[(nid, phase)] = ms
+        return {"by_type": by_type, "by_node": by_node, "total_ms": t0.elapsed_time(t1)}
+
+    def sync_gradients(self):
+        """Hook for the distributed executable (gradient all-reduce of replicated weights)."""
+
+    def update(self):
+        o = self.cfg.optimizer
+        self.step_count += 1
+        shadow = self.shadow
+        if o.kind == "adam":
+            K.adam_update(self.master, self.opt_m, self.opt_v, self.grads, shadow, 0.0, o.beta1, o.beta2, o.epsilon,
+                          o.weight_decay, 1.0, alpha_tensor=self.alpha_tensor)
+        else:
+            K.sgd_update(self.master, self.opt_m, self.grads, shadow, o.lr, o.momentum, o.nesterov, o.weight_decay)
+
+    def _pre_step(self):
+        """Per-step scalars that a captured graph reads from device memory."""
+        o = self.cfg.optimizer
+        t = self.step_count + 1
+        if o.kind == "adam":
+            alpha_t = o.lr * math.sqrt(1.0 - o.beta2 ** t) / (1.0 - o.beta1 ** t)
+            self.alpha_tensor.fill_(alpha_t)
+        if self.seed_tensor is not None:
+            self.seed_tensor.fill_((self.cfg.seed * 7919 + t * 104729) & 0x7FFFFFFFFFFFFFFF)
+
+    def _step_body(self):
+        self.forward()
+        self.compute_loss()
+        self.backward()
+        self.sync_gradients()
+        self.update()
+
+    def train_step(self, inputs: Optional[Dict[str, torch.Tensor]] = None, labels: Optional[torch.Tensor] = None):
+        """One optimisation step; returns the per-row loss tensor (device)."""
+        if inputs is not None or labels is not None:
+            self.set_inputs(inputs or {}, labels)
+        self._pre_step()
+        if self.cfg.use_cuda_graph and self.on_gpu:
+            if not getattr(self, "_warmed", False):
+                # the first step runs eagerly (lazy library initialisation must not happen during capture);
+                # the graph is captured at the second call, which then replays it
+                self._warmed = True
+                self._step_body()
+                return self.loss_rows
+            if self._graph is None:
+                torch.cuda.synchronize()
+                self._graph = torch.cuda.CUDAGraph()
+                cap_stream = torch.cuda.Stream()
+                cap_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(cap_stream):
+                    count = self.step_count
+                    l0 = K.launch_count()
+                    with torch.cuda.graph(self._graph, stream=cap_stream):
+                        self._step_body()
+                    self.launches_per_step = K.launch_count() - l0
+                    self.step_count = count
+                torch.cuda.current_stream().wait_stream(cap_stream)
+            self._graph.replay()
+            self.step_count += 1
+        else:
+            self._step_body()
+        return self.loss_rows
+
+    def infer(self, inputs: Dict[str, torch.Tensor]):
+        self.set_inputs(inputs)
+        self.forward()
+        op = self.ops[self.loss_value[0]] if self.loss_value is not None else None
+        if isinstance(op, SoftmaxOp):
+            return op.probabilities()
+        return self.values[self.loss_value].data if self.loss_value else None
+
+    def mean_loss(self) -> float:
+        return float(self.loss_rows.mean().item())
+
+    # ---- parameter access (checkpointing, tests)
+    def named_parameters(self):
+        for nid in self.param_nodes:
+            o, n = self.param_offsets[nid]
+            name = self.nodes[nid]["name"] or f"weight{nid}"
+            yield name, self.master[o:o + n].view(self.local_weight_shape(nid))
+
+    def named_gradients(self):
+        for nid in self.param_nodes:
+            o, n = self.param_offsets[nid]
+            name = self.nodes[nid]["name"] or f"weight{nid}"
+            yield name, self.grads[o:o + n].view(self.local_weight_shape(nid))
+
+    def state_dict(self):
+        sd = {"master": self.master, "step": self.step_count}
+        if self.cfg.training:
+            if self.opt_m is not None:
+                sd["opt_m"] = self.opt_m
+            if self.opt_v is not None:
+                sd["opt_v"] = self.opt_v
+        return sd
+
+    def load_state_dict(self, sd):
+        self.master.copy_(sd["master"])
+        if self.shadow is not None:
+            self.shadow.copy_(self.master)
+        self.step_count = int(sd.get("step", 0))
+        if self.cfg.training:
+            if "opt_m" in sd and self.opt_m is not None:
+                self.opt_m.copy_(sd["opt_m"])
+            if "opt_v" in sd and self.opt_v is not None:
+                self.opt_v.copy_(sd["opt_v"])
