@@ -48,6 +48,21 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   long long num_tiles;
   int *err;
+  // --- fused collectives (all optional) ---
+  // Scatter epilogue (GEMM -> reduce-scatter): when scatter_rows > 0 the output rows are split into blocks of
+  // scatter_rows rows owned by rank (row / scatter_rows); a tile is written into its owner's staging buffer
+  // scatter[owner] (a peer pointer over NVLink) at row  scatter_src * scatter_rows + row % scatter_rows, i.e.
+  // into slot `scatter_src` of the owner's [world][scatter_rows][N] partial-sum stage.
+  void *scatter[8];
+  int scatter_rows;
+  int scatter_src;
+  // Gated A operand (all-gather -> GEMM): rows of A arrive in blocks of gate_rows rows pushed by the peers;
+  // block s may be read once gate_flags[s] >= *gate_sync + 1.  mb_rotate starts the tile order at the
+  // m-blocks of the local shard so that math begins before any remote data has landed.
+  const unsigned long long *gate_flags;
+  unsigned long long *gate_sync;  // [0] epoch (u64), word 3 (u32) = CTAs finished
+  int gate_rows;
+  int mb_rotate;
 };
 
 // ----------------------------------------------------------------------------
@@ -212,6 +227,7 @@ __device__ __forceinline__ void tile_coords(long long tile, const GemmArgs &p, i
   int r = t - g * per_group;
   mb = first_m + (r % gsize);
   nb_ = r / gsize;
+  if (p.mb_rotate) mb = (mb + p.mb_rotate) % p.tiles_m;
 }
 
 template <int ES, int BN, bool A_MN, bool B_MN>
@@ -266,9 +282,35 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t gate_seen = 0;
       for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         int mb, nb_, bh, bb;
         tile_coords(tile, p, mb, nb_, bh, bb);
+        if (p.gate_flags) {
+          // rows of this m-block come from rank src's push: wait (bounded) until its flag reaches this call's epoch
+          const int src = (mb * BM) / p.gate_rows;
+          if (!((gate_seen >> src) & 1u)) {
+            const unsigned long long want = *p.gate_sync + 1;
+            uint64_t t0 = ffk_globaltimer();
+            while (true) {
+              unsigned long long v;
+              asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p.gate_flags + src) : "memory");
+              if (v >= want) break;
+              if (*abort_flag || ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (p.err) atomicCAS(p.err, 0, (int)FFK_ERR_TIMEOUT_PEER);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            gate_seen |= 1u << src;
+            // the pushed rows were written by a peer through the generic proxy; order them before the
+            // async-proxy (TMA) reads that follow
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
           if (!ok) break;
@@ -366,7 +408,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const long long c_base = (long long)bh * p.c_sh + (long long)bb * p.c_sb;
+      long long c_base = (long long)bh * p.c_sh + (long long)bb * p.c_sb;
+      void *Cout = p.C;
+      if (p.scatter_rows) {  // this tile belongs to rank `owner`: write it into slot scatter_src of the owner's stage
+        const int owner = (mb * BM) / p.scatter_rows;
+        Cout = p.scatter[owner];
+        c_base = (long long)(p.scatter_src - owner) * p.scatter_rows * p.ldc;
+      }
       const long long a_base = (long long)bh * p.add_sh + (long long)bb * p.add_sb;
       const int row0 = mb * BM + q * 32;          // first row of this warp's quarter
       const int rows_left = p.M - row0 - rsub;     // iteration i is valid iff 4*i < rows_left
@@ -399,7 +447,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
           }
         }
         if (simple && vec4) {
-          bf16 *cp = (bf16 *)p.C + c_base + (long long)(row0 + rsub) * p.ldc + col;
+          bf16 *cp = (bf16 *)Cout + c_base + (long long)(row0 + rsub) * p.ldc + col;
           const long long step = 4 * p.ldc;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -443,7 +491,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
               }
             }
             if (p.out_fp32) {
-              float *c = (float *)p.C + coff;
+              float *c = (float *)Cout + coff;
               if (vec4 && (((uintptr_t)c) & 15) == 0) {
                 float4 o = make_float4(v[0], v[1], v[2], v[3]);
                 if (p.accumulate) {
@@ -455,7 +503,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
                 for (int j = 0; j < 4; ++j) if (col + j < p.N) c[j] = p.accumulate ? c[j] + v[j] : v[j];
               }
             } else {
-              bf16 *c = (bf16 *)p.C + coff;
+              bf16 *c = (bf16 *)Cout + coff;
               if (vec4 && (((uintptr_t)c) & 7) == 0) {
                 if (p.accumulate) {
                   uint2 u = *reinterpret_cast<uint2 *>(c);
@@ -484,6 +532,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
                  : "memory");
+  }
+  if (p.gate_sync && threadIdx.x == 0) {
+    // the last CTA to leave advances the epoch the next call will wait for
+    unsigned int *done = (unsigned int *)p.gate_sync + 3;
+    __threadfence();
+    if (atomicAdd(done, 1u) == gridDim.x - 1) {
+      *p.gate_sync = *p.gate_sync + 1;
+      *done = 0;
+    }
   }
 }
 
@@ -638,6 +695,14 @@ struct FfkGemmDesc {
   int accumulate;
   int bn;                 // tile N: 0 = choose, else 64/128/256
   int max_ctas;           // 0 = one per SM
+  // fused collectives, see GemmArgs
+  void *scatter[8];
+  int scatter_rows;
+  int scatter_src;
+  const void *gate_flags;
+  void *gate_sync;
+  int gate_rows;
+  int mb_rotate;
 };
 
 // Returns 0 on success, a CUDA/driver error code otherwise, -2 for an
@@ -657,6 +722,7 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
     a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr;
+    if (d->scatter_rows || d->gate_flags) return -2;  // the fused-collective paths need TMA-addressable operands
     SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
     dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
     if (es == 2) gemm_simt_kernel<bf16><<<grid, block, 0, stream>>>(o, a);
@@ -688,6 +754,12 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
   a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
   a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
+  for (int i = 0; i < 8; ++i) a.scatter[i] = d->scatter[i];
+  a.scatter_rows = d->scatter_rows; a.scatter_src = d->scatter_src;
+  a.gate_flags = (const unsigned long long *)d->gate_flags; a.gate_sync = (unsigned long long *)d->gate_sync;
+  a.gate_rows = d->gate_rows; a.mb_rotate = d->mb_rotate;
+  if (a.scatter_rows && (a.scatter_rows % BM != 0 || a.nh * a.nb != 1)) return -2;
+  if (a.gate_flags && (a.gate_rows % BM != 0 || a.nh * a.nb != 1 || d->a_mn)) return -2;
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_gemm_err);
   a.err = (int *)errp;

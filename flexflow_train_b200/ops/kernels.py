@@ -52,6 +52,9 @@ class GemmDesc(ctypes.Structure):
         ("ld_add", c_longlong), ("add_sh", c_longlong), ("add_sb", c_longlong),
         ("alpha", c_float), ("act", c_int), ("out_fp32", c_int), ("accumulate", c_int),
         ("bn", c_int), ("max_ctas", c_int),
+        # fused collectives (see gemm_sm100.cu): scatter epilogue and gated A operand
+        ("scatter", c_void_p * 8), ("scatter_rows", c_int), ("scatter_src", c_int),
+        ("gate_flags", c_void_p), ("gate_sync", c_void_p), ("gate_rows", c_int), ("mb_rotate", c_int),
     ]
 
 
@@ -153,11 +156,18 @@ def _cuda_contig(*ts):
 def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, nh=1, nb=1,
              a_sh=0, a_sb=0, b_sh=0, b_sb=0, c_sh=0, c_sb=0, C2=None, bias=None, addend=None,
              ld_add=0, add_sh=0, add_sb=0, alpha=1.0, act=0, out_fp32=False, accumulate=False,
-             bn=0, max_ctas=0):
-    """D = epilogue(alpha * A[M,K] . B[N,K]^T) on raw pointers; see gemm_sm100.cu."""
+             bn=0, max_ctas=0, scatter=None, scatter_rows=0, scatter_src=0, gate_flags=None, gate_sync=None,
+             gate_rows=0, mb_rotate=0):
+    """D = epilogue(alpha * A[M,K] . B[N,K]^T) on raw pointers; see gemm_sm100.cu.
+
+    scatter / scatter_rows / scatter_src: write each output tile into the owning rank's staging buffer
+    (GEMM -> reduce-scatter).  gate_flags / gate_sync / gate_rows / mb_rotate: wait for pushed row blocks of A
+    (all-gather -> GEMM)."""
+    sc = (c_void_p * 8)(*([int(p) for p in scatter] + [None] * (8 - len(scatter)))) if scatter else (c_void_p * 8)()
     d = GemmDesc(M, N, K, nh, nb, es, int(a_mn), int(b_mn), A, lda, a_sh, a_sb, B, ldb, b_sh, b_sb,
                  C, ldc, c_sh, c_sb, C2, bias, addend, ld_add, add_sh, add_sb, alpha, act, int(out_fp32),
-                 int(accumulate), bn, max_ctas)
+                 int(accumulate), bn, max_ctas, sc, scatter_rows, scatter_src, gate_flags, gate_sync, gate_rows,
+                 mb_rotate)
     _check(lib().ffk_gemm(ctypes.byref(d), _stream()), "ffk_gemm")
 
 

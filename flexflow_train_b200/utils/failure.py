@@ -1,0 +1,163 @@
+"""Failure detection and host-side fault injection.
+
+The reference has neither: its CUDA / NCCL error checks abort the process
+(lib/kernels/include/kernels/device.h:88-110, lib/kernels/include/kernels/nccl.h:9-20).  Here
+
+* device-side waits on peers are bounded; when one runs out the kernel writes a code to a status word and
+  returns, and :meth:`DistContext.check_status` turns it into :class:`CommTimeoutError` on the host;
+* ranks publish heartbeats through the ``torch.distributed`` store; :class:`HeartbeatMonitor` reports ranks whose
+  heartbeat is older than a deadline, so survivors learn of a lost rank *before* their next launch;
+* :class:`FaultInjector` makes failures on the host only (raise, stall, drop a heartbeat, corrupt a file) --
+  nothing here ever faults, traps or hangs a GPU.
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+
+class CommTimeoutError(RuntimeError):
+    """A bounded device-side wait on a peer expired."""
+
+
+class RankFailure(RuntimeError):
+    """One or more ranks stopped publishing heartbeats."""
+
+    def __init__(self, ranks: List[int]):
+        super().__init__(f"ranks {ranks} are not responding")
+        self.ranks = ranks
+
+
+class InjectedFault(RuntimeError):
+    """Raised by FaultInjector at a configured point."""
+
+
+class HeartbeatMonitor:
+    """Heartbeats over a key-value store (``torch.distributed.TCPStore`` / ``HashStore`` / any object with
+    ``set(key, value)`` and ``get(key)``).  ``beat()`` is called once per step; ``dead_ranks()`` lists ranks whose
+    last beat is older than ``timeout_s`` (or that never beat after ``grace_s``)."""
+
+    def __init__(self, store, rank: int, world_size: int, timeout_s: float = 10.0, grace_s: float = 30.0, prefix: str = "hb"):
+        self.store, self.rank, self.world_size = store, rank, world_size
+        self.timeout_s, self.grace_s, self.prefix = timeout_s, grace_s, prefix
+        self.start = time.time()
+        self.suppressed = False  # set by the fault injector to emulate a silent rank
+
+    def beat(self, step: int = 0):
+        if self.suppressed:
+            return
+        self.store.set(f"{self.prefix}/{self.rank}", f"{time.time():.6f}:{step}")
+
+    def last_beat(self, rank: int) -> Optional[float]:
+        try:
+            v = self.store.get(f"{self.prefix}/{rank}")
+        except Exception:
+            return None
+        if isinstance(v, bytes):
+            v = v.decode()
+        try:
+            return float(str(v).split(":")[0])
+        except ValueError:
+            return None
+
+    def dead_ranks(self, now: Optional[float] = None) -> List[int]:
+        now = time.time() if now is None else now
+        dead = []
+        for r in range(self.world_size):
+            if r == self.rank:
+                continue
+            t = self.last_beat(r)
+            if t is None:
+                if now - self.start > self.grace_s:
+                    dead.append(r)
+            elif now - t > self.timeout_s:
+                dead.append(r)
+        return dead
+
+    def check(self):
+        dead = self.dead_ranks()
+        if dead:
+            raise RankFailure(dead)
+
+
+class DictStore:
+    """In-process store with the TCPStore surface used here; lets the monitor be tested without sockets."""
+
+    def __init__(self):
+        self._d: Dict[str, str] = {}
+        self._lock = threading.Lock()
+
+    def set(self, k, v):
+        with self._lock:
+            self._d[k] = v
+
+    def get(self, k):
+        with self._lock:
+            if k not in self._d:
+                raise KeyError(k)
+            return self._d[k]
+
+
+@dataclass
+class FaultInjector:
+    """Host-side fault plan: ``{"step": n, "kind": ...}`` entries fire when ``maybe_fail(step)`` reaches them.
+
+    kinds: ``raise`` (throw InjectedFault), ``stall`` (sleep ``seconds``), ``exit`` (leave the process between
+    steps with status ``code``), ``silence`` (stop heartbeats), ``corrupt`` (flip bytes of ``path``)."""
+    plan: List[dict] = field(default_factory=list)
+    rank: int = 0
+    monitor: Optional[HeartbeatMonitor] = None
+    fired: List[dict] = field(default_factory=list)
+
+    def maybe_fail(self, step: int):
+        for f in self.plan:
+            if f.get("step") != step or f.get("rank", self.rank) != self.rank or f in self.fired:
+                continue
+            self.fired.append(f)
+            kind = f.get("kind", "raise")
+            if kind == "raise":
+                raise InjectedFault(f"injected fault at step {step} on rank {self.rank}")
+            if kind == "stall":
+                time.sleep(float(f.get("seconds", 1.0)))
+            elif kind == "exit":
+                os._exit(int(f.get("code", 17)))
+            elif kind == "silence" and self.monitor is not None:
+                self.monitor.suppressed = True
+            elif kind == "corrupt":
+                corrupt_file(f["path"], int(f.get("offset", 64)), int(f.get("nbytes", 16)))
+
+
+def corrupt_file(path: str, offset: int = 64, nbytes: int = 16):
+    size = os.path.getsize(path)
+    offset = min(offset, max(size - nbytes, 0))
+    with open(path, "r+b") as fh:
+        fh.seek(offset)
+        data = bytearray(fh.read(nbytes))
+        for i in range(len(data)):
+            data[i] ^= 0xFF
+        fh.seek(offset)
+        fh.write(bytes(data))
+
+
+def run_with_recovery(step_fn: Callable[[int], None], num_steps: int, *, save_fn: Callable[[int], None],
+                      restore_fn: Callable[[], int], checkpoint_every: int = 1, max_restarts: int = 3,
+                      recoverable=(InjectedFault, CommTimeoutError, RankFailure)) -> dict:
+    """Drive ``step_fn`` for ``num_steps`` steps; on a recoverable failure restore the last checkpoint and continue.
+    Returns ``{"restarts": n, "steps_run": total step invocations}``."""
+    restarts, runs, step = 0, 0, 0
+    while step < num_steps:
+        try:
+            step_fn(step)
+            runs += 1
+            step += 1
+            if step % checkpoint_every == 0:
+                save_fn(step)
+        except recoverable:
+            restarts += 1
+            if restarts > max_restarts:
+                raise
+            step = restore_fn()
+    return {"restarts": restarts, "steps_run": runs}
