@@ -135,10 +135,11 @@ def main():
     model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind="adam", lr=lr), dist=dctx)
     ex = model.executable
     vocab = mcfg["vocab_size"]
-    local_batch = ex.local_batch if hasattr(ex, "local_batch") else global_batch
+    # every rank is handed the global batch (token ids are tiny); the strategy's Repartition keeps the local slice
+    local_batch = global_batch
 
     # synthetic data of the named shape: token ids uniform over the vocabulary, next-token labels
-    gen = torch.Generator().manual_seed(1234 + rank)
+    gen = torch.Generator().manual_seed(1234)
     n_host = 4
     if model_name == "bert":
         host_batches = [({"input_ids": torch.randint(0, 30522, (local_batch, seq, 1), generator=gen, dtype=torch.int32).pin_memory(),

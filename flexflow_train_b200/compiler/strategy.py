@@ -1,0 +1,185 @@
+"""Strategy selection: from a computation graph to the parallel computation graph that will be executed.
+
+``optimize`` is the counterpart of the reference's entry point
+(lib/compiler/src/compiler/compiler.cc:10-38): it dispatches on the algorithm (Unity best-first search over
+substitutions, MCMC over mapped PCGs, or plain data parallelism -- which the reference declares but leaves
+unimplemented).  The search is seeded with the canonical strategies that the substitution rules can express
+(pure data parallel, Megatron-style tensor parallel), each scored by the same machine-mapping DP, so a small
+budget already returns a sensible plan on deep repeated-layer models where blind search would not.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Dict, List, Optional, Tuple
+
+from .. import _ffcore as core
+
+
+def machine_for(world: int, num_nodes: int = 1) -> "core.MachineSpecification":
+    return core.MachineSpecification(num_nodes, max(world // num_nodes, 1))
+
+
+def _rules_named(rules, pred: Callable[[str], bool]):
+    return [r for r in rules if pred(r.name)]
+
+
+def cancellation_rules(rules):
+    return _rules_named(rules, lambda n: n.startswith("cancel"))
+
+
+def data_parallel_rules(rules, degree: int):
+    """Every generated rule that shards dim 0 (the sample dim) `degree` ways."""
+    sfx = (f"_0_{degree}", f"_0_{degree}_bias", f"_0_{degree}_affine")
+
+    def pred(n: str) -> bool:
+        if n.startswith("partition_attention_combine_") or n.startswith("partition_conv2d_combine_"):
+            return n.split("_")[3] == str(degree)
+        return n.startswith("partition_") and "_combine" in n and n.endswith(sfx)
+
+    return _rules_named(rules, pred)
+
+
+def apply_where(graph, rule, pred: Callable[[dict], bool], max_total_degree: int = 0):
+    """Apply `rule` at every match whose first pattern node satisfies pred(node dict)."""
+    changed = True
+    while changed:
+        changed = False
+        for m in core.find_pattern_matches(rule, graph):
+            if not pred(graph.node(m.nodes[0])):
+                continue
+            ng = core.apply_substitution(graph, rule, m)
+            if ng is None:
+                continue
+            if max_total_degree and any(o[1].total_degree > max_total_degree for n in ng.nodes() for o in n["outputs"]):
+                continue
+            graph = ng
+            changed = True
+            break
+    return graph
+
+
+def data_parallel_strategy(cg, world: int, rules=None):
+    ms = machine_for(world)
+    rules = rules or core.get_substitution_set(ms)
+    pcg = core.pcg_from_computation_graph(cg)
+    sel = data_parallel_rules(rules, world) + cancellation_rules(rules)
+    return core.apply_rules_exhaustively(pcg, sel, 100000, world)
+
+
+def tensor_parallel_strategy(cg, world: int, rules=None):
+    """Megatron-style template expressed with the substitution rules: attention heads sharded
+    (replicate-attention-reduce), the first Linear of each MLP column-parallel (replicate-linear-combine), the
+    second row-parallel (partition-linear-reduce), the pointwise ops between them sharded on the feature dim."""
+    ms = machine_for(world)
+    rules = rules or core.get_substitution_set(ms)
+    by_name = {r.name: r for r in rules}
+    g = core.pcg_from_computation_graph(cg)
+    W = world
+    for bias in ("", "_bias"):
+        r = by_name.get(f"replicate_attention_reduce_{W}{bias}")
+        if r is not None:
+            g = apply_where(g, r, lambda n: True, W)
+    # Linear layers: a Linear fed (through pointwise ops) by another Linear becomes row-parallel, its producer
+    # column-parallel
+    def producer_linear(graph, node):
+        v = dict((s, tuple(x)) for s, x in node["inputs"]).get("INPUT")
+        while v is not None:
+            p = graph.node(v[0])
+            if p["type"] == "LINEAR":
+                return p
+            if p["type"] in ("DROPOUT", "RELU", "GELU", "SIGMOID", "TANH", "CAST"):
+                v = tuple(p["inputs"][0][1])
+            else:
+                return None
+        return None
+
+    pairs = []
+    for n in g.nodes():
+        if n["type"] == "LINEAR":
+            p = producer_linear(g, n)
+            if p is not None and len(g.consumers((p["id"], "OUTPUT"))) == 1:
+                pairs.append((p["name"] or p["id"], n["name"] or n["id"]))
+    firsts = {a for a, _ in pairs}
+    seconds = {b for _, b in pairs}
+    key = lambda n: n["name"] or n["id"]
+    for bias in ("", "_bias"):
+        rc = by_name.get(f"replicate_linear_combine_{W}{bias}")
+        rr = by_name.get(f"partition_linear_reduce_{W}{bias}")
+        if rc is not None:
+            g = apply_where(g, rc, lambda n: key(n) in firsts, W)
+        if rr is not None:
+            g = apply_where(g, rr, lambda n: key(n) in seconds, W)
+    # shard the pointwise ops between the two Linears on the (last) feature dim, then cancel Combine/Repartition pairs
+    feature = [r for r in rules if r.name.startswith("partition_") and "_combine_" in r.name and
+               any(r.name.startswith(f"partition_{op}_combine_") for op in ("DROPOUT", "RELU", "GELU", "SIGMOID", "TANH"))
+               and r.name.endswith(f"_{W}") and not r.name.endswith(f"_0_{W}")]
+
+    def between(n):
+        v = tuple(n["inputs"][0][1])
+        return g.node(v[0])["type"] == "COMBINE"
+
+    for r in feature:
+        g = apply_where(g, r, between, W)
+    g = core.apply_rules_exhaustively(g, cancellation_rules(rules), 100000, W)
+    return g
+
+
+def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = "unity", budget: int = 0, alpha: float = 1.05,
+             estimator=None, rules=None, seed: int = 0, mcmc_iterations: int = 200, mcmc_temperature: float = 1.0,
+             substitution_frequency: float = 0.2, time_limit_s: float = 120.0, only_data_parallel: bool = False) -> dict:
+    """Search a strategy.  Returns ``{"pcg", "mapped_pcg", "runtime_ms", "memory_bytes", "stats", "candidates"}``."""
+    if machine is None:
+        machine = machine_for(world or 1)
+    W = machine.num_devices
+    estimator = estimator or core.CostEstimator(machine)
+    rules = rules or core.get_substitution_set(machine)
+    t0 = time.time()
+    base = core.pcg_from_computation_graph(cg)
+    cands: Dict[str, object] = {"single_device": base}
+    if W > 1:
+        cands[f"dp{W}"] = data_parallel_strategy(cg, W, rules)
+        if not only_data_parallel and algorithm != "data_parallel":
+            try:
+                cands[f"tp{W}"] = tensor_parallel_strategy(cg, W, rules)
+            except Exception:  # a model without the pattern simply has no such candidate
+                pass
+    scored = {k: core.evaluate_pcg(g, machine, estimator) for k, g in cands.items()}
+    if algorithm == "data_parallel" or only_data_parallel:
+        best_name = f"dp{W}" if W > 1 else "single_device"
+    elif algorithm == "tensor_parallel":
+        best_name = f"tp{W}" if f"tp{W}" in scored else min(scored, key=lambda k: scored[k]["runtime_ms"])
+    else:
+        best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
+    best = scored[best_name]
+    stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
+    if algorithm == "unity" and budget > 0 and W > 1:
+        use = rules if not only_data_parallel else data_parallel_rules(rules, W) + cancellation_rules(rules)
+        r = core.unity_search(best["pcg"], machine, estimator, use, alpha, budget, 100000, time_limit_s)
+        stats["unity"] = r["stats"]
+        if r["runtime_ms"] < best["runtime_ms"]:
+            best = r
+            stats["seed_strategy"] += "+unity"
+    elif algorithm == "mcmc" and W > 1:
+        r = core.mcmc_search(best["pcg"], machine, estimator, rules, mcmc_temperature, mcmc_iterations, substitution_frequency, seed)
+        stats["mcmc"] = r["stats"]
+        # MCMC scores with the simulator; re-score with the mapping DP for a comparable number
+        rescored = core.evaluate_pcg(r["pcg"], machine, estimator)
+        if rescored["runtime_ms"] < best["runtime_ms"]:
+            best = rescored
+            stats["seed_strategy"] += "+mcmc"
+    stats["search_seconds"] = time.time() - t0
+    out = dict(best)
+    out["stats"] = stats
+    return out
+
+
+def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
+    """Strategy for `world` ranks under an FFConfig: imported from a file if given, searched otherwise."""
+    if getattr(config, "import_strategy_file", None):
+        with open(config.import_strategy_file) as f:
+            return core.Graph.from_v1(f.read()), {"imported": config.import_strategy_file}
+    algo = getattr(config, "search_algorithm", "unity")
+    r = optimize(cg, world=world, algorithm=algo, budget=getattr(config, "search_budget", 0),
+                 alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
+                 only_data_parallel=getattr(config, "only_data_parallel", False))
+    return r["mapped_pcg"], r["stats"]

@@ -199,9 +199,11 @@ std::optional<Graph> apply_substitution(const Graph &g, const Substitution &s, c
   } catch (const std::exception &e) {
     return fail(e.what());
   }
+  std::set<NodeId> keep_even_if_unused;  // new producers of values that were graph outputs before the rewrite
   for (auto &io : s.outputs) {
     ValueRef old_v{m.nodes[io.pattern_node], io.pattern_slot};
     ValueRef new_v = io.out_node < 0 ? m.inputs[-io.out_node - 1] : ValueRef{new_ids[io.out_node], io.out_slot};
+    if (io.out_node >= 0 && g.consumers(old_v).empty()) keep_even_if_unused.insert(new_ids[io.out_node]);
     if (out.shape(old_v) != out.shape(new_v))
       return fail("interface shape changes from " + out.shape(old_v).str() + " to " + out.shape(new_v).str());
     out.replace_uses(old_v, new_v);
@@ -217,7 +219,7 @@ std::optional<Graph> apply_substitution(const Graph &g, const Substitution &s, c
   while (swept) {
     swept = false;
     for (NodeId n : new_ids) {  // only operators this rewrite created: a model output may legitimately end in a Combine
-      if (!out.has_node(n)) continue;
+      if (!out.has_node(n) || keep_even_if_unused.count(n)) continue;
       const Node &nd = out.node(n);
       if (!is_parallel_op(nd.type)) continue;
       bool used = false;

@@ -180,6 +180,17 @@ class NoopOp(OpImpl):
             self.ex.write_grad(b, g, self.acc["INPUT"])
 
 
+class SkippedOp(OpImpl):
+    """An operator whose result nobody on this rank needs (e.g. the Combine that would gather the model output
+    although the loss is taken on the local shard)."""
+
+    def setup(self):
+        pass
+
+    def forward(self):
+        pass
+
+
 # ------------------------------------------------------------------------------------------ Linear
 _ACT = {None: None, "RELU": "relu", "GELU": "gelu", "SIGMOID": "sigmoid", "TANH": "tanh"}
 
@@ -193,7 +204,7 @@ class LinearOp(OpImpl):
         x = self.x()
         self.x2d = x.view(-1, x.shape[-1])
         self.w = self.x("WEIGHT")
-        self.bias = self.x("BIAS") if "BIAS" in self.inputs else None
+        self.bias = self.x("BIAS") if ("BIAS" in self.inputs and self.ex.use_bias(self, "BIAS")) else None
         self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
         rows, cols = self.y2d.shape
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(rows, cols) if K.available() and self.ex.on_gpu else 0)
@@ -315,7 +326,7 @@ class AttentionOp(OpImpl):
             self.c_ctx = self.ctx
         self.alloc_out()
         self.bias_in = self.x("INPUT_BIAS") if "INPUT_BIAS" in self.inputs else None
-        self.bias_out = self.x("OUTPUT_BIAS") if "OUTPUT_BIAS" in self.inputs else None
+        self.bias_out = self.x("OUTPUT_BIAS") if ("OUTPUT_BIAS" in self.inputs and ex.use_bias(self, "OUTPUT_BIAS")) else None
         self.alpha = 1.0 / math.sqrt(kd)
         nbytes = self.probs.numel() * self.probs.element_size()
         ex.need_big_scratch(nbytes, 2 if self.p_drop > 0 else 1)
@@ -744,8 +755,13 @@ class Executable:
         return _TORCH_DT[name]
 
     def head_shards(self, op) -> int:
-        w = self.values[op.inputs["WEIGHT"]]
-        return getattr(w, "head_shards", 1)
+        """How many ways the heads of an attention operator are sharded on this rank (1 on a single device)."""
+        return getattr(self, "_head_shards", {}).get(op.nid, 1)
+
+    def use_bias(self, op, slot: str) -> bool:
+        """False when `slot` is the bias of an operator that produces partial sums and this rank is not the one
+        that contributes it (a row-parallel Linear adds its bias once, not once per shard)."""
+        return True
 
     def next_salt(self) -> int:
         self._salt += 1
@@ -816,7 +832,8 @@ class Executable:
 
     def _build_params(self):
         nodes, dev = self.nodes, self.device
-        self.param_nodes = [nid for nid in self.order if nodes[nid]["type"] == "WEIGHT"]
+        self.param_nodes = self.order_params([nid for nid in self.order if nodes[nid]["type"] == "WEIGHT"])
+        ordinal = {nid: i for i, nid in enumerate(nid for nid in self.order if nodes[nid]["type"] == "WEIGHT")}
         offs, total = {}, 0
         for nid in self.param_nodes:
             sh = nodes[nid]["outputs"][0][1]
@@ -831,7 +848,7 @@ class Executable:
         self.master = torch.zeros(max(total, 1), dtype=torch.float32, device=dev)
         self.shadow = torch.zeros(max(total, 1), dtype=torch.bfloat16, device=dev) if mixed else None
         if self.cfg.training:
-            self.grads = torch.zeros(max(total, 1), dtype=torch.bfloat16 if mixed else torch.float32, device=dev)
+            self.grads = self.alloc_grad_arena(max(total, 1), torch.bfloat16 if mixed else torch.float32)
             self.opt_m = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) \
                 if (self.cfg.optimizer.kind == "adam" or self.cfg.optimizer.momentum > 0) else None
             self.opt_v = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) if self.cfg.optimizer.kind == "adam" else None
@@ -839,7 +856,7 @@ class Executable:
             o, n = offs[nid]
             shape = self.local_weight_shape(nid)
             full = initialize(list(nodes[nid]["outputs"][0][1].sizes), nodes[nid]["attrs"].get("initializer"),
-                              base_seed=self.cfg.seed, ordinal=i)
+                              base_seed=self.cfg.seed, ordinal=ordinal[nid])
             self.master[o:o + n].copy_(self.shard_weight(nid, full).reshape(-1))
             b = self.values[(nid, "OUTPUT")]
             b.data = (self.shadow if mixed else self.master)[o:o + n].view(shape)
@@ -848,7 +865,34 @@ class Executable:
         if mixed:
             self.shadow.copy_(self.master)
 
-    # single-device: a weight's local shape is its full shape; the distributed executable overrides both
+    # value aliasing: an operator that forwards its input unchanged shares data *and* gradient buffers with it
+    def alias(self, nid: int, src: Value, slot: str = "OUTPUT"):
+        if not hasattr(self, "alias_of"):
+            self.alias_of = {}
+        self.alias_of[(nid, slot)] = src
+
+    def canon(self, v: Value) -> Value:
+        a = getattr(self, "alias_of", None)
+        if a:
+            while v in a:
+                v = a[v]
+        return v
+
+    # hooks the distributed executable overrides
+    def order_params(self, param_nodes):
+        return param_nodes
+
+    def alloc_grad_arena(self, numel, dtype):
+        return torch.zeros(numel, dtype=dtype, device=self.device)
+
+    def resolve_loss_value(self, v: Value) -> Value:
+        """The value the loss is computed on; the distributed executable steps back over a trailing Combine."""
+        return v
+
+    def local_label_rows(self, labels: torch.Tensor, rows: int) -> torch.Tensor:
+        return labels
+
+    # single-device: a weight's local shape is its full shape
     def local_weight_shape(self, nid):
         return list(self.nodes[nid]["outputs"][0][1].sizes)
 
@@ -869,9 +913,12 @@ class Executable:
         # a trailing softmax that only feeds the loss is fused into it
         self.loss_value: Optional[Value] = None
         if self.cfg.loss:
-            sinks = [tuple(v) for v in g.sink_values() if self.nodes[v[0]]["type"] not in ("WEIGHT", "INPUT")]
+            sinks = [self.resolve_loss_value(tuple(v)) for v in g.sink_values()
+                     if self.nodes[v[0]]["type"] not in ("WEIGHT", "INPUT")]
             named = [v for v in sinks if self.nodes[v[0]]["name"] == "out_prob"]
             self.loss_value = (named or sinks)[-1] if sinks else None
+            for nid in getattr(self, "_skip_nodes", ()):  # trailing parallel ops behind the loss input
+                self.ops[nid] = SkippedOp(self, nid, self.nodes[nid])
             if self.loss_value is not None:
                 op = self.ops[self.loss_value[0]]
                 if isinstance(op, SoftmaxOp) and self.cfg.loss == "sparse_categorical_crossentropy":
@@ -898,7 +945,10 @@ class Executable:
             self.labels = torch.zeros(rows, dtype=torch.int32, device=self.device)
         else:
             self.labels = torch.zeros(rows, cols, dtype=self.torch_dtype(sh.dtype), device=self.device)
-        self.loss_scale = 1.0 / rows
+        self.loss_scale = 1.0 / self.global_loss_rows(rows, sh)
+
+    def global_loss_rows(self, local_rows: int, shape) -> int:
+        return local_rows
 
     def _plan_gradients(self):
         pool = _GradPool(self.device)
@@ -910,33 +960,43 @@ class Executable:
             tgt = op.inputs["INPUT"] if (isinstance(op, SoftmaxOp) and op.fused_loss) else self.loss_value
             seeds.append(tgt)
         live: Dict[Value, torch.Tensor] = {}
+        canon = self.canon
 
         def ensure(v: Value):
-            b = self.values[v]
+            """Give v a gradient buffer; aliases share the buffer of the value they alias."""
+            c = canon(v)
+            b = self.values[c]
             if b.grad is None and b.requires_grad:
                 ref = b.data if b.data is not None else None
-                sizes = list(self.graph.shape(v).piece_sizes)
+                sizes = list(self.graph.shape(c).piece_sizes)
                 n = 1
                 for s in sizes:
                     n *= s
-                dt = ref.dtype if ref is not None else self.torch_dtype(self.graph.shape(v).dtype)
+                dt = ref.dtype if ref is not None else self.torch_dtype(self.graph.shape(c).dtype)
                 flat = pool.take(n, dt)
                 b.grad = flat.view(sizes)
-                live[v] = flat
+                live[c] = flat
+            if c != v and b.grad is not None:
+                self.values[v].grad = b.grad.view(list(self.graph.shape(v).piece_sizes))
 
         for v in seeds:
             ensure(v)
-            written[v] = True
+            written[canon(v)] = True
         for nid in reversed(self.order):
             op = self.ops[nid]
             if op.type in ("WEIGHT", "INPUT"):
                 continue
             # an op whose outputs received no gradient has nothing to propagate
             outs = [(nid, s) for s, _ in op.outputs]
-            op.has_grad = any(written.get(o, False) for o in outs)
+            op.has_grad = any(written.get(canon(o), False) for o in outs)
             if isinstance(op, BinaryOp) and op.fused_into_ln:
                 op.has_grad = False
+            if isinstance(op, SkippedOp):
+                op.has_grad = False
             if op.has_grad or (isinstance(op, SoftmaxOp) and op.fused_loss):
+                for o in outs:
+                    if self.values[o].requires_grad:
+                        ensure(o)
                 targets = list(op.inputs.items())
                 if isinstance(op, LayerNormOp) and op.fused_add is not None:
                     # the LayerNorm writes straight into the add's operands
@@ -944,8 +1004,8 @@ class Executable:
                     for s, v in add.inputs.items():
                         if self.values[v].requires_grad:
                             ensure(v)
-                            add.acc[s] = written.get(v, False)
-                            written[v] = True
+                            add.acc[s] = written.get(canon(v), False)
+                            written[canon(v)] = True
                     targets = [(s, v) for s, v in targets if s != "INPUT"]
                 if isinstance(op, SoftmaxOp) and op.fused_loss:
                     targets = []
@@ -954,11 +1014,11 @@ class Executable:
                     if not self.values[v].requires_grad:
                         continue
                     ensure(v)
-                    op.acc[s] = written.get(v, False) or (v in seen_here)
-                    seen_here.add(v)
-                for v in seen_here:
-                    written[v] = True
-            # outputs of this node are dead once its backward ran
+                    op.acc[s] = written.get(canon(v), False) or (canon(v) in seen_here)
+                    seen_here.add(canon(v))
+                for c in seen_here:
+                    written[c] = True
+            # outputs of this node are dead once its backward ran (aliases are released with their source)
             for o in outs:
                 if o in live:
                     pool.give(live.pop(o))
@@ -976,6 +1036,7 @@ class Executable:
                 src = inputs[name]
                 dst.copy_(src.reshape(dst.shape), non_blocking=True)
         if labels is not None and self.labels is not None:
+            labels = self.local_label_rows(labels, self.labels.shape[0])
             self.labels.copy_(labels.reshape(self.labels.shape), non_blocking=True)
 
     def forward(self):

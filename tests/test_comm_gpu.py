@@ -29,7 +29,13 @@ def _worker(rank, world, port, fn_name, q):
         from flexflow_train_b200.parallel.context import DistContext
 
         ctx = DistContext(rank, world, rank)
-        res = globals()[fn_name](ctx)
+        if ":" in fn_name:
+            import importlib
+
+            mod, f = fn_name.split(":")
+            res = getattr(importlib.import_module(mod), f)(ctx)
+        else:
+            res = globals()[fn_name](ctx)
         torch.cuda.synchronize()
         ctx.check_status()
         q.put((rank, "ok", res))
