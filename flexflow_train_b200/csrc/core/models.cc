@@ -318,6 +318,16 @@ Json default_dlrm_config() {
   c["embedding_data_type"] = "HALF"; c["final_activation"] = "RELU";
   return c;
 }
+// concat is limited to 8 numbered input slots (INPUT_0..INPUT_7): longer lists are concatenated in stages
+static V concat_many(GraphBuilder &b, std::vector<V> xs, int axis) {
+  while (xs.size() > 8) {
+    std::vector<V> head(xs.begin(), xs.begin() + 8);
+    V c = b.concat(head, axis);
+    xs.erase(xs.begin(), xs.begin() + 8);
+    xs.insert(xs.begin(), c);
+  }
+  return xs.size() == 1 ? xs[0] : b.concat(xs, axis);
+}
 static V dlrm_mlp(GraphBuilder &b, V x, const std::vector<long long> &sizes, long long seed, const std::string &p,
                   const std::string &last_act) {
   for (size_t i = 0; i + 1 < sizes.size(); ++i) {
@@ -358,14 +368,14 @@ Graph build_dlrm(const Json &user) {
   if (inter == "CAT") {
     std::vector<V> all{bot};
     all.insert(all.end(), embs.begin(), embs.end());
-    feat = b.concat(all, 1);
+    feat = concat_many(b, all, 1);
   } else if (inter == "DOT") {
     // pairwise dot products of the (1 + #tables) feature vectors, concatenated with the dense feature
     if (bottom.back() != dim) throw Error("dlrm: DOT interaction needs bottom MLP width == embedding_dim");
     std::vector<V> rows;
     rows.push_back(b.reshape(bot, {batch, 1, dim}));
     for (auto &e : embs) rows.push_back(b.reshape(e, {batch, 1, dim}));
-    V x = b.concat(rows, 1);                       // [batch, F, dim]
+    V x = concat_many(b, rows, 1);                 // [batch, F, dim]
     V xt = b.transpose(x, {0, 2, 1});              // [batch, dim, F]
     V z = b.batch_matmul(x, xt);                   // [batch, F, F]
     V zf = b.flat(z, 1, -1);

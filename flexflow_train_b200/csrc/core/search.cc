@@ -367,18 +367,44 @@ struct DP {
       for (int b : rl)
         for (auto &e : g.node(b).inputs)
           if (ll.count(e.src.node)) edges.push_back({e.src.node, b});
-      Front fl = solve(l, r, fixed), fr = solve(rt, r, fixed);
-      for (auto &a : fl)
-        for (auto &b : fr) {
-          MappingPoint p;
-          double move = 0;
-          for (auto &e : edges) move = std::max(move, movement(e.first, a.views.at(e.first), e.second, b.views.at(e.second)));
-          p.runtime_ms = a.runtime_ms + b.runtime_ms + move;
-          p.memory_bytes = a.memory_bytes + b.memory_bytes;
-          p.views = a.views;
-          p.views.insert(b.views.begin(), b.views.end());
-          res.push_back(p);
+      // The transfer cost across the split depends on the views of the boundary layers, so those views are
+      // enumerated here and imposed on both sub-problems as constraints (get_optimal_machine_mapping.cc:162-210).
+      std::vector<NodeId> boundary;
+      for (auto &e : edges) {
+        for (NodeId n : {e.first, e.second})
+          if (!fixed.count(n) && std::find(boundary.begin(), boundary.end(), n) == boundary.end()) boundary.push_back(n);
+      }
+      std::vector<std::vector<MachineView>> options;
+      size_t combos = 1;
+      for (NodeId n : boundary) {
+        options.push_back(allowed_machine_views(tasks(n), r, m));
+        if (options.back().empty()) { combos = 0; break; }
+        combos *= options.back().size();
+      }
+      if (combos > 256) {  // very wide boundaries: fall back to the lowest-start view of each layer
+        for (auto &o : options) o.resize(1);
+        combos = 1;
+      }
+      for (size_t ci = 0; ci < combos; ++ci) {
+        std::map<NodeId, MachineView> fx = fixed;
+        size_t rem = ci;
+        for (size_t bi = 0; bi < boundary.size(); ++bi) {
+          fx[boundary[bi]] = options[bi][rem % options[bi].size()];
+          rem /= options[bi].size();
         }
+        Front fl = solve(l, r, fx), fr = solve(rt, r, fx);
+        for (auto &a : fl)
+          for (auto &b : fr) {
+            MappingPoint p;
+            double move = 0;
+            for (auto &e : edges) move = std::max(move, movement(e.first, a.views.at(e.first), e.second, b.views.at(e.second)));
+            p.runtime_ms = a.runtime_ms + b.runtime_ms + move;
+            p.memory_bytes = a.memory_bytes + b.memory_bytes;
+            p.views = a.views;
+            p.views.insert(b.views.begin(), b.views.end());
+            res.push_back(p);
+          }
+      }
     } else {
       const SPTree &l = t.children[0], &rt = t.children[1];
       // (a) run the branches one after the other on all resources

@@ -180,6 +180,14 @@ std::optional<Graph> apply_substitution(const Graph &g, const Substitution &s, c
         ins.push_back({in.slot, src});
         if (!is_weight_slot(type, in.slot)) data_shapes.push_back({in.slot, out.shape(src)});
       }
+      if (on.template_node && s.pattern.nodes[*on.template_node].allow_extra_inputs) {
+        // inputs of the matched operator that the pattern did not name (an optional BIAS) carry over unchanged
+        for (auto &e : g.node(m.nodes[*on.template_node]).inputs) {
+          bool present = false;
+          for (auto &x : ins) if (x.dst_slot == e.dst_slot) present = true;
+          if (!present && !matched.count(e.src.node)) ins.push_back({e.dst_slot, e.src});
+        }
+      }
       Inferred inf = infer_shapes(type, attrs, data_shapes);
       // weight inputs must have the shard layout the operator expects (replication may be split between
       // sum and discard-copy degrees, see GraphBuilder::weight_for)

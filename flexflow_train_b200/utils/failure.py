@@ -52,8 +52,12 @@ class HeartbeatMonitor:
         self.store.set(f"{self.prefix}/{self.rank}", f"{time.time():.6f}:{step}")
 
     def last_beat(self, rank: int) -> Optional[float]:
+        key = f"{self.prefix}/{rank}"
         try:
-            v = self.store.get(f"{self.prefix}/{rank}")
+            # TCPStore.get blocks until the key exists; ask first where the store can say
+            if hasattr(self.store, "check") and not self.store.check([key]):
+                return None
+            v = self.store.get(key)
         except Exception:
             return None
         if isinstance(v, bytes):

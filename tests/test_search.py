@@ -1,0 +1,126 @@
+"""Machine views, machine-mapping DP, Unity / MCMC search, simulator (reference: lib/compiler/test)."""
+import itertools
+
+import pytest
+
+from flexflow_train_b200 import _ffcore as c
+from flexflow_train_b200.compiler import strategy as S
+
+
+def test_allowed_machine_views_are_contiguous_and_aligned():
+    ms = c.MachineSpecification(1, 8)
+    v = c.allowed_machine_views([4], 0, 8, ms)
+    assert len(v) == 2
+    assert [c.view_devices(x, [4], ms) for x in v] == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert c.view_devices(c.allowed_machine_views([2, 2], 4, 4, ms)[0], [2, 2], ms) == [4, 5, 6, 7]
+    assert c.allowed_machine_views([16], 0, 8, ms) == []
+    ms2 = c.MachineSpecification(2, 4)
+    v = c.allowed_machine_views([2, 4], 0, 8, ms2)
+    assert v[0]["dimensions"][0]["projection"] == "INTER_NODE" and v[0]["dimensions"][1]["projection"] == "INTRA_NODE"
+    assert c.view_devices(v[0], [2, 4], ms2) == list(range(8))
+
+
+def _chain(n_par, batch=64, width=256):
+    """input -> n_par parallel dense branches -> sum: a graph with a parallel split in its SP tree."""
+    b = c.GraphBuilder()
+    x = b.create_input([batch, width], "FLOAT")
+    ys = [b.dense(x, width, "RELU", False) for _ in range(n_par)]
+    y = ys[0]
+    for z in ys[1:]:
+        y = b.binary("EW_ADD", y, z)
+    b.softmax(y)
+    return b.graph
+
+
+@pytest.mark.parametrize("batch,width", [(64, 256), (8192, 8192)])
+def test_mapping_dp_matches_brute_force_on_parallel_split(batch, width):
+    g = _chain(2, batch, width)
+    ms = c.MachineSpecification(1, 2)
+    est = c.CostEstimator(ms)
+    pts = c.get_optimal_machine_mapping(g, None, ms, est, 1)
+    assert len(pts) == 1
+    dp_cost = pts[0]["runtime_ms"]
+    # brute force: either everything in series on one device, or the two branch Linears side by side on the two
+    # devices, which costs one transfer of a branch output (forward) and of its gradient (backward)
+    costs = {n["id"]: sum(est.op_cost(g, n["id"])[k] for k in ("fwd_ms", "bwd_ms")) for n in g.nodes()}
+    lin = [n["id"] for n in g.nodes() if n["type"] == "LINEAR"]
+    serial = sum(costs.values())
+    move = 2 * est.movement_cost_ms(batch * width * 4, False)
+    split = serial - min(costs[l] for l in lin) + 2 * move  # the branch input travels too
+    assert abs(dp_cost - min(serial, split)) < 1e-6 * serial
+    used = {tuple(c.view_devices(v, [], ms)) for v in pts[0]["views"].values()}
+    assert used == ({(0,)} if serial <= split else {(0,), (1,)})
+
+
+def test_memory_pareto_front():
+    g = _chain(2)
+    ms = c.MachineSpecification(1, 2)
+    pts = c.get_optimal_machine_mapping(g, None, ms, c.CostEstimator(ms), 4)
+    assert len(pts) >= 1
+    for a, b_ in itertools.combinations(pts, 2):  # no point dominates another
+        assert not (a["runtime_ms"] <= b_["runtime_ms"] and a["memory_bytes"] <= b_["memory_bytes"]) or a == b_
+
+
+def test_unity_search_improves_mlp_and_respects_budget():
+    g = c.build_model("mlp", {"batch_size": 4096, "input_dim": 4096, "hidden": [8192, 8192], "num_classes": 4096})
+    ms = c.MachineSpecification(1, 4)
+    est = c.CostEstimator(ms)
+    rules = c.get_substitution_set(ms)
+    base = c.evaluate_pcg(g, ms, est)["runtime_ms"]
+    r0 = c.unity_search(g, ms, est, rules, 1.05, 0, 100000, 60.0)
+    assert r0["runtime_ms"] == base and r0["stats"]["iterations"] == 0
+    r = c.unity_search(g, ms, est, rules, 1.3, 6, 100000, 60.0)
+    assert r["runtime_ms"] < base and r["stats"]["evaluated"] > 10
+    assert any(n["type"] in ("REPARTITION", "REPLICATE") for n in r["pcg"].nodes())
+    assert r["mapped_pcg"].is_mapped()
+
+
+def test_mcmc_is_deterministic_under_a_seed():
+    g = c.build_model("mlp", {"batch_size": 1024, "input_dim": 1024, "hidden": [2048], "num_classes": 1024})
+    ms = c.MachineSpecification(1, 4)
+    est = c.CostEstimator(ms)
+    rules = c.get_substitution_set(ms)
+    a = c.mcmc_search(g, ms, est, rules, 1.0, 40, 0.3, 0)
+    b_ = c.mcmc_search(g, ms, est, rules, 1.0, 40, 0.3, 0)
+    assert a["runtime_ms"] == b_["runtime_ms"] and a["stats"] == b_["stats"]
+    assert a["pcg"].signature() == b_["pcg"].signature()
+    d = c.mcmc_search(g, ms, est, rules, 1.0, 40, 0.3, 1)
+    assert d["stats"]["iterations"] == 40
+
+
+def test_simulator_forward_vs_forward_backward():
+    g = _chain(2)
+    ms = c.MachineSpecification(1, 2)
+    est = c.CostEstimator(ms)
+    m = c.evaluate_pcg(g, ms, est)["mapped_pcg"]
+    f = c.simulate_task_graph(m, ms, est, False)
+    fb = c.simulate_task_graph(m, ms, est, True)
+    assert 0 < f < fb
+
+
+def test_measured_costs_override_the_analytical_model():
+    g = c.build_model("mlp", {"batch_size": 64})
+    ms = c.MachineSpecification(1, 1)
+    est = c.CostEstimator(ms)
+    lin = [n["id"] for n in g.nodes() if n["type"] == "LINEAR"][0]
+    before = est.op_cost(g, lin)["fwd_ms"]
+    est.set_measured(est.op_cost_key(g, lin), 123.0, 456.0, 1.0)
+    after = est.op_cost(g, lin)
+    assert before != 123.0 and after["fwd_ms"] == 123.0 and after["bwd_ms"] == 456.0
+
+
+def test_optimize_picks_data_parallel_for_large_transformer_and_exports():
+    cfg = {"num_features": 1024, "sequence_length": 512, "batch_size": 16, "dim_feedforward": 4096, "num_heads": 8,
+           "num_decoder_layers": 2, "dropout": 0.1, "vocab_size": 8192}
+    g = c.build_model("transformer_lm", cfg)
+    r = S.optimize(g, world=8, algorithm="unity", budget=0)
+    assert r["stats"]["seed_strategy"].startswith("dp8")
+    assert set(r["stats"]["candidates"]) == {"single_device", "dp8", "tp8"}
+    text = r["mapped_pcg"].to_v1_string(parallel=True)
+    back = c.Graph.from_v1(text)
+    assert back.signature() == r["mapped_pcg"].signature()
+    tp = S.tensor_parallel_strategy(g, 8)
+    k = {}
+    for n in tp.nodes():
+        k[n["type"]] = k.get(n["type"], 0) + 1
+    assert k["REDUCTION"] == 4 and k["REPLICATE"] >= 4  # attention + row-parallel FFN per layer
