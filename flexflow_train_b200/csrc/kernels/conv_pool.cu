@@ -1,0 +1,533 @@
+// Convolution support kernels, pooling and batch normalisation for channels-last activations.
+//
+// Convolutions run as implicit-layout GEMMs on the tcgen05 GEMM of this library: activations are kept
+// channels-last ([N, H, W, C]) so that a 1x1 convolution *is* the GEMM [N*H*W, C] x [OC, C]^T with no data
+// movement, and a KxK convolution needs one im2col pass into a K-major bf16 matrix [N*OH*OW, KH*KW*C]
+// (k = (kh*KW + kw)*C + c, padded with zero columns to a multiple of 8 so every row starts on 16 bytes for TMA).
+// Bias and activation are applied by the GEMM epilogue.  Backward is two more GEMMs (dW = dY^T col,
+// dcol = dY W) followed by the gather-form col2im below (no atomics).
+//
+// The reference does these with cuDNN (lib/kernels/src/cuda/ops/conv_2d_kernels.cu, pool_2d_kernels.cu,
+// batch_norm_kernels.cu); here they are plain kernels written for HBM bandwidth: every pass is coalesced over
+// the channel dimension.
+#include "common.cuh"
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T *p);
+template <> __device__ __forceinline__ float ldf<float>(const float *p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16 *p) { return bf2f(*p); }
+template <typename T> __device__ __forceinline__ void stf(T *p, float v);
+template <> __device__ __forceinline__ void stf<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16 *p, float v) { *p = f2bf(v); }
+
+struct ConvGeom {
+  int N, C, H, W, KH, KW, SH, SW, PH, PW, OH, OW, Kp;
+  long long sn, sc, sh, sw;  // element strides of the activation tensor
+};
+
+// ------------------------------------------------------------------------------------------- im2col
+// vector path: bf16 channels-last, C % 8 == 0; one thread moves 8 channels (16 bytes)
+__global__ void im2col_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ col, ConvGeom g, long long total) {
+  const int c8n = g.C >> 3, kk_n = g.KH * g.KW;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c8 = (int)(t % c8n);
+    long long r = t / c8n;
+    int kk = (int)(r % kk_n);
+    long long row = r / kk_n;
+    int ow = (int)(row % g.OW);
+    long long r2 = row / g.OW;
+    int oh = (int)(r2 % g.OH);
+    int n = (int)(r2 / g.OH);
+    int kh = kk / g.KW, kw = kk - kh * g.KW;
+    int ih = oh * g.SH - g.PH + kh, iw = ow * g.SW - g.PW + kw;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
+      v = *reinterpret_cast<const uint4 *>(x + n * g.sn + ih * g.sh + iw * g.sw + c8 * 8);
+    *reinterpret_cast<uint4 *>(col + row * g.Kp + (long long)kk * g.C + c8 * 8) = v;
+  }
+}
+// generic path: any strides / dtype; one thread per (row, k) including the zero padding columns
+template <typename T>
+__global__ void im2col_kernel(const T *__restrict__ x, bf16 *__restrict__ col, ConvGeom g, long long total) {
+  const int K = g.KH * g.KW * g.C;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int k = (int)(t % g.Kp);
+    long long row = t / g.Kp;
+    float v = 0.f;
+    if (k < K) {
+      int kk = k / g.C, c = k - kk * g.C;
+      int kh = kk / g.KW, kw = kk - kh * g.KW;
+      int ow = (int)(row % g.OW);
+      long long r2 = row / g.OW;
+      int oh = (int)(r2 % g.OH);
+      int n = (int)(r2 / g.OH);
+      int ih = oh * g.SH - g.PH + kh, iw = ow * g.SW - g.PW + kw;
+      if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = ldf(x + n * g.sn + c * g.sc + ih * g.sh + iw * g.sw);
+    }
+    col[t] = f2bf(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- col2im (gather form)
+// dx[n, ih, iw, c] (+)= sum over (kh, kw) with (ih + PH - kh) % SH == 0 ... of dcol[(n, oh, ow), (kh, kw, c)]
+template <typename T>
+__global__ void col2im_kernel(const bf16 *__restrict__ dcol, T *__restrict__ dx, ConvGeom g, long long total, int accumulate) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % g.C);
+    long long r = t / g.C;
+    int iw = (int)(r % g.W);
+    long long r2 = r / g.W;
+    int ih = (int)(r2 % g.H);
+    int n = (int)(r2 / g.H);
+    float acc = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      int a = ih + g.PH - kh;
+      if (a < 0) break;
+      int oh = a / g.SH;
+      if (oh * g.SH != a || oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        int b = iw + g.PW - kw;
+        if (b < 0) break;
+        int ow = b / g.SW;
+        if (ow * g.SW != b || ow >= g.OW) continue;
+        long long row = ((long long)n * g.OH + oh) * g.OW + ow;
+        acc += bf2f(dcol[row * g.Kp + (long long)(kh * g.KW + kw) * g.C + c]);
+      }
+    }
+    T *p = dx + n * g.sn + c * g.sc + ih * g.sh + iw * g.sw;
+    if (accumulate) acc += ldf(p);
+    stf(p, acc);
+  }
+}
+// vector form: bf16 channels-last output, C % 8 == 0
+__global__ void col2im_vec_kernel(const bf16 *__restrict__ dcol, bf16 *__restrict__ dx, ConvGeom g, long long total, int accumulate) {
+  const int c8n = g.C >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c8 = (int)(t % c8n);
+    long long r = t / c8n;
+    int iw = (int)(r % g.W);
+    long long r2 = r / g.W;
+    int ih = (int)(r2 % g.H);
+    int n = (int)(r2 / g.H);
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      int a = ih + g.PH - kh;
+      if (a < 0) break;
+      int oh = a / g.SH;
+      if (oh * g.SH != a || oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        int b = iw + g.PW - kw;
+        if (b < 0) break;
+        int ow = b / g.SW;
+        if (ow * g.SW != b || ow >= g.OW) continue;
+        long long row = ((long long)n * g.OH + oh) * g.OW + ow;
+        uint4 v = *reinterpret_cast<const uint4 *>(dcol + row * g.Kp + (long long)(kh * g.KW + kw) * g.C + c8 * 8);
+        float2 f0 = unpack_bf162(v.x), f1 = unpack_bf162(v.y), f2 = unpack_bf162(v.z), f3 = unpack_bf162(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+    }
+    bf16 *p = dx + n * g.sn + ih * g.sh + iw * g.sw + c8 * 8;
+    if (accumulate) {
+      uint4 v = *reinterpret_cast<const uint4 *>(p);
+      float2 f0 = unpack_bf162(v.x), f1 = unpack_bf162(v.y), f2 = unpack_bf162(v.z), f3 = unpack_bf162(v.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+      acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+    uint4 o;
+    o.x = pack_bf162(acc[0], acc[1]); o.y = pack_bf162(acc[2], acc[3]);
+    o.z = pack_bf162(acc[4], acc[5]); o.w = pack_bf162(acc[6], acc[7]);
+    *reinterpret_cast<uint4 *>(p) = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- filter repacking
+// w [OC, C, KH, KW] -> wp [OC, Kp] with k = (kh*KW + kw)*C + c (zero padding columns)
+template <typename T>
+__global__ void filter_pack_kernel(const T *__restrict__ w, bf16 *__restrict__ wp, int OC, int C, int KH, int KW, int Kp) {
+  long long total = (long long)OC * Kp;
+  int K = C * KH * KW;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int k = (int)(t % Kp);
+    int oc = (int)(t / Kp);
+    float v = 0.f;
+    if (k < K) {
+      int kk = k / C, c = k - kk * C;
+      v = ldf(w + ((long long)oc * C + c) * KH * KW + kk);
+    }
+    wp[t] = f2bf(v);
+  }
+}
+// dwp [OC, Kp] (fp32) -> dw [OC, C, KH, KW] (+)=
+template <typename T>
+__global__ void filter_unpack_kernel(const float *__restrict__ dwp, T *__restrict__ dw, int OC, int C, int KH, int KW, int Kp,
+                                     int accumulate) {
+  long long total = (long long)OC * C * KH * KW;
+  int KK = KH * KW;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int kk = (int)(t % KK);
+    long long r = t / KK;
+    int c = (int)(r % C);
+    int oc = (int)(r / C);
+    float v = dwp[(long long)oc * Kp + (long long)kk * C + c];
+    if (accumulate) v += ldf(dw + t);
+    stf(dw + t, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- pooling
+// output channels-last [N, OH, OW, C]; input with arbitrary strides.  mode 0 = max (argmax window offset saved),
+// 1 = average over the valid (unpadded) window elements.
+template <typename T>
+__global__ void pool_fwd_kernel(const T *__restrict__ x, T *__restrict__ y, unsigned char *__restrict__ arg, ConvGeom g, int mode,
+                                long long total) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % g.C);
+    long long r = t / g.C;
+    int ow = (int)(r % g.OW);
+    long long r2 = r / g.OW;
+    int oh = (int)(r2 % g.OH);
+    int n = (int)(r2 / g.OH);
+    const T *base = x + n * g.sn + c * g.sc;
+    float best = -INFINITY, sum = 0.f;
+    int besti = 0, cnt = 0;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      int ih = oh * g.SH - g.PH + kh;
+      if (ih < 0 || ih >= g.H) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        int iw = ow * g.SW - g.PW + kw;
+        if (iw < 0 || iw >= g.W) continue;
+        float v = ldf(base + ih * g.sh + iw * g.sw);
+        if (v > best) { best = v; besti = kh * g.KW + kw; }
+        sum += v;
+        ++cnt;
+      }
+    }
+    if (mode == 0) {
+      stf(y + t, best);
+      if (arg) arg[t] = (unsigned char)besti;
+    } else {
+      stf(y + t, cnt ? sum / cnt : 0.f);
+    }
+  }
+}
+// gather-form backward: one thread per input element
+template <typename T>
+__global__ void pool_bwd_kernel(const T *__restrict__ dy, const unsigned char *__restrict__ arg, T *__restrict__ dx, ConvGeom g, int mode,
+                                long long total, int accumulate) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % g.C);
+    long long r = t / g.C;
+    int iw = (int)(r % g.W);
+    long long r2 = r / g.W;
+    int ih = (int)(r2 % g.H);
+    int n = (int)(r2 / g.H);
+    float acc = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      int a = ih + g.PH - kh;
+      if (a < 0) break;
+      int oh = a / g.SH;
+      if (oh * g.SH != a || oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        int b = iw + g.PW - kw;
+        if (b < 0) break;
+        int ow = b / g.SW;
+        if (ow * g.SW != b || ow >= g.OW) continue;
+        long long o = (((long long)n * g.OH + oh) * g.OW + ow) * g.C + c;
+        if (mode == 0) {
+          if (arg[o] == (unsigned char)(kh * g.KW + kw)) acc += ldf(dy + o);
+        } else {
+          int h0 = max(oh * g.SH - g.PH, 0), h1 = min(oh * g.SH - g.PH + g.KH, g.H);
+          int w0 = max(ow * g.SW - g.PW, 0), w1 = min(ow * g.SW - g.PW + g.KW, g.W);
+          acc += ldf(dy + o) / (float)((h1 - h0) * (w1 - w0));
+        }
+      }
+    }
+    T *p = dx + n * g.sn + c * g.sc + ih * g.sh + iw * g.sw;
+    if (accumulate) acc += ldf(p);
+    stf(p, acc);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- batch normalisation
+// x is [R, C] (channels-last rows).  Column statistics are reduced in two steps: BN_ROWS-row chunks produce
+// partial sums [chunks, 2, C] (fp32), a second kernel folds them.
+constexpr int BN_TX = 32, BN_TY = 8;
+
+template <typename T>
+__global__ void bn_partial_kernel(const T *__restrict__ a, const T *__restrict__ b, const T *__restrict__ relu_y, float *__restrict__ part,
+                                  const float *__restrict__ mean, const float *__restrict__ rstd, long long R, int C, int rows_per_chunk,
+                                  int mode) {
+  // mode 0: sums of a and a*a (forward statistics)
+  // mode 1: sums of dy and dy * xhat with a = dy, b = x (backward); dy is masked where relu_y <= 0
+  __shared__ float s0[BN_TY][BN_TX + 1], s1[BN_TY][BN_TX + 1];
+  int c = blockIdx.x * BN_TX + threadIdx.x;
+  long long r0 = (long long)blockIdx.y * rows_per_chunk;
+  long long r1 = r0 + rows_per_chunk < R ? r0 + rows_per_chunk : R;
+  float u = 0.f, v = 0.f;
+  if (c < C) {
+    float m = mode ? mean[c] : 0.f, rs = mode ? rstd[c] : 0.f;
+    for (long long r = r0 + threadIdx.y; r < r1; r += BN_TY) {
+      float av = ldf(a + r * C + c);
+      if (mode == 0) {
+        u += av;
+        v += av * av;
+      } else {
+        if (relu_y && ldf(relu_y + r * C + c) <= 0.f) av = 0.f;
+        float xh = (ldf(b + r * C + c) - m) * rs;
+        u += av;
+        v += av * xh;
+      }
+    }
+  }
+  s0[threadIdx.y][threadIdx.x] = u;
+  s1[threadIdx.y][threadIdx.x] = v;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+#pragma unroll
+    for (int i = 1; i < BN_TY; ++i) { u += s0[i][threadIdx.x]; v += s1[i][threadIdx.x]; }
+    part[((long long)blockIdx.y * 2 + 0) * C + c] = u;
+    part[((long long)blockIdx.y * 2 + 1) * C + c] = v;
+  }
+}
+__global__ void bn_finalize_stats_kernel(const float *__restrict__ part, int chunks, int C, long long R, float eps, float *__restrict__ mean,
+                                         float *__restrict__ rstd) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, q = 0.0;
+  for (int k = 0; k < chunks; ++k) { s += part[((long long)k * 2) * C + c]; q += part[((long long)k * 2 + 1) * C + c]; }
+  double m = s / (double)R;
+  double var = q / (double)R - m * m;
+  if (var < 0.0) var = 0.0;
+  mean[c] = (float)m;
+  rstd[c] = (float)(1.0 / sqrt(var + (double)eps));
+}
+// sums[0][c] = sum dy, sums[1][c] = sum dy*xhat; also writes dgamma/dbeta (+)= when given
+template <typename T>
+__global__ void bn_finalize_grads_kernel(const float *__restrict__ part, int chunks, int C, float *__restrict__ sums, T *__restrict__ dgamma,
+                                         T *__restrict__ dbeta, int acc_gamma, int acc_beta) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f, q = 0.f;
+  for (int k = 0; k < chunks; ++k) { s += part[((long long)k * 2) * C + c]; q += part[((long long)k * 2 + 1) * C + c]; }
+  sums[c] = s;
+  sums[C + c] = q;
+  if (dbeta) stf(dbeta + c, s + (acc_beta ? ldf(dbeta + c) : 0.f));
+  if (dgamma) stf(dgamma + c, q + (acc_gamma ? ldf(dgamma + c) : 0.f));
+}
+template <typename T>
+__global__ void bn_apply_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ gamma, const T *__restrict__ beta,
+                                const float *__restrict__ mean, const float *__restrict__ rstd, long long total, int C, int relu) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % C);
+    float v = (ldf(x + t) - mean[c]) * rstd[c];
+    if (gamma) v *= ldf(gamma + c);
+    if (beta) v += ldf(beta + c);
+    if (relu && v < 0.f) v = 0.f;
+    stf(y + t, v);
+  }
+}
+// two elements per thread for bf16 with even C
+__global__ void bn_apply_bf16x2_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, const bf16 *__restrict__ gamma,
+                                       const bf16 *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd,
+                                       long long pairs, int C, int relu) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < pairs; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)((t * 2) % C);
+    float2 v = unpack_bf162(reinterpret_cast<const uint32_t *>(x)[t]);
+    v.x = (v.x - mean[c]) * rstd[c];
+    v.y = (v.y - mean[c + 1]) * rstd[c + 1];
+    if (gamma) { v.x *= bf2f(gamma[c]); v.y *= bf2f(gamma[c + 1]); }
+    if (beta) { v.x += bf2f(beta[c]); v.y += bf2f(beta[c + 1]); }
+    if (relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); }
+    reinterpret_cast<uint32_t *>(y)[t] = pack_bf162(v.x, v.y);
+  }
+}
+// dx = gamma * rstd * (dy' - sum_dy / R - xhat * sum_dy_xhat / R)
+template <typename T>
+__global__ void bn_bwd_apply_kernel(const T *__restrict__ dy, const T *__restrict__ x, const T *__restrict__ relu_y, const T *__restrict__ gamma,
+                                    const float *__restrict__ mean, const float *__restrict__ rstd, const float *__restrict__ sums,
+                                    T *__restrict__ dx, long long total, int C, float inv_r, int accumulate) {
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(t % C);
+    float g = ldf(dy + t);
+    if (relu_y && ldf(relu_y + t) <= 0.f) g = 0.f;
+    float xh = (ldf(x + t) - mean[c]) * rstd[c];
+    float v = (g - sums[c] * inv_r - xh * sums[C + c] * inv_r) * rstd[c];
+    if (gamma) v *= ldf(gamma + c);
+    if (accumulate) v += ldf(dx + t);
+    stf(dx + t, v);
+  }
+}
+
+inline ConvGeom make_geom(const int *p, const long long *strides) {
+  ConvGeom g;
+  g.N = p[0]; g.C = p[1]; g.H = p[2]; g.W = p[3]; g.KH = p[4]; g.KW = p[5]; g.SH = p[6]; g.SW = p[7]; g.PH = p[8]; g.PW = p[9];
+  g.OH = p[10]; g.OW = p[11]; g.Kp = p[12];
+  g.sn = strides[0]; g.sc = strides[1]; g.sh = strides[2]; g.sw = strides[3];
+  return g;
+}
+inline bool vec_ok(const ConvGeom &g, const void *p) {
+  return g.sc == 1 && (g.C % 8) == 0 && (g.sw % 8) == 0 && (g.sh % 8) == 0 && (g.sn % 8) == 0 && ((uintptr_t)p % 16) == 0;
+}
+
+}  // namespace
+
+// geom: {N, C, H, W, KH, KW, SH, SW, PH, PW, OH, OW, Kp}; strides: element strides (n, c, h, w) of x.  dt: 0 fp32, 1 bf16.
+FFK_API int ffk_im2col(const void *x, void *col, const int *geom, const long long *strides, int dt, cudaStream_t st) {
+  ConvGeom g = make_geom(geom, strides);
+  long long rows = (long long)g.N * g.OH * g.OW;
+  if (rows <= 0) return 0;
+  int K = g.KH * g.KW * g.C;
+  if (g.Kp < K || (g.Kp % 8) != 0) return -2;
+  if (dt == 1 && vec_ok(g, x) && g.Kp == K) {
+    long long total = rows * g.KH * g.KW * (g.C / 8);
+    im2col_vec_kernel<<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)col, g, total);
+  } else {
+    long long total = rows * g.Kp;
+    if (dt == 1) im2col_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)col, g, total);
+    else if (dt == 0) im2col_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (bf16 *)col, g, total);
+    else return -2;
+  }
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_col2im(const void *dcol, void *dx, const int *geom, const long long *strides, int dt, int accumulate, cudaStream_t st) {
+  ConvGeom g = make_geom(geom, strides);
+  long long total = (long long)g.N * g.H * g.W * g.C;
+  if (total <= 0) return 0;
+  if (dt == 1 && vec_ok(g, dx)) {
+    long long tv = total / 8;
+    col2im_vec_kernel<<<ffk_blocks(tv, 256), 256, 0, st>>>((const bf16 *)dcol, (bf16 *)dx, g, tv, accumulate);
+  } else if (dt == 1) {
+    col2im_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dcol, (bf16 *)dx, g, total, accumulate);
+  } else if (dt == 0) {
+    col2im_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dcol, (float *)dx, g, total, accumulate);
+  } else {
+    return -2;
+  }
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_filter_pack(const void *w, void *wp, int OC, int C, int KH, int KW, int Kp, int dt, cudaStream_t st) {
+  long long total = (long long)OC * Kp;
+  if (total <= 0) return 0;
+  if (dt == 1) filter_pack_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)w, (bf16 *)wp, OC, C, KH, KW, Kp);
+  else if (dt == 0) filter_pack_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)w, (bf16 *)wp, OC, C, KH, KW, Kp);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_filter_unpack(const float *dwp, void *dw, int OC, int C, int KH, int KW, int Kp, int dt, int accumulate, cudaStream_t st) {
+  long long total = (long long)OC * C * KH * KW;
+  if (total <= 0) return 0;
+  if (dt == 1) filter_unpack_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>(dwp, (bf16 *)dw, OC, C, KH, KW, Kp, accumulate);
+  else if (dt == 0) filter_unpack_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>(dwp, (float *)dw, OC, C, KH, KW, Kp, accumulate);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+// mode: 0 max, 1 average.  arg: [N*OH*OW*C] bytes (max only; may be null for inference)
+FFK_API int ffk_pool2d_fwd(const void *x, void *y, void *arg, const int *geom, const long long *strides, int mode, int dt, cudaStream_t st) {
+  ConvGeom g = make_geom(geom, strides);
+  long long total = (long long)g.N * g.OH * g.OW * g.C;
+  if (total <= 0) return 0;
+  if (g.KH * g.KW > 255) return -2;
+  if (dt == 1) pool_fwd_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (unsigned char *)arg, g, mode, total);
+  else if (dt == 0) pool_fwd_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (float *)y, (unsigned char *)arg, g, mode, total);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_pool2d_bwd(const void *dy, const void *arg, void *dx, const int *geom, const long long *strides, int mode, int dt,
+                           int accumulate, cudaStream_t st) {
+  ConvGeom g = make_geom(geom, strides);
+  long long total = (long long)g.N * g.H * g.W * g.C;
+  if (total <= 0) return 0;
+  if (mode == 0 && !arg) return -2;
+  if (dt == 1) pool_bwd_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dy, (const unsigned char *)arg, (bf16 *)dx, g, mode, total, accumulate);
+  else if (dt == 0) pool_bwd_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)dy, (const unsigned char *)arg, (float *)dx, g, mode, total, accumulate);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+static int bn_chunks(long long R, int C, int *rows_per_chunk) {
+  int coltiles = (C + BN_TX - 1) / BN_TX;
+  long long want = (148 * 8 + coltiles - 1) / coltiles;
+  long long maxc = (R + 63) / 64;
+  long long chunks = want < maxc ? want : maxc;
+  if (chunks < 1) chunks = 1;
+  long long rpc = (R + chunks - 1) / chunks;
+  chunks = (R + rpc - 1) / rpc;
+  *rows_per_chunk = (int)rpc;
+  return (int)chunks;
+}
+// number of fp32 scratch elements the batch-norm entry points need
+FFK_API long long ffk_batchnorm_scratch(long long R, int C) {
+  int rpc;
+  int chunks = bn_chunks(R, C, &rpc);
+  return (long long)chunks * 2 * C + 2 * (long long)C;
+}
+
+// y = act((x - mean) * rstd * gamma + beta) with batch statistics; mean/rstd [C] fp32 are saved for backward
+FFK_API int ffk_batchnorm_fwd(const void *x, void *y, const void *gamma, const void *beta, float *mean, float *rstd, float *scratch,
+                              long long R, int C, float eps, int relu, int dt, cudaStream_t st) {
+  if (R <= 0 || C <= 0) return 0;
+  int rpc;
+  int chunks = bn_chunks(R, C, &rpc);
+  dim3 grid((C + BN_TX - 1) / BN_TX, chunks), block(BN_TX, BN_TY);
+  long long total = R * C;
+  if (dt == 1) {
+    bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
+    bn_finalize_stats_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    if ((C % 2) == 0 && ((uintptr_t)x % 4) == 0 && ((uintptr_t)y % 4) == 0)
+      bn_apply_bf16x2_kernel<<<ffk_blocks(total / 2, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta,
+                                                                         mean, rstd, total / 2, C, relu);
+    else
+      bn_apply_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta, mean,
+                                                                    rstd, total, C, relu);
+  } else if (dt == 0) {
+    bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
+    bn_finalize_stats_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    bn_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (float *)y, (const float *)gamma, (const float *)beta,
+                                                                   mean, rstd, total, C, relu);
+  } else {
+    return -2;
+  }
+  return (int)cudaGetLastError();
+}
+
+// relu_y: the forward output when a ReLU was fused (masks dy), else null.  dgamma/dbeta may be null.
+FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y, const void *gamma, const float *mean, const float *rstd,
+                              void *dx, void *dgamma, void *dbeta, float *scratch, long long R, int C, int dt, int accumulate_dx,
+                              int accumulate_gamma, int accumulate_beta, cudaStream_t st) {
+  if (R <= 0 || C <= 0) return 0;
+  int rpc;
+  int chunks = bn_chunks(R, C, &rpc);
+  dim3 grid((C + BN_TX - 1) / BN_TX, chunks), block(BN_TX, BN_TY);
+  float *sums = scratch + (long long)chunks * 2 * C;
+  long long total = R * C;
+  float inv_r = 1.0f / (float)R;
+  if (dt == 1) {
+    bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
+    bn_finalize_grads_kernel<bf16><<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, sums, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
+                                                                     accumulate_beta);
+    if (dx)
+      bn_bwd_apply_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
+                                                                        (const bf16 *)gamma, mean, rstd, sums, (bf16 *)dx, total, C, inv_r,
+                                                                        accumulate_dx);
+  } else if (dt == 0) {
+    bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
+    bn_finalize_grads_kernel<float><<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, sums, (float *)dgamma, (float *)dbeta,
+                                                                      accumulate_gamma, accumulate_beta);
+    if (dx)
+      bn_bwd_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y,
+                                                                         (const float *)gamma, mean, rstd, sums, (float *)dx, total, C, inv_r,
+                                                                         accumulate_dx);
+  } else {
+    return -2;
+  }
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,123 @@
+"""Micro-benchmarks of single kernels with roofline fractions.
+
+    python -m flexflow_train_b200.ops.bench_kernels --op gemm --m 8192 --n 8192 --k 8192
+    python -m flexflow_train_b200.ops.bench_kernels --op layernorm --rows 32768 --cols 2048
+
+Each run does warm-up launches, then times `--iters` launches with CUDA events on the launching stream; inputs are
+sized past L2 or L2 is flushed between launches (``--flush``).  Prints one JSON line per op with achieved
+throughput against the measured peaks.  Small `--iters` with `--warmup 1` gives a short launch list for a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..utils.profiling import roofline
+from . import kernels as K
+
+
+def _time(fn, warmup, iters, flush):
+    buf = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def bench_gemm(a):
+    m, n, k = a.m, a.n, a.k
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16) if a.bias else None
+    ms = _time(lambda: K.matmul_nt(x, w, out=out, bias=bias, act="relu" if a.relu else None), a.warmup, a.iters, a.flush)
+    r = roofline(ms, flops=2.0 * m * n * k, hbm_bytes=2.0 * (m * k + n * k + m * n))
+    ref = None
+    if a.compare:
+        ref = _time(lambda: torch.matmul(x, w.t(), out=out), a.warmup, a.iters, a.flush)
+    return {"op": "gemm_nt_bf16", "m": m, "n": n, "k": k, "bias": a.bias, "relu": a.relu, **r, "torch_matmul_ms": ref,
+            "gemm_error": K.gemm_last_error()}
+
+
+def bench_layernorm(a):
+    rows, cols = a.rows, a.cols
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    g = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(cols, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, device="cuda")
+    rstd = torch.empty(rows, device="cuda")
+    ms = _time(lambda: K.layernorm_fwd(x, g, b, 1e-5, out=y, mean=mean, rstd=rstd), a.warmup, a.iters, a.flush)
+    return {"op": "layernorm_fwd_bf16", "rows": rows, "cols": cols, **roofline(ms, hbm_bytes=4.0 * rows * cols)}
+
+
+def bench_softmax(a):
+    rows, cols = a.rows, a.cols
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    y = torch.empty_like(x)
+    ms = _time(lambda: K.softmax_fwd(x, out=y), a.warmup, a.iters, a.flush)
+    return {"op": "softmax_fwd_bf16", "rows": rows, "cols": cols, **roofline(ms, hbm_bytes=4.0 * rows * cols)}
+
+
+def bench_batchnorm(a):
+    rows, cols = a.rows, a.cols
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    g = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(cols, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    mean = torch.empty(cols, device="cuda")
+    rstd = torch.empty(cols, device="cuda")
+    scratch = torch.empty(K.batchnorm_scratch(rows, cols), device="cuda")
+    ms = _time(lambda: K.batchnorm_fwd(x, y, g, b, mean, rstd, scratch, rows, cols, 1e-5, relu=True), a.warmup, a.iters, a.flush)
+    # two reads of x (statistics, then normalise) and one write
+    return {"op": "batchnorm_fwd_bf16", "rows": rows, "cols": cols, **roofline(ms, hbm_bytes=6.0 * rows * cols)}
+
+
+def bench_im2col(a):
+    n, c, h, w = a.batch, a.channels, a.size, a.size
+    x = torch.randn(n, h, w, c, device="cuda").to(torch.bfloat16)
+    g = K.ConvGeometry(n, c, h, w, 3, 3, 1, 1, 1, 1, K.nhwc_strides(n, c, h, w))
+    col = torch.empty(g.rows, g.kp, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: K.im2col(x, col, g), a.warmup, a.iters, a.flush)
+    return {"op": "im2col_3x3_bf16", "n": n, "c": c, "hw": h, **roofline(ms, hbm_bytes=2.0 * (x.numel() + col.numel()))}
+
+
+OPS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
+       "im2col": bench_im2col}
+
+
+def main(argv=None):
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--op", choices=sorted(OPS), required=True)
+    p.add_argument("--m", type=int, default=8192)
+    p.add_argument("--n", type=int, default=8192)
+    p.add_argument("--k", type=int, default=8192)
+    p.add_argument("--rows", type=int, default=32768)
+    p.add_argument("--cols", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=32)
+    p.add_argument("--channels", type=int, default=192)
+    p.add_argument("--size", type=int, default=35)
+    p.add_argument("--bias", action="store_true")
+    p.add_argument("--relu", action="store_true")
+    p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
+    p.add_argument("--flush", action="store_true", help="write a buffer larger than L2 between timed launches")
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--iters", type=int, default=10)
+    a = p.parse_args(argv)
+    print(json.dumps(OPS[a.op](a)))
+
+
+if __name__ == "__main__":
+    main()

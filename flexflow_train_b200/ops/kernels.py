@@ -446,8 +446,11 @@ def _tlib():
 
 
 def permute(src, perm, out=None, accumulate=False):
-    """out = src.permute(perm), materialised contiguously (accumulate: out += ...)."""
-    _cuda_contig(src, out)
+    """out = src.permute(perm), materialised contiguously (accumulate: out += ...).  `src` may be any strided
+    view (an expanded tensor broadcasts)."""
+    _cuda_contig(out)
+    if not src.is_cuda:
+        raise KernelError("kernel called with a CPU tensor")
     sizes = [src.shape[p] for p in perm]
     strides = [src.stride(p) for p in perm]
     out = torch.empty(sizes, dtype=src.dtype, device=src.device) if out is None else out
@@ -594,3 +597,115 @@ def softmax_dropout_bwd(dy, y, dx, p, salt, seed_tensor=None, scale=1.0):
     rows = y.numel() // cols
     _check(_sdlib().ffk_softmax_dropout_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, scale, p,
                                             salt & (2**64 - 1), _p(seed_tensor), _dt(y), _stream()), "ffk_softmax_dropout_bwd")
+
+
+# --------------------------------------------------------------------------- convolution support, pooling, batch norm
+def _decl_conv(l):
+    P, I, L, F, S = c_void_p, c_int, c_longlong, c_float, c_void_p
+    IP, LP = ctypes.POINTER(c_int), ctypes.POINTER(c_longlong)
+    sig = {
+        "ffk_im2col": ([P, P, IP, LP, I, S], c_int),
+        "ffk_col2im": ([P, P, IP, LP, I, I, S], c_int),
+        "ffk_filter_pack": ([P, P, I, I, I, I, I, I, S], c_int),
+        "ffk_filter_unpack": ([P, P, I, I, I, I, I, I, I, S], c_int),
+        "ffk_pool2d_fwd": ([P, P, P, IP, LP, I, I, S], c_int),
+        "ffk_pool2d_bwd": ([P, P, P, IP, LP, I, I, I, S], c_int),
+        "ffk_batchnorm_scratch": ([L, I], c_longlong),
+        "ffk_batchnorm_fwd": ([P, P, P, P, P, P, P, L, I, F, I, I, S], c_int),
+        "ffk_batchnorm_bwd": ([P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, S], c_int),
+    }
+    for name, (args, res) in sig.items():
+        fn = getattr(l, name)
+        fn.argtypes = args
+        fn.restype = res
+
+
+_conv_declared = [False]
+
+
+def _clib():
+    l = lib()
+    if not _conv_declared[0]:
+        _decl_conv(l)
+        _conv_declared[0] = True
+    return l
+
+
+class ConvGeometry:
+    """Window geometry shared by im2col/col2im and pooling: logical NCHW extents, the activation's element strides
+    in (n, c, h, w) order, and the padded GEMM depth Kp."""
+
+    def __init__(self, n, c, h, w, kh, kw, sh, sw, ph, pw, strides, kp=None):
+        self.n, self.c, self.h, self.w = n, c, h, w
+        self.kh, self.kw, self.sh, self.sw, self.ph, self.pw = kh, kw, sh, sw, ph, pw
+        self.oh = (h + 2 * ph - kh) // sh + 1
+        self.ow = (w + 2 * pw - kw) // sw + 1
+        k = kh * kw * c
+        self.k = k
+        self.kp = (k + 7) // 8 * 8 if kp is None else kp
+        self.rows = n * self.oh * self.ow
+        self._geom = (c_int * 13)(n, c, h, w, kh, kw, sh, sw, ph, pw, self.oh, self.ow, self.kp)
+        self._strides = (c_longlong * 4)(*strides)
+
+
+def nhwc_strides(n, c, h, w):
+    return (h * w * c, 1, w * c, c)
+
+
+def nchw_strides(n, c, h, w):
+    return (c * h * w, h * w, w, 1)
+
+
+def im2col(x, col, geom: ConvGeometry):
+    _cuda_contig(x, col)
+    _check(_clib().ffk_im2col(x.data_ptr(), col.data_ptr(), geom._geom, geom._strides, _dt(x), _stream()), "ffk_im2col")
+
+
+def col2im(dcol, dx, geom: ConvGeometry, accumulate=False):
+    _cuda_contig(dcol, dx)
+    _check(_clib().ffk_col2im(dcol.data_ptr(), dx.data_ptr(), geom._geom, geom._strides, _dt(dx), int(accumulate), _stream()),
+           "ffk_col2im")
+
+
+def filter_pack(w, wp, oc, c, kh, kw, kp):
+    _cuda_contig(w, wp)
+    _check(_clib().ffk_filter_pack(w.data_ptr(), wp.data_ptr(), oc, c, kh, kw, kp, _dt(w), _stream()), "ffk_filter_pack")
+
+
+def filter_unpack(dwp, dw, oc, c, kh, kw, kp, accumulate=False):
+    _cuda_contig(dwp, dw)
+    if dwp.dtype != torch.float32:
+        raise KernelError("filter_unpack: packed gradient must be fp32")
+    _check(_clib().ffk_filter_unpack(dwp.data_ptr(), dw.data_ptr(), oc, c, kh, kw, kp, _dt(dw), int(accumulate), _stream()),
+           "ffk_filter_unpack")
+
+
+def pool2d_fwd(x, y, arg, geom: ConvGeometry, mode: str):
+    _cuda_contig(x, y, arg)
+    _check(_clib().ffk_pool2d_fwd(x.data_ptr(), y.data_ptr(), _p(arg), geom._geom, geom._strides, 0 if mode == "max" else 1, _dt(x),
+                                  _stream()), "ffk_pool2d_fwd")
+
+
+def pool2d_bwd(dy, arg, dx, geom: ConvGeometry, mode: str, accumulate=False):
+    _cuda_contig(dy, arg, dx)
+    _check(_clib().ffk_pool2d_bwd(dy.data_ptr(), _p(arg), dx.data_ptr(), geom._geom, geom._strides, 0 if mode == "max" else 1,
+                                  _dt(dy), int(accumulate), _stream()), "ffk_pool2d_bwd")
+
+
+def batchnorm_scratch(rows, cols) -> int:
+    """fp32 elements of scratch that batchnorm_fwd / batchnorm_bwd need for [rows, cols]."""
+    return int(_clib().ffk_batchnorm_scratch(rows, cols))
+
+
+def batchnorm_fwd(x, y, gamma, beta, mean, rstd, scratch, rows, cols, eps, relu=False):
+    _cuda_contig(x, y, gamma, beta, mean, rstd, scratch)
+    _check(_clib().ffk_batchnorm_fwd(x.data_ptr(), y.data_ptr(), _p(gamma), _p(beta), mean.data_ptr(), rstd.data_ptr(),
+                                     scratch.data_ptr(), rows, cols, eps, int(relu), _dt(x), _stream()), "ffk_batchnorm_fwd")
+
+
+def batchnorm_bwd(dy, x, relu_y, gamma, mean, rstd, dx, dgamma, dbeta, scratch, rows, cols, accumulate_dx=False,
+                  accumulate_gamma=False, accumulate_beta=False):
+    _cuda_contig(dy, x, relu_y, gamma, mean, rstd, dx, dgamma, dbeta, scratch)
+    _check(_clib().ffk_batchnorm_bwd(dy.data_ptr(), x.data_ptr(), _p(relu_y), _p(gamma), mean.data_ptr(), rstd.data_ptr(), _p(dx),
+                                     _p(dgamma), _p(dbeta), scratch.data_ptr(), rows, cols, _dt(dy), int(accumulate_dx),
+                                     int(accumulate_gamma), int(accumulate_beta), _stream()), "ffk_batchnorm_bwd")

@@ -707,17 +707,40 @@ class SoftmaxOp(OpImpl):
 # ------------------------------------------------------------------------------------------ shape ops
 @register("FLAT", "RESHAPE")
 class ReshapeOp(OpImpl):
+    """A view of the input.  A channels-last 4-D input (output of a convolution stack) with more than one spatial
+    position is first brought back to the logical NCHW order, since the flattened feature order is part of the
+    model's meaning (it indexes the rows of the following Linear's weight)."""
+    layout_aware = True
+
     def setup(self):
         sh = dict(self.outputs)["OUTPUT"]
+        self.permute = None
+        src = self.inputs["INPUT"]
+        if self.ex.is_nhwc(src):
+            n, c, h, w = [int(v) for v in self.ex.graph.shape(src).piece_sizes]
+            if h * w > 1 and c > 1:
+                self.permute = (n, c, h, w)
+                self.alloc_out()
+                return
         self.out().data = self.x().view(list(sh.piece_sizes))
 
     def forward(self):
-        pass
+        if self.permute:
+            n, c, h, w = self.permute
+            K.permute(self.x().view(n, h, w, c), (0, 3, 1, 2), out=self.out().data.view(n, c, h, w))
 
     def backward(self):
         b = self.buf("INPUT")
-        if b.requires_grad:
+        if not b.requires_grad:
+            return
+        if self.permute:
+            n, c, h, w = self.permute
+            K.permute(self.out().grad.view(n, c, h, w), (0, 2, 3, 1), out=b.grad.view(n, h, w, c), accumulate=self.acc["INPUT"])
+        else:
             self.ex.write_grad(b, self.out().grad, self.acc["INPUT"])
+
+
+_LAYOUT_TRANSPARENT = set(_UNARY) | set(_BINARY) | {"DROPOUT", "CAST", "NOOP", "IDENTITY"}
 
 
 # ------------------------------------------------------------------------------------------ the executable
@@ -733,6 +756,7 @@ class Executable:
         if self.on_gpu:
             K.lib()  # fail loudly if the kernel library is missing
         self.values: Dict[Value, _Buf] = {}
+        self.layout: Dict[Value, str] = {}
         self.ops: Dict[int, OpImpl] = {}
         self.order: List[int] = list(graph.topological_order())
         self._scratch_bytes = 0
@@ -762,6 +786,24 @@ class Executable:
         """False when `slot` is the bias of an operator that produces partial sums and this rank is not the one
         that contributes it (a row-parallel Linear adds its bias once, not once per shard)."""
         return True
+
+    # ---- physical layout: 4-D activations produced by convolution-stack operators are kept channels-last
+    def is_nhwc(self, v: Value) -> bool:
+        return self.layout.get(self.canon(v)) == "NHWC"
+
+    def mark_nhwc(self, v: Value):
+        self.layout[v] = "NHWC"
+
+    def _propagate_layout(self, op: OpImpl):
+        ins = [v for _, v in op.inputs.items() if len(self.graph.shape(v).piece_sizes) == 4]
+        flags = [self.is_nhwc(v) for v in ins]
+        if not any(flags) or getattr(op, "layout_aware", False):
+            return
+        if op.type in _LAYOUT_TRANSPARENT and all(flags):
+            for s, _ in op.outputs:
+                self.mark_nhwc((op.nid, s))
+            return
+        raise NotImplementedError(f"operator {op.type} ({op.node['name']}) got a channels-last input it cannot consume")
 
     def next_salt(self) -> int:
         self._salt += 1
@@ -820,7 +862,9 @@ class Executable:
             self.ops[nid] = cls(self, nid, n)
         self._fuse()
         for nid in self.order:
-            self.ops[nid].setup()
+            op = self.ops[nid]
+            op.setup()
+            self._propagate_layout(op)
         # 4. loss
         self._build_loss()
         # 5. gradient buffers + accumulate flags
@@ -1219,3 +1263,6 @@ class Executable:
                 self.opt_m.copy_(sd["opt_m"])
             if "opt_v" in sd and self.opt_v is not None:
                 self.opt_v.copy_(sd["opt_v"])
+
+
+from . import executor_ops  # noqa: E402,F401  (registers the convolution-stack and tensor-shape operators)

@@ -1,0 +1,456 @@
+"""Operator implementations for convolution stacks (Conv2D, Pool2D, BatchNorm) and the tensor-shape operators
+(Concat, Split, Transpose, Reverse, Gather, TopK, Reduce*, Broadcast).
+
+Convolution stacks keep their 4-D activations channels-last in memory (the logical shape stays NCHW): a 1x1
+convolution is then the GEMM [N*H*W, C] x [OC, C]^T on the activation as it lies, a KxK convolution needs one
+im2col pass into a K-major bf16 matrix, and pooling / batch-norm / channel concatenation are coalesced over
+channels.  The executable tracks which values are channels-last; operators here declare ``layout_aware``.
+
+Reference operators: lib/kernels/src/cuda/ops/{conv_2d,pool_2d,batch_norm,concat,split,transpose,reverse,gather,
+topk,reduce}_kernels.cu and the task wrappers in lib/task-spec/src/task-spec/ops/impl/.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..ops import kernels as K
+from .executor import _ACT, OpImpl, register
+
+
+def _sizes(op: OpImpl, slot="INPUT") -> List[int]:
+    return [int(v) for v in op.ex.graph.shape(op.inputs[slot]).piece_sizes]
+
+
+def _scratch_view(ex, slot: int, shape, dtype):
+    n = 1
+    for s in shape:
+        n *= s
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    return ex._big[slot][:nbytes].view(dtype).view(list(shape))
+
+
+def _elt(dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
+
+
+# ------------------------------------------------------------------------------------------ Conv2D
+@register("CONV2D")
+class Conv2dOp(OpImpl):
+    layout_aware = True
+
+    def setup(self):
+        a = self.attrs
+        if int(a.get("groups", 1) or 1) != 1:
+            raise NotImplementedError("grouped convolution")
+        x = self.x()
+        if x.dtype != torch.bfloat16:
+            raise NotImplementedError("Conv2D runs on the bf16 tensor-core path; use compute_dtype='bf16'")
+        n, c, h, w = _sizes(self)
+        oc, _, kh, kw = _sizes(self, "FILTER")
+        self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"])
+        strides = K.nhwc_strides(n, c, h, w) if self.in_nhwc else K.nchw_strides(n, c, h, w)
+        self.g = g = K.ConvGeometry(n, c, h, w, kh, kw, int(a["stride_h"]), int(a["stride_w"]), int(a["padding_h"]),
+                                    int(a["padding_w"]), strides)
+        self.oc = oc
+        self.act = _ACT[a.get("activation")]
+        y = torch.empty(n, g.oh, g.ow, oc, dtype=x.dtype, device=x.device)
+        self.out().data = y
+        self.ex.mark_nhwc((self.nid, "OUTPUT"))
+        self.y2d = y.view(g.rows, oc)
+        pointwise = kh == 1 and kw == 1 and c % 8 == 0
+        # the activation itself is the GEMM operand of a 1x1 stride-1 convolution over channels-last data
+        self.direct = pointwise and g.sh == 1 and g.sw == 1 and g.ph == 0 and g.pw == 0 and (self.in_nhwc or h * w == 1)
+        self.packed = not pointwise  # a 1x1 filter [OC, C, 1, 1] already is the K-major matrix [OC, C]
+        w_ = self.x("FILTER")
+        self.wp = torch.empty(oc, g.kp, dtype=torch.bfloat16, device=x.device) if self.packed else w_.view(oc, g.kp)
+        self.bias = self.x("BIAS") if "BIAS" in self.inputs else None
+        self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
+        if not self.direct:
+            self.ex.need_big_scratch(g.rows * g.kp * 2, 2)  # slot 0: col, slot 1: dcol
+        if self.packed:
+            self.ex.need_big_scratch(oc * g.kp * 4, 3)  # slot 2: packed filter gradient (fp32)
+        self.ex.need_scratch(4 * K.bias_act_bwd_scratch(g.rows, oc))
+        self._col = self._dcol = self._dwp = None
+
+    def _operand(self):
+        if self.direct:
+            return self.x().view(self.g.rows, self.g.kp)
+        if self._col is None:
+            self._col = _scratch_view(self.ex, 0, (self.g.rows, self.g.kp), torch.bfloat16)
+        K.im2col(self.x(), self._col, self.g)
+        return self._col
+
+    def forward(self):
+        if self.packed:
+            g = self.g
+            K.filter_pack(self.x("FILTER"), self.wp, self.oc, g.c, g.kh, g.kw, g.kp)
+        K.matmul_nt(self._operand(), self.wp, out=self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
+
+    def backward(self):
+        g = self.g
+        dy = self.out().grad.view(g.rows, self.oc)
+        if self.act is not None or self.bias is not None:
+            saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
+            bb = self.buf("BIAS") if self.bias is not None else None
+            K.bias_act_bwd(dy, saved, dy if self.act else None, bb.grad if bb is not None else None, self.ex.scratch_f32(), self.act,
+                           accumulate=self.acc.get("BIAS", False))
+        wb = self.buf("FILTER")
+        if wb.requires_grad:
+            col = self._operand()  # recomputed rather than kept: it is KH*KW times the activation
+            if self.packed:
+                if self._dwp is None:
+                    self._dwp = _scratch_view(self.ex, 2, (self.oc, g.kp), torch.float32)
+                K.matmul_tn(dy, col, out=self._dwp)
+                K.filter_unpack(self._dwp, wb.grad, self.oc, g.c, g.kh, g.kw, g.kp, accumulate=self.acc["FILTER"])
+            else:
+                K.matmul_tn(dy, col, out=wb.grad.view(self.oc, g.kp), accumulate=self.acc["FILTER"])
+        xb = self.buf("INPUT")
+        if xb.requires_grad:
+            if self.direct:
+                K.matmul_nn(dy, self.wp, out=xb.grad.view(g.rows, g.kp), accumulate=self.acc["INPUT"])
+            else:
+                if self._dcol is None:
+                    self._dcol = _scratch_view(self.ex, 1, (g.rows, g.kp), torch.bfloat16)
+                K.matmul_nn(dy, self.wp, out=self._dcol)
+                K.col2im(self._dcol, xb.grad, g, accumulate=self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ Pool2D
+@register("POOL2D")
+class Pool2dOp(OpImpl):
+    layout_aware = True
+
+    def setup(self):
+        a = self.attrs
+        if a.get("activation"):
+            raise NotImplementedError("Pool2D with a fused activation")
+        x = self.x()
+        n, c, h, w = _sizes(self)
+        self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"])
+        strides = K.nhwc_strides(n, c, h, w) if self.in_nhwc else K.nchw_strides(n, c, h, w)
+        self.g = g = K.ConvGeometry(n, c, h, w, int(a["kernel_h"]), int(a["kernel_w"]), int(a["stride_h"]), int(a["stride_w"]),
+                                    int(a["padding_h"]), int(a["padding_w"]), strides, kp=0)
+        on, oc, oh, ow = [int(v) for v in dict(self.outputs)["OUTPUT"].piece_sizes]
+        if (oh, ow) != (g.oh, g.ow):
+            raise ValueError(f"Pool2D output extent {(oh, ow)} does not match its window geometry {(g.oh, g.ow)}")
+        self.mode = "max" if a.get("pool_type", "MAX") == "MAX" else "avg"
+        self.out().data = torch.empty(n, g.oh, g.ow, c, dtype=x.dtype, device=x.device)
+        self.ex.mark_nhwc((self.nid, "OUTPUT"))
+        self.arg = torch.empty(n * g.oh * g.ow * c, dtype=torch.uint8, device=x.device) \
+            if (self.mode == "max" and self.ex.cfg.training) else None
+
+    def forward(self):
+        K.pool2d_fwd(self.x(), self.out().data, self.arg, self.g, self.mode)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            K.pool2d_bwd(self.out().grad.view(-1), self.arg, b.grad, self.g, self.mode, accumulate=self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ BatchNorm
+@register("BATCHNORM")
+class BatchNormOp(OpImpl):
+    """Training-mode batch normalisation (batch statistics) with the optional fused ReLU of the reference's
+    BatchNormAttrs.  Under data parallelism the statistics are those of the local shard of the batch."""
+    layout_aware = True
+
+    def setup(self):
+        x = self.x()
+        n, c, h, w = _sizes(self)
+        self.shape = (n, c, h, w)
+        self.rows, self.cols = n * h * w, c
+        self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"]) or h * w == 1 or c == 1
+        self.relu = bool(self.attrs.get("relu"))
+        self.eps = float(self.attrs.get("eps", 1e-5))
+        self.gamma = self.x("GAMMA") if "GAMMA" in self.inputs else None
+        self.beta = self.x("BETA") if "BETA" in self.inputs else None
+        self.out().data = torch.empty(n, h, w, c, dtype=x.dtype, device=x.device)
+        self.ex.mark_nhwc((self.nid, "OUTPUT"))
+        self.mean = torch.empty(c, dtype=torch.float32, device=x.device)
+        self.rstd = torch.empty(c, dtype=torch.float32, device=x.device)
+        self.xcl = None if self.in_nhwc else torch.empty(n, h, w, c, dtype=x.dtype, device=x.device)
+        self.ex.need_scratch(4 * K.batchnorm_scratch(self.rows, self.cols))
+
+    def _x(self):
+        if self.in_nhwc:
+            return self.x()
+        n, c, h, w = self.shape
+        K.permute(self.x().view(n, c, h, w), (0, 2, 3, 1), out=self.xcl)
+        return self.xcl
+
+    def forward(self):
+        K.batchnorm_fwd(self._x(), self.out().data, self.gamma, self.beta, self.mean, self.rstd, self.ex.scratch_f32(), self.rows,
+                        self.cols, self.eps, relu=self.relu)
+
+    def backward(self):
+        xb = self.buf("INPUT")
+        gb = self.buf("GAMMA") if self.gamma is not None else None
+        bb = self.buf("BETA") if self.beta is not None else None
+        dy = self.out().grad.view(-1)
+        x = self.x() if self.in_nhwc else self.xcl
+        dx = None
+        if xb.requires_grad:
+            dx = xb.grad if self.in_nhwc else torch.empty_like(self.xcl)
+        K.batchnorm_bwd(dy, x, self.out().data if self.relu else None, self.gamma, self.mean, self.rstd, dx,
+                        gb.grad if gb is not None and gb.requires_grad else None,
+                        bb.grad if bb is not None and bb.requires_grad else None, self.ex.scratch_f32(), self.rows, self.cols,
+                        accumulate_dx=self.acc.get("INPUT", False) and self.in_nhwc,
+                        accumulate_gamma=self.acc.get("GAMMA", False), accumulate_beta=self.acc.get("BETA", False))
+        if dx is not None and not self.in_nhwc:
+            n, c, h, w = self.shape
+            K.permute(dx.view(n, h, w, c), (0, 3, 1, 2), out=xb.grad.view(n, c, h, w), accumulate=self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ Concat / Split
+def _phys_axis(shape4_nhwc: bool, axis: int, ndim: int):
+    """Axis and extents in memory order for a logical axis of a tensor that may be stored channels-last."""
+    if not shape4_nhwc:
+        return axis
+    return {0: 0, 1: 3, 2: 1, 3: 2}[axis]
+
+
+def _phys_sizes(sizes, nhwc):
+    if nhwc:
+        n, c, h, w = sizes
+        return [n, h, w, c]
+    return list(sizes)
+
+
+@register("CONCAT")
+class ConcatOp(OpImpl):
+    layout_aware = True
+
+    def setup(self):
+        k = int(self.attrs.get("num_inputs", len(self.inputs)))
+        self.slots = [f"INPUT_{i}" for i in range(k)]
+        flags = [self.ex.is_nhwc(self.inputs[s]) for s in self.slots]
+        if any(flags) and not all(flags):
+            raise NotImplementedError("Concat of channels-last and plain inputs")
+        self.nhwc = all(flags) and len(_sizes(self, self.slots[0])) == 4
+        out_sizes = [int(v) for v in dict(self.outputs)["OUTPUT"].piece_sizes]
+        axis = int(self.attrs["axis"]) % len(out_sizes)
+        pa = _phys_axis(self.nhwc, axis, len(out_sizes))
+        po = _phys_sizes(out_sizes, self.nhwc)
+        y = self.alloc_out(shape=po)
+        if self.nhwc:
+            self.ex.mark_nhwc((self.nid, "OUTPUT"))
+        self.outer = 1
+        for s in po[:pa]:
+            self.outer *= s
+        inner = 1
+        for s in po[pa + 1:]:
+            inner *= s
+        self.dst_ld = po[pa] * inner
+        self.blocks, off = [], 0
+        for s in self.slots:
+            ext = _phys_sizes(_sizes(self, s), self.nhwc)[pa] * inner
+            self.blocks.append((s, off, ext))
+            off += ext
+
+    def forward(self):
+        y = self.out().data
+        for s, off, ext in self.blocks:
+            K.block_copy(self.x(s), 0, ext, y, off, self.dst_ld, self.outer, ext)
+
+    def backward(self):
+        dy = self.out().grad
+        for s, off, ext in self.blocks:
+            b = self.buf(s)
+            if b.requires_grad:
+                K.block_copy(dy, off, self.dst_ld, b.grad, 0, ext, self.outer, ext, accumulate=self.acc[s])
+
+
+@register("SPLIT")
+class SplitOp(OpImpl):
+    def setup(self):
+        sizes = _sizes(self)
+        axis = int(self.attrs["axis"]) % len(sizes)
+        self.outer = 1
+        for s in sizes[:axis]:
+            self.outer *= s
+        inner = 1
+        for s in sizes[axis + 1:]:
+            inner *= s
+        self.src_ld = sizes[axis] * inner
+        self.blocks, off = [], 0
+        for slot, sh in self.outputs:
+            ext = int(sh.piece_sizes[axis]) * inner
+            self.alloc_out(slot)
+            self.blocks.append((slot, off, ext))
+            off += ext
+
+    def forward(self):
+        x = self.x()
+        for slot, off, ext in self.blocks:
+            K.block_copy(x, off, self.src_ld, self.out(slot).data, 0, ext, self.outer, ext)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        acc = self.acc["INPUT"]
+        if not acc and any(self.out(slot).grad is None for slot, _, _ in self.blocks):
+            b.grad.zero_()  # parts nobody consumed contribute zero
+        for slot, off, ext in self.blocks:
+            g = self.out(slot).grad
+            if g is not None:
+                K.block_copy(g, 0, ext, b.grad, off, self.src_ld, self.outer, ext, accumulate=acc)
+
+
+# ------------------------------------------------------------------------------------------ Transpose / Reverse
+@register("TRANSPOSE")
+class TransposeOp(OpImpl):
+    def setup(self):
+        self.perm = [int(p) for p in self.attrs["permutation"]]
+        self.inv = [self.perm.index(i) for i in range(len(self.perm))]
+        self.alloc_out()
+
+    def forward(self):
+        K.permute(self.x(), self.perm, out=self.out().data)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if b.requires_grad:
+            K.permute(self.out().grad.view_as(self.out().data), self.inv, out=b.grad.view_as(self.x()), accumulate=self.acc["INPUT"])
+
+
+@register("REVERSE")
+class ReverseOp(OpImpl):
+    def setup(self):
+        self.axis = int(self.attrs["axis"]) % self.x().dim()
+        self.alloc_out()
+
+    def forward(self):
+        K.reverse(self.x(), self.out().data, self.axis)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        dy = self.out().grad.view_as(self.x())
+        if self.acc["INPUT"]:
+            t = torch.empty_like(dy)
+            K.reverse(dy, t, self.axis)
+            self.ex.write_grad(b, t, True)
+        else:
+            K.reverse(dy, b.grad.view_as(dy), self.axis)
+
+
+# ------------------------------------------------------------------------------------------ Gather / TopK
+@register("GATHER")
+class GatherOp(OpImpl):
+    def setup(self):
+        self.dim = int(self.attrs["dim"]) % self.x().dim()
+        self.alloc_out()
+
+    def forward(self):
+        K.gather(self.x(), self.x("INDEX"), self.out().data, self.dim)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        if not self.acc["INPUT"]:
+            b.grad.zero_()
+        K.gather_bwd(self.out().grad.view_as(self.out().data), self.x("INDEX"), b.grad.view_as(self.x()), self.dim)
+
+
+@register("TOPK")
+class TopKOp(OpImpl):
+    def setup(self):
+        self.k = int(self.attrs["k"])
+        self.alloc_out("OUTPUT")
+        self.alloc_out("INDEX", dtype=torch.int32)
+
+    def forward(self):
+        K.topk(self.x(), self.k, vals=self.out("OUTPUT").data, idxs=self.out("INDEX").data)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if b.requires_grad and self.out("OUTPUT").grad is not None:
+            K.topk_bwd(self.out("OUTPUT").grad.view_as(self.out("OUTPUT").data), self.out("INDEX").data, b.grad.view_as(self.x()),
+                       accumulate=self.acc["INPUT"])
+
+
+# ------------------------------------------------------------------------------------------ Reduce / Broadcast
+_REDUCE = {"REDUCE_SUM": "sum", "REDUCE_MEAN": "mean", "MEAN": "mean", "REDUCE_MAX": "max", "REDUCE_MIN": "min",
+           "REDUCE_PROD": "prod"}
+
+
+def _contiguous_run(axes, what):
+    axes = sorted(axes)
+    if axes != list(range(axes[0], axes[0] + len(axes))):
+        raise NotImplementedError(f"{what} over non-adjacent axes {axes}")
+    return axes
+
+
+@register(*_REDUCE.keys())
+class ReduceOp(OpImpl):
+    def setup(self):
+        self.op = _REDUCE[self.type]
+        sizes = _sizes(self)
+        axes = _contiguous_run([int(a) % len(sizes) for a in self.attrs["axes"]], "reduction")
+        self.outer = self.red = self.inner = 1
+        for i, s in enumerate(sizes):
+            if i < axes[0]:
+                self.outer *= s
+            elif i > axes[-1]:
+                self.inner *= s
+            else:
+                self.red *= s
+        self.alloc_out()
+
+    def forward(self):
+        K.reduce(self.x(), self.out().data, self.outer, self.red, self.inner, self.op)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        if self.op not in ("sum", "mean"):
+            raise NotImplementedError(f"backward of a {self.op} reduction")
+        K.reduce_bwd(self.out().grad.view(-1), b.grad.view(-1), self.outer, self.red, self.inner,
+                     1.0 if self.op == "sum" else 1.0 / self.red, accumulate=self.acc["INPUT"])
+
+
+@register("BROADCAST")
+class BroadcastOp(OpImpl):
+    def setup(self):
+        tgt = [int(v) for v in dict(self.outputs)["OUTPUT"].piece_sizes]
+        src = _sizes(self)
+        pad = [1] * (len(tgt) - len(src)) + src
+        self.src_view = pad
+        self.tgt = tgt
+        self.bcast_axes = [i for i, (a, b) in enumerate(zip(pad, tgt)) if a == 1 and b > 1]
+        self.alloc_out()
+
+    def forward(self):
+        x = self.x().view(self.src_view).expand(self.tgt)
+        K.permute(x, list(range(len(self.tgt))), out=self.out().data)
+
+    def backward(self):
+        b = self.buf("INPUT")
+        if not b.requires_grad:
+            return
+        dy = self.out().grad.view(self.tgt)
+        if not self.bcast_axes:
+            self.ex.write_grad(b, dy, self.acc["INPUT"])
+            return
+        axes = _contiguous_run(self.bcast_axes, "broadcast gradient")
+        outer = red = inner = 1
+        for i, s in enumerate(self.tgt):
+            if i < axes[0]:
+                outer *= s
+            elif i > axes[-1]:
+                inner *= s
+            else:
+                red *= s
+        if self.acc["INPUT"]:
+            t = torch.empty(outer * inner, dtype=dy.dtype, device=dy.device)
+            K.reduce(dy, t, outer, red, inner, "sum")
+            self.ex.write_grad(b, t, True)
+        else:
+            K.reduce(dy, b.grad.view(-1), outer, red, inner, "sum")

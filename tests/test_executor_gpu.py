@@ -71,3 +71,43 @@ def test_adam_cuda_graph_matches_eager():
     assert out[0][-1] < out[0][0]
     for a, b in zip(*out):
         assert abs(a - b) < 2e-2 * abs(a), out
+
+
+def _shape_ops_graph():
+    b = core.GraphBuilder()
+    x = b.create_input([8, 16], name="input")
+    idx = b.create_input([8, 5], dtype="INT32", name="index")
+    h = b.dense(x, 16, activation="TANH", name="fc0")
+    p0, p1 = b.split(h, [10, 6], 1, name="split")
+    a = b.reverse(p0, 1, name="rev")
+    t = b.transpose(p1, [1, 0], name="tr")
+    t = b.unary("SCALAR_MULTIPLY", t, 2.0, name="scale")
+    t = b.transpose(t, [1, 0], name="tr_back")
+    c = b.concat([a, t], 1, name="cat")
+    r = b.reduce("REDUCE_MEAN", c, [1], True, name="rowmean")
+    rb = b.broadcast(r, [8, 16], name="bcast")
+    c = b.binary("EW_SUB", c, rb, name="center")
+    top = b.top_k(c, 4, name="topk")[0]
+    gat = b.gather(c, idx, 1, name="gather")
+    f = b.concat([c, top, gat], 1, name="features")
+    y = b.dense(f, 8, name="fc1")
+    b.softmax(y, name="out_prob")
+    return b.graph
+
+
+def test_tensor_shape_operators_match_oracle():
+    g = _shape_ops_graph()
+    ex = Executable(g, ExecConfig(compute_dtype="fp32", seed=2))
+    oracle = TorchOracle(g, seed=2)
+    torch.manual_seed(0)
+    x = torch.randn(8, 16)
+    idx = torch.randint(0, 16, (8, 5), dtype=torch.int32)
+    labels = torch.randint(0, 8, (8,), dtype=torch.int32)
+    ex.set_inputs({"input": x.cuda(), "index": idx.cuda()}, labels.cuda())
+    ex.forward()
+    ex.compute_loss()
+    ex.backward()
+    rows_ref, grads_ref = oracle.loss_and_grads({"input": x, "index": idx}, labels)
+    assert rel(ex.loss_rows, rows_ref) < 2e-2
+    for name, g_ in ex.named_gradients():
+        assert rel(g_, grads_ref[name]) < 5e-2, (name, rel(g_, grads_ref[name]))
