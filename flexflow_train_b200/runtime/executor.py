@@ -1162,6 +1162,10 @@ class Executable:
     def sync_gradients(self):
         """Hook for the distributed executable (gradient all-reduce of replicated weights)."""
 
+    def zero_gradients(self):
+        """Nothing to clear: the plan marks, per gradient buffer, which operator writes it first (a plain store)
+        and which accumulate, so no buffer is read before it has been written in the same step."""
+
     def update(self):
         o = self.cfg.optimizer
         self.step_count += 1

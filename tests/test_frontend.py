@@ -1,0 +1,199 @@
+"""Frontends on the CPU execution path: layer API, torch.fx importer (+ text IR), ONNX importer, Keras classes."""
+from types import SimpleNamespace as NS
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from flexflow_train_b200.api import FFConfig
+from flexflow_train_b200.frontend import (ActiMode, AdamOptimizer, DataType, FFModel, LossType, MetricsType, PoolType, SGDOptimizer)
+from flexflow_train_b200.frontend import keras
+from flexflow_train_b200.frontend.onnx_model import ONNXModel
+from flexflow_train_b200.frontend.torch_fx import PyTorchModel
+
+
+def _toy_data(n=128, d=20, classes=4, seed=0):
+    rng = np.random.RandomState(seed)
+    x = rng.randn(n, d).astype(np.float32)
+    y = (x @ rng.randn(d, classes)).argmax(1).astype(np.int32).reshape(-1, 1)
+    return x, y
+
+
+def test_ffmodel_layer_api_fit_and_eval():
+    m = FFModel(FFConfig(batch_size=32))
+    x = m.create_tensor([32, 20], DataType.DT_FLOAT, name="x")
+    t = m.dense(x, 32, ActiMode.AC_MODE_RELU, name="fc1")
+    t = m.dropout(t, 0.0, 0)
+    t = m.softmax(m.dense(t, 4, name="fc2"))
+    m.compile(AdamOptimizer(m, alpha=0.01), LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY,
+              [MetricsType.METRICS_ACCURACY, MetricsType.METRICS_SPARSE_CATEGORICAL_CROSSENTROPY], device="cpu")
+    X, Y = _toy_data()
+    hist = m.fit(X, Y, epochs=15)
+    assert hist[-1] < 0.5 * hist[0]
+    assert m.eval(X, Y).accuracy > 0.9
+    assert m.get_layer_by_name("fc1").get_weight_tensor().dims == (32, 20)
+    assert m.label_tensor["dims"] == (32, 1)
+    assert len(m.get_layers()) == 4
+
+
+def test_ffmodel_piecewise_step_matches_fit_step():
+    def build():
+        m = FFModel(FFConfig(batch_size=16, seed=3))
+        x = m.create_tensor([16, 20], name="x")
+        m.softmax(m.dense(m.dense(x, 8, ActiMode.AC_MODE_TANH), 4))
+        m.compile(SGDOptimizer(m, lr=0.1, momentum=0.9), LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY, device="cpu")
+        return m
+    X, Y = _toy_data(16)
+    a, b = build(), build()
+    a.fit(X, Y, epochs=2)
+    dlx, dly = b.create_data_loader(b._inputs[0], X), b.create_data_loader(None, Y)
+    for _ in range(2):
+        dlx.reset(); dly.reset()
+        b._next_batch([dlx], dly)
+        b.forward(); b.zero_gradients(); b.backward(); b.update()
+    for (_, p), (_, q) in zip(a.executable.named_parameters(), b.executable.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-6)
+
+
+def test_all_layer_methods_build_a_valid_graph():
+    m = FFModel(FFConfig(batch_size=4))
+    x = m.create_tensor([4, 3, 16, 16], name="img")
+    t = m.conv2d(x, 8, 3, 3, 1, 1, 1, 1, ActiMode.AC_MODE_RELU)
+    t = m.batch_norm(t, relu=True)
+    t = m.pool2d(t, 2, 2, 2, 2, 0, 0, PoolType.POOL_MAX)
+    t = m.flat(t)
+    a, b = m.split(t, [256, 256], 1)
+    t = m.concat([m.add(a, b), m.subtract(a, b), m.multiply(a, b), m.max(a, b), m.min(a, b)], 1)
+    t = m.dense(t, 32)
+    for f in (m.exp, m.sin, m.cos, m.rsqrt, m.gelu, m.relu, m.sigmoid, m.tanh, m.elu, m.identity):
+        t = f(t)
+    t = m.scalar_true_divide(m.scalar_sub(m.scalar_add(m.scalar_multiply(m.pow(t, 2.0), 0.5), 1.0), 0.25), 2.0)
+    t = m.layer_norm(t, [-1])
+    t = m.reverse(m.transpose(m.reshape(t, [4, 4, 8]), [0, 2, 1]), 1)
+    t = m.batch_matmul(t, m.transpose(t, [0, 2, 1]))
+    t = m.reduce_sum(t, [2])
+    t = m.mean(m.reshape(t, [4, 2, 4]), [1])
+    q = m.create_tensor([4, 6, 16], name="seq")
+    att = m.multihead_attention(q, q, q, 16, 4)
+    ids = m.create_tensor([4, 6, 1], DataType.DT_INT32, name="ids")
+    emb = m.embedding(ids, 50, 16)
+    s = m.reduce_sum(m.add(att, emb), [1])
+    idx = m.create_tensor([4, 3], DataType.DT_INT32, name="gidx")
+    g = m.gather(s, idx, 1)
+    out = m.softmax(m.dense(m.concat([t, g], 1), 5))
+    assert out.dims == (4, 5)
+    types = {n["type"] for n in m.graph.nodes()}
+    for need in ("CONV2D", "BATCHNORM", "POOL2D", "SPLIT", "CONCAT", "BATCHMATMUL", "MULTIHEAD_ATTENTION", "EMBEDDING", "GATHER",
+                 "REVERSE", "TRANSPOSE", "REDUCE_SUM", "LAYERNORM"):
+        assert need in types, need
+
+
+class _Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1 = nn.Conv2d(3, 8, 3, padding=1)
+        self.bn = nn.BatchNorm2d(8)
+        self.pool = nn.MaxPool2d(2)
+        self.gap = nn.AdaptiveAvgPool2d((2, 2))
+        self.fc1 = nn.Linear(8 * 2 * 2, 32)
+        self.ln = nn.LayerNorm(32)
+        self.act = nn.GELU()
+        self.fc2 = nn.Linear(32, 5)
+        self.drop = nn.Dropout(0.0)
+
+    def forward(self, x):
+        t = torch.relu(self.bn(self.c1(x)))
+        t = self.gap(self.pool(t))
+        t = torch.flatten(t, 1)
+        a, b = torch.split(self.fc1(t), 16, 1)
+        t = torch.cat([a * 2.0, (b + a) / 2], 1)
+        t = self.act(self.ln(t)).view(t.size(0), -1)
+        t = t.unsqueeze(1).transpose(1, 2).reshape(t.shape[0], 32).contiguous().float()
+        return torch.softmax(self.fc2(self.drop(t)), -1)
+
+
+def test_torch_fx_import_matches_pytorch_and_text_ir_roundtrips(tmp_path):
+    torch.manual_seed(0)
+    net = _Net()
+    m = FFModel(FFConfig(batch_size=4))
+    x = m.create_tensor([4, 3, 8, 8], name="x")
+    pm = PyTorchModel(net)
+    outs = pm.torch_to_ff(m, [x])
+    assert len(outs) == 1 and outs[0].dims == (4, 5)
+    m.compile(SGDOptimizer(lr=0.01), LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY, device="cpu")
+    assert pm.copy_parameters(m) == len(list(net.parameters()))
+    xin = torch.randn(4, 3, 8, 8)
+    net.train()  # batch statistics, as the executor computes them
+    assert torch.allclose(net(xin), m.executable.infer({"x": xin}), atol=1e-5)
+    fn = tmp_path / "net.ir"
+    pm.torch_to_file(str(fn))
+    m2 = FFModel(FFConfig(batch_size=4))
+    PyTorchModel.file_to_ff(str(fn), m2, [m2.create_tensor([4, 3, 8, 8], name="x")])
+    assert m.graph.to_v1_string() == m2.graph.to_v1_string()
+
+
+def test_torch_fx_unsupported_module_is_reported():
+    class Bad(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.LSTM(4, 4)
+
+        def forward(self, x):
+            return self.l(x)
+    with pytest.raises(NotImplementedError):
+        PyTorchModel(Bad()).to_ir()
+
+
+def _onnx_attr(name, **kw):
+    return NS(name=name, ints=kw.get("ints"), floats=None, s=kw.get("s"), t=None, f=kw.get("f"), i=kw.get("i", 0), type=kw.get("type"))
+
+
+def test_onnx_importer_on_a_protobuf_shaped_graph():
+    init = lambda name, dims: NS(name=name, dims=dims, numpy_value=np.zeros(dims, np.float32))  # noqa: E731
+    shape_init = NS(name="shape", dims=[2], numpy_value=np.array([0, -1], np.int64))
+    nodes = [
+        NS(op_type="Conv", name="conv", input=["x", "w", "b"], output=["c"], attribute=[_onnx_attr("kernel_shape", ints=[3, 3]),
+                                                                                       _onnx_attr("pads", ints=[1, 1, 1, 1]),
+                                                                                       _onnx_attr("strides", ints=[1, 1])]),
+        NS(op_type="BatchNormalization", name="bn", input=["c"], output=["n"], attribute=[]),
+        NS(op_type="Relu", name="relu", input=["n"], output=["r"], attribute=[]),
+        NS(op_type="MaxPool", name="mp", input=["r"], output=["p"], attribute=[_onnx_attr("kernel_shape", ints=[2, 2]),
+                                                                               _onnx_attr("strides", ints=[2, 2])]),
+        NS(op_type="GlobalAveragePool", name="gap", input=["p"], output=["g"], attribute=[]),
+        NS(op_type="Reshape", name="rs", input=["g", "shape"], output=["f"], attribute=[]),
+        NS(op_type="Gemm", name="fc", input=["f", "fw", "fb"], output=["l"], attribute=[_onnx_attr("transB", i=1, type=2)]),
+        NS(op_type="Dropout", name="do", input=["l"], output=["d"], attribute=[_onnx_attr("ratio", f=0.25, type=1)]),
+        NS(op_type="Softmax", name="sm", input=["d"], output=["y"], attribute=[_onnx_attr("axis", i=1, type=2)]),
+    ]
+    graph = NS(node=nodes, initializer=[init("w", [8, 3, 3, 3]), init("b", [8]), init("fw", [10, 8]), init("fb", [10]), shape_init],
+               output=[NS(name="y")])
+    m = FFModel(FFConfig(batch_size=2))
+    x = m.create_tensor([2, 3, 8, 8], name="x")
+    outs = ONNXModel(NS(graph=graph)).apply(m, {"x": x})
+    assert outs[0].dims == (2, 10)
+    kinds = [n["type"] for n in m.graph.nodes() if n["type"] not in ("WEIGHT", "INPUT")]
+    assert kinds == ["CONV2D", "BATCHNORM", "RELU", "POOL2D", "POOL2D", "RESHAPE", "LINEAR", "DROPOUT", "SOFTMAX"]
+    with pytest.raises(NotImplementedError):
+        ONNXModel(NS(graph=NS(node=[NS(op_type="LSTM", name="l", input=["x"], output=["y"], attribute=[])], initializer=[], output=[]))) \
+            .apply(m, {"x": x})
+
+
+def test_keras_sequential_and_functional_models_train():
+    from flexflow_train_b200.frontend.keras.callbacks import EpochVerifyMetrics, LearningRateScheduler
+    from flexflow_train_b200.frontend.keras.layers import Dense, concatenate
+
+    X, Y = _toy_data()
+    m = keras.Sequential([Dense(32, activation="relu", input_shape=(20,)), Dense(4, activation="softmax")])
+    m.compile(optimizer=keras.optimizers.Adam(0.01), loss="sparse_categorical_crossentropy", metrics=["accuracy"], batch_size=32,
+              device="cpu")
+    h = m.fit(X, Y, epochs=30, callbacks=[EpochVerifyMetrics(95), LearningRateScheduler(lambda e: 0.01)])
+    assert h.history["accuracy"][-1] >= 0.95 and len(h.epoch) < 30  # stopped early
+    a, b = keras.Input((20,), name="a"), keras.Input((20,), name="b")
+    out = Dense(4, activation="softmax")(concatenate([Dense(16, activation="relu")(a), Dense(16, activation="tanh")(b)]))
+    fm = keras.Model([a, b], out)
+    fm.compile("sgd", "sparse_categorical_crossentropy", ["accuracy"], batch_size=32, device="cpu")
+    hist = fm.fit([X, X], Y, epochs=3).history["loss"]
+    assert hist[-1] < hist[0]
+    assert fm.predict([X, X]).shape == (128, 4)
+    assert fm.evaluate([X, X], Y)["samples"] == 128
