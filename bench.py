@@ -30,6 +30,19 @@ MODEL_CONFIGS = {
                                              "dim_feedforward": 2048, "num_heads": 8, "num_decoder_layers": 2,
                                              "dropout": 0.1, "vocab_size": 4096}),
     "bert_base": ("bert", {"token_ids": True, "batch_size": 64, "sequence_length": 512, "vocab_size": 30528}),
+    "inception_v3": ("inception_v3", {"batch_size": 256, "num_classes": 1000}),
+    "dlrm": ("dlrm", {"batch_size": 4096, "embedding_dim": 64, "embedding_bag_size": 1, "embedding_size": [1000000] * 8,
+                      "dense_arch_layer_sizes": [13, 512, 256, 64], "over_arch_layer_sizes": [512, 512, 256, 1],
+                      "arch_interaction_op": "DOT", "final_activation": "SIGMOID", "embedding_data_type": "FLOAT",
+                      "embedding_init_range": 0.01}),
+}
+# optimizer and loss per model, as the benchmark configurations name them
+TRAINING = {
+    "transformer_large": ("adam", 1e-4, 0.0, "sparse_categorical_crossentropy"),
+    "transformer_small": ("adam", 1e-4, 0.0, "sparse_categorical_crossentropy"),
+    "bert_base": ("adam", 1e-4, 0.0, "sparse_categorical_crossentropy"),
+    "inception_v3": ("sgd", 0.01, 0.9, "sparse_categorical_crossentropy"),
+    "dlrm": ("sgd", 0.01, 0.0, "mean_squared_error_avg_reduce"),
 }
 
 
@@ -91,6 +104,79 @@ def reference_arm(args):
     return 0
 
 
+def torch_arm(args):
+    """Library baseline on one GPU: the same computation graph evaluated with stock PyTorch operators (cuBLAS /
+    cuDNN / the library attention kernel) under bf16 autocast with fp32 master weights and torch.optim, fed and
+    timed the same way.  None of this repository's kernels or executors are on this path."""
+    import torch
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.bin.run_model import synthetic_batch
+    from flexflow_train_b200.runtime.torch_oracle import TorchOracle
+
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
+        print(json.dumps({"impl": "torch", "unavailable": "the PyTorch library baseline is single-GPU"}))
+        return 0
+    model_name, mcfg = MODEL_CONFIGS[args.model]
+    opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
+    global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
+    g = core.build_model(model_name, dict(mcfg))
+    try:
+        orc = TorchOracle(g, loss=loss_kind, seed=0, device="cuda", dropout=True)
+        orc.use_sdpa = True
+        params = list(orc.params.values())
+        opt = torch.optim.Adam(params, lr=lr, fused=True) if opt_kind == "adam" else torch.optim.SGD(params, lr=lr, momentum=momentum)
+
+        class _Shape:  # the batch generator only needs the loss value of the graph
+            loss_value = orc.loss_value
+        host = [synthetic_batch(g, _Shape, loss_kind, seed=1234 + i) for i in range(4)]
+        if "vocab_size" in mcfg:
+            gen = torch.Generator().manual_seed(1234)
+            for i, (ins, lab) in enumerate(host):
+                lab.copy_(torch.randint(0, mcfg["vocab_size"], lab.shape, generator=gen, dtype=lab.dtype))
+        dev = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host]
+
+        def step(ins, lab):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                pred = orc.forward(ins)
+            loss = orc.loss(pred.float(), lab).mean()
+            loss.backward()
+            opt.step()
+            return loss
+
+        for i in range(max(args.warmup, 3)):
+            step(*dev[i % 4])
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(*dev[i % 4])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            ins, lab = host[i % 4]
+            loss = step({k: v.cuda(non_blocking=True) for k, v in ins.items()}, lab.cuda(non_blocking=True))
+            float(loss)
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    except torch.OutOfMemoryError as e:
+        print(json.dumps({"impl": "torch", "unavailable": f"out of memory on this config: {str(e)[:120]}"}))
+        return 0
+    print(json.dumps({"metric": "train samples/s (searched strategy)", "value": global_batch / (ms / 1e3), "unit": "samples/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast", "data": "synthetic", "impl": "torch",
+                      "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "parallelism": "single",
+                                 "optimizer": opt_kind, "lr": lr}, "clocks": clocks,
+                      "e2e": {"value": global_batch / (e2e_ms / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms},
+                      "gpu_launches": 0, "final_loss": float(loss)}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -103,6 +189,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "torch":
+        return torch_arm(args)
     if args.warmup < 3:
         args.warmup = 3
 
@@ -127,14 +215,15 @@ def main():
 
     model_name, mcfg = MODEL_CONFIGS[args.model]
     mcfg = dict(mcfg)
-    global_batch, seq = mcfg["batch_size"], mcfg["sequence_length"]
+    global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
+    opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
                          search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel"}.get(args.strategy, "unity"),
                          import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
-    lr = 1e-4
-    model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind="adam", lr=lr), dist=dctx)
+    model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind=opt_kind, lr=lr, momentum=momentum),
+                        loss=loss_kind, dist=dctx)
     ex = model.executable
-    vocab = mcfg["vocab_size"]
+    vocab = mcfg.get("vocab_size", 0)
     # every rank is handed the global batch (token ids are tiny); the strategy's Repartition keeps the local slice
     local_batch = global_batch
 
@@ -147,10 +236,15 @@ def main():
                          torch.where(torch.rand(local_batch, seq, generator=gen) < 0.15,
                                      torch.randint(0, 30522, (local_batch, seq), generator=gen), torch.tensor(-1)).to(torch.int32).pin_memory())
                         for _ in range(n_host)]
-    else:
+    elif model_name == "transformer_lm":
         host_batches = [({"input_ids": torch.randint(0, vocab, (local_batch, seq, 1), generator=gen, dtype=torch.int32).pin_memory()},
                          torch.randint(0, vocab, (local_batch, seq), generator=gen, dtype=torch.int32).pin_memory())
                         for _ in range(n_host)]
+    else:  # images / dense + sparse features drawn as the config names them, shapes from the graph's inputs
+        from flexflow_train_b200.bin.run_model import synthetic_batch
+        host_batches = [synthetic_batch(model.graph, ex, loss_kind, seed=1234 + i) for i in range(n_host)]
+        if model_name == "dlrm":  # binary labels
+            host_batches = [(i, (l > 0.5).to(l.dtype).pin_memory()) for i, l in host_batches]
     dev_batches = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host_batches]
 
     def barrier():
@@ -206,7 +300,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq,
                        "parallelism": getattr(ex, "parallelism", "single"), "layers": mcfg.get("num_decoder_layers", 12),
-                       "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768)), "optimizer": "adam", "lr": lr,
+                       "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768)), "optimizer": opt_kind, "lr": lr,
                        "l2": "activations and weights per step (>100 GB) exceed the 126 MB L2; no flush needed",
                        "cuda_graph": bool(ex.cfg.use_cuda_graph), "tokens_per_s": value * seq},
             "clocks": clocks,

@@ -66,10 +66,17 @@ def data_parallel_strategy(cg, world: int, rules=None):
     return core.apply_rules_exhaustively(pcg, sel, 100000, world)
 
 
-def tensor_parallel_strategy(cg, world: int, rules=None):
+def tensor_parallel_strategy(cg, world: int, rules=None, sequence_parallel: bool = True):
     """Megatron-style template expressed with the substitution rules: attention heads sharded
     (replicate-attention-reduce), the first Linear of each MLP column-parallel (replicate-linear-combine), the
-    second row-parallel (partition-linear-reduce), the pointwise ops between them sharded on the feature dim."""
+    second row-parallel (partition-linear-reduce), the pointwise ops between them sharded on the feature dim.
+
+    With ``sequence_parallel`` every operator the template leaves replicated (LayerNorm, residual add, dropout,
+    embedding, the vocabulary projection and softmax) is then sharded over the sample dim with the data-parallel
+    rules.  The activations between two tensor-parallel regions are thereby held as row shards: each Reduction is
+    followed by a Repartition (together a reduce-scatter, fused into the producing GEMM) and each Replicate is
+    preceded by a Combine (together an all-gather, fused into the consuming GEMM), and nothing is computed
+    redundantly."""
     ms = machine_for(world)
     rules = rules or core.get_substitution_set(ms)
     by_name = {r.name: r for r in rules}
@@ -114,14 +121,38 @@ def tensor_parallel_strategy(cg, world: int, rules=None):
                any(r.name.startswith(f"partition_{op}_combine_") for op in ("DROPOUT", "RELU", "GELU", "SIGMOID", "TANH"))
                and r.name.endswith(f"_{W}") and not r.name.endswith(f"_0_{W}")]
 
-    def between(n):
-        v = tuple(n["inputs"][0][1])
-        return g.node(v[0])["type"] == "COMBINE"
+    def between(rule_dim):
+        def pred(n):
+            v = tuple(n["inputs"][0][1])
+            # only the feature (last) dim continues the column-parallel sharding of the producing Linear
+            return g.node(v[0])["type"] == "COMBINE" and rule_dim == len(n["outputs"][0][1].sizes) - 1
+        return pred
 
     for r in feature:
-        g = apply_where(g, r, between, W)
+        g = apply_where(g, r, between(int(r.name.split("_")[-2])), W)
     g = core.apply_rules_exhaustively(g, cancellation_rules(rules), 100000, W)
-    return g
+    if sequence_parallel:
+        g = shard_replicated_operators(g, W, rules)
+    return core.merge_duplicate_parallel_ops(g)
+
+
+def shard_replicated_operators(g, world: int, rules):
+    """Apply the sample-dim (dim 0) partition rules to every operator whose activations are still unsharded,
+    then cancel the Combine/Repartition pairs that meet."""
+    weight_slots = ("WEIGHT", "BIAS", "GAMMA", "BETA", "FILTER", "INPUT_BIAS", "OUTPUT_BIAS")
+
+    def unsharded(graph):
+        def pred(n):
+            if n["type"] in ("INPUT", "WEIGHT") or core.is_parallel_op(n["type"]):
+                return False
+            acts = [graph.shape(tuple(v)) for s, v in n["inputs"] if s not in weight_slots]
+            outs = [o[1] for o in n["outputs"]]
+            return all(sh.total_degree == 1 for sh in acts + outs) and all(sh.sizes[0] % world == 0 for sh in acts + outs)
+        return pred
+
+    for r in data_parallel_rules(rules, world):
+        g = apply_where(g, r, unsharded(g), world)
+    return core.apply_rules_exhaustively(g, cancellation_rules(rules), 100000, world)
 
 
 def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = "unity", budget: int = 0, alpha: float = 1.05,

@@ -796,7 +796,37 @@ std::string legacy_rule_as_dot(const Json &rule) {
 }
 
 // ---------------------------------------------------------------- python bindings
+// Parallel operators with the same kind, attributes and input compute the same tensor: keep one of each and
+// point every consumer at it (applying a rule once per input slot of an operator leaves such copies behind, e.g.
+// three Replicates of the same tensor in front of self-attention).
+Graph merge_duplicate_parallel_ops(const Graph &g_in) {
+  Graph g = g_in;
+  bool changed = true;
+  while (changed) {
+    changed = false;
+    std::map<std::string, NodeId> seen;
+    for (NodeId n : g.topological_order()) {
+      const Node &nd = g.node(n);
+      if (!is_parallel_op(nd.type) || nd.inputs.size() != 1 || nd.outputs.size() != 1) continue;
+      std::string key = to_string(nd.type) + "|" + nd.attrs.dump() + "|" + std::to_string(nd.inputs[0].src.node) + ":" +
+                        to_string(nd.inputs[0].src.slot);
+      auto it = seen.find(key);
+      if (it == seen.end()) {
+        seen[key] = n;
+        continue;
+      }
+      ValueRef from{n, nd.outputs[0].slot}, to{it->second, g.node(it->second).outputs[0].slot};
+      g.replace_uses(from, to);
+      g.remove_node(n);
+      changed = true;
+      break;
+    }
+  }
+  return g;
+}
+
 void bind_substitutions(py::module &m) {
+  m.def("merge_duplicate_parallel_ops", &merge_duplicate_parallel_ops);
   py::class_<Substitution>(m, "Substitution")
       .def_readonly("name", &Substitution::name)
       .def("to_json", [](const Substitution &s) { return json_to_py(s.to_json()); })

@@ -28,7 +28,7 @@ from ..runtime import executor as E
 from ..runtime.executor import ExecConfig, Executable, OpImpl, Value, register
 from . import comm
 from .context import DistContext
-from .fused_ops import GradAllReduce
+from .fused_ops import AllGatherGemm, GemmReduceScatter, GradAllReduce
 
 PARALLEL = ("REPARTITION", "COMBINE", "REPLICATE", "REDUCTION")
 
@@ -41,7 +41,14 @@ def _degree(attrs) -> int:
 
 
 class _ParallelOp(OpImpl):
-    """Common part: on one device, or inside a weight chain, a parallel operator is an alias of its input."""
+    """Common part: on one device, or inside a weight chain, a parallel operator is an alias of its input.
+
+    ``absorbed`` marks an operator whose collective is executed inside a neighbouring GEMM (see ``FuseIn`` /
+    ``FuseOut``): it only owns buffers.  ``pair`` links Reduction->Repartition and Combine->Replicate couples
+    that are not fused into a GEMM: together they are one reduce-scatter / all-gather instead of an all-reduce
+    followed by a slice."""
+    absorbed = False
+    pair = None
 
     def is_alias(self) -> bool:
         ex = self.ex
@@ -63,19 +70,27 @@ class RepartitionOp(_ParallelOp):
         if self.is_alias():
             return self.alias_setup()
         self.check_degree()
-        x = self.x()
-        self.dim = int(self.attrs["repartition_dim"]) % x.dim()
-        self.piece = x.shape[self.dim] // self.ex.dist.world_size
-        self.alloc_out()
+        y = self.alloc_out()
+        self.dim = int(self.attrs["repartition_dim"]) % y.dim()
+        self.piece = y.shape[self.dim]
 
     def forward(self):
-        if self.is_alias():
+        if self.is_alias() or self.absorbed:
+            return
+        if self.pair is not None:  # Reduction -> Repartition(0): one reduce-scatter of the partial sums
+            dist.reduce_scatter_tensor(self.out().data.view(-1), self.pair.x().view(-1), group=self.ex.dist.group)
             return
         r = self.ex.dist.rank
         self.out().data.copy_(self.x().narrow(self.dim, r * self.piece, self.piece))
 
     def backward(self):
-        if self.is_alias():
+        if self.is_alias() or self.absorbed:
+            return
+        if self.pair is not None:
+            b = self.pair.buf("INPUT")
+            if b.requires_grad:
+                g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), 0, self.ex.dist.world_size, self.ex.dist.group)
+                self.ex.write_grad(b, g, self.pair.acc["INPUT"])
             return
         b = self.buf("INPUT")
         if b.requires_grad:
@@ -90,16 +105,19 @@ class CombineOp(_ParallelOp):
             return self.alias_setup()
         self.check_degree()
         self.dim = int(self.attrs["combine_dim"]) % self.x().dim()
+        if self.absorbed:
+            self.out().data = self.fuse.bind_gathered(self)  # the staging buffer of the fused all-gather
+            return
         self.alloc_out()
 
     def forward(self):
-        if self.is_alias():
+        if self.is_alias() or self.absorbed:
             return
         comm.nccl_all_gather_dim(self.x(), self.dim, self.ex.dist.world_size, self.ex.dist.group, out=self.out().data)
 
     def backward(self):
-        if self.is_alias():
-            return
+        if self.is_alias() or self.absorbed or self.pair is not None:
+            return  # (paired: the Replicate reduce-scattered straight into this operator's input gradient)
         b = self.buf("INPUT")
         if b.requires_grad:
             piece = self.x().shape[self.dim]
@@ -119,7 +137,18 @@ class ReplicateOp(_ParallelOp):
         pass
 
     def backward(self):
-        if self.is_alias():
+        if self.is_alias() or self.absorbed:
+            return
+        if self.pair is not None:  # Combine(0) -> Replicate: sum over ranks and keep the own rows = reduce-scatter
+            cb = self.pair.buf("INPUT")
+            if cb.requires_grad:
+                full = self.out().grad.view(-1)
+                if self.pair.acc["INPUT"]:
+                    t = torch.empty(full.numel() // self.ex.dist.world_size, dtype=full.dtype, device=full.device)
+                    dist.reduce_scatter_tensor(t, full, group=self.ex.dist.group)
+                    self.ex.write_grad(cb, t, True)
+                else:
+                    dist.reduce_scatter_tensor(cb.grad.view(-1), full, group=self.ex.dist.group)
             return
         b = self.buf("INPUT")
         if b.requires_grad:
@@ -134,6 +163,9 @@ class ReductionOp(_ParallelOp):
         if self.is_alias():
             return self.alias_setup()
         self.check_degree()
+        if self.absorbed or self.pair is not None:
+            self.out().data = None  # nobody reads the unreduced full tensor: the Repartition holds the result
+            return
         # the partial sum is reduced in place and every rank keeps the full result
         self.out().data = self.x()
         self.ex.alias(self.nid, self.inputs["INPUT"])
@@ -141,18 +173,167 @@ class ReductionOp(_ParallelOp):
     def forward(self):
         if self.ex.dist is None or self.ex.dist.world_size == 1 or self.nid in getattr(self.ex, "weight_chain_nodes", ()):
             return
+        if self.absorbed or self.pair is not None:
+            return
         dist.all_reduce(self.x(), group=self.ex.dist.group)
 
 
+class FuseIn:
+    """Combine(dim 0) -> Replicate -> GEMM: the operand arrives as row shards.
+
+    Forward runs the all-gather inside the GEMM (peers push their shard into this rank's staging buffer; the TMA
+    producer waits per row block).  The staging buffer *is* the Combine's output, so the weight-gradient GEMM of
+    backward reads the gathered operand from it.  Backward of the pair is a reduce-scatter of the data
+    gradient's partial sums, run inside the data-gradient GEMM whose epilogue scatters tiles to their owners."""
+
+    def __init__(self, ex: "DistExecutable", combine: CombineOp, replicate: ReplicateOp):
+        self.ex, self.combine, self.replicate = ex, combine, replicate
+        self.ag: Optional[AllGatherGemm] = None
+
+    def bind_gathered(self, combine: CombineOp) -> torch.Tensor:
+        x = combine.x()
+        self.rows_local, self.k = x.numel() // x.shape[-1], x.shape[-1]
+        self.ag = AllGatherGemm(self.ex.ctx, self.rows_local, self.k, x.dtype)
+        self.rs = self.ex.shared_reduce_scatter(self.rows_local * self.ex.ctx.world_size, self.k, x.dtype)
+        full = [int(v) for v in dict(combine.outputs)["OUTPUT"].piece_sizes]
+        return self.ag.gathered_t.view(full)
+
+    def gemm(self, w, out, bias=None, act=None, pre_act_out=None):
+        self.ag(self.combine.x().view(self.rows_local, self.k), w, out, bias=bias, act=act, pre_act_out=pre_act_out)
+
+    def grad_gemm(self, dy, w, accumulate: bool):
+        """d(shard) (+)= reduce_scatter(dy @ w) with w [N_local, K] used as the [k, n] operand."""
+        b = self.combine.buf("INPUT")
+        if not b.requires_grad:
+            return
+        g = b.grad.view(self.rows_local, self.k)
+        self.rs(dy, w, g, residual=g if accumulate else None, w_kn=True)
+
+
+class FuseOut:
+    """GEMM -> Reduction -> Repartition(dim 0): the partial sums are wanted as row shards.
+
+    Forward: the GEMM epilogue writes each output tile into the owning rank's stage and a flag-gated kernel sums
+    the staged partials into the Repartition's output.  Backward: the shard gradients are all-gathered inside the
+    data-gradient GEMM; the gathered dY stays in the staging buffer for the weight and bias gradients."""
+
+    def __init__(self, ex: "DistExecutable", reduction: ReductionOp, repartition: RepartitionOp, rows: int, n: int, dtype):
+        self.ex, self.reduction, self.repartition = ex, reduction, repartition
+        W = ex.ctx.world_size
+        self.rows, self.n = rows, n
+        self.rs = ex.shared_reduce_scatter(rows, n, dtype)
+        self.ag = ex.shared_grad_gather(rows // W, n, dtype)
+
+    def gemm(self, x, w, bias=None):
+        out = self.repartition.out().data
+        self.rs(x, w, out.view(self.rows // self.ex.ctx.world_size, self.n), bias=bias)
+
+    def gather_grad_gemm(self, w, dx, accumulate=False):
+        dy_shard = self.repartition.out().grad.view(self.rows // self.ex.ctx.world_size, self.n)
+        if dx is None:
+            dx = self.ex.discard_buffer(self.rows, w.shape[1], dy_shard.dtype)
+        self.ag(dy_shard, w, dx, w_kn=True, accumulate=accumulate)
+        return self.ag.gathered_t
+
+
 class DistExecutable(Executable):
-    def __init__(self, pcg, cfg: Optional[ExecConfig], ctx: DistContext, bucket_mb: int = 128, overlap: bool = True):
+    def __init__(self, pcg, cfg: Optional[ExecConfig], ctx: DistContext, bucket_mb: int = 128, overlap: bool = True,
+                 fuse_collectives: bool = True):
         self.ctx = ctx
+        self.fuse_collectives = fuse_collectives
+        self._rs_shared: Dict[tuple, GemmReduceScatter] = {}
+        self._ag_shared: Dict[tuple, AllGatherGemm] = {}
+        self._discard: Dict[tuple, torch.Tensor] = {}
+        self.fused_in: List[int] = []
+        self.fused_out: List[int] = []
         self.bucket_bytes = bucket_mb << 20
         self.overlap = overlap
         self._pre_analyse(pcg, ctx)
         super().__init__(pcg, cfg, dist=ctx)
         self._plan_buckets()
         self.parallelism = self._describe()
+
+    # ------------------------------------------------------------------ fused collectives
+    def shared_reduce_scatter(self, rows, n, dtype) -> GemmReduceScatter:
+        """Stages are scratch within one call (a barrier opens every call), so operators of one shape share them."""
+        key = (rows, n, dtype)
+        if key not in self._rs_shared:
+            self._rs_shared[key] = GemmReduceScatter(self.ctx, rows, n, dtype)
+        return self._rs_shared[key]
+
+    def shared_grad_gather(self, rows_local, k, dtype) -> AllGatherGemm:
+        key = (rows_local, k, dtype)
+        if key not in self._ag_shared:
+            self._ag_shared[key] = AllGatherGemm(self.ctx, rows_local, k, dtype)
+        return self._ag_shared[key]
+
+    def discard_buffer(self, rows, cols, dtype):
+        key = (rows, cols, dtype)
+        if key not in self._discard:
+            self._discard[key] = torch.empty(rows, cols, dtype=dtype, device=self.device)
+        return self._discard[key]
+
+    def _fuse(self):
+        super()._fuse()
+        W = self.ctx.world_size
+        if W == 1:
+            return
+        g = self.graph
+        bf16 = self.cfg.compute_dtype == "bf16"
+
+        def sole_consumer(v, kind):
+            cons = g.consumers(v)
+            if len({c[0] for c in cons}) != 1:
+                return None
+            op = self.ops[cons[0][0]]
+            return op if op.type == kind and op.nid not in self.weight_chain_nodes else None
+
+        for nid in self.order:
+            op = self.ops[nid]
+            # ---- Reduction -> Repartition(0)
+            if isinstance(op, ReductionOp) and nid not in self.weight_chain_nodes and _degree(op.attrs) == W:
+                rep = sole_consumer((nid, "OUTPUT"), "REPARTITION")
+                if rep is None or int(rep.attrs["repartition_dim"]) != 0 or _degree(rep.attrs) != W:
+                    continue
+                prod = self.ops[op.inputs["INPUT"][0]]
+                sizes = [int(v) for v in g.shape(op.inputs["INPUT"]).piece_sizes]
+                rows, n = 1, sizes[-1]
+                for v in sizes[:-1]:
+                    rows *= v
+                fusable = (self.fuse_collectives and bf16 and isinstance(prod, (E.LinearOp, E.AttentionOp)) and
+                           (isinstance(prod, E.AttentionOp) or prod.fuse_in is None) and
+                           len(g.consumers(op.inputs["INPUT"])) == 1 and rows % (128 * W) == 0 and n % 8 == 0 and
+                           not prod.attrs.get("activation") and sizes[0] % W == 0)
+                if fusable:
+                    prod.fuse_out = FuseOut(self, op, rep, rows, n, torch.bfloat16)
+                    op.absorbed = rep.absorbed = True
+                    self.fused_out.append(prod.nid)
+                elif sizes[0] % W == 0:
+                    op.pair, rep.pair = rep, op
+            # ---- Combine(0) -> Replicate
+            if isinstance(op, CombineOp) and nid not in self.weight_chain_nodes and _degree(op.attrs) == W \
+                    and int(op.attrs["combine_dim"]) % len(g.shape((nid, "OUTPUT")).sizes) == 0:
+                rpl = sole_consumer((nid, "OUTPUT"), "REPLICATE")
+                if rpl is None or _degree(rpl.attrs) != W:
+                    continue
+                cons = g.consumers((rpl.nid, "OUTPUT"))
+                users = {c[0] for c in cons}
+                sizes = [int(v) for v in g.shape(op.inputs["INPUT"]).piece_sizes]
+                rows_local, k = 1, sizes[-1]
+                for v in sizes[:-1]:
+                    rows_local *= v
+                user = self.ops[next(iter(users))] if len(users) == 1 else None
+                slots_ok = user is not None and (
+                    (isinstance(user, E.LinearOp) and [c[1] for c in cons] == ["INPUT"]) or
+                    (isinstance(user, E.AttentionOp) and sorted(c[1] for c in cons) == ["KEY", "QUERY", "VALUE"]))
+                if self.fuse_collectives and bf16 and slots_ok and rows_local % 128 == 0 and k % 8 == 0:
+                    fi = FuseIn(self, op, rpl)
+                    op.fuse = fi
+                    user.fuse_in = fi
+                    op.absorbed = rpl.absorbed = True
+                    self.fused_in.append(user.nid)
+                else:
+                    op.pair, rpl.pair = rpl, op
 
     # ------------------------------------------------------------------ static analysis of the strategy
     def _pre_analyse(self, g, ctx):

@@ -63,12 +63,17 @@ class GemmReduceScatter:
         self.bar_base = ctx.alloc_flags(w)
         self.sync_sig, self.sync_red, self.sync_bar = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
 
-    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None, bias=None):
+    def __call__(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None, bias=None,
+                 w_kn: bool = False):
+        """`w` is [N, K] (K-major, a Linear weight) or, with ``w_kn``, [K, N] (the same weight used transposed, as
+        in a data-gradient GEMM).  `bias` (length N) is added by the GEMM epilogue of the calling rank only --
+        pass it on one rank.  `residual` [rows/world, N] is added to the reduced shard."""
         ctx = self.ctx
         rows, k = x.shape
         # peers may still be reducing the previous call's partials out of their stages
         comm.barrier(ctx, self.bar_base, self.sync_bar)
-        K.gemm_raw(M=rows, N=self.n, K=k, A=x.data_ptr(), lda=k, B=w.data_ptr(), ldb=k, C=self.stage.local_ptr, ldc=self.n,
+        K.gemm_raw(M=rows, N=self.n, K=k, A=x.data_ptr(), lda=k, B=w.data_ptr(), ldb=self.n if w_kn else k, b_mn=w_kn,
+                   C=self.stage.local_ptr, ldc=self.n, bias=None if bias is None else bias.data_ptr(),
                    scatter=self.stage.peer_ptrs, scatter_rows=self.rows_per, scatter_src=ctx.rank)
         comm.signal(ctx, self.stage, self.flag_base, self.sync_sig)
         comm.reduce_partials(ctx, self.stage_t, out, ctx.world_size, self.flag_base, self.sync_red, residual=residual)
@@ -92,10 +97,13 @@ class AllGatherGemm:
         self.sync_push, self.sync_gate, self.sync_bar = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
         self.side = torch.cuda.Stream() if overlap else None
 
-    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, act=None, pre_act_out=None):
+    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, act=None, pre_act_out=None,
+                 w_kn: bool = False, accumulate: bool = False):
+        """`w` is [N, K] or, with ``w_kn``, [K, N].  After the call ``gathered_t`` holds the gathered operand
+        (all ranks' row shards in rank order), which backward passes reuse."""
         ctx = self.ctx
         W = ctx.world_size
-        n = w.shape[0]
+        n = w.shape[1] if w_kn else w.shape[0]
         # nobody may overwrite a staging buffer that a peer's previous GEMM might still be reading
         comm.barrier(ctx, self.bar_base, self.sync_bar)
         main = torch.cuda.current_stream()
@@ -105,8 +113,9 @@ class AllGatherGemm:
                 comm.push_rows(ctx, x_local, self.gathered, ctx.rank * self.shard_bytes, self.flag_base, self.sync_push, blocks=24)
         else:
             comm.push_rows(ctx, x_local, self.gathered, ctx.rank * self.shard_bytes, self.flag_base, self.sync_push)
-        K.gemm_raw(M=W * self.rows_local, N=n, K=self.k, A=self.gathered.local_ptr, lda=self.k, B=w.data_ptr(), ldb=self.k,
-                   C=out.data_ptr(), ldc=n, bias=None if bias is None else bias.data_ptr(),
+        K.gemm_raw(M=W * self.rows_local, N=n, K=self.k, A=self.gathered.local_ptr, lda=self.k, B=w.data_ptr(),
+                   ldb=n if w_kn else self.k, b_mn=w_kn, C=out.data_ptr(), ldc=n, accumulate=accumulate,
+                   out_fp32=out.dtype == torch.float32, bias=None if bias is None else bias.data_ptr(),
                    act=K.ACT_CODES[act] if not isinstance(act, int) else act,
                    C2=None if pre_act_out is None else pre_act_out.data_ptr(),
                    gate_flags=ctx.flags.local_ptr + self.flag_base * 8, gate_sync=self.sync_gate.data_ptr(),

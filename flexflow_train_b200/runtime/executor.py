@@ -134,6 +134,17 @@ class OpImpl:
         """input slots that receive a gradient from this op"""
         return [s for s, v in self.inputs.items() if self.ex.values[v].requires_grad]
 
+    def extra_grad_targets(self):
+        """(pseudo slot, value) pairs whose gradient this operator's backward writes although the value is not
+        one of its inputs; the accumulate flag arrives in ``self.acc[pseudo slot]``."""
+        fi = getattr(self, "fuse_in", None)
+        return [("FUSE_IN", fi.combine.inputs["INPUT"])] if fi is not None else []
+
+    def extra_grad_sources(self):
+        """Values whose gradient this operator's backward reads although they are not its outputs."""
+        fo = getattr(self, "fuse_out", None)
+        return [(fo.repartition.nid, "OUTPUT")] if fo is not None else []
+
 
 _REGISTRY: Dict[str, type] = {}
 
@@ -197,23 +208,43 @@ _ACT = {None: None, "RELU": "relu", "GELU": "gelu", "SIGMOID": "sigmoid", "TANH"
 
 @register("LINEAR")
 class LinearOp(OpImpl):
+    """y = act(x W^T + b).  Under tensor parallelism the distributed executable may attach ``fuse_in`` (the
+    input arrives as row shards: all-gather fused into this GEMM) or ``fuse_out`` (the output is a partial sum
+    that is wanted as row shards: reduce-scatter fused into this GEMM); see parallel/dist_executor.py."""
+    fuse_in = None
+    fuse_out = None
+
     def setup(self):
         self.act = _ACT[self.attrs.get("activation")]
-        y = self.alloc_out()
-        self.y2d = y.view(-1, y.shape[-1])
+        if self.fuse_out is None:
+            y = self.alloc_out()
+            self.y2d = y.view(-1, y.shape[-1])
+        else:
+            self.y2d = None  # the reduced shards land in the Repartition's output
         x = self.x()
         self.x2d = x.view(-1, x.shape[-1])
         self.w = self.x("WEIGHT")
         self.bias = self.x("BIAS") if ("BIAS" in self.inputs and self.ex.use_bias(self, "BIAS")) else None
-        self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
-        rows, cols = self.y2d.shape
+        rows, cols = self.x2d.shape[0], self.w.shape[0]
+        self.pre = torch.empty(rows, cols, dtype=x.dtype, device=x.device) if (self.act == "gelu" and self.ex.cfg.training) else None
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(rows, cols) if K.available() and self.ex.on_gpu else 0)
 
     def forward(self):
-        K.matmul_nt(self.x2d, self.w, out=self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
+        if self.fuse_in is not None:
+            self.fuse_in.gemm(self.w, self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
+        elif self.fuse_out is not None:
+            self.fuse_out.gemm(self.x2d, self.w, bias=self.bias)
+        else:
+            K.matmul_nt(self.x2d, self.w, out=self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
 
     def backward(self):
-        dy = self.out().grad.view_as(self.y2d)
+        xb = self.buf("INPUT")
+        if self.fuse_out is not None:
+            # gathers the row shards of dY from all ranks and, in the same kernel, computes dX = dY W
+            dy = self.fuse_out.gather_grad_gemm(self.w, xb.grad.view_as(self.x2d) if xb.requires_grad else None,
+                                                accumulate=self.acc.get("INPUT", False))
+        else:
+            dy = self.out().grad.view_as(self.y2d)
         if self.act is not None or self.bias is not None:
             saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
             bb = self.buf("BIAS") if self.bias is not None else None
@@ -222,8 +253,12 @@ class LinearOp(OpImpl):
         wb = self.buf("WEIGHT")
         if wb.requires_grad:
             K.matmul_tn(dy, self.x2d, out=wb.grad, accumulate=self.acc["WEIGHT"])
-        xb = self.buf("INPUT")
-        if xb.requires_grad:
+        if self.fuse_out is not None:
+            return
+        if self.fuse_in is not None:
+            # dX partial sums -> reduce-scatter into the row shard's gradient
+            self.fuse_in.grad_gemm(dy, self.w, self.acc.get("FUSE_IN", False))
+        elif xb.requires_grad:
             K.matmul_nn(dy, self.w, out=xb.grad.view_as(self.x2d), accumulate=self.acc["INPUT"])
 
 
@@ -274,6 +309,8 @@ class AttentionOp(OpImpl):
     and is laid out here as four row-major blocks Wq [H*kdim, q_in], Wk [H*kdim, k_in], Wv [H*vdim, v_in],
     Wo [embed, H*vdim], so that self-attention runs one fused QKV GEMM.  Scores are scaled by 1/sqrt(kdim).
     """
+    fuse_in = None   # see LinearOp: all-gather fused into the QKV projection
+    fuse_out = None  # reduce-scatter fused into the output projection
 
     def setup(self):
         a = self.attrs
@@ -285,6 +322,8 @@ class AttentionOp(OpImpl):
         self.B, self.Sq, self.dq = q.shape
         self.Sk, self.dk, self.dv = k.shape[1], k.shape[2], v.shape[2]
         self.self_attn = self.inputs["QUERY"] == self.inputs["KEY"] == self.inputs["VALUE"]
+        if not self.self_attn:
+            self.fuse_in = None
         H, kd, vd = self.H, self.kd, self.vd
         w = self.x("WEIGHT").view(-1)
         o0 = 0
@@ -324,7 +363,8 @@ class AttentionOp(OpImpl):
         self.ctx = torch.empty(self.B * self.Sq, H * vd, dtype=dt, device=dev)
         if not self.core16:
             self.c_ctx = self.ctx
-        self.alloc_out()
+        if self.fuse_out is None:
+            self.alloc_out()
         self.bias_in = self.x("INPUT_BIAS") if "INPUT_BIAS" in self.inputs else None
         self.bias_out = self.x("OUTPUT_BIAS") if ("OUTPUT_BIAS" in self.inputs and ex.use_bias(self, "OUTPUT_BIAS")) else None
         self.alpha = 1.0 / math.sqrt(kd)
@@ -359,7 +399,9 @@ class AttentionOp(OpImpl):
     def forward(self):
         H, kd, vd, Sq, Sk = self.H, self.kd, self.vd, self.Sq, self.Sk
         q2 = self.x("QUERY").view(-1, self.dq)
-        if self.self_attn:
+        if self.fuse_in is not None:
+            self.fuse_in.gemm(self.wqkv, self.qkv, bias=self.bias_in)
+        elif self.self_attn:
             K.matmul_nt(q2, self.wqkv, out=self.qkv, bias=self.bias_in)
         else:
             K.matmul_nt(q2, self.wq, out=self.qv)
@@ -388,13 +430,18 @@ class AttentionOp(OpImpl):
                  self.c_ctx, H * vd, vd, Sq * H * vd)
         if self.core16:
             K.cast(self.c_ctx, self.ctx)
-        y = self.out().data
-        K.matmul_nt(self.ctx, self.wo, out=y.view(-1, self.embed), bias=self.bias_out)
+        if self.fuse_out is not None:
+            self.fuse_out.gemm(self.ctx, self.wo, bias=self.bias_out)
+        else:
+            K.matmul_nt(self.ctx, self.wo, out=self.out().data.view(-1, self.embed), bias=self.bias_out)
 
     def backward(self):
         H, kd, vd, Sq, Sk = self.H, self.kd, self.vd, self.Sq, self.Sk
         ex = self.ex
-        dy = self.out().grad.view(-1, self.embed)
+        if self.fuse_out is not None:
+            dy = self.fuse_out.gather_grad_gemm(self.wo, self.dctx)
+        else:
+            dy = self.out().grad.view(-1, self.embed)
         wbuf = self.buf("WEIGHT")
         wg = wbuf.grad.view(-1)
         accw = self.acc["WEIGHT"]
@@ -404,7 +451,8 @@ class AttentionOp(OpImpl):
             K.bias_act_bwd(dy, None, None, self.buf("OUTPUT_BIAS").grad, ex.scratch_f32(), None,
                            accumulate=self.acc.get("OUTPUT_BIAS", False))
         K.matmul_tn(dy, self.ctx, out=g_wo, accumulate=accw)
-        K.matmul_nn(dy, self.wo, out=self.dctx)
+        if self.fuse_out is None:
+            K.matmul_nn(dy, self.wo, out=self.dctx)
         p = self.probs
         if self.p_drop > 0:  # regenerate the dropped probabilities (mask is a function of the step seed)
             p = ex.big_scratch(1, self.probs)
@@ -441,7 +489,9 @@ class AttentionOp(OpImpl):
                 K.bias_act_bwd(self.dqkv, None, None, self.buf("INPUT_BIAS").grad, ex.scratch_f32(), None,
                                accumulate=self.acc.get("INPUT_BIAS", False))
             K.matmul_tn(self.dqkv, q2, out=wg[:n_q + n_k + n_v].view(self.ldqkv, self.dq), accumulate=accw)
-            if qb.requires_grad:
+            if self.fuse_in is not None:
+                self.fuse_in.grad_gemm(self.dqkv, self.wqkv, self.acc.get("FUSE_IN", False))
+            elif qb.requires_grad:
                 K.matmul_nn(self.dqkv, self.wqkv, out=qb.grad.view(-1, self.dq), accumulate=self.acc["QUERY"])
         else:
             k2, v2 = self.x("KEY").view(-1, self.dk), self.x("VALUE").view(-1, self.dv)
@@ -1005,6 +1055,12 @@ class Executable:
             seeds.append(tgt)
         live: Dict[Value, torch.Tensor] = {}
         canon = self.canon
+        hold_until: Dict[Value, int] = {}
+        held_by: Dict[int, List[Value]] = {}
+        for nid, op in self.ops.items():
+            for v in op.extra_grad_sources():
+                hold_until[canon(v)] = nid
+                held_by.setdefault(nid, []).append(canon(v))
 
         def ensure(v: Value):
             """Give v a gradient buffer; aliases share the buffer of the value they alias."""
@@ -1041,7 +1097,8 @@ class Executable:
                 for o in outs:
                     if self.values[o].requires_grad:
                         ensure(o)
-                targets = list(op.inputs.items())
+                # an operator with a fused collective writes the gradient of a value it does not consume itself
+                targets = list(op.inputs.items()) + list(op.extra_grad_targets())
                 if isinstance(op, LayerNormOp) and op.fused_add is not None:
                     # the LayerNorm writes straight into the add's operands
                     add = op.fused_add
@@ -1062,8 +1119,12 @@ class Executable:
                     seen_here.add(canon(v))
                 for c in seen_here:
                     written[c] = True
-            # outputs of this node are dead once its backward ran (aliases are released with their source)
+            # outputs of this node are dead once its backward ran (aliases are released with their source), unless
+            # an earlier operator reads them in its own backward (fused collectives): then they live until that one
             for o in outs:
+                if o in live and o not in hold_until:
+                    pool.give(live.pop(o))
+            for o in held_by.get(nid, ()):
                 if o in live:
                     pool.give(live.pop(o))
         self.grad_pool_bytes = pool.total_bytes

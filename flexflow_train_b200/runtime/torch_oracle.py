@@ -195,6 +195,10 @@ class TorchOracle:
         Q = F.linear(q, wq, bq).view(B, Sq, H, kd).transpose(1, 2)
         Kt = F.linear(k, wk, bk).view(B, Sk, H, kd).transpose(1, 2)
         Vt = F.linear(v, wv, bv).view(B, Sk, H, vd).transpose(1, 2)
+        if getattr(self, "use_sdpa", False):  # library attention kernel (used by the PyTorch baseline arm of the bench)
+            pdrop = float(a.get("dropout", 0)) if (self.use_dropout and self.training) else 0.0
+            ctx = F.scaled_dot_product_attention(Q, Kt, Vt, dropout_p=pdrop, is_causal=self.causal)
+            return F.linear(ctx.transpose(1, 2).reshape(B, Sq, H * vd), wo, ins.get("OUTPUT_BIAS"))
         s = (Q @ Kt.transpose(-1, -2)) / math.sqrt(kd)
         if self.causal:
             mask = torch.tril(torch.ones(Sq, Sk, dtype=torch.bool, device=s.device))

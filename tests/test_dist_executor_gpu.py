@@ -18,10 +18,14 @@ def _train(ctx, which):
 
     cg = core.build_model("transformer_lm", CFG)
     W = ctx.world_size
-    pcg = S.data_parallel_strategy(cg, W) if which == "dp" else S.tensor_parallel_strategy(cg, W)
+    if which == "dp":
+        pcg = S.data_parallel_strategy(cg, W)
+    else:
+        pcg = S.tensor_parallel_strategy(cg, W, sequence_parallel=which != "tp_replicated")
     opt = OptimizerConfig(kind="adam", lr=1e-3)
     single = Executable(cg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"))
-    multi = DistExecutable(pcg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"), ctx)
+    multi = DistExecutable(pcg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"), ctx,
+                           fuse_collectives=which != "tp_nccl")
     torch.manual_seed(0)
     ids = torch.randint(0, 512, (8, 128, 1), dtype=torch.int32, device=ctx.device)
     labels = torch.randint(0, 512, (8, 128), dtype=torch.int32, device=ctx.device)
@@ -32,7 +36,8 @@ def _train(ctx, which):
         multi.train_step({"input_ids": ids}, labels)
         b.append(multi.mean_loss())
     ctx.check_status()
-    return {"single": a, "multi": b, "parallelism": multi.parallelism}
+    return {"single": a, "multi": b, "parallelism": multi.parallelism, "fused_in": len(multi.fused_in),
+            "fused_out": len(multi.fused_out)}
 
 
 def w_dp(ctx):
@@ -43,11 +48,26 @@ def w_tp(ctx):
     return _train(ctx, "tp")
 
 
-@pytest.mark.parametrize("which", ["dp", "tp"])
+def w_tp_nccl(ctx):
+    return _train(ctx, "tp_nccl")
+
+
+def w_tp_replicated(ctx):
+    return _train(ctx, "tp_replicated")
+
+
+@pytest.mark.parametrize("which", ["dp", "tp", "tp_nccl", "tp_replicated"])
 def test_two_rank_training_matches_single_gpu(which):
+    """dp: data parallel with the fused gradient all-reduce.  tp: tensor + sequence parallel with the collectives
+    fused into the GEMMs (all-gather -> GEMM, GEMM -> reduce-scatter).  tp_nccl: the same strategy on NCCL
+    reduce-scatter / all-gather.  tp_replicated: the plain Megatron template with replicated activations."""
     res = _run("test_dist_executor_gpu:w_" + which)
     for r, out in res.items():
-        assert which in out["parallelism"], out
+        assert which[:2] in out["parallelism"], out
+        if which == "tp":  # per layer: attention and the MLP each have one fused input and one fused output
+            assert out["fused_in"] == 4 and out["fused_out"] == 4, out
+        else:
+            assert out["fused_in"] == 0 and out["fused_out"] == 0, out
         for x, y in zip(out["single"], out["multi"]):
             assert abs(x - y) < 3e-2 * abs(x), out
         assert out["multi"][-1] < out["multi"][0]
