@@ -186,6 +186,8 @@ def main():
     ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--strategy", default="search", help="search | dp | tp | <path to strategy json>")
+    ap.add_argument("--no-fused-collectives", action="store_true",
+                    help="tensor-parallel collectives through NCCL instead of inside the GEMM kernels (baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -218,6 +220,7 @@ def main():
     global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
     opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
+                         fuse_collectives=not args.no_fused_collectives,
                          search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel"}.get(args.strategy, "unity"),
                          import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
     model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind=opt_kind, lr=lr, momentum=momentum),
@@ -302,7 +305,8 @@ def main():
                        "parallelism": getattr(ex, "parallelism", "single"), "layers": mcfg.get("num_decoder_layers", 12),
                        "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768)), "optimizer": opt_kind, "lr": lr,
                        "l2": "activations and weights per step (>100 GB) exceed the 126 MB L2; no flush needed",
-                       "cuda_graph": bool(ex.cfg.use_cuda_graph), "tokens_per_s": value * seq},
+                       "cuda_graph": bool(ex.cfg.use_cuda_graph), "tokens_per_s": value * seq,
+                       "fused_collective_gemms": len(getattr(ex, "fused_in", [])) + len(getattr(ex, "fused_out", []))},
             "clocks": clocks,
             "e2e": {"value": global_batch / (e2e_ms / 1e3), "unit": "samples/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},

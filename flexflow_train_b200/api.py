@@ -40,6 +40,7 @@ class FFConfig:
     export_strategy_computation_graph_file: Optional[str] = None
     compute_dtype: str = "bf16"
     use_cuda_graph: bool = True
+    fuse_collectives: bool = True  # run all-gather / reduce-scatter inside the neighbouring GEMMs (else NCCL)
     seed: int = 0
 
 
@@ -126,7 +127,7 @@ def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None
         from .compiler.strategy import choose_strategy
         strategy, stats = choose_strategy(cg, world, config)
         from .parallel.dist_executor import DistExecutable
-        ex = DistExecutable(strategy, exec_cfg, dist)
+        ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives)
     else:
         if config.import_strategy_file:
             with open(config.import_strategy_file) as f:

@@ -293,14 +293,30 @@ __global__ void bn_partial_kernel(const T *__restrict__ a, const T *__restrict__
     part[((long long)blockIdx.y * 2 + 1) * C + c] = v;
   }
 }
+// Fold the per-chunk partial sums: block = 32 columns x 8 chunk lanes, fixed summation order.
+__device__ __forceinline__ void bn_fold(const float *__restrict__ part, int chunks, int C, int c, float &s, float &q) {
+  __shared__ float fs[8][33], fq[8][33];
+  float a = 0.f, b = 0.f;
+  if (c < C)
+    for (int k = threadIdx.y; k < chunks; k += 8) {
+      a += part[((long long)k * 2) * C + c];
+      b += part[((long long)k * 2 + 1) * C + c];
+    }
+  fs[threadIdx.y][threadIdx.x] = a;
+  fq[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  s = q = 0.f;
+  if (threadIdx.y == 0)
+    for (int i = 0; i < 8; ++i) { s += fs[i][threadIdx.x]; q += fq[i][threadIdx.x]; }
+}
 __global__ void bn_finalize_stats_kernel(const float *__restrict__ part, int chunks, int C, long long R, float eps, float *__restrict__ mean,
                                          float *__restrict__ rstd) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s = 0.0, q = 0.0;
-  for (int k = 0; k < chunks; ++k) { s += part[((long long)k * 2) * C + c]; q += part[((long long)k * 2 + 1) * C + c]; }
-  double m = s / (double)R;
-  double var = q / (double)R - m * m;
+  int c = blockIdx.x * 32 + threadIdx.x;
+  float s, q;
+  bn_fold(part, chunks, C, c, s, q);
+  if (threadIdx.y != 0 || c >= C) return;
+  double m = (double)s / (double)R;
+  double var = (double)q / (double)R - m * m;
   if (var < 0.0) var = 0.0;
   mean[c] = (float)m;
   rstd[c] = (float)(1.0 / sqrt(var + (double)eps));
@@ -309,10 +325,10 @@ __global__ void bn_finalize_stats_kernel(const float *__restrict__ part, int chu
 template <typename T>
 __global__ void bn_finalize_grads_kernel(const float *__restrict__ part, int chunks, int C, float *__restrict__ sums, T *__restrict__ dgamma,
                                          T *__restrict__ dbeta, int acc_gamma, int acc_beta) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float s = 0.f, q = 0.f;
-  for (int k = 0; k < chunks; ++k) { s += part[((long long)k * 2) * C + c]; q += part[((long long)k * 2 + 1) * C + c]; }
+  int c = blockIdx.x * 32 + threadIdx.x;
+  float s, q;
+  bn_fold(part, chunks, C, c, s, q);
+  if (threadIdx.y != 0 || c >= C) return;
   sums[c] = s;
   sums[C + c] = q;
   if (dbeta) stf(dbeta + c, s + (acc_beta ? ldf(dbeta + c) : 0.f));
@@ -359,6 +375,240 @@ __global__ void bn_bwd_apply_kernel(const T *__restrict__ dy, const T *__restric
     if (gamma) v *= ldf(gamma + c);
     if (accumulate) v += ldf(dx + t);
     stf(dx + t, v);
+  }
+}
+
+
+// ---- vector forms for bf16 channels-last data with C % 8 == 0: one thread handles 8 channels (16 bytes)
+__device__ __forceinline__ void unpack8(const uint4 &v, float *f) {
+  float2 a = unpack_bf162(v.x), b = unpack_bf162(v.y), c = unpack_bf162(v.z), d = unpack_bf162(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float *f) {
+  uint4 o;
+  o.x = pack_bf162(f[0], f[1]); o.y = pack_bf162(f[2], f[3]); o.z = pack_bf162(f[4], f[5]); o.w = pack_bf162(f[6], f[7]);
+  return o;
+}
+
+__global__ void pool_fwd_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, unsigned char *__restrict__ arg, ConvGeom g, int mode,
+                                    long long total) {
+  const int c8n = g.C >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c8 = (int)(t % c8n);
+    long long r = t / c8n;
+    int ow = (int)(r % g.OW);
+    long long r2 = r / g.OW;
+    int oh = (int)(r2 % g.OH);
+    int n = (int)(r2 / g.OH);
+    const bf16 *base = x + n * g.sn + c8 * 8;
+    float best[8], sum[8];
+    int besti[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { best[i] = -INFINITY; sum[i] = 0.f; besti[i] = 0; }
+    int cnt = 0;
+    const int h0 = max(oh * g.SH - g.PH, 0), h1 = min(oh * g.SH - g.PH + g.KH, g.H);
+    const int w0 = max(ow * g.SW - g.PW, 0), w1 = min(ow * g.SW - g.PW + g.KW, g.W);
+    for (int ih = h0; ih < h1; ++ih) {
+      for (int iw = w0; iw < w1; ++iw) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4 *>(base + ih * g.sh + iw * g.sw), f);
+        const int off = (ih - (oh * g.SH - g.PH)) * g.KW + (iw - (ow * g.SW - g.PW));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (f[i] > best[i]) { best[i] = f[i]; besti[i] = off; }
+          sum[i] += f[i];
+        }
+        ++cnt;
+      }
+    }
+    if (mode == 0) {
+      *reinterpret_cast<uint4 *>(y + t * 8) = pack8(best);
+      if (arg) {
+        uint2 a;
+        a.x = besti[0] | (besti[1] << 8) | (besti[2] << 16) | (besti[3] << 24);
+        a.y = besti[4] | (besti[5] << 8) | (besti[6] << 16) | (besti[7] << 24);
+        *reinterpret_cast<uint2 *>(arg + t * 8) = a;
+      }
+    } else {
+      const float inv = cnt ? 1.f / cnt : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum[i] *= inv;
+      *reinterpret_cast<uint4 *>(y + t * 8) = pack8(sum);
+    }
+  }
+}
+
+__global__ void pool_bwd_vec_kernel(const bf16 *__restrict__ dy, const unsigned char *__restrict__ arg, bf16 *__restrict__ dx, ConvGeom g,
+                                    int mode, long long total, int accumulate) {
+  const int c8n = g.C >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    int c8 = (int)(t % c8n);
+    long long r = t / c8n;
+    int iw = (int)(r % g.W);
+    long long r2 = r / g.W;
+    int ih = (int)(r2 % g.H);
+    int n = (int)(r2 / g.H);
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      int a = ih + g.PH - kh;
+      if (a < 0) break;
+      int oh = a / g.SH;
+      if (oh * g.SH != a || oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        int b = iw + g.PW - kw;
+        if (b < 0) break;
+        int ow = b / g.SW;
+        if (ow * g.SW != b || ow >= g.OW) continue;
+        long long o = ((((long long)n * g.OH + oh) * g.OW + ow) * c8n + c8) * 8;
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4 *>(dy + o), f);
+        if (mode == 0) {
+          uint2 am = *reinterpret_cast<const uint2 *>(arg + o);
+          const unsigned int me = (unsigned int)(kh * g.KW + kw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (((am.x >> (8 * i)) & 0xFFu) == me) acc[i] += f[i];
+            if (((am.y >> (8 * i)) & 0xFFu) == me) acc[4 + i] += f[4 + i];
+          }
+        } else {
+          int h0 = max(oh * g.SH - g.PH, 0), h1 = min(oh * g.SH - g.PH + g.KH, g.H);
+          int w0 = max(ow * g.SW - g.PW, 0), w1 = min(ow * g.SW - g.PW + g.KW, g.W);
+          const float inv = 1.f / (float)((h1 - h0) * (w1 - w0));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i] * inv;
+        }
+      }
+    }
+    bf16 *p = dx + n * g.sn + ih * g.sh + iw * g.sw + c8 * 8;
+    if (accumulate) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4 *>(p), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    *reinterpret_cast<uint4 *>(p) = pack8(acc);
+  }
+}
+
+// Batch-norm column statistics, vector form.  Thread (g, lane) of a block owns channel group g (8 channels) and
+// walks rows lane, lane + lanes, ... of the block's row chunk; consecutive threads read consecutive 16-byte
+// pieces of memory (the last group of a row is followed by the first group of the next row).  Per-lane sums go
+// through shared memory in a fixed order, so the result does not depend on scheduling.
+constexpr int BNV_THREADS = 256;
+__global__ void bn_partial_vec_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ b, const bf16 *__restrict__ relu_y,
+                                      float *__restrict__ part, const float *__restrict__ mean, const float *__restrict__ rstd, long long R,
+                                      int C, int rows_per_chunk, int mode) {
+  extern __shared__ float sred[];  // [lanes][2][C]
+  const int groups = C >> 3;
+  const int lanes = BNV_THREADS / groups;
+  const int gidx = threadIdx.x % groups, lane = threadIdx.x / groups;
+  long long r0 = (long long)blockIdx.x * rows_per_chunk;
+  long long r1 = r0 + rows_per_chunk < R ? r0 + rows_per_chunk : R;
+  float u[8], v[8], m[8], rs[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { u[i] = 0.f; v[i] = 0.f; m[i] = 0.f; rs[i] = 0.f; }
+  if (lane < lanes) {
+    if (mode) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { m[i] = mean[gidx * 8 + i]; rs[i] = rstd[gidx * 8 + i]; }
+    }
+    long long r = r0 + lane;
+    if (mode == 0) {
+      // four rows per trip: four independent 16-byte loads in flight per thread
+      for (; r + 3LL * lanes < r1; r += 4LL * lanes) {
+        uint4 q0 = *reinterpret_cast<const uint4 *>(a + r * C + gidx * 8);
+        uint4 q1 = *reinterpret_cast<const uint4 *>(a + (r + lanes) * C + gidx * 8);
+        uint4 q2 = *reinterpret_cast<const uint4 *>(a + (r + 2LL * lanes) * C + gidx * 8);
+        uint4 q3 = *reinterpret_cast<const uint4 *>(a + (r + 3LL * lanes) * C + gidx * 8);
+        float f0[8], f1[8], f2[8], f3[8];
+        unpack8(q0, f0); unpack8(q1, f1); unpack8(q2, f2); unpack8(q3, f3);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          u[i] += (f0[i] + f1[i]) + (f2[i] + f3[i]);
+          v[i] += (f0[i] * f0[i] + f1[i] * f1[i]) + (f2[i] * f2[i] + f3[i] * f3[i]);
+        }
+      }
+    }
+    for (; r < r1; r += lanes) {
+      const long long off = r * C + gidx * 8;
+      float av[8];
+      unpack8(*reinterpret_cast<const uint4 *>(a + off), av);
+      if (mode == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { u[i] += av[i]; v[i] += av[i] * av[i]; }
+      } else {
+        float xv[8];
+        unpack8(*reinterpret_cast<const uint4 *>(b + off), xv);
+        if (relu_y) {
+          float yv[8];
+          unpack8(*reinterpret_cast<const uint4 *>(relu_y + off), yv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) if (yv[i] <= 0.f) av[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { u[i] += av[i]; v[i] += av[i] * (xv[i] - m[i]) * rs[i]; }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sred[(lane * 2 + 0) * C + gidx * 8 + i] = u[i];
+      sred[(lane * 2 + 1) * C + gidx * 8 + i] = v[i];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += BNV_THREADS) {
+    float s = 0.f;
+    for (int l = 0; l < lanes; ++l) s += sred[l * 2 * C + c];
+    part[(long long)blockIdx.x * 2 * C + c] = s;
+  }
+}
+__global__ void bn_apply_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, const bf16 *__restrict__ gamma,
+                                    const bf16 *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd,
+                                    long long total8, int C, int relu) {
+  const int groups = C >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total8; t += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(t % groups) * 8;
+    float f[8];
+    unpack8(reinterpret_cast<const uint4 *>(x)[t], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = (f[i] - mean[c + i]) * rstd[c + i];
+      if (gamma) v *= bf2f(gamma[c + i]);
+      if (beta) v += bf2f(beta[c + i]);
+      if (relu) v = fmaxf(v, 0.f);
+      f[i] = v;
+    }
+    reinterpret_cast<uint4 *>(y)[t] = pack8(f);
+  }
+}
+__global__ void bn_bwd_apply_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x, const bf16 *__restrict__ relu_y,
+                                        const bf16 *__restrict__ gamma, const float *__restrict__ mean, const float *__restrict__ rstd,
+                                        const float *__restrict__ sums, bf16 *__restrict__ dx, long long total8, int C, float inv_r,
+                                        int accumulate) {
+  const int groups = C >> 3;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total8; t += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(t % groups) * 8;
+    float g[8], xv[8], o[8];
+    unpack8(reinterpret_cast<const uint4 *>(dy)[t], g);
+    unpack8(reinterpret_cast<const uint4 *>(x)[t], xv);
+    if (relu_y) {
+      float yv[8];
+      unpack8(reinterpret_cast<const uint4 *>(relu_y)[t], yv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) if (yv[i] <= 0.f) g[i] = 0.f;
+    }
+    if (accumulate) unpack8(reinterpret_cast<const uint4 *>(dx)[t], o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float rs = rstd[c + i];
+      const float xh = (xv[i] - mean[c + i]) * rs;
+      float v = (g[i] - sums[c + i] * inv_r - xh * sums[C + c + i] * inv_r) * rs;
+      if (gamma) v *= bf2f(gamma[c + i]);
+      o[i] = accumulate ? o[i] + v : v;
+    }
+    reinterpret_cast<uint4 *>(dx)[t] = pack8(o);
   }
 }
 
@@ -435,6 +685,11 @@ FFK_API int ffk_pool2d_fwd(const void *x, void *y, void *arg, const int *geom, c
   long long total = (long long)g.N * g.OH * g.OW * g.C;
   if (total <= 0) return 0;
   if (g.KH * g.KW > 255) return -2;
+  if (dt == 1 && vec_ok(g, x) && ((uintptr_t)y % 16) == 0 && ((uintptr_t)arg % 8) == 0) {
+    long long tv = total / 8;
+    pool_fwd_vec_kernel<<<ffk_blocks(tv, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (unsigned char *)arg, g, mode, tv);
+    return (int)cudaGetLastError();
+  }
   if (dt == 1) pool_fwd_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (unsigned char *)arg, g, mode, total);
   else if (dt == 0) pool_fwd_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (float *)y, (unsigned char *)arg, g, mode, total);
   else return -2;
@@ -447,6 +702,12 @@ FFK_API int ffk_pool2d_bwd(const void *dy, const void *arg, void *dx, const int 
   long long total = (long long)g.N * g.H * g.W * g.C;
   if (total <= 0) return 0;
   if (mode == 0 && !arg) return -2;
+  if (dt == 1 && vec_ok(g, dx) && ((uintptr_t)dy % 16) == 0 && ((uintptr_t)arg % 8) == 0) {
+    long long tv = total / 8;
+    pool_bwd_vec_kernel<<<ffk_blocks(tv, 256), 256, 0, st>>>((const bf16 *)dy, (const unsigned char *)arg, (bf16 *)dx, g, mode, tv,
+                                                             accumulate);
+    return (int)cudaGetLastError();
+  }
   if (dt == 1) pool_bwd_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dy, (const unsigned char *)arg, (bf16 *)dx, g, mode, total, accumulate);
   else if (dt == 0) pool_bwd_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)dy, (const unsigned char *)arg, (float *)dx, g, mode, total, accumulate);
   else return -2;
@@ -464,11 +725,28 @@ static int bn_chunks(long long R, int C, int *rows_per_chunk) {
   *rows_per_chunk = (int)rpc;
   return (int)chunks;
 }
+static bool bn_vec_ok(int C, const void *a, const void *b, const void *c) {
+  return (C % 8) == 0 && C / 8 <= BNV_THREADS && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && ((uintptr_t)c % 16) == 0;
+}
+static int bn_chunks_vec(long long R, int C, int *rows_per_chunk) {
+  const int lanes = BNV_THREADS / (C / 8);
+  long long maxc = (R + 4LL * lanes - 1) / (4LL * lanes);  // at least ~4 rows per thread
+  long long chunks = maxc < 148 * 4 ? maxc : 148 * 4;
+  if (chunks < 1) chunks = 1;
+  long long rpc = (R + chunks - 1) / chunks;
+  chunks = (R + rpc - 1) / rpc;
+  *rows_per_chunk = (int)rpc;
+  return (int)chunks;
+}
 // number of fp32 scratch elements the batch-norm entry points need
 FFK_API long long ffk_batchnorm_scratch(long long R, int C) {
   int rpc;
-  int chunks = bn_chunks(R, C, &rpc);
-  return (long long)chunks * 2 * C + 2 * (long long)C;
+  long long chunks = bn_chunks(R, C, &rpc);
+  if ((C % 8) == 0 && C / 8 <= BNV_THREADS) {
+    long long cv = bn_chunks_vec(R, C, &rpc);
+    if (cv > chunks) chunks = cv;
+  }
+  return chunks * 2 * C + 2 * (long long)C;
 }
 
 // y = act((x - mean) * rstd * gamma + beta) with batch statistics; mean/rstd [C] fp32 are saved for backward
@@ -479,9 +757,20 @@ FFK_API int ffk_batchnorm_fwd(const void *x, void *y, const void *gamma, const v
   int chunks = bn_chunks(R, C, &rpc);
   dim3 grid((C + BN_TX - 1) / BN_TX, chunks), block(BN_TX, BN_TY);
   long long total = R * C;
+  if (dt == 1 && bn_vec_ok(C, x, y, x)) {
+    int rv;
+    int cv = bn_chunks_vec(R, C, &rv);
+    const int lanes = BNV_THREADS / (C / 8);
+    bn_partial_vec_kernel<<<cv, BNV_THREADS, (size_t)lanes * 2 * C * sizeof(float), st>>>((const bf16 *)x, nullptr, nullptr, scratch, nullptr,
+                                                                                          nullptr, R, C, rv, 0);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, cv, C, R, eps, mean, rstd);
+    bn_apply_vec_kernel<<<ffk_blocks(total / 8, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta, mean,
+                                                                    rstd, total / 8, C, relu);
+    return (int)cudaGetLastError();
+  }
   if (dt == 1) {
     bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
-    bn_finalize_stats_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
     if ((C % 2) == 0 && ((uintptr_t)x % 4) == 0 && ((uintptr_t)y % 4) == 0)
       bn_apply_bf16x2_kernel<<<ffk_blocks(total / 2, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta,
                                                                          mean, rstd, total / 2, C, relu);
@@ -490,7 +779,7 @@ FFK_API int ffk_batchnorm_fwd(const void *x, void *y, const void *gamma, const v
                                                                     rstd, total, C, relu);
   } else if (dt == 0) {
     bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
-    bn_finalize_stats_kernel<<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
     bn_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (float *)y, (const float *)gamma, (const float *)beta,
                                                                    mean, rstd, total, C, relu);
   } else {
@@ -510,9 +799,24 @@ FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y,
   float *sums = scratch + (long long)chunks * 2 * C;
   long long total = R * C;
   float inv_r = 1.0f / (float)R;
+  if (dt == 1 && bn_vec_ok(C, dy, x, relu_y) && (!dx || ((uintptr_t)dx % 16) == 0)) {
+    int rv;
+    int cv = bn_chunks_vec(R, C, &rv);
+    const int lanes = BNV_THREADS / (C / 8);
+    float *sums_v = scratch + (long long)cv * 2 * C;
+    bn_partial_vec_kernel<<<cv, BNV_THREADS, (size_t)lanes * 2 * C * sizeof(float), st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
+                                                                                          scratch, mean, rstd, R, C, rv, 1);
+    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, cv, C, sums_v, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
+                                                                     accumulate_beta);
+    if (dx)
+      bn_bwd_apply_vec_kernel<<<ffk_blocks(total / 8, 256), 256, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
+                                                                          (const bf16 *)gamma, mean, rstd, sums_v, (bf16 *)dx, total / 8, C,
+                                                                          inv_r, accumulate_dx);
+    return (int)cudaGetLastError();
+  }
   if (dt == 1) {
     bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
-    bn_finalize_grads_kernel<bf16><<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, sums, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
+    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, sums, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
                                                                      accumulate_beta);
     if (dx)
       bn_bwd_apply_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
@@ -520,7 +824,7 @@ FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y,
                                                                         accumulate_dx);
   } else if (dt == 0) {
     bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
-    bn_finalize_grads_kernel<float><<<(C + 127) / 128, 128, 0, st>>>(scratch, chunks, C, sums, (float *)dgamma, (float *)dbeta,
+    bn_finalize_grads_kernel<float><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, sums, (float *)dgamma, (float *)dbeta,
                                                                       accumulate_gamma, accumulate_beta);
     if (dx)
       bn_bwd_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y,

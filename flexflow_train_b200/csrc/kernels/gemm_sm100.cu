@@ -47,6 +47,11 @@ struct GemmArgs {
   int aux_fp32;    // bias / addend / C2 are float (fp32 activations) instead of bf16
   int tiles_m, tiles_n;
   long long num_tiles;
+  // Split-K: a problem with few output tiles and a very long K (the weight gradient of a convolution:
+  // [OC, KH*KW*C] accumulated over N*OH*OW rows) is cut into split_k ranges of kb_per_split k-blocks; the work
+  // items are (tile, split) pairs and every split adds its partial into the fp32 output with atomics.
+  int split_k;
+  int kb_per_split;
   int *err;
   // --- fused collectives (all optional) ---
   // Scatter epilogue (GEMM -> reduce-scatter): when scatter_rows > 0 the output rows are split into blocks of
@@ -252,6 +257,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+  const long long num_items = p.num_tiles * p.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -283,7 +289,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       uint32_t gate_seen = 0;
-      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const long long tile = item % p.num_tiles;
+        const int kb0 = (int)(item / p.num_tiles) * p.kb_per_split;
+        const int kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
         int mb, nb_, bh, bb;
         tile_coords(tile, p, mb, nb_, bh, bb);
         if (p.gate_flags) {
@@ -311,7 +320,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
             asm volatile("fence.proxy.async.global;" ::: "memory");
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
           if (!ok) break;
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
@@ -351,12 +360,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int kb0 = (int)(item / p.num_tiles) * p.kb_per_split;
+        const int kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
         ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
         uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after();
@@ -367,7 +378,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
             tc_mma<ES == 4>(d_tmem, adesc + (uint64_t)((k * Cfg::A_KADV) >> 4), bdesc + (uint64_t)((k * Cfg::B_KADV) >> 4),
-                            Cfg::IDESC, (kb | k) != 0 ? 1u : 0u);
+                            Cfg::IDESC, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -394,14 +405,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     const uint32_t wr_base = smem_u32(stg + lane * 32);
     const uint32_t rd_even = smem_u32(stg + rsub * 32 + ((unit ^ rsub) << 2));            // rows with (rr & 7) == rsub
     const uint32_t rd_odd = smem_u32(stg + (rsub + 4) * 32 + ((unit ^ (rsub + 4)) << 2));  // rows with (rr & 7) == rsub + 4
-    const bool simple = !p.out_fp32 && !p.accumulate && !p.C2 && !p.addend && !p.aux_fp32 &&
+    const bool simple = p.split_k == 1 && !p.out_fp32 && !p.accumulate && !p.C2 && !p.addend && !p.aux_fp32 &&
                         (p.act == ACT_NONE || p.act == ACT_RELU) && (p.ldc % 4 == 0) && (((uintptr_t)p.C) & 7) == 0 &&
                         (p.c_sh % 4 == 0) && (p.c_sb % 4 == 0);
     const float relu_floor = p.act == ACT_RELU ? 0.f : -INFINITY;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+    for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const long long tile = item % p.num_tiles;
+      const bool first_split = item < p.num_tiles;  // the bias is added once
       int mb, nb_, bh, bb;
       tile_coords(tile, p, mb, nb_, bh, bb);
       ok = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
@@ -435,7 +448,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
         const bool col_ok = col < p.N;
         const bool vec4 = col + 4 <= p.N;
         float b4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (p.bias && col_ok) {
+        if (p.bias && col_ok && first_split) {
           if (vec4 && !p.aux_fp32 && ((((uintptr_t)p.bias) & 7) == 0)) {
             uint2 u = *reinterpret_cast<const uint2 *>((const bf16 *)p.bias + col);
             float2 x0 = unpack_bf162(u.x), x1 = unpack_bf162(u.y);
@@ -492,7 +505,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
             }
             if (p.out_fp32) {
               float *c = (float *)Cout + coff;
-              if (vec4 && (((uintptr_t)c) & 15) == 0) {
+              if (p.split_k > 1) {  // partial sum of one K range: the output was cleared (or holds the accumuland)
+                for (int j = 0; j < 4; ++j) if (col + j < p.N) atomicAdd(c + j, v[j]);
+              } else if (vec4 && (((uintptr_t)c) & 15) == 0) {
                 float4 o = make_float4(v[0], v[1], v[2], v[3]);
                 if (p.accumulate) {
                   float4 old = *reinterpret_cast<float4 *>(c);
@@ -645,7 +660,25 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int
   args.tiles_m = (args.M + BM - 1) / BM;
   args.tiles_n = (args.N + BN - 1) / BN;
   args.num_tiles = (long long)args.tiles_m * args.tiles_n * args.nh * args.nb;
-  long long grid = args.num_tiles < max_ctas ? args.num_tiles : max_ctas;
+  args.split_k = 1;
+  const int num_kb = (args.K + Cfg::BK - 1) / Cfg::BK;
+  args.kb_per_split = num_kb;
+  const bool plain = args.out_fp32 && !args.C2 && !args.addend && args.act == ACT_NONE && !args.scatter_rows && !args.gate_flags &&
+                     args.nh * args.nb == 1 && args.alpha == 1.0f;
+  if (plain && args.num_tiles * 2 <= max_ctas && num_kb >= 16) {
+    int want = (int)(max_ctas / args.num_tiles);
+    if (want > num_kb / 8) want = num_kb / 8;
+    if (want > 1) {
+      args.kb_per_split = (num_kb + want - 1) / want;
+      args.split_k = (num_kb + args.kb_per_split - 1) / args.kb_per_split;
+      if (!args.accumulate) {
+        cudaError_t e = cudaMemset2DAsync(args.C, (size_t)args.ldc * 4, 0, (size_t)args.N * 4, (size_t)args.M, stream);
+        if (e != cudaSuccess) return (int)e;
+      }
+    }
+  }
+  long long items = args.num_tiles * args.split_k;
+  long long grid = items < max_ctas ? items : max_ctas;
   if (grid < 1) return 0;
   kern<<<(unsigned)grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
   return (int)cudaGetLastError();
@@ -721,7 +754,7 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
-    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr;
+    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0;
     if (d->scatter_rows || d->gate_flags) return -2;  // the fused-collective paths need TMA-addressable operands
     SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
     dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);

@@ -50,6 +50,16 @@ class _ParallelOp(OpImpl):
     absorbed = False
     pair = None
 
+    def communicates(self) -> bool:
+        """Does this operator call NCCL in forward or backward?"""
+        if self.is_alias() or self.absorbed or isinstance(self, E.SkippedOp):
+            return False
+        if self.type == "REPARTITION" and self.pair is None:
+            return self.buf("INPUT").requires_grad  # forward is a local slice; backward all-gathers
+        if self.type == "COMBINE" and self.pair is not None:
+            return True
+        return True
+
     def is_alias(self) -> bool:
         ex = self.ex
         return ex.dist is None or ex.dist.world_size == 1 or self.nid in getattr(ex, "weight_chain_nodes", ())
@@ -250,6 +260,11 @@ class DistExecutable(Executable):
         self.overlap = overlap
         self._pre_analyse(pcg, ctx)
         super().__init__(pcg, cfg, dist=ctx)
+        # NCCL collectives are issued eagerly: a plan that still contains one (a parallel operator that is neither
+        # an alias nor absorbed into a GEMM and that communicates) is not captured into a CUDA graph
+        self.nccl_ops = [nid for nid, op in self.ops.items() if isinstance(op, _ParallelOp) and op.communicates()]
+        if self.nccl_ops and self.cfg.use_cuda_graph:
+            self.cfg.use_cuda_graph = False
         self._plan_buckets()
         self.parallelism = self._describe()
 

