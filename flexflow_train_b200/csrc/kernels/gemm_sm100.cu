@@ -28,7 +28,8 @@
 namespace {
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int GEMM_THREADS = 384;  // TMA warp, MMA warp, 8 epilogue warps, 2 copy warps (all-gather push)
+constexpr int COPY_THREADS = 64;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 struct GemmArgs {
@@ -68,6 +69,19 @@ struct GemmArgs {
   unsigned long long *gate_sync;  // [0] epoch (u64), word 3 (u32) = CTAs finished
   int gate_rows;
   int mb_rotate;
+  // Push (the sending half of all-gather -> GEMM, in the same kernel): two warps of every CTA copy this rank's
+  // row shard (push_nvec 16-byte vectors at push_src) into every peer's staging buffer push_dst[p] at vector
+  // offset push_off, while the other warps already multiply the local shard; the last CTA to finish raises
+  // push_flag[p] (this rank's flag on peer p) to *push_sync + 1.  Because the copy warps live in the GEMM's own
+  // CTAs, the transfer can never be starved of SMs by the GEMM that waits for it.
+  const uint4 *push_src;
+  long long push_nvec;
+  long long push_off;
+  void *push_dst[8];
+  unsigned long long *push_flag[8];
+  unsigned long long *push_sync;  // [0] epoch (u64), word 3 (u32) = CTAs finished copying
+  int push_world;
+  int push_rank;
 };
 
 // ----------------------------------------------------------------------------
@@ -386,6 +400,45 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
         if (!ok) break;
         tc_commit(&tmem_full[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------ all-gather push (two warps)
+    if (p.push_src) {
+      const int t = (int)threadIdx.x - 10 * 32;
+      const long long stride = (long long)gridDim.x * COPY_THREADS;
+      unsigned int *done = (unsigned int *)p.push_sync + 2;  // [2]: local copy, [3]: remote copies
+      // phase 0 copies the shard into this rank's own staging slot (the GEMM reads every row from the staging
+      // buffer) and raises the local flag; phase 1 sends it to the peers and raises this rank's flag there
+      for (int phase = 0; phase < 2; ++phase) {
+        const int k0 = phase, k1 = phase ? p.push_world : 1;
+        if (k0 < k1) {
+          long long i = (long long)blockIdx.x * COPY_THREADS + t;
+          for (; i + 3 * stride < p.push_nvec; i += 4 * stride) {  // four loads in flight per thread
+            uint4 v0 = p.push_src[i], v1 = p.push_src[i + stride], v2 = p.push_src[i + 2 * stride], v3 = p.push_src[i + 3 * stride];
+            for (int k = k0; k < k1; ++k) {
+              uint4 *d = (uint4 *)p.push_dst[(p.push_rank + k) % p.push_world] + p.push_off;
+              d[i] = v0; d[i + stride] = v1; d[i + 2 * stride] = v2; d[i + 3 * stride] = v3;
+            }
+          }
+          for (; i < p.push_nvec; i += stride) {
+            uint4 v = p.push_src[i];
+            for (int k = k0; k < k1; ++k) ((uint4 *)p.push_dst[(p.push_rank + k) % p.push_world] + p.push_off)[i] = v;
+          }
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;" ::"n"(COPY_THREADS) : "memory");
+        if (t == 0) {
+          if (atomicAdd(done + phase, 1u) == gridDim.x - 1) {
+            __threadfence_system();
+            const unsigned long long epoch = *p.push_sync + 1;
+            for (int k = k0; k < k1; ++k)
+              asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.push_flag[(p.push_rank + k) % p.push_world]), "l"(epoch)
+                           : "memory");
+            done[phase] = 0;
+            if (phase == 1) *p.push_sync = epoch;
+          }
+        }
       }
     }
   } else {
@@ -736,6 +789,15 @@ struct FfkGemmDesc {
   void *gate_sync;
   int gate_rows;
   int mb_rotate;
+  // in-kernel push of this rank's shard to the peers (see GemmArgs)
+  const void *push_src;
+  long long push_bytes;
+  long long push_dst_offset;
+  void *push_dst[8];
+  void *push_flag[8];
+  void *push_sync;
+  int push_world;
+  int push_rank;
 };
 
 // Returns 0 on success, a CUDA/driver error code otherwise, -2 for an
@@ -754,8 +816,8 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
-    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0;
-    if (d->scatter_rows || d->gate_flags) return -2;  // the fused-collective paths need TMA-addressable operands
+    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr;
+    if (d->scatter_rows || d->gate_flags || d->push_src) return -2;  // the fused-collective paths need TMA-addressable operands
     SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
     dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
     if (es == 2) gemm_simt_kernel<bf16><<<grid, block, 0, stream>>>(o, a);
@@ -793,6 +855,12 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   a.gate_rows = d->gate_rows; a.mb_rotate = d->mb_rotate;
   if (a.scatter_rows && (a.scatter_rows % BM != 0 || a.nh * a.nb != 1)) return -2;
   if (a.gate_flags && (a.gate_rows % BM != 0 || a.nh * a.nb != 1 || d->a_mn)) return -2;
+  a.push_src = (const uint4 *)d->push_src;
+  a.push_nvec = d->push_bytes / 16; a.push_off = d->push_dst_offset / 16;
+  for (int i = 0; i < 8; ++i) { a.push_dst[i] = d->push_dst[i]; a.push_flag[i] = (unsigned long long *)d->push_flag[i]; }
+  a.push_sync = (unsigned long long *)d->push_sync; a.push_world = d->push_world; a.push_rank = d->push_rank;
+  if (a.push_src && ((d->push_bytes & 15) || (d->push_dst_offset & 15) || ((uintptr_t)d->push_src & 15) || a.push_world > 8 || !a.push_sync))
+    return -2;
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_gemm_err);
   a.err = (int *)errp;

@@ -55,6 +55,9 @@ class GemmDesc(ctypes.Structure):
         # fused collectives (see gemm_sm100.cu): scatter epilogue and gated A operand
         ("scatter", c_void_p * 8), ("scatter_rows", c_int), ("scatter_src", c_int),
         ("gate_flags", c_void_p), ("gate_sync", c_void_p), ("gate_rows", c_int), ("mb_rotate", c_int),
+        # in-kernel push of this rank's shard to the peers' staging buffers (all-gather -> GEMM)
+        ("push_src", c_void_p), ("push_bytes", c_longlong), ("push_dst_offset", c_longlong), ("push_dst", c_void_p * 8),
+        ("push_flag", c_void_p * 8), ("push_sync", c_void_p), ("push_world", c_int), ("push_rank", c_int),
     ]
 
 
@@ -157,7 +160,7 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
              a_sh=0, a_sb=0, b_sh=0, b_sb=0, c_sh=0, c_sb=0, C2=None, bias=None, addend=None,
              ld_add=0, add_sh=0, add_sb=0, alpha=1.0, act=0, out_fp32=False, accumulate=False,
              bn=0, max_ctas=0, scatter=None, scatter_rows=0, scatter_src=0, gate_flags=None, gate_sync=None,
-             gate_rows=0, mb_rotate=0):
+             gate_rows=0, mb_rotate=0, push=None):
     """D = epilogue(alpha * A[M,K] . B[N,K]^T) on raw pointers; see gemm_sm100.cu.
 
     scatter / scatter_rows / scatter_src: write each output tile into the owning rank's staging buffer
@@ -168,6 +171,11 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
                  C, ldc, c_sh, c_sb, C2, bias, addend, ld_add, add_sh, add_sb, alpha, act, int(out_fp32),
                  int(accumulate), bn, max_ctas, sc, scatter_rows, scatter_src, gate_flags, gate_sync, gate_rows,
                  mb_rotate)
+    if push is not None:  # dict(src, nbytes, dst_offset, dst=[peer ptrs], flag=[peer flag ptrs], sync, world, rank)
+        d.push_src, d.push_bytes, d.push_dst_offset = push["src"], push["nbytes"], push["dst_offset"]
+        d.push_dst = (c_void_p * 8)(*([int(x) for x in push["dst"]] + [None] * (8 - len(push["dst"]))))
+        d.push_flag = (c_void_p * 8)(*([int(x) for x in push["flag"]] + [None] * (8 - len(push["flag"]))))
+        d.push_sync, d.push_world, d.push_rank = push["sync"], push["world"], push["rank"]
     _check(lib().ffk_gemm(ctypes.byref(d), _stream()), "ffk_gemm")
 
 

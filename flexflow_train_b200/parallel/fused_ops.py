@@ -95,7 +95,6 @@ class AllGatherGemm:
         self.flag_base = ctx.alloc_flags(w)
         self.bar_base = ctx.alloc_flags(w)
         self.sync_push, self.sync_gate, self.sync_bar = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
-        self.side = torch.cuda.Stream() if overlap else None
 
     def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, act=None, pre_act_out=None,
                  w_kn: bool = False, accumulate: bool = False):
@@ -106,22 +105,20 @@ class AllGatherGemm:
         n = w.shape[1] if w_kn else w.shape[0]
         # nobody may overwrite a staging buffer that a peer's previous GEMM might still be reading
         comm.barrier(ctx, self.bar_base, self.sync_bar)
-        main = torch.cuda.current_stream()
-        if self.side is not None:
-            self.side.wait_stream(main)
-            with torch.cuda.stream(self.side):
-                comm.push_rows(ctx, x_local, self.gathered, ctx.rank * self.shard_bytes, self.flag_base, self.sync_push, blocks=24)
-        else:
-            comm.push_rows(ctx, x_local, self.gathered, ctx.rank * self.shard_bytes, self.flag_base, self.sync_push)
+        es = x_local.element_size()
+        if self.k * es % 16 != 0:
+            raise ValueError("row size must be a multiple of 16 bytes")
+        flag_ptrs = [p + (self.flag_base + ctx.rank) * 8 for p in ctx.flags.peer_ptrs]
+        # one kernel: two warps of every CTA push the local shard to the peers while the rest start on the local rows
         K.gemm_raw(M=W * self.rows_local, N=n, K=self.k, A=self.gathered.local_ptr, lda=self.k, B=w.data_ptr(),
                    ldb=n if w_kn else self.k, b_mn=w_kn, C=out.data_ptr(), ldc=n, accumulate=accumulate,
                    out_fp32=out.dtype == torch.float32, bias=None if bias is None else bias.data_ptr(),
                    act=K.ACT_CODES[act] if not isinstance(act, int) else act,
                    C2=None if pre_act_out is None else pre_act_out.data_ptr(),
                    gate_flags=ctx.flags.local_ptr + self.flag_base * 8, gate_sync=self.sync_gate.data_ptr(),
-                   gate_rows=self.rows_local, mb_rotate=ctx.rank * (self.rows_local // 128))
-        if self.side is not None:
-            main.wait_stream(self.side)
+                   gate_rows=self.rows_local, mb_rotate=ctx.rank * (self.rows_local // 128),
+                   push=dict(src=x_local.data_ptr(), nbytes=self.shard_bytes, dst_offset=ctx.rank * self.shard_bytes,
+                             dst=self.gathered.peer_ptrs, flag=flag_ptrs, sync=self.sync_push.data_ptr(), world=W, rank=ctx.rank))
         return out
 
 
