@@ -1,0 +1,67 @@
+/* C interface of the compiler core: build computation graphs, (de)serialise them in the v1 JSON format and
+ * run the strategy search, through opaque handles.  Counterpart of the reference's C headers
+ * (lib/pcg/ffi/include/flexflow/pcg.h, lib/compiler/ffi/include/flexflow/compiler.h,
+ * lib/ffi/include/flexflow/flexflow.h), whose implementation files are one-line stubs; this one is complete.
+ *
+ * The symbols live in the same shared object as the Python module (_ffcore*.so): load it with dlopen / ctypes.
+ * Every function that can fail returns 0 on success and non-zero on failure; ffc_last_error() then describes
+ * the failure (thread-local).  Strings returned by the library are released with ffc_string_free.  */
+#ifndef FFC_FFI_H
+#define FFC_FFI_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ffc_builder ffc_builder_t;
+typedef struct ffc_graph ffc_graph_t;
+typedef struct {
+  int node;
+  int slot; /* value of the Slot enumeration; ffc_slot_name / ffc_slot_from_name convert */
+} ffc_value_t;
+
+const char *ffc_last_error(void);
+void ffc_string_free(char *s);
+const char *ffc_slot_name(int slot);
+int ffc_slot_from_name(const char *name);
+
+/* ---- computation graph builder */
+ffc_builder_t *ffc_builder_create(void);
+void ffc_builder_destroy(ffc_builder_t *b);
+int ffc_builder_create_input(ffc_builder_t *b, const int64_t *dims, int ndims, const char *dtype, const char *name, ffc_value_t *out);
+int ffc_builder_create_weight(ffc_builder_t *b, const int64_t *dims, int ndims, const char *dtype, const char *initializer_json,
+                              const char *name, ffc_value_t *out);
+/* Generic layer: op_type is the operator's name ("LINEAR", "EW_ADD", ...), attrs_json its attribute object,
+ * inputs/input_slots the operands by slot name.  Missing weight operands are created with default initializers. */
+int ffc_builder_add_layer(ffc_builder_t *b, const char *op_type, const char *attrs_json, const ffc_value_t *inputs,
+                          const char *const *input_slots, int num_inputs, const char *name, ffc_value_t *outputs, int max_outputs,
+                          int *num_outputs);
+/* Convenience wrappers of the most common layers (activation: NULL or "RELU", "GELU", "SIGMOID", "TANH") */
+int ffc_builder_dense(ffc_builder_t *b, ffc_value_t x, int64_t out_channels, const char *activation, int use_bias, const char *name,
+                      ffc_value_t *out);
+int ffc_builder_conv2d(ffc_builder_t *b, ffc_value_t x, int64_t out_channels, int kernel_h, int kernel_w, int stride_h, int stride_w,
+                       int padding_h, int padding_w, const char *activation, int groups, int use_bias, const char *name, ffc_value_t *out);
+int ffc_builder_unary(ffc_builder_t *b, const char *op, ffc_value_t x, int has_scalar, double scalar, const char *name, ffc_value_t *out);
+int ffc_builder_binary(ffc_builder_t *b, const char *op, ffc_value_t x, ffc_value_t y, const char *name, ffc_value_t *out);
+int ffc_builder_softmax(ffc_builder_t *b, ffc_value_t x, int dim, const char *name, ffc_value_t *out);
+int ffc_builder_value_shape(const ffc_builder_t *b, ffc_value_t v, int64_t *dims, int max_dims, int *ndims);
+/* A copy of the graph built so far */
+ffc_graph_t *ffc_builder_graph(const ffc_builder_t *b);
+
+/* ---- graphs */
+ffc_graph_t *ffc_model_build(const char *model_name, const char *config_json);
+ffc_graph_t *ffc_graph_from_json(const char *v1_json);
+char *ffc_graph_to_json(const ffc_graph_t *g, int parallel, int indent);
+char *ffc_graph_to_dot(const ffc_graph_t *g);
+int ffc_graph_num_nodes(const ffc_graph_t *g);
+void ffc_graph_destroy(ffc_graph_t *g);
+
+/* ---- strategy search.  algorithm: "unity", "mcmc" or "data_parallel".  On success *out is the mapped parallel
+ * computation graph (owned by the caller) and *runtime_ms its estimated step time. */
+int ffc_graph_optimize(const ffc_graph_t *cg, int num_nodes, int gpus_per_node, const char *algorithm, int budget, double alpha,
+                       unsigned seed, ffc_graph_t **out, double *runtime_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

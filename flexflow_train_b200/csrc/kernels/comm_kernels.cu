@@ -145,7 +145,35 @@ __global__ void allreduce_scale_kernel(PeerPtrs buf, PeerPtrs flags, int flag_ba
     const long long per = (nvec + world - 1) / world;
     const long long v0 = per * rank, v1 = min(nvec, per * (rank + 1));
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+    long long i = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    // main loop: four vectors per trip so that 4 x (world - 1) remote 16-byte loads are in flight per thread --
+    // a peer load takes a few microseconds over NVLink and the link is only filled by many outstanding requests
+    for (; i + 3 * stride < v1; i += 4 * stride) {
+      float acc[4][8], t[8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ld8f((const T *)buf.p[rank] + offset + (i + u * stride) * 8, acc[u]);
+#pragma unroll
+      for (int k = 1; k < MAX_RANKS; ++k) {
+        if (k < world) {
+          const T *src = (const T *)buf.p[(rank + k) % world] + offset;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            ld8f(src + (i + u * stride) * 8, t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[u][j] += t[j];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] *= scale;
+#pragma unroll
+        for (int k = 0; k < MAX_RANKS; ++k)
+          if (k < world) st8f((T *)buf.p[(rank + k) % world] + offset + (i + u * stride) * 8, acc[u]);
+      }
+    }
+    for (; i < v1; i += stride) {
       float acc[8], t[8];
       ld8f((const T *)buf.p[rank] + offset + i * 8, acc);
 #pragma unroll
