@@ -110,9 +110,71 @@ struct AllReduceSync {
   unsigned int *blocks_done;      // local: blocks that finished their slice
 };
 
-template <typename T>
+// Optimizer fused into the all-reduce (sharded update): the rank that reduced a slice of the gradient also owns
+// that slice of the fp32 master weights and moments, applies the update there and sends the new bf16 weights
+// (not the gradient) to every rank.  The update is thereby done once per element instead of once per rank.
+struct UpdateArgs {
+  float *w, *m, *v;        // local fp32 master weights and optimizer state (whole arena; only owned slices are touched)
+  PeerPtrs shadow;         // bf16 weight arenas of all ranks
+  const float *alpha_ptr;  // Adam: bias-corrected step size of this step (device memory)
+  int kind;                // 0 Adam, 1 SGD
+  float lr, beta1, beta2, eps, wd, momentum;
+  int nesterov;
+};
+
+__device__ __forceinline__ void fused_update8(const UpdateArgs &u, float alpha_t, long long e, const float *g, int rank, int world) {
+  float w[8], o[8];
+  *reinterpret_cast<float4 *>(w) = *reinterpret_cast<const float4 *>(u.w + e);
+  *reinterpret_cast<float4 *>(w + 4) = *reinterpret_cast<const float4 *>(u.w + e + 4);
+  if (u.kind == 0) {
+    float m[8], v[8];
+    *reinterpret_cast<float4 *>(m) = *reinterpret_cast<const float4 *>(u.m + e);
+    *reinterpret_cast<float4 *>(m + 4) = *reinterpret_cast<const float4 *>(u.m + e + 4);
+    *reinterpret_cast<float4 *>(v) = *reinterpret_cast<const float4 *>(u.v + e);
+    *reinterpret_cast<float4 *>(v + 4) = *reinterpret_cast<const float4 *>(u.v + e + 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gt = g[j] + u.wd * w[j];
+      m[j] = u.beta1 * m[j] + (1.f - u.beta1) * gt;
+      v[j] = u.beta2 * v[j] + (1.f - u.beta2) * gt * gt;
+      w[j] -= alpha_t * m[j] / (sqrtf(v[j]) + u.eps);
+    }
+    *reinterpret_cast<float4 *>(u.m + e) = *reinterpret_cast<float4 *>(m);
+    *reinterpret_cast<float4 *>(u.m + e + 4) = *reinterpret_cast<float4 *>(m + 4);
+    *reinterpret_cast<float4 *>(u.v + e) = *reinterpret_cast<float4 *>(v);
+    *reinterpret_cast<float4 *>(u.v + e + 4) = *reinterpret_cast<float4 *>(v + 4);
+  } else {
+    float mo[8];
+    if (u.momentum > 0.f) {
+      *reinterpret_cast<float4 *>(mo) = *reinterpret_cast<const float4 *>(u.m + e);
+      *reinterpret_cast<float4 *>(mo + 4) = *reinterpret_cast<const float4 *>(u.m + e + 4);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gt = g[j] + u.wd * w[j];
+      if (u.momentum > 0.f) {
+        mo[j] = mo[j] * u.momentum + gt;
+        gt = u.nesterov ? gt + u.momentum * mo[j] : mo[j];
+      }
+      w[j] -= u.lr * gt;
+    }
+    if (u.momentum > 0.f) {
+      *reinterpret_cast<float4 *>(u.m + e) = *reinterpret_cast<float4 *>(mo);
+      *reinterpret_cast<float4 *>(u.m + e + 4) = *reinterpret_cast<float4 *>(mo + 4);
+    }
+  }
+  *reinterpret_cast<float4 *>(u.w + e) = *reinterpret_cast<float4 *>(w);
+  *reinterpret_cast<float4 *>(u.w + e + 4) = *reinterpret_cast<float4 *>(w + 4);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = w[j];
+#pragma unroll
+  for (int k = 0; k < MAX_RANKS; ++k)
+    if (k < world) st8f((bf16 *)u.shadow.p[(rank + k) % world] + e, o);
+}
+
+template <typename T, bool UPDATE>
 __global__ void allreduce_scale_kernel(PeerPtrs buf, PeerPtrs flags, int flag_base, long long offset, long long n, float scale, int rank,
-                                       int world, AllReduceSync sync, int *status) {
+                                       int world, AllReduceSync sync, int *status, UpdateArgs upd) {
   __shared__ unsigned long long epoch;
   __shared__ int go;
   if (threadIdx.x == 0) epoch = *sync.epoch_ctr + 1;
@@ -141,6 +203,7 @@ __global__ void allreduce_scale_kernel(PeerPtrs buf, PeerPtrs flags, int flag_ba
   __syncthreads();
   if (go) {
     // ---- reduce my slice, write it everywhere
+    const float alpha_t = (UPDATE && upd.alpha_ptr) ? *upd.alpha_ptr : upd.lr;
     const long long nvec = n / 8;
     const long long per = (nvec + world - 1) / world;
     const long long v0 = per * rank, v1 = min(nvec, per * (rank + 1));
@@ -168,9 +231,13 @@ __global__ void allreduce_scale_kernel(PeerPtrs buf, PeerPtrs flags, int flag_ba
       for (int u = 0; u < 4; ++u) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[u][j] *= scale;
+        if (UPDATE) {
+          fused_update8(upd, alpha_t, offset + (i + u * stride) * 8, acc[u], rank, world);
+        } else {
 #pragma unroll
-        for (int k = 0; k < MAX_RANKS; ++k)
-          if (k < world) st8f((T *)buf.p[(rank + k) % world] + offset + (i + u * stride) * 8, acc[u]);
+          for (int k = 0; k < MAX_RANKS; ++k)
+            if (k < world) st8f((T *)buf.p[(rank + k) % world] + offset + (i + u * stride) * 8, acc[u]);
+        }
       }
     }
     for (; i < v1; i += stride) {
@@ -187,12 +254,16 @@ __global__ void allreduce_scale_kernel(PeerPtrs buf, PeerPtrs flags, int flag_ba
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] *= scale;
+      if (UPDATE) {
+        fused_update8(upd, alpha_t, offset + i * 8, acc, rank, world);
+      } else {
 #pragma unroll
-      for (int k = 0; k < MAX_RANKS; ++k)
-        if (k < world) st8f((T *)buf.p[(rank + k) % world] + offset + i * 8, acc);
+        for (int k = 0; k < MAX_RANKS; ++k)
+          if (k < world) st8f((T *)buf.p[(rank + k) % world] + offset + i * 8, acc);
+      }
     }
-    // tail (n % 8 elements) is handled by rank 0
-    if (rank == 0 && blockIdx.x == 0) {
+    // tail (n % 8 elements) is handled by rank 0 (the fused update requires n % 8 == 0)
+    if (!UPDATE && rank == 0 && blockIdx.x == 0) {
       for (long long i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
         float a = 0.f;
         for (int k = 0; k < world; ++k) a += (float)((const T *)buf.p[k])[offset + i];
@@ -370,13 +441,36 @@ FFK_API int ffk_grad_allreduce_scale(void *const *buf_peers, void *const *flag_p
   s.started = (unsigned int *)sync_words + 2;
   s.blocks_done = (unsigned int *)sync_words + 3;
   if (blocks <= 0) blocks = 32;
+  UpdateArgs none = {};
   if (dt == 1)
-    allreduce_scale_kernel<bf16><<<blocks, 512, 0, st>>>(make_ptrs(buf_peers, world), make_ptrs(flag_peers, world), flag_base, offset, n, scale, rank,
-                                                         world, s, status);
+    allreduce_scale_kernel<bf16, false><<<blocks, 512, 0, st>>>(make_ptrs(buf_peers, world), make_ptrs(flag_peers, world), flag_base, offset, n, scale,
+                                                                rank, world, s, status, none);
   else if (dt == 0)
-    allreduce_scale_kernel<float><<<blocks, 512, 0, st>>>(make_ptrs(buf_peers, world), make_ptrs(flag_peers, world), flag_base, offset, n, scale, rank,
-                                                          world, s, status);
+    allreduce_scale_kernel<float, false><<<blocks, 512, 0, st>>>(make_ptrs(buf_peers, world), make_ptrs(flag_peers, world), flag_base, offset, n, scale,
+                                                                 rank, world, s, status, none);
   else return -2;
+  return (int)cudaGetLastError();
+}
+
+// Gradient reduce-scatter + optimizer update of the owned slice + all-gather of the new bf16 weights, one kernel.
+// grads: bf16 arenas (symmetric), shadow: bf16 weight arenas (symmetric), w/m/v: local fp32 arenas.  offset and n
+// are in elements, multiples of 8.  kind: 0 Adam (alpha_ptr = device pointer to the step size), 1 SGD.
+FFK_API int ffk_grad_allreduce_update(void *const *grad_peers, void *const *shadow_peers, float *w, float *m, float *v, void *const *flag_peers,
+                                      int flag_base, long long offset, long long n, float scale, int rank, int world, void *sync_words,
+                                      int *status, int kind, float lr, const float *alpha_ptr, float beta1, float beta2, float eps, float wd,
+                                      float momentum, int nesterov, int blocks, cudaStream_t st) {
+  if (world > MAX_RANKS || (n & 7) || (offset & 7)) return -2;
+  if (n <= 0) return 0;
+  AllReduceSync s;
+  s.epoch_ctr = (unsigned long long *)sync_words;
+  s.started = (unsigned int *)sync_words + 2;
+  s.blocks_done = (unsigned int *)sync_words + 3;
+  if (blocks <= 0) blocks = 32;
+  UpdateArgs u;
+  u.w = w; u.m = m; u.v = v; u.shadow = make_ptrs(shadow_peers, world); u.alpha_ptr = alpha_ptr; u.kind = kind; u.lr = lr;
+  u.beta1 = beta1; u.beta2 = beta2; u.eps = eps; u.wd = wd; u.momentum = momentum; u.nesterov = nesterov;
+  allreduce_scale_kernel<bf16, true><<<blocks, 512, 0, st>>>(make_ptrs(grad_peers, world), make_ptrs(flag_peers, world), flag_base, offset, n, scale,
+                                                             rank, world, s, status, u);
   return (int)cudaGetLastError();
 }
 

@@ -25,6 +25,7 @@ def _lib():
         sig = {
             "ffk_comm_barrier": [PP, I, I, I, P, P, P],
             "ffk_grad_allreduce_scale": [PP, PP, I, L, L, F, I, I, P, P, I, I, P],
+            "ffk_grad_allreduce_update": [PP, PP, P, P, P, PP, I, L, L, F, I, I, P, P, I, F, P, F, F, F, F, F, I, I, P],
             "ffk_push_rows": [P, PP, L, L, PP, I, I, I, P, I, I, P],
             "ffk_reduce_partials": [P, P, P, L, I, P, I, P, P, I, I, P],
             "ffk_alltoall_embedding_fwd": [P, P, P, PP, I, I, I, I, I, I, I, I, P],
@@ -61,6 +62,19 @@ def grad_allreduce_scale(ctx: DistContext, buf: SymmetricBuffer, offset_elems: i
     _chk(_lib().ffk_grad_allreduce_scale(buf.ptr_array, ctx.flags.ptr_array, flag_base, offset_elems, n, scale, ctx.rank,
                                          ctx.world_size, sync.data_ptr(), ctx.status.data_ptr(), dt, blocks, _stream()),
          "ffk_grad_allreduce_scale")
+
+
+def grad_allreduce_update(ctx: DistContext, grads: SymmetricBuffer, shadow: SymmetricBuffer, master, m, v, offset_elems: int, n: int,
+                          scale: float, opt, alpha_ptr, flag_base: int, sync: torch.Tensor, blocks: int = 32):
+    """Reduce-scatter grads[offset : offset+n], apply the optimizer to the owned slice of master/m/v and write the new
+    bf16 weights into every rank's `shadow`.  `opt` is an OptimizerConfig; offset and n are multiples of 8."""
+    kind = 0 if opt.kind == "adam" else 1
+    mp = m.data_ptr() if m is not None else None
+    vp = v.data_ptr() if v is not None else None
+    _chk(_lib().ffk_grad_allreduce_update(grads.ptr_array, shadow.ptr_array, master.data_ptr(), mp, vp, ctx.flags.ptr_array, flag_base,
+                                          offset_elems, n, scale, ctx.rank, ctx.world_size, sync.data_ptr(), ctx.status.data_ptr(), kind,
+                                          opt.lr, alpha_ptr, opt.beta1, opt.beta2, opt.epsilon, opt.weight_decay, opt.momentum,
+                                          int(opt.nesterov), blocks, _stream()), "ffk_grad_allreduce_update")
 
 
 def push_rows(ctx: DistContext, src: torch.Tensor, dst: SymmetricBuffer, dst_byte_offset: int, flag_base: int,

@@ -248,9 +248,10 @@ class FuseOut:
 
 class DistExecutable(Executable):
     def __init__(self, pcg, cfg: Optional[ExecConfig], ctx: DistContext, bucket_mb: int = 128, overlap: bool = True,
-                 fuse_collectives: bool = True):
+                 fuse_collectives: bool = True, fuse_optimizer: bool = True):
         self.ctx = ctx
         self.fuse_collectives = fuse_collectives
+        self.fuse_optimizer = fuse_optimizer
         self._rs_shared: Dict[tuple, GemmReduceScatter] = {}
         self._ag_shared: Dict[tuple, AllGatherGemm] = {}
         self._discard: Dict[tuple, torch.Tensor] = {}
@@ -436,6 +437,13 @@ class DistExecutable(Executable):
         self.grad_ar = GradAllReduce(self.ctx, numel, dtype)
         return self.grad_ar.tensor
 
+    def alloc_shadow_arena(self, numel):
+        # peers write the updated weights of the slices they own straight into this arena
+        self.shadow_buf = self.ctx.symmetric(numel * 2)
+        t = self.shadow_buf.view(torch.bfloat16, numel=numel)
+        t.zero_()
+        return t
+
     def head_shards(self, op) -> int:
         w = op.inputs.get("WEIGHT")
         if w is None:
@@ -506,6 +514,10 @@ class DistExecutable(Executable):
             self._launch_after.setdefault(nid, []).append(bi)
         self.side = torch.cuda.Stream() if self.overlap else None
         self._pending = False
+        # sharded update inside the all-reduce: bf16 mixed precision, every bucket a multiple of 8 elements
+        o = self.cfg.optimizer
+        self.fused_update = bool(self.fuse_optimizer and self.buckets and self.shadow is not None and o.kind in ("adam", "sgd")
+                                 and all((e - s) % 8 == 0 and s % 8 == 0 for s, e in self.buckets))
 
     def backward(self):
         if not getattr(self, "buckets", None):
@@ -520,15 +532,45 @@ class DistExecutable(Executable):
         for bi in self._launch_after.get(-1, ()):
             self._launch_bucket(bi, main)
 
+    def _reduce_bucket(self, s, e):
+        if self.fused_update:
+            self.grad_ar.run_update(self.shadow_buf, self.master, self.opt_m, self.opt_v, self.cfg.optimizer,
+                                    self.alpha_tensor.data_ptr(), scale=1.0, offset=s, n=e - s)
+        else:
+            self.grad_ar.run(scale=1.0, offset=s, n=e - s)
+
     def _launch_bucket(self, bi, main):
         s, e = self.buckets[bi]
         if self.side is not None:
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
-                self.grad_ar.run(scale=1.0, offset=s, n=e - s)
+                self._reduce_bucket(s, e)
             self._pending = True
         else:
-            self.grad_ar.run(scale=1.0, offset=s, n=e - s)
+            self._reduce_bucket(s, e)
+
+    def update(self, start: int = 0):
+        # replicated parameters were updated (sharded over ranks) by the bucket kernels
+        super().update(self.rep_numel if getattr(self, "fused_update", False) else start)
+
+    def consolidate_state(self):
+        """With the sharded update every rank holds current fp32 master weights and moments only for the slices it
+        owns; this gathers them so that every rank (and a checkpoint) has the whole state again."""
+        if not getattr(self, "fused_update", False):
+            return
+        for t in (self.master, self.opt_m, self.opt_v):
+            if t is None:
+                continue
+            keep = torch.zeros_like(t[:self.rep_numel])
+            for s, e in self.buckets:
+                a, b = self.grad_ar.owned_ranges(s, e - s)
+                keep[a:b] = t[a:b]
+            dist.all_reduce(keep, group=self.ctx.group)
+            t[:self.rep_numel].copy_(keep)
+
+    def state_dict(self):
+        self.consolidate_state()
+        return super().state_dict()
 
     def sync_gradients(self):
         if self.side is not None and self._pending:

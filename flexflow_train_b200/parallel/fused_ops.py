@@ -47,6 +47,22 @@ class GradAllReduce:
         comm.grad_allreduce_scale(self.ctx, self.buf, offset, n, scale, self.dtype, self.flag_base, self.sync, self.blocks)
 
 
+    def run_update(self, shadow, master, m, v, opt, alpha_ptr, scale: float = 1.0, offset: int = 0, n: Optional[int] = None):
+        """Sharded-update form: reduce-scatter the gradients, update the owned slice of the fp32 state, all-gather
+        the new bf16 weights into every rank's `shadow` (a SymmetricBuffer).  The gradient arena is left partly
+        reduced (each rank holds nothing useful in it afterwards)."""
+        n = self.numel - offset if n is None else n
+        comm.grad_allreduce_update(self.ctx, self.buf, shadow, master, m, v, offset, n, scale, opt, alpha_ptr, self.flag_base, self.sync,
+                                   self.blocks)
+
+    def owned_ranges(self, offset: int, n: int):
+        """[start, end) element range of [offset, offset+n) whose optimizer state this rank owns under run_update."""
+        nvec = n // 8
+        per = (nvec + self.ctx.world_size - 1) // self.ctx.world_size
+        v0, v1 = per * self.ctx.rank, min(nvec, per * (self.ctx.rank + 1))
+        return offset + v0 * 8, offset + max(v1, v0) * 8
+
+
 class GemmReduceScatter:
     """F1.  y_shard[rows/world, N] = sum_over_ranks( x_r[rows, K_r] @ w_r[N, K_r]^T )  (+ residual shard)."""
 

@@ -940,7 +940,7 @@ class Executable:
         self.num_params = total
         mixed = self.cfg.compute_dtype == "bf16"
         self.master = torch.zeros(max(total, 1), dtype=torch.float32, device=dev)
-        self.shadow = torch.zeros(max(total, 1), dtype=torch.bfloat16, device=dev) if mixed else None
+        self.shadow = self.alloc_shadow_arena(max(total, 1)) if mixed else None
         if self.cfg.training:
             self.grads = self.alloc_grad_arena(max(total, 1), torch.bfloat16 if mixed else torch.float32)
             self.opt_m = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) \
@@ -978,6 +978,10 @@ class Executable:
 
     def alloc_grad_arena(self, numel, dtype):
         return torch.zeros(numel, dtype=dtype, device=self.device)
+
+    def alloc_shadow_arena(self, numel):
+        """The bf16 copy of the weights that the kernels read (the fp32 master arena is only touched by the update)."""
+        return torch.zeros(numel, dtype=torch.bfloat16, device=self.device)
 
     def resolve_loss_value(self, v: Value) -> Value:
         """The value the loss is computed on; the distributed executable steps back over a trailing Combine."""
@@ -1227,15 +1231,21 @@ class Executable:
         """Nothing to clear: the plan marks, per gradient buffer, which operator writes it first (a plain store)
         and which accumulate, so no buffer is read before it has been written in the same step."""
 
-    def update(self):
+    def update(self, start: int = 0):
+        """Optimizer step over the parameter arena from element `start` (the distributed executable updates the
+        replicated prefix inside its gradient all-reduce and passes the end of that prefix here)."""
         o = self.cfg.optimizer
         self.step_count += 1
-        shadow = self.shadow
+        if start >= self.master.numel():
+            return
+        sl = slice(start, None)
+        shadow = self.shadow[sl] if self.shadow is not None else None
         if o.kind == "adam":
-            K.adam_update(self.master, self.opt_m, self.opt_v, self.grads, shadow, 0.0, o.beta1, o.beta2, o.epsilon,
+            K.adam_update(self.master[sl], self.opt_m[sl], self.opt_v[sl], self.grads[sl], shadow, 0.0, o.beta1, o.beta2, o.epsilon,
                           o.weight_decay, 1.0, alpha_tensor=self.alpha_tensor)
         else:
-            K.sgd_update(self.master, self.opt_m, self.grads, shadow, o.lr, o.momentum, o.nesterov, o.weight_decay)
+            K.sgd_update(self.master[sl], self.opt_m[sl] if self.opt_m is not None else None, self.grads[sl], shadow, o.lr, o.momentum,
+                         o.nesterov, o.weight_decay)
 
     def _pre_step(self):
         """Per-step scalars that a captured graph reads from device memory."""
