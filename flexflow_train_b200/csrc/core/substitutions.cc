@@ -465,6 +465,52 @@ Substitution create_partition_layernorm_combine(int dim, int degree, bool affine
   s.outputs = {{0, Slot::OUTPUT, li + 1, Slot::OUTPUT}};
   return s;
 }
+// BatchNorm over a partitioned sample dim: every shard normalises with the statistics of its own samples (the
+// usual data-parallel batch norm); scale and shift are replicated.
+Substitution create_partition_batchnorm_combine(int dim, int degree, bool affine) {
+  Substitution s;
+  s.name = "partition_batchnorm_combine" + sfx(dim, degree) + (affine ? "_affine" : "");
+  PatternNode n;
+  n.constraints = {op_is(OpType::BATCHNORM), attr_eq("affine", affine)};
+  n.inputs = {gin(Slot::INPUT, 0)};
+  if (affine) { n.inputs.push_back(gin(Slot::GAMMA, 1)); n.inputs.push_back(gin(Slot::BETA, 2)); }
+  s.pattern.nodes = {n};
+  s.pattern.num_inputs = affine ? 3 : 1;
+  s.pattern.input_constraints[0] = {{TensorConstraint::NUM_DIMS_AT_LEAST, 0, dim + 2}, {TensorConstraint::DIM_DIVISIBLE_BY, dim, degree}, {TensorConstraint::DIM_DEGREE_EQUAL, dim, 1}};
+  s.out_nodes.push_back(repartition(ogin(Slot::INPUT, 0), dim, degree));
+  std::vector<OutInput> ins = {onin(Slot::INPUT, 0)};
+  if (affine) {
+    s.out_nodes.push_back(replicate(ogin(Slot::INPUT, 1), degree));
+    s.out_nodes.push_back(replicate(ogin(Slot::INPUT, 2), degree));
+    ins.push_back(onin(Slot::GAMMA, 1));
+    ins.push_back(onin(Slot::BETA, 2));
+  }
+  s.out_nodes.push_back(templated(0, ins));
+  int li = (int)s.out_nodes.size() - 1;
+  s.out_nodes.push_back(combine(onin(Slot::INPUT, li), dim, degree));
+  s.outputs = {{0, Slot::OUTPUT, li + 1, Slot::OUTPUT}};
+  return s;
+}
+// Concat of `num_inputs` tensors along `axis`, all partitioned on another dim
+Substitution create_partition_concat_combine(int num_inputs, int axis, int dim, int degree) {
+  Substitution s;
+  s.name = "partition_concat" + std::to_string(num_inputs) + "_axis" + std::to_string(axis) + "_combine" + sfx(dim, degree);
+  PatternNode n;
+  n.constraints = {op_is(OpType::CONCAT), attr_eq("axis", axis), attr_eq("num_inputs", num_inputs)};
+  for (int i = 0; i < num_inputs; ++i) n.inputs.push_back(gin(input_slot_n(i), i));
+  s.pattern.nodes = {n};
+  s.pattern.num_inputs = num_inputs;
+  std::vector<OutInput> ins;
+  for (int i = 0; i < num_inputs; ++i) {
+    s.pattern.input_constraints[i] = {{TensorConstraint::NUM_DIMS_AT_LEAST, 0, std::max(dim, axis) + 1}, {TensorConstraint::DIM_DIVISIBLE_BY, dim, degree}, {TensorConstraint::DIM_DEGREE_EQUAL, dim, 1}};
+    s.out_nodes.push_back(repartition(ogin(Slot::INPUT, i), dim, degree));
+    ins.push_back(onin(input_slot_n(i), i));
+  }
+  s.out_nodes.push_back(templated(0, ins));
+  s.out_nodes.push_back(combine(onin(Slot::INPUT, num_inputs), dim, degree));
+  s.outputs = {{0, Slot::OUTPUT, num_inputs + 1, Slot::OUTPUT}};
+  return s;
+}
 Substitution create_partition_embedding_combine(int dim, int degree) {
   Substitution s;
   s.name = "partition_embedding_combine" + sfx(dim, degree);
@@ -545,6 +591,16 @@ std::vector<Substitution> get_substitution_set(const MachineSpec &m, int max_dim
       r.push_back(create_partition_binary_combine(OpType::EW_MUL, dim, d));
       for (int sd = 0; sd < max_dims; ++sd)
         if (sd != dim) r.push_back(create_partition_softmax_combine(sd, dim, d));
+      if (dim == 0) {  // sample-dim rules of the convolution-stack and shape operators
+        for (OpType u : {OpType::POOL2D, OpType::FLAT, OpType::NOOP, OpType::ELU, OpType::EXP, OpType::SCALAR_MULTIPLY, OpType::SCALAR_ADD})
+          r.push_back(create_partition_unary_combine(u, dim, d));
+        r.push_back(create_partition_binary_combine(OpType::EW_SUB, dim, d));
+        r.push_back(create_partition_binary_combine(OpType::BATCHMATMUL, dim, d));
+        r.push_back(create_partition_batchnorm_combine(dim, d, true));
+        r.push_back(create_partition_batchnorm_combine(dim, d, false));
+        for (int k = 2; k <= 8; ++k)
+          for (int axis = 1; axis < max_dims; ++axis) r.push_back(create_partition_concat_combine(k, axis, dim, d));
+      }
       if (dim < max_dims - 1) {
         r.push_back(create_partition_layernorm_combine(dim, d, true));
         r.push_back(create_partition_layernorm_combine(dim, d, false));

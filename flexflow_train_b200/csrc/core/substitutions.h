@@ -103,6 +103,8 @@ Substitution create_partition_binary_combine(OpType op, int dim, int degree);
 Substitution create_partition_softmax_combine(int softmax_dim, int dim, int degree);
 Substitution create_partition_layernorm_combine(int dim, int degree, bool affine);
 Substitution create_partition_embedding_combine(int dim, int degree);
+Substitution create_partition_batchnorm_combine(int dim, int degree, bool affine);
+Substitution create_partition_concat_combine(int num_inputs, int axis, int dim, int degree);
 Substitution create_fuse_linear_activation(const std::string &activation);
 Substitution create_cancel_combine_repartition();   // Combine(d,k) -> Repartition(d,k)  ==> identity
 Substitution create_cancel_repartition_combine();

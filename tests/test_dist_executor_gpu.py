@@ -81,3 +81,70 @@ def test_two_rank_training_matches_single_gpu(which):
         for x, y in zip(out["single"], out["multi"]):
             assert abs(x - y) < 3e-2 * abs(x), out
         assert out["multi"][-1] < out["multi"][0]
+
+
+def _train_graph(ctx, build, loss, inputs_fn, steps=4):
+    """Single-GPU vs data-parallel training of an arbitrary graph on the same global batch."""
+    from flexflow_train_b200.compiler import strategy as S
+    from flexflow_train_b200.parallel.dist_executor import DistExecutable
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+
+    cg = build()
+    pcg = S.data_parallel_strategy(cg, ctx.world_size)
+    opt = OptimizerConfig(kind="sgd", lr=0.05, momentum=0.9)
+    cfg = dict(compute_dtype="bf16", seed=2, optimizer=opt, device=f"cuda:{ctx.rank}", loss=loss)
+    single = Executable(cg, ExecConfig(**cfg))
+    multi = DistExecutable(pcg, ExecConfig(**cfg), ctx)
+    torch.manual_seed(0)
+    inputs, labels = inputs_fn(ctx.device)
+    a, b = [], []
+    for _ in range(steps):
+        single.train_step(inputs, labels)
+        a.append(single.mean_loss())
+        multi.train_step(inputs, labels)
+        b.append(multi.mean_loss())
+    ctx.check_status()
+    return {"single": a, "multi": b, "parallelism": multi.parallelism, "nccl_ops": len(multi.nccl_ops)}
+
+
+def w_conv_dp(ctx):
+    from flexflow_train_b200 import _ffcore as core
+
+    def build():
+        b = core.GraphBuilder()
+        x = b.create_input([8, 3, 20, 20], name="input")
+        t = b.conv2d(x, 16, 3, 3, 1, 1, 1, 1, activation="RELU", name="c1")
+        t = b.pool2d(t, 2, 2, 2, 2, 0, 0, pool_type="MAX", name="p1")
+        l = b.conv2d(t, 16, 1, 1, name="b1")
+        r = b.conv2d(t, 8, 3, 3, 1, 1, 1, 1, activation="RELU", name="b2")
+        t = b.concat([l, r], 1, name="cat")
+        t = b.pool2d(t, 10, 10, 1, 1, 0, 0, pool_type="AVG", name="gap")
+        b.softmax(b.dense(b.flat(t, name="flat"), 10, name="fc"), name="out_prob")
+        return b.graph
+    return _train_graph(ctx, build, "sparse_categorical_crossentropy",
+                        lambda dev: ({"input": torch.randn(8, 3, 20, 20, device=dev)}, torch.randint(0, 10, (8,), dtype=torch.int32, device=dev)))
+
+
+def w_dlrm_dp(ctx):
+    from flexflow_train_b200 import _ffcore as core
+
+    cfg = {"batch_size": 64, "embedding_dim": 16, "embedding_bag_size": 1, "embedding_size": [500, 300], "dense_arch_layer_sizes": [13, 32, 16],
+           "over_arch_layer_sizes": [48, 32, 1], "arch_interaction_op": "CAT", "final_activation": "SIGMOID"}
+
+    def data(dev):
+        ins = {"dense": torch.randn(64, 13, device=dev), "sparse0": torch.randint(0, 500, (64, 1), device=dev),
+               "sparse1": torch.randint(0, 300, (64, 1), device=dev)}
+        return ins, torch.rand(64, 1, device=dev)
+    return _train_graph(ctx, lambda: core.build_model("dlrm", cfg), "mean_squared_error_avg_reduce", data)
+
+
+@pytest.mark.parametrize("which", ["conv_dp", "dlrm_dp"])
+def test_data_parallel_convolution_stack_and_dlrm_match_single_gpu(which):
+    """Batch norm is left out of the convolution stack on purpose: under data parallelism it normalises with the
+    statistics of the local samples, which is not the single-GPU function."""
+    res = _run("test_dist_executor_gpu:w_" + which)
+    for r, out in res.items():
+        assert "dp" in out["parallelism"], out
+        for x, y in zip(out["single"], out["multi"]):
+            assert abs(x - y) < 5e-2 * abs(x) + 1e-3, out
+        assert out["multi"][-1] < out["multi"][0], out

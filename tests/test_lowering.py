@@ -70,3 +70,61 @@ def test_shard_expansion_and_machine_slicing_on_a_mapped_pcg():
     # all-reduced; nothing else moves
     moved = [i for i in inv if i["task"] == "COPY"]
     assert all(i["op_type"] in ("REPARTITION", "COMBINE", "REPLICATE", "REDUCTION", "COPY") for i in moved)
+
+
+def test_task_argument_accessor_runs_a_lowered_linear_layer_forward_backward_update():
+    """Task bodies written against the accessor execute the lowered invocations of one Linear layer + loss + SGD
+    and reproduce a plain PyTorch step."""
+    import torch
+
+    from flexflow_train_b200.runtime.task_accessor import TaskArgumentAccessor, run_invocations, value_key
+
+    b = core.GraphBuilder()
+    x = b.create_input([4, 6], name="x")
+    y = b.dense(x, 3, use_bias=True, name="fc")
+    g = b.graph
+    nodes = {n["id"]: n for n in g.nodes()}
+    inv = L.lower(g, logit=tuple(y), loss="mean_squared_error_avg_reduce", optimizer={"type": "sgd", "lr": 0.1})
+    torch.manual_seed(0)
+    xin, w0, b0, target = torch.randn(4, 6), torch.randn(3, 6), torch.randn(3), torch.randn(4, 3)
+    table = {}
+
+    def fwd_source(acc: TaskArgumentAccessor):
+        data = {"x": xin, "fc.weight": w0.clone(), "fc.bias": b0.clone()}[acc.name]
+        acc.set_output(data)
+
+    def fwd_linear(acc):
+        acc.set_output(acc.get_tensor("INPUT") @ acc.get_tensor("WEIGHT").t() + acc.get_tensor("BIAS"))
+
+    def loss(acc):
+        pred = acc.get_tensor("INPUT") if acc.has("INPUT") else list(acc.tensors.values())[-1]
+        acc.set_output(2.0 * (pred - target) / pred.numel(), acc.invocation["outputs"][0]["slot"], "GRAD")
+
+    def bwd_linear(acc):
+        dy = acc.get_tensor("OUTPUT", "GRAD")
+        for v in acc.invocation["outputs"]:
+            slot = v.get("as", v["slot"])
+            src = nodes[v["node"]]["name"]
+            if src == "fc.weight":
+                acc.tensors[value_key(v)] = dy.t() @ acc.get_tensor("INPUT")
+            elif src == "fc.bias":
+                acc.tensors[value_key(v)] = dy.sum(0)
+            else:
+                acc.tensors[value_key(v)] = dy @ acc.get_tensor("WEIGHT")
+
+    def upd(acc):
+        ins = acc.invocation["inputs"]
+        w = acc.tensors[value_key(next(v for v in ins if v["role"] == "FWD"))]
+        gr = acc.tensors[value_key(next(v for v in ins if v["role"] == "GRAD"))]
+        w -= 0.1 * gr
+
+    bodies = {("FWD", "INPUT"): fwd_source, ("FWD", "WEIGHT"): fwd_source, ("FWD", "LINEAR"): fwd_linear, ("LOSS", "*"): loss,
+              ("BWD", "LINEAR"): bwd_linear, ("UPD", "*"): upd}
+    run_invocations(inv, bodies, table, op_attrs_of=lambda n: nodes[n]["attrs"])
+    wt = w0.clone().requires_grad_(True)
+    bt = b0.clone().requires_grad_(True)
+    ((xin @ wt.t() + bt - target) ** 2).mean().backward()
+    got_w = next(t for k, t in table.items() if nodes[k[0]]["name"] == "fc.weight" and k[2] == "FWD")
+    got_b = next(t for k, t in table.items() if nodes[k[0]]["name"] == "fc.bias" and k[2] == "FWD")
+    assert torch.allclose(got_w, w0 - 0.1 * wt.grad, atol=1e-6)
+    assert torch.allclose(got_b, b0 - 0.1 * bt.grad, atol=1e-6)

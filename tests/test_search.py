@@ -124,3 +124,22 @@ def test_optimize_picks_data_parallel_for_large_transformer_and_exports():
     for n in tp.nodes():
         k[n["type"]] = k.get(n["type"], 0) + 1
     assert k["REDUCTION"] == 4 and k["REPLICATE"] >= 4  # attention + row-parallel FFN per layer
+
+
+def test_data_parallel_strategy_shards_every_operator_of_every_model_family():
+    """The sample-dim rules cover convolution stacks (conv, batch norm, pooling, concat, flat), recommendation
+    models (embedding, cast, concat) and MLPs: no operator is left replicated, and activations cross ranks only at
+    the model's inputs and outputs."""
+    for name, cfg in (("inception_v3", {"batch_size": 8}), ("dlrm", {"batch_size": 16}), ("candle_uno", {"batch_size": 8}),
+                      ("bert", {"batch_size": 4, "token_ids": True, "num_encoder_layers": 2})):
+        cg = c.build_model(name, cfg)
+        g = S.data_parallel_strategy(cg, 2)
+        nodes = {n["id"]: n for n in g.nodes()}
+        replicated = [n["type"] for n in g.nodes() if not c.is_parallel_op(n["type"]) and n["type"] not in ("WEIGHT", "INPUT")
+                      and n["outputs"][0][1].total_degree == 1]
+        assert replicated == [], (name, replicated)
+        n_inputs = sum(1 for n in cg.nodes() if n["type"] == "INPUT")
+        n_sinks = len([v for v in cg.sink_values() if nodes.get(v[0], {"type": ""})["type"] not in ("WEIGHT", "INPUT")])
+        moves = [n for n in g.nodes() if n["type"] in ("REPARTITION", "COMBINE")
+                 and nodes[n["inputs"][0][1][0]]["type"] != "WEIGHT" and not c.is_parallel_op(nodes[n["inputs"][0][1][0]]["type"])]
+        assert len(moves) <= n_inputs + max(n_sinks, 2), (name, len(moves))
