@@ -395,17 +395,18 @@ FFK_API long long ffk_bias_act_bwd_scratch(int rows, int cols) {
 }
 // dz = dy * act'(saved); dbias (+)= column sums of dz.  dz may alias dy or be null
 // (bias gradient only); dbias may be null.  `partial` is caller-provided scratch.
-FFK_API int ffk_bias_act_bwd(const void *dy, const void *saved, void *dz, void *dbias, float *partial, int rows,
-                             int cols, int act, int dt, int accumulate, cudaStream_t st) {
+static int bias_act_bwd_impl(const void *dy, const void *saved, void *dz, void *dbias, float *partial, int rows, int cols, int act, int dt,
+                             int accumulate, float drop_p, unsigned long long drop_salt, const void *drop_seed_ptr, cudaStream_t st) {
   if (rows <= 0 || cols <= 0) return 0;
   int gy = rows / 64; if (gy < 1) gy = 1; if (gy > 64) gy = 64;
   if (dt == DT_BF16 && cols % 8 == 0 && (((uintptr_t)dy | (uintptr_t)saved | (uintptr_t)dz) & 15) == 0) {
     dim3 vgrid((cols + 255) / 256, gy), vblock(32, 8);
     vec::bias_act_bwd_vec_kernel<<<vgrid, vblock, 0, st>>>((const bf16 *)dy, (const bf16 *)saved, (bf16 *)dz, dbias ? partial : nullptr, rows,
-                                                          cols, act);
+                                                          cols, act, drop_p, drop_salt, (const unsigned long long *)drop_seed_ptr);
     if (dbias) colsum_finish_kernel<bf16><<<(cols + 255) / 256, 256, 0, st>>>(partial, gy, cols, (bf16 *)dbias, accumulate);
     return (int)cudaGetLastError();
   }
+  if (drop_p > 0.f) return -2;  // the fused-dropout form exists for the 16-byte vector path only
   dim3 grid((cols + 31) / 32, gy), block(32, 8);
   DISPATCH_FLOAT(dt, {
     bias_act_bwd_kernel<T><<<grid, block, 0, st>>>((const T *)dy, (const T *)saved, (T *)dz, dbias ? partial : nullptr,
@@ -413,4 +414,14 @@ FFK_API int ffk_bias_act_bwd(const void *dy, const void *saved, void *dz, void *
     if (dbias) colsum_finish_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(partial, gy, cols, (T *)dbias, accumulate);
   });
   return (int)cudaGetLastError();
+}
+FFK_API int ffk_bias_act_bwd(const void *dy, const void *saved, void *dz, void *dbias, float *partial, int rows,
+                             int cols, int act, int dt, int accumulate, cudaStream_t st) {
+  return bias_act_bwd_impl(dy, saved, dz, dbias, partial, rows, cols, act, dt, accumulate, 0.f, 0ull, nullptr, st);
+}
+// Same, with the gradient first taken back through a dropout applied after the activation (bf16, cols % 8 == 0).
+FFK_API int ffk_bias_act_dropout_bwd(const void *dy, const void *saved, void *dz, void *dbias, float *partial, int rows, int cols, int act,
+                                     int dt, int accumulate, float drop_p, unsigned long long drop_salt, const void *drop_seed_ptr,
+                                     cudaStream_t st) {
+  return bias_act_bwd_impl(dy, saved, dz, dbias, partial, rows, cols, act, dt, accumulate, drop_p, drop_salt, drop_seed_ptr, st);
 }

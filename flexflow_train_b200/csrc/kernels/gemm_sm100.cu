@@ -53,6 +53,13 @@ struct GemmArgs {
   // items are (tile, split) pairs and every split adds its partial into the fp32 output with atomics.
   int split_k;
   int kb_per_split;
+  // Dropout fused into the epilogue (after the activation): element (row, col) is kept when the counter-based
+  // generator says so for flat index row * ldc + col -- the same function of (seed, index) as the stand-alone
+  // dropout kernel, so backward regenerates the mask.  drop_seed_ptr (device memory) holds the per-step seed.
+  float drop_p;
+  float drop_scale;
+  unsigned long long drop_salt;
+  const unsigned long long *drop_seed_ptr;
   int *err;
   // --- fused collectives (all optional) ---
   // Scatter epilogue (GEMM -> reduce-scatter): when scatter_rows > 0 the output rows are split into blocks of
@@ -458,7 +465,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     const uint32_t wr_base = smem_u32(stg + lane * 32);
     const uint32_t rd_even = smem_u32(stg + rsub * 32 + ((unit ^ rsub) << 2));            // rows with (rr & 7) == rsub
     const uint32_t rd_odd = smem_u32(stg + (rsub + 4) * 32 + ((unit ^ (rsub + 4)) << 2));  // rows with (rr & 7) == rsub + 4
-    const bool simple = p.split_k == 1 && !p.out_fp32 && !p.accumulate && !p.C2 && !p.addend && !p.aux_fp32 &&
+    const bool simple = p.split_k == 1 && p.drop_p == 0.f && !p.out_fp32 && !p.accumulate && !p.C2 && !p.addend && !p.aux_fp32 &&
                         (p.act == ACT_NONE || p.act == ACT_RELU) && (p.ldc % 4 == 0) && (((uintptr_t)p.C) & 7) == 0 &&
                         (p.c_sh % 4 == 0) && (p.c_sb % 4 == 0);
     const float relu_floor = p.act == ACT_RELU ? 0.f : -INFINITY;
@@ -545,6 +552,17 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
             if (p.act != ACT_NONE) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) v[j] = act_fwd(v[j], p.act);
+            }
+            if (p.drop_p > 0.f) {
+              const unsigned long long seed = p.drop_seed_ptr ? p.drop_salt * 0x9E3779B97F4A7C15ull + *p.drop_seed_ptr : p.drop_salt;
+              const uint32_t thr = ffk_drop_threshold(p.drop_p);
+              if (vec4 && (coff & 3) == 0) {
+                const uint32_t keep = ffk_keep4(seed, (unsigned long long)(coff >> 2), thr);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = ((keep >> j) & 1u) ? v[j] * p.drop_scale : 0.f;
+              } else {
+                for (int j = 0; j < 4; ++j) v[j] = ffk_keep(seed, (unsigned long long)(coff + j), thr) ? v[j] * p.drop_scale : 0.f;
+              }
             }
             if (p.addend) {
               const long long aoff = a_base + (long long)row * p.ld_add + col;
@@ -798,6 +816,10 @@ struct FfkGemmDesc {
   void *push_sync;
   int push_world;
   int push_rank;
+  // dropout in the epilogue (see GemmArgs); drop_p = 0 disables it
+  float drop_p;
+  unsigned long long drop_salt;
+  const void *drop_seed_ptr;
 };
 
 // Returns 0 on success, a CUDA/driver error code otherwise, -2 for an
@@ -816,8 +838,8 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
-    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr;
-    if (d->scatter_rows || d->gate_flags || d->push_src) return -2;  // the fused-collective paths need TMA-addressable operands
+    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr; a.drop_p = 0.f;
+    if (d->scatter_rows || d->gate_flags || d->push_src || d->drop_p > 0.f) return -2;  // the fused-collective paths need TMA-addressable operands
     SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
     dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
     if (es == 2) gemm_simt_kernel<bf16><<<grid, block, 0, stream>>>(o, a);
@@ -855,6 +877,9 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   a.gate_rows = d->gate_rows; a.mb_rotate = d->mb_rotate;
   if (a.scatter_rows && (a.scatter_rows % BM != 0 || a.nh * a.nb != 1)) return -2;
   if (a.gate_flags && (a.gate_rows % BM != 0 || a.nh * a.nb != 1 || d->a_mn)) return -2;
+  a.drop_p = d->drop_p; a.drop_scale = d->drop_p > 0.f ? 1.0f / (1.0f - d->drop_p) : 1.f; a.drop_salt = d->drop_salt;
+  a.drop_seed_ptr = (const unsigned long long *)d->drop_seed_ptr;
+  if (a.drop_p > 0.f && (a.nh * a.nb != 1 || d->out_fp32 || d->accumulate)) return -2;
   a.push_src = (const uint4 *)d->push_src;
   a.push_nvec = d->push_bytes / 16; a.push_off = d->push_dst_offset / 16;
   for (int i = 0; i < 8; ++i) { a.push_dst[i] = d->push_dst[i]; a.push_flag[i] = (unsigned long long *)d->push_flag[i]; }

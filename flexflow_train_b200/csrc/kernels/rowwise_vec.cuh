@@ -176,7 +176,10 @@ template <int VPT>
 __global__ void layernorm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x, const bf16 *__restrict__ gamma,
                                          const float *__restrict__ mean, const float *__restrict__ rstd, bf16 *__restrict__ dx,
                                          bf16 *__restrict__ dx2, float *__restrict__ partial, int rows, int cols, int acc1, int acc2) {
-  __shared__ float red[32];
+  // the two row sums are reduced together through a double-buffered slot: one barrier per row
+  __shared__ float2 red2[2][32];
+  int parity = 0;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   float gm[VPT][8], dg[VPT][8], db[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -204,8 +207,14 @@ __global__ void layernorm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16
         s2 += g[i][j] * xh[i][j];
       }
     }
-    const float m1 = block_sum(s1, red) / cols;
-    const float m2 = block_sum(s2, red) / cols;
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) red2[parity][wid] = make_float2(s1, s2);
+    __syncthreads();
+    float t1 = 0.f, t2 = 0.f;
+    for (int k = 0; k < nw; ++k) { float2 q = red2[parity][k]; t1 += q.x; t2 += q.y; }
+    parity ^= 1;
+    const float m1 = t1 / cols, m2 = t2 / cols;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
@@ -246,8 +255,14 @@ __global__ void layernorm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16
 // ---------------------------------------------------------------- bias / activation backward
 // block (32, 8): thread (tx, ty) owns columns [blockIdx.x*256 + tx*8, +8) of rows ty, ty+8*gridDim.y, ...
 // dz = dy * act'(saved); partial[blockIdx.y][col] = column sums over this block's rows.
+// With drop_p > 0 the incoming gradient first goes back through the dropout that the forward GEMM epilogue
+// applied after the activation (mask regenerated from (seed, flat index)).
 static __global__ void bias_act_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ saved, bf16 *__restrict__ dz,
-                                        float *__restrict__ partial, int rows, int cols, int act) {
+                                        float *__restrict__ partial, int rows, int cols, int act, float drop_p,
+                                        unsigned long long drop_salt, const unsigned long long *drop_seed_ptr) {
+  const unsigned long long dseed = drop_seed_ptr ? drop_salt * 0x9E3779B97F4A7C15ull + *drop_seed_ptr : drop_salt;
+  const uint32_t dthr = ffk_drop_threshold(drop_p);
+  const float dscale = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   __shared__ float red[8][32][9];
   const int c0 = blockIdx.x * 256 + threadIdx.x * 8;
   float acc[8];
@@ -258,6 +273,14 @@ static __global__ void bias_act_bwd_vec_kernel(const bf16 *__restrict__ dy, cons
       long long off = (long long)r * cols + c0;
       float g[8];
       ld8(dy + off, g);
+      if (drop_p > 0.f) {
+        const uint32_t k0 = ffk_keep4(dseed, (unsigned long long)(off >> 2), dthr), k1 = ffk_keep4(dseed, (unsigned long long)(off >> 2) + 1, dthr);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          g[j] = ((k0 >> j) & 1u) ? g[j] * dscale : 0.f;
+          g[4 + j] = ((k1 >> j) & 1u) ? g[4 + j] * dscale : 0.f;
+        }
+      }
       if (act != ACT_NONE) {
         float sv[8];
         ld8(saved + off, sv);

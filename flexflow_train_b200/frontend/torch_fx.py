@@ -128,9 +128,13 @@ class PyTorchModel:
     # ---- stage 1
     def trace(self):
         if self._traced is None:
+            hf_trace = None
             if self.is_hf_model:
-                from transformers.utils.fx import symbolic_trace as hf_trace
-
+                try:  # the HuggingFace tracer (concrete shapes for control flow) was removed from recent releases
+                    from transformers.utils.fx import symbolic_trace as hf_trace
+                except ImportError:
+                    hf_trace = None
+            if hf_trace is not None:
                 self._traced = hf_trace(self.model, input_names=self.input_names)
             else:
                 import torch.fx

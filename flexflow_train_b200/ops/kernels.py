@@ -58,6 +58,8 @@ class GemmDesc(ctypes.Structure):
         # in-kernel push of this rank's shard to the peers' staging buffers (all-gather -> GEMM)
         ("push_src", c_void_p), ("push_bytes", c_longlong), ("push_dst_offset", c_longlong), ("push_dst", c_void_p * 8),
         ("push_flag", c_void_p * 8), ("push_sync", c_void_p), ("push_world", c_int), ("push_rank", c_int),
+        # dropout applied by the epilogue after the activation
+        ("drop_p", c_float), ("drop_salt", c_ulonglong), ("drop_seed_ptr", c_void_p),
     ]
 
 
@@ -160,7 +162,7 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
              a_sh=0, a_sb=0, b_sh=0, b_sb=0, c_sh=0, c_sb=0, C2=None, bias=None, addend=None,
              ld_add=0, add_sh=0, add_sb=0, alpha=1.0, act=0, out_fp32=False, accumulate=False,
              bn=0, max_ctas=0, scatter=None, scatter_rows=0, scatter_src=0, gate_flags=None, gate_sync=None,
-             gate_rows=0, mb_rotate=0, push=None):
+             gate_rows=0, mb_rotate=0, push=None, dropout=None):
     """D = epilogue(alpha * A[M,K] . B[N,K]^T) on raw pointers; see gemm_sm100.cu.
 
     scatter / scatter_rows / scatter_src: write each output tile into the owning rank's staging buffer
@@ -171,6 +173,9 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
                  C, ldc, c_sh, c_sb, C2, bias, addend, ld_add, add_sh, add_sb, alpha, act, int(out_fp32),
                  int(accumulate), bn, max_ctas, sc, scatter_rows, scatter_src, gate_flags, gate_sync, gate_rows,
                  mb_rotate)
+    if dropout is not None:  # (p, salt, seed tensor or None)
+        d.drop_p, d.drop_salt = float(dropout[0]), int(dropout[1]) & (2**64 - 1)
+        d.drop_seed_ptr = None if dropout[2] is None else dropout[2].data_ptr()
     if push is not None:  # dict(src, nbytes, dst_offset, dst=[peer ptrs], flag=[peer flag ptrs], sync, world, rank)
         d.push_src, d.push_bytes, d.push_dst_offset = push["src"], push["nbytes"], push["dst_offset"]
         d.push_dst = (c_void_p * 8)(*([int(x) for x in push["dst"]] + [None] * (8 - len(push["dst"]))))
@@ -192,8 +197,9 @@ def _es(t):
 
 
 def matmul_nt(a, b, out=None, *, bias=None, act=None, addend=None, pre_act_out=None, alpha=1.0,
-              accumulate=False, out_dtype=None, bn=0):
-    """out[M,N] = a[M,K] @ b[N,K]^T (+bias, activation, +addend).  Linear forward."""
+              accumulate=False, out_dtype=None, bn=0, dropout=None):
+    """out[M,N] = a[M,K] @ b[N,K]^T (+bias, activation, dropout, +addend).  Linear forward.
+    dropout = (p, salt, seed_tensor): applied by the epilogue after the activation."""
     M, K = a.shape
     N = b.shape[0]
     out = _gemm_out(out, M, N, a, out_dtype)
@@ -201,7 +207,7 @@ def matmul_nt(a, b, out=None, *, bias=None, act=None, addend=None, pre_act_out=N
     gemm_raw(M=M, N=N, K=K, A=a.data_ptr(), lda=K, B=b.data_ptr(), ldb=K, C=out.data_ptr(), ldc=N,
              es=_es(a), C2=_p(pre_act_out), bias=_p(bias), addend=_p(addend), ld_add=N, alpha=alpha,
              act=ACT_CODES[act] if not isinstance(act, int) else act, out_fp32=out.dtype == torch.float32,
-             accumulate=accumulate, bn=bn)
+             accumulate=accumulate, bn=bn, dropout=dropout)
     return out
 
 
@@ -307,10 +313,22 @@ def bias_act_bwd_scratch(rows, cols) -> int:
     return lib().ffk_bias_act_bwd_scratch(rows, cols)
 
 
-def bias_act_bwd(dy, saved, dz, dbias, scratch, act, accumulate=False):
-    """dz = dy * act'(saved); dbias (+)= column sums of dz."""
+def bias_act_bwd(dy, saved, dz, dbias, scratch, act, accumulate=False, dropout=None):
+    """dz = dy * act'(saved); dbias (+)= column sums of dz.  dropout = (p, salt, seed_tensor): dy first goes back
+    through the dropout that the forward GEMM epilogue applied after the activation."""
     rows, cols = dy.shape
     _cuda_contig(dy, saved, dz, dbias, scratch)
+    if dropout is not None and dropout[0] > 0:
+        l = lib()
+        if not getattr(l, "_bad_declared", False):
+            l.ffk_bias_act_dropout_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                   c_float, c_ulonglong, c_void_p, c_void_p]
+            l.ffk_bias_act_dropout_bwd.restype = c_int
+            l._bad_declared = True
+        _check(l.ffk_bias_act_dropout_bwd(dy.data_ptr(), _p(saved), _p(dz), _p(dbias), _p(scratch), rows, cols,
+                                          ACT_CODES[act] if not isinstance(act, int) else act, _dt(dy), int(accumulate), float(dropout[0]),
+                                          int(dropout[1]) & (2**64 - 1), _p(dropout[2]), _stream()), "ffk_bias_act_dropout_bwd")
+        return
     _check(lib().ffk_bias_act_bwd(dy.data_ptr(), _p(saved), _p(dz), _p(dbias), _p(scratch), rows, cols,
                                   ACT_CODES[act] if not isinstance(act, int) else act, _dt(dy), int(accumulate),
                                   _stream()), "ffk_bias_act_bwd")

@@ -208,8 +208,8 @@ class FuseIn:
         full = [int(v) for v in dict(combine.outputs)["OUTPUT"].piece_sizes]
         return self.ag.gathered_t.view(full)
 
-    def gemm(self, w, out, bias=None, act=None, pre_act_out=None):
-        self.ag(self.combine.x().view(self.rows_local, self.k), w, out, bias=bias, act=act, pre_act_out=pre_act_out)
+    def gemm(self, w, out, bias=None, act=None, pre_act_out=None, dropout=None):
+        self.ag(self.combine.x().view(self.rows_local, self.k), w, out, bias=bias, act=act, pre_act_out=pre_act_out, dropout=dropout)
 
     def grad_gemm(self, dy, w, accumulate: bool):
         """d(shard) (+)= reduce_scatter(dy @ w) with w [N_local, K] used as the [k, n] operand."""

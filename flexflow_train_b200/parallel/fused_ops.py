@@ -113,7 +113,7 @@ class AllGatherGemm:
         self.sync_push, self.sync_gate, self.sync_bar = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
 
     def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, act=None, pre_act_out=None,
-                 w_kn: bool = False, accumulate: bool = False):
+                 w_kn: bool = False, accumulate: bool = False, dropout=None):
         """`w` is [N, K] or, with ``w_kn``, [K, N].  After the call ``gathered_t`` holds the gathered operand
         (all ranks' row shards in rank order), which backward passes reuse."""
         ctx = self.ctx
@@ -132,7 +132,7 @@ class AllGatherGemm:
                    act=K.ACT_CODES[act] if not isinstance(act, int) else act,
                    C2=None if pre_act_out is None else pre_act_out.data_ptr(),
                    gate_flags=ctx.flags.local_ptr + self.flag_base * 8, gate_sync=self.sync_gate.data_ptr(),
-                   gate_rows=self.rows_local, mb_rotate=ctx.rank * (self.rows_local // 128),
+                   gate_rows=self.rows_local, mb_rotate=ctx.rank * (self.rows_local // 128), dropout=dropout,
                    push=dict(src=x_local.data_ptr(), nbytes=self.shard_bytes, dst_offset=ctx.rank * self.shard_bytes,
                              dst=self.gathered.peer_ptrs, flag=flag_ptrs, sync=self.sync_push.data_ptr(), world=W, rank=ctx.rank))
         return out

@@ -111,3 +111,23 @@ def test_tensor_shape_operators_match_oracle():
     assert rel(ex.loss_rows, rows_ref) < 2e-2
     for name, g_ in ex.named_gradients():
         assert rel(g_, grads_ref[name]) < 5e-2, (name, rel(g_, grads_ref[name]))
+
+
+def test_dropout_fused_into_the_linear_epilogue_trains_like_the_separate_kernel():
+    """Same salts and step seeds give the same masks, so the two executors follow the same trajectory."""
+    cfg = dict(SMALL_LM, dropout=0.2)
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32, device="cuda")
+    out = []
+    for fuse in (False, True):
+        g = core.build_model("transformer_lm", cfg)
+        ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, fuse_dropout=fuse, optimizer=OptimizerConfig(kind="adam", lr=1e-3)))
+        fused = sum(1 for op in ex.ops.values() if getattr(op, "fused_into", None) is not None)
+        assert (fused > 0) == fuse
+        ls = []
+        for _ in range(4):
+            ex.train_step({"input_ids": ids}, labels)
+            ls.append(ex.mean_loss())
+        out.append(ls)
+    for a, b in zip(*out):
+        assert abs(a - b) < 2e-2 * abs(a), out

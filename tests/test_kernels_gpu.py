@@ -267,3 +267,40 @@ def test_embedding():
     k.embedding_bwd(idx, dout, dt)
     ref = torch.zeros_like(table).index_add_(0, idx.reshape(-1), dout.reshape(-1, 64))
     assert torch.allclose(dt, ref, atol=1e-4)
+
+
+def test_dropout_fused_into_gemm_epilogue_and_its_backward_use_the_standalone_mask(K=k):
+    """matmul_nt(..., dropout=) must draw exactly the mask of the stand-alone dropout kernel for the same
+    (salt, step seed), and bias_act_bwd(..., dropout=) must take the gradient back through that mask."""
+    torch.manual_seed(0)
+    m, n, k, p, salt = 512, 384, 256, 0.25, 0x1234567
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    seed = torch.tensor([987654321], dtype=torch.int64, device="cuda")
+    pre = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    fused = K.matmul_nt(x, w, bias=bias, act="gelu", pre_act_out=pre, dropout=(p, salt, seed))
+    plain = K.matmul_nt(x, w, bias=bias, act="gelu")
+    ref = torch.empty_like(plain)
+    K.dropout(plain, p, salt, out=ref, seed_tensor=seed)
+    assert torch.equal(fused == 0, ref == 0)                      # the same elements are dropped
+    live = plain != 0                                             # GELU is exactly 0 for very negative inputs
+    frac = float((fused[live] == 0).float().mean())
+    assert abs(frac - p) < 0.02
+    assert ((fused.float() - ref.float()).abs() <= 0.02 * ref.float().abs() + 1e-3).all()
+    # backward: dz = gelu'(pre) * dropout_mask(dy) / (1 - p); bias gradient = column sums
+    dy = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    scratch = torch.empty(K.bias_act_bwd_scratch(m, n), device="cuda")
+    dz, db = torch.empty_like(dy), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    K.bias_act_bwd(dy, pre, dz, db, scratch, "gelu", dropout=(p, salt, seed))
+    dmask = torch.empty_like(dy)
+    K.dropout(dy, p, salt, out=dmask, seed_tensor=seed)
+    dz2, db2 = torch.empty_like(dy), torch.empty_like(db)
+    K.bias_act_bwd(dmask, pre, dz2, db2, scratch, "gelu")
+    assert torch.equal(dz == 0, dz2 == 0)
+    assert rel(dz, dz2) < 1e-2 and rel(db, db2) < 2e-2
+    # a different step seed draws a different mask
+    seed2 = seed + 1
+    other = K.matmul_nt(x, w, bias=bias, act="gelu", dropout=(p, salt, seed2))
+    assert not torch.equal(other == 0, fused == 0)
+    assert K.gemm_last_error() == 0
