@@ -200,6 +200,65 @@ __global__ void softmax_ce_kernel(const T *__restrict__ logits, const L *__restr
   }
 }
 
+// bf16 rows with cols % 8 == 0: 16-byte accesses; one pass finds the row maximum and the sum of exponentials
+// together (online softmax), a second pass over the (cache-resident) row writes the gradient.
+template <typename L>
+__global__ void softmax_ce_vec_kernel(const bf16 *__restrict__ logits, const L *__restrict__ labels, bf16 *__restrict__ probs,
+                                      bf16 *__restrict__ dlogits, float *__restrict__ loss, int rows, int cols, float grad_scale) {
+  __shared__ float2 red[32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  const int nvec = cols >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const bf16 *px = logits + (long long)row * cols;
+    const long long label = (long long)labels[row];
+    float m = -INFINITY, s = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float v[8];
+      vec::ld8(px + i * 8, v);
+      float vm = v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) vm = fmaxf(vm, v[j]);
+      const float nm = fmaxf(m, vm);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += __expf(v[j] - nm);
+      s = s * __expf(m - nm) + acc;
+      m = nm;
+    }
+    // combine (m, s) pairs: warp, then block
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+      const float nm = fmaxf(m, om);
+      s = (nm == -INFINITY) ? 0.f : s * __expf(m - nm) + os * __expf(om - nm);
+      m = nm;
+    }
+    __syncthreads();  // the previous row's readers are done with `red`
+    if (lane == 0) red[wid] = make_float2(m, s);
+    __syncthreads();
+    float M = -INFINITY, S = 0.f;
+    for (int k = 0; k < nw; ++k) M = fmaxf(M, red[k].x);
+    for (int k = 0; k < nw; ++k) S += (red[k].x == -INFINITY) ? 0.f : red[k].y * __expf(red[k].x - M);
+    const float inv = 1.f / S;
+    const bool valid = label >= 0 && label < cols;
+    if (threadIdx.x == 0 && loss) loss[row] = valid ? (__logf(S) + M - bf2f(px[valid ? label : 0])) : 0.f;
+    if (probs || dlogits) {
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float v[8], g[8];
+        vec::ld8(px + i * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __expf(v[j] - M) * inv;
+        if (probs) vec::st8(probs + (long long)row * cols + i * 8, v);
+        if (dlogits) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = valid ? (v[j] - ((long long)(i * 8 + j) == label ? 1.f : 0.f)) * grad_scale : 0.f;
+          vec::st8(dlogits + (long long)row * cols + i * 8, g);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ loss gradients
 enum { LOSS_SPARSE_CCE = 0, LOSS_CCE = 1, LOSS_MSE_AVG = 2, LOSS_IDENTITY = 3, LOSS_MSE_SUM = 4 };
 // dlogit for losses whose input is already a probability / prediction tensor.
@@ -402,6 +461,17 @@ FFK_API int ffk_softmax_ce(const void *logits, const void *labels, void *probs, 
   if (rows <= 0) return 0;
   int threads = cols >= 4096 ? 1024 : 256;
   int grid = rows < 148 * 4 ? rows : 148 * 4;
+  if (dt == 1 && cols % 8 == 0 && (((uintptr_t)logits | (uintptr_t)probs | (uintptr_t)dlogits) & 15) == 0) {
+    int vthreads = cols >= 8192 ? 512 : 256;
+    int vgrid = rows < 148 * 8 ? rows : 148 * 8;
+    if (label_dt == 3)
+      softmax_ce_vec_kernel<long long><<<vgrid, vthreads, 0, st>>>((const bf16 *)logits, (const long long *)labels, (bf16 *)probs,
+                                                                   (bf16 *)dlogits, loss, rows, cols, grad_scale);
+    else
+      softmax_ce_vec_kernel<int><<<vgrid, vthreads, 0, st>>>((const bf16 *)logits, (const int *)labels, (bf16 *)probs, (bf16 *)dlogits, loss,
+                                                             rows, cols, grad_scale);
+    return (int)cudaGetLastError();
+  }
   DISPATCH_FLOAT(dt, {
     if (label_dt == 3)
       softmax_ce_kernel<T, long long><<<grid, threads, 0, st>>>((const T *)logits, (const long long *)labels,

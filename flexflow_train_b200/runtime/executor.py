@@ -61,6 +61,7 @@ class ExecConfig:
     # Transformer it costs more in the epilogue (which is on the GEMM's critical path) than the separate
     # bandwidth-bound dropout kernel it removes (343.8 vs 335.2 ms per step).
     fuse_dropout: bool = False
+    keep_dropped_probs: bool = True  # attention: keep dropout(P) for backward when device memory allows
 
 
 class _Buf:
@@ -379,7 +380,15 @@ class AttentionOp(OpImpl):
         self.bias_out = self.x("OUTPUT_BIAS") if ("OUTPUT_BIAS" in self.inputs and ex.use_bias(self, "OUTPUT_BIAS")) else None
         self.alpha = 1.0 / math.sqrt(kd)
         nbytes = self.probs.numel() * self.probs.element_size()
-        ex.need_big_scratch(nbytes, 2 if self.p_drop > 0 else 1)
+        # The dropped probabilities feed the P.V GEMM and, in backward, the dV GEMM.  Keeping them costs one
+        # score-sized tensor per layer and saves regenerating them (a read and a write of that tensor); it is
+        # done while plenty of device memory is free, otherwise they are rebuilt in a shared scratch buffer.
+        self.kept_p = None
+        if self.p_drop > 0 and ex.cfg.training and ex.on_gpu and ex.cfg.keep_dropped_probs:
+            free, _total = torch.cuda.mem_get_info(ex.device)
+            if free > 8 * nbytes + (40 << 30):
+                self.kept_p = torch.empty_like(self.probs)
+        ex.need_big_scratch(nbytes, 2 if (self.p_drop > 0 and self.kept_p is None) else 1)
         ex.need_scratch(4 * K.bias_act_bwd_scratch(self.B * self.Sq, max(self.ldqkv, self.embed)) if ex.on_gpu else 0)
         self.salt = ex.next_salt()
         self.es = 2
@@ -428,12 +437,13 @@ class AttentionOp(OpImpl):
         causal_q = Sq if self.ex.cfg.causal_attention else 0
         p = self.probs
         if self.p_drop > 0 and K.softmax_dropout_supported(self.probs):
-            p = self.ex.big_scratch(1, self.probs)  # probabilities and their dropped copy in one pass
+            # probabilities and their dropped copy in one pass
+            p = self.kept_p if self.kept_p is not None else self.ex.big_scratch(1, self.probs)
             K.softmax_dropout_fwd(self.probs, self.probs, p, self.p_drop, self.salt, self.ex.seed_tensor, causal_q=causal_q)
         else:
             K.softmax_fwd(self.probs, out=self.probs, causal_q=causal_q)
             if self.p_drop > 0:
-                p = self.ex.big_scratch(1, self.probs)
+                p = self.kept_p if self.kept_p is not None else self.ex.big_scratch(1, self.probs)
                 K.dropout(self.probs, self.p_drop, self.salt, out=p, seed_tensor=self.ex.seed_tensor)
         # ctx[b,sq,h,:] = p . v
         self._bg(Sq, vd, Sk, p, Sk, Sq * Sk, H * Sq * Sk, False, self.c_v, self.ldv, vd, Sk * self.ldv, True,
@@ -464,7 +474,9 @@ class AttentionOp(OpImpl):
         if self.fuse_out is None:
             K.matmul_nn(dy, self.wo, out=self.dctx)
         p = self.probs
-        if self.p_drop > 0:  # regenerate the dropped probabilities (mask is a function of the step seed)
+        if self.p_drop > 0 and self.kept_p is not None:
+            p = self.kept_p
+        elif self.p_drop > 0:  # regenerate the dropped probabilities (mask is a function of the step seed)
             p = ex.big_scratch(1, self.probs)
             K.dropout(self.probs, self.p_drop, self.salt, out=p, seed_tensor=ex.seed_tensor)
         dP = ex.big_scratch(0, self.probs)
