@@ -592,8 +592,22 @@ std::vector<Substitution> get_substitution_set(const MachineSpec &m, int max_dim
       for (int sd = 0; sd < max_dims; ++sd)
         if (sd != dim) r.push_back(create_partition_softmax_combine(sd, dim, d));
       if (dim == 0) {  // sample-dim rules of the convolution-stack and shape operators
-        for (OpType u : {OpType::POOL2D, OpType::FLAT, OpType::NOOP, OpType::ELU, OpType::EXP, OpType::SCALAR_MULTIPLY, OpType::SCALAR_ADD})
+        for (OpType u : {OpType::POOL2D, OpType::FLAT, OpType::NOOP, OpType::ELU, OpType::EXP, OpType::SCALAR_MULTIPLY, OpType::SCALAR_ADD,
+                         OpType::RESHAPE})  // (a Reshape that does not keep dim 0 fails shape inference and is skipped)
           r.push_back(create_partition_unary_combine(u, dim, d));
+        // Transpose with the sample dim left in place
+        for (int nd = 3; nd <= max_dims; ++nd) {
+          std::vector<int> perm(nd);
+          for (int i = 0; i < nd; ++i) perm[i] = i;
+          do {
+            Substitution t = create_partition_unary_combine(OpType::TRANSPOSE, dim, d);
+            std::string tag;
+            for (int v : perm) tag += std::to_string(v);
+            t.name = "partition_TRANSPOSE" + tag + "_combine" + sfx(dim, d);
+            t.pattern.nodes[0].constraints.push_back(attr_eq("permutation", Json::from_ints(std::vector<long long>(perm.begin(), perm.end()))));
+            r.push_back(t);
+          } while (std::next_permutation(perm.begin() + 1, perm.end()));
+        }
         r.push_back(create_partition_binary_combine(OpType::EW_SUB, dim, d));
         r.push_back(create_partition_binary_combine(OpType::BATCHMATMUL, dim, d));
         r.push_back(create_partition_batchnorm_combine(dim, d, true));
