@@ -60,6 +60,10 @@ struct GemmArgs {
   float drop_scale;
   unsigned long long drop_salt;
   const unsigned long long *drop_seed_ptr;
+  // Output through TMA stores (bf16 output, bias + ReLU/none only): each epilogue warp converts its 32 x 32 chunk
+  // into a swizzled bf16 tile in shared memory and one lane issues a bulk tensor store; rows and columns past the
+  // matrix edge are clipped by the tensor map.
+  int tma_store;
   int *err;
   // --- fused collectives (all optional) ---
   // Scatter epilogue (GEMM -> reduce-scatter): when scatter_rows > 0 the output rows are split into blocks of
@@ -215,7 +219,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (STAGE_BYTES <= 32768) ? 6 : (STAGE_BYTES <= 49152 ? 4 : 3);
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 8 * 32 * 32 * 4 /*epilogue staging*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/ + 8 * 32 * 32 * 4 /*epilogue staging*/;
   // K-major: one 8-row group is 8*128 B apart (SBO), LBO is the fixed 16 B.
   // MN-major: 8 k-rows of one 64-wide chunk are 128 B apart, 8-row groups are
   // 1024 B apart (SBO) and the next MN chunk starts BK*128 B later (LBO).
@@ -256,10 +260,21 @@ __device__ __forceinline__ void tile_coords(long long tile, const GemmArgs &p, i
   if (p.mb_rotate) mb = (mb + p.mb_rotate) % p.tiles_m;
 }
 
+__device__ __forceinline__ void tma_store_4d(uint32_t smem_src, const CUtensorMap *map, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(smem_src), "r"(x),
+               "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+
+// Output maps of the scatter epilogue: one per owning rank's staging buffer (peer memory).
+struct ScatterMaps {
+  CUtensorMap m[8];
+};
+
 template <int ES, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-                  const GemmArgs p) {
+                  const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ ScatterMaps smaps, const GemmArgs p) {
   using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -273,7 +288,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
   uint64_t *tmem_empty = bars + 2 * STAGES + 2;  // [2]
   uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
-  float *epi_stage = (float *)(smem + STAGES * Cfg::STAGE_BYTES + 256);  // 8 epilogue warps x 32x32 fp32
+  float *epi_stage = (float *)(smem + STAGES * Cfg::STAGE_BYTES + 512);  // 8 epilogue warps x 4 KB, 512-byte aligned (TMA store source)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -471,6 +486,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     const float relu_floor = p.act == ACT_RELU ? 0.f : -INFINITY;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t store_it = 0;  // TMA-store chunks issued by this warp (selects the staging buffer)
     bool ok = true;
     for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const long long tile = item % p.num_tiles;
@@ -494,6 +510,62 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * HALF_COLS);
       uint32_t r[32];
       tmem_ld32(t_base, r);
+      if (p.tma_store) {
+        // lane = row of this warp's 32-row quarter, r[j] = column c0 + j: the lane writes its row (32 bf16 = 64 B,
+        // as four 16-byte pieces at SWIZZLE_64B positions) and lane 0 stores the 32 x 32 tile
+        const uint32_t sbase = smem_u32(stg);
+        const bool bias_vec = p.bias && ((((uintptr_t)p.bias) & 15) == 0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
+          tmem_ld_wait();
+          const uint32_t buf = sbase + (store_it & 1u) * 2048u;
+          if (store_it >= 2) {  // the store issued two chunks ago has finished reading this buffer
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+          }
+          const int col = nb_ * BN + half * HALF_COLS + c0;
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            const int cq = col + qd * 8;
+            if (p.bias) {
+              if (bias_vec && cq + 8 <= p.N) {
+                uint4 u = *reinterpret_cast<const uint4 *>((const bf16 *)p.bias + cq);
+                float2 x0 = unpack_bf162(u.x), x1 = unpack_bf162(u.y), x2 = unpack_bf162(u.z), x3 = unpack_bf162(u.w);
+                b8[0] = x0.x; b8[1] = x0.y; b8[2] = x1.x; b8[3] = x1.y; b8[4] = x2.x; b8[5] = x2.y; b8[6] = x3.x; b8[7] = x3.y;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (cq + j < p.N) b8[j] = bf2f(((const bf16 *)p.bias)[cq + j]);
+              }
+            }
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = fmaxf(fmaf(__uint_as_float(r[qd * 8 + j]), p.alpha, b8[j]), relu_floor);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + (uint32_t)(lane * 64) + (uint32_t)((qd ^ ((lane >> 1) & 3)) << 4)),
+                         "r"(pack_bf162(v[0], v[1])), "r"(pack_bf162(v[2], v[3])), "r"(pack_bf162(v[4], v[5])), "r"(pack_bf162(v[6], v[7]))
+                         : "memory");
+          }
+          if (c0 + 32 < HALF_COLS) tmem_ld32(t_base + (uint32_t)(c0 + 32), r);  // overlaps the store below
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (p.scatter_rows) {  // the tile goes into slot scatter_src of its owner's stage (a peer's memory)
+              const int owner = (mb * BM) / p.scatter_rows;
+              tma_store_4d(buf, &smaps.m[owner], col, row0 + (p.scatter_src - owner) * p.scatter_rows, 0, 0);
+            } else {
+              tma_store_4d(buf, &tmapC, col, row0, bh, bb);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          ++store_it;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
         tmem_ld_wait();
@@ -610,6 +682,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    // every bulk store this warp issued must have completed before the CTA's shared memory goes away
+    if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -716,10 +790,27 @@ int make_operand_map(CUtensorMap *map, const void *ptr, int es, long long contig
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// Output map for the TMA-store epilogue: boxes of 32 rows x 32 bf16 columns (64 bytes, SWIZZLE_64B).
+int make_store_map(CUtensorMap *map, void *ptr, long long cols, long long rows, long long ld, int nh, long long sh, int nb, long long sb) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)nh, (cuuint64_t)nb};
+  long long sh_b = (nh > 1 ? sh : ld * rows) * 2, sb_b = (nb > 1 ? sb : (nh > 1 ? sh * nh : ld * rows)) * 2;
+  if (sh_b <= 0) sh_b = 16;
+  if (sb_b <= 0) sb_b = 16;
+  cuuint64_t strides[3] = {(cuuint64_t)(ld * 2), (cuuint64_t)sh_b, (cuuint64_t)sb_b};
+  cuuint32_t box[4] = {32, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 __device__ int g_gemm_err = 0;
 
 template <int ES, int BN, bool A_MN, bool B_MN>
-int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int max_ctas, cudaStream_t stream) {
+int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const ScatterMaps &sm, GemmArgs &args, int max_ctas,
+               cudaStream_t stream) {
   using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
   static bool attr_done = false;
   auto kern = gemm_sm100_kernel<ES, BN, A_MN, B_MN>;
@@ -751,17 +842,18 @@ int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int
   long long items = args.num_tiles * args.split_k;
   long long grid = items < max_ctas ? items : max_ctas;
   if (grid < 1) return 0;
-  kern<<<(unsigned)grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+  if (args.split_k > 1) args.tma_store = 0;
+  kern<<<(unsigned)grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, tc, sm, args);
   return (int)cudaGetLastError();
 }
 
 template <int ES, int BN>
-int launch_major(bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, GemmArgs &args, int max_ctas,
-                 cudaStream_t stream) {
-  if (!a_mn && !b_mn) return launch_cfg<ES, BN, false, false>(ta, tb, args, max_ctas, stream);
-  if (!a_mn && b_mn) return launch_cfg<ES, BN, false, true>(ta, tb, args, max_ctas, stream);
-  if (a_mn && !b_mn) return launch_cfg<ES, BN, true, false>(ta, tb, args, max_ctas, stream);
-  return launch_cfg<ES, BN, true, true>(ta, tb, args, max_ctas, stream);
+int launch_major(bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const ScatterMaps &sm,
+                 GemmArgs &args, int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_cfg<ES, BN, false, false>(ta, tb, tc, sm, args, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_cfg<ES, BN, false, true>(ta, tb, tc, sm, args, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_cfg<ES, BN, true, false>(ta, tb, tc, sm, args, max_ctas, stream);
+  return launch_cfg<ES, BN, true, true>(ta, tb, tc, sm, args, max_ctas, stream);
 }
 
 int sm_count() {
@@ -822,6 +914,13 @@ struct FfkGemmDesc {
   const void *drop_seed_ptr;
 };
 
+static int g_disable_tma_store = 0;
+static int g_disable_scatter_tma = 0;
+// Scatter epilogue (GEMM -> reduce-scatter) through TMA stores into the peers' stages (1) or per-lane stores (0).
+FFK_API void ffk_gemm_set_scatter_tma_store(int enabled) { g_disable_scatter_tma = enabled ? 0 : 1; }
+// Switches the TMA-store epilogue off (1) or on (0) process-wide; for A/B measurements.
+FFK_API void ffk_gemm_set_tma_store(int enabled) { g_disable_tma_store = enabled ? 0 : 1; }
+
 // Returns 0 on success, a CUDA/driver error code otherwise, -2 for an
 // argument the TMA path cannot express (unaligned base or stride).
 FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
@@ -838,7 +937,7 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.C2 = d->C2; a.bias = d->bias; a.addend = d->addend;
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
-    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr; a.drop_p = 0.f;
+    a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr; a.drop_p = 0.f; a.tma_store = 0;
     if (d->scatter_rows || d->gate_flags || d->push_src || d->drop_p > 0.f) return -2;  // the fused-collective paths need TMA-addressable operands
     SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
     dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
@@ -890,13 +989,32 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   cudaGetSymbolAddress(&errp, g_gemm_err);
   a.err = (int *)errp;
   int max_ctas = d->max_ctas > 0 ? d->max_ctas : sm_count();
+  // TMA-store epilogue for the plain bf16 case (bias + ReLU/none) when the output can be described by a tensor map
+  CUtensorMap tc = ta;
+  a.tma_store = 0;
+  static ScatterMaps sm_zero = {};
+  ScatterMaps sm = sm_zero;
+  const bool store_ok = es == 2 && !d->out_fp32 && !d->accumulate && !d->C2 && !d->addend && (d->act == ACT_NONE || d->act == ACT_RELU) &&
+                        d->drop_p == 0.f && (((uintptr_t)d->C) & 15) == 0 && (d->ldc * 2) % 16 == 0 &&
+                        (a.nh == 1 || (d->c_sh * 2) % 16 == 0) && (a.nb == 1 || (d->c_sb * 2) % 16 == 0) && !g_disable_tma_store;
+  if (store_ok && !d->scatter_rows) {
+    if (make_store_map(&tc, d->C, d->N, d->M, d->ldc, a.nh, d->c_sh, a.nb, d->c_sb) == 0) a.tma_store = 1;
+  } else if (store_ok && !g_disable_scatter_tma) {
+    // one map per owner: its stage is [world][scatter_rows][N]; M / scatter_rows owners
+    const int owners = (d->M + d->scatter_rows - 1) / d->scatter_rows;
+    bool ok = owners <= 8;
+    for (int o = 0; ok && o < owners; ++o)
+      ok = d->scatter[o] && (((uintptr_t)d->scatter[o]) & 15) == 0 &&
+           make_store_map(&sm.m[o], d->scatter[o], d->N, (long long)owners * d->scatter_rows, d->ldc, 1, 0, 1, 0) == 0;
+    if (ok) a.tma_store = 1;
+  }
   if (es == 2) {
-    if (bn == 256) return launch_major<2, 256>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
-    if (bn == 128) return launch_major<2, 128>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
-    return launch_major<2, 64>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+    if (bn == 256) return launch_major<2, 256>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
+    if (bn == 128) return launch_major<2, 128>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
+    return launch_major<2, 64>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
   } else {
-    if (bn == 128) return launch_major<4, 128>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
-    return launch_major<4, 64>(d->a_mn, d->b_mn, ta, tb, a, max_ctas, stream);
+    if (bn == 128) return launch_major<4, 128>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
+    return launch_major<4, 64>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
   }
 }
 

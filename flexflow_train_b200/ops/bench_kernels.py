@@ -36,7 +36,24 @@ def _time(fn, warmup, iters, flush):
     return total / iters
 
 
+def bench_gemm_batched(a):
+    """nb problems out[b] = x[b] @ w[b]^T, the shape of the attention score GEMM (short K, output-bound)."""
+    nb, m, n, k = a.batched, a.m, a.n, a.k
+    x = torch.randn(nb, m, k, device="cuda").to(torch.bfloat16)
+    w = torch.randn(nb, n, k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(nb, m, n, device="cuda", dtype=torch.bfloat16)
+
+    def run():
+        K.gemm_raw(M=m, N=n, K=k, A=x.data_ptr(), lda=k, a_sb=m * k, B=w.data_ptr(), ldb=k, b_sb=n * k, C=out.data_ptr(), ldc=n, c_sb=m * n, nb=nb)
+    ms = _time(run, a.warmup, a.iters, a.flush)
+    r = roofline(ms, flops=2.0 * nb * m * n * k, hbm_bytes=2.0 * nb * (m * k + n * k + m * n))
+    ref = _time(lambda: torch.bmm(x, w.transpose(1, 2), out=out), a.warmup, a.iters, a.flush) if a.compare else None
+    return {"op": "gemm_nt_bf16_batched", "batch": nb, "m": m, "n": n, "k": k, **r, "torch_bmm_ms": ref, "gemm_error": K.gemm_last_error()}
+
+
 def bench_gemm(a):
+    if a.batched:
+        return bench_gemm_batched(a)
     m, n, k = a.m, a.n, a.k
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
@@ -113,9 +130,16 @@ def main(argv=None):
     p.add_argument("--relu", action="store_true")
     p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
     p.add_argument("--flush", action="store_true", help="write a buffer larger than L2 between timed launches")
+    p.add_argument("--no-tma-store", action="store_true", help="GEMM epilogue through per-lane global stores instead of TMA stores")
+    p.add_argument("--tma-store", action="store_true", help="GEMM epilogue through TMA stores")
+    p.add_argument("--batched", type=int, default=0, help="gemm: run as a batch of this many [m, n, k] problems (attention-shaped)")
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--iters", type=int, default=10)
     a = p.parse_args(argv)
+    if a.no_tma_store:
+        K.lib().ffk_gemm_set_tma_store(0)
+    if a.tma_store:
+        K.lib().ffk_gemm_set_tma_store(1)
     print(json.dumps(OPS[a.op](a)))
 
 

@@ -76,6 +76,9 @@ def lib():
                 f"{_LIB_PATH} is missing: run `python build.py` (nvcc, sm_100a) before using the GPU path")
         _lib = ctypes.CDLL(_LIB_PATH)
         _declare(_lib)
+        # epilogue through TMA stores: FFK_TMA_STORE=1/0 overrides the library default
+        if os.environ.get("FFK_TMA_STORE") in ("0", "1"):
+            _lib.ffk_gemm_set_tma_store(int(os.environ["FFK_TMA_STORE"]))
     return _lib
 
 

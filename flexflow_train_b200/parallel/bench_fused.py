@@ -56,6 +56,7 @@ def main(argv=None):
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--only", default="f1,f2,f3,f4")
+    p.add_argument("--no-scatter-tma", action="store_true", help="F1: per-lane stores into the peers' stages instead of TMA stores")
     a = p.parse_args(argv)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -63,6 +64,9 @@ def main(argv=None):
     ctx = DistContext(rank, world, local)
     W, dev, bf = world, ctx.device, torch.bfloat16
     only = set(a.only.split(","))
+    if a.no_scatter_tma:
+        from ..ops import kernels as K
+        K.lib().ffk_gemm_set_scatter_tma_store(0)
     es = 2
 
     def emit(d):

@@ -131,3 +131,45 @@ def test_dropout_fused_into_the_linear_epilogue_trains_like_the_separate_kernel(
         out.append(ls)
     for a, b in zip(*out):
         assert abs(a - b) < 2e-2 * abs(a), out
+
+
+def test_run_model_cli_trains_checkpoints_and_resumes(tmp_path, capsys):
+    """The run-model tool end to end on one GPU: train, write checkpoints, resume from the newest one."""
+    from flexflow_train_b200.bin import run_model
+    from flexflow_train_b200.utils import checkpoint as ckpt
+
+    cfg = '{"num_features": 64, "sequence_length": 32, "batch_size": 4, "dim_feedforward": 128, "num_heads": 2, ' \
+          '"num_encoder_layers": 1, "num_decoder_layers": 1, "vocab_size": 64}'
+    args = ["--model", "transformer", "--model-config", cfg, "--iterations", "4", "-p", "2", "--checkpoint-dir", str(tmp_path),
+            "--checkpoint-every", "2", "--no-cuda-graph", "-ll:gpu", "1", "-ll:fsize", "14000"]
+    assert run_model.main(args) == 0
+    first = capsys.readouterr().out
+    assert "iter 0: loss" in first and "samples/s" in first
+    last = ckpt.latest(str(tmp_path))
+    assert last is not None and last.endswith("step00000004")
+    assert run_model.main(args + ["--resume"]) == 0
+    second = capsys.readouterr().out
+    assert "resumed from" in second and "at step 4" in second
+    assert ckpt.latest(str(tmp_path)).endswith("step00000008")
+
+
+def test_checkpoint_roundtrip_restores_training_state_on_gpu(tmp_path):
+    from flexflow_train_b200.utils import checkpoint as ckpt
+
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32, device="cuda")
+
+    def make():
+        return Executable(core.build_model("transformer_lm", SMALL_LM),
+                          ExecConfig(compute_dtype="bf16", seed=9, optimizer=OptimizerConfig(kind="adam", lr=1e-3)))
+    a = make()
+    for _ in range(3):
+        a.train_step({"input_ids": ids}, labels)
+    path = ckpt.save(str(tmp_path), a)
+    a.train_step({"input_ids": ids}, labels)
+    want = a.mean_loss()
+    b = make()
+    meta = ckpt.load(path, b)
+    assert meta["step"] == 3 and b.step_count == 3
+    b.train_step({"input_ids": ids}, labels)
+    assert abs(b.mean_loss() - want) < 1e-3 * abs(want)
