@@ -62,6 +62,13 @@ class ExecConfig:
     # bandwidth-bound dropout kernel it removes (343.8 vs 335.2 ms per step).
     fuse_dropout: bool = False
     keep_dropped_probs: bool = True  # attention: keep dropout(P) for backward when device memory allows
+    # Attention core in blocks: scores, probabilities and their gradients of a few batch elements (or head groups)
+    # at a time live in small reused buffers and backward recomputes the probabilities of a block, so no
+    # B x H x S x S tensor is ever stored (saves 2 such tensors per layer; 48 GB on the large Transformer).
+    # Value: target bytes of one block's score tensor; 0 = off (whole-batch kernels, probabilities saved), which
+    # is faster when the memory is there: 329.9 vs 371.8 ms per step on the large Transformer with 32 MB blocks --
+    # many small kernels with partial last waves cost more than the HBM round trips they avoid.
+    attention_block_bytes: int = 0
 
 
 class _Buf:
@@ -370,7 +377,19 @@ class AttentionOp(OpImpl):
             self.c_ctx = torch.empty(self.B * self.Sq, H * vd, dtype=cdt, device=dev)
         else:
             self.c_q, self.c_k, self.c_v = self.qv, self.kv, self.vv
-        self.probs = torch.empty(self.B, H, self.Sq, self.Sk, dtype=cdt, device=dev)
+        per_batch = H * self.Sq * self.Sk * 2
+        blk = int(ex.cfg.attention_block_bytes)
+        self.cb = 0   # batch elements per block (0 = unblocked)
+        self.hb = H   # heads per block
+        if ex.on_gpu and blk > 0 and self.B * per_batch > 2 * blk:
+            if per_batch <= blk:
+                self.cb = max(1, min(self.B, blk // per_batch))
+            else:  # one batch element at a time, a group of heads per block
+                self.cb = 1
+                self.hb = max(1, min(H, (H * blk) // per_batch))
+                while H % self.hb:
+                    self.hb -= 1
+        self.probs = torch.empty(self.B if not self.cb else 0, H, self.Sq, self.Sk, dtype=cdt, device=dev)
         self.ctx = torch.empty(self.B * self.Sq, H * vd, dtype=dt, device=dev)
         if not self.core16:
             self.c_ctx = self.ctx
@@ -380,15 +399,20 @@ class AttentionOp(OpImpl):
         self.bias_out = self.x("OUTPUT_BIAS") if ("OUTPUT_BIAS" in self.inputs and ex.use_bias(self, "OUTPUT_BIAS")) else None
         self.alpha = 1.0 / math.sqrt(kd)
         nbytes = self.probs.numel() * self.probs.element_size()
+        if self.cb:
+            self.kept_p = None
+            # scores/probabilities, dropped probabilities, d(scores) of one block
+            ex.need_big_scratch(self.cb * self.hb * self.Sq * self.Sk * 2, 3)
         # The dropped probabilities feed the P.V GEMM and, in backward, the dV GEMM.  Keeping them costs one
         # score-sized tensor per layer and saves regenerating them (a read and a write of that tensor); it is
         # done while plenty of device memory is free, otherwise they are rebuilt in a shared scratch buffer.
         self.kept_p = None
-        if self.p_drop > 0 and ex.cfg.training and ex.on_gpu and ex.cfg.keep_dropped_probs:
+        if not self.cb and self.p_drop > 0 and ex.cfg.training and ex.on_gpu and ex.cfg.keep_dropped_probs:
             free, _total = torch.cuda.mem_get_info(ex.device)
             if free > 8 * nbytes + (40 << 30):
                 self.kept_p = torch.empty_like(self.probs)
-        ex.need_big_scratch(nbytes, 2 if (self.p_drop > 0 and self.kept_p is None) else 1)
+        if not self.cb:
+            ex.need_big_scratch(nbytes, 2 if (self.p_drop > 0 and self.kept_p is None) else 1)
         ex.need_scratch(4 * K.bias_act_bwd_scratch(self.B * self.Sq, max(self.ldqkv, self.embed)) if ex.on_gpu else 0)
         self.salt = ex.next_salt()
         self.es = 2
@@ -410,10 +434,75 @@ class AttentionOp(OpImpl):
                 self.c_dq, self.c_dk, self.c_dv, self.c_dctx = self.dq_, self.dk_, self.dv_, self.dctx
 
     # batched GEMM over (head, batch) on strided [tokens, H*d] views
-    def _bg(self, M, N, Kd, A, lda, a_sh, a_sb, a_mn, Bm, ldb, b_sh, b_sb, b_mn, C, ldc, c_sh, c_sb, alpha=1.0):
+    def _bg(self, M, N, Kd, A, lda, a_sh, a_sb, a_mn, Bm, ldb, b_sh, b_sb, b_mn, C, ldc, c_sh, c_sb, alpha=1.0, nb=None, nh=None):
         K.gemm_raw(M=M, N=N, K=Kd, A=A.data_ptr(), lda=lda, a_sh=a_sh, a_sb=a_sb, a_mn=a_mn, B=Bm.data_ptr(), ldb=ldb,
-                   b_sh=b_sh, b_sb=b_sb, b_mn=b_mn, C=C.data_ptr(), ldc=ldc, c_sh=c_sh, c_sb=c_sb, nh=self.H,
-                   nb=self.B, alpha=alpha, es=self.es, out_fp32=C.dtype == torch.float32)
+                   b_sh=b_sh, b_sb=b_sb, b_mn=b_mn, C=C.data_ptr(), ldc=ldc, c_sh=c_sh, c_sb=c_sb, nh=self.H if nh is None else nh,
+                   nb=self.B if nb is None else nb, alpha=alpha, es=self.es, out_fp32=C.dtype == torch.float32)
+
+    # ---- L2-blocked core: batch elements [b0, b0 + n) x heads [h0, h0 + hb) at a time in reused block buffers
+    def _blocks(self):
+        ci = 0
+        for b0 in range(0, self.B, self.cb):
+            for h0 in range(0, self.H, self.hb):
+                yield ci, b0, min(self.cb, self.B - b0), h0
+                ci += 1
+
+    def _block_buffers(self, n):
+        shape = (n, self.hb, self.Sq, self.Sk)
+        nbytes = n * self.hb * self.Sq * self.Sk * 2
+        return [self.ex._big[i][:nbytes].view(torch.bfloat16).view(shape) for i in range(3)]
+
+    def _rows(self, t, b0, n, S, h0, d):
+        """Rows of batch elements [b0, b0+n) and the columns of heads [h0, h0+hb) of a [tokens, H*d] view."""
+        return t[b0 * S:(b0 + n) * S, h0 * d:(h0 + self.hb) * d]
+
+    def _block_probs(self, ci, b0, n, h0, S, Pd):
+        """S <- softmax(alpha * q k^T) for the block; Pd <- dropout(S) when dropout is on.  Returns the operand of P.V"""
+        hb, kd, Sq, Sk = self.hb, self.kd, self.Sq, self.Sk
+        q, k = self._rows(self.c_q, b0, n, Sq, h0, kd), self._rows(self.c_k, b0, n, Sk, h0, kd)
+        self._bg(Sq, Sk, kd, q, self.ldq, kd, Sq * self.ldq, False, k, self.ldk, kd, Sk * self.ldk, False, S, Sk, Sq * Sk, hb * Sq * Sk,
+                 alpha=self.alpha, nb=n, nh=hb)
+        causal_q = Sq if self.ex.cfg.causal_attention else 0
+        salt = self.salt + 0x51ED27 * (ci + 1)  # every block draws its own mask, the same in forward and backward
+        if self.p_drop > 0 and K.softmax_dropout_supported(S):
+            K.softmax_dropout_fwd(S, S, Pd, self.p_drop, salt, self.ex.seed_tensor, causal_q=causal_q)
+            return Pd, salt
+        K.softmax_fwd(S, out=S, causal_q=causal_q)
+        if self.p_drop > 0:
+            K.dropout(S, self.p_drop, salt, out=Pd, seed_tensor=self.ex.seed_tensor)
+            return Pd, salt
+        return S, salt
+
+    def _forward_core_blocked(self):
+        hb, vd, Sq, Sk, Hvd = self.hb, self.vd, self.Sq, self.Sk, self.H * self.vd
+        for ci, b0, n, h0 in self._blocks():
+            S, Pd, _ = self._block_buffers(n)
+            p, _salt = self._block_probs(ci, b0, n, h0, S, Pd)
+            v = self._rows(self.c_v, b0, n, Sk, h0, vd)
+            self._bg(Sq, vd, Sk, p, Sk, Sq * Sk, hb * Sq * Sk, False, v, self.ldv, vd, Sk * self.ldv, True,
+                     self._rows(self.c_ctx, b0, n, Sq, h0, vd), Hvd, vd, Sq * Hvd, nb=n, nh=hb)
+
+    def _backward_core_blocked(self):
+        hb, kd, vd, Sq, Sk, Hvd = self.hb, self.kd, self.vd, self.Sq, self.Sk, self.H * self.vd
+        for ci, b0, n, h0 in self._blocks():
+            S, Pd, dP = self._block_buffers(n)
+            p, salt = self._block_probs(ci, b0, n, h0, S, Pd)  # recomputed: nothing of size B*H*S*S is ever stored
+            q, k = self._rows(self.c_q, b0, n, Sq, h0, kd), self._rows(self.c_k, b0, n, Sk, h0, kd)
+            v, dctx = self._rows(self.c_v, b0, n, Sk, h0, vd), self._rows(self.c_dctx, b0, n, Sq, h0, vd)
+            self._bg(Sq, Sk, vd, dctx, Hvd, vd, Sq * Hvd, False, v, self.ldv, vd, Sk * self.ldv, False, dP, Sk, Sq * Sk, hb * Sq * Sk,
+                     nb=n, nh=hb)
+            self._bg(Sk, vd, Sq, p, Sk, Sq * Sk, hb * Sq * Sk, True, dctx, Hvd, vd, Sq * Hvd, True,
+                     self._rows(self.c_dv, b0, n, Sk, h0, vd), self.ldv, vd, Sk * self.ldv, nb=n, nh=hb)
+            if K.softmax_dropout_supported(S):
+                K.softmax_dropout_bwd(dP, S, dP, self.p_drop, salt, self.ex.seed_tensor, scale=self.alpha)
+            else:
+                if self.p_drop > 0:
+                    K.dropout(dP, self.p_drop, salt, out=dP, seed_tensor=self.ex.seed_tensor)
+                K.softmax_bwd(dP, S, dx=dP, scale=self.alpha)
+            self._bg(Sq, kd, Sk, dP, Sk, Sq * Sk, hb * Sq * Sk, False, k, self.ldk, kd, Sk * self.ldk, True,
+                     self._rows(self.c_dq, b0, n, Sq, h0, kd), self.ldq, kd, Sq * self.ldq, nb=n, nh=hb)
+            self._bg(Sk, kd, Sq, dP, Sk, Sq * Sk, hb * Sq * Sk, True, q, self.ldq, kd, Sq * self.ldq, True,
+                     self._rows(self.c_dk, b0, n, Sk, h0, kd), self.ldk, kd, Sk * self.ldk, nb=n, nh=hb)
 
     def forward(self):
         H, kd, vd, Sq, Sk = self.H, self.kd, self.vd, self.Sq, self.Sk
@@ -431,6 +520,9 @@ class AttentionOp(OpImpl):
                 K.cast(self.qkv, self.c_qkv)
             else:
                 K.cast(self.qv, self.c_q); K.cast(self.kv, self.c_k); K.cast(self.vv, self.c_v)
+        if self.cb:
+            self._forward_core_blocked()
+            return self._forward_out()
         # scores[b,h,sq,sk] = alpha * q . k^T
         self._bg(Sq, Sk, kd, self.c_q, self.ldq, kd, Sq * self.ldq, False, self.c_k, self.ldk, kd, Sk * self.ldk, False,
                  self.probs, Sk, Sq * Sk, H * Sq * Sk, alpha=self.alpha)
@@ -448,6 +540,9 @@ class AttentionOp(OpImpl):
         # ctx[b,sq,h,:] = p . v
         self._bg(Sq, vd, Sk, p, Sk, Sq * Sk, H * Sq * Sk, False, self.c_v, self.ldv, vd, Sk * self.ldv, True,
                  self.c_ctx, H * vd, vd, Sq * H * vd)
+        self._forward_out()
+
+    def _forward_out(self):
         if self.core16:
             K.cast(self.c_ctx, self.ctx)
         if self.fuse_out is not None:
@@ -473,6 +568,11 @@ class AttentionOp(OpImpl):
         K.matmul_tn(dy, self.ctx, out=g_wo, accumulate=accw)
         if self.fuse_out is None:
             K.matmul_nn(dy, self.wo, out=self.dctx)
+        if self.core16:
+            K.cast(self.dctx, self.c_dctx)
+        if self.cb:
+            self._backward_core_blocked()
+            return self._backward_projections(wg, accw, n_q, n_k, n_v)
         p = self.probs
         if self.p_drop > 0 and self.kept_p is not None:
             p = self.kept_p
@@ -480,8 +580,6 @@ class AttentionOp(OpImpl):
             p = ex.big_scratch(1, self.probs)
             K.dropout(self.probs, self.p_drop, self.salt, out=p, seed_tensor=ex.seed_tensor)
         dP = ex.big_scratch(0, self.probs)
-        if self.core16:
-            K.cast(self.dctx, self.c_dctx)
         # dP[b,h,sq,sk] = dctx[b,sq,h,:] . v[b,sk,h,:]^T
         self._bg(Sq, Sk, vd, self.c_dctx, H * vd, vd, Sq * H * vd, False, self.c_v, self.ldv, vd, Sk * self.ldv, False,
                  dP, Sk, Sq * Sk, H * Sq * Sk)
@@ -499,6 +597,11 @@ class AttentionOp(OpImpl):
                  self.c_dq, self.ldq, kd, Sq * self.ldq)
         self._bg(Sk, kd, Sq, dP, Sk, Sq * Sk, H * Sq * Sk, True, self.c_q, self.ldq, kd, Sq * self.ldq, True,
                  self.c_dk, self.ldk, kd, Sk * self.ldk)
+        self._backward_projections(wg, accw, n_q, n_k, n_v)
+
+    def _backward_projections(self, wg, accw, n_q, n_k, n_v):
+        H, kd, vd = self.H, self.kd, self.vd
+        ex = self.ex
         if self.core16:
             if self.self_attn:
                 K.cast(self.c_dqkv, self.dqkv)

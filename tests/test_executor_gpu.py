@@ -173,3 +173,48 @@ def test_checkpoint_roundtrip_restores_training_state_on_gpu(tmp_path):
     assert meta["step"] == 3 and b.step_count == 3
     b.train_step({"input_ids": ids}, labels)
     assert abs(b.mean_loss() - want) < 1e-3 * abs(want)
+
+
+@pytest.mark.parametrize("block_bytes", [0, 16384, 8192])
+def test_blocked_attention_core_matches_oracle(block_bytes):
+    """The L2-blocked attention core (blocks of batch elements, or of head groups of one batch element, with the
+    probabilities recomputed in backward) computes the same loss and gradients as the whole-batch core."""
+    g = core.build_model("transformer_lm", SMALL_LM)
+    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=3, attention_block_bytes=block_bytes))
+    att = [op for op in ex.ops.values() if op.type == "MULTIHEAD_ATTENTION"][0]
+    assert (att.cb > 0) == (block_bytes > 0)
+    if block_bytes == 8192:
+        assert att.hb == 1 and att.cb == 1
+    oracle = TorchOracle(g, seed=3)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32)
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32)
+    ex.set_inputs({"input_ids": ids.cuda()}, labels.cuda())
+    ex.forward()
+    ex.compute_loss()
+    ex.backward()
+    rows_ref, grads_ref = oracle.loss_and_grads({"input_ids": ids}, labels)
+    assert rel(ex.loss_rows, rows_ref) < 6e-2
+    for name, g_ in ex.named_gradients():
+        assert rel(g_, grads_ref[name]) < 0.3, (name, rel(g_, grads_ref[name]))
+
+
+def test_blocked_attention_with_dropout_is_consistent_between_forward_and_backward():
+    """With dropout the blocked core regenerates each block's mask in backward; training must still converge and
+    the CUDA-graph replay must follow the eager trajectory."""
+    cfg = dict(SMALL_LM, dropout=0.1)
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32, device="cuda")
+    out = []
+    for use_graph in (False, True):
+        g = core.build_model("transformer_lm", cfg)
+        ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, use_cuda_graph=use_graph, attention_block_bytes=16384,
+                                      optimizer=OptimizerConfig(kind="adam", lr=1e-3)))
+        ls = []
+        for _ in range(6):
+            ex.train_step({"input_ids": ids}, labels)
+            ls.append(ex.mean_loss())
+        out.append(ls)
+    assert out[0][-1] < out[0][0]
+    for a, b in zip(*out):
+        assert abs(a - b) < 2e-2 * abs(a), out
