@@ -293,12 +293,13 @@ __global__ void bn_partial_kernel(const T *__restrict__ a, const T *__restrict__
     part[((long long)blockIdx.y * 2 + 1) * C + c] = v;
   }
 }
-// Fold the per-chunk partial sums: block = 32 columns x 8 chunk lanes, fixed summation order.
+// Fold the per-chunk partial sums: block = 32 columns x BN_FOLD chunk lanes, fixed summation order.
+constexpr int BN_FOLD = 32;
 __device__ __forceinline__ void bn_fold(const float *__restrict__ part, int chunks, int C, int c, float &s, float &q) {
-  __shared__ float fs[8][33], fq[8][33];
+  __shared__ float fs[BN_FOLD][33], fq[BN_FOLD][33];
   float a = 0.f, b = 0.f;
   if (c < C)
-    for (int k = threadIdx.y; k < chunks; k += 8) {
+    for (int k = threadIdx.y; k < chunks; k += BN_FOLD) {
       a += part[((long long)k * 2) * C + c];
       b += part[((long long)k * 2 + 1) * C + c];
     }
@@ -307,7 +308,7 @@ __device__ __forceinline__ void bn_fold(const float *__restrict__ part, int chun
   __syncthreads();
   s = q = 0.f;
   if (threadIdx.y == 0)
-    for (int i = 0; i < 8; ++i) { s += fs[i][threadIdx.x]; q += fq[i][threadIdx.x]; }
+    for (int i = 0; i < BN_FOLD; ++i) { s += fs[i][threadIdx.x]; q += fq[i][threadIdx.x]; }
 }
 __global__ void bn_finalize_stats_kernel(const float *__restrict__ part, int chunks, int C, long long R, float eps, float *__restrict__ mean,
                                          float *__restrict__ rstd) {
@@ -567,19 +568,25 @@ __global__ void bn_partial_vec_kernel(const bf16 *__restrict__ a, const bf16 *__
 __global__ void bn_apply_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, const bf16 *__restrict__ gamma,
                                     const bf16 *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd,
                                     long long total8, int C, int relu) {
+  // the grid-stride step is a multiple of the number of channel groups, so a thread stays on one group and
+  // keeps that group's scale and shift in registers: y = x * scale + shift
   const int groups = C >> 3;
-  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total8; t += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(t % groups) * 8;
+  const long long usable = ((long long)gridDim.x * blockDim.x / groups) * groups;
+  const long long t0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t0 >= usable) return;
+  const int c = (int)(t0 % groups) * 8;
+  float sc[8], sh[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    sc[i] = rstd[c + i] * (gamma ? bf2f(gamma[c + i]) : 1.f);
+    sh[i] = (beta ? bf2f(beta[c + i]) : 0.f) - mean[c + i] * sc[i];
+  }
+  const float floor_ = relu ? 0.f : -INFINITY;
+  for (long long t = t0; t < total8; t += usable) {
     float f[8];
     unpack8(reinterpret_cast<const uint4 *>(x)[t], f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float v = (f[i] - mean[c + i]) * rstd[c + i];
-      if (gamma) v *= bf2f(gamma[c + i]);
-      if (beta) v += bf2f(beta[c + i]);
-      if (relu) v = fmaxf(v, 0.f);
-      f[i] = v;
-    }
+    for (int i = 0; i < 8; ++i) f[i] = fmaxf(fmaf(f[i], sc[i], sh[i]), floor_);
     reinterpret_cast<uint4 *>(y)[t] = pack8(f);
   }
 }
@@ -587,9 +594,23 @@ __global__ void bn_bwd_apply_vec_kernel(const bf16 *__restrict__ dy, const bf16 
                                         const bf16 *__restrict__ gamma, const float *__restrict__ mean, const float *__restrict__ rstd,
                                         const float *__restrict__ sums, bf16 *__restrict__ dx, long long total8, int C, float inv_r,
                                         int accumulate) {
+  // dx = a * dy' + b * x + c per channel (constants kept in registers, see bn_apply_vec_kernel):
+  //   xh = (x - mean) * rstd;  dx = gamma * rstd * (dy' - s1/R - xh * s2/R)
   const int groups = C >> 3;
-  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total8; t += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(t % groups) * 8;
+  const long long usable = ((long long)gridDim.x * blockDim.x / groups) * groups;
+  const long long t0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t0 >= usable) return;
+  const int c = (int)(t0 % groups) * 8;
+  float ka[8], kb[8], kc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float rs = rstd[c + i], g = gamma ? bf2f(gamma[c + i]) : 1.f;
+    const float s1 = sums[c + i] * inv_r, s2 = sums[C + c + i] * inv_r;
+    ka[i] = g * rs;
+    kb[i] = -g * rs * rs * s2;
+    kc[i] = g * rs * (mean[c + i] * rs * s2 - s1);
+  }
+  for (long long t = t0; t < total8; t += usable) {
     float g[8], xv[8], o[8];
     unpack8(reinterpret_cast<const uint4 *>(dy)[t], g);
     unpack8(reinterpret_cast<const uint4 *>(x)[t], xv);
@@ -602,10 +623,7 @@ __global__ void bn_bwd_apply_vec_kernel(const bf16 *__restrict__ dy, const bf16 
     if (accumulate) unpack8(reinterpret_cast<const uint4 *>(dx)[t], o);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float rs = rstd[c + i];
-      const float xh = (xv[i] - mean[c + i]) * rs;
-      float v = (g[i] - sums[c + i] * inv_r - xh * sums[C + c + i] * inv_r) * rs;
-      if (gamma) v *= bf2f(gamma[c + i]);
+      const float v = fmaf(ka[i], g[i], fmaf(kb[i], xv[i], kc[i]));
       o[i] = accumulate ? o[i] + v : v;
     }
     reinterpret_cast<uint4 *>(dx)[t] = pack8(o);
@@ -763,14 +781,14 @@ FFK_API int ffk_batchnorm_fwd(const void *x, void *y, const void *gamma, const v
     const int lanes = BNV_THREADS / (C / 8);
     bn_partial_vec_kernel<<<cv, BNV_THREADS, (size_t)lanes * 2 * C * sizeof(float), st>>>((const bf16 *)x, nullptr, nullptr, scratch, nullptr,
                                                                                           nullptr, R, C, rv, 0);
-    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, cv, C, R, eps, mean, rstd);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, cv, C, R, eps, mean, rstd);
     bn_apply_vec_kernel<<<ffk_blocks(total / 8, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta, mean,
                                                                     rstd, total / 8, C, relu);
     return (int)cudaGetLastError();
   }
   if (dt == 1) {
     bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
-    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
     if ((C % 2) == 0 && ((uintptr_t)x % 4) == 0 && ((uintptr_t)y % 4) == 0)
       bn_apply_bf16x2_kernel<<<ffk_blocks(total / 2, 256), 256, 0, st>>>((const bf16 *)x, (bf16 *)y, (const bf16 *)gamma, (const bf16 *)beta,
                                                                          mean, rstd, total / 2, C, relu);
@@ -779,7 +797,7 @@ FFK_API int ffk_batchnorm_fwd(const void *x, void *y, const void *gamma, const v
                                                                     rstd, total, C, relu);
   } else if (dt == 0) {
     bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)x, nullptr, nullptr, scratch, nullptr, nullptr, R, C, rpc, 0);
-    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
+    bn_finalize_stats_kernel<<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, chunks, C, R, eps, mean, rstd);
     bn_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)x, (float *)y, (const float *)gamma, (const float *)beta,
                                                                    mean, rstd, total, C, relu);
   } else {
@@ -806,7 +824,7 @@ FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y,
     float *sums_v = scratch + (long long)cv * 2 * C;
     bn_partial_vec_kernel<<<cv, BNV_THREADS, (size_t)lanes * 2 * C * sizeof(float), st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
                                                                                           scratch, mean, rstd, R, C, rv, 1);
-    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, cv, C, sums_v, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
+    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, cv, C, sums_v, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
                                                                      accumulate_beta);
     if (dx)
       bn_bwd_apply_vec_kernel<<<ffk_blocks(total / 8, 256), 256, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
@@ -816,7 +834,7 @@ FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y,
   }
   if (dt == 1) {
     bn_partial_kernel<bf16><<<grid, block, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
-    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, sums, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
+    bn_finalize_grads_kernel<bf16><<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, chunks, C, sums, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_gamma,
                                                                      accumulate_beta);
     if (dx)
       bn_bwd_apply_kernel<bf16><<<ffk_blocks(total, 256), 256, 0, st>>>((const bf16 *)dy, (const bf16 *)x, (const bf16 *)relu_y,
@@ -824,7 +842,7 @@ FFK_API int ffk_batchnorm_bwd(const void *dy, const void *x, const void *relu_y,
                                                                         accumulate_dx);
   } else if (dt == 0) {
     bn_partial_kernel<float><<<grid, block, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y, scratch, mean, rstd, R, C, rpc, 1);
-    bn_finalize_grads_kernel<float><<<(C + 31) / 32, dim3(32, 8), 0, st>>>(scratch, chunks, C, sums, (float *)dgamma, (float *)dbeta,
+    bn_finalize_grads_kernel<float><<<(C + 31) / 32, dim3(32, BN_FOLD), 0, st>>>(scratch, chunks, C, sums, (float *)dgamma, (float *)dbeta,
                                                                       accumulate_gamma, accumulate_beta);
     if (dx)
       bn_bwd_apply_kernel<float><<<ffk_blocks(total, 256), 256, 0, st>>>((const float *)dy, (const float *)x, (const float *)relu_y,

@@ -119,7 +119,11 @@ template <int VPT>
 __global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ b, const bf16 *__restrict__ gamma,
                                          const bf16 *__restrict__ beta, bf16 *__restrict__ xsum, bf16 *__restrict__ y,
                                          float *__restrict__ mean, float *__restrict__ rstd, int rows, int cols, float eps) {
-  __shared__ float red[32];
+  // two block reductions per row (mean, then centred variance), each through its own double-buffered slot so
+  // that one barrier per reduction suffices
+  __shared__ float red_a[2][32], red_b[2][32];
+  int parity = 0;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   float gm[VPT][8], bt[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -148,13 +152,24 @@ __global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += v[i][j];
     }
-    const float mu = block_sum(s, red) / cols;
+    s = warp_sum(s);
+    if (lane == 0) red_a[parity][wid] = s;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < nw; ++k) tot += red_a[parity][k];
+    const float mu = tot / cols;
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; ss += d * d; }
-    const float rs = rsqrtf(block_sum(ss, red) / cols + eps);
+    ss = warp_sum(ss);
+    if (lane == 0) red_b[parity][wid] = ss;
+    __syncthreads();
+    float tot2 = 0.f;
+    for (int k = 0; k < nw; ++k) tot2 += red_b[parity][k];
+    parity ^= 1;
+    const float rs = rsqrtf(tot2 / cols + eps);
     if (threadIdx.x == 0) {
       if (mean) mean[row] = mu;
       if (rstd) rstd[row] = rs;
