@@ -61,6 +61,7 @@ class ExecConfig:
     # Transformer it costs more in the epilogue (which is on the GEMM's critical path) than the separate
     # bandwidth-bound dropout kernel it removes (343.8 vs 335.2 ms per step).
     fuse_dropout: bool = False
+    fold_dropout_backward: bool = True  # Linear -> Dropout: mask the gradient inside the Linear's bias/activation backward
     keep_dropped_probs: bool = True  # attention: keep dropout(P) for backward when device memory allows
     # Attention core in blocks: scores, probabilities and their gradients of a few batch elements (or head groups)
     # at a time live in small reused buffers and backward recomputes the probabilities of a block, so no
@@ -155,7 +156,11 @@ class OpImpl:
     def extra_grad_sources(self):
         """Values whose gradient this operator's backward reads although they are not its outputs."""
         fo = getattr(self, "fuse_out", None)
-        return [(fo.repartition.nid, "OUTPUT")] if fo is not None else []
+        out = [(fo.repartition.nid, "OUTPUT")] if fo is not None else []
+        d = getattr(self, "bwd_dropout", None)
+        if d is not None:
+            out.append((d.nid, "OUTPUT"))
+        return out
 
 
 _REGISTRY: Dict[str, type] = {}
@@ -226,6 +231,8 @@ class LinearOp(OpImpl):
     fuse_in = None
     fuse_out = None
     fused_dropout = None  # a Dropout that directly follows: applied by this GEMM's epilogue, undone in its backward
+    bwd_dropout = None    # a Dropout that directly follows and runs as its own kernel in forward; its backward (masking
+                          # the incoming gradient) is folded into this operator's bias/activation backward pass
 
     def _drop(self):
         d = self.fused_dropout
@@ -262,7 +269,14 @@ class LinearOp(OpImpl):
                                                 accumulate=self.acc.get("INPUT", False))
         else:
             dy = self.out().grad.view_as(self.y2d)
-        if self.act is not None or self.bias is not None or self.fused_dropout is not None:
+        if self.bwd_dropout is not None:
+            d = self.bwd_dropout
+            src = d.out().grad.view_as(self.y2d)  # gradient w.r.t. the dropped output; masked and passed on in one pass
+            saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
+            bb = self.buf("BIAS") if self.bias is not None else None
+            K.bias_act_bwd(src, saved, dy, bb.grad if bb is not None else None, self.ex.scratch_f32(), self.act,
+                           accumulate=self.acc.get("BIAS", False), dropout=(d.p, d.salt, self.ex.seed_tensor))
+        elif self.act is not None or self.bias is not None or self.fused_dropout is not None:
             saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
             bb = self.buf("BIAS") if self.bias is not None else None
             rewrite = self.act is not None or self.fused_dropout is not None
@@ -774,6 +788,7 @@ class BinaryOp(OpImpl):
 @register("DROPOUT")
 class DropoutOp(OpImpl):
     fused_into = None  # the Linear whose GEMM epilogue applies this dropout (then this operator is an alias)
+    bwd_folded = None  # the Linear whose backward also undoes this dropout (forward stays a kernel of its own)
 
     def setup(self):
         self.p = float(self.attrs["rate"]) if self.ex.cfg.training else 0.0
@@ -785,6 +800,9 @@ class DropoutOp(OpImpl):
                 return
             self.fused_into.fused_dropout = None
             self.fused_into = None
+        if self.bwd_folded is not None and not self.p > 0:
+            self.bwd_folded.bwd_dropout = None
+            self.bwd_folded = None
         if self.p > 0:
             self.alloc_out()
         else:
@@ -796,7 +814,7 @@ class DropoutOp(OpImpl):
 
     def backward(self):
         b = self.buf("INPUT")
-        if not b.requires_grad or self.fused_into is not None:
+        if not b.requires_grad or self.fused_into is not None or self.bwd_folded is not None:
             return
         dy = self.out().grad
         if self.p > 0:
@@ -1144,6 +1162,17 @@ class Executable:
                     prod.fused_into_ln = True
             # Linear -> Dropout: the GEMM epilogue applies the mask (bf16, 16-byte rows; not for a row-parallel GEMM
             # whose output is still a partial sum)
+            if (isinstance(op, DropoutOp) and not self.cfg.fuse_dropout and self.cfg.fold_dropout_backward and self.on_gpu and self.cfg.training
+                    and self.cfg.compute_dtype == "bf16" and float(op.attrs.get("rate", 0)) > 0):
+                # backward half only: Linear -> Dropout with the dropout's gradient masking folded into the Linear's
+                # bias/activation backward kernel
+                src = op.inputs["INPUT"]
+                prod = self.ops[src[0]]
+                cols = int(g.shape(src).piece_sizes[-1])
+                if (isinstance(prod, LinearOp) and prod.bwd_dropout is None and len(g.consumers(src)) == 1 and cols % 8 == 0
+                        and g.shape(src).sum_degree == 1 and g.shape(src).dtype in ("FLOAT", "HALF", "BFLOAT16")):
+                    prod.bwd_dropout = op
+                    op.bwd_folded = prod
             if (isinstance(op, DropoutOp) and self.cfg.fuse_dropout and self.on_gpu and self.cfg.training
                     and self.cfg.compute_dtype == "bf16" and float(op.attrs.get("rate", 0)) > 0):
                 src = op.inputs["INPUT"]

@@ -218,3 +218,25 @@ def test_blocked_attention_with_dropout_is_consistent_between_forward_and_backwa
     assert out[0][-1] < out[0][0]
     for a, b in zip(*out):
         assert abs(a - b) < 2e-2 * abs(a), out
+
+
+def test_dropout_backward_folded_into_linear_backward_gives_the_same_gradients():
+    """Masks are a function of (salt, step seed, index), so an executor that folds the dropout's backward into the
+    preceding Linear's bias/activation kernel and one that runs it as a separate kernel see identical masks."""
+    cfg = dict(SMALL_LM, dropout=0.3)
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32, device="cuda")
+    grads = []
+    for fold in (False, True):
+        g = core.build_model("transformer_lm", cfg)
+        ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, fold_dropout_backward=fold))
+        folded = sum(1 for op in ex.ops.values() if getattr(op, "bwd_folded", None) is not None)
+        assert (folded > 0) == fold
+        ex.set_inputs({"input_ids": ids}, labels)
+        ex._pre_step()
+        ex.forward()
+        ex.compute_loss()
+        ex.backward()
+        grads.append({k: v.float().clone() for k, v in ex.named_gradients()})
+    for k in grads[0]:
+        assert rel(grads[1][k], grads[0][k]) < 2e-2, (k, rel(grads[1][k], grads[0][k]))
