@@ -185,7 +185,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
     ap.add_argument("--no-cuda-graph", action="store_true")
-    ap.add_argument("--strategy", default="search", help="search | dp | tp | <path to strategy json>")
+    ap.add_argument("--strategy", default="search", help="search | dp | tp | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
     ap.add_argument("--no-fused-collectives", action="store_true",
                     help="tensor-parallel collectives through NCCL instead of inside the GEMM kernels (baseline)")
     args = ap.parse_args()
@@ -221,7 +221,7 @@ def main():
     opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
                          fuse_collectives=not args.no_fused_collectives,
-                         search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel"}.get(args.strategy, "unity"),
+                         search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel", "tables": "table_parallel"}.get(args.strategy, "unity"),
                          import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
     model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind=opt_kind, lr=lr, momentum=momentum),
                         loss=loss_kind, dist=dctx)

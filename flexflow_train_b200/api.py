@@ -30,7 +30,7 @@ class FFConfig:
     enable_profiling: bool = False
     search_budget: int = 0
     search_alpha: float = 1.05
-    search_algorithm: str = "unity"  # "unity" | "mcmc" | "data_parallel" | "none"
+    search_algorithm: str = "unity"  # "unity" | "mcmc" | "data_parallel" | "tensor_parallel" | "table_parallel"
     only_data_parallel: bool = False
     enable_parameter_parallel: bool = True
     enable_attribute_parallel: bool = True

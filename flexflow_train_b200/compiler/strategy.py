@@ -39,13 +39,15 @@ def data_parallel_rules(rules, degree: int):
     return _rules_named(rules, pred)
 
 
-def apply_where(graph, rule, pred: Callable[[dict], bool], max_total_degree: int = 0):
-    """Apply `rule` at every match whose first pattern node satisfies pred(node dict)."""
+def apply_where(graph, rule, pred: Callable, max_total_degree: int = 0, with_graph: bool = False):
+    """Apply `rule` at every match whose first pattern node satisfies pred(node dict) -- or pred(graph, node dict)
+    with ``with_graph``, for predicates that look at the node's neighbours in the current graph."""
     changed = True
     while changed:
         changed = False
         for m in core.find_pattern_matches(rule, graph):
-            if not pred(graph.node(m.nodes[0])):
+            node = graph.node(m.nodes[0])
+            if not (pred(graph, node) if with_graph else pred(node)):
                 continue
             ng = core.apply_substitution(graph, rule, m)
             if ng is None:
@@ -64,6 +66,43 @@ def data_parallel_strategy(cg, world: int, rules=None):
     pcg = core.pcg_from_computation_graph(cg)
     sel = data_parallel_rules(rules, world) + cancellation_rules(rules)
     return core.apply_rules_exhaustively(pcg, sel, 100000, world)
+
+
+def _on_table_side(graph, n) -> bool:
+    """Is `n` an Embedding, the Reshape of one, or the Concat that stacks such lookups?"""
+    t = n["type"]
+    if t == "EMBEDDING":
+        return True
+    if t in ("RESHAPE", "FLAT"):
+        return graph.node(tuple(n["inputs"][0][1])[0])["type"] == "EMBEDDING"
+    if t == "CONCAT":
+        prods = [graph.node(tuple(v)[0]) for _, v in n["inputs"]]
+        return all(p["type"] != "CONCAT" and _on_table_side(graph, p) for p in prods)
+    return False
+
+
+def has_stacked_embeddings(cg) -> bool:
+    return any(n["type"] == "CONCAT" and _on_table_side(cg, n) for n in cg.nodes())
+
+
+def table_parallel_strategy(cg, world: int, rules=None):
+    """Embedding tables model-parallel, everything else data-parallel (the recommendation-model layout).
+
+    The lookups and the Concat that stacks them stay unpartitioned operators on whole tables -- placed on
+    different devices, which is the reference's inter-operator parallelism over the parallel branches of the
+    series-parallel decomposition (lib/compiler/src/compiler/machine_mapping/get_optimal_machine_mapping.cc:215-263)
+    -- and every other operator is sharded over the sample dim.  The Repartition(0) that the first data-parallel
+    consumer puts behind the Concat is the all-to-all from table owners to sample owners; no table is ever
+    replicated, so no table-sized gradient crosses the links."""
+    ms = machine_for(world)
+    rules = rules or core.get_substitution_set(ms)
+    g = core.pcg_from_computation_graph(cg)
+    if not has_stacked_embeddings(g):
+        raise ValueError("no stacked embedding lookups in this graph")
+    for r in data_parallel_rules(rules, world):
+        g = apply_where(g, r, lambda graph, n: not _on_table_side(graph, n), world, with_graph=True)
+    g = core.apply_rules_exhaustively(g, cancellation_rules(rules), 100000, world)
+    return core.merge_duplicate_parallel_ops(g)
 
 
 def tensor_parallel_strategy(cg, world: int, rules=None, sequence_parallel: bool = True):
@@ -174,11 +213,15 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
                 cands[f"tp{W}"] = tensor_parallel_strategy(cg, W, rules)
             except Exception:  # a model without the pattern simply has no such candidate
                 pass
+            if has_stacked_embeddings(cg):
+                cands[f"dp{W}+tables_mp{W}"] = table_parallel_strategy(cg, W, rules)
     scored = {k: core.evaluate_pcg(g, machine, estimator) for k, g in cands.items()}
     if algorithm == "data_parallel" or only_data_parallel:
         best_name = f"dp{W}" if W > 1 else "single_device"
     elif algorithm == "tensor_parallel":
         best_name = f"tp{W}" if f"tp{W}" in scored else min(scored, key=lambda k: scored[k]["runtime_ms"])
+    elif algorithm == "table_parallel":
+        best_name = f"dp{W}+tables_mp{W}" if f"dp{W}+tables_mp{W}" in scored else min(scored, key=lambda k: scored[k]["runtime_ms"])
     else:
         best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
     best = scored[best_name]

@@ -372,10 +372,12 @@ Graph build_dlrm(const Json &user) {
   } else if (inter == "DOT") {
     // pairwise dot products of the (1 + #tables) feature vectors, concatenated with the dense feature
     if (bottom.back() != dim) throw Error("dlrm: DOT interaction needs bottom MLP width == embedding_dim");
+    // the lookups are stacked on their own first, so that a strategy can keep that stack table-parallel and hand
+    // it to the sample-parallel rest of the model in one all-to-all
     std::vector<V> rows;
-    rows.push_back(b.reshape(bot, {batch, 1, dim}));
     for (auto &e : embs) rows.push_back(b.reshape(e, {batch, 1, dim}));
-    V x = concat_many(b, rows, 1);                 // [batch, F, dim]
+    V stack = rows.size() > 1 ? concat_many(b, rows, 1) : rows[0];
+    V x = b.concat({b.reshape(bot, {batch, 1, dim}), stack}, 1);  // [batch, F, dim]
     V xt = b.transpose(x, {0, 2, 1});              // [batch, dim, F]
     V z = b.batch_matmul(x, xt);                   // [batch, F, F]
     V zf = b.flat(z, 1, -1);

@@ -51,9 +51,30 @@ def bench_gemm_batched(a):
     return {"op": "gemm_nt_bf16_batched", "batch": nb, "m": m, "n": n, "k": k, **r, "torch_bmm_ms": ref, "gemm_error": K.gemm_last_error()}
 
 
+def bench_gemm_layouts(a):
+    """The three GEMMs of a Linear layer with `m` tokens, `k` inputs, `n` outputs: forward (NT), data gradient
+    (NN: dY[m,n] . W[n,k]) and weight gradient (TN: dY[m,n]^T . X[m,k])."""
+    m, n, k = a.m, a.n, a.k
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    y, dx, dw = torch.empty(m, n, device="cuda", dtype=torch.bfloat16), torch.empty_like(x), torch.empty_like(w)
+    out = {"op": "linear_gemms_bf16", "tokens": m, "in": k, "out": n}
+    flops = 2.0 * m * n * k
+    for name, fn, ref in (("fwd_nt", lambda: K.matmul_nt(x, w, out=y), lambda: torch.matmul(x, w.t(), out=y)),
+                          ("dgrad_nn", lambda: K.matmul_nn(dy, w, out=dx), lambda: torch.matmul(dy, w, out=dx)),
+                          ("wgrad_tn", lambda: K.matmul_tn(dy, x, out=dw), lambda: torch.matmul(dy.t(), x, out=dw))):
+        ms = _time(fn, a.warmup, a.iters, a.flush)
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "torch_ms": _time(ref, a.warmup, a.iters, a.flush) if a.compare else None}
+    out["gemm_error"] = K.gemm_last_error()
+    return out
+
+
 def bench_gemm(a):
     if a.batched:
         return bench_gemm_batched(a)
+    if a.layouts:
+        return bench_gemm_layouts(a)
     m, n, k = a.m, a.n, a.k
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
@@ -132,6 +153,7 @@ def main(argv=None):
     p.add_argument("--flush", action="store_true", help="write a buffer larger than L2 between timed launches")
     p.add_argument("--no-tma-store", action="store_true", help="GEMM epilogue through per-lane global stores instead of TMA stores")
     p.add_argument("--tma-store", action="store_true", help="GEMM epilogue through TMA stores")
+    p.add_argument("--layouts", action="store_true", help="gemm: time the forward / data-gradient / weight-gradient GEMMs of a Linear")
     p.add_argument("--batched", type=int, default=0, help="gemm: run as a batch of this many [m, n, k] problems (attention-shaped)")
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--iters", type=int, default=10)

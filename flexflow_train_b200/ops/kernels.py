@@ -441,6 +441,18 @@ def embedding_bwd(idx, dout, dtable, aggr="sum"):
     return dtable
 
 
+def embedding_sgd(idx, dout, table, lr, aggr="sum"):
+    """Sparse plain-SGD step of an fp32 table from the gradient of the gathered rows: table[idx] -= lr * dout."""
+    bag = idx.shape[-1] if dout.dim() == idx.dim() else 1
+    tokens = idx.numel() // bag
+    _cuda_contig(idx, dout, table)
+    if table.dtype != torch.float32:
+        raise KernelError("embedding_sgd needs an fp32 table")
+    _check(lib().ffk_embedding_sgd(idx.data_ptr(), dout.data_ptr(), table.data_ptr(), tokens, bag, table.shape[1], table.shape[0],
+                                   lr / bag if aggr == "avg" else lr, _dt(idx), _dt(dout), _stream()), "ffk_embedding_sgd")
+    return table
+
+
 # --------------------------------------------------------------------------- data movement
 def _decl_tensor_ops(l):
     P, I, L, F, S = c_void_p, c_int, c_longlong, c_float, c_void_p

@@ -14,7 +14,8 @@ operators at all.  Here
   NVLink peer memory, bucketed and launched on a side stream while backward is still running.
 
 Supported strategies: one mesh axis (every parallel degree equals the world size), which covers pure data
-parallelism, pure tensor parallelism and per-operator mixtures of the two.
+parallelism, pure tensor parallelism, per-operator mixtures of the two, and model-parallel embedding tables
+under a data-parallel model (``AllToAllEmbeddingOp``).
 """
 from __future__ import annotations
 
@@ -28,7 +29,7 @@ from ..runtime import executor as E
 from ..runtime.executor import ExecConfig, Executable, OpImpl, Value, register
 from . import comm
 from .context import DistContext
-from .fused_ops import AllGatherGemm, GemmReduceScatter, GradAllReduce
+from .fused_ops import AllGatherGemm, AllToAllEmbedding, GemmReduceScatter, GradAllReduce
 
 PARALLEL = ("REPARTITION", "COMBINE", "REPLICATE", "REDUCTION")
 
@@ -188,6 +189,41 @@ class ReductionOp(_ParallelOp):
         dist.all_reduce(self.x(), group=self.ex.dist.group)
 
 
+class AllToAllEmbeddingOp(_ParallelOp):
+    """The Repartition(0) behind a stack of whole-table Embeddings (tables model-parallel, samples data-parallel).
+
+    Takes the place of the lookups, their Reshapes, the Concat and the Repartition: every rank gathers, for the
+    whole batch, the rows of the tables it owns and writes them straight into the sample owners' buffers over
+    NVLink (forward); backward pulls the rows of d(stack) from the sample owners and applies the sparse SGD
+    update to the local tables.  No table and no table-sized gradient ever leaves its rank."""
+    group = None
+
+    def communicates(self) -> bool:
+        return False  # peer-memory kernels with device-side barriers, no NCCL call
+
+    def setup(self):
+        ex, grp = self.ex, self.group
+        W, r = ex.ctx.world_size, ex.ctx.rank
+        sh = dict(self.outputs)["OUTPUT"]
+        lb, T, dim = [int(v) for v in sh.piece_sizes]
+        local = [ex.sparse_tables[m["weight"]] for t, m in enumerate(grp["members"]) if t % W == r]
+        dt = ex.torch_dtype(sh.dtype)
+        self.f4 = AllToAllEmbedding(ex.ctx, local, T, dim, lb, out_dtype=dt)
+        b = self.out()
+        b.data, b.grad = self.f4.out_t, self.f4.dout_t
+        self.index_values = [m["index"] for m in grp["members"]]
+        idx0 = ex.values[self.index_values[0]].data
+        self.idx = torch.empty(lb * W, T, dtype=idx0.dtype, device=ex.device)
+        ex.values[self.inputs["INPUT"]].requires_grad = False  # the stack itself is never materialised
+
+    def forward(self):
+        torch.cat([self.ex.values[v].data.view(-1, 1) for v in self.index_values], dim=1, out=self.idx)
+        self.f4.forward(self.idx)
+
+    def backward(self):
+        self.f4.backward_sgd(self.idx, self.ex.cfg.optimizer.lr)
+
+
 class FuseIn:
     """Combine(dim 0) -> Replicate -> GEMM: the operand arrives as row shards.
 
@@ -289,11 +325,83 @@ class DistExecutable(Executable):
             self._discard[key] = torch.empty(rows, cols, dtype=dtype, device=self.device)
         return self._discard[key]
 
+    # ------------------------------------------------------------------ model-parallel embedding tables
+    def _find_table_groups(self) -> List[dict]:
+        """Repartition(0, world) <- Concat(axis 1) <- Reshape <- Embedding(whole table, whole batch, bag of one)."""
+        g, nodes, W = self.graph, self.nodes, self.ctx.world_size
+        groups = []
+        for nid in self.order:
+            n = nodes[nid]
+            if n["type"] != "REPARTITION" or nid in self.weight_chain_nodes or _degree(n["attrs"]) != W \
+                    or int(n["attrs"]["repartition_dim"]) != 0:
+                continue
+            src = tuple(n["inputs"][0][1])
+            c = nodes[src[0]]
+            csh = g.shape(src)
+            if c["type"] != "CONCAT" or len(g.consumers(src)) != 1 or len(csh.sizes) != 3 or csh.total_degree != 1 \
+                    or int(c["attrs"]["axis"]) % 3 != 1 or csh.sizes[0] % W != 0:
+                continue
+            members, skipped, ok = [], [c["id"]], True
+            for _, v in sorted(c["inputs"], key=lambda sv: int(sv[0].split("_")[-1])):
+                v = tuple(v)
+                p = nodes[v[0]]
+                if p["type"] in ("RESHAPE", "FLAT") and len(g.consumers(v)) == 1:
+                    skipped.append(p["id"])
+                    v = tuple(p["inputs"][0][1])
+                    p = nodes[v[0]]
+                ins = {s: tuple(x) for s, x in p["inputs"]}
+                if p["type"] != "EMBEDDING" or len(g.consumers(v)) != 1 or nodes[ins["WEIGHT"][0]]["type"] != "WEIGHT" \
+                        or nodes[ins["INPUT"][0]]["type"] != "INPUT":
+                    ok = False
+                    break
+                ish, wsh = g.shape(ins["INPUT"]), g.shape(ins["WEIGHT"])
+                bag = 1
+                for d in ish.sizes[1:]:
+                    bag *= d
+                if bag != 1 or ish.total_degree != 1 or wsh.total_degree != 1 or ish.sizes[0] != csh.sizes[0] \
+                        or wsh.sizes[1] != csh.sizes[2] or len(g.consumers(ins["WEIGHT"])) != 1:
+                    ok = False
+                    break
+                skipped.append(p["id"])
+                members.append({"embedding": p["id"], "weight": ins["WEIGHT"][0], "index": ins["INPUT"]})
+            idx_types = {g.shape(m["index"]).dtype for m in members}
+            if ok and len(members) == csh.sizes[1] and len(members) % W == 0 and len(idx_types) == 1:
+                groups.append({"repartition": nid, "members": members, "skipped": skipped})
+        return groups
+
+    def sparse_weight_nodes(self):
+        self.table_groups: List[dict] = []
+        self._table_index: Dict[int, int] = {}
+        self._group_embeddings = set()
+        if self.ctx.world_size > 1 and self.fuse_collectives:
+            self.table_groups = self._find_table_groups()
+            for grp in self.table_groups:
+                for t, m in enumerate(grp["members"]):
+                    self._table_index[m["weight"]] = t
+                    self._group_embeddings.add(m["embedding"])
+        out = super().sparse_weight_nodes()
+        if not out:
+            self.table_groups = []  # the optimizer is not plain SGD: tables stay in the dense arenas
+        return out
+
+    def sparse_embedding_allowed(self, embedding_nid: int) -> bool:
+        # a replicated (data-parallel) table cannot take per-rank sparse updates; a model-parallel one can
+        return embedding_nid in self._group_embeddings
+
+    def owns_sparse_table(self, nid: int) -> bool:
+        return self._table_index[nid] % self.ctx.world_size == self.ctx.rank
+
     def _fuse(self):
         super()._fuse()
         W = self.ctx.world_size
         if W == 1:
             return
+        for grp in getattr(self, "table_groups", ()):
+            for nid in grp["skipped"]:
+                self.ops[nid] = E.SkippedOp(self, nid, self.nodes[nid])
+            op = AllToAllEmbeddingOp(self, grp["repartition"], self.nodes[grp["repartition"]])
+            op.group = grp
+            self.ops[grp["repartition"]] = op
         g = self.graph
         bf16 = self.cfg.compute_dtype == "bf16"
 
@@ -587,6 +695,8 @@ class DistExecutable(Executable):
                     kinds.add("tp")
                 elif sh.degrees and sh.degrees[0] > 1:
                     kinds.add("dp")
+        if getattr(self, "table_groups", None):
+            kinds.add("tables_mp")
         if not kinds:
             return f"replicated{W}"
         return "+".join(f"{k}{W}" for k in sorted(kinds))

@@ -70,6 +70,11 @@ class ExecConfig:
     # is faster when the memory is there: 329.9 vs 371.8 ms per step on the large Transformer with 32 MB blocks --
     # many small kernels with partial last waves cost more than the HBM round trips they avoid.
     attention_block_bytes: int = 0
+    # Embedding tables trained by plain SGD (no momentum, no weight decay) are kept as fp32 tables outside the
+    # parameter arenas and updated row by row from the output gradient inside the Embedding's backward, so a
+    # step touches batch x dim elements of a table instead of the whole table three times (gradient clear,
+    # dense scatter target, dense update).
+    sparse_embedding_update: bool = True
 
 
 class _Buf:
@@ -859,13 +864,17 @@ class EmbeddingOp(OpImpl):
         self.aggr = "avg" if self.attrs.get("aggr") == "AVG" else "sum"
         self.alloc_out()
         self.table = self.x("WEIGHT")
+        self.sparse = self.inputs["WEIGHT"][0] in self.ex.sparse_tables
 
     def forward(self):
         K.embedding_fwd(self.x(), self.table, self.out().data, aggr=self.aggr)
 
     def backward(self):
         wb = self.buf("WEIGHT")
-        if wb.requires_grad:
+        if self.sparse:
+            # table[idx] -= lr * d(out): the update itself, no table-sized gradient exists
+            K.embedding_sgd(self.x(), self.out().grad.view_as(self.out().data), self.table, self.ex.cfg.optimizer.lr, aggr=self.aggr)
+        elif wb.requires_grad:
             if not self.acc["WEIGHT"]:
                 wb.grad.zero_()
             K.embedding_bwd(self.x(), self.out().grad.view_as(self.out().data), wb.grad, aggr=self.aggr)
@@ -1076,9 +1085,34 @@ class Executable:
         self._big = [torch.empty(max(self._big_scratch_bytes, 1), dtype=torch.uint8, device=self.device)
                      for _ in range(max(self._big_scratch_slots, 1))]
 
+    def sparse_weight_nodes(self) -> List[int]:
+        """Weights that are the table of exactly one Embedding and can take the sparse SGD update."""
+        o = self.cfg.optimizer
+        if not (self.cfg.training and self.cfg.sparse_embedding_update and o.kind == "sgd" and o.momentum == 0
+                and o.weight_decay == 0):
+            return []
+        out = []
+        for nid in self.order:
+            if self.nodes[nid]["type"] != "WEIGHT":
+                continue
+            cons = self.graph.consumers((nid, "OUTPUT"))
+            if len(cons) == 1 and cons[0][1] == "WEIGHT" and self.nodes[cons[0][0]]["type"] == "EMBEDDING" \
+                    and self.sparse_embedding_allowed(cons[0][0]):
+                out.append(nid)
+        return out
+
+    def sparse_embedding_allowed(self, embedding_nid: int) -> bool:
+        return True
+
+    def owns_sparse_table(self, nid: int) -> bool:
+        """Does this rank hold the sparsely updated table `nid`?  (Model-parallel tables live on one rank each.)"""
+        return True
+
     def _build_params(self):
         nodes, dev = self.nodes, self.device
-        self.param_nodes = self.order_params([nid for nid in self.order if nodes[nid]["type"] == "WEIGHT"])
+        sparse = set(self.sparse_weight_nodes())
+        self.sparse_tables: Dict[int, Optional[torch.Tensor]] = {}
+        self.param_nodes = self.order_params([nid for nid in self.order if nodes[nid]["type"] == "WEIGHT" and nid not in sparse])
         ordinal = {nid: i for i, nid in enumerate(nid for nid in self.order if nodes[nid]["type"] == "WEIGHT")}
         offs, total = {}, 0
         for nid in self.param_nodes:
@@ -1110,6 +1144,15 @@ class Executable:
                 b.grad = self.grads[o:o + n].view(shape)
         if mixed:
             self.shadow.copy_(self.master)
+        for nid in sorted(sparse):
+            t = None
+            if self.owns_sparse_table(nid):
+                full = initialize(list(nodes[nid]["outputs"][0][1].sizes), nodes[nid]["attrs"].get("initializer"),
+                                  base_seed=self.cfg.seed, ordinal=ordinal[nid])
+                t = full.to(device=dev, dtype=torch.float32).contiguous()
+            self.sparse_tables[nid] = t
+            b = self.values[(nid, "OUTPUT")]
+            b.data, b.requires_grad = t, False
 
     # value aliasing: an operator that forwards its input unchanged shares data *and* gradient buffers with it
     def alias(self, nid: int, src: Value, slot: str = "OUTPUT"):
@@ -1487,6 +1530,9 @@ class Executable:
             o, n = self.param_offsets[nid]
             name = self.nodes[nid]["name"] or f"weight{nid}"
             yield name, self.master[o:o + n].view(self.local_weight_shape(nid))
+        for nid, t in self.sparse_tables.items():
+            if t is not None:
+                yield self.nodes[nid]["name"] or f"weight{nid}", t
 
     def named_gradients(self):
         for nid in self.param_nodes:
@@ -1496,6 +1542,9 @@ class Executable:
 
     def state_dict(self):
         sd = {"master": self.master, "step": self.step_count}
+        for nid, t in self.sparse_tables.items():
+            if t is not None:
+                sd[f"table.{self.nodes[nid]['name'] or nid}"] = t
         if self.cfg.training:
             if self.opt_m is not None:
                 sd["opt_m"] = self.opt_m
@@ -1508,6 +1557,10 @@ class Executable:
         if self.shadow is not None:
             self.shadow.copy_(self.master)
         self.step_count = int(sd.get("step", 0))
+        for nid, t in self.sparse_tables.items():
+            key = f"table.{self.nodes[nid]['name'] or nid}"
+            if t is not None and key in sd:
+                t.copy_(sd[key])
         if self.cfg.training:
             if "opt_m" in sd and self.opt_m is not None:
                 self.opt_m.copy_(sd["opt_m"])

@@ -110,6 +110,12 @@ def gather_full_parameters(path: str) -> Dict[str, torch.Tensor]:
     out = {}
     for name, l in sd["layout"].items():
         out[name] = sd["master"][l["offset"]:l["offset"] + l["numel"]].view(l["shape"]).clone()
+    # sparsely updated embedding tables are stored whole, under "table.<name>", by the rank that owns them
+    for fn in sorted(x for x in os.listdir(path) if re.fullmatch(r"rank\d+\.pt", x)):
+        other = sd if fn == "rank0.pt" else torch.load(os.path.join(path, fn), map_location="cpu", weights_only=False)
+        for k, v in other.items():
+            if isinstance(k, str) and k.startswith("table."):
+                out[k[len("table."):]] = v.to(torch.float32)
     return out
 
 
@@ -125,6 +131,12 @@ def load_resharded(path: str, executable) -> dict:
         o, n = executable.param_offsets[nid]
         shard = executable.shard_weight(nid, full[name].view(list(executable.nodes[nid]["outputs"][0][1].sizes)))
         executable.master[o:o + n].copy_(shard.reshape(-1))
+    for nid, t in getattr(executable, "sparse_tables", {}).items():
+        name = executable.nodes[nid]["name"] or str(nid)
+        if t is not None:
+            if name not in full:
+                raise CheckpointError(f"embedding table {name} is not in the checkpoint")
+            t.copy_(full[name].view(t.shape))
     if executable.shadow is not None:
         executable.shadow.copy_(executable.master)
     with open(os.path.join(path, "meta.json")) as f:

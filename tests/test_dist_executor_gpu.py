@@ -148,3 +148,52 @@ def test_data_parallel_convolution_stack_and_dlrm_match_single_gpu(which):
         for x, y in zip(out["single"], out["multi"]):
             assert abs(x - y) < 5e-2 * abs(x) + 1e-3, out
         assert out["multi"][-1] < out["multi"][0], out
+
+
+def w_dlrm_tables(ctx):
+    """Embedding tables model-parallel (one all-to-all kernel in each direction), MLPs data-parallel."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.compiler import strategy as S
+    from flexflow_train_b200.parallel.dist_executor import AllToAllEmbeddingOp, DistExecutable
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+
+    cfg = {"batch_size": 64, "embedding_dim": 16, "embedding_bag_size": 1, "embedding_size": [500, 300, 200, 100],
+           "dense_arch_layer_sizes": [13, 32, 16], "over_arch_layer_sizes": [48, 32, 1], "arch_interaction_op": "DOT",
+           "final_activation": "SIGMOID", "embedding_data_type": "FLOAT"}
+    cg = core.build_model("dlrm", cfg)
+    pcg = S.table_parallel_strategy(cg, ctx.world_size)
+    opt = OptimizerConfig(kind="sgd", lr=0.05, momentum=0.0)
+    ecfg = dict(compute_dtype="bf16", seed=2, optimizer=opt, device=f"cuda:{ctx.rank}", loss="mean_squared_error_avg_reduce")
+    single = Executable(cg, ExecConfig(**ecfg))
+    multi = DistExecutable(pcg, ExecConfig(use_cuda_graph=True, **ecfg), ctx)
+    torch.manual_seed(0)
+    ins = {"dense": torch.randn(64, 13, device=ctx.device)}
+    for i, n in enumerate(cfg["embedding_size"]):
+        ins[f"sparse{i}"] = torch.randint(0, n, (64, 1), device=ctx.device)
+    labels = torch.rand(64, 1, device=ctx.device)
+    a, b = [], []
+    for _ in range(6):
+        single.train_step(ins, labels)
+        a.append(single.mean_loss())
+        multi.train_step(ins, labels)
+        b.append(multi.mean_loss())
+    ctx.check_status()
+    names = {single.nodes[n]["name"]: t for n, t in single.sparse_tables.items()}
+    owned = {multi.nodes[n]["name"]: t for n, t in multi.sparse_tables.items() if t is not None}
+    diff = max(float((names[k] - t).abs().max()) for k, t in owned.items())
+    moved = max(float((t - t.mean()).abs().max()) for t in owned.values())
+    return {"single": a, "multi": b, "parallelism": multi.parallelism, "owned": sorted(owned), "table_diff": diff, "moved": moved,
+            "a2a_ops": sum(isinstance(o, AllToAllEmbeddingOp) for o in multi.ops.values()), "graph": bool(multi.cfg.use_cuda_graph),
+            "dense_params": int(multi.num_params)}
+
+
+def test_model_parallel_embedding_tables_match_single_gpu():
+    res = _run("test_dist_executor_gpu:w_dlrm_tables")
+    for r, out in res.items():
+        assert out["parallelism"] == "dp2+tables_mp2" and out["a2a_ops"] == 1 and out["graph"], out
+        assert out["owned"] == [f"emb{r}.weight", f"emb{r + 2}.weight"], out   # table t lives on rank t % world
+        assert out["dense_params"] < 20000, out                                # no table in the dense arenas
+        for x, y in zip(out["single"], out["multi"]):
+            assert abs(x - y) < 5e-2 * abs(x) + 1e-3, out
+        assert out["table_diff"] < 2e-3, out
+        assert out["multi"][-1] < out["multi"][0], out

@@ -240,3 +240,41 @@ def test_dropout_backward_folded_into_linear_backward_gives_the_same_gradients()
         grads.append({k: v.float().clone() for k, v in ex.named_gradients()})
     for k in grads[0]:
         assert rel(grads[1][k], grads[0][k]) < 2e-2, (k, rel(grads[1][k], grads[0][k]))
+
+
+def test_sparse_embedding_update_matches_the_dense_update():
+    """Plain SGD on an embedding table: rows updated from the output gradient inside the Embedding's backward give the
+    same training as the dense table gradient + dense update, and the table then lives outside the parameter arenas."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+
+    cfg = {"batch_size": 64, "embedding_dim": 16, "embedding_bag_size": 1, "embedding_size": [500, 300],
+           "dense_arch_layer_sizes": [13, 32, 16], "over_arch_layer_sizes": [48, 32, 1], "arch_interaction_op": "DOT",
+           "final_activation": "SIGMOID", "embedding_data_type": "FLOAT"}
+    cg = core.build_model("dlrm", cfg)
+    opt = OptimizerConfig(kind="sgd", lr=0.05, momentum=0.0)
+    mk = lambda sparse: Executable(cg, ExecConfig(compute_dtype="bf16", seed=2, optimizer=opt, loss="mean_squared_error_avg_reduce",
+                                                  sparse_embedding_update=sparse))
+    dense, sparse = mk(False), mk(True)
+    assert not dense.sparse_tables and len(sparse.sparse_tables) == 2
+    assert sparse.num_params < dense.num_params - 800 * 16 + 128
+    torch.manual_seed(0)
+    ins = {"dense": torch.randn(64, 13, device="cuda"), "sparse0": torch.randint(0, 500, (64, 1), device="cuda"),
+           "sparse1": torch.randint(0, 300, (64, 1), device="cuda")}
+    labels = torch.rand(64, 1, device="cuda")
+    for _ in range(5):
+        dense.train_step(ins, labels)
+        sparse.train_step(ins, labels)
+        assert abs(dense.mean_loss() - sparse.mean_loss()) < 3e-2 * abs(dense.mean_loss()) + 1e-4
+    d = dict(dense.named_parameters())
+    s = dict(sparse.named_parameters())
+    for name in ("emb0.weight", "emb1.weight"):
+        assert s[name].dtype == torch.float32
+        # the dense path rounds the table gradient to bf16 before the update; the sparse path does not
+        assert float((d[name] - s[name]).abs().max()) < 2e-3
+    sd = sparse.state_dict()
+    assert "table.emb0.weight" in sd
+    # a momentum optimizer keeps the dense path
+    mom = Executable(cg, ExecConfig(compute_dtype="bf16", seed=2, optimizer=OptimizerConfig(kind="sgd", lr=0.05, momentum=0.9),
+                                    loss="mean_squared_error_avg_reduce"))
+    assert not mom.sparse_tables

@@ -143,3 +143,38 @@ def test_data_parallel_strategy_shards_every_operator_of_every_model_family():
         moves = [n for n in g.nodes() if n["type"] in ("REPARTITION", "COMBINE")
                  and nodes[n["inputs"][0][1][0]]["type"] != "WEIGHT" and not c.is_parallel_op(nodes[n["inputs"][0][1][0]]["type"])]
         assert len(moves) <= n_inputs + max(n_sinks, 2), (name, len(moves))
+
+
+def test_table_parallel_strategy_keeps_lookups_whole_and_shards_the_rest():
+    """Recommendation-model layout: Embeddings and the Concat stacking them stay unpartitioned (placed per table),
+    one Repartition(0) hands the stack to the data-parallel rest, and no table is replicated."""
+    cfg = {"batch_size": 64, "embedding_dim": 16, "embedding_bag_size": 1, "embedding_size": [500, 300, 200, 100],
+           "dense_arch_layer_sizes": [13, 32, 16], "over_arch_layer_sizes": [48, 32, 1], "arch_interaction_op": "DOT",
+           "embedding_data_type": "FLOAT"}
+    cg = c.build_model("dlrm", cfg)
+    assert S.has_stacked_embeddings(cg)
+    g = S.table_parallel_strategy(cg, 4)
+    nodes = {n["id"]: n for n in g.nodes()}
+    embs = [n for n in nodes.values() if n["type"] == "EMBEDDING"]
+    assert len(embs) == 4
+    for e in embs:
+        assert e["outputs"][0][1].total_degree == 1
+        w = dict((s, tuple(v)) for s, v in e["inputs"])["WEIGHT"]
+        assert nodes[w[0]]["type"] == "WEIGHT"  # no Replicate / Repartition between the table and its lookup
+    stacks = [n for n in nodes.values() if n["type"] == "CONCAT" and n["outputs"][0][1].total_degree == 1]
+    assert len(stacks) == 1
+    cons = g.consumers((stacks[0]["id"], "OUTPUT"))
+    assert len(cons) == 1 and nodes[cons[0][0]]["type"] == "REPARTITION"
+    rep = nodes[cons[0][0]]
+    assert rep["outputs"][0][1].degrees[0] == 4
+    for n in nodes.values():
+        if n["type"] == "LINEAR":
+            assert n["outputs"][0][1].degrees[0] == 4
+    # the search offers it as a candidate next to pure data parallelism, and it is far cheaper than replicating tables
+    r = S.optimize(cg, world=4)
+    cands = r["stats"]["candidates"]
+    assert "dp4+tables_mp4" in cands and cands["dp4+tables_mp4"] <= cands["dp4"]
+    forced = S.optimize(cg, world=4, algorithm="table_parallel")
+    assert forced["stats"]["seed_strategy"] == "dp4+tables_mp4"
+    with pytest.raises(ValueError):
+        S.table_parallel_strategy(c.build_model("mlp", {}), 2)
