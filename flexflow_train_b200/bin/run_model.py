@@ -51,7 +51,8 @@ def synthetic_batch(graph, executable, loss: str, seed: int = 0, pinned: bool = 
             t = torch.randn(sizes, generator=gen)
         inputs[name] = t.pin_memory() if pinned and torch.cuda.is_available() else t
     lv = executable.loss_value
-    lsizes = [int(s) for s in graph.shape(lv).sizes] if lv is not None else [1, 1]
+    # the loss value is a node of the executable's own (possibly parallel) graph; `sizes` are its global sizes
+    lsizes = [int(s) for s in executable.graph.shape(lv).sizes] if lv is not None else [1, 1]
     rows = 1
     for s in lsizes[:-1]:
         rows *= s
@@ -75,7 +76,7 @@ def main(argv=None) -> int:
     p.add_argument("--optimizer", choices=["sgd", "adam"], default="adam")
     p.add_argument("--search-budget", type=int, default=0)
     p.add_argument("--search-alpha", type=float, default=1.05)
-    p.add_argument("--search-algorithm", choices=["unity", "mcmc", "data_parallel", "tensor_parallel"], default="unity")
+    p.add_argument("--search-algorithm", choices=["unity", "mcmc", "data_parallel", "tensor_parallel", "table_parallel"], default="unity")
     p.add_argument("--only-data-parallel", action="store_true")
     p.add_argument("--enable-parameter-parallel", action="store_true")
     p.add_argument("--enable-attribute-parallel", action="store_true")

@@ -706,35 +706,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
 
 // ----------------------------------------------------------------------------
 // General-shape fallback.  TMA needs 16-byte aligned bases and row pitches; operands that cannot offer
-// that (a 10-class classifier head, odd feature counts) take this plain shared-memory-tiled kernel.
-// Same semantics and epilogue as the tensor-core kernel; it is not a hot path.
+// that (a 10-class classifier head, odd feature counts) take this shared-memory-tiled CUDA-core kernel.
+// Same semantics and epilogue as the tensor-core kernel.
 // ----------------------------------------------------------------------------
 struct SimtOperands {
   const void *A, *B;
   long long lda, a_sh, a_sb, ldb, b_sh, b_sb;
   int a_mn, b_mn;
+  int kw;           // warps sharing one tile (splitting k): 1, 2, 4 or 8
+  int group_batch;  // the block's 8 / kw tiles are consecutive batch entries (else consecutive row tiles)
 };
-template <typename T>
-__global__ void gemm_simt_kernel(SimtOperands o, GemmArgs p) {
-  __shared__ float sa[16][17], sb[16][17];
-  const int batch = blockIdx.z, bh = batch % p.nh, bb = batch / p.nh;
-  const T *A = (const T *)o.A + (long long)bh * o.a_sh + (long long)bb * o.a_sb;
-  const T *B = (const T *)o.B + (long long)bh * o.b_sh + (long long)bb * o.b_sb;
-  const int tx = threadIdx.x, ty = threadIdx.y;
-  const int m = blockIdx.y * 16 + ty, n = blockIdx.x * 16 + tx;
-  float acc = 0.f;
-  for (int k0 = 0; k0 < p.K; k0 += 16) {
-    int am = blockIdx.y * 16 + ty, ak = k0 + tx;
-    sa[ty][tx] = (am < p.M && ak < p.K) ? (float)(o.a_mn ? A[(long long)ak * o.lda + am] : A[(long long)am * o.lda + ak]) : 0.f;
-    int bn_ = blockIdx.x * 16 + ty, bk = k0 + tx;
-    sb[ty][tx] = (bn_ < p.N && bk < p.K) ? (float)(o.b_mn ? B[(long long)bk * o.ldb + bn_] : B[(long long)bn_ * o.ldb + bk]) : 0.f;
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < 16; ++k) acc += sa[ty][k] * sb[tx][k];
-    __syncthreads();
-  }
-  if (m >= p.M || n >= p.N) return;
-  float v = acc * p.alpha;
+// alpha, bias, pre-activation copy, activation, addend, accumulate, store: the tensor-core kernel's epilogue for one value
+__device__ __forceinline__ void simt_epilogue(const GemmArgs &p, float v, int bh, int bb, int m, int n) {
+  v *= p.alpha;
   if (p.bias) v += ld_aux(p.bias, n, p.aux_fp32);
   const long long coff = (long long)bh * p.c_sh + (long long)bb * p.c_sb + (long long)m * p.ldc + n;
   if (p.C2) st_aux(p.C2, coff, p.aux_fp32, v);
@@ -746,6 +730,173 @@ __global__ void gemm_simt_kernel(SimtOperands o, GemmArgs p) {
   } else {
     bf16 *c = (bf16 *)p.C + coff;
     *c = f2bf(p.accumulate ? bf2f(*c) + v : v);
+  }
+}
+
+// A block has 8 warps and works on 32x32 output tiles.  `kw` warps (1, 2, 4 or 8) share one tile and split its
+// k range in chunks of 32 (chunk c goes to k-slot c % kw); the block's 8 / kw tiles are consecutive batch
+// entries (small batched problems) or consecutive row tiles.  Warps work without block-wide barriers: a warp
+// loads its next chunk of A and B into registers (all 64 loads in flight, coalesced along whichever dim is
+// contiguous) while it computes on the chunk staged in its own shared-memory region, every lane accumulating
+// one output row of 32 values.  The partial tiles of the warps sharing a tile are summed through shared memory
+// at the end.  A weight-gradient GEMM with a small output and a long reduction dim (the batch) thereby still has
+// 8 warps per tile in flight, a GEMM with a tiny k costs one chunk, and a batch of tiny problems fills its blocks.
+constexpr int ST = 32;
+constexpr int SIMT_WARPS = 8;
+constexpr int SA_LD = 33;  // lane-indexed reads and transposed writes without bank conflicts
+constexpr int SB_LD = 36;  // rows read as float4
+constexpr int SIMT_WARP_FLOATS = ST * SA_LD + ST * SB_LD;
+constexpr int SIMT_SMEM_BYTES = SIMT_WARPS * SIMT_WARP_FLOATS * 4;
+
+template <typename T>
+__device__ __forceinline__ void simt_fetch(float (&r)[ST], const T *X, long long ld, int mn_major, int k0, int x0, int lane, int K, int X_extent) {
+  if (mn_major) {  // X[k][x]: lanes along x, registers along k
+    const int x = x0 + lane;
+#pragma unroll
+    for (int i = 0; i < ST; ++i) {
+      const int k = k0 + i;
+      r[i] = (k < K && x < X_extent) ? (float)X[(long long)k * ld + x] : 0.f;
+    }
+  } else {         // X[x][k]: lanes along k, registers along x
+    const int k = k0 + lane;
+#pragma unroll
+    for (int i = 0; i < ST; ++i) {
+      const int x = x0 + i;
+      r[i] = (k < K && x < X_extent) ? (float)X[(long long)x * ld + k] : 0.f;
+    }
+  }
+}
+// stage as s[k][x] with row pitch LD
+template <int LD>
+__device__ __forceinline__ void simt_stage(float *s, const float (&r)[ST], int mn_major, int lane) {
+  if (mn_major) {
+#pragma unroll
+    for (int i = 0; i < ST; ++i) s[i * LD + lane] = r[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < ST; ++i) s[lane * LD + i] = r[i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SIMT_WARPS * 32, 2) gemm_simt_kernel(SimtOperands o, GemmArgs p) {
+  extern __shared__ __align__(16) float simt_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float *sa = simt_smem + warp * SIMT_WARP_FLOATS, *sb = sa + ST * SA_LD;
+  const int kw = o.kw, ti = warp / kw, ks = warp % kw, tpb = SIMT_WARPS / kw;
+  int batch = blockIdx.z, tile_m = blockIdx.y;
+  if (o.group_batch) batch = blockIdx.z * tpb + ti;
+  else tile_m = blockIdx.y * tpb + ti;
+  const int m0 = tile_m * ST, n0 = blockIdx.x * ST;
+  const bool active = batch < p.nh * p.nb && m0 < p.M;
+  const int bh = batch % p.nh, bb = batch / p.nh;
+  const T *A = (const T *)o.A + (long long)bh * o.a_sh + (long long)bb * o.a_sb;
+  const T *B = (const T *)o.B + (long long)bh * o.b_sh + (long long)bb * o.b_sb;
+  float acc[ST];
+#pragma unroll
+  for (int i = 0; i < ST; ++i) acc[i] = 0.f;
+  if (active) {
+    const int chunks = (p.K + ST - 1) / ST;
+    float ra[ST], rb[ST];
+    if (ks < chunks) {
+      simt_fetch<T>(ra, A, o.lda, o.a_mn, ks * ST, m0, lane, p.K, p.M);
+      simt_fetch<T>(rb, B, o.ldb, o.b_mn, ks * ST, n0, lane, p.K, p.N);
+    }
+    for (int c = ks; c < chunks; c += kw) {
+      simt_stage<SA_LD>(sa, ra, o.a_mn, lane);
+      simt_stage<SB_LD>(sb, rb, o.b_mn, lane);
+      __syncwarp();
+      if (c + kw < chunks) {  // next chunk's loads fly while this one is computed
+        simt_fetch<T>(ra, A, o.lda, o.a_mn, (c + kw) * ST, m0, lane, p.K, p.M);
+        simt_fetch<T>(rb, B, o.ldb, o.b_mn, (c + kw) * ST, n0, lane, p.K, p.N);
+      }
+      const int kmax = min(ST, p.K - c * ST);  // a short (last) chunk costs only its own k steps
+#pragma unroll 2
+      for (int k = 0; k < kmax; ++k) {
+        const float a = sa[k * SA_LD + lane];
+        const float4 *bv = reinterpret_cast<const float4 *>(sb + k * SB_LD);
+#pragma unroll
+        for (int j = 0; j < ST / 4; ++j) {
+          const float4 b = bv[j];
+          acc[4 * j + 0] += a * b.x;
+          acc[4 * j + 1] += a * b.y;
+          acc[4 * j + 2] += a * b.z;
+          acc[4 * j + 3] += a * b.w;
+        }
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();  // every warp is done with its staging region: reuse the memory for the partial tiles
+  float *red = simt_smem;  // [warp][m][SA_LD]
+#pragma unroll
+  for (int n = 0; n < ST; ++n) red[(warp * ST + lane) * SA_LD + n] = acc[n];
+  __syncthreads();
+  if (!active) return;
+  const int n = n0 + lane;
+  for (int ml = ks; ml < ST; ml += kw) {
+    const int m = m0 + ml;
+    if (m >= p.M || n >= p.N) continue;
+    float v = 0.f;
+    for (int w = ti * kw; w < ti * kw + kw; ++w) v += red[(w * ST + ml) * SA_LD + lane];
+    simt_epilogue(p, v, bh, bb, m, n);
+  }
+}
+
+// Batches of small problems (an interaction layer's 9x9x64 products): one warp per batch entry.  The warp
+// stages its A[M,K] and B[N,K] panels in shared memory (row pitch K+1, so rows start in different banks), then
+// every lane computes whole outputs, lane l the outputs l, l+32, ... in row-major order.  Index arithmetic is
+// incremental (no divisions), so a 9x9x64 product costs a few hundred instructions per warp.
+constexpr int SB_WARPS = 8;
+constexpr int SB_FLOATS = 2304;  // per warp: (M + N) * (K + 1) floats
+constexpr int SB_SMEM_BYTES = SB_WARPS * SB_FLOATS * 4;
+
+template <typename T>
+__device__ __forceinline__ void small_stage(float *s, const T *X, int rows, int K, long long ld, int mn_major, int lane) {
+  const int ldk = K + 1;
+  if (!mn_major) {  // X[x][k]: k runs fastest
+    int x = 0, k = lane;
+    while (k >= K) { k -= K; ++x; }
+    while (x < rows) {
+      s[x * ldk + k] = (float)X[(long long)x * ld + k];
+      k += 32;
+      while (k >= K) { k -= K; ++x; }
+    }
+  } else {          // X[k][x]: x runs fastest
+    int k = 0, x = lane;
+    while (x >= rows) { x -= rows; ++k; }
+    while (k < K) {
+      s[x * ldk + k] = (float)X[(long long)k * ld + x];
+      x += 32;
+      while (x >= rows) { x -= rows; ++k; }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SB_WARPS * 32) gemm_small_batched_kernel(SimtOperands o, GemmArgs p) {
+  extern __shared__ __align__(16) float simt_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int batch = blockIdx.x * SB_WARPS + warp;
+  if (batch >= p.nh * p.nb) return;  // warps never meet at a block-wide barrier
+  const int bh = batch % p.nh, bb = batch / p.nh;
+  const T *A = (const T *)o.A + (long long)bh * o.a_sh + (long long)bb * o.a_sb;
+  const T *B = (const T *)o.B + (long long)bh * o.b_sh + (long long)bb * o.b_sb;
+  const int ldk = p.K + 1;
+  float *sa = simt_smem + warp * SB_FLOATS, *sb = sa + p.M * ldk;
+  small_stage<T>(sa, A, p.M, p.K, o.lda, o.a_mn, lane);
+  small_stage<T>(sb, B, p.N, p.K, o.ldb, o.b_mn, lane);
+  __syncwarp();
+  int m = 0, n = lane;
+  while (n >= p.N) { n -= p.N; ++m; }
+  while (m < p.M) {
+    const float *ar = sa + m * ldk, *br = sb + n * ldk;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < p.K; ++k) acc += ar[k] * br[k];
+    simt_epilogue(p, acc, bh, bb, m, n);
+    n += 32;
+    while (n >= p.N) { n -= p.N; ++m; }
   }
 }
 
@@ -930,7 +1081,12 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
   bool tma_ok = !(((uintptr_t)d->A & 15) || ((uintptr_t)d->B & 15)) && !((d->lda * es) % 16 || (d->ldb * es) % 16) &&
                 !((d->nh > 1 && ((d->a_sh * es) % 16 || (d->b_sh * es) % 16)) || (d->nb > 1 && ((d->a_sb * es) % 16 || (d->b_sb * es) % 16))) &&
                 !(es == 4 && (d->a_mn || d->b_mn));  // tf32 operands must be K-major
-  if (!tma_ok) {
+  const bool fused = d->scatter_rows || d->gate_flags || d->push_src || d->drop_p > 0.f;
+  // many small problems: one warp each on the CUDA cores beats one mostly empty 128-row tensor-core tile each
+  const long long nbatch = (long long)(d->nh < 1 ? 1 : d->nh) * (d->nb < 1 ? 1 : d->nb);
+  const bool small_batched = !fused && nbatch >= 32 && (long long)d->M * d->N <= 1024 &&
+                             (long long)(d->M + d->N) * (d->K + 1) <= SB_FLOATS;
+  if (!tma_ok || small_batched) {
     GemmArgs a;
     a.M = d->M; a.N = d->N; a.K = d->K; a.nh = d->nh < 1 ? 1 : d->nh; a.nb = d->nb < 1 ? 1 : d->nb;
     a.C = d->C; a.ldc = d->ldc; a.c_sh = d->c_sh; a.c_sb = d->c_sb;
@@ -938,11 +1094,39 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     a.ld_add = d->ld_add; a.add_sh = d->add_sh; a.add_sb = d->add_sb;
     a.alpha = d->alpha; a.act = d->act; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate; a.aux_fp32 = es == 4;
     a.tiles_m = a.tiles_n = 0; a.num_tiles = 0; a.err = nullptr; a.split_k = 1; a.kb_per_split = 0; a.push_src = nullptr; a.drop_p = 0.f; a.tma_store = 0;
-    if (d->scatter_rows || d->gate_flags || d->push_src || d->drop_p > 0.f) return -2;  // the fused-collective paths need TMA-addressable operands
-    SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn};
-    dim3 grid((d->N + 15) / 16, (d->M + 15) / 16, a.nh * a.nb), block(16, 16);
-    if (es == 2) gemm_simt_kernel<bf16><<<grid, block, 0, stream>>>(o, a);
-    else gemm_simt_kernel<float><<<grid, block, 0, stream>>>(o, a);
+    if (fused) return -2;  // the fused-collective paths need TMA-addressable operands
+    if (small_batched) {
+      static bool sb_attr = false;
+      if (!sb_attr) {
+        if (cudaFuncSetAttribute(gemm_small_batched_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_small_batched_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM_BYTES) != cudaSuccess)
+          return (int)cudaGetLastError();
+        sb_attr = true;
+      }
+      SimtOperands so{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn, 1, 1};
+      const int blocks = (int)((nbatch + SB_WARPS - 1) / SB_WARPS);
+      if (es == 2) gemm_small_batched_kernel<bf16><<<blocks, SB_WARPS * 32, SB_SMEM_BYTES, stream>>>(so, a);
+      else gemm_small_batched_kernel<float><<<blocks, SB_WARPS * 32, SB_SMEM_BYTES, stream>>>(so, a);
+      return (int)cudaGetLastError();
+    }
+    const int chunks = (d->K + ST - 1) / ST, tiles_m = (d->M + ST - 1) / ST, nbatch = a.nh * a.nb;
+    int kw = 1;
+    while (kw < SIMT_WARPS && kw < chunks) kw *= 2;
+    const int tpb = SIMT_WARPS / kw;
+    const int group_batch = tiles_m == 1 && nbatch > 1;
+    SimtOperands o{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn, kw, group_batch};
+    static bool simt_attr = false;
+    if (!simt_attr) {
+      if (cudaFuncSetAttribute(gemm_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SIMT_SMEM_BYTES) != cudaSuccess ||
+          cudaFuncSetAttribute(gemm_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SIMT_SMEM_BYTES) != cudaSuccess)
+        return (int)cudaGetLastError();
+      simt_attr = true;
+    }
+    const int gy = group_batch ? tiles_m : (tiles_m + tpb - 1) / tpb, gz = group_batch ? (nbatch + tpb - 1) / tpb : nbatch;
+    if (gy > 65535 || gz > 65535) return -2;
+    dim3 grid((d->N + ST - 1) / ST, gy, gz), block(SIMT_WARPS * 32);
+    if (es == 2) gemm_simt_kernel<bf16><<<grid, block, SIMT_SMEM_BYTES, stream>>>(o, a);
+    else gemm_simt_kernel<float><<<grid, block, SIMT_SMEM_BYTES, stream>>>(o, a);
     return (int)cudaGetLastError();
   }
   int bn = d->bn;

@@ -161,6 +161,47 @@ def _cuda_contig(*ts):
 
 
 # --------------------------------------------------------------------------- GEMM
+_REPACK_SCRATCH = {}          # operand slot -> uint8 scratch (grows to the largest operand repacked so far)
+_REPACK_RETIRED = []          # outgrown scratches stay allocated: a captured CUDA graph may still address them
+_REPACK_MIN_FLOPS = 2.0e6     # below this the general-shape kernel is a single cheap launch anyway
+
+
+def _tma_addressable(ptr, ld, sh, sb, nh, nb, es) -> bool:
+    """TMA wants a 16-byte aligned base and pitches that are multiples of 16 bytes."""
+    if ptr % 16 or (ld * es) % 16:
+        return False
+    return not ((nh > 1 and (sh * es) % 16) or (nb > 1 and (sb * es) % 16))
+
+
+def _repack_operand(slot, ptr, ld, rows, cols, nh, sh, nb, sb, es):
+    """Copy an operand whose rows TMA cannot address into a scratch with the pitch rounded up to 16 bytes.
+    Returns (ptr, ld, sh, sb) of the copy, or None when the operand's batches are not evenly spaced rows.
+
+    The scratch is per operand slot and reused by later calls on the same stream; the copy is one small strided
+    kernel, after which odd feature counts (13 dense features, a 145-wide concatenation, a 9 x 9 interaction)
+    run on the tensor cores instead of the general-shape kernel."""
+    batches = max(nh, 1) * max(nb, 1)
+    if batches > 1:
+        if nh > 1 and nb > 1:
+            if sh != rows * ld or sb != nh * sh:
+                return None
+        elif (nh > 1 and sh != rows * ld) or (nb > 1 and sb != rows * ld):
+            return None
+    pad = 16 // es
+    ld2 = (cols + pad - 1) // pad * pad
+    total_rows = batches * rows
+    need = total_rows * ld2 * es
+    dev = torch.cuda.current_device()
+    buf = _REPACK_SCRATCH.get((slot, dev))
+    if buf is None or buf.numel() < need:
+        if buf is not None:
+            _REPACK_RETIRED.append(buf)
+        buf = torch.empty(max(need, 1 << 20, 2 * (buf.numel() if buf is not None else 0)), dtype=torch.uint8, device=f"cuda:{dev}")
+        _REPACK_SCRATCH[(slot, dev)] = buf
+    _check(_tlib().ffk_block_copy(ptr, ld, buf.data_ptr(), ld2, total_rows, cols, es, 0, 0, _stream()), "ffk_block_copy(repack)")
+    return buf.data_ptr(), ld2, rows * ld2, (nh if nh > 1 else 1) * rows * ld2
+
+
 def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, nh=1, nb=1,
              a_sh=0, a_sb=0, b_sh=0, b_sb=0, c_sh=0, c_sb=0, C2=None, bias=None, addend=None,
              ld_add=0, add_sh=0, add_sb=0, alpha=1.0, act=0, out_fp32=False, accumulate=False,
@@ -171,6 +212,18 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
     scatter / scatter_rows / scatter_src: write each output tile into the owning rank's staging buffer
     (GEMM -> reduce-scatter).  gate_flags / gate_sync / gate_rows / mb_rotate: wait for pushed row blocks of A
     (all-gather -> GEMM)."""
+    plain = not scatter and gate_flags is None and push is None and dropout is None
+    # (batches of small problems have a kernel of their own that reads any layout: same condition as in ffk_gemm)
+    small_batched = max(nh, 1) * max(nb, 1) >= 32 and M * N <= 1024 and (M + N) * (K + 1) <= 2304
+    if plain and not small_batched and 2.0 * M * N * K * max(nh, 1) * max(nb, 1) >= _REPACK_MIN_FLOPS:
+        if not _tma_addressable(A, lda, a_sh, a_sb, nh, nb, es):
+            r = _repack_operand("A", A, lda, K if a_mn else M, M if a_mn else K, nh, a_sh, nb, a_sb, es)
+            if r is not None:
+                A, lda, a_sh, a_sb = r
+        if not _tma_addressable(B, ldb, b_sh, b_sb, nh, nb, es):
+            r = _repack_operand("B", B, ldb, K if b_mn else N, N if b_mn else K, nh, b_sh, nb, b_sb, es)
+            if r is not None:
+                B, ldb, b_sh, b_sb = r
     sc = (c_void_p * 8)(*([int(p) for p in scatter] + [None] * (8 - len(scatter)))) if scatter else (c_void_p * 8)()
     d = GemmDesc(M, N, K, nh, nb, es, int(a_mn), int(b_mn), A, lda, a_sh, a_sb, B, ldb, b_sh, b_sb,
                  C, ldc, c_sh, c_sb, C2, bias, addend, ld_add, add_sh, add_sb, alpha, act, int(out_fp32),

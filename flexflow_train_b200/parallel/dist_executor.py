@@ -380,16 +380,25 @@ class DistExecutable(Executable):
                     self._table_index[m["weight"]] = t
                     self._group_embeddings.add(m["embedding"])
         out = super().sparse_weight_nodes()
-        if not out:
+        if not all(m["weight"] in out for grp in self.table_groups for m in grp["members"]):
             self.table_groups = []  # the optimizer is not plain SGD: tables stay in the dense arenas
+            self._table_index = {}
         return out
 
     def sparse_embedding_allowed(self, embedding_nid: int) -> bool:
-        # a replicated (data-parallel) table cannot take per-rank sparse updates; a model-parallel one can
-        return embedding_nid in self._group_embeddings
+        """A model-parallel table can take sparse updates; so can one whose lookup runs unsharded on every rank
+        (all ranks then apply the same update from the same whole batch).  A table under a Replicate cannot: its
+        ranks see different samples and their row updates would have to be exchanged."""
+        if embedding_nid in self._group_embeddings:
+            return True
+        n = self.nodes[embedding_nid]
+        ins = {s: tuple(v) for s, v in n["inputs"]}
+        whole = all(self.graph.shape(v).total_degree == 1 for v in ins.values()) and n["outputs"][0][1].total_degree == 1
+        return whole and self.nodes[ins["WEIGHT"][0]]["type"] == "WEIGHT"
 
     def owns_sparse_table(self, nid: int) -> bool:
-        return self._table_index[nid] % self.ctx.world_size == self.ctx.rank
+        t = self._table_index.get(nid)
+        return True if t is None else t % self.ctx.world_size == self.ctx.rank
 
     def _fuse(self):
         super()._fuse()

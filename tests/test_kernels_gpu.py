@@ -87,6 +87,56 @@ def test_gemm_batched_strided():
     assert k.gemm_last_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 512, 13), (100, 1, 256), (37, 145, 4099), (9, 9, 64), (70, 33, 31)])
+def test_gemm_general_shape_kernel_all_layouts(M, N, K):
+    """Operands whose row pitch is not a multiple of 16 bytes cannot be described to TMA and take the CUDA-core
+    kernel: every layout, tiles cut by all three extents, the epilogue, batches and a long reduction dim."""
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    tol = 2e-2
+    assert rel(k.matmul_nt(a, b), ref) < tol
+    assert rel(k.matmul_nt(a, b, bias=bias, act="relu"), torch.relu(ref + bias.float())) < tol
+    bt = b.t().contiguous()  # [K, N]
+    assert rel(k.matmul_nn(a, bt), ref) < tol
+    at = a.t().contiguous()  # [K, M]
+    assert rel(k.matmul_tn(at, bt), ref) < tol
+    acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    k.matmul_tn(at, bt, out=acc, accumulate=True)
+    assert rel(acc, 1.0 + ref) < tol
+    if M * N <= 4096:  # a batch of small problems, strided
+        nb = 5
+        x = torch.randn(nb, M, K, device=DEV, dtype=torch.bfloat16)
+        w = torch.randn(nb, N, K, device=DEV, dtype=torch.bfloat16)
+        out = torch.empty(nb, M, N, device=DEV, dtype=torch.bfloat16)
+        k.gemm_raw(M=M, N=N, K=K, A=x.data_ptr(), lda=K, a_sb=M * K, B=w.data_ptr(), ldb=K, b_sb=N * K, C=out.data_ptr(), ldc=N,
+                   c_sb=M * N, nb=nb)
+        assert rel(out, torch.einsum("bmk,bnk->bmn", x.float(), w.float())) < tol
+    assert k.gemm_last_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(9, 9, 64), (64, 9, 9), (9, 64, 9), (32, 32, 35), (1, 7, 130)])
+def test_gemm_batches_of_small_problems(M, N, K):
+    """One warp per problem: K-major and MN-major operands, aligned or not, with the epilogue."""
+    torch.manual_seed(7)
+    nb = 300
+    x = torch.randn(nb, M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(nb, N, K, device=DEV, dtype=torch.bfloat16)
+    ref = torch.einsum("bmk,bnk->bmn", x.float(), w.float())
+    out = torch.empty(nb, M, N, device=DEV, dtype=torch.bfloat16)
+    k.gemm_raw(M=M, N=N, K=K, A=x.data_ptr(), lda=K, a_sb=M * K, B=w.data_ptr(), ldb=K, b_sb=N * K, C=out.data_ptr(), ldc=N, c_sb=M * N, nb=nb)
+    assert rel(out, ref) < 1e-2
+    xt = x.transpose(1, 2).contiguous()  # [nb, K, M]
+    wt = w.transpose(1, 2).contiguous()  # [nb, K, N]
+    acc = torch.ones(nb, M, N, device=DEV, dtype=torch.float32)
+    k.gemm_raw(M=M, N=N, K=K, A=xt.data_ptr(), lda=M, a_mn=True, a_sb=M * K, B=wt.data_ptr(), ldb=N, b_mn=True, b_sb=N * K,
+               C=acc.data_ptr(), ldc=N, c_sb=M * N, nb=nb, out_fp32=True, accumulate=True, alpha=0.5)
+    assert rel(acc, 1.0 + 0.5 * ref) < 1e-2
+    assert k.gemm_last_error() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_unary_binary(dtype):
     torch.manual_seed(6)
