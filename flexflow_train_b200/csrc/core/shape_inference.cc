@@ -205,10 +205,14 @@ Inferred infer_shapes(OpType type, const Json &a, const SlotShapes &in) {
       int64_t sh = a.at("stride_h").as_int(), sw = a.at("stride_w").as_int();
       int64_t ph = a.at("padding_h").as_int(), pw = a.at("padding_w").as_int();
       int64_t groups = a.get_int("groups", 1);
-      require(groups == 1, "conv2d: groups must be 1");
+      require(groups >= 1, "conv2d: groups must be positive");
       require(x.dims[2].degree == 1 && x.dims[3].degree == 1, "conv2d: spatial dims cannot be sharded");
       int nd = x.dims[0].degree, cd = x.dims[1].degree;
       int64_t ic = x.dims[1].size;
+      // (the reference's shape inference asserts groups == 1, lib/op-attrs/src/op-attrs/ops/conv_2d.cc; grouped
+      // convolutions are accepted here as long as the channel dims stay whole)
+      require(groups == 1 || (ic % groups == 0 && oc % groups == 0), "conv2d: groups must divide input and output channels");
+      require(groups == 1 || (cd == 1 && x.discard_copy_degree == 1), "conv2d: channels of a grouped convolution cannot be sharded");
       int64_t oh = conv_out(x.dims[2].size, kh, sh, ph), ow = conv_out(x.dims[3].size, kw, sw, pw);
       require(oh > 0 && ow > 0, "conv2d: kernel larger than padded input");
       out(Slot::OUTPUT, with_degrees({x.dims[0].size, oc, oh, ow}, {nd, x.discard_copy_degree, 1, 1}, x.sum_degree * cd, 1, x.dtype));

@@ -100,6 +100,35 @@ __global__ void reduce_bwd_kernel(const T *__restrict__ dy, T *__restrict__ dx, 
   }
 }
 
+// backward of max / min / prod over the middle dim: x, dx [o, r, in]; y, dy [o, in].
+//   max, min: the gradient goes to every element equal to the result (each tie gets the whole gradient, as in
+//             the derivative of amax/amin taken one-sided); prod: dx = dy * y / x (x == 0: product of the others
+//             recomputed).
+template <typename T>
+__global__ void reduce_select_bwd_kernel(const T *__restrict__ x, const T *__restrict__ y, const T *__restrict__ dy, T *__restrict__ dx,
+                                         long long outer, long long red, long long inner, int op, int accumulate) {
+  long long total = outer * red * inner;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long in = i % inner, o = i / (red * inner);
+    float xv = (float)x[i], yv = (float)y[o * inner + in], g = (float)dy[o * inner + in];
+    float r;
+    if (op == 4) {
+      if (xv != 0.f) r = g * yv / xv;
+      else {
+        float others = 1.f;
+        long long me = (i / inner) % red;
+        for (long long j = 0; j < red; ++j)
+          if (j != me) others *= (float)x[(o * red + j) * inner + in];
+        r = g * others;
+      }
+    } else {
+      r = (xv == yv) ? g : 0.f;
+    }
+    dx[i] = (T)(accumulate ? (float)dx[i] + r : r);
+  }
+}
+
 // torch.gather along `dim`: x [outer, xd, inner], index/out [outer, id, inner]
 template <typename T, typename I>
 __global__ void gather_kernel(const T *__restrict__ x, const I *__restrict__ idx, T *__restrict__ y, long long outer, long long xd,
@@ -254,6 +283,17 @@ FFK_API int ffk_reduce_bwd(const void *dy, void *dx, long long outer, long long 
   int grid = ffk_blocks(outer * red * inner, 256);
   if (dt == 0) reduce_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)dy, (float *)dx, outer, red, inner, scale, accumulate);
   else if (dt == 1) reduce_bwd_kernel<bf16><<<grid, 256, 0, st>>>((const bf16 *)dy, (bf16 *)dx, outer, red, inner, scale, accumulate);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+// op: 2 = max, 3 = min, 4 = prod (the codes of ffk_reduce)
+FFK_API int ffk_reduce_select_bwd(const void *x, const void *y, const void *dy, void *dx, long long outer, long long red, long long inner,
+                                  int op, int dt, int accumulate, cudaStream_t st) {
+  if (outer * red * inner <= 0) return 0;
+  if (op < 2 || op > 4) return -2;
+  int grid = ffk_blocks(outer * red * inner, 256);
+  if (dt == 0) reduce_select_bwd_kernel<float><<<grid, 256, 0, st>>>((const float *)x, (const float *)y, (const float *)dy, (float *)dx, outer, red, inner, op, accumulate);
+  else if (dt == 1) reduce_select_bwd_kernel<bf16><<<grid, 256, 0, st>>>((const bf16 *)x, (const bf16 *)y, (const bf16 *)dy, (bf16 *)dx, outer, red, inner, op, accumulate);
   else return -2;
   return (int)cudaGetLastError();
 }

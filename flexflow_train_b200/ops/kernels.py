@@ -516,6 +516,7 @@ def _decl_tensor_ops(l):
         "ffk_block_copy": [P, L, P, L, L, L, I, I, I, S],
         "ffk_reduce": [P, P, L, L, L, I, I, S],
         "ffk_reduce_bwd": [P, P, L, L, L, F, I, I, S],
+        "ffk_reduce_select_bwd": [P, P, P, P, L, L, L, I, I, I, S],
         "ffk_gather": [P, P, P, L, L, L, L, I, I, S],
         "ffk_gather_bwd": [P, P, P, L, L, L, L, I, I, S],
         "ffk_topk": [P, P, P, I, I, I, I, S],
@@ -590,6 +591,13 @@ def reduce_bwd(dy, dx, outer, red, inner, scale=1.0, accumulate=False):
     _cuda_contig(dy, dx)
     _check(_tlib().ffk_reduce_bwd(dy.data_ptr(), dx.data_ptr(), outer, red, inner, scale, _dt(dy), int(accumulate), _stream()),
            "ffk_reduce_bwd")
+
+
+def reduce_select_bwd(x, y, dy, dx, outer, red, inner, op, accumulate=False):
+    """Backward of a max / min / prod reduction over the middle dim of x[outer, red, inner] (y, dy: [outer, inner])."""
+    _cuda_contig(x, y, dy, dx)
+    _check(_tlib().ffk_reduce_select_bwd(x.data_ptr(), y.data_ptr(), dy.data_ptr(), dx.data_ptr(), outer, red, inner, REDUCE_OPS[op],
+                                         _dt(x), int(accumulate), _stream()), "ffk_reduce_select_bwd")
 
 
 def gather(x, idx, out, dim):

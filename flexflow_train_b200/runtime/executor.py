@@ -743,6 +743,7 @@ _BINARY = {"EW_ADD": "add", "EW_SUB": "sub", "EW_MUL": "mul", "EW_DIV": "div", "
 @register(*_BINARY.keys())
 class BinaryOp(OpImpl):
     fused_into_ln = False
+    _bfull = _da = _dbfull = None
 
     def setup(self):
         self.op = _BINARY[self.type]
@@ -759,14 +760,32 @@ class BinaryOp(OpImpl):
         lb, rb = self.buf("LHS_INPUT"), self.buf("RHS_INPUT")
         dy = self.out().grad
         a, b = lb.data, rb.data
-        if a.shape != b.shape:
+        if a.shape != b.shape and self.op in ("add", "sub"):
             if lb.requires_grad:
-                self.ex.write_grad(lb, dy, self.acc["LHS_INPUT"]) if self.op in ("add", "sub") else self._bcast_unsupported()
+                self.ex.write_grad(lb, dy, self.acc["LHS_INPUT"])
             if rb.requires_grad:
-                red = dy.float().reshape(-1, b.numel()).sum(0).to(dy.dtype) if self.op in ("add", "sub") else self._bcast_unsupported()
+                red = dy.float().reshape(-1, b.numel()).sum(0).to(dy.dtype)
                 if self.op == "sub":
                     red = -red
                 self.ex.write_grad(rb, red.view_as(b), self.acc["RHS_INPUT"])
+            return
+        if a.shape != b.shape:
+            # mul / div / max / min with the right operand repeated along the leading dims: the element-wise
+            # gradients are taken against the materialised repeat, then summed over the repeats
+            reps = a.numel() // b.numel()
+            if self._bfull is None:
+                self._bfull = torch.empty_like(a)
+                self._da = torch.empty_like(a)
+                self._dbfull = torch.empty_like(a)
+            K.permute(b.reshape(1, -1).expand(reps, b.numel()), (0, 1), out=self._bfull.view(reps, -1))
+            K.binary_bwd(self.op, a, self._bfull, dy.view_as(a), self._da, self._dbfull)
+            if lb.requires_grad:
+                self.ex.write_grad(lb, self._da, self.acc["LHS_INPUT"])
+            if rb.requires_grad:
+                red = torch.empty_like(b) if self.acc["RHS_INPUT"] else rb.grad.view_as(b)
+                K.reduce(self._dbfull.view(-1), red.view(-1), 1, reps, b.numel(), "sum")
+                if self.acc["RHS_INPUT"]:
+                    self.ex.write_grad(rb, red, True)
             return
         if self.op == "add":
             if lb.requires_grad:
@@ -785,9 +804,6 @@ class BinaryOp(OpImpl):
             self.ex.write_grad(rb, tb, self.acc["RHS_INPUT"])
         else:
             K.binary_bwd(self.op, a, b, dy, da, db, accumulate=acc)
-
-    def _bcast_unsupported(self):
-        raise NotImplementedError("backward of a broadcasting mul/div/max/min")
 
 
 @register("DROPOUT")

@@ -42,11 +42,12 @@ class Conv2dOp(OpImpl):
 
     def setup(self):
         a = self.attrs
-        if int(a.get("groups", 1) or 1) != 1:
-            raise NotImplementedError("grouped convolution")
+        self.groups = int(a.get("groups", 1) or 1)
         x = self.x()
         if x.dtype != torch.bfloat16:
             raise NotImplementedError("Conv2D runs on the bf16 tensor-core path; use compute_dtype='bf16'")
+        if self.groups != 1:
+            return self._setup_grouped()
         n, c, h, w = _sizes(self)
         oc, _, kh, kw = _sizes(self, "FILTER")
         self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"])
@@ -75,6 +76,70 @@ class Conv2dOp(OpImpl):
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(g.rows, oc))
         self._col = self._dcol = self._dwp = None
 
+    # ---- grouped convolution: one im2col + GEMM per group on strided views of the same buffers.  Group j reads
+    # input channels [j*cg, (j+1)*cg) (a channel offset into the activation, same strides), filter rows
+    # [j*ocg, (j+1)*ocg) and writes output columns [j*ocg, (j+1)*ocg) of the [rows, oc] result (ldc = oc).
+    def _setup_grouped(self):
+        a, x, G = self.attrs, self.x(), self.groups
+        n, c, h, w = _sizes(self)
+        oc, cg, kh, kw = _sizes(self, "FILTER")
+        if c % G or oc % G or cg != c // G:
+            raise ValueError(f"Conv2D groups={G} does not divide channels {c} -> {oc} (filter has {cg} input channels)")
+        self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"])
+        strides = K.nhwc_strides(n, c, h, w) if self.in_nhwc else K.nchw_strides(n, c, h, w)
+        self.cstride = strides[1]
+        self.g = g = K.ConvGeometry(n, cg, h, w, kh, kw, int(a["stride_h"]), int(a["stride_w"]), int(a["padding_h"]),
+                                    int(a["padding_w"]), strides)
+        self.oc, self.ocg, self.cg = oc, oc // G, cg
+        self.act = _ACT[a.get("activation")]
+        y = torch.empty(n, g.oh, g.ow, oc, dtype=x.dtype, device=x.device)
+        self.out().data = y
+        self.ex.mark_nhwc((self.nid, "OUTPUT"))
+        self.y2d = y.view(g.rows, oc)
+        self.direct, self.packed = False, True
+        self.wp = torch.empty(G, self.ocg, g.kp, dtype=torch.bfloat16, device=x.device)
+        self.bias = self.x("BIAS") if "BIAS" in self.inputs else None
+        self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
+        self.ex.need_big_scratch(g.rows * g.kp * 2, 2)
+        self.ex.need_big_scratch(self.ocg * g.kp * 4, 3)
+        self.ex.need_scratch(4 * K.bias_act_bwd_scratch(g.rows, oc))
+        self._col = self._dcol = self._dwp = None
+
+    def _group_input(self, t, j):
+        return t.view(-1)[j * self.cg * self.cstride:]
+
+    def _forward_grouped(self):
+        g, G, ocg = self.g, self.groups, self.ocg
+        w_ = self.x("FILTER").view(G, ocg, -1)
+        if self._col is None:
+            self._col = _scratch_view(self.ex, 0, (g.rows, g.kp), torch.bfloat16)
+        for j in range(G):
+            K.filter_pack(w_[j], self.wp[j], ocg, g.c, g.kh, g.kw, g.kp)
+            K.im2col(self._group_input(self.x(), j), self._col, g)
+            K.gemm_raw(M=g.rows, N=ocg, K=g.kp, A=self._col.data_ptr(), lda=g.kp, B=self.wp[j].data_ptr(), ldb=g.kp,
+                       C=self.y2d.data_ptr() + j * ocg * 2, ldc=self.oc,
+                       C2=None if self.pre is None else self.pre.data_ptr() + j * ocg * 2,
+                       bias=None if self.bias is None else self.bias.data_ptr() + j * ocg * 2, act=K.ACT_CODES[self.act])
+
+    def _backward_grouped(self, dy):
+        g, G, ocg = self.g, self.groups, self.ocg
+        wb, xb = self.buf("FILTER"), self.buf("INPUT")
+        if self._dwp is None:
+            self._dwp = _scratch_view(self.ex, 2, (ocg, g.kp), torch.float32)
+            self._dcol = _scratch_view(self.ex, 1, (g.rows, g.kp), torch.bfloat16)
+        for j in range(G):
+            dyj = dy.data_ptr() + j * ocg * 2
+            if wb.requires_grad:
+                K.im2col(self._group_input(self.x(), j), self._col, g)
+                # dW_j[ocg, kp] = dY_j^T . col  (both operands read along their rows: MN-major)
+                K.gemm_raw(M=ocg, N=g.kp, K=g.rows, A=dyj, lda=self.oc, a_mn=True, B=self._col.data_ptr(), ldb=g.kp, b_mn=True,
+                           C=self._dwp.data_ptr(), ldc=g.kp, out_fp32=True)
+                K.filter_unpack(self._dwp, wb.grad.view(G, ocg, -1)[j], ocg, g.c, g.kh, g.kw, g.kp, accumulate=self.acc["FILTER"])
+            if xb.requires_grad:
+                K.gemm_raw(M=g.rows, N=g.kp, K=ocg, A=dyj, lda=self.oc, B=self.wp[j].data_ptr(), ldb=g.kp, b_mn=True,
+                           C=self._dcol.data_ptr(), ldc=g.kp)
+                K.col2im(self._dcol, self._group_input(xb.grad, j), g, accumulate=self.acc["INPUT"])
+
     def _operand(self):
         if self.direct:
             return self.x().view(self.g.rows, self.g.kp)
@@ -84,6 +149,8 @@ class Conv2dOp(OpImpl):
         return self._col
 
     def forward(self):
+        if self.groups != 1:
+            return self._forward_grouped()
         if self.packed:
             g = self.g
             K.filter_pack(self.x("FILTER"), self.wp, self.oc, g.c, g.kh, g.kw, g.kp)
@@ -97,6 +164,8 @@ class Conv2dOp(OpImpl):
             bb = self.buf("BIAS") if self.bias is not None else None
             K.bias_act_bwd(dy, saved, dy if self.act else None, bb.grad if bb is not None else None, self.ex.scratch_f32(), self.act,
                            accumulate=self.acc.get("BIAS", False))
+        if self.groups != 1:
+            return self._backward_grouped(dy)
         wb = self.buf("FILTER")
         if wb.requires_grad:
             col = self._operand()  # recomputed rather than kept: it is KH*KW times the activation
@@ -122,8 +191,7 @@ class Pool2dOp(OpImpl):
 
     def setup(self):
         a = self.attrs
-        if a.get("activation"):
-            raise NotImplementedError("Pool2D with a fused activation")
+        self.act = {"RELU": "relu", "SIGMOID": "sigmoid", "TANH": "tanh", "GELU": "gelu"}[a["activation"]] if a.get("activation") else None
         x = self.x()
         n, c, h, w = _sizes(self)
         self.in_nhwc = self.ex.is_nhwc(self.inputs["INPUT"])
@@ -138,14 +206,28 @@ class Pool2dOp(OpImpl):
         self.ex.mark_nhwc((self.nid, "OUTPUT"))
         self.arg = torch.empty(n * g.oh * g.ow * c, dtype=torch.uint8, device=x.device) \
             if (self.mode == "max" and self.ex.cfg.training) else None
+        # fused activation (Pool2DAttrs.activation): the pooled values are kept for its backward
+        self.pooled = torch.empty_like(self.out().data) if (self.act and self.ex.cfg.training) else None
+        self.dpool = torch.empty_like(self.out().data) if self.pooled is not None else None
 
     def forward(self):
-        K.pool2d_fwd(self.x(), self.out().data, self.arg, self.g, self.mode)
+        y = self.out().data
+        if self.act is None:
+            K.pool2d_fwd(self.x(), y, self.arg, self.g, self.mode)
+            return
+        t = self.pooled if self.pooled is not None else y
+        K.pool2d_fwd(self.x(), t, self.arg, self.g, self.mode)
+        K.unary_fwd(self.act, t, out=y)
 
     def backward(self):
         b = self.buf("INPUT")
-        if b.requires_grad:
-            K.pool2d_bwd(self.out().grad.view(-1), self.arg, b.grad, self.g, self.mode, accumulate=self.acc["INPUT"])
+        if not b.requires_grad:
+            return
+        dy = self.out().grad.view(-1)
+        if self.act is not None:
+            K.unary_bwd(self.act, self.pooled.view(-1), self.out().data.view(-1), dy, dx=self.dpool.view(-1))
+            dy = self.dpool.view(-1)
+        K.pool2d_bwd(dy, self.arg, b.grad, self.g, self.mode, accumulate=self.acc["INPUT"])
 
 
 # ------------------------------------------------------------------------------------------ BatchNorm
@@ -409,7 +491,9 @@ class ReduceOp(OpImpl):
         if not b.requires_grad:
             return
         if self.op not in ("sum", "mean"):
-            raise NotImplementedError(f"backward of a {self.op} reduction")
+            K.reduce_select_bwd(self.x().view(-1), self.out().data.view(-1), self.out().grad.view(-1), b.grad.view(-1), self.outer,
+                                self.red, self.inner, self.op, accumulate=self.acc["INPUT"])
+            return
         K.reduce_bwd(self.out().grad.view(-1), b.grad.view(-1), self.outer, self.red, self.inner,
                      1.0 if self.op == "sum" else 1.0 / self.red, accumulate=self.acc["INPUT"])
 

@@ -177,6 +177,33 @@ def test_single_convolution_matches_oracle(k, s, p, cin, cout):
     assert K.gemm_last_error() == 0
 
 
+@pytest.mark.parametrize("groups,cin,cout,k", [(2, 16, 24, 3), (4, 16, 16, 1), (16, 16, 16, 3)])
+def test_grouped_convolution_matches_oracle(groups, cin, cout, k):
+    """Grouped (down to depthwise) convolution: per group one im2col + GEMM on channel slices of the same buffers."""
+    b = core.GraphBuilder()
+    x = b.create_input([4, cin, 12, 12], name="input")
+    t = b.conv2d(x, cin, 1, 1, name="pre")
+    t = b.conv2d(t, cout, k, k, 1, 1, k // 2, k // 2, activation="RELU", groups=groups, name="gconv")
+    t = b.pool2d(t, 2, 2, 2, 2, 0, 0, pool_type="AVG", name="pool")
+    t = b.dense(b.flat(t, name="flat"), 10, name="fc")
+    b.softmax(t, name="out_prob")
+    g = b.graph
+    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5))
+    oracle = TorchOracle(g, seed=5)
+    torch.manual_seed(1)
+    xin = torch.randn(4, cin, 12, 12) + 0.5
+    labels = torch.randint(0, 10, (4,), dtype=torch.int32)
+    ex.set_inputs({"input": xin.cuda()}, labels.cuda())
+    ex.forward()
+    ex.compute_loss()
+    ex.backward()
+    rows_ref, grads_ref = oracle.loss_and_grads({"input": xin}, labels)
+    assert rel(ex.loss_rows, rows_ref) < 3e-2
+    for name, g_ in ex.named_gradients():
+        assert rel(g_, grads_ref[name]) < 8e-2, (name, rel(g_, grads_ref[name]))
+    assert K.gemm_last_error() == 0
+
+
 def test_split_k_weight_gradient_gemm_matches_fp32():
     torch.manual_seed(3)
     rows, oc, kp = 40000, 96, 288

@@ -113,6 +113,43 @@ def test_tensor_shape_operators_match_oracle():
         assert rel(g_, grads_ref[name]) < 5e-2, (name, rel(g_, grads_ref[name]))
 
 
+def _reduce_broadcast_pool_graph():
+    """max / min / prod reductions, mul / div with a row vector repeated over the batch, pooling with a fused ReLU."""
+    b = core.GraphBuilder()
+    x = b.create_input([8, 16], name="input")
+    h = b.dense(x, 16, activation="TANH", name="fc0")
+    cmax = b.reduce("REDUCE_MAX", h, [0], False, name="colmax")            # [16]
+    cmin = b.unary("EXP", b.reduce("REDUCE_MIN", h, [0], False, name="colmin"), name="exp_colmin")
+    m = b.binary("EW_MUL", h, cmax, name="scale_by_max")
+    d = b.binary("EW_DIV", m, cmin, name="div_by_min")
+    shifted = b.unary("SCALAR_ADD", h, 1.5, name="shift")
+    p0, _ = b.split(shifted, [3, 13], 1, name="first3")
+    pr = b.reduce("REDUCE_PROD", p0, [1], True, name="rowprod")               # [8, 1]
+    img = b.reshape(d, [8, 1, 4, 4], name="as_image")
+    pooled = b.pool2d(img, 2, 2, 2, 2, 0, 0, "MAX", "RELU", name="pool_relu")
+    f = b.concat([d, pr, b.flat(pooled, 1, -1, name="flat")], 1, name="features")
+    y = b.dense(f, 8, name="fc1")
+    b.softmax(y, name="out_prob")
+    return b.graph
+
+
+def test_reductions_broadcast_products_and_activated_pooling_match_oracle():
+    g = _reduce_broadcast_pool_graph()
+    ex = Executable(g, ExecConfig(compute_dtype="fp32", seed=3))
+    oracle = TorchOracle(g, seed=3)
+    torch.manual_seed(1)
+    x = torch.randn(8, 16)
+    labels = torch.randint(0, 8, (8,), dtype=torch.int32)
+    ex.set_inputs({"input": x.cuda()}, labels.cuda())
+    ex.forward()
+    ex.compute_loss()
+    ex.backward()
+    rows_ref, grads_ref = oracle.loss_and_grads({"input": x}, labels)
+    assert rel(ex.loss_rows, rows_ref) < 2e-2
+    for name, g_ in ex.named_gradients():
+        assert rel(g_, grads_ref[name]) < 5e-2, (name, rel(g_, grads_ref[name]))
+
+
 def test_dropout_fused_into_the_linear_epilogue_trains_like_the_separate_kernel():
     """Same salts and step seeds give the same masks, so the two executors follow the same trajectory."""
     cfg = dict(SMALL_LM, dropout=0.2)
