@@ -851,25 +851,34 @@ constexpr int SB_WARPS = 8;
 constexpr int SB_FLOATS = 2304;  // per warp: (M + N) * (K + 1) floats
 constexpr int SB_SMEM_BYTES = SB_WARPS * SB_FLOATS * 4;
 
+// advance a (slow, fast) index pair by 32 positions in fast-dim-first order
+__device__ __forceinline__ void small_advance(int &slow, int &fast, int extent) {
+  fast += 32;
+  while (fast >= extent) { fast -= extent; ++slow; }
+}
+// Panel X (rows x K, either layout) -> s[x * (K + 1) + k]; four independent loads in flight per lane.
 template <typename T>
 __device__ __forceinline__ void small_stage(float *s, const T *X, int rows, int K, long long ld, int mn_major, int lane) {
-  const int ldk = K + 1;
-  if (!mn_major) {  // X[x][k]: k runs fastest
-    int x = 0, k = lane;
-    while (k >= K) { k -= K; ++x; }
-    while (x < rows) {
-      s[x * ldk + k] = (float)X[(long long)x * ld + k];
-      k += 32;
-      while (k >= K) { k -= K; ++x; }
+  const int ldk = K + 1, total = rows * K;
+  const int fast_extent = mn_major ? rows : K;   // the dim that is contiguous in memory
+  int slow = lane / fast_extent, fast = lane - slow * fast_extent;
+  for (int e = lane; e < total; e += 128) {
+    int sl[4], fa[4];
+    T v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sl[j] = slow; fa[j] = fast;
+      small_advance(slow, fast, fast_extent);
     }
-  } else {          // X[k][x]: x runs fastest
-    int k = 0, x = lane;
-    while (x >= rows) { x -= rows; ++k; }
-    while (k < K) {
-      s[x * ldk + k] = (float)X[(long long)k * ld + x];
-      x += 32;
-      while (x >= rows) { x -= rows; ++k; }
-    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (e + 32 * j < total) v[j] = X[(long long)sl[j] * ld + fa[j]];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (e + 32 * j < total) {
+        const int x = mn_major ? fa[j] : sl[j], k = mn_major ? sl[j] : fa[j];
+        s[x * ldk + k] = (float)v[j];
+      }
   }
 }
 
@@ -883,7 +892,7 @@ __global__ void __launch_bounds__(SB_WARPS * 32) gemm_small_batched_kernel(SimtO
   const T *A = (const T *)o.A + (long long)bh * o.a_sh + (long long)bb * o.a_sb;
   const T *B = (const T *)o.B + (long long)bh * o.b_sh + (long long)bb * o.b_sb;
   const int ldk = p.K + 1;
-  float *sa = simt_smem + warp * SB_FLOATS, *sb = sa + p.M * ldk;
+  float *sa = simt_smem + warp * ((p.M + p.N) * ldk), *sb = sa + p.M * ldk;
   small_stage<T>(sa, A, p.M, p.K, o.lda, o.a_mn, lane);
   small_stage<T>(sb, B, p.N, p.K, o.ldb, o.b_mn, lane);
   __syncwarp();
@@ -1105,8 +1114,10 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
       }
       SimtOperands so{d->A, d->B, d->lda, d->a_sh, d->a_sb, d->ldb, d->b_sh, d->b_sb, d->a_mn, d->b_mn, 1, 1};
       const int blocks = (int)((nbatch + SB_WARPS - 1) / SB_WARPS);
-      if (es == 2) gemm_small_batched_kernel<bf16><<<blocks, SB_WARPS * 32, SB_SMEM_BYTES, stream>>>(so, a);
-      else gemm_small_batched_kernel<float><<<blocks, SB_WARPS * 32, SB_SMEM_BYTES, stream>>>(so, a);
+      // only the panels' own size: more resident warps per SM hide the staging loads
+      const int smem = SB_WARPS * (d->M + d->N) * (d->K + 1) * 4;
+      if (es == 2) gemm_small_batched_kernel<bf16><<<blocks, SB_WARPS * 32, smem, stream>>>(so, a);
+      else gemm_small_batched_kernel<float><<<blocks, SB_WARPS * 32, smem, stream>>>(so, a);
       return (int)cudaGetLastError();
     }
     const int chunks = (d->K + ST - 1) / ST, tiles_m = (d->M + ST - 1) / ST, nbatch = a.nh * a.nb;

@@ -506,6 +506,42 @@ def embedding_sgd(idx, dout, table, lr, aggr="sum"):
     return table
 
 
+_stack_declared = [False]
+
+
+def _stack_lib():
+    l = lib()
+    if not _stack_declared[0]:
+        P, I, F = c_void_p, c_int, c_float
+        PP = ctypes.POINTER(c_void_p)
+        l.ffk_alltoall_embedding_fwd.argtypes = [P, P, P, PP, I, I, I, I, I, I, I, I, P]
+        l.ffk_alltoall_embedding_bwd.argtypes = [P, P, P, P, PP, I, I, I, I, I, I, F, I, I, P]
+        l.ffk_alltoall_embedding_fwd.restype = l.ffk_alltoall_embedding_bwd.restype = c_int
+        _stack_declared[0] = True
+    return l
+
+
+def embedding_stack_fwd(table_ptrs, entries, idx, out):
+    """out[b, t, :] = table_t[idx[b, t], :] for T fp32 tables of equal width in one launch (`table_ptrs`, `entries`:
+    int64 device tensors of the tables' addresses and row counts).  The single-device form of the all-to-all
+    embedding gather."""
+    _cuda_contig(table_ptrs, entries, idx, out)
+    b, t, dim = out.shape
+    peers = (c_void_p * 1)(out.data_ptr())
+    _check(_stack_lib().ffk_alltoall_embedding_fwd(table_ptrs.data_ptr(), entries.data_ptr(), idx.data_ptr(), peers, b, b, t, dim, 0, 1,
+                                                   _dt(out), _dt(idx), _stream()), "ffk_alltoall_embedding_fwd")
+    return out
+
+
+def embedding_stack_sgd(table_ptrs, entries, idx, dout, lr):
+    """table_t[idx[b, t], :] -= lr * dout[b, t, :] for all T tables in one launch."""
+    _cuda_contig(table_ptrs, entries, idx, dout)
+    b, t, dim = dout.shape
+    peers = (c_void_p * 1)(dout.data_ptr())
+    _check(_stack_lib().ffk_alltoall_embedding_bwd(table_ptrs.data_ptr(), None, entries.data_ptr(), idx.data_ptr(), peers, b, b, t, dim, 0, 1,
+                                                   lr, _dt(dout), _dt(idx), _stream()), "ffk_alltoall_embedding_bwd")
+
+
 # --------------------------------------------------------------------------- data movement
 def _decl_tensor_ops(l):
     P, I, L, F, S = c_void_p, c_int, c_longlong, c_float, c_void_p

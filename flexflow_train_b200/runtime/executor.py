@@ -257,6 +257,11 @@ class LinearOp(OpImpl):
         rows, cols = self.x2d.shape[0], self.w.shape[0]
         self.pre = torch.empty(rows, cols, dtype=x.dtype, device=x.device) if (self.act == "gelu" and self.ex.cfg.training) else None
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(rows, cols) if K.available() and self.ex.on_gpu else 0)
+        # A small layer under a large batch: the weight gradient has a handful of output tiles and a reduction over
+        # thousands of rows.  Computed into an fp32 scratch, the GEMM splits that reduction over all SMs (one CTA
+        # streaming 4096 rows takes ~25 us; 148 CTAs sharing them a few); a cast then adds it into the bf16 gradient.
+        if self.ex.cfg.training and self.ex.wgrad_splits(rows, cols, self.w.shape[1], x.dtype):
+            self.ex.need_scratch(4 * cols * self.w.shape[1])
 
     def forward(self):
         if self.fuse_in is not None:
@@ -289,7 +294,7 @@ class LinearOp(OpImpl):
                            self.ex.scratch_f32(), self.act, accumulate=self.acc.get("BIAS", False), dropout=self._drop())
         wb = self.buf("WEIGHT")
         if wb.requires_grad:
-            K.matmul_tn(dy, self.x2d, out=wb.grad, accumulate=self.acc["WEIGHT"])
+            self.ex.wgrad_gemm(dy, self.x2d, wb.grad, self.acc["WEIGHT"])
         if self.fuse_out is not None:
             return
         if self.fuse_in is not None:
@@ -433,6 +438,8 @@ class AttentionOp(OpImpl):
         if not self.cb:
             ex.need_big_scratch(nbytes, 2 if (self.p_drop > 0 and self.kept_p is None) else 1)
         ex.need_scratch(4 * K.bias_act_bwd_scratch(self.B * self.Sq, max(self.ldqkv, self.embed)) if ex.on_gpu else 0)
+        if ex.cfg.training and ex.wgrad_splits(self.B * self.Sq, self.embed, self.H * self.vd, torch.bfloat16):
+            ex.need_scratch(4 * self.embed * self.H * self.vd)
         self.salt = ex.next_salt()
         self.es = 2
         if self.ex.cfg.training:
@@ -584,7 +591,7 @@ class AttentionOp(OpImpl):
         if self.bias_out is not None:
             K.bias_act_bwd(dy, None, None, self.buf("OUTPUT_BIAS").grad, ex.scratch_f32(), None,
                            accumulate=self.acc.get("OUTPUT_BIAS", False))
-        K.matmul_tn(dy, self.ctx, out=g_wo, accumulate=accw)
+        self.ex.wgrad_gemm(dy, self.ctx, g_wo, accw)
         if self.fuse_out is None:
             K.matmul_nn(dy, self.wo, out=self.dctx)
         if self.core16:
@@ -896,6 +903,32 @@ class EmbeddingOp(OpImpl):
             K.embedding_bwd(self.x(), self.out().grad.view_as(self.out().data), wb.grad, aggr=self.aggr)
 
 
+class EmbeddingStackOp(OpImpl):
+    """Takes the place of a Concat(axis 1) whose inputs are all single-index lookups into sparsely updated tables
+    (through their Reshapes): one kernel gathers from all tables straight into the stacked [batch, tables, dim]
+    tensor, one kernel applies all tables' sparse SGD updates from the stack's gradient.  The lookups, Reshapes
+    and the Concat's copies disappear (recommendation models: 4 launches and 2 copies per table per step)."""
+    members = None  # [(weight node, index value)] in stack order
+
+    def setup(self):
+        ex = self.ex
+        tables = [ex.sparse_tables[w] for w, _ in self.members]
+        self.table_ptrs = torch.tensor([t.data_ptr() for t in tables], dtype=torch.int64, device=ex.device)
+        self.entries = torch.tensor([t.shape[0] for t in tables], dtype=torch.int64, device=ex.device)
+        y = self.alloc_out()
+        idx0 = ex.values[self.members[0][1]].data
+        self.idx = torch.empty(y.shape[0], len(tables), dtype=idx0.dtype, device=ex.device)
+        for v in self.inputs.values():
+            ex.values[v].requires_grad = False  # the per-table outputs are never materialised
+
+    def forward(self):
+        torch.cat([self.ex.values[v].data.view(-1, 1) for _, v in self.members], dim=1, out=self.idx)
+        K.embedding_stack_fwd(self.table_ptrs, self.entries, self.idx, self.out().data)
+
+    def backward(self):
+        K.embedding_stack_sgd(self.table_ptrs, self.entries, self.idx, self.out().grad.view_as(self.out().data), self.ex.cfg.optimizer.lr)
+
+
 @register("SOFTMAX")
 class SoftmaxOp(OpImpl):
     fused_loss = False  # set when this softmax feeds the loss: probabilities are then not materialised
@@ -1049,6 +1082,23 @@ class Executable:
     def big_scratch(self, slot: int, like: torch.Tensor):
         n = like.numel() * like.element_size()
         return self._big[slot][:n].view(like.dtype).view(like.shape)
+
+    # A small layer under a large batch: its weight gradient has a handful of output tiles and a reduction over
+    # thousands of rows, so a direct GEMM keeps a few CTAs streaming all rows while the other SMs idle.  Computed into
+    # an fp32 scratch instead, the GEMM splits the reduction over all SMs; a cast then adds it into the bf16 gradient.
+    @staticmethod
+    def wgrad_splits(rows: int, n_out: int, k_in: int, dtype) -> bool:
+        tiles = ((n_out + 127) // 128) * ((k_in + 127) // 128)
+        return dtype == torch.bfloat16 and tiles * 2 <= 148 and rows >= 1024
+
+    def wgrad_gemm(self, dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor, accumulate: bool):
+        """out[n_out, k_in] (+)= dy[rows, n_out]^T . x[rows, k_in]"""
+        if self.wgrad_splits(dy.shape[0], out.shape[0], out.shape[1], out.dtype) and self._scratch.numel() >= out.numel():
+            part = self._scratch[:out.numel()].view(out.shape)
+            K.matmul_tn(dy, x, out=part)
+            K.cast(part, out, accumulate=accumulate)
+        else:
+            K.matmul_tn(dy, x, out=out, accumulate=accumulate)
 
     def write_grad(self, buf: _Buf, g: torch.Tensor, accumulate: bool):
         tgt = buf.grad.view(-1)
@@ -1208,8 +1258,50 @@ class Executable:
     def shard_weight(self, nid, full):
         return full
 
+    def embedding_stack_members(self, concat_nid: int):
+        """If node `concat_nid` is a Concat(axis 1) of [batch, 1, dim] Reshapes of single-index lookups into sparsely
+        updated tables this rank holds: ([(weight node, index value)], [nodes made redundant]); else None."""
+        g, nodes = self.graph, self.nodes
+        c = nodes[concat_nid]
+        sh = c["outputs"][0][1]
+        if c["type"] != "CONCAT" or len(sh.sizes) != 3 or int(c["attrs"]["axis"]) % 3 != 1 or sh.total_degree != 1:
+            return None
+        members, redundant = [], []
+        for _, v in sorted(c["inputs"], key=lambda sv: int(sv[0].split("_")[-1])):
+            v = tuple(v)
+            p = nodes[v[0]]
+            if p["type"] in ("RESHAPE", "FLAT") and len(g.consumers(v)) == 1:
+                redundant.append(p["id"])
+                v = tuple(p["inputs"][0][1])
+                p = nodes[v[0]]
+            if p["type"] != "EMBEDDING" or len(g.consumers(v)) != 1:
+                return None
+            ins = {s: tuple(x) for s, x in p["inputs"]}
+            w, i = ins["WEIGHT"], ins["INPUT"]
+            ish = g.shape(i)
+            bag = 1
+            for d in ish.sizes[1:]:
+                bag *= d
+            if self.sparse_tables.get(w[0]) is None or bag != 1 or ish.sizes[0] != sh.sizes[0] or ish.total_degree != 1 \
+                    or g.shape(w).sizes[1] != sh.sizes[2]:
+                return None
+            redundant.append(p["id"])
+            members.append((w[0], i))
+        if len(members) != sh.sizes[1] or len({g.shape(i).dtype for _, i in members}) != 1:
+            return None
+        return members, redundant
+
     def _fuse(self):
         g = self.graph
+        for nid in self.order:
+            found = self.embedding_stack_members(nid) if self.sparse_tables else None
+            if found is not None:
+                members, redundant = found
+                for r in redundant:
+                    self.ops[r] = SkippedOp(self, r, self.nodes[r])
+                op = EmbeddingStackOp(self, nid, self.nodes[nid])
+                op.members = members
+                self.ops[nid] = op
         for nid in self.order:
             op = self.ops[nid]
             if isinstance(op, LayerNormOp):
@@ -1327,6 +1419,9 @@ class Executable:
             # an op whose outputs received no gradient has nothing to propagate
             outs = [(nid, s) for s, _ in op.outputs]
             op.has_grad = any(written.get(canon(o), False) for o in outs)
+            # per output: does any consumer write its gradient?  (an unused output of a multi-output operator has a
+            # gradient buffer that nobody fills)
+            op.grad_written = {o[1]: written.get(canon(o), False) for o in outs}
             if isinstance(op, BinaryOp) and op.fused_into_ln:
                 op.has_grad = False
             if isinstance(op, SkippedOp):

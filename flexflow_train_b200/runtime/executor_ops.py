@@ -372,11 +372,12 @@ class SplitOp(OpImpl):
         if not b.requires_grad:
             return
         acc = self.acc["INPUT"]
-        if not acc and any(self.out(slot).grad is None for slot, _, _ in self.blocks):
+        live = {slot: self.out(slot).grad is not None and self.grad_written.get(slot, False) for slot, _, _ in self.blocks}
+        if not acc and not all(live.values()):
             b.grad.zero_()  # parts nobody consumed contribute zero
         for slot, off, ext in self.blocks:
             g = self.out(slot).grad
-            if g is not None:
+            if live[slot]:
                 K.block_copy(g, 0, ext, b.grad, off, self.src_ld, self.outer, ext, accumulate=acc)
 
 
