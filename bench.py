@@ -99,7 +99,7 @@ def reference_arm(args):
     # allowed fails before any build starts (no setup.py / pyproject.toml; its legacy bindings need the
     # absent cmake_build_extension package and a Legion runtime).  Nothing of it can be run here.
     print(json.dumps({"impl": "reference", "unavailable":
-                      "pip install of /root/reference fails offline: no setup.py/pyproject.toml at the root; "
+                      "pip install of the reference tree fails offline: no setup.py/pyproject.toml at its root; "
                       "bindings/python/old needs cmake_build_extension + Legion/Realm, not in the wheelhouse"}))
     return 0
 

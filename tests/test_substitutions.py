@@ -123,7 +123,9 @@ def test_attention_rules():
     assert att["outputs"][0][1].degrees == [2, 1, 1]
 
 
-REF = "/root/reference/substitutions"
+# the reference checkout sits beside this repository (or where FF_REFERENCE_DIR points)
+REF = os.path.join(os.environ.get("FF_REFERENCE_DIR") or
+                   os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"), "substitutions")
 
 
 @pytest.mark.skipif(not os.path.exists(REF), reason="legacy rule files not available")
