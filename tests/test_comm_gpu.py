@@ -190,3 +190,41 @@ def test_alltoall_embedding_matches_reference():
     res = _run("w_alltoall_embedding")
     for r, errs in res.items():
         assert max(errs) < 1e-4, (r, errs)
+
+
+def w_wait_expires(ctx):
+    import time
+
+    from flexflow_train_b200.ops import kernels as K
+    from flexflow_train_b200.parallel import comm
+    from flexflow_train_b200.utils.failure import CommTimeoutError
+
+    n = 4096
+    stage = torch.ones(1, n, device=ctx.device, dtype=torch.bfloat16)
+    out = torch.zeros(n, device=ctx.device, dtype=torch.bfloat16)
+    base, sync = ctx.alloc_flags(1), ctx.new_sync()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    comm.reduce_partials(ctx, stage, out, 1, base, sync)  # waits for a source flag that no peer will ever raise
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    try:
+        ctx.check_status()
+        raised = False
+    except CommTimeoutError:
+        raised = True
+    # the kernel returned by itself: the context is intact, later work runs, the status word is clear again
+    a = torch.randn(256, 128, device=ctx.device, dtype=torch.bfloat16)
+    b = torch.randn(192, 128, device=ctx.device, dtype=torch.bfloat16)
+    err = float((K.matmul_nt(a, b).float() - a.float() @ b.float().t()).abs().max())
+    ctx.check_status()
+    return {"raised": raised, "waited": waited, "untouched": float(out.float().abs().max()) == 0.0, "gemm_err": err}
+
+
+def test_device_side_wait_runs_out_and_reports_instead_of_hanging():
+    """Failure detection on the device: a peer that never signals costs the bounded wait (about two seconds), after
+    which the kernel records a timeout code that the host turns into CommTimeoutError; nothing hangs or faults."""
+    out = _run("w_wait_expires", world=1)[0]
+    assert out["raised"] and out["untouched"], out
+    assert 1.0 < out["waited"] < 20.0, out
+    assert out["gemm_err"] < 1.0, out
