@@ -335,6 +335,25 @@ FFK_API int ffk_layernorm_fwd(const void *a, const void *b, const void *gamma, c
   if (dt == 1 && ln_vec_ok(cols, a, b, gamma, beta, xsum, y)) {
     int vpt = ln_vpt(cols), threads = cols / 8 / vpt;
     const bf16 *A = (const bf16 *)a, *B = (const bf16 *)b, *G = (const bf16 *)gamma, *Bt = (const bf16 *)beta;
+    // rows of up to 2048 elements in steps of 256: one warp per row, no block-wide barriers in the row loop
+    if (cols % 256 == 0 && cols <= 2048 && rows >= 8) {
+      const int wv = cols / 256;
+      long long want = ((long long)rows + 7) / 8;
+      const int grid = (int)(want < 148 * 2 ? want : 148 * 2);
+#define LN_WARP(V) vec::layernorm_fwd_warp_kernel<V><<<grid, 256, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, eps)
+      switch (wv) {
+        case 1: LN_WARP(1); break;
+        case 2: LN_WARP(2); break;
+        case 3: LN_WARP(3); break;
+        case 4: LN_WARP(4); break;
+        case 5: LN_WARP(5); break;
+        case 6: LN_WARP(6); break;
+        case 7: LN_WARP(7); break;
+        default: LN_WARP(8); break;
+      }
+#undef LN_WARP
+      return (int)cudaGetLastError();
+    }
     if (vpt == 1) vec::layernorm_fwd_vec_kernel<1><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);
     else if (vpt == 2) vec::layernorm_fwd_vec_kernel<2><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);
     else vec::layernorm_fwd_vec_kernel<4><<<rows_grid(rows), threads, 0, st>>>(A, B, G, Bt, (bf16 *)xsum, (bf16 *)y, mean, rstd, rows, cols, eps);

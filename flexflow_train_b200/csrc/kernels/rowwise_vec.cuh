@@ -15,6 +15,10 @@ __device__ __forceinline__ void ld8(const bf16 *p, float *v) {
   float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
   v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
 }
+__device__ __forceinline__ void unpack8(const uint4 &u, float *v) {
+  float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
 __device__ __forceinline__ void st8(bf16 *p, const float *v) {
   *reinterpret_cast<uint4 *>(p) = make_uint4(pack_bf162(v[0], v[1]), pack_bf162(v[2], v[3]), pack_bf162(v[4], v[5]), pack_bf162(v[6], v[7]));
 }
@@ -131,16 +135,27 @@ __global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 
     if (gamma) ld8(gamma + c0, gm[i]);
     if (beta) ld8(beta + c0, bt[i]);
   }
+  // the next row's 16-byte pieces are fetched into registers before this row's two reductions, so that every
+  // thread keeps loads in flight across the barriers
+  uint4 na[VPT], nb[VPT];
+  if ((int)blockIdx.x < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)blockIdx.x * cols + (i * blockDim.x + threadIdx.x) * 8;
+      na[i] = *reinterpret_cast<const uint4 *>(a + off);
+      if (b) nb[i] = *reinterpret_cast<const uint4 *>(b + off);
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     float v[VPT][8];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
-      ld8(a + off, v[i]);
+      unpack8(na[i], v[i]);
       if (b) {
         float w[8];
-        ld8(b + off, w);
+        unpack8(nb[i], w);
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[i][j] += w[j];
         if (xsum) {
@@ -151,6 +166,15 @@ __global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+    const int next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        long long off = (long long)next * cols + (i * blockDim.x + threadIdx.x) * 8;
+        na[i] = *reinterpret_cast<const uint4 *>(a + off);
+        if (b) nb[i] = *reinterpret_cast<const uint4 *>(b + off);
+      }
     }
     s = warp_sum(s);
     if (lane == 0) red_a[parity][wid] = s;
@@ -183,6 +207,78 @@ __global__ void layernorm_fwd_vec_kernel(const bf16 *__restrict__ a, const bf16 
         v[i][j] = gamma ? o * gm[i][j] + (beta ? bt[i][j] : 0.f) : o;
       }
       st8(y + off, v[i]);
+    }
+  }
+}
+// LayerNorm forward, one warp per row: cols = 256 * VPT (up to 2048).  A lane holds VPT 16-byte pieces of the row
+// (piece i of lane l = elements [(i * 32 + l) * 8, +8): coalesced), all loaded before anything is computed, so a
+// warp has VPT (2 VPT with a fused add) loads in flight and the two row reductions are warp shuffles: no
+// block-wide barrier after the one that stages gamma / beta in shared memory.
+template <int VPT>
+__global__ void __launch_bounds__(256, 2) layernorm_fwd_warp_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ b,
+                                                                    const bf16 *__restrict__ gamma, const bf16 *__restrict__ beta,
+                                                                    bf16 *__restrict__ xsum, bf16 *__restrict__ y, float *__restrict__ mean,
+                                                                    float *__restrict__ rstd, int rows, float eps) {
+  constexpr int COLS = 256 * VPT, NV = 32 * VPT;
+  __shared__ uint4 g_s[NV], b_s[NV];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < NV; i += blockDim.x) {
+    if (gamma) g_s[i] = reinterpret_cast<const uint4 *>(gamma)[i];
+    if (beta) b_s[i] = reinterpret_cast<const uint4 *>(beta)[i];
+  }
+  __syncthreads();
+  for (int row = blockIdx.x * wpb + wid; row < rows; row += gridDim.x * wpb) {
+    const long long base = (long long)row * COLS;
+    const uint4 *ar = reinterpret_cast<const uint4 *>(a + base);
+    uint4 ua[VPT], ub[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) ua[i] = ar[i * 32 + lane];
+    if (b) {
+      const uint4 *br = reinterpret_cast<const uint4 *>(b + base);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) ub[i] = br[i * 32 + lane];
+    }
+    float v[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      unpack8(ua[i], v[i]);
+      if (b) {
+        float w[8];
+        unpack8(ub[i], w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += w[j];
+        if (xsum) {
+          st8(xsum + base + (i * 32 + lane) * 8, v[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = bf2f(f2bf(v[i][j]));  // statistics of the value backward will read
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+    const float mu = warp_sum(s) * (1.0f / COLS);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { float d = v[i][j] - mu; ss += d * d; }
+    const float rs = rsqrtf(warp_sum(ss) * (1.0f / COLS) + eps);
+    if (lane == 0) {
+      if (mean) mean[row] = mu;
+      if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      float g8[8], b8[8];
+      if (gamma) unpack8(g_s[i * 32 + lane], g8);
+      if (beta) unpack8(b_s[i * 32 + lane], b8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o = (v[i][j] - mu) * rs;
+        v[i][j] = gamma ? o * g8[j] + (beta ? b8[j] : 0.f) : o;
+      }
+      st8(y + base + (i * 32 + lane) * 8, v[i]);
     }
   }
 }
