@@ -315,3 +315,46 @@ def test_sparse_embedding_update_matches_the_dense_update():
     mom = Executable(cg, ExecConfig(compute_dtype="bf16", seed=2, optimizer=OptimizerConfig(kind="sgd", lr=0.05, momentum=0.9),
                                     loss="mean_squared_error_avg_reduce"))
     assert not mom.sparse_tables
+
+
+def test_checkpoint_carries_sparse_embedding_tables(tmp_path):
+    """Sparsely updated tables live outside the parameter arena: a checkpoint stores them by name, a plain load
+    restores them, and a load by name moves them between the sparse and the dense (arena) representation."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+    from flexflow_train_b200.utils import checkpoint as ckpt
+
+    cfg = {"batch_size": 64, "embedding_dim": 16, "embedding_bag_size": 1, "embedding_size": [500, 300],
+           "dense_arch_layer_sizes": [13, 32, 16], "over_arch_layer_sizes": [48, 32, 1], "arch_interaction_op": "DOT",
+           "final_activation": "SIGMOID", "embedding_data_type": "FLOAT"}
+    cg = core.build_model("dlrm", cfg)
+    mk = lambda sparse, seed: Executable(cg, ExecConfig(compute_dtype="bf16", seed=seed, loss="mean_squared_error_avg_reduce",
+                                                        optimizer=OptimizerConfig(kind="sgd", lr=0.05), sparse_embedding_update=sparse))
+    torch.manual_seed(0)
+    ins = {"dense": torch.randn(64, 13, device="cuda"), "sparse0": torch.randint(0, 500, (64, 1), device="cuda"),
+           "sparse1": torch.randint(0, 300, (64, 1), device="cuda")}
+    labels = torch.rand(64, 1, device="cuda")
+    a = mk(True, 2)
+    for _ in range(3):
+        a.train_step(ins, labels)
+    path = ckpt.save(str(tmp_path), a)
+    b = mk(True, 9)  # other initial weights
+    ckpt.load(path, b)
+    pa, pb = dict(a.named_parameters()), dict(b.named_parameters())
+    assert set(pa) == set(pb) and "emb0.weight" in pa
+    for k in pa:
+        assert torch.equal(pa[k], pb[k]), k
+    a.train_step(ins, labels)
+    b.train_step(ins, labels)
+    assert abs(a.mean_loss() - b.mean_loss()) < 1e-6
+    # by name into an executable that keeps the tables in the dense arenas, and back
+    d = mk(False, 9)
+    ckpt.load_resharded(path, d)
+    pd = dict(d.named_parameters())
+    full = ckpt.gather_full_parameters(path)
+    for k in ("emb0.weight", "emb1.weight", "top0.weight"):
+        assert torch.equal(pd[k].cpu(), full[k]), k
+    path2 = ckpt.save(str(tmp_path / "dense"), d)
+    e = mk(True, 11)
+    ckpt.load_resharded(path2, e)
+    assert torch.equal(dict(e.named_parameters())["emb1.weight"].cpu(), full["emb1.weight"])
