@@ -75,6 +75,10 @@ class ExecConfig:
     # step touches batch x dim elements of a table instead of the whole table three times (gradient clear,
     # dense scatter target, dense update).
     sparse_embedding_update: bool = True
+    # K x K convolutions: keep the forward pass's im2col matrix for the weight-gradient GEMM instead of recomputing
+    # it in backward (it is KH*KW times the activation, so this trades memory for one im2col pass per convolution
+    # and step).  Value: total bytes that may be kept, claimed by the convolutions in graph order; 0 = recompute.
+    keep_im2col_bytes: int = 48 << 30
 
 
 class _Buf:

@@ -75,6 +75,15 @@ class Conv2dOp(OpImpl):
         self.ex.need_big_scratch(oc * g.kp * 4, 3)
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(g.rows, oc))
         self._col = self._dcol = self._dwp = None
+        self._kept = None
+        col_bytes = g.rows * g.kp * 2
+        claimed = getattr(self.ex, "_im2col_kept_bytes", 0)
+        if not self.direct and self.ex.cfg.training and self.buf("FILTER").requires_grad and \
+                claimed + col_bytes <= self.ex.cfg.keep_im2col_bytes:
+            free = torch.cuda.mem_get_info(x.device)[0] if x.is_cuda else 0
+            if col_bytes * 4 < free:  # never take more than a quarter of what is left
+                self._kept = torch.empty(g.rows, g.kp, dtype=torch.bfloat16, device=x.device)
+                self.ex._im2col_kept_bytes = claimed + col_bytes
 
     # ---- grouped convolution: one im2col + GEMM per group on strided views of the same buffers.  Group j reads
     # input channels [j*cg, (j+1)*cg) (a channel offset into the activation, same strides), filter rows
@@ -143,6 +152,9 @@ class Conv2dOp(OpImpl):
     def _operand(self):
         if self.direct:
             return self.x().view(self.g.rows, self.g.kp)
+        if self._kept is not None:  # this convolution's own matrix, still valid in backward
+            K.im2col(self.x(), self._kept, self.g)
+            return self._kept
         if self._col is None:
             self._col = _scratch_view(self.ex, 0, (self.g.rows, self.g.kp), torch.bfloat16)
         K.im2col(self.x(), self._col, self.g)
@@ -168,7 +180,8 @@ class Conv2dOp(OpImpl):
             return self._backward_grouped(dy)
         wb = self.buf("FILTER")
         if wb.requires_grad:
-            col = self._operand()  # recomputed rather than kept: it is KH*KW times the activation
+            # the forward pass's matrix when it was kept, else recomputed (it is KH*KW times the activation)
+            col = self._kept if self._kept is not None else self._operand()
             if self._dwp is None:
                 self._dwp = _scratch_view(self.ex, 2, (self.oc, g.kp), torch.float32)
             K.matmul_tn(dy, col, out=self._dwp)
