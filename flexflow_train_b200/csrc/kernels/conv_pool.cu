@@ -21,25 +21,71 @@ template <typename T> __device__ __forceinline__ void stf(T *p, float v);
 template <> __device__ __forceinline__ void stf<float>(float *p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16 *p, float v) { *p = f2bf(v); }
 
+// Division by a runtime constant as multiply-high + shift (numerators below 2^31).  The window kernels decompose a
+// flat index into (n, h, w, kernel tap, channel group) for every 16 bytes they move; with hardware 64-bit divisions
+// that index arithmetic, not memory, bounded them.
+struct FastDiv {
+  unsigned d, mul, sh;
+};
+__device__ __forceinline__ unsigned fdiv(unsigned n, const FastDiv &f) { return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.sh); }
+__device__ __forceinline__ void fdivmod(unsigned n, const FastDiv &f, unsigned &q, unsigned &r) {
+  q = fdiv(n, f);
+  r = n - q * f.d;
+}
+
 struct ConvGeom {
   int N, C, H, W, KH, KW, SH, SW, PH, PW, OH, OW, Kp;
   long long sn, sc, sh, sw;  // element strides of the activation tensor
+  FastDiv f_c8, f_kk, f_kw, f_ow, f_oh, f_w, f_h, f_sh, f_sw;
 };
+// flat index -> (c8, a, b, n) where the index runs over [n][b_extent... ] as n, B, A, c8 from slow to fast
+__device__ __forceinline__ void split3(long long t, const FastDiv &f_c8, const FastDiv &f_a, const FastDiv &f_b, bool small, int c8n, int A,
+                                       int B, int &c8, int &a, int &b, int &n) {
+  if (small) {
+    unsigned r, r2, uc, ua, ub;
+    fdivmod((unsigned)t, f_c8, r, uc);
+    fdivmod(r, f_a, r2, ua);
+    unsigned un;
+    fdivmod(r2, f_b, un, ub);
+    c8 = (int)uc; a = (int)ua; b = (int)ub; n = (int)un;
+  } else {
+    c8 = (int)(t % c8n);
+    long long r = t / c8n;
+    a = (int)(r % A);
+    long long r2 = r / A;
+    b = (int)(r2 % B);
+    n = (int)(r2 / B);
+  }
+}
 
 // ------------------------------------------------------------------------------------------- im2col
 // vector path: bf16 channels-last, C % 8 == 0; one thread moves 8 channels (16 bytes)
 __global__ void im2col_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ col, ConvGeom g, long long total) {
   const int c8n = g.C >> 3, kk_n = g.KH * g.KW;
+  const bool small = total < (1ll << 31);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    int c8 = (int)(t % c8n);
-    long long r = t / c8n;
-    int kk = (int)(r % kk_n);
-    long long row = r / kk_n;
-    int ow = (int)(row % g.OW);
-    long long r2 = row / g.OW;
-    int oh = (int)(r2 % g.OH);
-    int n = (int)(r2 / g.OH);
-    int kh = kk / g.KW, kw = kk - kh * g.KW;
+    int c8, kk, ow, oh, n, kh, kw;
+    long long row;
+    if (small) {
+      unsigned r, uc, uk, urow, r2, uow, uoh, un, ukh;
+      fdivmod((unsigned)t, g.f_c8, r, uc);
+      fdivmod(r, g.f_kk, urow, uk);
+      fdivmod(urow, g.f_ow, r2, uow);
+      fdivmod(r2, g.f_oh, un, uoh);
+      ukh = fdiv(uk, g.f_kw);
+      c8 = (int)uc; kk = (int)uk; row = urow; ow = (int)uow; oh = (int)uoh; n = (int)un; kh = (int)ukh; kw = kk - kh * g.KW;
+    } else {
+      c8 = (int)(t % c8n);
+      long long r = t / c8n;
+      kk = (int)(r % kk_n);
+      row = r / kk_n;
+      ow = (int)(row % g.OW);
+      long long r2 = row / g.OW;
+      oh = (int)(r2 % g.OH);
+      n = (int)(r2 / g.OH);
+      kh = kk / g.KW;
+      kw = kk - kh * g.KW;
+    }
     int ih = oh * g.SH - g.PH + kh, iw = ow * g.SW - g.PW + kw;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
@@ -103,25 +149,22 @@ __global__ void col2im_kernel(const bf16 *__restrict__ dcol, T *__restrict__ dx,
 // vector form: bf16 channels-last output, C % 8 == 0
 __global__ void col2im_vec_kernel(const bf16 *__restrict__ dcol, bf16 *__restrict__ dx, ConvGeom g, long long total, int accumulate) {
   const int c8n = g.C >> 3;
+  const bool small = total < (1ll << 31);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    int c8 = (int)(t % c8n);
-    long long r = t / c8n;
-    int iw = (int)(r % g.W);
-    long long r2 = r / g.W;
-    int ih = (int)(r2 % g.H);
-    int n = (int)(r2 / g.H);
+    int c8, iw, ih, n;
+    split3(t, g.f_c8, g.f_w, g.f_h, small, c8n, g.W, g.H, c8, iw, ih, n);
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int kh = 0; kh < g.KH; ++kh) {
       int a = ih + g.PH - kh;
       if (a < 0) break;
-      int oh = a / g.SH;
+      int oh = (int)fdiv((unsigned)a, g.f_sh);
       if (oh * g.SH != a || oh >= g.OH) continue;
       for (int kw = 0; kw < g.KW; ++kw) {
         int b = iw + g.PW - kw;
         if (b < 0) break;
-        int ow = b / g.SW;
+        int ow = (int)fdiv((unsigned)b, g.f_sw);
         if (ow * g.SW != b || ow >= g.OW) continue;
         long long row = ((long long)n * g.OH + oh) * g.OW + ow;
         uint4 v = *reinterpret_cast<const uint4 *>(dcol + row * g.Kp + (long long)(kh * g.KW + kw) * g.C + c8 * 8);
@@ -394,13 +437,10 @@ __device__ __forceinline__ uint4 pack8(const float *f) {
 __global__ void pool_fwd_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__ y, unsigned char *__restrict__ arg, ConvGeom g, int mode,
                                     long long total) {
   const int c8n = g.C >> 3;
+  const bool small = total < (1ll << 31);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    int c8 = (int)(t % c8n);
-    long long r = t / c8n;
-    int ow = (int)(r % g.OW);
-    long long r2 = r / g.OW;
-    int oh = (int)(r2 % g.OH);
-    int n = (int)(r2 / g.OH);
+    int c8, ow, oh, n;
+    split3(t, g.f_c8, g.f_ow, g.f_oh, small, c8n, g.OW, g.OH, c8, ow, oh, n);
     const bf16 *base = x + n * g.sn + c8 * 8;
     float best[8], sum[8];
     int besti[8];
@@ -442,25 +482,22 @@ __global__ void pool_fwd_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict
 __global__ void pool_bwd_vec_kernel(const bf16 *__restrict__ dy, const unsigned char *__restrict__ arg, bf16 *__restrict__ dx, ConvGeom g,
                                     int mode, long long total, int accumulate) {
   const int c8n = g.C >> 3;
+  const bool small = total < (1ll << 31);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    int c8 = (int)(t % c8n);
-    long long r = t / c8n;
-    int iw = (int)(r % g.W);
-    long long r2 = r / g.W;
-    int ih = (int)(r2 % g.H);
-    int n = (int)(r2 / g.H);
+    int c8, iw, ih, n;
+    split3(t, g.f_c8, g.f_w, g.f_h, small, c8n, g.W, g.H, c8, iw, ih, n);
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int kh = 0; kh < g.KH; ++kh) {
       int a = ih + g.PH - kh;
       if (a < 0) break;
-      int oh = a / g.SH;
+      int oh = (int)fdiv((unsigned)a, g.f_sh);
       if (oh * g.SH != a || oh >= g.OH) continue;
       for (int kw = 0; kw < g.KW; ++kw) {
         int b = iw + g.PW - kw;
         if (b < 0) break;
-        int ow = b / g.SW;
+        int ow = (int)fdiv((unsigned)b, g.f_sw);
         if (ow * g.SW != b || ow >= g.OW) continue;
         long long o = ((((long long)n * g.OH + oh) * g.OW + ow) * c8n + c8) * 8;
         float f[8];
@@ -630,11 +667,25 @@ __global__ void bn_bwd_apply_vec_kernel(const bf16 *__restrict__ dy, const bf16 
   }
 }
 
+inline FastDiv make_fd(int d_) {
+  FastDiv f;
+  unsigned d = d_ < 1 ? 1u : (unsigned)d_;
+  f.d = d;
+  if (d == 1) { f.mul = 0; f.sh = 0; return f; }
+  unsigned l = 0;
+  while ((1ull << l) < d) ++l;  // ceil(log2(d))
+  const unsigned p = 31 + l;
+  f.mul = (unsigned)(((1ull << p) + d - 1) / d);
+  f.sh = p - 32;
+  return f;
+}
 inline ConvGeom make_geom(const int *p, const long long *strides) {
   ConvGeom g;
   g.N = p[0]; g.C = p[1]; g.H = p[2]; g.W = p[3]; g.KH = p[4]; g.KW = p[5]; g.SH = p[6]; g.SW = p[7]; g.PH = p[8]; g.PW = p[9];
   g.OH = p[10]; g.OW = p[11]; g.Kp = p[12];
   g.sn = strides[0]; g.sc = strides[1]; g.sh = strides[2]; g.sw = strides[3];
+  g.f_c8 = make_fd(g.C >> 3); g.f_kk = make_fd(g.KH * g.KW); g.f_kw = make_fd(g.KW); g.f_ow = make_fd(g.OW); g.f_oh = make_fd(g.OH);
+  g.f_w = make_fd(g.W); g.f_h = make_fd(g.H); g.f_sh = make_fd(g.SH); g.f_sw = make_fd(g.SW);
   return g;
 }
 inline bool vec_ok(const ConvGeom &g, const void *p) {
