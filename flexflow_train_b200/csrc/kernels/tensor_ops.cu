@@ -69,6 +69,34 @@ __global__ void block_copy_kernel(const T *__restrict__ src, long long src_ld, T
   }
 }
 
+// 16-byte form of the same copy: block, both pitches and both bases are multiples of 16 bytes and there are fewer
+// than 2^31 pieces, so the row / column split is a multiply-high instead of a 64-bit division per 2-byte element
+// (channel concatenation of channels-last activations is this case).
+struct CopyDiv {
+  unsigned d, mul, sh;
+};
+__global__ void block_copy_vec_kernel(const uint4 *__restrict__ src, long long src_ld, uint4 *__restrict__ dst, long long dst_ld,
+                                      unsigned total, CopyDiv f, int accumulate_bf16) {
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const unsigned o = f.d == 1 ? i : (__umulhi(i, f.mul) >> f.sh), b = i - o * f.d;
+    uint4 v = src[(long long)o * src_ld + b];
+    uint4 *p = dst + (long long)o * dst_ld + b;
+    if (accumulate_bf16) {
+      const uint4 w = *p;
+      const unsigned *vs = reinterpret_cast<const unsigned *>(&v), *ws = reinterpret_cast<const unsigned *>(&w);
+      unsigned r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 x = unpack_bf162(vs[j]), y = unpack_bf162(ws[j]);
+        r[j] = pack_bf162(x.x + y.x, x.y + y.y);
+      }
+      v = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    *p = v;
+  }
+}
+
 enum { RED_SUM = 0, RED_MEAN = 1, RED_MAX = 2, RED_MIN = 3, RED_PROD = 4 };
 // x viewed as [outer, red, inner] -> y [outer, inner]
 template <typename T>
@@ -255,6 +283,25 @@ FFK_API int ffk_transpose2d(const void *src, void *dst, int batch, int rows, int
 FFK_API int ffk_block_copy(const void *src, long long src_ld, void *dst, long long dst_ld, long long outer, long long block, int es,
                            int dt, int accumulate, cudaStream_t st) {
   if (outer * block <= 0) return 0;
+  {
+    const long long bytes = block * es, sp = src_ld * es, dp = dst_ld * es, pieces = outer * (bytes / 16);
+    const bool vec = bytes % 16 == 0 && sp % 16 == 0 && dp % 16 == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)dst % 16) == 0 &&
+                     pieces < (1ll << 31) && (!accumulate || dt == 1);
+    if (vec) {
+      CopyDiv f;
+      const unsigned d = (unsigned)(bytes / 16);
+      f.d = d; f.mul = 0; f.sh = 0;
+      if (d > 1) {
+        unsigned l = 0;
+        while ((1ull << l) < d) ++l;
+        f.mul = (unsigned)(((1ull << (31 + l)) + d - 1) / d);
+        f.sh = l - 1;
+      }
+      block_copy_vec_kernel<<<ffk_blocks(pieces, 256), 256, 0, st>>>((const uint4 *)src, sp / 16, (uint4 *)dst, dp / 16, (unsigned)pieces, f,
+                                                                     accumulate);
+      return (int)cudaGetLastError();
+    }
+  }
   int grid = ffk_blocks(outer * block, 256);
   if (accumulate) {
     if (dt == 0) block_copy_kernel<float><<<grid, 256, 0, st>>>((const float *)src, src_ld, (float *)dst, dst_ld, outer, block, 1);
