@@ -36,7 +36,7 @@ __device__ __forceinline__ void fdivmod(unsigned n, const FastDiv &f, unsigned &
 struct ConvGeom {
   int N, C, H, W, KH, KW, SH, SW, PH, PW, OH, OW, Kp;
   long long sn, sc, sh, sw;  // element strides of the activation tensor
-  FastDiv f_c8, f_kk, f_kw, f_ow, f_oh, f_w, f_h, f_sh, f_sw;
+  FastDiv f_c8, f_kk, f_kw, f_ow, f_oh, f_w, f_h, f_sh, f_sw, f_kp, f_c;
 };
 // flat index -> (c8, a, b, n) where the index runs over [n][b_extent... ] as n, B, A, c8 from slow to fast
 __device__ __forceinline__ void split3(long long t, const FastDiv &f_c8, const FastDiv &f_a, const FastDiv &f_b, bool small, int c8n, int A,
@@ -97,17 +97,36 @@ __global__ void im2col_vec_kernel(const bf16 *__restrict__ x, bf16 *__restrict__
 template <typename T>
 __global__ void im2col_kernel(const T *__restrict__ x, bf16 *__restrict__ col, ConvGeom g, long long total) {
   const int K = g.KH * g.KW * g.C;
+  const bool small = total < (1ll << 31);
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    int k = (int)(t % g.Kp);
-    long long row = t / g.Kp;
+    int k;
+    long long row;
+    if (small) {
+      unsigned urow, uk;
+      fdivmod((unsigned)t, g.f_kp, urow, uk);
+      k = (int)uk; row = urow;
+    } else {
+      k = (int)(t % g.Kp);
+      row = t / g.Kp;
+    }
     float v = 0.f;
     if (k < K) {
-      int kk = k / g.C, c = k - kk * g.C;
-      int kh = kk / g.KW, kw = kk - kh * g.KW;
-      int ow = (int)(row % g.OW);
-      long long r2 = row / g.OW;
-      int oh = (int)(r2 % g.OH);
-      int n = (int)(r2 / g.OH);
+      int kk, c, kh, kw, ow, oh, n;
+      if (small) {
+        unsigned ukk, uc, ukh, r2, uow, un, uoh;
+        fdivmod((unsigned)k, g.f_c, ukk, uc);
+        ukh = fdiv(ukk, g.f_kw);
+        fdivmod((unsigned)row, g.f_ow, r2, uow);
+        fdivmod(r2, g.f_oh, un, uoh);
+        kk = (int)ukk; c = (int)uc; kh = (int)ukh; kw = kk - kh * g.KW; ow = (int)uow; oh = (int)uoh; n = (int)un;
+      } else {
+        kk = k / g.C; c = k - kk * g.C;
+        kh = kk / g.KW; kw = kk - kh * g.KW;
+        ow = (int)(row % g.OW);
+        long long r2 = row / g.OW;
+        oh = (int)(r2 % g.OH);
+        n = (int)(r2 / g.OH);
+      }
       int ih = oh * g.SH - g.PH + kh, iw = ow * g.SW - g.PW + kw;
       if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = ldf(x + n * g.sn + c * g.sc + ih * g.sh + iw * g.sw);
     }
@@ -686,6 +705,7 @@ inline ConvGeom make_geom(const int *p, const long long *strides) {
   g.sn = strides[0]; g.sc = strides[1]; g.sh = strides[2]; g.sw = strides[3];
   g.f_c8 = make_fd(g.C >> 3); g.f_kk = make_fd(g.KH * g.KW); g.f_kw = make_fd(g.KW); g.f_ow = make_fd(g.OW); g.f_oh = make_fd(g.OH);
   g.f_w = make_fd(g.W); g.f_h = make_fd(g.H); g.f_sh = make_fd(g.SH); g.f_sw = make_fd(g.SW);
+  g.f_kp = make_fd(g.Kp); g.f_c = make_fd(g.C);
   return g;
 }
 inline bool vec_ok(const ConvGeom &g, const void *p) {
