@@ -389,21 +389,29 @@ FFK_API int ffk_cast(const void *src, int sdt, void *dst, int ddt, long long n, 
   return (int)cudaGetLastError();
 }
 // Number of float slots `partial` must hold for ffk_bias_act_bwd.
-FFK_API long long ffk_bias_act_bwd_scratch(int rows, int cols) {
-  int gy = rows / 64; if (gy < 1) gy = 1; if (gy > 64) gy = 64;
-  return (long long)gy * cols;
+// Row chunks of the column reduction: at least 64 rows each, and enough chunks that a narrow matrix (768 columns =
+// three column blocks) still fills the GPU.
+static int bias_act_row_chunks(int rows, int cols) {
+  const int col_blocks = (cols + 255) / 256;
+  int cap = (148 * 4 + col_blocks - 1) / col_blocks;
+  if (cap < 64) cap = 64;
+  int gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > cap) gy = cap;
+  return gy;
 }
+FFK_API long long ffk_bias_act_bwd_scratch(int rows, int cols) { return (long long)bias_act_row_chunks(rows, cols) * cols; }
 // dz = dy * act'(saved); dbias (+)= column sums of dz.  dz may alias dy or be null
 // (bias gradient only); dbias may be null.  `partial` is caller-provided scratch.
 static int bias_act_bwd_impl(const void *dy, const void *saved, void *dz, void *dbias, float *partial, int rows, int cols, int act, int dt,
                              int accumulate, float drop_p, unsigned long long drop_salt, const void *drop_seed_ptr, cudaStream_t st) {
   if (rows <= 0 || cols <= 0) return 0;
-  int gy = rows / 64; if (gy < 1) gy = 1; if (gy > 64) gy = 64;
+  const int gy = bias_act_row_chunks(rows, cols);
   if (dt == DT_BF16 && cols % 8 == 0 && (((uintptr_t)dy | (uintptr_t)saved | (uintptr_t)dz) & 15) == 0) {
     dim3 vgrid((cols + 255) / 256, gy), vblock(32, 8);
     vec::bias_act_bwd_vec_kernel<<<vgrid, vblock, 0, st>>>((const bf16 *)dy, (const bf16 *)saved, (bf16 *)dz, dbias ? partial : nullptr, rows,
                                                           cols, act, drop_p, drop_salt, (const unsigned long long *)drop_seed_ptr);
-    if (dbias) colsum_finish_kernel<bf16><<<(cols + 255) / 256, 256, 0, st>>>(partial, gy, cols, (bf16 *)dbias, accumulate);
+    if (dbias) vec::fold_partials_kernel<bf16><<<(cols + 31) / 32, dim3(32, 32), 0, st>>>(partial, gy, cols, (bf16 *)dbias, (bf16 *)nullptr, accumulate);
     return (int)cudaGetLastError();
   }
   if (drop_p > 0.f) return -2;  // the fused-dropout form exists for the 16-byte vector path only

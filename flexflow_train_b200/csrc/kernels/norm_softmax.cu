@@ -120,20 +120,6 @@ __global__ void layernorm_bwd_kernel(const T *__restrict__ dy, const T *__restri
     }
   }
 }
-template <typename T>
-__global__ void layernorm_bwd_finish_kernel(const float *__restrict__ partial, int nparts, int cols, T *dgamma,
-                                            T *dbeta, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float g = 0.f, b = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    g += partial[(long long)p * cols + c];
-    b += partial[((long long)nparts + p) * cols + c];
-  }
-  if (dgamma) stf(dgamma + c, accumulate ? ldf(dgamma + c) + g : g);
-  if (dbeta) stf(dbeta + c, accumulate ? ldf(dbeta + c) + b : b);
-}
-
 // ------------------------------------------------------------------ Softmax
 // y = softmax(scale * x) over the last dim.  causal_q > 0: row r is query
 // position (r % causal_q) and keys past it are masked out.
@@ -386,7 +372,7 @@ FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, 
     else if (vpt == 2) vec::layernorm_bwd_vec_kernel<2><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     else vec::layernorm_bwd_vec_kernel<4><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     if (part)
-      layernorm_bwd_finish_kernel<bf16><<<(cols + 255) / 256, 256, 0, st>>>(part, grid, cols, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_params);
+      vec::fold_partials_kernel<bf16><<<(cols + 31) / 32, dim3(32, 32), 0, st>>>(part, grid, cols, (bf16 *)dgamma, (bf16 *)dbeta, accumulate_params);
     return (int)cudaGetLastError();
   }
   DISPATCH_FLOAT(dt, {
@@ -400,8 +386,7 @@ FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, 
       layernorm_bwd_kernel<T, 32><<<grid, 512, 0, st>>>((const T *)dy, (const T *)x, (const T *)gamma, mean, rstd,
                                                          (T *)dx, (T *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);
     if (part)
-      layernorm_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(part, grid, cols, (T *)dgamma, (T *)dbeta,
-                                                                          accumulate_params);
+      vec::fold_partials_kernel<T><<<(cols + 31) / 32, dim3(32, 32), 0, st>>>(part, grid, cols, (T *)dgamma, (T *)dbeta, accumulate_params);
   });
   return (int)cudaGetLastError();
 }
