@@ -352,9 +352,25 @@ FFK_API int ffk_layernorm_fwd(const void *a, const void *b, const void *gamma, c
   return (int)cudaGetLastError();
 }
 
-static int ln_bwd_grid(int rows) { return rows < 296 ? rows : 296; }
-// floats of scratch needed by ffk_layernorm_bwd
-FFK_API long long ffk_layernorm_bwd_scratch(int rows, int cols) { return 2ll * ln_bwd_grid(rows) * cols; }
+// Persistent blocks of the backward kernel: as many per SM as its registers allow for the block size in use (narrow
+// rows mean small blocks, of which two per SM left most of the SM idle); each block writes one partial row of
+// dgamma / dbeta, which the fold kernel sums.
+static int ln_bwd_grid(int rows, int cols, bool vec) {
+  int per_sm = 2;
+  if (vec && ln_vpt(cols) > 0) {
+    const int threads = cols / 8 / ln_vpt(cols);
+    per_sm = 768 / threads;
+    if (per_sm < 2) per_sm = 2;
+    if (per_sm > 8) per_sm = 8;
+  }
+  const int g = 148 * per_sm;
+  return rows < g ? rows : g;
+}
+// floats of scratch needed by ffk_layernorm_bwd (the larger of the two kernel forms' needs)
+FFK_API long long ffk_layernorm_bwd_scratch(int rows, int cols) {
+  const int a = ln_bwd_grid(rows, cols, true), b = ln_bwd_grid(rows, cols, false);
+  return 2ll * (a > b ? a : b) * cols;
+}
 
 // dx (+)= LN backward; dgamma/dbeta (+)= column sums.  `partial` is scratch of
 // ffk_layernorm_bwd_scratch(rows, cols) floats.  cols <= 16384.
@@ -363,9 +379,10 @@ FFK_API int ffk_layernorm_bwd(const void *dy, const void *x, const void *gamma, 
                               int accumulate_dx, int accumulate_dx2, int accumulate_params, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols > 16384) return -2;
-  int grid = ln_bwd_grid(rows);
+  const bool vec = dt == 1 && ln_vec_ok(cols, dy, x, gamma, dx, dx2, nullptr);
+  int grid = ln_bwd_grid(rows, cols, vec);
   float *part = (dgamma || dbeta) ? partial : nullptr;
-  if (dt == 1 && ln_vec_ok(cols, dy, x, gamma, dx, dx2, nullptr)) {
+  if (vec) {
     int vpt = ln_vpt(cols), threads = cols / 8 / vpt;
     const bf16 *DY = (const bf16 *)dy, *X = (const bf16 *)x, *G = (const bf16 *)gamma;
     if (vpt == 1) vec::layernorm_bwd_vec_kernel<1><<<grid, threads, 0, st>>>(DY, X, G, mean, rstd, (bf16 *)dx, (bf16 *)dx2, part, rows, cols, accumulate_dx, accumulate_dx2);

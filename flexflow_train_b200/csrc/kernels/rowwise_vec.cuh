@@ -299,15 +299,36 @@ __global__ void layernorm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16
 #pragma unroll
     for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; if (!gamma) gm[i][j] = 1.f; }
   }
+  // the next row's pieces of dy and x travel while this row is reduced and written (see the forward kernel)
+  uint4 ng[VPT], nx[VPT];
+  if ((int)blockIdx.x < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      long long off = (long long)blockIdx.x * cols + (i * blockDim.x + threadIdx.x) * 8;
+      ng[i] = *reinterpret_cast<const uint4 *>(dy + off);
+      nx[i] = *reinterpret_cast<const uint4 *>(x + off);
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mu = mean[row], rs = rstd[row];
     float g[VPT][8], xh[VPT][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      long long off = (long long)row * cols + (i * blockDim.x + threadIdx.x) * 8;
-      ld8(dy + off, g[i]);
-      ld8(x + off, xh[i]);
+      unpack8(ng[i], g[i]);
+      unpack8(nx[i], xh[i]);
+    }
+    const int next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        long long off = (long long)next * cols + (i * blockDim.x + threadIdx.x) * 8;
+        ng[i] = *reinterpret_cast<const uint4 *>(dy + off);
+        nx[i] = *reinterpret_cast<const uint4 *>(x + off);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         xh[i][j] = (xh[i][j] - mu) * rs;

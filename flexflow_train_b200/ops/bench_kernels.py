@@ -101,6 +101,21 @@ def bench_layernorm(a):
     return {"op": "layernorm_fwd_bf16", "rows": rows, "cols": cols, **roofline(ms, hbm_bytes=4.0 * rows * cols)}
 
 
+def bench_layernorm_bwd(a):
+    rows, cols = a.rows, a.cols
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    g = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
+    mean = x.float().mean(1)
+    rstd = torch.rsqrt(x.float().var(1, unbiased=False) + 1e-5)
+    dx = torch.empty_like(x)
+    dg, db = torch.empty_like(g), torch.empty_like(g)
+    scratch = torch.empty(K.layernorm_bwd_scratch(rows, cols), device="cuda")
+    ms = _time(lambda: K.layernorm_bwd(dy, x, g, mean, rstd, dx, dg, db, scratch), a.warmup, a.iters, a.flush)
+    # reads dy and x, writes dx
+    return {"op": "layernorm_bwd_bf16", "rows": rows, "cols": cols, **roofline(ms, hbm_bytes=6.0 * rows * cols)}
+
+
 def bench_softmax(a):
     rows, cols = a.rows, a.cols
     x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
@@ -132,7 +147,7 @@ def bench_im2col(a):
     return {"op": "im2col_3x3_bf16", "n": n, "c": c, "hw": h, **roofline(ms, hbm_bytes=2.0 * (x.numel() + col.numel()))}
 
 
-OPS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
+OPS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "layernorm_bwd": bench_layernorm_bwd, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
        "im2col": bench_im2col}
 
 
