@@ -506,6 +506,37 @@ def embedding_sgd(idx, dout, table, lr, aggr="sum"):
     return table
 
 
+METRIC_FLAGS = {"accuracy": 1, "categorical_crossentropy": 2, "sparse_categorical_crossentropy": 4, "mean_squared_error": 8,
+                "root_mean_squared_error": 16, "mean_absolute_error": 32}
+_metrics_declared = [False]
+
+
+def metrics_update(pred, label, acc, metrics=("accuracy",)):
+    """Add one batch to the device accumulator `acc` (8 float64: samples, correct, cce, sparse cce, mse, rmse, mae, -)
+    in one launch and without a host synchronisation.  pred: [n, c] fp32/bf16; label: [n] int32/int64 class ids, or
+    [n, c] targets of pred's dtype."""
+    l = lib()
+    if not _metrics_declared[0]:
+        l.ffk_metrics_update.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        l.ffk_metrics_update.restype = c_int
+        _metrics_declared[0] = True
+    _cuda_contig(pred, label, acc)
+    n, c = pred.shape
+    if acc.dtype != torch.float64 or acc.numel() < 8:
+        raise KernelError("metrics accumulator must be 8 float64 values")
+    flags = 0
+    for m in metrics:
+        flags |= METRIC_FLAGS[m]
+    sparse = label.dtype in (torch.int32, torch.int64)
+    if not sparse and (label.dtype != pred.dtype or label.numel() != pred.numel()):
+        raise KernelError("dense metric targets must have the predictions' dtype and shape")
+    if sparse and label.numel() != n:
+        raise KernelError("sparse metric labels must be one class id per row")
+    _check(l.ffk_metrics_update(pred.data_ptr(), label.data_ptr() if sparse else None, None if sparse else label.data_ptr(), n, c,
+                                _dt(pred), _dt(label) if sparse else 0, flags, acc.data_ptr(), _stream()), "ffk_metrics_update")
+    return acc
+
+
 _stack_declared = [False]
 
 

@@ -3,7 +3,9 @@
 ``PerfMetrics`` has the fields of the reference's struct (lib/kernels/include/kernels/perf_metrics.dtg.toml):
 train_all, train_correct, cce, sparse_cce, mse, rmse, mae, start/current time; ``update`` computes them for a
 batch from predictions and labels (the reference's metrics kernels, lib/kernels/src/cuda/metrics_functions.cu:48-98,
-accumulate the same sums with atomics).  ``StepLogger`` writes one JSON line per step.
+accumulate the same sums with atomics).  Batches on the GPU go through ``ffk_metrics_update`` (csrc/kernels/metrics.cu):
+one launch per batch into a device accumulator that is read when a number is asked for.  ``StepLogger`` writes one
+JSON line per step.
 """
 from __future__ import annotations
 
@@ -32,10 +34,60 @@ class PerfMetrics:
     current_time: float = field(default_factory=time.time)
 
     def reset(self):
+        acc = self.__dict__.get("_dev")
+        if acc is not None:
+            acc.zero_()
+            self.__dict__["_dirty"] = False
         self.__init__()
+
+    # ---- device path: batches whose predictions live on the GPU are added by one kernel launch into a device
+    # accumulator (no host synchronisation per step); the fields above are refreshed from it when they are read
+    def _update_on_device(self, pred, label, metrics) -> bool:
+        from ..ops import kernels as K
+        if not (pred.is_cuda and K.available() and pred.dtype in (torch.float32, torch.bfloat16)):
+            return False
+        p = pred.detach().reshape(-1, pred.shape[-1]).contiguous()
+        n = p.shape[0]
+        sparse = label.dim() == 1 or label.numel() == n
+        lab = label.detach().to(p.device)
+        if sparse:
+            lab = lab.reshape(-1)
+            if lab.dtype not in (torch.int32, torch.int64):
+                lab = lab.long()
+        else:
+            lab = lab.reshape(n, -1).to(p.dtype)
+        acc = self.__dict__.get("_dev")
+        if acc is None or acc.device != p.device:
+            self.pull()
+            acc = torch.zeros(8, dtype=torch.float64, device=p.device)
+            self.__dict__["_dev"] = acc
+        K.metrics_update(p, lab.contiguous(), acc, [m for m in metrics if m in K.METRIC_FLAGS])
+        self.__dict__["_dirty"] = True
+        return True
+
+    def pull(self):
+        """Fold the device accumulator into the host fields (one device-to-host read)."""
+        acc = self.__dict__.get("_dev")
+        if acc is None or not self.__dict__.get("_dirty"):
+            return self
+        v = acc.cpu().tolist()
+        acc.zero_()
+        self.__dict__["_dirty"] = False
+        self.train_all += int(round(v[0]))
+        self.train_correct += int(round(v[1]))
+        self.cce_loss += v[2]
+        self.sparse_cce_loss += v[3]
+        self.mse_loss += v[4]
+        self.rmse_loss += v[5]
+        self.mae_loss += v[6]
+        return self
 
     def update(self, pred: torch.Tensor, label: torch.Tensor, metrics: Iterable[str] = ("accuracy",)):
         """pred: [N, C] probabilities or values; label: [N] class ids (sparse) or [N, C] targets."""
+        metrics = tuple(metrics)
+        if self._update_on_device(pred, label, metrics):
+            self.current_time = time.time()
+            return self
         p = pred.detach().float().reshape(-1, pred.shape[-1])
         n = p.shape[0]
         sparse = label.dim() == 1 or label.numel() == n
@@ -62,12 +114,15 @@ class PerfMetrics:
 
     @property
     def accuracy(self) -> float:
+        self.pull()
         return self.train_correct / max(self.train_all, 1)
 
     def throughput(self) -> float:
+        self.pull()
         return self.train_all / max(self.current_time - self.start_time, 1e-9)
 
     def summary(self) -> dict:
+        self.pull()
         n = max(self.train_all, 1)
         return {"samples": self.train_all, "accuracy": self.accuracy, "cce": self.cce_loss / n,
                 "sparse_cce": self.sparse_cce_loss / n, "mse": self.mse_loss / n, "rmse": self.rmse_loss / n,

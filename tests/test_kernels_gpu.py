@@ -354,3 +354,26 @@ def test_dropout_fused_into_gemm_epilogue_and_its_backward_use_the_standalone_ma
     other = K.matmul_nt(x, w, bias=bias, act="gelu", dropout=(p, salt, seed2))
     assert not torch.equal(other == 0, fused == 0)
     assert K.gemm_last_error() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_metrics_kernel_matches_the_host_computation(dtype):
+    """Accuracy and the five losses accumulated on the device over two batches equal the torch computation on the host."""
+    from flexflow_train_b200.utils.metrics import METRICS, PerfMetrics
+
+    torch.manual_seed(8)
+    dev_m, host_m = PerfMetrics(), PerfMetrics()
+    for n, c in ((300, 10), (77, 1000)):
+        p = torch.softmax(torch.randn(n, c), -1).to(dtype)
+        sparse = torch.randint(0, c, (n,), dtype=torch.int32)
+        dense = torch.softmax(torch.randn(n, c), -1).to(dtype)
+        for lab in (sparse, dense):
+            dev_m.update(p.cuda(), lab.cuda(), METRICS)
+            host_m.update(p, lab if lab.dtype == torch.int32 else lab.float(), METRICS)
+    a, b = dev_m.summary(), host_m.summary()
+    assert a["samples"] == b["samples"] == 2 * (300 + 77)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    for key in ("accuracy", "cce", "sparse_cce", "mse", "rmse", "mae"):
+        assert abs(a[key] - b[key]) <= tol * abs(b[key]) + 1e-7, (key, a[key], b[key])
+    dev_m.reset()
+    assert dev_m.summary()["samples"] == 0
