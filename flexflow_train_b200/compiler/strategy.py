@@ -253,7 +253,18 @@ def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
         with open(config.import_strategy_file) as f:
             return core.Graph.from_v1(f.read()), {"imported": config.import_strategy_file}
     algo = getattr(config, "search_algorithm", "unity")
+    rules, extra = None, {}
+    path = getattr(config, "substitution_json_path", None)
+    if path:
+        # legacy TASO-format rule collection (the reference's --substitution-json): the rules that convert are added
+        # to the generated set, so the templates still find their rules by name and the search can apply the rest
+        with open(path) as f:
+            legacy, st = core.load_legacy_rules(f.read())
+        rules = list(core.get_substitution_set(machine_for(world))) + [r for r in legacy if r.is_valid()]
+        extra = {"substitution_json": {"path": path, "rules_in_file": st["num_rules"], "rules_loaded": st["num_converted"]}}
     r = optimize(cg, world=world, algorithm=algo, budget=getattr(config, "search_budget", 0),
                  alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
-                 only_data_parallel=getattr(config, "only_data_parallel", False))
-    return r["mapped_pcg"], r["stats"]
+                 only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules)
+    stats = dict(r["stats"])
+    stats.update(extra)
+    return r["mapped_pcg"], stats

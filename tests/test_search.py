@@ -178,3 +178,24 @@ def test_table_parallel_strategy_keeps_lookups_whole_and_shards_the_rest():
     assert forced["stats"]["seed_strategy"] == "dp4+tables_mp4"
     with pytest.raises(ValueError):
         S.table_parallel_strategy(c.build_model("mlp", {}), 2)
+
+
+def test_substitution_json_rules_join_the_search(tmp_path):
+    """FFConfig.substitution_json_path (the reference's --substitution-json): a legacy rule collection is loaded and
+    offered to the search next to the generated rules."""
+    import json
+    import os
+
+    from flexflow_train_b200.api import FFConfig
+
+    ref = os.path.join(os.environ.get("FF_REFERENCE_DIR") or
+                       os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"),
+                       "substitutions", "test_subst.json")
+    if not os.path.exists(ref):
+        pytest.skip("legacy rule files not available")
+    cg = c.build_model("mlp", {})
+    cfg = FFConfig(batch_size=64, search_budget=4, substitution_json_path=ref)
+    pcg, stats = S.choose_strategy(cg, 2, cfg)
+    assert stats["substitution_json"]["rules_in_file"] == 1 and stats["substitution_json"]["rules_loaded"] == 1
+    assert "unity" in stats and len(pcg.nodes()) > 0
+    json.dumps(stats["substitution_json"])
