@@ -132,9 +132,20 @@ def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None
         if config.import_strategy_file:
             with open(config.import_strategy_file) as f:
                 strategy = core.Graph.from_v1(f.read())
-        ex = Executable(strategy, exec_cfg)
+        if device == "cpu":
+            # reference-semantics execution on the host (fp32, torch autograd): for machines without a GPU and for
+            # checking a model before it goes to one
+            from .runtime.cpu_executor import CpuExecutable
+            exec_cfg.compute_dtype = "fp32"
+            ex = CpuExecutable(strategy, exec_cfg)
+        else:
+            ex = Executable(strategy, exec_cfg)
     cm = CompiledModel(cg, ex, strategy, stats)
     if config.export_strategy_file and (dist is None or dist.rank == 0):
         with open(config.export_strategy_file, "w") as f:
             f.write(strategy.to_v1_string(parallel=True, indent=1))
+    if config.export_strategy_computation_graph_file and (dist is None or dist.rank == 0):
+        # the chosen parallel computation graph as a dot file (the reference's --export-strategy-computation-graph-file)
+        with open(config.export_strategy_computation_graph_file, "w") as f:
+            f.write(strategy.as_dot())
     return cm

@@ -39,6 +39,28 @@ def data_parallel_rules(rules, degree: int):
     return _rules_named(rules, pred)
 
 
+def is_parameter_parallel_rule(name: str) -> bool:
+    """Rules that shard an operator's weights (column / row parallel Linear, head-parallel attention)."""
+    return name.startswith(("replicate_linear_combine", "partition_linear_reduce", "replicate_attention_reduce"))
+
+
+def is_attribute_parallel_rule(name: str) -> bool:
+    """Partition rules on a dim other than the sample dim (the reference's attribute parallelism)."""
+    if not (name.startswith("partition_") and "_combine_" in name):
+        return False
+    parts = name.replace("_bias", "").replace("_affine", "").split("_")
+    tail = parts[parts.index("combine") + 1:]
+    if len(tail) < 2 or not all(t.isdigit() for t in tail[-2:]):
+        return False  # rules without a dim in their name shard the sample dim
+    return int(tail[-2]) != 0
+
+
+def filter_rules(rules, enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True):
+    return [r for r in rules
+            if (enable_parameter_parallel or not is_parameter_parallel_rule(r.name))
+            and (enable_attribute_parallel or not is_attribute_parallel_rule(r.name))]
+
+
 def apply_where(graph, rule, pred: Callable, max_total_degree: int = 0, with_graph: bool = False):
     """Apply `rule` at every match whose first pattern node satisfies pred(node dict) -- or pred(graph, node dict)
     with ``with_graph``, for predicates that look at the node's neighbours in the current graph."""
@@ -196,7 +218,8 @@ def shard_replicated_operators(g, world: int, rules):
 
 def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = "unity", budget: int = 0, alpha: float = 1.05,
              estimator=None, rules=None, seed: int = 0, mcmc_iterations: int = 200, mcmc_temperature: float = 1.0,
-             substitution_frequency: float = 0.2, time_limit_s: float = 120.0, only_data_parallel: bool = False) -> dict:
+             substitution_frequency: float = 0.2, time_limit_s: float = 120.0, only_data_parallel: bool = False,
+             enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True) -> dict:
     """Search a strategy.  Returns ``{"pcg", "mapped_pcg", "runtime_ms", "memory_bytes", "stats", "candidates"}``."""
     if machine is None:
         machine = machine_for(world or 1)
@@ -208,7 +231,7 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
     cands: Dict[str, object] = {"single_device": base}
     if W > 1:
         cands[f"dp{W}"] = data_parallel_strategy(cg, W, rules)
-        if not only_data_parallel and algorithm != "data_parallel":
+        if not only_data_parallel and algorithm != "data_parallel" and enable_parameter_parallel:
             try:
                 cands[f"tp{W}"] = tensor_parallel_strategy(cg, W, rules)
             except Exception:  # a model without the pattern simply has no such candidate
@@ -228,13 +251,15 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
     stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
     if algorithm == "unity" and budget > 0 and W > 1:
         use = rules if not only_data_parallel else data_parallel_rules(rules, W) + cancellation_rules(rules)
+        use = filter_rules(use, enable_parameter_parallel, enable_attribute_parallel)
         r = core.unity_search(best["pcg"], machine, estimator, use, alpha, budget, 100000, time_limit_s)
         stats["unity"] = r["stats"]
         if r["runtime_ms"] < best["runtime_ms"]:
             best = r
             stats["seed_strategy"] += "+unity"
     elif algorithm == "mcmc" and W > 1:
-        r = core.mcmc_search(best["pcg"], machine, estimator, rules, mcmc_temperature, mcmc_iterations, substitution_frequency, seed)
+        r = core.mcmc_search(best["pcg"], machine, estimator, filter_rules(rules, enable_parameter_parallel, enable_attribute_parallel),
+                             mcmc_temperature, mcmc_iterations, substitution_frequency, seed)
         stats["mcmc"] = r["stats"]
         # MCMC scores with the simulator; re-score with the mapping DP for a comparable number
         rescored = core.evaluate_pcg(r["pcg"], machine, estimator)
@@ -264,7 +289,9 @@ def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
         extra = {"substitution_json": {"path": path, "rules_in_file": st["num_rules"], "rules_loaded": st["num_converted"]}}
     r = optimize(cg, world=world, algorithm=algo, budget=getattr(config, "search_budget", 0),
                  alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
-                 only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules)
+                 only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules,
+                 enable_parameter_parallel=getattr(config, "enable_parameter_parallel", True),
+                 enable_attribute_parallel=getattr(config, "enable_attribute_parallel", True))
     stats = dict(r["stats"])
     stats.update(extra)
     return r["mapped_pcg"], stats

@@ -199,3 +199,45 @@ def test_substitution_json_rules_join_the_search(tmp_path):
     assert stats["substitution_json"]["rules_in_file"] == 1 and stats["substitution_json"]["rules_loaded"] == 1
     assert "unity" in stats and len(pcg.nodes()) > 0
     json.dumps(stats["substitution_json"])
+
+
+def test_parameter_and_attribute_parallel_flags_restrict_the_search():
+    ms = c.MachineSpecification(1, 4)
+    rules = c.get_substitution_set(ms)
+    names = [r.name for r in rules]
+    assert any(S.is_parameter_parallel_rule(n) for n in names) and any(S.is_attribute_parallel_rule(n) for n in names)
+    assert S.is_attribute_parallel_rule("partition_RELU_combine_1_4") and not S.is_attribute_parallel_rule("partition_RELU_combine_0_4")
+    assert not S.is_attribute_parallel_rule("partition_conv2d_combine_4_bias")
+    assert S.is_attribute_parallel_rule("partition_linear_combine_1_2_bias") and S.is_parameter_parallel_rule("replicate_linear_combine_4")
+    kept = S.filter_rules(rules, enable_parameter_parallel=False, enable_attribute_parallel=False)
+    assert kept and not any(S.is_parameter_parallel_rule(r.name) or S.is_attribute_parallel_rule(r.name) for r in kept)
+    assert len(S.filter_rules(rules)) == len(rules)
+    cg = c.build_model("transformer_lm", {"num_features": 64, "sequence_length": 16, "batch_size": 8, "dim_feedforward": 128,
+                                          "num_heads": 2, "num_decoder_layers": 1, "vocab_size": 64})
+    full = S.optimize(cg, world=2)
+    no_pp = S.optimize(cg, world=2, enable_parameter_parallel=False)
+    assert "tp2" in full["stats"]["candidates"] and "tp2" not in no_pp["stats"]["candidates"]
+
+
+def test_compile_on_cpu_exports_strategy_and_graph_files(tmp_path):
+    """api.compile(device="cpu") trains on the host executor; the strategy JSON and the dot file of the chosen
+    graph are written where FFConfig says."""
+    import torch
+
+    from flexflow_train_b200 import api
+    from flexflow_train_b200.runtime.executor import OptimizerConfig
+
+    cfg = api.FFConfig(batch_size=16, export_strategy_file=str(tmp_path / "strategy.json"),
+                       export_strategy_computation_graph_file=str(tmp_path / "pcg.dot"))
+    cm = api.compile("mlp", {"batch_size": 16}, config=cfg, optimizer=OptimizerConfig(kind="sgd", lr=0.1), device="cpu")
+    g = cm.graph
+    ins = {}
+    for n in g.nodes():
+        if n["type"] == "INPUT":
+            ins[n["name"]] = torch.randn([int(v) for v in n["outputs"][0][1].sizes])
+    out_sizes = [int(v) for v in g.shape(cm.executable.loss_value).sizes]
+    labels = torch.randint(0, out_sizes[-1], (out_sizes[0],), dtype=torch.int32)
+    losses = [cm.train_step(ins, labels) for _ in range(5)]
+    assert losses[-1] < losses[0]
+    assert (tmp_path / "pcg.dot").read_text().lstrip().startswith("digraph")
+    assert c.Graph.from_v1((tmp_path / "strategy.json").read_text()).signature() == g.signature()
