@@ -94,6 +94,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# how each model's timed steps relate to the 126 MB L2 (timing rule: inputs larger than L2, or a flush between steps)
+L2_NOTE = {
+    "transformer_large": "activations and weights per step (>100 GB) exceed the 126 MB L2; no flush needed",
+    "transformer_small": "weights, optimizer state and activations per step (>1 GB) exceed the 126 MB L2; no flush needed",
+    "bert_base": "activations and weights per step (>10 GB) exceed the 126 MB L2; no flush needed",
+    "inception_v3": "activations per step (>20 GB) exceed the 126 MB L2; no flush needed",
+    "dlrm": "2 GB of embedding tables, rows drawn at random: every step's lookups miss L2; the MLP working set (a few MB) stays resident, as it does in training",
+}
+
+
 def reference_arm(args):
     # The reference is C++/CMake with no Python project at its root; the one offline pip install that is
     # allowed fails before any build starts (no setup.py / pyproject.toml; its legacy bindings need the
@@ -302,9 +312,12 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq,
-                       "parallelism": getattr(ex, "parallelism", "single"), "layers": mcfg.get("num_decoder_layers", 12),
-                       "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768)), "optimizer": opt_kind, "lr": lr,
-                       "l2": "activations and weights per step (>100 GB) exceed the 126 MB L2; no flush needed",
+                       "parallelism": getattr(ex, "parallelism", "single"),
+                       **({"layers": mcfg.get("num_decoder_layers", mcfg.get("num_encoder_layers", 12)),
+                           "d_model": mcfg.get("num_features", mcfg.get("hidden_size", 768))}
+                          if model_name in ("transformer_lm", "transformer", "bert") else {}),
+                       "optimizer": opt_kind, "lr": lr,
+                       "l2": L2_NOTE[args.model],
                        "cuda_graph": bool(ex.cfg.use_cuda_graph), "tokens_per_s": value * seq,
                        "fused_collective_gemms": len(getattr(ex, "fused_in", [])) + len(getattr(ex, "fused_out", []))},
             "clocks": clocks,
