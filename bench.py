@@ -55,8 +55,51 @@ class ClockSampler:
         self.proc = None
         self.lines = []
         self.gpu_index = gpu_index
+        self.nvml = None       # (module, device handle) when NVML can be read in-process
+        self.samples = []      # (sm MHz, max MHz, reason bitmask) from NVML
+        self._stop = False
+
+    def _nvml_open(self):
+        import pynvml
+        pynvml.nvmlInit()
+        h = None
+        try:  # the CUDA device's own UUID, so that device ordering cannot pick another GPU
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            h = None
+        if h is None:
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+        pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)  # fails here rather than in the thread
+        return pynvml, h
+
+    def _nvml_sample(self):
+        nv, h = self.nvml
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.samples.append((float(sm), float(mx), int(get(h))))
+        except Exception:
+            pass
+
+    def _nvml_loop(self):
+        # read-only queries; every 5 ms for the first second (a timed region can be a few milliseconds), then every 100 ms
+        n = 0
+        while not self._stop:
+            self._nvml_sample()
+            n += 1
+            time.sleep(0.005 if n < 200 else 0.1)
 
     def start(self):
+        try:
+            self.nvml = self._nvml_open()
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
                                           "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -70,6 +113,17 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self._nvml_sample()  # at least one reading taken while the last timed kernels are still in flight
+            self._stop = True
+            self.thread.join(timeout=2)
+            sm = sorted(x[0] for x in self.samples)
+            mask = 0
+            for x in self.samples:
+                mask |= x[2]
+            names = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max((x[1] for x in self.samples), default=None),
+                    "reasons": sorted(n for n, bit in names if mask & bit), "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
