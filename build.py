@@ -6,7 +6,7 @@
 
 Both are compiled straight with nvcc / g++ (no JIT cache), so the shared
 objects sit inside the package and travel with a copy of the tree.
-Usage: python build.py [--force] [--kernels-only|--core-only] [-v]
+Usage: python build.py [--force] [--kernels-only|--core-only] [--sanitize] [--ptxas-info] [-v]
 """
 import glob
 import os
@@ -64,27 +64,31 @@ def build_kernels(force=False, verbose=False, ptxas_info=False):
     return out
 
 
-def build_core(force=False, verbose=False):
+def build_core(force=False, verbose=False, sanitize=False):
+    """The compiler core.  ``sanitize``: a second copy instrumented with UBSan (undefined behaviour aborts the
+    process), written to build/core_ubsan/ and never into the package; the test suite loads it by path."""
     import pybind11
 
-    os.makedirs(os.path.join(BUILD, "core"), exist_ok=True)
+    sub = "core_ubsan" if sanitize else "core"
+    os.makedirs(os.path.join(BUILD, sub), exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cc")))
     if not srcs:
         return None
     hdrs = glob.glob(os.path.join(CSRC, "*.h"))
     ext = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
-    out = os.path.join(PKG, "_ffcore" + ext)
+    out = os.path.join(BUILD, sub, "_ffcore" + ext) if sanitize else os.path.join(PKG, "_ffcore" + ext)
     inc = ["-I" + pybind11.get_include(), "-I" + sysconfig.get_paths()["include"], "-I" + CSRC]
+    opt = ["-O1", "-g", "-fsanitize=undefined", "-fno-sanitize-recover=undefined"] if sanitize else ["-O2"]
     objs, jobs = [], []
     for s in srcs:
-        o = os.path.join(BUILD, "core", os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(BUILD, sub, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or _stale(o, [s] + hdrs):
-            jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-sign-compare"] + inc + ["-c", s, "-o", o])
+            jobs.append(["g++"] + opt + ["-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-sign-compare"] + inc + ["-c", s, "-o", o])
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         list(ex.map(lambda c: _run(c, verbose), jobs))
     if jobs or force or _stale(out, objs):
-        _run(["g++", "-shared", "-o", out] + objs, verbose)
+        _run(["g++", "-shared", "-o", out] + objs + (["-fsanitize=undefined"] if sanitize else []), verbose)
     return out
 
 
@@ -99,3 +103,5 @@ if __name__ == "__main__":
         print(build_kernels(force, verbose, ptxas_info="--ptxas-info" in sys.argv))
     if "--kernels-only" not in sys.argv:
         print(build_core(force, verbose))
+        if "--sanitize" in sys.argv:
+            print(build_core(force, verbose, sanitize=True))
