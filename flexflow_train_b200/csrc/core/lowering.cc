@@ -41,6 +41,34 @@ Json invocation(const std::string &task, NodeId node, const Node &n) {
   j["outputs"] = Json::array();
   return j;
 }
+// Pass-state predicates, checked at pass boundaries (the reference asserts no_part_of_graph_is_* before a pass and
+// graph_is_fully_* after it, e.g. lib/task-spec/src/task-spec/dynamic_graph/shard_expansion.cc:142,149): a pass
+// applied twice, or in the wrong order, is a programming error that should fail at once, not produce a plan with
+// duplicated backward tasks.
+int count_task(const Json &list, const std::string &task) {
+  int n = 0;
+  for (auto &inv : list.items())
+    if (inv.at("task").as_string() == task) ++n;
+  return n;
+}
+bool no_part_is_pass_expanded(const Json &list) { return count_task(list, "BWD") == 0; }
+bool no_part_has_loss(const Json &list) { return count_task(list, "LOSS") == 0; }
+bool no_part_has_updates(const Json &list) { return count_task(list, "UPD") == 0; }
+bool no_part_has_copies(const Json &list) { return count_task(list, "COPY") == 0; }
+bool no_part_is_shard_expanded(const Json &list) {
+  for (auto &inv : list.items())
+    if (!inv.at("shard").is_null() || !inv.at("device").is_null()) return false;
+  return true;
+}
+bool fully_shard_expanded(const Json &list) {
+  for (auto &inv : list.items())
+    if (inv.at("shard").is_null() || inv.at("device").is_null()) return false;
+  return true;
+}
+void require_state(bool ok, const char *pass, const char *what) {
+  if (!ok) throw Error(std::string(pass) + ": " + what);
+}
+
 bool is_float(DataType d) { return d == DataType::FLOAT || d == DataType::HALF || d == DataType::DOUBLE || d == DataType::BFLOAT16; }
 
 std::map<ValueRef, bool> grad_values(const Graph &g) {
@@ -76,6 +104,8 @@ Json make_dynamic_graph(const Graph &g) {
 
 // every operator that propagates a gradient gets a BWD twin, appended in reverse topological order
 Json perform_pass_expansion(const Graph &g, const Json &list) {
+  require_state(no_part_is_pass_expanded(list), "pass expansion", "the graph already has backward tasks");
+  require_state(no_part_is_shard_expanded(list), "pass expansion", "the graph is already shard-expanded");
   Json out = list;
   auto req = grad_values(g);
   auto order = g.topological_order();
@@ -108,6 +138,8 @@ Json perform_pass_expansion(const Graph &g, const Json &list) {
 
 // LOSS consumes the logit and the label and produces the logit's gradient; it sits between the last FWD and the first BWD
 Json perform_loss_insertion(const Graph &g, const Json &list, const ValueRef &logit, const Json &loss_attrs) {
+  require_state(no_part_has_loss(list), "loss insertion", "the graph already has a loss task");
+  require_state(no_part_is_shard_expanded(list), "loss insertion", "the graph is already shard-expanded");
   Json out = Json::array();
   Json loss = Json::object();
   loss["task"] = "LOSS";
@@ -133,6 +165,8 @@ Json perform_loss_insertion(const Graph &g, const Json &list, const ValueRef &lo
 
 // one UPD invocation per trainable weight, with the optimizer's state slots (SGD: momentum; Adam: m, v)
 Json perform_update_insertion(const Graph &g, const Json &list, const Json &optimizer_attrs) {
+  require_state(no_part_has_updates(list), "update insertion", "the graph already has update tasks");
+  require_state(no_part_is_shard_expanded(list), "update insertion", "the graph is already shard-expanded");
   Json out = list;
   std::string kind = optimizer_attrs.get_string("type", "sgd");
   std::vector<std::string> slots;
@@ -167,6 +201,8 @@ static std::vector<int> devices_of(const Graph &g, NodeId n, const MachineSpec &
 // where a consumer's devices differ from its producer's, a COPY invocation moves the value (and, in the
 // backward direction, its gradient)
 Json perform_copy_insertion(const Graph &g, const Json &list, const MachineSpec &m) {
+  require_state(no_part_has_copies(list), "copy insertion", "the graph already has copy tasks");
+  require_state(no_part_is_shard_expanded(list), "copy insertion", "copies are inserted before shard expansion");
   Json out = Json::array();
   for (auto &inv : list.items()) {
     const std::string task = inv.at("task").as_string();
@@ -203,6 +239,7 @@ Json perform_copy_insertion(const Graph &g, const Json &list, const MachineSpec 
 
 // one invocation per shard of the operator's task space, bound to the device its machine view assigns
 Json perform_shard_expansion(const Graph &g, const Json &list, const MachineSpec &m) {
+  require_state(no_part_is_shard_expanded(list), "shard expansion", "the graph is already shard-expanded");
   Json out = Json::array();
   for (auto &inv : list.items()) {
     NodeId n = (NodeId)inv.at("node").as_int();
@@ -222,13 +259,15 @@ Json perform_shard_expansion(const Graph &g, const Json &list, const MachineSpec
       out.push_back(x);
     }
   }
+  require_state(fully_shard_expanded(out), "shard expansion", "a task was left without shard or device");
   return out;
 }
 
 Json perform_machine_slicing(const Json &list, int device) {
+  require_state(fully_shard_expanded(list), "machine slicing", "the graph must be shard-expanded first");
   Json out = Json::array();
   for (auto &inv : list.items())
-    if (inv.at("device").is_null() || inv.at("device").as_int() == device) out.push_back(inv);
+    if (inv.at("device").as_int() == device) out.push_back(inv);
   return out;
 }
 

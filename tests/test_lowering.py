@@ -2,6 +2,8 @@
 (reference: lib/task-spec/src/task-spec/dynamic_graph/*.cc and their tests under lib/task-spec/test)."""
 from collections import Counter
 
+import pytest
+
 from flexflow_train_b200 import _ffcore as core
 from flexflow_train_b200.compiler import strategy as S
 from flexflow_train_b200.runtime import lowering as L
@@ -128,3 +130,28 @@ def test_task_argument_accessor_runs_a_lowered_linear_layer_forward_backward_upd
     got_b = next(t for k, t in table.items() if nodes[k[0]]["name"] == "fc.bias" and k[2] == "FWD")
     assert torch.allclose(got_w, w0 - 0.1 * wt.grad, atol=1e-6)
     assert torch.allclose(got_b, b0 - 0.1 * bt.grad, atol=1e-6)
+
+
+def test_passes_check_the_state_they_require():
+    """Pass-state invariants at pass boundaries: a pass applied twice or out of order fails at once."""
+    from flexflow_train_b200 import _ffcore as core
+
+    cg = core.build_model("mlp", {})
+    ms = core.MachineSpecification(1, 2)
+    l0 = core.make_dynamic_graph(cg)
+    l1 = core.perform_pass_expansion(cg, l0)
+    with pytest.raises(core.CoreError, match="already has backward"):
+        core.perform_pass_expansion(cg, l1)
+    l2 = core.perform_update_insertion(cg, l1, {"type": "sgd"})
+    with pytest.raises(core.CoreError, match="already has update"):
+        core.perform_update_insertion(cg, l2, {"type": "sgd"})
+    with pytest.raises(core.CoreError, match="shard-expanded first"):
+        core.perform_machine_slicing(l2, 0)
+    l3 = core.perform_copy_insertion(cg, l2, ms)
+    l4 = core.perform_shard_expansion(cg, l3, ms)
+    assert all(i["shard"] is not None and i["device"] is not None for i in l4)
+    for fn in (lambda: core.perform_shard_expansion(cg, l4, ms), lambda: core.perform_copy_insertion(cg, l4, ms),
+               lambda: core.perform_pass_expansion(cg, l4)):
+        with pytest.raises(core.CoreError, match="shard-expanded"):
+            fn()
+    assert len(core.perform_machine_slicing(l4, 0)) > 0
