@@ -165,3 +165,66 @@ def run_with_recovery(step_fn: Callable[[int], None], num_steps: int, *, save_fn
                 raise
             step = restore_fn()
     return {"restarts": restarts, "steps_run": runs}
+
+
+class CollectiveWatchdog:
+    """Bounds the library collectives (NCCL on GPUs, gloo on the host) the way the device-side waits bound the
+    peer-memory kernels: the process group is created with a short timeout and asynchronous error handling, a
+    collective that a peer never joins then raises instead of blocking for the default half hour, and the failure
+    is turned into ``RankFailure`` after the communicator has been aborted so that no later call can block on it.
+
+        wd = CollectiveWatchdog(timeout_s=5)
+        wd.init_process_group("nccl", rank=r, world_size=w, device_id=dev)   # or wd.adopt(existing default group)
+        wd.run(dist.all_reduce, t)                                            # raises RankFailure on a dead peer
+    """
+
+    def __init__(self, timeout_s: float = 30.0, monitor: Optional[HeartbeatMonitor] = None):
+        self.timeout_s = float(timeout_s)
+        self.monitor = monitor
+        self.aborted = False
+
+    def init_process_group(self, backend: str, **kw):
+        import datetime
+
+        import torch.distributed as dist
+        if backend == "nccl":
+            # surface a collective that timed out or failed as an exception in the calling thread
+            os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # a rank that dies while bound to a multicast object faults its peers
+        dist.init_process_group(backend, timeout=datetime.timedelta(seconds=self.timeout_s), **kw)
+        return self
+
+    def abort(self):
+        """Tear the communicator down without waiting for outstanding collectives."""
+        import torch.distributed as dist
+        if self.aborted or not dist.is_initialized():
+            return
+        self.aborted = True
+        try:
+            pg = dist.distributed_c10d._get_default_group()
+            for dev in ("cuda", "cpu"):
+                try:
+                    be = pg._get_backend(__import__("torch").device(dev))
+                except Exception:
+                    continue
+                ab = getattr(be, "abort", None) or getattr(be, "_abort", None)
+                if ab is not None:
+                    ab()
+        except Exception:
+            pass
+
+    def run(self, fn: Callable, *args, **kw):
+        """Run one collective; a timeout or communicator error becomes RankFailure naming the ranks the heartbeat
+        monitor (if any) holds for dead."""
+        try:
+            out = fn(*args, **kw)
+            work = out if hasattr(out, "wait") else None
+            if work is not None:
+                work.wait()
+            return out
+        except InjectedFault:
+            raise
+        except Exception as e:  # torch raises RuntimeError / DistBackendError with backend-specific text
+            dead = self.monitor.dead_ranks() if self.monitor is not None else []
+            self.abort()
+            raise RankFailure(dead) from e

@@ -81,3 +81,55 @@ def test_rank_exit_is_detected_by_survivors_before_next_collective():
         kind, (done, dead) = by_rank[r][0]
         assert kind == "rank_failure" and dead == [fail_rank]
         assert done == fail_step  # every step before the failure completed on the survivors
+
+
+def _watchdog_worker(rank, world, port, q):
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    from flexflow_train_b200.utils import failure as F
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    wd = F.CollectiveWatchdog(timeout_s=3.0).init_process_group("gloo", rank=rank, world_size=world)
+    t = torch.ones(4)
+    wd.run(dist.all_reduce, t)  # everyone takes part: fine
+    ok = float(t[0]) == world
+    if rank == world - 1:
+        # this rank leaves between steps (no collective of its own in flight) and never joins the next one
+        q.put((rank, "left", ok))
+        q.close(); q.join_thread()
+        time.sleep(8)
+        os._exit(0)
+    t0 = time.time()
+    try:
+        wd.run(dist.all_reduce, t)
+        res = "completed"
+    except F.RankFailure:
+        res = "rank_failure"
+    q.put((rank, res, time.time() - t0))
+    q.close(); q.join_thread()
+    os._exit(0)
+
+
+def test_collective_watchdog_turns_a_missing_peer_into_rank_failure():
+    """Host-side failure injection on gloo ranks: a peer that never joins a collective makes the survivors' call end
+    with RankFailure within the process-group timeout instead of blocking."""
+    import torch.multiprocessing as mp
+
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_watchdog_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    msgs = [q.get(timeout=90) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    by_rank = {m[0]: m for m in msgs}
+    assert by_rank[world - 1][1] == "left" and by_rank[world - 1][2]
+    for r in range(world - 1):
+        assert by_rank[r][1] == "rank_failure", by_rank
+        assert by_rank[r][2] < 30, by_rank
