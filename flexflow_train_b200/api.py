@@ -34,6 +34,7 @@ class FFConfig:
     only_data_parallel: bool = False
     enable_parameter_parallel: bool = True
     enable_attribute_parallel: bool = True
+    score_hybrid_strategies: bool = False  # also estimate data x tensor parallel meshes (reported, not executed)
     substitution_json_path: Optional[str] = None
     export_strategy_file: Optional[str] = None
     import_strategy_file: Optional[str] = None

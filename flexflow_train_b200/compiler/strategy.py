@@ -197,6 +197,32 @@ def tensor_parallel_strategy(cg, world: int, rules=None, sequence_parallel: bool
     return core.merge_duplicate_parallel_ops(g)
 
 
+def hybrid_strategy(cg, dp: int, tp: int, rules=None):
+    """Data parallel of degree `dp` around tensor parallel of degree `tp` (dp * tp devices): the Megatron template at
+    degree tp with replicated activations, then the sample-dim rules at degree dp on every operator.  The
+    Combine(0, dp) that each data-parallel operator ends with is commuted past the template's Replicate / Reduction
+    so that it meets the next operator's Repartition(0, dp) and cancels; what remains is one Repartition of the
+    inputs, one Combine of the output and the tensor-parallel collectives inside each data-parallel replica.
+
+    The single-axis SPMD executor does not run such a graph; the strategy can be scored, searched from, exported and
+    imported."""
+    world = dp * tp
+    ms = machine_for(world)
+    rules = rules or core.get_substitution_set(ms)
+    if dp == 1:
+        return tensor_parallel_strategy(cg, tp, rules)
+    if tp == 1:
+        return data_parallel_strategy(cg, dp, rules)
+    g = tensor_parallel_strategy(cg, tp, rules, sequence_parallel=False)
+    g = core.apply_rules_exhaustively(g, data_parallel_rules(rules, dp) + cancellation_rules(rules), 100000, world)
+    tidy = cancellation_rules(rules) + list(core.get_commute_rules())
+    while True:
+        n0 = len(g.nodes())
+        g = core.apply_rules_exhaustively(core.merge_duplicate_parallel_ops(g), tidy, 100000, world)
+        if len(g.nodes()) == n0:
+            return g
+
+
 def shard_replicated_operators(g, world: int, rules):
     """Apply the sample-dim (dim 0) partition rules to every operator whose activations are still unsharded,
     then cancel the Combine/Repartition pairs that meet."""
@@ -219,7 +245,7 @@ def shard_replicated_operators(g, world: int, rules):
 def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = "unity", budget: int = 0, alpha: float = 1.05,
              estimator=None, rules=None, seed: int = 0, mcmc_iterations: int = 200, mcmc_temperature: float = 1.0,
              substitution_frequency: float = 0.2, time_limit_s: float = 120.0, only_data_parallel: bool = False,
-             enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True) -> dict:
+             enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True, score_hybrid: bool = False) -> dict:
     """Search a strategy.  Returns ``{"pcg", "mapped_pcg", "runtime_ms", "memory_bytes", "stats", "candidates"}``."""
     if machine is None:
         machine = machine_for(world or 1)
@@ -239,6 +265,18 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
             if has_stacked_embeddings(cg):
                 cands[f"dp{W}+tables_mp{W}"] = table_parallel_strategy(cg, W, rules)
     scored = {k: core.evaluate_pcg(g, machine, estimator) for k, g in cands.items()}
+    # data x tensor parallel meshes: scored for the report (and exportable through hybrid_strategy), never chosen,
+    # because the single-axis executor cannot run them
+    hybrid_scores = {}
+    if score_hybrid and W >= 4 and f"tp{W}" in cands:
+        tp = 2
+        while tp < W:
+            if W % tp == 0:
+                try:
+                    hybrid_scores[f"dp{W // tp}xtp{tp}"] = core.evaluate_pcg(hybrid_strategy(cg, W // tp, tp, rules), machine, estimator)["runtime_ms"]
+                except Exception:
+                    pass
+            tp *= 2
     if algorithm == "data_parallel" or only_data_parallel:
         best_name = f"dp{W}" if W > 1 else "single_device"
     elif algorithm == "tensor_parallel":
@@ -249,6 +287,8 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
         best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
     best = scored[best_name]
     stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
+    if hybrid_scores:
+        stats["hybrid_candidates_not_executable"] = hybrid_scores
     if algorithm == "unity" and budget > 0 and W > 1:
         use = rules if not only_data_parallel else data_parallel_rules(rules, W) + cancellation_rules(rules)
         use = filter_rules(use, enable_parameter_parallel, enable_attribute_parallel)
@@ -291,7 +331,8 @@ def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
                  alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
                  only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules,
                  enable_parameter_parallel=getattr(config, "enable_parameter_parallel", True),
-                 enable_attribute_parallel=getattr(config, "enable_attribute_parallel", True))
+                 enable_attribute_parallel=getattr(config, "enable_attribute_parallel", True),
+                 score_hybrid=getattr(config, "score_hybrid_strategies", False))
     stats = dict(r["stats"])
     stats.update(extra)
     return r["mapped_pcg"], stats

@@ -567,6 +567,20 @@ static Substitution cancel_pair_shared(OpType first, OpType second, const std::s
   s.outputs = {{0, Slot::OUTPUT, 0, Slot::OUTPUT}, {1, Slot::OUTPUT, -1, Slot::OUTPUT}};
   return s;
 }
+// first -> second  ==>  second -> first, both re-created from the matched operators' own attributes.  Shape inference
+// on the swapped pair decides whether the swap is legal at a match (the interface shape must come out unchanged).
+// Used to bring a Combine next to the Repartition behind a Replicate / Reduction (hybrid data x tensor parallel
+// graphs), after which the pair cancels.
+static Substitution commute_pair(OpType first, OpType second, const std::string &name) {
+  Substitution s = cancel_pair(first, second, name);
+  s.out_nodes = {templated(1, {ogin(Slot::INPUT, 0)}), templated(0, {onin(Slot::INPUT, 0)})};
+  s.outputs = {{1, Slot::OUTPUT, 1, Slot::OUTPUT}};
+  return s;
+}
+std::vector<Substitution> get_commute_rules() {
+  return {commute_pair(OpType::COMBINE, OpType::REPLICATE, "commute_combine_replicate"),
+          commute_pair(OpType::COMBINE, OpType::REDUCTION, "commute_combine_reduction")};
+}
 Substitution create_cancel_combine_repartition() { return cancel_pair(OpType::COMBINE, OpType::REPARTITION, "cancel_combine_repartition"); }
 Substitution create_cancel_repartition_combine() { return cancel_pair(OpType::REPARTITION, OpType::COMBINE, "cancel_repartition_combine"); }
 Substitution create_cancel_replicate_reduction_free() { return cancel_pair(OpType::REPLICATE, OpType::NOOP, "cancel_replicate_noop"); }
@@ -936,6 +950,7 @@ void bind_substitutions(py::module &m) {
   m.def("create_partition_layernorm_combine", &create_partition_layernorm_combine);
   m.def("create_partition_embedding_combine", &create_partition_embedding_combine);
   m.def("create_fuse_linear_activation", &create_fuse_linear_activation);
+  m.def("get_commute_rules", &get_commute_rules);
   m.def("create_cancel_combine_repartition", &create_cancel_combine_repartition);
   m.def("create_cancel_repartition_combine", &create_cancel_repartition_combine);
   m.def("load_legacy_rules", [](py::object collection) {

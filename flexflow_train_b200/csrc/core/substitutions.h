@@ -110,6 +110,9 @@ Substitution create_cancel_combine_repartition();   // Combine(d,k) -> Repartiti
 Substitution create_cancel_repartition_combine();
 Substitution create_cancel_replicate_reduction_free();  // Replicate(k) feeding only a Combine-free noop (kept for completeness)
 std::vector<Substitution> get_substitution_set(const MachineSpec &m, int max_dims = 4);
+// Combine -> Replicate / Reduction  ==>  Replicate / Reduction -> Combine (not part of the default set: the
+// tensor+sequence-parallel template wants Combine(0) -> Replicate to stay adjacent, as that pair is one all-gather)
+std::vector<Substitution> get_commute_rules();
 
 // legacy TASO rule files: {"_t":"RuleCollection","rule":[{"name","srcOp":[...],"dstOp":[...],"mappedOutput":[...]}]}
 struct LegacyRuleStats {

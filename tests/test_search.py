@@ -241,3 +241,27 @@ def test_compile_on_cpu_exports_strategy_and_graph_files(tmp_path):
     assert losses[-1] < losses[0]
     assert (tmp_path / "pcg.dot").read_text().lstrip().startswith("digraph")
     assert c.Graph.from_v1((tmp_path / "strategy.json").read_text()).signature() == g.signature()
+
+
+def test_hybrid_data_x_tensor_parallel_strategy_is_clean_and_scored():
+    """dp2 x tp4 on 8 devices: the commute rules bring every data-parallel Combine next to the following Repartition,
+    so only the input Repartition and the output Combine remain around the tensor-parallel collectives."""
+    cfg = {"num_features": 128, "sequence_length": 32, "batch_size": 16, "dim_feedforward": 256, "num_heads": 8,
+           "num_decoder_layers": 2, "vocab_size": 256}
+    cg = c.build_model("transformer_lm", cfg)
+    assert all(r.is_valid() for r in c.get_commute_rules())
+    g = S.hybrid_strategy(cg, 2, 4)
+    nodes = {n["id"]: n for n in g.nodes()}
+    act_parallel = [n for n in nodes.values() if n["type"] in ("COMBINE", "REPARTITION")
+                    and nodes[tuple(n["inputs"][0][1])[0]]["type"] != "WEIGHT"]
+    assert sorted(n["type"] for n in act_parallel) == ["COMBINE", "REPARTITION"]
+    lin = [n["outputs"][0][1] for n in nodes.values() if n["type"] == "LINEAR"]
+    assert any(list(sh.degrees) == [2, 1, 4] for sh in lin) and any(sh.sum_degree == 4 and sh.degrees[0] == 2 for sh in lin)
+    assert max(n["outputs"][0][1].total_degree for n in nodes.values()) == 8
+    text = g.to_v1_string(parallel=True)
+    assert c.Graph.from_v1(text).signature() == g.signature()
+    r = S.optimize(cg, world=8, score_hybrid=True)
+    hy = r["stats"]["hybrid_candidates_not_executable"]
+    assert set(hy) == {"dp4xtp2", "dp2xtp4"} and all(v > 0 for v in hy.values())
+    assert "x" not in r["stats"]["seed_strategy"]
+    assert "hybrid_candidates_not_executable" not in S.optimize(cg, world=8)["stats"]
