@@ -7,6 +7,7 @@ namespace ff {
 void bind_substitutions(py::module &m);
 void bind_search(py::module &m);
 void bind_lowering(py::module &m);
+void bind_utils(py::module &m);
 }  // namespace ff
 
 using namespace ff;
@@ -385,4 +386,5 @@ PYBIND11_MODULE(_ffcore, m) {
   bind_substitutions(m);
   bind_search(m);
   bind_lowering(m);
+  bind_utils(m);
 }

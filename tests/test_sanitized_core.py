@@ -49,6 +49,15 @@ DRIVER = textwrap.dedent('''
             core.Graph.from_v1(r["mapped_pcg"].to_v1_string(parallel=True))
         low = L.lower(S.optimize(cg, world=2, algorithm="data_parallel")["mapped_pcg"], optimizer={"kind": "adam"})
         assert len(low) > 0
+    U = core.utils
+    assert U.positive_mul(6, 7) == 42 and U.orthotope_flatten([2, 3, 4], [1, 2, 3]) == 23
+    try:
+        U.positive_mul(2 ** 62, 4)
+        raise SystemExit("overflow not reported")
+    except OverflowError:
+        pass
+    assert U.lift_coord([2, 3, 4], [[0, 1], [2]], U.project_coord([2, 3, 4], [[0, 1], [2]], [1, 2, 3])) == [1, 2, 3]
+    assert len(U.union_find_groups([(1, 2), (3, 4), (2, 3)])) == 1 and U.dedup_queue_order([2, 2, 1])[1] == [2, 1]
     print(json.dumps({"models": done, "rules": len(rules)}))
 ''')
 
