@@ -14,6 +14,7 @@
 #include <algorithm>
 #include <set>
 
+#include <cmath>
 #include "pyjson.h"
 #include "search.h"
 
@@ -285,7 +286,54 @@ Json lower_training_graph(const Graph &g, const MachineSpec &m, const std::optio
   return l;
 }
 
+// Optimizer attributes (lib/pcg/include/pcg/optimizers/{sgd,adam}_optimizer_attrs.dtg.toml) and the per-iteration
+// schedule of Adam's bias correction (lib/pcg/src/pcg/optimizer_attrs.cc:7-25): beta_t and beta2_t are the running
+// powers of beta1 and beta2, alpha_t = alpha * sqrt(1 - beta2_t) / (1 - beta_t) the step size of that iteration.
+Json make_sgd_optimizer_attrs(double lr, double momentum, bool nesterov, double weight_decay) {
+  if (lr < 0 || momentum < 0 || weight_decay < 0) throw Error("sgd optimizer: negative hyper-parameter");
+  Json a = Json::object();
+  a["type"] = "sgd";
+  a["lr"] = lr;
+  a["momentum"] = momentum;
+  a["nesterov"] = nesterov;
+  a["weight_decay"] = weight_decay;
+  return a;
+}
+Json make_adam_optimizer_attrs(double alpha, double beta1, double beta2, double weight_decay, double epsilon) {
+  if (alpha < 0 || beta1 < 0 || beta1 >= 1 || beta2 < 0 || beta2 >= 1 || epsilon <= 0) throw Error("adam optimizer: hyper-parameter out of range");
+  Json a = Json::object();
+  a["type"] = "adam";
+  a["alpha"] = alpha;
+  a["beta1"] = beta1;
+  a["beta2"] = beta2;
+  a["weight_decay"] = weight_decay;
+  a["epsilon"] = epsilon;
+  a["alpha_t"] = alpha;   // before the first iteration
+  a["beta_t"] = 1.0;
+  a["beta2_t"] = 1.0;
+  return a;
+}
+Json get_optimizer_attrs_for_next_iter(const Json &old) {
+  const std::string type = old.get_string("type", "sgd");
+  if (type == "sgd") return old;  // nothing changes between iterations
+  if (type != "adam") throw Error("unknown optimizer type " + type);
+  Json a = old;
+  const double beta_t = old.at("beta_t").as_float() * old.at("beta1").as_float();
+  const double beta2_t = old.at("beta2_t").as_float() * old.at("beta2").as_float();
+  a["beta_t"] = beta_t;
+  a["beta2_t"] = beta2_t;
+  a["alpha_t"] = old.at("alpha").as_float() * std::sqrt(1.0 - beta2_t) / (1.0 - beta_t);
+  return a;
+}
+
 void bind_lowering(py::module &m) {
+  m.def("make_sgd_optimizer_attrs", [](double lr, double momentum, bool nesterov, double wd) {
+    return json_to_py(make_sgd_optimizer_attrs(lr, momentum, nesterov, wd));
+  }, py::arg("lr"), py::arg("momentum") = 0.0, py::arg("nesterov") = false, py::arg("weight_decay") = 0.0);
+  m.def("make_adam_optimizer_attrs", [](double alpha, double b1, double b2, double wd, double eps) {
+    return json_to_py(make_adam_optimizer_attrs(alpha, b1, b2, wd, eps));
+  }, py::arg("alpha") = 1e-3, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("weight_decay") = 0.0, py::arg("epsilon") = 1e-8);
+  m.def("get_optimizer_attrs_for_next_iter", [](py::object a) { return json_to_py(get_optimizer_attrs_for_next_iter(json_from_py(a))); });
   m.def("make_dynamic_graph", [](const Graph &g) { return json_to_py(make_dynamic_graph(g)); });
   m.def("perform_pass_expansion", [](const Graph &g, py::object l) { return json_to_py(perform_pass_expansion(g, json_from_py(l))); });
   m.def("perform_loss_insertion", [](const Graph &g, py::object l, py::object logit, py::object attrs) {

@@ -155,3 +155,28 @@ def test_passes_check_the_state_they_require():
         with pytest.raises(core.CoreError, match="shard|backward"):
             fn()
     assert len(core.perform_machine_slicing(l4, 0)) > 0
+
+
+def test_optimizer_attrs_and_adam_bias_correction_schedule():
+    import math
+
+    from flexflow_train_b200 import _ffcore as core
+
+    sgd = core.make_sgd_optimizer_attrs(0.1, momentum=0.9, nesterov=True, weight_decay=1e-4)
+    assert sgd == {"type": "sgd", "lr": 0.1, "momentum": 0.9, "nesterov": True, "weight_decay": 1e-4}
+    assert core.get_optimizer_attrs_for_next_iter(sgd) == sgd
+    a = core.make_adam_optimizer_attrs(alpha=1e-3, beta1=0.9, beta2=0.999)
+    assert a["beta_t"] == 1.0 and a["beta2_t"] == 1.0
+    for t in range(1, 6):
+        a = core.get_optimizer_attrs_for_next_iter(a)
+        assert a["beta_t"] == pytest.approx(0.9 ** t) and a["beta2_t"] == pytest.approx(0.999 ** t)
+        # the executors' closed form for step t
+        assert a["alpha_t"] == pytest.approx(1e-3 * math.sqrt(1 - 0.999 ** t) / (1 - 0.9 ** t))
+    with pytest.raises(core.CoreError):
+        core.make_adam_optimizer_attrs(beta1=1.0)
+    with pytest.raises(core.CoreError):
+        core.make_sgd_optimizer_attrs(-1.0)
+    # the update-insertion pass takes these attribute objects as they are
+    cg = core.build_model("mlp", {})
+    l = core.perform_update_insertion(cg, core.perform_pass_expansion(cg, core.make_dynamic_graph(cg)), a)
+    assert any(i["task"] == "UPD" and any(v["role"] == "OPT:m" for v in i["inputs"]) for i in l)
