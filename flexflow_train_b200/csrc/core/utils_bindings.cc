@@ -3,6 +3,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "flag_protocol.h"
 #include "utils.h"
 
 namespace py = pybind11;
@@ -155,6 +156,28 @@ void bind_utils(py::module &root) {
     if (!ids.empty()) g.remove_edge(ids.front());
     return py::make_tuple(g.nodes().size(), between, g.num_edges(), g.outgoing(a).size(), g.incoming(b).size());
   });
+  // ---- flag protocol of the peer-memory kernels, with threads as ranks
+  m.def("flag_protocol_rounds", [](int ranks, int epochs, int silent_rank, int silent_after, int limit_ms) {
+    std::vector<flagproto::RankResult> res;
+    {
+      py::gil_scoped_release release;
+      res = flagproto::run_rounds(ranks, epochs, silent_rank, silent_after, limit_ms);
+    }
+    py::list out;
+    for (auto &r : res) {
+      py::dict d;
+      d["epochs_done"] = r.epochs_done;
+      d["ok"] = r.report.ok;
+      d["waiter"] = r.report.waiter;
+      d["peer"] = r.report.peer;
+      d["expected"] = r.report.expected;
+      d["seen"] = r.report.seen;
+      d["checksum"] = r.checksum;
+      d["seconds"] = r.seconds;
+      out.append(d);
+    }
+    return out;
+  }, py::arg("ranks"), py::arg("epochs"), py::arg("silent_rank") = -1, py::arg("silent_after") = 0, py::arg("limit_ms") = 2000);
   // ---- formatters
   m.def("dot_text", [](const std::vector<std::string> &nodes, const std::vector<std::pair<std::string, std::string>> &edges) {
     DotFile d("g");

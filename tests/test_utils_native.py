@@ -113,3 +113,25 @@ def test_graph_variants_and_formatters():
     dot = U.dot_text(["a", 'b"q'], [("a", 'b"q')])
     assert dot.startswith("digraph g {") and "subgraph cluster_0" in dot and '"a" -> "b\\"q";' in dot and 'shape="record"' in dot
     assert U.record_text(["op", "x|y"], ["in", "out"]) == "{op|x\\|y|{in|out}}"
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_flag_protocol_with_threads_as_ranks(ranks):
+    """The epoch-flag protocol of the peer-memory kernels on host threads: publish, barrier, read, barrier for many
+    epochs without ever resetting a flag; every rank sees every peer's value of the same epoch."""
+    epochs = 300
+    res = U.flag_protocol_rounds(ranks, epochs)
+    want = sum(e * 1000 + p for e in range(1, epochs + 1) for p in range(ranks))
+    for r in res:
+        assert r["ok"] and r["epochs_done"] == epochs and r["checksum"] == want, r
+
+
+def test_flag_protocol_bounded_wait_reports_a_silent_rank():
+    """A rank that stops signalling (it left between steps) costs its peers one bounded wait; each reports who it
+    waited for, the epoch it expected and the epoch it saw, and nobody spins on."""
+    res = U.flag_protocol_rounds(3, 50, silent_rank=1, silent_after=7, limit_ms=300)
+    assert res[1]["ok"] and res[1]["epochs_done"] == 7
+    for r in (res[0], res[2]):
+        assert not r["ok"] and r["epochs_done"] == 7
+        assert (r["peer"], r["expected"], r["seen"]) == (1, 8, 7)
+        assert 0.25 < r["seconds"] < 5.0
