@@ -65,15 +65,19 @@ def synthetic_batch(graph, executable, loss: str, seed: int = 0, pinned: bool = 
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="run-model", description=__doc__.split("\n")[0])
+    p.add_argument("graph_json", nargs="?", help="a v1 JSON file (computation graph, parallel or mapped parallel computation graph) to "
+                   "train instead of a model-zoo model: as the reference's run-model, 5 iterations of SGD(0.001, momentum 0.9) "
+                   "unless --iterations / --optimizer / --learning-rate say otherwise")
+    p.add_argument("--device", choices=["cuda", "cpu"], default=None, help="cpu: host executor (fp32); default: the GPU")
     p.add_argument("--model", default="transformer", choices=sorted(core.model_names()))
     p.add_argument("--model-config", help="JSON object overriding fields of the model's default config")
     p.add_argument("-e", "--epochs", type=int, default=1)
     p.add_argument("-b", "--batch-size", type=int, default=None)
     p.add_argument("-p", "--print-freq", type=int, default=10)
     p.add_argument("-d", "--dataset", default=None, help="ignored: data is synthetic")
-    p.add_argument("--iterations", type=int, default=20, help="steps per epoch")
+    p.add_argument("--iterations", type=int, default=None, help="steps per epoch (default 20; 5 for a graph file)")
     p.add_argument("--learning-rate", type=float, default=1e-3)
-    p.add_argument("--optimizer", choices=["sgd", "adam"], default="adam")
+    p.add_argument("--optimizer", choices=["sgd", "adam"], default=None, help="default adam; sgd with momentum 0.9 for a graph file")
     p.add_argument("--search-budget", type=int, default=0)
     p.add_argument("--search-alpha", type=float, default=1.05)
     p.add_argument("--search-algorithm", choices=["unity", "mcmc", "data_parallel", "tensor_parallel", "table_parallel"], default="unity")
@@ -112,6 +116,13 @@ def main(argv=None) -> int:
     if ignored and rank == 0:
         print(f"note: runtime resource flags {ignored} are not needed here and were ignored", file=sys.stderr)
 
+    device = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if a.iterations is None:
+        a.iterations = 5 if a.graph_json else 20
+    momentum = 0.9 if (a.graph_json and a.optimizer in (None, "sgd")) else 0.0
+    if a.optimizer is None:
+        a.optimizer = "sgd" if a.graph_json else "adam"
+    sync = torch.cuda.synchronize if device == "cuda" else (lambda: None)
     mcfg = json.loads(a.model_config) if a.model_config else {}
     if a.batch_size:
         mcfg["batch_size"] = a.batch_size
@@ -122,7 +133,16 @@ def main(argv=None) -> int:
                        enable_attribute_parallel=a.enable_attribute_parallel, substitution_json_path=a.substitution_json,
                        export_strategy_file=a.export_strategy, import_strategy_file=a.import_strategy, compute_dtype=a.compute_dtype,
                        use_cuda_graph=not a.no_cuda_graph, seed=a.seed)
-    cm = api.compile(a.model, mcfg, config=cfg, optimizer=OptimizerConfig(kind=a.optimizer, lr=a.learning_rate), loss=loss, dist=dist_ctx)
+    model = a.model
+    if a.graph_json:
+        with open(a.graph_json) as f:
+            model = core.Graph.from_v1(f.read())
+        parallel = any(core.is_parallel_op(n["type"]) for n in model.nodes())
+        if parallel and world > 1:
+            cfg.import_strategy_file = a.graph_json  # the file is the strategy
+        loss = "sparse_categorical_crossentropy"
+    cm = api.compile(model, mcfg, config=cfg, optimizer=OptimizerConfig(kind=a.optimizer, lr=a.learning_rate, momentum=momentum),
+                     loss=loss, dist=dist_ctx, device=device)
     ex = cm.executable
     if a.resume and a.checkpoint_dir:
         last = ckpt.latest(a.checkpoint_dir)
@@ -132,10 +152,13 @@ def main(argv=None) -> int:
                 print(f"resumed from {last} at step {meta['step']}")
     inputs, labels = synthetic_batch(cm.graph, ex, loss, seed=1234)
     logger = StepLogger(a.log_file, rank)
-    batch = mcfg.get("batch_size", core.default_model_config(a.model).get("batch_size", 0))
+    if a.graph_json:
+        batch = next((int(n["outputs"][0][1].sizes[0]) for n in cm.graph.nodes() if n["type"] == "INPUT"), 0)
+    else:
+        batch = mcfg.get("batch_size", core.default_model_config(a.model).get("batch_size", 0))
     step = ex.step_count
     for epoch in range(a.epochs):
-        torch.cuda.synchronize()
+        sync()
         t0 = time.perf_counter()
         for it in range(a.iterations):
             want_loss = a.print_freq > 0 and (it % a.print_freq == 0 or it == a.iterations - 1)
@@ -147,12 +170,12 @@ def main(argv=None) -> int:
             if a.checkpoint_dir and a.checkpoint_every and step % a.checkpoint_every == 0:
                 ckpt.save(a.checkpoint_dir, ex, step, rank=rank, world_size=world, strategy=cm.strategy,
                           barrier=(torch.distributed.barrier if world > 1 else None))
-        torch.cuda.synchronize()
+        sync()
         dt = time.perf_counter() - t0
         if rank == 0:
             print(f"epoch {epoch}: {a.iterations} iterations in {dt:.3f} s, {a.iterations * batch / dt:.1f} samples/s "
                   f"(host wall clock, includes H2D copies and loss reads)")
-    if a.profiling and rank == 0:
+    if a.profiling and rank == 0 and device == "cuda":
         prof = ex.profile_step()
         for (typ, phase), ms in sorted(prof["by_type"].items(), key=lambda kv: -kv[1])[:20]:
             print(f"  {typ:24s} {phase:4s} {ms:9.3f} ms")

@@ -40,9 +40,11 @@ def save(directory: str, executable, step: Optional[int] = None, *, rank: int = 
     os.makedirs(path, exist_ok=True)
     sd = {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in executable.state_dict().items()}
     sd["rng_cpu"] = torch.get_rng_state()
-    layout = {name: {"offset": executable.param_offsets[nid][0], "numel": executable.param_offsets[nid][1],
-                     "shape": list(executable.local_weight_shape(nid))}
-              for nid, name in ((n, executable.nodes[n]["name"] or f"weight{n}") for n in executable.param_nodes)}
+    layout = {}
+    if hasattr(executable, "param_nodes"):  # arena executors; the host executor keeps its parameters by name
+        layout = {name: {"offset": executable.param_offsets[nid][0], "numel": executable.param_offsets[nid][1],
+                         "shape": list(executable.local_weight_shape(nid))}
+                  for nid, name in ((n, executable.nodes[n]["name"] or f"weight{n}") for n in executable.param_nodes)}
     sd["layout"] = layout
     fn = os.path.join(path, f"rank{rank}.pt")
     tmp = fn + ".tmp"
@@ -95,7 +97,9 @@ def load(path: str, executable, *, rank: int = 0, verify: bool = True) -> dict:
         sd = torch.load(fn, map_location="cpu", weights_only=False)
     except Exception as e:
         raise CheckpointError(f"{fn} cannot be read: {e}") from e
-    if sd["master"].numel() != executable.master.numel():
+    if ("master" in sd) != hasattr(executable, "master"):
+        raise CheckpointError("the checkpoint was written by another kind of executor (arena / host); use load_resharded")
+    if "master" in sd and sd["master"].numel() != executable.master.numel():
         raise CheckpointError("parameter arena size differs: the checkpoint belongs to another model or strategy "
                               "(use load_resharded to change the strategy)")
     executable.load_state_dict(sd)
@@ -108,6 +112,8 @@ def gather_full_parameters(path: str) -> Dict[str, torch.Tensor]:
     """All parameters of a single-rank (or replicated) checkpoint by name, as fp32 tensors."""
     sd = torch.load(os.path.join(path, "rank0.pt"), map_location="cpu", weights_only=False)
     out = {}
+    if "params" in sd:  # written by the host executor: parameters by name
+        return {k: v.to(torch.float32) for k, v in sd["params"].items()}
     for name, l in sd["layout"].items():
         out[name] = sd["master"][l["offset"]:l["offset"] + l["numel"]].view(l["shape"]).clone()
     # sparsely updated embedding tables are stored whole, under "table.<name>", by the rank that owns them

@@ -91,3 +91,36 @@ def test_run_model_parses_reference_flags():
         with redirect_stdout(buf):
             run_model.main(["--help"])
     assert True
+
+
+def test_run_model_trains_a_graph_file_on_the_host(tmp_path, capsys):
+    """run-model <graph.json>: the reference's usage (a serialized graph, 5 iterations of SGD with momentum 0.9), here
+    on the host executor so that it runs without a GPU."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.bin import run_model
+
+    path = tmp_path / "mlp.json"
+    path.write_text(core.build_model("mlp", {"batch_size": 16}).to_v1_string())
+    assert run_model.main([str(path), "--device", "cpu", "-p", "1"]) == 0
+    out = capsys.readouterr().out
+    losses = [float(l.rsplit("loss", 1)[1]) for l in out.splitlines() if "loss" in l and l.startswith("epoch 0 iter")]
+    assert len(losses) == 5 and losses[-1] < losses[0], out
+    assert "5 iterations" in out
+
+
+def test_run_model_checkpoints_and_resumes_on_the_host(tmp_path, capsys):
+    from flexflow_train_b200.bin import run_model
+    from flexflow_train_b200.utils import checkpoint as ckpt
+
+    cfg = '{"num_features": 32, "sequence_length": 16, "batch_size": 4, "dim_feedforward": 64, "num_heads": 2, ' \
+          '"num_encoder_layers": 1, "num_decoder_layers": 1, "vocab_size": 32}'
+    base = ["--model", "transformer", "--model-config", cfg, "-p", "1", "--checkpoint-dir", str(tmp_path), "--device", "cpu"]
+    assert run_model.main(base + ["--iterations", "4", "--checkpoint-every", "2"]) == 0
+    first = capsys.readouterr().out
+    assert ckpt.latest(str(tmp_path)).endswith("step00000004")
+    assert run_model.main(base + ["--iterations", "2", "--resume"]) == 0
+    second = capsys.readouterr().out
+    assert "resumed from" in second and "at step 4" in second
+    last_before = float([l for l in first.splitlines() if "iter 3" in l][0].rsplit("loss", 1)[1])
+    first_after = float([l for l in second.splitlines() if "iter 0" in l][0].rsplit("loss", 1)[1])
+    assert first_after < last_before    # training went on from the restored weights, not from a fresh initialisation
