@@ -124,3 +124,28 @@ def test_run_model_checkpoints_and_resumes_on_the_host(tmp_path, capsys):
     last_before = float([l for l in first.splitlines() if "iter 3" in l][0].rsplit("loss", 1)[1])
     first_after = float([l for l in second.splitlines() if "iter 0" in l][0].rsplit("loss", 1)[1])
     assert first_after < last_before    # training went on from the restored weights, not from a fresh initialisation
+
+
+def test_bench_contract_pieces_that_need_no_gpu():
+    """`bench.py --impl reference` prints the one-line unavailable record and exits 0; the clock sampler degrades to a
+    record with no samples when neither NVML nor nvidia-smi can be read."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    rec = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and "unavailable" in rec and len(rec["unavailable"]) > 20
+    sys.path.insert(0, root)
+    try:
+        import bench
+    finally:
+        sys.path.pop(0)
+    assert set(bench.MODEL_CONFIGS) == set(bench.TRAINING) == set(bench.L2_NOTE)
+    s = bench.ClockSampler(0)
+    s.start()
+    out = s.stop()
+    assert "sm_mhz" in out and "reasons" in out
