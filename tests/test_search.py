@@ -265,3 +265,41 @@ def test_hybrid_data_x_tensor_parallel_strategy_is_clean_and_scored():
     assert set(hy) == {"dp4xtp2", "dp2xtp4"} and all(v > 0 for v in hy.values())
     assert "x" not in r["stats"]["seed_strategy"]
     assert "hybrid_candidates_not_executable" not in S.optimize(cg, world=8)["stats"]
+
+
+def test_every_strategy_template_computes_the_function_of_the_computation_graph():
+    """Parallel operators are the identity on the logical tensor, so a strategy evaluated as a plain graph must give
+    the loss and gradients of the computation graph it came from -- bit for bit.  This pins the wiring that the
+    substitutions (including the commute and cancellation rules of the hybrid builder) leave behind."""
+    import torch
+
+    from flexflow_train_b200.runtime.torch_oracle import TorchOracle
+
+    cfg = {"num_features": 64, "sequence_length": 16, "batch_size": 8, "dim_feedforward": 128, "num_heads": 4,
+           "num_decoder_layers": 2, "vocab_size": 64, "dropout": 0.0}
+    cg = c.build_model("transformer_lm", cfg)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (8, 16, 1), dtype=torch.int32)
+    labels = torch.randint(0, 64, (8, 16), dtype=torch.int32)
+    rows0, grads0 = TorchOracle(cg, seed=3).loss_and_grads({"input_ids": ids}, labels)
+    strategies = {"dp4": S.data_parallel_strategy(cg, 4), "tp4": S.tensor_parallel_strategy(cg, 4),
+                  "tp4_replicated": S.tensor_parallel_strategy(cg, 4, sequence_parallel=False),
+                  "dp2xtp4": S.hybrid_strategy(cg, 2, 4), "dp4xtp2": S.hybrid_strategy(cg, 4, 2),
+                  "searched8": S.optimize(cg, world=8, budget=4)["mapped_pcg"]}
+    for name, g in strategies.items():
+        rows, grads = TorchOracle(g, seed=3).loss_and_grads({"input_ids": ids}, labels)
+        assert torch.equal(rows, rows0), name
+        assert set(grads) == set(grads0), name
+        for k in grads0:
+            assert torch.equal(grads[k], grads0[k]), (name, k)
+    dl = {"batch_size": 16, "embedding_dim": 8, "embedding_bag_size": 1, "embedding_size": [50, 30, 20, 10],
+          "dense_arch_layer_sizes": [13, 16, 8], "over_arch_layer_sizes": [24, 16, 1], "arch_interaction_op": "DOT",
+          "final_activation": "SIGMOID", "embedding_data_type": "FLOAT"}
+    dcg = c.build_model("dlrm", dl)
+    ins = {"dense": torch.randn(16, 13)}
+    for i, n in enumerate(dl["embedding_size"]):
+        ins[f"sparse{i}"] = torch.randint(0, n, (16, 1))
+    y = torch.rand(16, 1)
+    a = TorchOracle(dcg, seed=1, loss="mean_squared_error_avg_reduce").loss_and_grads(ins, y)
+    b = TorchOracle(S.table_parallel_strategy(dcg, 4), seed=1, loss="mean_squared_error_avg_reduce").loss_and_grads(ins, y)
+    assert torch.equal(a[0], b[0]) and all(torch.equal(a[1][k], b[1][k]) for k in a[1])
