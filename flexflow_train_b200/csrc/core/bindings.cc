@@ -172,6 +172,15 @@ PYBIND11_MODULE(_ffcore, m) {
   m.def("is_weight_slot", [](const std::string &t, const std::string &s) { return is_weight_slot(optype_from_string(t), slot_from_string(s)); });
   m.def("is_parallel_op", [](const std::string &t) { return is_parallel_op(optype_from_string(t)); });
   m.def("operator_task_space", [](const Graph &g, NodeId n) { return operator_task_space(g.node(n), g); });
+  m.def("operator_full_task_degrees", [](const Graph &g, NodeId n) { return operator_full_task_degrees(g.node(n), g); });
+  m.def("operator_tensor_coord", [](const Graph &g, NodeId n, const std::vector<int> &task, const std::string &slot, bool is_output) {
+    TensorCoord c = operator_tensor_coord(g.node(n), g, task, slot_from_string(slot), is_output);
+    py::dict d;
+    d["shard"] = c.shard;
+    d["sum"] = c.sum_component;
+    d["discard_copy"] = c.discard_copy_component;
+    return d;
+  }, py::arg("graph"), py::arg("node"), py::arg("task"), py::arg("slot") = "OUTPUT", py::arg("is_output") = true);
   m.def("operator_types", []() {
     std::vector<std::string> r;
 #define X(n) r.push_back(#n);

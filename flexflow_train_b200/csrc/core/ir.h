@@ -240,6 +240,9 @@ struct TensorCoord {
 // full (non-minimal) task-space degrees of an operator: one entry per output shard dim,
 // then sum, then discard-copy
 std::vector<int> operator_full_task_degrees(const Node &n, const Graph &g);
+// Implemented for Input, Weight, the element-wise unary and binary operators, Transpose, Linear (the reference's list)
+// and the four parallel operators; other operators throw.
+TensorCoord operator_tensor_coord(const Node &n, const Graph &g, const std::vector<int> &task, Slot slot, bool is_output);
 
 // ---------------------------------------------------------------- v1 file format
 // lib/pcg/include/pcg/file_format/v1/** : {"raw_graph": {"node_labels", "output_labels", "graph"}}

@@ -532,6 +532,119 @@ std::vector<int> operator_full_task_degrees(const Node &n, const Graph &g) {
   d.push_back(s->discard_copy_degree);
   return d;
 }
+// Task coordinate (one entry per full task degree: output shard dims..., sum, discard-copy) -> the shard coordinate of
+// one of the operator's tensors.  The Linear rules follow the degree algebra of its shape inference: the task's sum
+// component enumerates (input sum replica, input-channel shard), the output-channel shard is the input's discard-copy
+// replica, and a weight piece is replicated over (input sum replica, flattened batch shard).
+static bool is_elementwise_unary(OpType t) {
+  switch (t) {
+    case OpType::RELU: case OpType::SIGMOID: case OpType::TANH: case OpType::GELU: case OpType::ELU: case OpType::EXP:
+    case OpType::IDENTITY: case OpType::NOOP: case OpType::RSQRT: case OpType::SIN: case OpType::COS: case OpType::POW:
+    case OpType::SCALAR_MULTIPLY: case OpType::SCALAR_ADD: case OpType::SCALAR_SUB: case OpType::SCALAR_TRUE_DIV:
+    case OpType::DROPOUT: case OpType::CAST:
+      return true;
+    default: return false;
+  }
+}
+static bool is_elementwise_binary(OpType t) {
+  return t == OpType::EW_ADD || t == OpType::EW_SUB || t == OpType::EW_MUL || t == OpType::EW_DIV || t == OpType::EW_MAX ||
+         t == OpType::EW_MIN;
+}
+TensorCoord operator_tensor_coord(const Node &n, const Graph &g, const std::vector<int> &task, Slot slot, bool is_output) {
+  const std::vector<int> full = operator_full_task_degrees(n, g);
+  if (task.size() != full.size()) throw Error("task coordinate has " + std::to_string(task.size()) + " components, the task space " + std::to_string(full.size()));
+  for (size_t i = 0; i < task.size(); ++i)
+    if (task[i] < 0 || task[i] >= full[i]) throw Error("task coordinate outside the task space");
+  const int nd = (int)task.size() - 2;
+  TensorCoord same;
+  same.shard.assign(task.begin(), task.begin() + nd);
+  same.sum_component = task[nd];
+  same.discard_copy_component = task[nd + 1];
+  auto input_shape = [&](Slot s) -> const PShape & {
+    const InEdge *e = n.in(s);
+    if (!e) throw Error("operator has no input in slot " + to_string(s));
+    return g.shape(e->src);
+  };
+  if (n.type == OpType::INPUT || n.type == OpType::WEIGHT) {
+    if (!is_output) throw Error("source operators have no inputs");
+    return same;
+  }
+  if (is_elementwise_unary(n.type)) return same;
+  if (is_elementwise_binary(n.type)) {
+    if (!is_output && input_shape(slot).degrees() != n.outputs.at(0).shape.degrees())
+      throw Error("shard mapping of a broadcasting binary operator");
+    return same;
+  }
+  if (n.type == OpType::TRANSPOSE) {
+    if (is_output) return same;
+    auto perm = n.attrs.at("permutation").as_ints();
+    TensorCoord c = same;
+    for (int i = 0; i < nd; ++i) c.shard[(size_t)perm[i]] = task[i];  // output dim i is input dim perm[i]
+    return c;
+  }
+  if (n.type == OpType::LINEAR) {
+    if (is_output) return same;
+    const PShape &x = input_shape(Slot::INPUT);
+    const int k = x.dims.back().degree;
+    const int kk = task[nd] % k, s = task[nd] / k, o = task[nd - 1];
+    auto xdeg = x.degrees();
+    int flat_batch = 0;
+    for (int i = 0; i < nd - 1; ++i) flat_batch = flat_batch * xdeg[i] + task[i];
+    int others = 1;
+    for (int i = 0; i < nd - 1; ++i) others *= xdeg[i];
+    TensorCoord c;
+    if (slot == Slot::INPUT) {
+      c.shard.assign(task.begin(), task.begin() + nd - 1);
+      c.shard.push_back(kk);
+      c.sum_component = s;
+      c.discard_copy_component = o;
+    } else if (slot == Slot::WEIGHT) {
+      c.shard = {o, kk};
+      c.sum_component = 0;
+      c.discard_copy_component = s * others + flat_batch;
+    } else if (slot == Slot::BIAS) {
+      // the bias is either a partial-sum tensor (one term per task sum component, as the degree algebra has it) or,
+      // as the generated rules feed it, replicated to every task; either way only sum component 0 may add it
+      const PShape &bs = input_shape(Slot::BIAS);
+      c.shard = {o};
+      if (bs.sum_degree > 1) {
+        c.sum_component = task[nd] % bs.sum_degree;
+        c.discard_copy_component = flat_batch % bs.discard_copy_degree;
+      } else {
+        c.sum_component = 0;
+        c.discard_copy_component = (task[nd] * others + flat_batch) % bs.discard_copy_degree;
+      }
+    } else {
+      throw Error("linear has no slot " + to_string(slot));
+    }
+    return c;
+  }
+  // parallel operators: the task grid is the more parallel side (see operator_full_task_degrees)
+  if (n.type == OpType::REPARTITION || n.type == OpType::COMBINE) {
+    const bool rep = n.type == OpType::REPARTITION;
+    const PShape &ref = rep ? n.outputs.at(0).shape : input_shape(Slot::INPUT);
+    const int dim = ref.norm_dim((int)n.attrs.at(rep ? "repartition_dim" : "combine_dim").as_int());
+    const int k = (int)n.attrs.at(rep ? "repartition_degree" : "combine_degree").as_int();
+    if (is_output == rep) return same;        // the side the task grid was taken from
+    TensorCoord c = same;
+    c.shard[(size_t)dim] = task[dim] / k;     // k consecutive fine shards make one coarse shard
+    return c;
+  }
+  if (n.type == OpType::REPLICATE) {
+    if (is_output) return same;
+    TensorCoord c = same;
+    c.discard_copy_component = task[nd + 1] / (int)n.attrs.at("replicate_degree").as_int();
+    return c;
+  }
+  if (n.type == OpType::REDUCTION) {
+    if (!is_output) return same;
+    TensorCoord c = same;
+    c.sum_component = task[nd] / (int)n.attrs.at("reduction_degree").as_int();
+    return c;
+  }
+  throw Error("no operator-to-tensor shard mapping for " + to_string(n.type));
+}
+
 std::vector<int> operator_task_space(const Node &n, const Graph &g) {
   std::vector<int> r;
   for (int d : operator_full_task_degrees(n, g)) if (d > 1) r.push_back(d);
