@@ -224,6 +224,67 @@ std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task
   return devs;
 }
 
+// ---------------------------------------------------------------- tensor set movement
+// Which pieces travel between which devices when `src` (placed by view `vs`) feeds `dst` (placed by `vd`): for every
+// task of the consumer, the shard of the tensor it reads (operator_tensor_coord) is looked up among the producer's
+// tasks; a piece whose producing and consuming tasks sit on different devices is one communication edge
+// (compiler/machine_mapping/abstracted_tensor_set_movement -> TensorSetMovement{CommunicationEdge -> bytes}).
+static int flat_minimal_task(const std::vector<int> &full, const std::vector<int> &task) {
+  int f = 0;
+  for (size_t i = 0; i < full.size(); ++i)
+    if (full[i] > 1) f = f * full[i] + task[i];
+  return f;
+}
+static void for_each_task(const std::vector<int> &full, const std::function<void(const std::vector<int> &)> &fn) {
+  std::vector<int> t(full.size(), 0);
+  while (true) {
+    fn(t);
+    int i = (int)full.size() - 1;
+    while (i >= 0 && ++t[i] == full[i]) t[i--] = 0;
+    if (i < 0) return;
+  }
+}
+std::vector<CommunicationEdge> get_tensor_set_movement(const Graph &g, NodeId src, const MachineView &vs, NodeId dst, const MachineView &vd,
+                                                       const MachineSpec &m) {
+  const Node &p = g.node(src), &c = g.node(dst);
+  const std::vector<int> fp = operator_full_task_degrees(p, g), fc = operator_full_task_degrees(c, g);
+  const std::vector<int> dp = view_devices(vs, operator_task_space(p, g), m), dc = view_devices(vd, operator_task_space(c, g), m);
+  std::vector<CommunicationEdge> out;
+  std::set<std::tuple<int, int, std::vector<int>>> seen;
+  for (auto &e : c.inputs) {
+    if (e.src.node != src) continue;
+    using Key = std::vector<int>;  // shard..., sum, copy
+    auto key_of = [](const TensorCoord &tc) {
+      Key k = tc.shard;
+      k.push_back(tc.sum_component);
+      k.push_back(tc.discard_copy_component);
+      return k;
+    };
+    std::map<Key, int> producer_device;
+    for_each_task(fp, [&](const std::vector<int> &t) {
+      producer_device[key_of(operator_tensor_coord(p, g, t, e.src.slot, true))] = dp.at((size_t)flat_minimal_task(fp, t));
+    });
+    const double bytes = (double)g.shape(e.src).piece_bytes();
+    for_each_task(fc, [&](const std::vector<int> &t) {
+      Key k = key_of(operator_tensor_coord(c, g, t, e.dst_slot, false));
+      auto it = producer_device.find(k);
+      if (it == producer_device.end()) throw Error("tensor set movement: the consumer reads a piece its producer does not make");
+      const int to = dc.at((size_t)flat_minimal_task(fc, t));
+      if (it->second != to && seen.insert({it->second, to, k}).second) out.push_back({it->second, to, bytes});
+    });
+  }
+  return out;
+}
+// max over the point-to-point edges of bytes / bandwidth (lib/local-execution/.../local_cost_estimator.cc:155-179)
+double tensor_set_movement_cost_ms(const std::vector<CommunicationEdge> &edges, const MachineSpec &m, const CostEstimator &est) {
+  double worst = 0;
+  for (auto &e : edges) {
+    const bool inter = e.src_device / m.num_gpus_per_node != e.dst_device / m.num_gpus_per_node;
+    worst = std::max(worst, est.movement_cost_ms(e.bytes, inter));
+  }
+  return worst;
+}
+
 // ---------------------------------------------------------------- SP decomposition of a graph
 static DiGraph graph_digraph(const Graph &g) {
   DiGraph d;
@@ -726,6 +787,22 @@ void bind_search(py::module &m) {
     py::list l;
     for (auto &v : allowed_machine_views(task, Resources{start, count}, ms)) l.append(json_to_py(v.to_json()));
     return l;
+  });
+  m.def("get_tensor_set_movement", [](const Graph &g, NodeId src, py::object vs, NodeId dst, py::object vd, const MachineSpec &ms) {
+    py::list out;
+    for (auto &e : get_tensor_set_movement(g, src, MachineView::from_json(json_from_py(vs)), dst, MachineView::from_json(json_from_py(vd)), ms)) {
+      py::dict d;
+      d["src"] = e.src_device;
+      d["dst"] = e.dst_device;
+      d["bytes"] = e.bytes;
+      out.append(d);
+    }
+    return out;
+  });
+  m.def("tensor_set_movement_cost_ms", [](const Graph &g, NodeId src, py::object vs, NodeId dst, py::object vd, const MachineSpec &ms,
+                                          const CostEstimator &est) {
+    return tensor_set_movement_cost_ms(get_tensor_set_movement(g, src, MachineView::from_json(json_from_py(vs)), dst,
+                                                               MachineView::from_json(json_from_py(vd)), ms), ms, est);
   });
   m.def("view_devices", [](py::object view, std::vector<int> task, const MachineSpec &ms) {
     return view_devices(MachineView::from_json(json_from_py(view)), task, ms);

@@ -66,6 +66,14 @@ struct Resources {
 };
 std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m);
 std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task_degrees, const MachineSpec &m);
+// one tensor piece that has to travel between two devices
+struct CommunicationEdge {
+  int src_device, dst_device;
+  double bytes;
+};
+std::vector<CommunicationEdge> get_tensor_set_movement(const Graph &g, NodeId src, const MachineView &vs, NodeId dst, const MachineView &vd,
+                                                       const MachineSpec &m);
+double tensor_set_movement_cost_ms(const std::vector<CommunicationEdge> &edges, const MachineSpec &m, const CostEstimator &est);
 
 struct MappingPoint {
   double runtime_ms = 0;

@@ -129,3 +129,34 @@ def test_elementwise_transpose_and_parallel_operator_mappings():
         core.operator_tensor_coord(pg, tnode, [1, 0, 0, 0, 0], "INPUT", False)      # outside the (all-ones) task space
     with pytest.raises(core.CoreError):
         core.operator_tensor_coord(g, _first(g, "SOFTMAX"), [0] * len(core.operator_full_task_degrees(g, _first(g, "SOFTMAX"))), "INPUT", False)
+
+
+def test_tensor_set_movement_lists_the_pieces_that_change_device():
+    """Producer and consumer on the same view: nothing moves.  The consumer's view shifted to other devices: every
+    piece travels once, from the device that made it to the device that reads it."""
+    cg = core.build_model("mlp", {"batch_size": 8})
+    ms = core.MachineSpecification(1, 8)
+    est = core.CostEstimator(ms)
+    g = S.data_parallel_strategy(cg, 4)
+    rep = _first(g, "REPARTITION", lambda n: g.node(tuple(n["inputs"][0][1])[0])["type"] == "INPUT")
+    lin = g.consumers((rep, "OUTPUT"))[0][0]
+    assert g.node(lin)["type"] == "LINEAR"
+    lo, hi = core.allowed_machine_views([4], 0, 8, ms)            # devices 0-3 and 4-7
+    assert core.get_tensor_set_movement(g, rep, lo, lin, lo, ms) == []
+    edges = core.get_tensor_set_movement(g, rep, lo, lin, hi, ms)
+    piece = g.shape((rep, "OUTPUT")).piece_bytes
+    assert sorted((e["src"], e["dst"]) for e in edges) == [(0, 4), (1, 5), (2, 6), (3, 7)]
+    assert all(e["bytes"] == piece for e in edges)
+    assert core.tensor_set_movement_cost_ms(g, rep, lo, lin, hi, ms, est) == pytest.approx(est.movement_cost_ms(piece, False))
+    assert core.tensor_set_movement_cost_ms(g, rep, lo, lin, lo, ms, est) == 0.0
+    # column-parallel Linear: replica c of the input feeds the task that computes output-channel shard c
+    rules = core.get_substitution_set(ms)
+    r = {x.name: x for x in rules}["replicate_linear_combine_4_bias"]
+    pcg = core.pcg_from_computation_graph(cg)
+    tp = core.apply_substitution(pcg, r, core.find_pattern_matches(r, pcg)[0])
+    lin2 = _first(tp, "LINEAR", lambda n: n["outputs"][0][1].total_degree == 4)
+    src = dict((s, tuple(v)) for s, v in tp.node(lin2)["inputs"])["INPUT"]
+    assert tp.node(src[0])["type"] == "REPLICATE"
+    assert core.get_tensor_set_movement(tp, src[0], lo, lin2, lo, ms) == []
+    moved = core.get_tensor_set_movement(tp, src[0], lo, lin2, hi, ms)
+    assert sorted((e["src"], e["dst"]) for e in moved) == [(0, 4), (1, 5), (2, 6), (3, 7)]
