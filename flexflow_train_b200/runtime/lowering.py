@@ -24,5 +24,7 @@ def lower(graph, machine=None, *, logit=None, loss: str = "sparse_categorical_cr
         logit = sinks[-1] if sinks else None
     inv = core.lower_training_graph(graph, machine, logit, {"type": loss}, optimizer or {"type": "sgd"}, distributed)
     if device is not None:
+        if not distributed:  # a single-device lowering is not shard-expanded: all of it belongs to device 0
+            return inv if device == 0 else []
         inv = core.perform_machine_slicing(inv, device)
     return inv
