@@ -542,6 +542,8 @@ static bool is_elementwise_unary(OpType t) {
     case OpType::IDENTITY: case OpType::NOOP: case OpType::RSQRT: case OpType::SIN: case OpType::COS: case OpType::POW:
     case OpType::SCALAR_MULTIPLY: case OpType::SCALAR_ADD: case OpType::SCALAR_SUB: case OpType::SCALAR_TRUE_DIV:
     case OpType::DROPOUT: case OpType::CAST:
+    // row-wise operators whose normalised dim is unsharded (their shape inference requires that) map like element-wise ones
+    case OpType::SOFTMAX: case OpType::LAYERNORM:
       return true;
     default: return false;
   }

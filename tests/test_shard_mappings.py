@@ -127,8 +127,9 @@ def test_elementwise_transpose_and_parallel_operator_mappings():
     assert core.operator_tensor_coord(pg, tnode, [0, 0, 0, 0, 0], "INPUT", False)["shard"] == [0, 0, 0]
     with pytest.raises(core.CoreError):
         core.operator_tensor_coord(pg, tnode, [1, 0, 0, 0, 0], "INPUT", False)      # outside the (all-ones) task space
-    with pytest.raises(core.CoreError):
-        core.operator_tensor_coord(g, _first(g, "SOFTMAX"), [0] * len(core.operator_full_task_degrees(g, _first(g, "SOFTMAX"))), "INPUT", False)
+    att = _first(g, "MULTIHEAD_ATTENTION")
+    with pytest.raises(core.CoreError):   # no mapping for attention (nor in the reference)
+        core.operator_tensor_coord(g, att, [0] * len(core.operator_full_task_degrees(g, att)), "QUERY", False)
 
 
 def test_tensor_set_movement_lists_the_pieces_that_change_device():
@@ -160,3 +161,32 @@ def test_tensor_set_movement_lists_the_pieces_that_change_device():
     assert core.get_tensor_set_movement(tp, src[0], lo, lin2, lo, ms) == []
     moved = core.get_tensor_set_movement(tp, src[0], lo, lin2, hi, ms)
     assert sorted((e["src"], e["dst"]) for e in moved) == [(0, 4), (1, 5), (2, 6), (3, 7)]
+
+
+def test_strategies_evaluated_shard_by_shard_give_the_unsharded_result():
+    """The PCG executed the way its degrees say (pieces cut by Repartition, copied by Replicate, added by Reduction,
+    concatenated by Combine; one Linear product per task) reproduces the computation graph's output."""
+    from flexflow_train_b200.runtime.spmd_sim import ShardedEvaluation
+    from flexflow_train_b200.runtime.torch_oracle import TorchOracle
+
+    cg = core.build_model("mlp", {"batch_size": 8})
+    oracle = TorchOracle(cg, seed=5)
+    params = {k: v.detach().double() for k, v in oracle.params.items()}
+    torch.manual_seed(0)
+    inputs = {n["name"]: torch.randn([int(v) for v in n["outputs"][0][1].sizes], dtype=torch.float64)
+              for n in cg.nodes() if n["type"] == "INPUT"}
+    ref = ShardedEvaluation(core.pcg_from_computation_graph(cg), params, inputs)
+    sink = tuple(cg.sink_values()[-1])
+    want = ref.assemble(sink)
+    assert torch.allclose(want.float(), oracle.forward({k: v.float() for k, v in inputs.items()}).detach(), atol=1e-5)
+    rules = core.get_substitution_set(core.MachineSpecification(1, 8))
+    strategies = {"dp4": S.data_parallel_strategy(cg, 4, rules), "tp4": S.tensor_parallel_strategy(cg, 4, rules),
+                  "tp4_replicated": S.tensor_parallel_strategy(cg, 4, rules, sequence_parallel=False),
+                  "dp2xtp4": S.hybrid_strategy(cg, 2, 4, rules)}
+    for name, g in strategies.items():
+        ev = ShardedEvaluation(g, params, inputs)
+        out_value = tuple(g.sink_values()[-1])
+        got = ev.assemble(out_value)
+        assert torch.allclose(got, want, atol=1e-9), (name, float((got - want).abs().max()))
+        # the strategy really ran sharded: some Linear was computed in more than one task
+        assert any(len(p) > 1 for (nid, _), p in ev.pieces.items() if ev.nodes[nid]["type"] == "LINEAR"), name
