@@ -63,7 +63,26 @@ def synthetic_batch(graph, executable, loss: str, seed: int = 0, pinned: bool = 
     return inputs, (labels.pin_memory() if pinned and torch.cuda.is_available() else labels)
 
 
+def split_runtime_flags(argv):
+    """Separates the Legion/Realm resource flags (``-ll:gpu 1``, ``-lg:prof 2`` ...) and their values from the rest
+    of the command line, so that a flag's value can never be taken for a positional argument."""
+    rest, ignored = [], []
+    i = 0
+    while i < len(argv):
+        tok = argv[i]
+        if tok.startswith("-ll:") or tok.startswith("-lg:"):
+            ignored.append(tok)
+            if "=" not in tok and i + 1 < len(argv) and not argv[i + 1].startswith("-"):
+                ignored.append(argv[i + 1])
+                i += 1
+        else:
+            rest.append(tok)
+        i += 1
+    return rest, ignored
+
+
 def main(argv=None) -> int:
+    argv, ignored = split_runtime_flags(list(sys.argv[1:] if argv is None else argv))
     p = argparse.ArgumentParser(prog="run-model", description=__doc__.split("\n")[0])
     p.add_argument("graph_json", nargs="?", help="a v1 JSON file (computation graph, parallel or mapped parallel computation graph) to "
                    "train instead of a model-zoo model: as the reference's run-model, 5 iterations of SGD(0.001, momentum 0.9) "
@@ -95,11 +114,7 @@ def main(argv=None) -> int:
     p.add_argument("--resume", action="store_true")
     p.add_argument("--log-file")
     p.add_argument("--seed", type=int, default=0)
-    a, extra = p.parse_known_args(argv)
-    ignored = [x for x in extra if x.startswith("-ll:") or x.startswith("-lg:")]
-    unknown = [x for x in extra if x not in ignored and not x.lstrip("-").isdigit()]
-    if unknown and not ignored:
-        p.error(f"unrecognised arguments: {unknown}")
+    a = p.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -175,7 +190,9 @@ def main(argv=None) -> int:
         if rank == 0:
             print(f"epoch {epoch}: {a.iterations} iterations in {dt:.3f} s, {a.iterations * batch / dt:.1f} samples/s "
                   f"(host wall clock, includes H2D copies and loss reads)")
-    if a.profiling and rank == 0 and device == "cuda":
+    if a.profiling and world > 1 and rank == 0:
+        print("note: --profiling times one rank's operators in isolation and is skipped with more than one rank", file=sys.stderr)
+    if a.profiling and world == 1 and device == "cuda":
         prof = ex.profile_step()
         for (typ, phase), ms in sorted(prof["by_type"].items(), key=lambda kv: -kv[1])[:20]:
             print(f"  {typ:24s} {phase:4s} {ms:9.3f} ms")

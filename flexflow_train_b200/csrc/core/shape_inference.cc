@@ -92,8 +92,13 @@ Json default_initializer(OpType type, Slot s, const Json &attrs, const SlotShape
     else fan_in = (double)in.dims.at(1).size / attrs.get_int("groups", 1) * attrs.at("kernel_h").as_int() * attrs.at("kernel_w").as_int();
     double bound = 1.0 / std::sqrt(fan_in);
     if (s == Slot::BIAS) return uniform(-bound, bound);
-    // kaiming uniform with a = sqrt(5) has the same bound 1/sqrt(fan_in)
-    return uniform(-bound, bound);
+    // the projection: KaimingNormalAttrs{a = sqrt(5), FAN_IN, LEAKY_RELU, seed 0} (linear.cc:253-259)
+    Json v = Json::object();
+    v["a"] = (double)std::sqrt(5.0f);
+    v["mode"] = "FAN_IN";
+    v["nonlinearity"] = "LEAKY_RELU";
+    v["seed"] = 0;
+    return init_obj("kaiming_normal", v);
   }
   if (type == OpType::EMBEDDING) {
     Json v = Json::object();

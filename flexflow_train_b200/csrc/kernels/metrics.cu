@@ -5,13 +5,16 @@
 // accumulator when it wants the numbers).  Counterpart of update_metrics_sparse_label_kernel /
 // update_metrics_label_kernel (lib/kernels/src/cuda/metrics_functions.cu:48-98), which add into a CUDAPerfMetrics
 // struct with global atomics, one thread per sample; here one warp reads a sample's row coalesced and a block adds
-// its partial sums with one atomic per metric.
+// its partial sums with one atomic per metric.  The definitions are the reference's: squared and absolute errors are
+// summed over a sample's classes (not averaged), sparse labels are compared as one-hot targets, and probabilities
+// are clamped at 1e-8 before the logarithm.
 #include "common.cuh"
 
 namespace {
 
 // accumulator slots (doubles)
 enum { M_ALL = 0, M_CORRECT, M_CCE, M_SCCE, M_MSE, M_RMSE, M_MAE, M_SLOTS };
+constexpr float LOG_MIN_VALUE = 1e-8f;
 // request bits
 enum { F_ACCURACY = 1, F_CCE = 2, F_SCCE = 4, F_MSE = 8, F_RMSE = 16, F_MAE = 32 };
 
@@ -35,17 +38,22 @@ __global__ void metrics_kernel(const T *__restrict__ pred, const void *__restric
     int besti = 0x7fffffff;
     float cce = 0.f, se = 0.f, ae = 0.f, tbest = -INFINITY;
     int tbesti = 0x7fffffff;
+    long long sparse_t = -1;
+    if (!label_d) sparse_t = label64 ? ((const long long *)label_i)[row] : (long long)((const int *)label_i)[row];
     for (int j = lane; j < c; j += 32) {
       const float v = ldm<T>(p, j);
       if (v > best) { best = v; besti = j; }
+      float t;
       if (label_d) {
-        const float t = ldm<T>(label_d, row * c + j);
+        t = ldm<T>(label_d, row * c + j);
         if (t > tbest) { tbest = t; tbesti = j; }
-        cce -= t * logf(fmaxf(v, 1e-30f));
-        const float d = v - t;
-        se += d * d;
-        ae += fabsf(d);
+        cce -= t * logf(fmaxf(v, LOG_MIN_VALUE));
+      } else {
+        t = (long long)j == sparse_t ? 1.f : 0.f;
       }
+      const float d = v - t;
+      se += d * d;
+      ae += fabsf(d);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -64,14 +72,14 @@ __global__ void metrics_kernel(const T *__restrict__ pred, const void *__restric
       if (label_d) {
         if (flags & F_ACCURACY) sums[M_CORRECT] += besti == tbesti ? 1.f : 0.f;
         if (flags & F_CCE) sums[M_CCE] += cce;
-        if (flags & F_MSE) sums[M_MSE] += se / c;
-        if (flags & F_RMSE) sums[M_RMSE] += sqrtf(se / c);
-        if (flags & F_MAE) sums[M_MAE] += ae / c;
       } else {
-        const long long t = label64 ? ((const long long *)label_i)[row] : (long long)((const int *)label_i)[row];
+        const long long t = sparse_t;
         if (flags & F_ACCURACY) sums[M_CORRECT] += (long long)besti == t ? 1.f : 0.f;
-        if ((flags & F_SCCE) && t >= 0 && t < c) sums[M_SCCE] -= logf(fmaxf(ldm<T>(p, t), 1e-30f));
+        if ((flags & F_SCCE) && t >= 0 && t < c) sums[M_SCCE] -= logf(fmaxf(ldm<T>(p, t), LOG_MIN_VALUE));
       }
+      if (flags & F_MSE) sums[M_MSE] += se;
+      if (flags & F_RMSE) sums[M_RMSE] += sqrtf(se);
+      if (flags & F_MAE) sums[M_MAE] += ae;
     }
   }
   if (lane == 0 && wid < 8) {

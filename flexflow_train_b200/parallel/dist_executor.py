@@ -689,6 +689,12 @@ class DistExecutable(Executable):
         self.consolidate_state()
         return super().state_dict()
 
+    def named_parameters(self):
+        """fp32 master weights by name.  A collective when the update is sharded (every rank must call it): the
+        slices other ranks own are gathered first."""
+        self.consolidate_state()
+        return super().named_parameters()
+
     def sync_gradients(self):
         if self.side is not None and self._pending:
             torch.cuda.current_stream().wait_stream(self.side)

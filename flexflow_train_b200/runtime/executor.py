@@ -1520,12 +1520,20 @@ class Executable:
             if getattr(op, "has_grad", False):
                 op.backward()
 
-    def profile_step(self):
-        """Run one eager step with CUDA events around every operator's forward and backward.
+    def profile_step(self, update: bool = False):
+        """Run one eager forward + backward with CUDA events around every operator's forward and backward.
 
         Returns ``{"by_type": {(op type, phase): ms}, "by_node": {(node id, phase): ms}, "total_ms": ms}``.
         This is the per-layer timing the reference collects through its ``profile(...)`` wrapper
-        (lib/task-spec/include/task-spec/profiling.h:11-24) and the source of measured operator costs."""
+        (lib/task-spec/include/task-spec/profiling.h:11-24) and the source of measured operator costs.
+
+        Profiling is an observation: weights, optimizer state and the step counter are left as they were unless
+        `update=True` asks for the optimizer step to be run (and timed) as well.  Activations and gradient
+        buffers are overwritten, as by any step.  A multi-rank executable refuses: its gradient reduction and
+        fused collectives need every rank inside the same step."""
+        if self.dist is not None and self.dist.world_size > 1:
+            raise RuntimeError("profile_step() runs one rank's operators in isolation; with more than one rank the "
+                               "collectives inside the step would wait for peers that are not in it")
         self._pre_step()
         recs = []
 
@@ -1545,8 +1553,9 @@ class Executable:
             op = self.ops[nid]
             if getattr(op, "has_grad", False):
                 timed((nid, "bwd"), op.backward)
-        timed((-2, "sync_gradients"), self.sync_gradients)
-        timed((-3, "update"), self.update)
+        if update:
+            timed((-2, "sync_gradients"), self.sync_gradients)
+            timed((-3, "update"), self.update)
         t1.record()
         torch.cuda.synchronize()
         by_type, by_node = {}, {}

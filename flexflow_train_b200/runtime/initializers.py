@@ -64,9 +64,10 @@ def initialize(shape: Sequence[int], init: dict | None, *, base_seed: int = 0, o
         out.normal_(0.0, math.sqrt(2.0 / (fan_in + fan_out)), generator=gen)
     elif kind == "kaiming_normal":
         fan_in, fan_out = _fans(shape)
-        fan = fan_out if v.get("mode", "fan_in") == "fan_out" else fan_in
+        fan = fan_out if str(v.get("mode", "fan_in")).lower() == "fan_out" else fan_in
         a = float(v.get("a", 0.0))
-        gain = math.sqrt(2.0 / (1 + a * a)) if v.get("nonlinearity", "leaky_relu") in ("relu", "leaky_relu") else 1.0
+        nl = str(v.get("nonlinearity", "leaky_relu")).lower()
+        gain = math.sqrt(2.0) if nl == "relu" else (math.sqrt(2.0 / (1 + a * a)) if nl == "leaky_relu" else 1.0)
         out.normal_(0.0, gain / math.sqrt(max(fan, 1)), generator=gen)
     else:
         raise ValueError(f"unknown initializer kind {kind!r}")

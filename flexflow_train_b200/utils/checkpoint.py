@@ -35,6 +35,9 @@ def _sha(path: str) -> str:
 
 def save(directory: str, executable, step: Optional[int] = None, *, rank: int = 0, world_size: int = 1, strategy=None,
          barrier=None, extra: Optional[dict] = None) -> str:
+    if world_size > 1 and barrier is None:
+        # without a barrier rank 0 could write the metadata (and its checksum list) before the other ranks' files exist
+        raise CheckpointError("save() with world_size > 1 needs a barrier callable (e.g. torch.distributed.barrier)")
     step = executable.step_count if step is None else step
     path = os.path.join(directory, f"step{step:08d}")
     os.makedirs(path, exist_ok=True)
@@ -91,7 +94,9 @@ def load(path: str, executable, *, rank: int = 0, verify: bool = True) -> dict:
         raise CheckpointError(f"{fn} is missing: the checkpoint was written by {meta['world_size']} ranks")
     if verify:
         want = meta["files"].get(os.path.basename(fn))
-        if want is not None and _sha(fn) != want:
+        if want is None:
+            raise CheckpointError(f"{fn} has no recorded checksum in meta.json (written after the metadata?)")
+        if _sha(fn) != want:
             raise CheckpointError(f"{fn} does not match its recorded checksum (corrupt file)")
     try:
         sd = torch.load(fn, map_location="cpu", weights_only=False)

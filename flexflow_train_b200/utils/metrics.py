@@ -95,20 +95,24 @@ class PerfMetrics:
         if "accuracy" in metrics:
             tgt = label.reshape(-1).long() if sparse else label.reshape(n, -1).argmax(1)
             self.train_correct += int((p.argmax(1).to(tgt.device) == tgt).sum().item())
+        # the reference's definitions: probabilities clamped at 1e-8 before the logarithm, squared / absolute errors
+        # summed over a sample's classes, sparse labels compared as one-hot targets
         if sparse and "sparse_categorical_crossentropy" in metrics:
             tgt = label.reshape(-1).long().to(p.device)
-            self.sparse_cce_loss += float(-torch.log(p.gather(1, tgt[:, None]).clamp_min(1e-30)).sum().item())
-        if not sparse:
+            self.sparse_cce_loss += float(-torch.log(p.gather(1, tgt[:, None]).clamp_min(1e-8)).sum().item())
+        if sparse:
+            t = torch.nn.functional.one_hot(label.reshape(-1).long().to(p.device), p.shape[1]).float()
+        else:
             t = label.reshape(n, -1).float().to(p.device)
             if "categorical_crossentropy" in metrics:
-                self.cce_loss += float(-(t * torch.log(p.clamp_min(1e-30))).sum().item())
-            d = p - t
-            if "mean_squared_error" in metrics:
-                self.mse_loss += float((d * d).mean(1).sum().item())
-            if "root_mean_squared_error" in metrics:
-                self.rmse_loss += float((d * d).mean(1).sqrt().sum().item())
-            if "mean_absolute_error" in metrics:
-                self.mae_loss += float(d.abs().mean(1).sum().item())
+                self.cce_loss += float(-(t * torch.log(p.clamp_min(1e-8))).sum().item())
+        d = p - t
+        if "mean_squared_error" in metrics:
+            self.mse_loss += float((d * d).sum(1).sum().item())
+        if "root_mean_squared_error" in metrics:
+            self.rmse_loss += float((d * d).sum(1).sqrt().sum().item())
+        if "mean_absolute_error" in metrics:
+            self.mae_loss += float(d.abs().sum(1).sum().item())
         self.current_time = time.time()
         return self
 

@@ -126,6 +126,23 @@ def test_run_model_checkpoints_and_resumes_on_the_host(tmp_path, capsys):
     assert first_after < last_before    # training went on from the restored weights, not from a fresh initialisation
 
 
+def test_run_model_ignores_runtime_resource_flags_and_their_values(tmp_path, capsys):
+    """`-ll:gpu 1 -ll:fsize 14000` (the reference's resource flags) must not leak their values into the positional
+    graph-file argument, in either position relative to the other flags."""
+    from flexflow_train_b200.bin import run_model
+
+    assert run_model.split_runtime_flags(["-ll:gpu", "1", "--model", "mlp", "-lg:prof=2", "-ll:fsize", "14000", "-b", "8"]) == (
+        ["--model", "mlp", "-b", "8"], ["-ll:gpu", "1", "-lg:prof=2", "-ll:fsize", "14000"])
+    cfg = '{"batch_size": 8}'
+    args = ["--model", "mlp", "--model-config", cfg, "--iterations", "3", "-p", "1", "--device", "cpu", "-ll:gpu", "1", "-ll:fsize", "14000"]
+    assert run_model.main(args) == 0
+    assert run_model.main(["-ll:gpu", "1"] + args[:-4]) == 0
+    out = capsys.readouterr()
+    assert out.out.count("iter 2: loss") == 2 and "were ignored" in out.err
+    with pytest.raises(SystemExit):  # an unknown flag is still an error
+        run_model.main(args + ["--no-such-flag"])
+
+
 def test_bench_contract_pieces_that_need_no_gpu():
     """`bench.py --impl reference` prints the one-line unavailable record and exits 0; the clock sampler degrades to a
     record with no samples when neither NVML nor nvidia-smi can be read."""

@@ -54,6 +54,21 @@ def test_mlp_loss_decreases():
     assert losses[-1] < 0.8 * losses[0] and losses[-1] < losses[len(losses) // 2], losses
 
 
+def test_profile_step_leaves_weights_and_optimizer_state_alone():
+    g = core.build_model("transformer_lm", SMALL_LM)
+    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, use_cuda_graph=False, optimizer=OptimizerConfig(kind="adam", lr=1e-3)))
+    ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 256, (4, 64), dtype=torch.int32, device="cuda")
+    ex.train_step({"input_ids": ids}, labels)
+    before = (ex.master.clone(), ex.opt_m.clone(), ex.opt_v.clone(), ex.step_count)
+    prof = ex.profile_step()
+    assert prof["total_ms"] > 0 and ("LINEAR", "fwd") in prof["by_type"] and ("update", "update") not in prof["by_type"]
+    assert torch.equal(before[0], ex.master) and torch.equal(before[1], ex.opt_m) and torch.equal(before[2], ex.opt_v)
+    assert ex.step_count == before[3]
+    prof = ex.profile_step(update=True)
+    assert ("update", "update") in prof["by_type"] and ex.step_count == before[3] + 1 and not torch.equal(before[0], ex.master)
+
+
 def test_adam_cuda_graph_matches_eager():
     cfg = dict(SMALL_LM, dropout=0.1)
     ids = torch.randint(0, 256, (4, 64, 1), dtype=torch.int32, device="cuda")

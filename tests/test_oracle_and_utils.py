@@ -118,8 +118,14 @@ def test_perf_metrics_accuracy_and_losses():
     m2.update(p, t, ("accuracy", "categorical_crossentropy", "mean_squared_error", "root_mean_squared_error", "mean_absolute_error"))
     assert m2.train_correct == 3 and abs(m2.cce_loss - want) < 1e-5
     d = p - t
-    assert abs(m2.mse_loss - (d * d).mean(1).sum().item()) < 1e-6
-    assert abs(m2.mae_loss - d.abs().mean(1).sum().item()) < 1e-6
+    # the reference's formulas (lib/kernels/src/cuda/metrics_functions.cu:78-96): per-sample sums over the classes
+    assert abs(m2.mse_loss - (d * d).sum(1).sum().item()) < 1e-6
+    assert abs(m2.rmse_loss - (d * d).sum(1).sqrt().sum().item()) < 1e-6
+    assert abs(m2.mae_loss - d.abs().sum(1).sum().item()) < 1e-6
+    # sparse labels are scored against their one-hot targets
+    m3 = PerfMetrics()
+    m3.update(p, torch.tensor([0, 1, 1, 0]), ("mean_squared_error", "root_mean_squared_error", "mean_absolute_error"))
+    assert abs(m3.mse_loss - m2.mse_loss) < 1e-6 and abs(m3.rmse_loss - m2.rmse_loss) < 1e-6 and abs(m3.mae_loss - m2.mae_loss) < 1e-6
     assert m2.summary()["samples"] == 4
 
 
@@ -195,6 +201,14 @@ def test_checkpoint_roundtrip_latest_and_corruption(tmp_path):
     # an incomplete checkpoint (no metadata) is not picked up
     os.makedirs(tmp_path / "step00000009")
     assert ckpt.latest(str(tmp_path)) == p
+    # several ranks without a barrier: refused, because the metadata could be written before the other ranks' files
+    with pytest.raises(ckpt.CheckpointError):
+        ckpt.save(str(tmp_path / "nobarrier"), a, world_size=2)
+    # a rank file the metadata does not list (written after it) is refused on load
+    import shutil
+    shutil.copy(os.path.join(p, "rank0.pt"), os.path.join(p, "rank1.pt"))
+    with pytest.raises(ckpt.CheckpointError, match="no recorded checksum"):
+        ckpt.load(p, _FakeExec(4), rank=1)
     # a flipped byte is caught by the checksum
     F.corrupt_file(os.path.join(p, "rank0.pt"), offset=200)
     with pytest.raises(ckpt.CheckpointError):
