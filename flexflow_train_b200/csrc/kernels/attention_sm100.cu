@@ -1,0 +1,907 @@
+// attention_sm100.cu -- fused multi-head attention core for Blackwell (sm_100a), forward and backward.
+//
+//   O = dropout(softmax(scale * Q K^T [+ causal mask])) V          per (batch, head)
+//
+// Replaces the cuDNN multi-head-attention calls of the reference
+// (lib/kernels/src/cuda/ops/attention_kernels.cu:224-285: cudnnMultiHeadAttnForward / BackwardData /
+// BackwardWeights) for the score / softmax / context part; the projections stay GEMMs.  The [Sq, Sk] score
+// matrix never exists in global memory: scores are produced by tcgen05.mma into tensor memory (TMEM), turned into
+// probabilities by one thread per query row, written as bf16 into shared memory and multiplied with V by the
+// tensor core again.  Only the row log-sum-exp is kept for backward, which recomputes the scores tile by tile.
+//
+// Layouts.  Q, K, V, O, dO, dQ, dK, dV are [batch * seq, ld] bf16 matrices in which head h occupies the D
+// columns starting at h * D (so the packed output of one QKV projection GEMM is used as it lies); D is 64 or 128.
+//
+// Dropout is counter based: element (b, h, q, k) is kept when 16 bits of hash(seed, row * ceil(Sk / 4) + k / 4),
+// row = (b * H + h) * Sq + q, selected by k % 4, are >= p * 65536 (common.cuh: ffk_rand16x4), so backward
+// regenerates the mask.  The 1 / (1 - p) factor is applied once per output row / gradient tile.
+//
+// Forward CTA (320 threads) = one 128-query block of one (batch, head):
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through a two-stage ring
+//   warp 1      MMA issuer:   S[t] = Q K_j^T   (TMEM, two stages)   and   Opart[t] = P_j V_j   (TMEM, two stages)
+//   warps 2-5   softmax:      thread = query row; running max / sum, P_j -> shared memory (bf16, 128-byte swizzle)
+//   warps 6-9   accumulate:   thread = query row; O = O * alpha_j + Opart[t] in registers, final scale and store
+//
+// Backward CTA (320 threads) = one 128-query block of one (batch, head), looping over tiles of 64 keys:
+//   S = Q K_j^T, dP = dO V_j^T (TMEM, two stages) -> thread per query row computes P and dS = P o (dP - delta)
+//   -> shared memory -> dV_j^T = dO^T P, dK_j^T = Q^T dS (TMEM, read out and added to fp32 accumulators in
+//   global memory by four read-out warps) and dQ += dS K_j (TMEM accumulator, stored once at the end).
+//
+// Every mbarrier wait is bounded (tcgen05.cuh); on expiry the CTA records a code in the library's error word,
+// frees its TMEM and returns.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int ATT_THREADS = 320;
+constexpr int BQ = 128;    // query rows per CTA
+constexpr int BKF = 128;   // keys per forward tile
+constexpr int BKB = 64;    // keys per backward tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnArgs {
+  int B, H, Sq, Sk;
+  float scale;            // applied to Q K^T
+  int causal;             // 1: key k is visible to query q iff k <= q (Sq == Sk)
+  float drop_p;
+  unsigned long long drop_salt;
+  const unsigned long long *drop_seed_ptr;
+  bf16 *O;                // forward output [B*Sq, ldo]
+  long long ldo;
+  float *lse;             // [B, H, Sq] log2-domain log-sum-exp of the scaled scores
+  // backward only
+  const float *delta;     // [B, H, Sq] rowsum(dO o O)
+  bf16 *dQ;
+  long long lddq;
+  float *dK_acc, *dV_acc; // [B, H, Sk, D] fp32, zeroed by the caller
+  int *err;
+};
+
+__device__ __forceinline__ unsigned long long attn_seed(const AttnArgs &p) {
+  return p.drop_seed_ptr ? p.drop_salt * 0x9E3779B97F4A7C15ull + *p.drop_seed_ptr : p.drop_salt;
+}
+
+// instruction descriptor: D f32, A/B bf16, majors, N, M
+__host__ __device__ constexpr uint32_t attn_idesc(int M, int N, int a_mn, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+// keep bits of the four keys 4*g4 .. 4*g4+3 of one row
+__device__ __forceinline__ uint64_t attn_rand4(unsigned long long seed, unsigned long long row_groups_base, int g4) {
+  return ffk_rand16x4(seed, row_groups_base + (unsigned long long)g4);
+}
+
+// ================================================================================================ forward
+template <int D>
+struct FwdCfg {
+  static constexpr int PANELS = D / 64;              // 64-column (128-byte) panels per row of Q / K / V
+  static constexpr int Q_BYTES = BQ * D * 2;
+  static constexpr int KV_BYTES = BKF * D * 2;       // one K or one V tile
+  static constexpr int P_BYTES = BQ * BKF * 2;       // 32 KB
+  static constexpr int STAGES = 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + STAGES * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + STAGES * KV_BYTES;
+  static constexpr int OFF_SCALE = OFF_P + P_BYTES;          // [2][128] floats alpha, then [128] final factors
+  static constexpr int OFF_BAR = OFF_SCALE + 3 * 128 * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;    // barriers + alignment slack
+  static constexpr int TMEM_S = 0;                           // S[t] at columns t * 128
+  static constexpr int TMEM_O = 256;                         // Opart[t] at columns 256 + t * D
+  static constexpr uint32_t IDESC_S = attn_idesc(128, BKF, 0, 0);
+  static constexpr uint32_t IDESC_PV = attn_idesc(128, D, 0, 1);
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnArgs p) {
+  using C = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float *alpha_s = (float *)(smem + C::OFF_SCALE);   // [2][128]
+  float *final_s = alpha_s + 256;                    // [128]
+  uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
+  uint64_t *q_full = bars;            // 1
+  uint64_t *k_full = bars + 1;        // [2]
+  uint64_t *v_full = bars + 3;        // [2]
+  uint64_t *k_empty = bars + 5;       // [2]
+  uint64_t *v_empty = bars + 7;       // [2]
+  uint64_t *s_full = bars + 9;        // [2]
+  uint64_t *s_empty = bars + 11;      // [2] 4 warps
+  uint64_t *p_full = bars + 13;       // 4 warps
+  uint64_t *p_empty = bars + 14;      // commit
+  uint64_t *o_full = bars + 15;       // [2] commit
+  uint64_t *o_empty = bars + 17;      // [2] 4 warps
+  uint64_t *a_full = bars + 19;       // [2] 4 warps (alpha written)
+  uint64_t *a_empty = bars + 21;      // [2] 4 warps (alpha read)
+  uint64_t *fin = bars + 23;          // 4 warps (final factors written)
+  uint32_t *tmem_slot = (uint32_t *)(bars + 24);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.Sq + BQ - 1) / BQ;
+  const int qb = blockIdx.x % nqb;
+  const int bh = blockIdx.x / nqb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int q0 = qb * BQ;
+  int n_tiles = (p.Sk + BKF - 1) / BKF;
+  if (p.causal) {
+    const int last = (min(q0 + BQ, p.Sq) - 1) / BKF + 1;   // tiles that contain a key <= the block's last query
+    n_tiles = min(n_tiles, last);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 4);
+      mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 4);
+    }
+    mbar_init(p_full, 4); mbar_init(p_empty, 1); mbar_init(fin, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, C::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::PANELS; ++c) tma_load_4d(smem_u32(smem + C::OFF_Q + c * BQ * 128), &tmQ, q_full, c * 64, q0, h, b);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        ok = mbar_wait(&k_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+        if (!ok) break;
+        mbar_expect_tx(&k_full[t], C::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::PANELS; ++c)
+          tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKF * 128), &tmK, &k_full[t], c * 64, j * BKF, h, b);
+        ok = mbar_wait(&v_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+        if (!ok) break;
+        mbar_expect_tx(&v_full[t], C::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::PANELS; ++c)
+          tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKF * 128), &tmV, &v_full[t], c * 64, j * BKF, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+      const uint32_t sq = smem_u32(smem + C::OFF_Q);
+      auto issue_s = [&](int j) -> bool {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(&k_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(&s_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);   // panel, then 32 bytes per k-step
+          tc_mma<false>(d_tmem, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[t]);
+        tc_commit(&k_empty[t]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+        ok = mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
+             mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
+             mbar_wait(&o_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sp = smem_u32(smem + C::OFF_P);
+        const uint32_t sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
+#pragma unroll
+        for (int ks = 0; ks < BKF / 16; ++ks) {
+          // A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
+          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+          const uint32_t b_off = (uint32_t)(ks * 16 * 128);
+          tc_mma<false>(d_tmem, make_smem_desc(sp + a_off, 16, 1024), make_smem_desc(sv + b_off, BKF * 128, 1024), C::IDESC_PV,
+                        ks != 0 ? 1u : 0u);
+        }
+        tc_commit(&o_full[t]);
+        tc_commit(&v_empty[t]);
+        tc_commit(p_empty);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ softmax: thread = query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q = q0 + r;
+    const float sl2 = p.scale * LOG2E;
+    float m = -INFINITY, l = 0.f;
+    const bool drop = p.drop_p > 0.f;
+    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const unsigned long long seed = drop ? attn_seed(p) : 0ull;
+    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
+    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    uint8_t *prow = smem + C::OFF_P + r * 128;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int t = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      ok = mbar_wait(&s_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_s = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_S + t * 128);
+      const int k0 = j * BKF;
+      // columns of this tile that exist / are visible to this row
+      int kmax = p.Sk - k0;                       // columns >= kmax are padding
+      if (p.causal) kmax = min(kmax, q - k0 + 1);
+      const bool full = kmax >= BKF;
+      uint32_t rr[32];
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(t_s + (uint32_t)(c * 32), rr);
+        tmem_ld_wait();
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(rr[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i < kmax) ? __uint_as_float(rr[i]) : -INFINITY);
+        }
+      }
+      float m_new = fmaxf(m, mx * sl2);
+      if (m_new == -INFINITY) m_new = 0.f;        // a row with nothing visible yet (only padding rows get here)
+      const float alpha = exp2f(m - m_new);
+      ok = mbar_wait(&a_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      alpha_s[t * 128 + r] = alpha;
+      __threadfence_block();
+      warp_arrive(&a_full[t], lane);
+      ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(t_s + (uint32_t)(c * 32), rr);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(fmaf(__uint_as_float(rr[i]), sl2, -m_new));
+          if (!full && c * 32 + i >= kmax) e = 0.f;
+          lsum += e;
+          pv[i] = e;
+        }
+        if (drop) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint64_t z = attn_rand4(seed, row_base, (k0 >> 2) + c * 8 + g);
+            if ((uint32_t)(z & 0xFFFFu) < thr) pv[4 * g] = 0.f;
+            if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) pv[4 * g + 1] = 0.f;
+            if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) pv[4 * g + 2] = 0.f;
+            if ((uint32_t)(z >> 48) < thr) pv[4 * g + 3] = 0.f;
+          }
+        }
+        // 32 probabilities = 64 bytes = four 16-byte chunks 4c .. 4c+3 of this row; chunk index XOR (row % 8) within
+        // its 64-key panel is the 128-byte swizzle the MMA descriptor expects
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int chunk = c * 4 + u;
+          const uint32_t addr = smem_u32(prow + (chunk >> 3) * (BQ * 128)) + (uint32_t)((((chunk & 7) ^ (r & 7))) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf162(pv[8 * u], pv[8 * u + 1])),
+                       "r"(pack_bf162(pv[8 * u + 2], pv[8 * u + 3])), "r"(pack_bf162(pv[8 * u + 4], pv[8 * u + 5])),
+                       "r"(pack_bf162(pv[8 * u + 6], pv[8 * u + 7]))
+                       : "memory");
+        }
+      }
+      tc_fence_before();
+      warp_arrive(&s_empty[t], lane);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      warp_arrive(p_full, lane);
+      l = l * alpha + lsum;
+      m = m_new;
+    }
+    if (ok) {
+      // final factor of this row: 1 / (sum * keep probability); log-sum-exp for backward
+      const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
+      final_s[r] = l > 0.f ? inv_keep / l : 0.f;
+      if (q < p.Sq && p.lse) p.lse[((long long)(b * p.H + h)) * p.Sq + q] = l > 0.f ? m + log2f(l) : INFINITY;
+      __threadfence_block();
+      warp_arrive(fin, lane);
+    }
+  } else {
+    // ------------------------------------------------------------------ accumulate: thread = query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q = q0 + r;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int t = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      ok = mbar_wait(&a_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float alpha = alpha_s[t * 128 + r];
+      warp_arrive(&a_empty[t], lane);
+      ok = mbar_wait(&o_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_o = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_O + t * D);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(t_o + (uint32_t)(c * 32), rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(rr[i]));
+      }
+      tc_fence_before();
+      warp_arrive(&o_empty[t], lane);
+    }
+    if (ok) {
+      ok = mbar_wait(fin, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && q < p.Sq) {
+      const float f = final_s[r];
+      bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 v = make_uint4(pack_bf162(o[8 * c] * f, o[8 * c + 1] * f), pack_bf162(o[8 * c + 2] * f, o[8 * c + 3] * f),
+                             pack_bf162(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf162(o[8 * c + 6] * f, o[8 * c + 7] * f));
+        *reinterpret_cast<uint4 *>(orow + 8 * c) = v;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ================================================================================================ backward
+// delta[b, h, q] = sum_c dO[b, q, h, c] * O[b, q, h, c]; one warp per (row, head)
+template <int D>
+__global__ void attn_delta_kernel(const bf16 *__restrict__ dO, long long lddo, const bf16 *__restrict__ O, long long ldo,
+                                  float *__restrict__ delta, int B, int H, int Sq) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)B * Sq * H;
+  if (w >= total) return;
+  const int h = (int)(w % H);
+  const long long row = w / H;   // b * Sq + q
+  const bf16 *a = dO + row * lddo + (long long)h * D, *c = O + row * ldo + (long long)h * D;
+  float s = 0.f;
+  constexpr int PER = D / 32;    // 2 or 4 elements per lane
+  if constexpr (PER == 4) {
+    uint2 ua = *reinterpret_cast<const uint2 *>(a + lane * 4), uc = *reinterpret_cast<const uint2 *>(c + lane * 4);
+    float2 a0 = unpack_bf162(ua.x), a1 = unpack_bf162(ua.y), c0 = unpack_bf162(uc.x), c1 = unpack_bf162(uc.y);
+    s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  } else {
+    uint32_t ua = *reinterpret_cast<const uint32_t *>(a + lane * 2), uc = *reinterpret_cast<const uint32_t *>(c + lane * 2);
+    float2 a0 = unpack_bf162(ua), c0 = unpack_bf162(uc);
+    s = a0.x * c0.x + a0.y * c0.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long b = row / Sq, q = row - b * Sq;
+    delta[(b * H + h) * Sq + q] = s;
+  }
+}
+
+// fp32 accumulators [B, H, Sk, D] -> bf16 [B*Sk, ld] (head h at columns h*D)
+template <int D>
+__global__ void attn_acc_to_bf16_kernel(const float *__restrict__ acc, bf16 *__restrict__ out, long long ld, int B, int H, int Sk) {
+  const long long total = (long long)B * H * Sk * (D / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c4 = (int)(i % (D / 4));
+    long long rest = i / (D / 4);
+    const int k = (int)(rest % Sk);
+    rest /= Sk;
+    const int h = (int)(rest % H);
+    const long long b = rest / H;
+    const float4 v = *reinterpret_cast<const float4 *>(acc + i * 4);
+    *reinterpret_cast<uint2 *>(out + (b * Sk + k) * ld + (long long)h * D + c4 * 4) = make_uint2(pack_bf162(v.x, v.y), pack_bf162(v.z, v.w));
+  }
+}
+
+struct BwdCfg {
+  static constexpr int D = 128;
+  static constexpr int Q_BYTES = BQ * D * 2;          // 32 KB (also dO)
+  static constexpr int KV_BYTES = BKB * D * 2;        // 16 KB: two panels of [64 keys x 128 B]
+  static constexpr int PS_BYTES = BQ * BKB * 2;       // 16 KB: P or dS tile, [128 rows x 128 B]
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + Q_BYTES;
+  static constexpr int OFF_K = OFF_DO + Q_BYTES;      // [2]
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;  // [2]
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;  // [2]
+  static constexpr int OFF_DS = OFF_P + 2 * PS_BYTES; // [2]
+  static constexpr int OFF_BAR = OFF_DS + 2 * PS_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_S = 0;      // S[t] at t*64
+  static constexpr int TMEM_DP = 128;   // dP[t] at 128 + t*64
+  static constexpr int TMEM_DVT = 256;  // 64 columns
+  static constexpr int TMEM_DKT = 320;  // 64 columns
+  static constexpr int TMEM_DQ = 384;   // 128 columns
+  static constexpr uint32_t IDESC_S = attn_idesc(128, BKB, 0, 0);     // Q K^T, dO V^T
+  static constexpr uint32_t IDESC_T = attn_idesc(128, BKB, 1, 1);     // dO^T P, Q^T dS   (both operands MN-major)
+  static constexpr uint32_t IDESC_DQ = attn_idesc(128, D, 0, 1);      // dS K
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
+  using C = BwdCfg;
+  constexpr int D = C::D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
+  uint64_t *q_full = bars;            // Q and dO
+  uint64_t *k_full = bars + 1;        // [2]
+  uint64_t *v_full = bars + 3;        // [2]
+  uint64_t *k_empty = bars + 5;       // [2] commit
+  uint64_t *v_empty = bars + 7;       // [2] commit
+  uint64_t *sdp_full = bars + 9;      // [2] commit
+  uint64_t *sdp_empty = bars + 11;    // [2] 4 warps
+  uint64_t *pds_full = bars + 13;     // [2] 4 warps
+  uint64_t *pds_empty = bars + 15;    // [2] commit
+  uint64_t *dkv_full = bars + 17;     // commit
+  uint64_t *dkv_empty = bars + 18;    // 4 warps
+  uint64_t *dq_full = bars + 19;      // commit
+  uint32_t *tmem_slot = (uint32_t *)(bars + 20);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.Sq + BQ - 1) / BQ;
+  const int qb = blockIdx.x % nqb;
+  const int bh = blockIdx.x / nqb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int q0 = qb * BQ;
+  int n_tiles = (p.Sk + BKB - 1) / BKB;
+  if (p.causal) n_tiles = min(n_tiles, (min(q0 + BQ, p.Sq) - 1) / BKB + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&sdp_empty[s], 4); mbar_init(&pds_full[s], 4); mbar_init(&pds_empty[s], 1);
+    }
+    mbar_init(dkv_full, 1); mbar_init(dkv_empty, 4); mbar_init(dq_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * C::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem_u32(smem + C::OFF_Q + c * BQ * 128), &tmQ, q_full, c * 64, q0, h, b);
+        tma_load_4d(smem_u32(smem + C::OFF_DO + c * BQ * 128), &tmDO, q_full, c * 64, q0, h, b);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        ok = mbar_wait(&k_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+        if (!ok) break;
+        mbar_expect_tx(&k_full[t], C::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKB * 128), &tmK, &k_full[t], c * 64, j * BKB, h, b);
+        ok = mbar_wait(&v_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
+        if (!ok) break;
+        mbar_expect_tx(&v_full[t], C::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKB * 128), &tmV, &v_full[t], c * 64, j * BKB, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+      const uint32_t sq = smem_u32(smem + C::OFF_Q), sdo = smem_u32(smem + C::OFF_DO);
+      // S[t] = Q K_j^T and dP[t] = dO V_j^T : K-major operands, k-steps of 16 head-dim columns
+      auto issue_sdp = [&](int j) -> bool {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(&k_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(&sdp_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES), sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+          const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
+          tc_mma<false>(tmem_base + (uint32_t)(C::TMEM_S + t * 64), make_smem_desc(sq + a_off, 16, 1024), make_smem_desc(sk + b_off, 16, 1024),
+                        C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
+        if (!mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+          const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
+          tc_mma<false>(tmem_base + (uint32_t)(C::TMEM_DP + t * 64), make_smem_desc(sdo + a_off, 16, 1024), make_smem_desc(sv + b_off, 16, 1024),
+                        C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
+        tc_commit(&sdp_full[t]);
+        tc_commit(&v_empty[t]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_sdp(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int t = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (j + 1 < n_tiles) { ok = issue_sdp(j + 1); if (!ok) break; }
+        ok = mbar_wait(&pds_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
+             mbar_wait(dkv_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sp = smem_u32(smem + C::OFF_P + t * C::PS_BYTES), sds = smem_u32(smem + C::OFF_DS + t * C::PS_BYTES);
+        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES);
+        // dV_j^T [D x 64] = dO^T P and dK_j^T = Q^T dS: A = dO / Q read M-major (M = head dim: two 64-column panels, LBO = panel
+        // stride), B = P / dS read N-major (N = 64 keys, one panel); every k-step is 16 query rows = 2048 bytes
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {
+          const uint32_t off = (uint32_t)(ks * 16 * 128);
+          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DVT, make_smem_desc(sdo + off, BQ * 128, 1024), make_smem_desc(sp + off, BQ * 128, 1024),
+                        C::IDESC_T, ks != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {
+          const uint32_t off = (uint32_t)(ks * 16 * 128);
+          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DKT, make_smem_desc(sq + off, BQ * 128, 1024), make_smem_desc(sds + off, BQ * 128, 1024),
+                        C::IDESC_T, ks != 0 ? 1u : 0u);
+        }
+        tc_commit(dkv_full);
+        // dQ += dS K_j: A = dS K-major (64 keys = one panel, 32 bytes per k-step), B = K_j N-major (N = head dim, 16 key rows per step)
+#pragma unroll
+        for (int ks = 0; ks < BKB / 16; ++ks) {
+          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DQ, make_smem_desc(sds + (uint32_t)(ks * 32), 16, 1024),
+                        make_smem_desc(sk + (uint32_t)(ks * 16 * 128), BKB * 128, 1024), C::IDESC_DQ, (j | ks) != 0 ? 1u : 0u);
+        }
+        tc_commit(&k_empty[t]);
+        tc_commit(&pds_empty[t]);
+      }
+      if (ok) tc_commit(dq_full);
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ softmax / dS: thread = query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q = q0 + r;
+    const float sl2 = p.scale * LOG2E;
+    const bool row_ok = q < p.Sq;
+    const long long stat = ((long long)(b * p.H + h)) * p.Sq + q;
+    const float lse = row_ok ? p.lse[stat] : INFINITY;
+    const float dlt = row_ok ? p.delta[stat] : 0.f;
+    const bool drop = p.drop_p > 0.f;
+    const float inv_keep = drop ? 1.f / (1.f - p.drop_p) : 1.f;
+    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const unsigned long long seed = drop ? attn_seed(p) : 0ull;
+    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
+    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int t = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      ok = mbar_wait(&sdp_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
+           mbar_wait(&pds_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const int k0 = j * BKB;
+      int kmax = p.Sk - k0;
+      if (p.causal) kmax = min(kmax, q - k0 + 1);
+      uint8_t *prow = smem + C::OFF_P + t * C::PS_BYTES + r * 128;
+      uint8_t *dsrow = smem + C::OFF_DS + t * C::PS_BYTES + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + t * 64 + c * 32), rs);
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + t * 64 + c * 32), rd);
+        tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -lse));
+          if (c * 32 + i >= kmax) e = 0.f;
+          pv[i] = e;
+          ds[i] = __uint_as_float(rd[i]) * inv_keep;
+        }
+        if (drop) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint64_t z = attn_rand4(seed, row_base, (k0 >> 2) + c * 8 + g);
+            const bool d0 = (uint32_t)(z & 0xFFFFu) < thr, d1 = (uint32_t)((z >> 16) & 0xFFFFu) < thr;
+            const bool d2 = (uint32_t)((z >> 32) & 0xFFFFu) < thr, d3 = (uint32_t)(z >> 48) < thr;
+            // dropped: contributes nothing to dV, and its dP is zero
+            if (d0) ds[4 * g] = 0.f;
+            if (d1) ds[4 * g + 1] = 0.f;
+            if (d2) ds[4 * g + 2] = 0.f;
+            if (d3) ds[4 * g + 3] = 0.f;
+            const float p0 = pv[4 * g], p1 = pv[4 * g + 1], p2 = pv[4 * g + 2], p3 = pv[4 * g + 3];
+            ds[4 * g] = p0 * (ds[4 * g] - dlt);
+            ds[4 * g + 1] = p1 * (ds[4 * g + 1] - dlt);
+            ds[4 * g + 2] = p2 * (ds[4 * g + 2] - dlt);
+            ds[4 * g + 3] = p3 * (ds[4 * g + 3] - dlt);
+            if (d0) pv[4 * g] = 0.f;
+            if (d1) pv[4 * g + 1] = 0.f;
+            if (d2) pv[4 * g + 2] = 0.f;
+            if (d3) pv[4 * g + 3] = 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ds[i] = pv[i] * (ds[i] - dlt);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int chunk = c * 4 + u;   // 0..7 within the single 64-key panel
+          const uint32_t sw = (uint32_t)((chunk ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(prow) + sw), "r"(pack_bf162(pv[8 * u], pv[8 * u + 1])),
+                       "r"(pack_bf162(pv[8 * u + 2], pv[8 * u + 3])), "r"(pack_bf162(pv[8 * u + 4], pv[8 * u + 5])),
+                       "r"(pack_bf162(pv[8 * u + 6], pv[8 * u + 7]))
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(dsrow) + sw), "r"(pack_bf162(ds[8 * u], ds[8 * u + 1])),
+                       "r"(pack_bf162(ds[8 * u + 2], ds[8 * u + 3])), "r"(pack_bf162(ds[8 * u + 4], ds[8 * u + 5])),
+                       "r"(pack_bf162(ds[8 * u + 6], ds[8 * u + 7]))
+                       : "memory");
+        }
+      }
+      tc_fence_before();
+      warp_arrive(&sdp_empty[t], lane);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      warp_arrive(&pds_full[t], lane);
+    }
+    // dQ of this block: scale * accumulator -> bf16
+    if (ok) {
+      ok = mbar_wait(dq_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      bf16 *dqrow = p.dQ + ((long long)b * p.Sq + q) * p.lddq + (long long)h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_DQ + c * 32), rr);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 v = make_uint4(pack_bf162(__uint_as_float(rr[8 * u]) * p.scale, __uint_as_float(rr[8 * u + 1]) * p.scale),
+                                 pack_bf162(__uint_as_float(rr[8 * u + 2]) * p.scale, __uint_as_float(rr[8 * u + 3]) * p.scale),
+                                 pack_bf162(__uint_as_float(rr[8 * u + 4]) * p.scale, __uint_as_float(rr[8 * u + 5]) * p.scale),
+                                 pack_bf162(__uint_as_float(rr[8 * u + 6]) * p.scale, __uint_as_float(rr[8 * u + 7]) * p.scale));
+            *reinterpret_cast<uint4 *>(dqrow + c * 32 + 8 * u) = v;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ read-out of dV_j^T / dK_j^T: thread = head-dim index
+    const int quarter = warp & 3;
+    const int dcol = quarter * 32 + lane;
+    const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
+    float *dv_base = p.dV_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
+    float *dk_base = p.dK_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      ok = mbar_wait(dkv_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const int k0 = j * BKB;
+      uint32_t rv[2][32], rk[2][32];
+      tmem_ld32(lane_base + (uint32_t)C::TMEM_DVT, rv[0]);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + 32), rv[1]);
+      tmem_ld32(lane_base + (uint32_t)C::TMEM_DKT, rk[0]);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + 32), rk[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      warp_arrive(dkv_empty, lane);
+      const int kn = min(BKB, p.Sk - k0);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kk = c * 32 + i;
+          if (kk < kn) {
+            atomicAdd(dv_base + (long long)(k0 + kk) * D, __uint_as_float(rv[c][i]) * inv_keep);
+            atomicAdd(dk_base + (long long)(k0 + kk) * D, __uint_as_float(rk[c][i]) * p.scale);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+// 4-D map {head-dim column, row within the sequence, head, batch} of a [B*S, ld] matrix; box = 64 columns x box_rows rows
+int make_head_map(CUtensorMap *map, const void *ptr, int D, int S, long long ld, int H, int B, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)(ld * 2), (cuuint64_t)(D * 2), (cuuint64_t)((long long)S * ld * 2)};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+__device__ int g_attn_err = 0;
+
+bool aligned16(const void *p, long long ld) { return (((uintptr_t)p) & 15) == 0 && (ld * 2) % 16 == 0; }
+
+}  // namespace
+
+// One attention call.  Plain C struct so ctypes can fill it.
+struct FfkAttnDesc {
+  int B, H, Sq, Sk, D;
+  float scale;
+  int causal;
+  float drop_p;
+  unsigned long long drop_salt;
+  const void *drop_seed_ptr;   // device u64 (per-step seed) or null
+  const void *Q; long long ldq;
+  const void *K; long long ldk;
+  const void *V; long long ldv;
+  void *O; long long ldo;
+  void *lse;                   // [B, H, Sq] float
+  // backward
+  const void *dO; long long lddo;
+  void *delta;                 // [B, H, Sq] float scratch
+  void *dQ; long long lddq;
+  void *dK; long long lddk;
+  void *dV; long long lddv;
+  void *acc;                   // 2 * B*H*Sk*D floats of scratch (dK and dV accumulators)
+};
+
+// 1 when the fused kernels cover this head dimension / direction
+FFK_API int ffk_attention_supported(int D, int backward) { return backward ? (D == 128) : (D == 64 || D == 128); }
+FFK_API long long ffk_attention_bwd_scratch_floats(int B, int H, int Sk, int D) { return 2ll * B * H * Sk * D; }
+
+FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
+  if (d->D != 64 && d->D != 128) return -2;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Sk <= 0) return 0;
+  if (!aligned16(d->Q, d->ldq) || !aligned16(d->K, d->ldk) || !aligned16(d->V, d->ldv) || !aligned16(d->O, d->ldo)) return -2;
+  if (d->causal && d->Sq != d->Sk) return -2;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_head_map(&tq, d->Q, d->D, d->Sq, d->ldq, d->H, d->B, BQ))) return r;
+  if ((r = make_head_map(&tk, d->K, d->D, d->Sk, d->ldk, d->H, d->B, BKF))) return r;
+  if ((r = make_head_map(&tv, d->V, d->D, d->Sk, d->ldv, d->H, d->B, BKF))) return r;
+  AttnArgs a = {};
+  a.B = d->B; a.H = d->H; a.Sq = d->Sq; a.Sk = d->Sk; a.scale = d->scale; a.causal = d->causal;
+  a.drop_p = d->drop_p; a.drop_salt = d->drop_salt; a.drop_seed_ptr = (const unsigned long long *)d->drop_seed_ptr;
+  a.O = (bf16 *)d->O; a.ldo = d->ldo; a.lse = (float *)d->lse;
+  void *errp = nullptr;
+  cudaGetSymbolAddress(&errp, g_attn_err);
+  a.err = (int *)errp;
+  const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
+  if (grid > 0x7fffffffll) return -2;
+  if (d->D == 128) {
+    static bool attr = false;
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr = true;
+    }
+    attn_fwd_kernel<128><<<(unsigned)grid, ATT_THREADS, FwdCfg<128>::SMEM_BYTES, stream>>>(tq, tk, tv, a);
+  } else {
+    static bool attr = false;
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr = true;
+    }
+    attn_fwd_kernel<64><<<(unsigned)grid, ATT_THREADS, FwdCfg<64>::SMEM_BYTES, stream>>>(tq, tk, tv, a);
+  }
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
+  if (d->D != 128) return -2;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Sk <= 0) return 0;
+  if (!aligned16(d->Q, d->ldq) || !aligned16(d->K, d->ldk) || !aligned16(d->V, d->ldv) || !aligned16(d->O, d->ldo) ||
+      !aligned16(d->dO, d->lddo) || !aligned16(d->dQ, d->lddq) || !aligned16(d->dK, d->lddk) || !aligned16(d->dV, d->lddv) ||
+      (((uintptr_t)d->acc) & 15))
+    return -2;
+  if (d->causal && d->Sq != d->Sk) return -2;
+  constexpr int D = 128;
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_head_map(&tq, d->Q, D, d->Sq, d->ldq, d->H, d->B, BQ))) return r;
+  if ((r = make_head_map(&tdo, d->dO, D, d->Sq, d->lddo, d->H, d->B, BQ))) return r;
+  if ((r = make_head_map(&tk, d->K, D, d->Sk, d->ldk, d->H, d->B, BKB))) return r;
+  if ((r = make_head_map(&tv, d->V, D, d->Sk, d->ldv, d->H, d->B, BKB))) return r;
+  const long long n_acc = (long long)d->B * d->H * d->Sk * D;
+  cudaError_t e = cudaMemsetAsync(d->acc, 0, (size_t)(2 * n_acc) * sizeof(float), stream);
+  if (e != cudaSuccess) return (int)e;
+  {
+    const long long warps = (long long)d->B * d->Sq * d->H;
+    attn_delta_kernel<D><<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const bf16 *)d->dO, d->lddo, (const bf16 *)d->O, d->ldo,
+                                                                           (float *)d->delta, d->B, d->H, d->Sq);
+  }
+  AttnArgs a = {};
+  a.B = d->B; a.H = d->H; a.Sq = d->Sq; a.Sk = d->Sk; a.scale = d->scale; a.causal = d->causal;
+  a.drop_p = d->drop_p; a.drop_salt = d->drop_salt; a.drop_seed_ptr = (const unsigned long long *)d->drop_seed_ptr;
+  a.lse = (float *)d->lse; a.delta = (const float *)d->delta;
+  a.dQ = (bf16 *)d->dQ; a.lddq = d->lddq;
+  a.dK_acc = (float *)d->acc; a.dV_acc = (float *)d->acc + n_acc;
+  void *errp = nullptr;
+  cudaGetSymbolAddress(&errp, g_attn_err);
+  a.err = (int *)errp;
+  static bool attr = false;
+  if (!attr) {
+    e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
+  if (grid > 0x7fffffffll) return -2;
+  attn_bwd_kernel<<<(unsigned)grid, ATT_THREADS, BwdCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  const int cblocks = ffk_blocks(n_acc / 4, 256);
+  attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dK_acc, (bf16 *)d->dK, d->lddk, d->B, d->H, d->Sk);
+  attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dV_acc, (bf16 *)d->dV, d->lddv, d->B, d->H, d->Sk);
+  return (int)cudaGetLastError();
+}
+
+// Reads (and clears) the error word of the attention kernels' bounded waits.  Synchronises the device.
+FFK_API int ffk_attention_last_error() {
+  int v = 0, z = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  cudaMemcpyFromSymbol(&v, g_attn_err, sizeof(int));
+  cudaMemcpyToSymbol(g_attn_err, &z, sizeof(int));
+  return v;
+}

@@ -63,6 +63,18 @@ class GemmDesc(ctypes.Structure):
     ]
 
 
+class AttnDesc(ctypes.Structure):
+    _fields_ = [
+        ("B", c_int), ("H", c_int), ("Sq", c_int), ("Sk", c_int), ("D", c_int), ("scale", c_float), ("causal", c_int),
+        ("drop_p", c_float), ("drop_salt", c_ulonglong), ("drop_seed_ptr", c_void_p),
+        ("Q", c_void_p), ("ldq", c_longlong), ("K", c_void_p), ("ldk", c_longlong), ("V", c_void_p), ("ldv", c_longlong),
+        ("O", c_void_p), ("ldo", c_longlong), ("lse", c_void_p),
+        ("dO", c_void_p), ("lddo", c_longlong), ("delta", c_void_p),
+        ("dQ", c_void_p), ("lddq", c_longlong), ("dK", c_void_p), ("lddk", c_longlong), ("dV", c_void_p), ("lddv", c_longlong),
+        ("acc", c_void_p),
+    ]
+
+
 def available() -> bool:
     return os.path.exists(_LIB_PATH)
 
@@ -87,6 +99,10 @@ def _declare(l):
     sig = {
         "ffk_gemm": [ctypes.POINTER(GemmDesc), S],
         "ffk_gemm_last_error": [],
+        "ffk_attention_fwd": [ctypes.POINTER(AttnDesc), S],
+        "ffk_attention_bwd": [ctypes.POINTER(AttnDesc), S],
+        "ffk_attention_last_error": [],
+        "ffk_attention_supported": [I, I],
         "ffk_unary_fwd": [I, P, P, L, F, I, S],
         "ffk_unary_bwd": [I, P, P, P, P, L, F, I, I, S],
         "ffk_binary_fwd": [I, P, P, P, L, L, I, S],
@@ -114,6 +130,9 @@ def _declare(l):
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = c_int
+    if hasattr(l, "ffk_attention_bwd_scratch_floats"):
+        l.ffk_attention_bwd_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        l.ffk_attention_bwd_scratch_floats.restype = c_longlong
     for name in ("ffk_bias_act_bwd_scratch", "ffk_layernorm_bwd_scratch"):
         if hasattr(l, name):
             fn = getattr(l, name)
@@ -242,6 +261,100 @@ def gemm_raw(*, M, N, K, A, lda, B, ldb, C, ldc, a_mn=False, b_mn=False, es=2, n
 
 def gemm_last_error() -> int:
     return lib().ffk_gemm_last_error()
+
+
+# --------------------------------------------------------------------------- fused attention
+def attention_supported(head_dim: int, backward: bool = True) -> bool:
+    """True when the fused attention kernels cover this head dimension (forward: 64 and 128; backward: 128)."""
+    return bool(lib().ffk_attention_supported(int(head_dim), int(backward)))
+
+
+def attention_bwd_scratch_floats(B, H, Sk, D) -> int:
+    return int(lib().ffk_attention_bwd_scratch_floats(B, H, Sk, D))
+
+
+def attention_last_error() -> int:
+    return lib().ffk_attention_last_error()
+
+
+def _attn_view(t, D, H):
+    """A [B*S, >= H*D] bf16 matrix view (last dim contiguous) -> (pointer, leading dimension)."""
+    if t.dtype != torch.bfloat16 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] < H * D:
+        raise KernelError("attention operands are 2-D bf16 CUDA matrices [batch*seq, heads*head_dim] with unit column stride")
+    return t.data_ptr(), t.stride(0)
+
+
+def _attn_desc(B, H, Sq, Sk, D, scale, causal, dropout):
+    d = AttnDesc()
+    d.B, d.H, d.Sq, d.Sk, d.D, d.scale, d.causal = B, H, Sq, Sk, D, float(scale), int(bool(causal))
+    if dropout is not None and dropout[0] > 0:
+        p, salt, seed = dropout
+        d.drop_p, d.drop_salt, d.drop_seed_ptr = float(p), int(salt) & 0xFFFFFFFFFFFFFFFF, _p(seed)
+    return d
+
+
+def attention_fwd(q, k, v, out, lse, *, B, H, Sq, Sk, D, scale, causal=False, dropout=None):
+    """out[b, q, h, :] = dropout(softmax(scale * q k^T)) v for every (batch, head); q / k / v / out are [B*S, ld] bf16
+    matrices with head h in columns [h*D, (h+1)*D) (views into a packed QKV buffer are fine).  lse [B, H, Sq] fp32
+    receives the row log-sum-exp (base 2, of the scaled scores) that `attention_bwd` needs.
+    dropout = (p, salt, seed tensor or None)."""
+    d = _attn_desc(B, H, Sq, Sk, D, scale, causal, dropout)
+    d.Q, d.ldq = _attn_view(q, D, H)
+    d.K, d.ldk = _attn_view(k, D, H)
+    d.V, d.ldv = _attn_view(v, D, H)
+    d.O, d.ldo = _attn_view(out, D, H)
+    if lse.dtype != torch.float32 or lse.numel() < B * H * Sq or not lse.is_contiguous():
+        raise KernelError("lse must be a contiguous fp32 tensor of B*H*Sq elements")
+    d.lse = lse.data_ptr()
+    _check(lib().ffk_attention_fwd(ctypes.byref(d), _stream()), "ffk_attention_fwd")
+    return out
+
+
+def attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, *, B, H, Sq, Sk, D, scale, causal=False, dropout=None):
+    """Gradients of `attention_fwd` with respect to q, k, v (same layouts).  delta: fp32 scratch of B*H*Sq elements;
+    acc: fp32 scratch of attention_bwd_scratch_floats(B, H, Sk, D) elements."""
+    d = _attn_desc(B, H, Sq, Sk, D, scale, causal, dropout)
+    d.Q, d.ldq = _attn_view(q, D, H)
+    d.K, d.ldk = _attn_view(k, D, H)
+    d.V, d.ldv = _attn_view(v, D, H)
+    d.O, d.ldo = _attn_view(out, D, H)
+    d.dO, d.lddo = _attn_view(dout, D, H)
+    d.dQ, d.lddq = _attn_view(dq, D, H)
+    d.dK, d.lddk = _attn_view(dk, D, H)
+    d.dV, d.lddv = _attn_view(dv, D, H)
+    if delta.dtype != torch.float32 or delta.numel() < B * H * Sq or acc.dtype != torch.float32 or acc.numel() < 2 * B * H * Sk * D:
+        raise KernelError("attention_bwd scratch too small")
+    d.lse, d.delta, d.acc = lse.data_ptr(), delta.data_ptr(), acc.data_ptr()
+    _check(lib().ffk_attention_bwd(ctypes.byref(d), _stream()), "ffk_attention_bwd")
+
+
+def attention_keep_mask(B, H, Sq, Sk, p, salt, seed=None, device="cpu"):
+    """The dropout keep mask [B, H, Sq, Sk] (bool) the fused attention kernels draw: a host restatement of the
+    counter-based generator, for tests and debugging."""
+    M = (1 << 64) - 1
+
+    def u64(x):  # python int (mod 2^64) -> int64 tensor value
+        x &= M
+        return x - (1 << 64) if x >= (1 << 63) else x
+
+    sd = int(salt) & M
+    if seed is not None:
+        sd = (sd * 0x9E3779B97F4A7C15 + int(seed)) & M
+    groups = (Sk + 3) // 4
+    rows = torch.arange(B * H * Sq, dtype=torch.int64, device=device)[:, None]
+    g = torch.arange(groups, dtype=torch.int64, device=device)[None, :]
+    z = (rows * groups + g) * u64(0x9E3779B97F4A7C15) + u64(sd)
+
+    def lsr(x, n):  # logical shift right on int64
+        return (x >> n) & ((1 << (64 - n)) - 1)
+
+    z = (z ^ lsr(z, 30)) * u64(0xBF58476D1CE4E5B9)
+    z = (z ^ lsr(z, 27)) * u64(0x94D049BB133111EB)
+    z = z ^ lsr(z, 31)
+    thr = int(p * 65536.0)
+    fields = torch.stack([lsr(z, 16 * i) & 0xFFFF if i else z & 0xFFFF for i in range(4)], dim=-1)  # [rows, groups, 4]
+    keep = (fields >= thr).reshape(B * H * Sq, groups * 4)[:, :Sk]
+    return keep.reshape(B, H, Sq, Sk)
 
 
 def _es(t):

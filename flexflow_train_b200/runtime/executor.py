@@ -63,6 +63,10 @@ class ExecConfig:
     fuse_dropout: bool = False
     fold_dropout_backward: bool = True  # Linear -> Dropout: mask the gradient inside the Linear's bias/activation backward
     keep_dropped_probs: bool = True  # attention: keep dropout(P) for backward when device memory allows
+    # Attention core (scores, softmax, dropout, context) in one tcgen05 kernel per direction, without a score tensor in
+    # global memory, where the head dimension is covered (ops/kernels.py: attention_supported); otherwise the
+    # batched-GEMM + softmax path below runs.
+    fused_attention: bool = True
     # Attention core in blocks: scores, probabilities and their gradients of a few batch elements (or head groups)
     # at a time live in small reused buffers and backward recomputes the probabilities of a block, so no
     # B x H x S x S tensor is ever stored (saves 2 such tensors per layer; 48 GB on the large Transformer).
@@ -405,11 +409,17 @@ class AttentionOp(OpImpl):
             self.c_ctx = torch.empty(self.B * self.Sq, H * vd, dtype=cdt, device=dev)
         else:
             self.c_q, self.c_k, self.c_v = self.qv, self.kv, self.vv
+        self.fused = bool(ex.on_gpu and ex.cfg.fused_attention and kd == vd and K.attention_supported(kd, backward=ex.cfg.training)
+                          and (not ex.cfg.causal_attention or self.Sq == self.Sk))
         per_batch = H * self.Sq * self.Sk * 2
         blk = int(ex.cfg.attention_block_bytes)
         self.cb = 0   # batch elements per block (0 = unblocked)
         self.hb = H   # heads per block
-        if ex.on_gpu and blk > 0 and self.B * per_batch > 2 * blk:
+        if self.fused:
+            self.lse = torch.empty(self.B, H, self.Sq, dtype=torch.float32, device=dev)
+            if ex.cfg.training:   # delta [B, H, Sq] followed by the fp32 dK / dV accumulators
+                ex.need_scratch(4 * (self.B * H * self.Sq + 4 + K.attention_bwd_scratch_floats(self.B, H, self.Sk, kd)))
+        elif ex.on_gpu and blk > 0 and self.B * per_batch > 2 * blk:
             if per_batch <= blk:
                 self.cb = max(1, min(self.B, blk // per_batch))
             else:  # one batch element at a time, a group of heads per block
@@ -417,7 +427,7 @@ class AttentionOp(OpImpl):
                 self.hb = max(1, min(H, (H * blk) // per_batch))
                 while H % self.hb:
                     self.hb -= 1
-        self.probs = torch.empty(self.B if not self.cb else 0, H, self.Sq, self.Sk, dtype=cdt, device=dev)
+        self.probs = torch.empty(self.B if not (self.cb or self.fused) else 0, H, self.Sq, self.Sk, dtype=cdt, device=dev)
         self.ctx = torch.empty(self.B * self.Sq, H * vd, dtype=dt, device=dev)
         if not self.core16:
             self.c_ctx = self.ctx
@@ -435,11 +445,11 @@ class AttentionOp(OpImpl):
         # score-sized tensor per layer and saves regenerating them (a read and a write of that tensor); it is
         # done while plenty of device memory is free, otherwise they are rebuilt in a shared scratch buffer.
         self.kept_p = None
-        if not self.cb and self.p_drop > 0 and ex.cfg.training and ex.on_gpu and ex.cfg.keep_dropped_probs:
+        if not self.cb and not self.fused and self.p_drop > 0 and ex.cfg.training and ex.on_gpu and ex.cfg.keep_dropped_probs:
             free, _total = torch.cuda.mem_get_info(ex.device)
             if free > 8 * nbytes + (40 << 30):
                 self.kept_p = torch.empty_like(self.probs)
-        if not self.cb:
+        if not self.cb and not self.fused:
             ex.need_big_scratch(nbytes, 2 if (self.p_drop > 0 and self.kept_p is None) else 1)
         ex.need_scratch(4 * K.bias_act_bwd_scratch(self.B * self.Sq, max(self.ldqkv, self.embed)) if ex.on_gpu else 0)
         if ex.cfg.training and ex.wgrad_splits(self.B * self.Sq, self.embed, self.H * self.vd, torch.bfloat16):
@@ -550,6 +560,10 @@ class AttentionOp(OpImpl):
                 K.cast(self.qkv, self.c_qkv)
             else:
                 K.cast(self.qv, self.c_q); K.cast(self.kv, self.c_k); K.cast(self.vv, self.c_v)
+        if self.fused:
+            K.attention_fwd(self.c_q, self.c_k, self.c_v, self.c_ctx, self.lse, B=self.B, H=H, Sq=Sq, Sk=Sk, D=kd, scale=self.alpha,
+                            causal=self.ex.cfg.causal_attention, dropout=self._fused_dropout())
+            return self._forward_out()
         if self.cb:
             self._forward_core_blocked()
             return self._forward_out()
@@ -571,6 +585,9 @@ class AttentionOp(OpImpl):
         self._bg(Sq, vd, Sk, p, Sk, Sq * Sk, H * Sq * Sk, False, self.c_v, self.ldv, vd, Sk * self.ldv, True,
                  self.c_ctx, H * vd, vd, Sq * H * vd)
         self._forward_out()
+
+    def _fused_dropout(self):
+        return (self.p_drop, self.salt, self.ex.seed_tensor) if self.p_drop > 0 else None
 
     def _forward_out(self):
         if self.core16:
@@ -600,6 +617,14 @@ class AttentionOp(OpImpl):
             K.matmul_nn(dy, self.wo, out=self.dctx)
         if self.core16:
             K.cast(self.dctx, self.c_dctx)
+        if self.fused:
+            n_stat = self.B * H * Sq
+            n_stat += (-n_stat) % 4   # keeps the accumulators 16-byte aligned
+            scratch = ex.scratch_f32()
+            K.attention_bwd(self.c_q, self.c_k, self.c_v, self.c_ctx, self.lse, self.c_dctx, self.c_dq, self.c_dk, self.c_dv,
+                            scratch[:n_stat], scratch[n_stat:], B=self.B, H=H, Sq=Sq, Sk=Sk, D=kd, scale=self.alpha,
+                            causal=ex.cfg.causal_attention, dropout=self._fused_dropout())
+            return self._backward_projections(wg, accw, n_q, n_k, n_v)
         if self.cb:
             self._backward_core_blocked()
             return self._backward_projections(wg, accw, n_q, n_k, n_v)

@@ -173,7 +173,10 @@ def test_single_convolution_matches_oracle(k, s, p, cin, cout):
     rows_ref, grads_ref = oracle.loss_and_grads({"input": xin}, labels)
     assert rel(ex.loss_rows, rows_ref) < 3e-2
     for name, g_ in ex.named_gradients():
-        assert rel(g_, grads_ref[name]) < 8e-2, (name, rel(g_, grads_ref[name]))
+        # a bias gradient is a sum of thousands of bf16-rounded activation gradients of both signs: its relative
+        # error is several times that of the weight gradients
+        tol = 0.25 if name.endswith(".bias") else 8e-2
+        assert rel(g_, grads_ref[name]) < tol, (name, rel(g_, grads_ref[name]))
     assert K.gemm_last_error() == 0
 
 
