@@ -382,42 +382,60 @@ std::optional<SPTree> get_series_parallel_decomposition(const DiGraph &g_in) {
     for (int t : kv.first)
       if (g.predecessors(t) != heads[kv.second]) return std::nullopt;
 
+  // Series and parallel reductions of the two-terminal multigraph, driven by a work list: a junction with one edge in and
+  // one edge out is spliced away; two edges between the same pair of junctions merge into one.  Labels are moved, never
+  // copied, so the whole reduction is near linear in the number of operators.
   struct Edge { int u, v; SPTree label; bool alive; };
   std::vector<Edge> edges;
+  std::map<int, std::set<size_t>> in_e, out_e;
+  std::map<std::pair<int, int>, size_t> between;  // the one alive edge between a pair of junctions
+  std::vector<int> work;
+  std::function<void(Edge)> add_edge = [&](Edge e) {
+    auto key = std::make_pair(e.u, e.v);
+    auto it = between.find(key);
+    if (it != between.end()) {  // parallel reduction with the edge already there
+      Edge &o = edges[it->second];
+      std::vector<SPTree> cs;
+      cs.push_back(std::move(o.label));
+      cs.push_back(std::move(e.label));
+      o.label = SPTree::parallel(std::move(cs));
+      work.push_back(e.u);
+      work.push_back(e.v);
+      return;
+    }
+    const size_t id = edges.size();
+    edges.push_back(std::move(e));
+    between[key] = id;
+    in_e[edges[id].v].insert(id);
+    out_e[edges[id].u].insert(id);
+    work.push_back(edges[id].u);
+    work.push_back(edges[id].v);
+  };
   for (int n : g.nodes()) {
     int u = g.predecessors(n).empty() ? SRC : junction_of_succset[g.successors(*g.predecessors(n).begin())];
     int v = g.successors(n).empty() ? SNK : junction_of_succset[g.successors(n)];
-    edges.push_back({u, v, SPTree::leaf(n), true});
+    add_edge({u, v, SPTree::leaf(n), true});
   }
-  bool changed = true;
-  while (changed) {
-    changed = false;
-    // parallel reduction
-    std::map<std::pair<int, int>, std::vector<size_t>> groups;
-    for (size_t i = 0; i < edges.size(); ++i) if (edges[i].alive) groups[{edges[i].u, edges[i].v}].push_back(i);
-    for (auto &kv : groups) {
-      if (kv.second.size() < 2) continue;
-      std::vector<SPTree> cs;
-      for (size_t i : kv.second) { cs.push_back(edges[i].label); edges[i].alive = false; }
-      edges.push_back({kv.first.first, kv.first.second, SPTree::parallel(cs), true});
-      changed = true;
+  while (!work.empty()) {
+    const int v = work.back();
+    work.pop_back();
+    if (v == SRC || v == SNK) continue;
+    auto ii = in_e.find(v), oi = out_e.find(v);
+    if (ii == in_e.end() || oi == out_e.end() || ii->second.size() != 1 || oi->second.size() != 1) continue;
+    const size_t a = *ii->second.begin(), b = *oi->second.begin();
+    if (a == b) continue;
+    Edge ne{edges[a].u, edges[b].v, SPTree(), true};
+    std::vector<SPTree> cs;
+    cs.push_back(std::move(edges[a].label));
+    cs.push_back(std::move(edges[b].label));
+    ne.label = SPTree::series(std::move(cs));
+    for (size_t dead : {a, b}) {
+      edges[dead].alive = false;
+      in_e[edges[dead].v].erase(dead);
+      out_e[edges[dead].u].erase(dead);
+      between.erase({edges[dead].u, edges[dead].v});
     }
-    // series reduction
-    std::map<int, std::vector<size_t>> in_e, out_e;
-    for (size_t i = 0; i < edges.size(); ++i) if (edges[i].alive) { in_e[edges[i].v].push_back(i); out_e[edges[i].u].push_back(i); }
-    for (auto &kv : in_e) {
-      int v = kv.first;
-      if (v == SRC || v == SNK) continue;
-      if (kv.second.size() == 1 && out_e[v].size() == 1) {
-        size_t a = kv.second[0], b = out_e[v][0];
-        if (!edges[a].alive || !edges[b].alive || a == b) continue;
-        Edge ne{edges[a].u, edges[b].v, SPTree::series({edges[a].label, edges[b].label}), true};
-        edges[a].alive = edges[b].alive = false;
-        edges.push_back(ne);
-        changed = true;
-        break;  // indices into in_e/out_e are stale now
-      }
-    }
+    add_edge(std::move(ne));
   }
   std::vector<size_t> alive;
   for (size_t i = 0; i < edges.size(); ++i) if (edges[i].alive) alive.push_back(i);

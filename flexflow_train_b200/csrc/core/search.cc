@@ -351,19 +351,60 @@ void prune(Front &f, int max_front) {
   f.swap(out);
 }
 
+// 64-bit mixing for structural hashes
+inline uint64_t mix64(uint64_t h, uint64_t v) {
+  h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+  h *= 0xBF58476D1CE4E5B9ull;
+  return h ^ (h >> 29);
+}
+inline uint64_t hash_str(const std::string &s) {
+  uint64_t h = 1469598103934665603ull;
+  for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+  return h;
+}
+
+// One sub-problem of the DP: a subtree of the binary SP tree with its leaves and a hash of everything inside it that
+// the result depends on (operator cost keys, task spaces, the edges between its leaves).  Two subtrees with the same
+// hash -- in this graph or in another candidate of the same search whose rewritten region lies elsewhere -- are the same
+// sub-problem, which is what lets the cache survive from one candidate to the next
+// (compiler/machine_mapping/machine_mapping_cache.cc keys its table by the problem tree in the same way).
+struct Sub {
+  SPTree::Kind kind = SPTree::Leaf;
+  int node = -1;
+  int left = -1, right = -1;
+  std::vector<int> leaves;  // sorted
+  uint64_t hash = 0;
+  double work_ms = 0;  // sum of the operators' forward + backward times
+};
+
 struct DP {
   const Graph &g;
   const MachineSpec &m;
   const CostEstimator &est;
   int max_front;
+  MachineMappingCache &cache;
   std::map<NodeId, OpCost> cost_cache;
   std::map<NodeId, std::vector<int>> task_cache;
-  // memo key: (tree node pointer, resources, fixed views of leaves inside the subtree)
-  std::map<std::string, Front> memo;
+  std::map<NodeId, uint64_t> node_hash;
+  std::vector<Sub> subs;
+  // operators that are not leaves of the tree but ride along with one that is: a weight or input with its chain of
+  // parallel operators is placed with (and its time and memory are added to) the operator that consumes it
+  std::map<NodeId, std::vector<NodeId>> attached;
 
   const OpCost &cost(NodeId n) {
     auto it = cost_cache.find(n);
-    if (it == cost_cache.end()) it = cost_cache.emplace(n, est.op_cost(g.node(n), g)).first;
+    if (it == cost_cache.end()) {
+      OpCost c = est.op_cost(g.node(n), g);
+      auto at = attached.find(n);
+      if (at != attached.end())
+        for (NodeId a : at->second) {
+          OpCost ca = est.op_cost(g.node(a), g);
+          c.fwd_ms += ca.fwd_ms;
+          c.bwd_ms += ca.bwd_ms;
+          c.memory_bytes += ca.memory_bytes;
+        }
+      it = cost_cache.emplace(n, c).first;
+    }
     return it->second;
   }
   const std::vector<int> &tasks(NodeId n) {
@@ -371,33 +412,122 @@ struct DP {
     if (it == task_cache.end()) it = task_cache.emplace(n, operator_task_space(g.node(n), g)).first;
     return it->second;
   }
-  static void leaves(const SPTree &t, std::set<int> &out) {
-    if (t.kind == SPTree::Leaf) out.insert(t.node);
-    else for (auto &c : t.children) leaves(c, out);
+  uint64_t hash_of_node(NodeId n) {
+    auto it = node_hash.find(n);
+    if (it != node_hash.end()) return it->second;
+    const Node &nd = g.node(n);
+    uint64_t h = mix64(hash_str(CostEstimator::op_cost_key(nd, g)), (uint64_t)n);
+    for (auto &o : nd.outputs) h = mix64(h, hash_str(o.shape.str()));
+    for (auto &e : nd.inputs) h = mix64(h, ((uint64_t)e.src.node << 8) ^ (uint64_t)e.src.slot);
+    auto at = attached.find(n);
+    if (at != attached.end())
+      for (NodeId a : at->second) h = mix64(h, mix64(hash_str(CostEstimator::op_cost_key(g.node(a), g)), (uint64_t)a));
+    return node_hash[n] = h;
   }
-  // cost of moving the tensors on edges a->b when the two operators sit on different device sets
+  int add_leaf(int node) {
+    Sub s;
+    s.kind = SPTree::Leaf;
+    s.node = node;
+    s.leaves = {node};
+    s.hash = mix64(0x1111, hash_of_node(node));
+    s.work_ms = cost(node).total_ms();
+    subs.push_back(std::move(s));
+    return (int)subs.size() - 1;
+  }
+  int add_pair(SPTree::Kind kind, int li, int ri) {
+    Sub s;
+    s.kind = kind;
+    s.left = li;
+    s.right = ri;
+    const Sub &l = subs[(size_t)li], &r = subs[(size_t)ri];
+    s.leaves.resize(l.leaves.size() + r.leaves.size());
+    std::merge(l.leaves.begin(), l.leaves.end(), r.leaves.begin(), r.leaves.end(), s.leaves.begin());
+    s.hash = mix64(mix64(kind == SPTree::Series ? 0x2222 : 0x3333, l.hash), r.hash);
+    s.work_ms = l.work_ms + r.work_ms;
+    subs.push_back(std::move(s));
+    return (int)subs.size() - 1;
+  }
+  // Binary grouping of the children [lo, hi) of an n-ary node.  The cut goes where the hash of the two neighbouring
+  // children is smallest, so the shape of the grouping depends only on what the children are, never on how many there
+  // are or where a rewrite happened: after a substitution every group that does not contain a rewritten operator is
+  // the same sub-problem as before (same hash) and comes out of the cache.  Expected depth is logarithmic.
+  int group(SPTree::Kind kind, const std::vector<int> &kids, size_t lo, size_t hi) {
+    if (hi - lo == 1) return kids[lo];
+    size_t cut = lo + 1;
+    uint64_t best = ~0ull;
+    for (size_t i = lo + 1; i < hi; ++i) {
+      const uint64_t pr = mix64(subs[(size_t)kids[i - 1]].hash, subs[(size_t)kids[i]].hash);
+      if (pr < best) { best = pr; cut = i; }
+    }
+    const int l = group(kind, kids, lo, cut), r = group(kind, kids, cut, hi);
+    return add_pair(kind, l, r);
+  }
+  int annotate(const SPTree &t) {
+    if (t.kind == SPTree::Leaf) return add_leaf(t.node);
+    std::vector<int> kids;
+    for (auto &c : t.children) kids.push_back(annotate(c));
+    if (t.kind == SPTree::Parallel)  // branches in a canonical order
+      std::sort(kids.begin(), kids.end(), [&](int a, int b) { return subs[(size_t)a].hash < subs[(size_t)b].hash; });
+    return group(t.kind, kids, 0, kids.size());
+  }
+  static bool has(const std::vector<int> &sorted, int v) { return std::binary_search(sorted.begin(), sorted.end(), v); }
+
+  // Cost of the tensors on edges a -> b.  Nothing moves when b's devices all hold what a produced (same device set, or a
+  // subset of it); otherwise the pieces that travel are worked out from the two operators' shard mappings
+  // (get_tensor_set_movement) where both have one, and priced as whole pieces otherwise.  Forward activation and
+  // backward gradient both cross the edge.
   double movement(NodeId a, const MachineView &va, NodeId b, const MachineView &vb) {
     std::vector<int> da = view_devices(va, tasks(a), m), db = view_devices(vb, tasks(b), m);
     std::sort(da.begin(), da.end());
     std::sort(db.begin(), db.end());
-    // an unsharded tensor is present on every device of the (single-node) job: no movement
     if (da == db) return 0.0;
     if (std::includes(da.begin(), da.end(), db.begin(), db.end())) return 0.0;
-    double bytes = 0;
-    for (auto &e : g.node(b).inputs)
-      if (e.src.node == a) bytes += (double)g.shape(e.src).piece_bytes();
-    bool inter = (da.front() / m.num_gpus_per_node) != (db.front() / m.num_gpus_per_node);
-    return 2.0 * est.movement_cost_ms(bytes, inter);  // forward activation + backward gradient
+    std::string key = std::to_string(hash_of_node(a)) + va.str() + ">" + std::to_string(hash_of_node(b)) + vb.str();
+    auto it = cache.movement.find(key);
+    if (it != cache.movement.end()) return it->second;
+    double c;
+    try {
+      c = 2.0 * tensor_set_movement_cost_ms(get_tensor_set_movement(g, a, va, b, vb, m), m, est);
+    } catch (const std::exception &) {
+      double bytes = 0;
+      for (auto &e : g.node(b).inputs)
+        if (e.src.node == a) bytes += (double)g.shape(e.src).piece_bytes();
+      bool inter = (da.front() / m.num_gpus_per_node) != (db.front() / m.num_gpus_per_node);
+      c = 2.0 * est.movement_cost_ms(bytes, inter);
+    }
+    return cache.movement[key] = c;
   }
 
-  Front solve(const SPTree &t, Resources r, const std::map<NodeId, MachineView> &fixed) {
-    std::set<int> ls;
-    leaves(t, ls);
-    std::string key = std::to_string((uintptr_t)&t) + "@" + std::to_string(r.start) + "+" + std::to_string(r.count);
+  // Views a boundary layer is tried at inside `r`.  On one node of a switch-connected machine any two placements that
+  // differ by a permutation of the devices cost the same, so it is enough to distinguish "at the start of the slice"
+  // from "at the start of its second half" (the two sides a resource split can give to parallel branches); machines
+  // with several nodes keep every aligned start, because crossing a node boundary changes the bandwidth.
+  std::vector<MachineView> boundary_views(NodeId n, const Resources &r) {
+    std::vector<MachineView> all = allowed_machine_views(tasks(n), r, m);
+    if (m.num_nodes > 1 || all.size() <= 2) return all;
+    int count = 1;
+    for (int d : tasks(n)) count *= d;
+    std::vector<MachineView> out;
+    const int half = r.start + r.count / 2;
+    for (auto &v : all) {
+      const int start = v.start_node * m.num_gpus_per_node + v.start_device;
+      if (start == r.start || (start == half && count <= r.count / 2)) out.push_back(v);
+    }
+    return out.empty() ? all : out;
+  }
+
+  Front solve(int si, Resources r, const std::map<NodeId, MachineView> &fixed) {
+    const Sub &sub = subs[(size_t)si];
+    struct { SPTree::Kind kind; int node; } t{sub.kind, sub.node};
+    std::string key = std::to_string(sub.hash) + "@" + std::to_string(r.start) + "+" + std::to_string(r.count) + "/" + std::to_string(max_front);
     for (auto &kv : fixed)
-      if (ls.count(kv.first)) key += ";" + std::to_string(kv.first) + kv.second.str();
-    auto it = memo.find(key);
-    if (it != memo.end()) return it->second;
+      if (has(sub.leaves, kv.first)) key += ";" + std::to_string(kv.first) + kv.second.str();
+    auto it = cache.table.find(key);
+    if (it != cache.table.end()) {
+      ++cache.hits;
+      return it->second;
+    }
+    ++cache.misses;
     Front res;
     if (t.kind == SPTree::Leaf) {
       const OpCost &c = cost(t.node);
@@ -419,15 +549,12 @@ struct DP {
         res.push_back(p);
       }
     } else if (t.kind == SPTree::Series) {
-      const SPTree &l = t.children[0], &rt = t.children[1];
-      std::set<int> ll, rl;
-      leaves(l, ll);
-      leaves(rt, rl);
+      const Sub &l = subs[(size_t)sub.left], &rt = subs[(size_t)sub.right];
       // boundary: producers in the left subtree with consumers in the right subtree
       std::vector<std::pair<NodeId, NodeId>> edges;
-      for (int b : rl)
+      for (int b : rt.leaves)
         for (auto &e : g.node(b).inputs)
-          if (ll.count(e.src.node)) edges.push_back({e.src.node, b});
+          if (has(l.leaves, e.src.node)) edges.push_back({e.src.node, b});
       // The transfer cost across the split depends on the views of the boundary layers, so those views are
       // enumerated here and imposed on both sub-problems as constraints (get_optimal_machine_mapping.cc:162-210).
       std::vector<NodeId> boundary;
@@ -438,22 +565,26 @@ struct DP {
       std::vector<std::vector<MachineView>> options;
       size_t combos = 1;
       for (NodeId n : boundary) {
-        options.push_back(allowed_machine_views(tasks(n), r, m));
+        options.push_back(boundary_views(n, r));
         if (options.back().empty()) { combos = 0; break; }
         combos *= options.back().size();
       }
-      if (combos > 256) {  // very wide boundaries: fall back to the lowest-start view of each layer
+      if (combos > 256) {  // very wide boundaries: the lowest-start view of each layer (counted, so a caller can tell)
         for (auto &o : options) o.resize(1);
         combos = 1;
+        ++cache.truncated_boundaries;
       }
       for (size_t ci = 0; ci < combos; ++ci) {
-        std::map<NodeId, MachineView> fx = fixed;
+        std::map<NodeId, MachineView> fx;
+        // only constraints on leaves of this subtree matter below
+        for (auto &kv : fixed)
+          if (has(sub.leaves, kv.first)) fx.insert(kv);
         size_t rem = ci;
         for (size_t bi = 0; bi < boundary.size(); ++bi) {
           fx[boundary[bi]] = options[bi][rem % options[bi].size()];
           rem /= options[bi].size();
         }
-        Front fl = solve(l, r, fx), fr = solve(rt, r, fx);
+        Front fl = solve(sub.left, r, fx), fr = solve(sub.right, r, fx);
         for (auto &a : fl)
           for (auto &b : fr) {
             MappingPoint p;
@@ -467,9 +598,8 @@ struct DP {
           }
       }
     } else {
-      const SPTree &l = t.children[0], &rt = t.children[1];
       // (a) run the branches one after the other on all resources
-      Front fl = solve(l, r, fixed), fr = solve(rt, r, fixed);
+      Front fl = solve(sub.left, r, fixed), fr = solve(sub.right, r, fixed);
       for (auto &a : fl)
         for (auto &b : fr) {
           MappingPoint p;
@@ -479,11 +609,12 @@ struct DP {
           p.views.insert(b.views.begin(), b.views.end());
           res.push_back(p);
         }
-      // (b) split the resources (power-of-two halves) and run the branches side by side
-      if (r.count >= 2 && r.count % 2 == 0) {
+      // (b) split the resources (power-of-two halves) and run the branches side by side; a branch without work (weights,
+      // inputs, a residual connection) gains nothing from devices of its own
+      if (r.count >= 2 && r.count % 2 == 0 && subs[(size_t)sub.left].work_ms > 0 && subs[(size_t)sub.right].work_ms > 0) {
         Resources r1{r.start, r.count / 2}, r2{r.start + r.count / 2, r.count / 2};
         for (int swap = 0; swap < 2; ++swap) {
-          Front a_ = solve(l, swap ? r2 : r1, fixed), b_ = solve(rt, swap ? r1 : r2, fixed);
+          Front a_ = solve(sub.left, swap ? r2 : r1, fixed), b_ = solve(sub.right, swap ? r1 : r2, fixed);
           for (auto &a : a_)
             for (auto &b : b_) {
               MappingPoint p;
@@ -497,19 +628,29 @@ struct DP {
       }
     }
     prune(res, max_front);
-    memo[key] = res;
+    cache.table[key] = res;
     return res;
   }
 };
 }  // namespace
 
 MachineMappingResult get_optimal_machine_mapping(const Graph &pcg, const SPTree &binary_tree, const MachineSpec &m, const CostEstimator &est,
-                                                 int max_front) {
-  if (!sp_is_binary(binary_tree)) throw Error("machine mapping needs a binary SP tree");
-  DP dp{pcg, m, est, std::max(1, max_front)};
+                                                 int max_front, MachineMappingCache *cache) {
+  MachineMappingCache local;
+  DP dp{pcg, m, est, std::max(1, max_front), cache ? *cache : local};
+  const int root = dp.annotate(binary_tree);
   MachineMappingResult r;
-  r.front = dp.solve(binary_tree, Resources{0, m.num_devices()}, {});
+  r.front = dp.solve(root, Resources{0, m.num_devices()}, {});
   return r;
+}
+
+std::vector<std::pair<uint64_t, int>> debug_sub_hashes(const Graph &pcg, const MachineSpec &m, const CostEstimator &est) {
+  MachineMappingCache local;
+  DP dp{pcg, m, est, 1, local};
+  dp.annotate(normalize_sp(get_graph_sp_decomposition(pcg)));
+  std::vector<std::pair<uint64_t, int>> out;
+  for (auto &s : dp.subs) out.push_back({s.hash, (int)s.leaves.size()});
+  return out;
 }
 
 Graph mapped_pcg_from_pcg_and_mapping(const Graph &pcg, const std::map<NodeId, MachineView> &mapping) {
@@ -519,18 +660,81 @@ Graph mapped_pcg_from_pcg_and_mapping(const Graph &pcg, const std::map<NodeId, M
   return g;
 }
 
-SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est) {
+// Weights and inputs, each with the parallel operators that follow it in a chain, as {chain nodes} -> consumer.
+// A chain whose end feeds several operators belongs to the first of them in topological order.
+static std::map<NodeId, std::vector<NodeId>> source_chains(const Graph &g) {
+  std::map<NodeId, int> topo_pos;
+  int i = 0;
+  for (NodeId n : g.topological_order()) topo_pos[n] = i++;
+  std::map<NodeId, std::vector<NodeId>> by_consumer;
+  for (auto &kv : g.nodes()) {
+    if (kv.second.type != OpType::WEIGHT && kv.second.type != OpType::INPUT) continue;
+    std::vector<NodeId> chain{kv.first};
+    NodeId cur = kv.first;
+    while (true) {
+      auto succ = g.successors(cur);
+      if (succ.size() == 1 && is_parallel_op(g.node(succ[0]).type) && g.predecessors(succ[0]).size() == 1) {
+        cur = succ[0];
+        chain.push_back(cur);
+      } else break;
+    }
+    auto succ = g.successors(cur);
+    if (succ.empty()) continue;  // an unused source stays a leaf of its own
+    NodeId consumer = succ[0];
+    for (NodeId c : succ)
+      if (topo_pos[c] < topo_pos[consumer]) consumer = c;
+    auto &v = by_consumer[consumer];
+    v.insert(v.end(), chain.begin(), chain.end());
+  }
+  // a consumer that is itself part of a chain cannot happen (chains end where a non-parallel operator or a join begins)
+  return by_consumer;
+}
+
+SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est, MachineMappingCache *cache) {
   SearchResult r;
   r.pcg = pcg;
-  SPTree tree = balanced_binary_sp_tree(get_graph_sp_decomposition(pcg));
-  MachineMappingResult mm = get_optimal_machine_mapping(pcg, tree, m, est, 1);
-  if (!mm.feasible()) {
+  // The tree the DP works on holds the computation only.  Sources (weights, inputs and the parallel operators chained to
+  // them) are placed with their consumers: as branches of the SP tree they would nest the whole graph one level deeper
+  // per weight, and a rewrite anywhere would change every enclosing sub-problem.
+  std::map<NodeId, std::vector<NodeId>> attached = source_chains(pcg);
+  std::set<NodeId> riding;
+  for (auto &kv : attached) riding.insert(kv.second.begin(), kv.second.end());
+  DiGraph d;
+  for (auto &kv : pcg.nodes()) {
+    if (riding.count(kv.first)) continue;
+    d.add_node(kv.first);
+    for (auto &e : kv.second.inputs)
+      if (!riding.count(e.src.node)) d.add_edge(e.src.node, kv.first);
+  }
+  SPTree tree;
+  if (auto t = get_series_parallel_decomposition(d)) tree = normalize_sp(*t);
+  else tree = normalize_sp(escribano_sp_ization(d));
+  MachineMappingCache local;
+  DP dp{pcg, m, est, 1, cache ? *cache : local};
+  dp.attached = attached;
+  const int root = dp.annotate(tree);
+  Front front = dp.solve(root, Resources{0, m.num_devices()}, {});
+  if (front.empty()) {
     r.runtime_ms = std::numeric_limits<double>::infinity();
     return r;
   }
-  r.mapping = mm.best_runtime().views;
-  r.runtime_ms = mm.best_runtime().runtime_ms;
-  r.memory_bytes = mm.best_runtime().memory_bytes;
+  const MappingPoint &best = front.front();
+  r.mapping = best.views;
+  r.runtime_ms = best.runtime_ms;
+  r.memory_bytes = best.memory_bytes;
+  // sources sit on the devices of their consumer: the first allowed view inside the consumer's device range
+  for (auto &kv : attached) {
+    auto cv = r.mapping.find(kv.first);
+    if (cv == r.mapping.end()) continue;
+    std::vector<int> devs = view_devices(cv->second, operator_task_space(pcg.node(kv.first), pcg), m);
+    const int lo = *std::min_element(devs.begin(), devs.end()), hi = *std::max_element(devs.begin(), devs.end());
+    for (NodeId a : kv.second) {
+      const std::vector<int> ts = operator_task_space(pcg.node(a), pcg);
+      auto vs = allowed_machine_views(ts, Resources{lo, hi - lo + 1}, m);
+      if (vs.empty()) vs = allowed_machine_views(ts, Resources{0, m.num_devices()}, m);
+      if (!vs.empty()) r.mapping[a] = vs.front();
+    }
+  }
   return r;
 }
 
@@ -578,7 +782,8 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
   };
   std::priority_queue<State> queue;
   std::set<std::string> seen;
-  SearchResult best = evaluate_pcg(start, m, est);
+  MachineMappingCache cache;  // shared by every candidate: only the sub-problems around a rewritten region are solved anew
+  SearchResult best = evaluate_pcg(start, m, est, &cache);
   queue.push({best.runtime_ms, start});
   seen.insert(start.signature());
   long long evaluated = 1, generated = 0;
@@ -589,22 +794,42 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
     queue.pop();
     if (cur.cost > cfg.alpha * best.runtime_ms) continue;
     int candidates = 0;
+    auto consider = [&](const Graph &ng, bool keep_anyway) {
+      ++generated;
+      if ((int)ng.num_nodes() > cfg.max_num_ops) return;
+      if (!seen.insert(ng.signature()).second) return;
+      ++candidates;
+      SearchResult r = evaluate_pcg(ng, m, est, &cache);
+      ++evaluated;
+      if (r.runtime_ms < best.runtime_ms) best = r;
+      if (keep_anyway ? std::isfinite(r.runtime_ms) : r.runtime_ms <= cfg.alpha * best.runtime_ms) queue.push({r.runtime_ms, ng});
+    };
     for (auto &rule : rules) {
       if (candidates >= cfg.max_candidates_per_step || elapsed() > cfg.time_limit_s) break;
-      for (auto &mt : find_pattern_matches(rule.pattern, cur.g)) {
-        if (candidates >= cfg.max_candidates_per_step) break;
-        auto ng = apply_substitution(cur.g, rule, mt);
-        if (!ng) continue;
-        ++generated;
-        if ((int)ng->num_nodes() > cfg.max_num_ops) continue;
-        std::string sig = ng->signature();
-        if (!seen.insert(sig).second) continue;
-        ++candidates;
-        SearchResult r = evaluate_pcg(*ng, m, est);
-        ++evaluated;
-        if (r.runtime_ms < best.runtime_ms) best = r;
-        if (r.runtime_ms <= cfg.alpha * best.runtime_ms) queue.push({r.runtime_ms, *ng});
+      auto matches = find_pattern_matches(rule.pattern, cur.g);
+      if (matches.empty()) continue;
+      // Compound move: the rule applied at every place it matches.  A data- or tensor-parallel plan differs from the
+      // serial graph by one rule application per operator, and each of them alone makes the graph slower (a Repartition
+      // and a Combine around one operator) until its neighbours follow and the pairs cancel; as one move the whole step
+      // is a single candidate, so the search can cross that ridge.  Such a candidate stays in the queue even when it is
+      // outside the alpha band: its value shows only after the cancellation rules have been applied to it.
+      if (cfg.compound_moves && matches.size() > 1) {
+        std::vector<Substitution> one{rule};
+        Graph all = apply_rules_exhaustively(cur.g, one, 100000, m.num_devices());
+        if (cfg.cancel_after_compound && !cfg.cleanup_rules.empty()) {
+          std::vector<Substitution> cl;
+          for (int ci : cfg.cleanup_rules) cl.push_back(rules.at((size_t)ci));
+          all = apply_rules_exhaustively(all, cl, 100000, m.num_devices());
+        }
+        consider(all, true);
       }
+      if (cfg.single_moves)
+        for (auto &mt : matches) {
+          if (candidates >= cfg.max_candidates_per_step || elapsed() > cfg.time_limit_s) break;
+          auto ng = apply_substitution(cur.g, rule, mt);
+          if (!ng) continue;
+          consider(*ng, false);
+        }
     }
   }
   best.stats = Json::object();
@@ -613,6 +838,9 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
   best.stats["generated"] = generated;
   best.stats["seconds"] = elapsed();
   best.stats["cost_queries"] = est.num_queries;
+  best.stats["cache_hits"] = cache.hits;
+  best.stats["cache_misses"] = cache.misses;
+  best.stats["truncated_boundaries"] = cache.truncated_boundaries;
   return best;
 }
 
@@ -696,6 +924,9 @@ SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEst
   best.mapping = cur_map;
   best.runtime_ms = cur_cost;
   int accepted = 0, substitutions = 0;
+  // relative: the temperature is a fraction of the starting cost, so that "a candidate 1 % worse" means the same
+  // whether a step takes 3 ms or 300 ms; absolute: the reference's exp(-delta / temperature) with delta in ms
+  const double temperature = cfg.relative_temperature ? cfg.temperature * std::max(cur_cost, 1e-9) : cfg.temperature;
   for (int it = 0; it < cfg.num_iterations; ++it) {
     Graph cand = cur;
     auto cand_map = cur_map;
@@ -729,7 +960,7 @@ SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEst
       cand_map[n] = vs[rng() % vs.size()];
     }
     double c = score(cand, cand_map);
-    double accept_p = c <= cur_cost ? 1.0 : std::exp(-(c - cur_cost) / std::max(1e-9, cfg.temperature));
+    double accept_p = c <= cur_cost ? 1.0 : std::exp(-(c - cur_cost) / std::max(1e-12, temperature));
     if (uni(rng) < accept_p) {
       cur = cand;
       cur_map = cand_map;
@@ -828,27 +1059,33 @@ void bind_search(py::module &m) {
     return pts;
   }, py::arg("pcg"), py::arg("tree") = py::none(), py::arg("machine") = MachineSpec(), py::arg("estimator") = CostEstimator(),
         py::arg("max_front") = 1);
+  m.def("debug_sub_hashes", &debug_sub_hashes);
   m.def("evaluate_pcg", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est) { return result_to_py(evaluate_pcg(g, ms, est)); });
   m.def("apply_rules_exhaustively", [](const Graph &g, std::vector<Substitution> rules, int max_app, int max_deg) {
     return apply_rules_exhaustively(g, rules, max_app, max_deg);
   }, py::arg("graph"), py::arg("rules"), py::arg("max_applications") = 100000, py::arg("max_total_degree") = 0);
   m.def("unity_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double alpha,
-                           int budget, int max_num_ops, double time_limit_s) {
+                           int budget, int max_num_ops, double time_limit_s, bool compound_moves, bool single_moves) {
     UnityConfig c;
     c.alpha = alpha; c.budget = budget; c.max_num_ops = max_num_ops; c.time_limit_s = time_limit_s;
+    c.compound_moves = compound_moves; c.single_moves = single_moves;
+    // rules that only remove parallel operators (a Combine meeting a Repartition and the like) tidy up after a compound move
+    for (size_t i = 0; i < rules.size(); ++i)
+      if (rules[i].name.rfind("cancel_", 0) == 0) c.cleanup_rules.push_back((int)i);
     py::gil_scoped_release rel;
     SearchResult r = unity_search(g, ms, est, rules, c);
     py::gil_scoped_acquire acq;
     return result_to_py(r);
   }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("alpha") = 1.05, py::arg("budget") = 10,
-        py::arg("max_num_ops") = 100000, py::arg("time_limit_s") = 120.0);
+        py::arg("max_num_ops") = 100000, py::arg("time_limit_s") = 120.0, py::arg("compound_moves") = true, py::arg("single_moves") = true);
   m.def("mcmc_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double temperature,
-                          int iters, double sub_freq, unsigned seed) {
+                          int iters, double sub_freq, unsigned seed, bool relative) {
     MCMCConfig c;
     c.temperature = temperature; c.num_iterations = iters; c.substitution_frequency = sub_freq; c.seed = seed;
+    c.relative_temperature = relative;
     return result_to_py(mcmc_search(g, ms, est, rules, c));
   }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("temperature") = 1.0, py::arg("num_iterations") = 100,
-        py::arg("substitution_frequency") = 0.2, py::arg("seed") = 0);
+        py::arg("substitution_frequency") = 0.2, py::arg("seed") = 0, py::arg("relative_temperature") = false);
   m.def("simulate_task_graph", &simulate_task_graph, py::arg("mapped_pcg"), py::arg("machine"), py::arg("estimator"),
         py::arg("include_backward") = false);
   m.def("mapped_pcg_from_pcg_and_mapping", [](const Graph &g, py::dict mapping) {

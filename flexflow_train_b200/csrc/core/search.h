@@ -90,8 +90,19 @@ struct MachineMappingResult {
 // (get_pcg_series_parallel_decomposition.cc:12-78); falls back to SP-ization when the graph is not SP.
 SPTree get_graph_sp_decomposition(const Graph &g, bool *exact = nullptr);
 
+// Results of DP sub-problems, keyed by a structural hash of the sub-problem (subtree content, resources, imposed views).
+// One cache may serve every candidate of a search: sub-problems outside the region a substitution rewrote hash the same
+// and are not solved again (compiler/machine_mapping/machine_mapping_cache.cc).
+struct MachineMappingCache {
+  std::map<std::string, std::vector<MappingPoint>> table;
+  std::map<std::string, double> movement;  // priced tensor set movements by (producer, view, consumer, view)
+  long long hits = 0, misses = 0;
+  long long truncated_boundaries = 0;  // series splits whose boundary had more than 256 view combinations
+};
+
+// `tree`: any SP decomposition of `pcg`; nodes with more than two children are grouped into pairs internally.
 MachineMappingResult get_optimal_machine_mapping(const Graph &pcg, const SPTree &binary_tree, const MachineSpec &m,
-                                                 const CostEstimator &est, int max_front = 1);
+                                                 const CostEstimator &est, int max_front = 1, MachineMappingCache *cache = nullptr);
 
 struct SearchResult {
   Graph pcg;
@@ -108,8 +119,12 @@ struct UnityConfig {
   int max_num_ops = 100000;
   int max_candidates_per_step = 4000;
   double time_limit_s = 120.0;
+  bool single_moves = true;     // one candidate per (rule, match), as the reference does
+  bool compound_moves = true;   // plus one candidate per rule: that rule applied wherever it matches
+  bool cancel_after_compound = true;
+  std::vector<int> cleanup_rules;  // indices (into the rule list) of the rules applied exhaustively after a compound move
 };
-SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est);
+SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est, MachineMappingCache *cache = nullptr);
 SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
                           const UnityConfig &cfg);
 // apply every rule whose name passes `filter` wherever it matches, repeatedly, until nothing applies
@@ -121,6 +136,7 @@ struct MCMCConfig {
   int num_iterations = 100;
   double substitution_frequency = 0.2;
   unsigned seed = 0;
+  bool relative_temperature = false;  // temperature as a fraction of the starting cost instead of milliseconds
 };
 SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
                          const MCMCConfig &cfg);

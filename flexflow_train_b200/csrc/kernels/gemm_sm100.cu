@@ -101,13 +101,17 @@ struct GemmArgs {
 // A 128-byte swizzle row holds 128/ES elements, which is also the K extent of a
 // pipeline stage for K-major operands and the MN extent of one TMA box for
 // MN-major operands.
-template <int ES, int BN, bool A_MN, bool B_MN>
+// CTA2: a pair of CTAs (cluster of 2, tcgen05 cta_group::2) computes a 256 x BN tile: each CTA stages its own 128 rows of
+// A and its own BN / 2 rows of B, the even CTA issues the MMAs for both and each CTA drains the 128 x BN accumulator in its own
+// tensor memory.  Per SM and k-block this halves the B traffic into shared memory, which leaves room for a deeper ring.
+template <int ES, int BN, bool A_MN, bool B_MN, bool CTA2 = false>
 struct GemmCfg {
   static constexpr int ROW_ELEMS = 128 / ES;       // elements per 128-byte row
   static constexpr int BK = ROW_ELEMS;             // k extent per stage
   static constexpr int UMMA_K = 32 / ES;           // k per tcgen05.mma
+  static constexpr int BN_CTA = CTA2 ? BN / 2 : BN;  // rows of B staged by one CTA
   static constexpr int A_BYTES = BM * BK * ES;     // 16 KB
-  static constexpr int B_BYTES = BN * BK * ES;
+  static constexpr int B_BYTES = BN_CTA * BK * ES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (STAGE_BYTES <= 32768) ? 6 : (STAGE_BYTES <= 49152 ? 4 : 3);
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
@@ -124,7 +128,7 @@ struct GemmCfg {
                                     | ((ES == 2 ? 1u : 2u) << 7)               // A: bf16 / tf32
                                     | ((ES == 2 ? 1u : 2u) << 10)              // B
                                     | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16)
-                                    | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                    | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((CTA2 ? 2 * BM : BM) >> 4) << 24);
 };
 
 __device__ __forceinline__ float ld_aux(const void *p, long long i, int fp32) {
@@ -157,11 +161,17 @@ struct ScatterMaps {
   CUtensorMap m[8];
 };
 
-template <int ES, int BN, bool A_MN, bool B_MN>
+template <int ES, int BN, bool A_MN, bool B_MN, bool CTA2>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                   const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ ScatterMaps smaps, const GemmArgs p) {
-  using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
+  using Cfg = GemmCfg<ES, BN, A_MN, B_MN, CTA2>;
+  static_assert(!CTA2 || ES == 2, "CTA pairs are built for bf16 operands");
+  // worker = the unit that owns output tiles: a CTA, or a CTA pair (rank 0 = the CTA that issues the MMAs)
+  const uint32_t pair_rank = CTA2 ? cluster_ctarank() : 0u;
+  const unsigned worker = CTA2 ? blockIdx.x >> 1 : blockIdx.x;
+  const unsigned num_workers = CTA2 ? gridDim.x >> 1 : gridDim.x;
+  constexpr int TILE_M = CTA2 ? 2 * BM : BM;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to.
@@ -188,19 +198,27 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tmem_full[s], 1);
-      mbar_init(&tmem_empty[s], 8);
+      mbar_init(&tmem_empty[s], CTA2 ? 16 : 8);  // the epilogue warps of both CTAs of a pair report to the even CTA
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)Cfg::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CTA2) {  // the same warp of both CTAs allocates for the pair
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"((uint32_t)Cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"((uint32_t)Cfg::TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA2) cluster_sync_all();  // the partner's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -211,12 +229,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       uint32_t gate_seen = 0;
-      for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      for (long long item = worker; item < num_items && ok; item += num_workers) {
         const long long tile = item % p.num_tiles;
         const int kb0 = (int)(item / p.num_tiles) * p.kb_per_split;
         const int kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
         int mb, nb_, bh, bb;
         tile_coords(tile, p, mb, nb_, bh, bb);
+        const int a_row = mb * TILE_M + (int)pair_rank * BM;            // this CTA's 128 rows of A
+        const int b_row = nb_ * BN + (int)pair_rank * Cfg::BN_CTA;      // and its rows of B
         if (p.gate_flags) {
           // rows of this m-block come from rank src's push: wait (bounded) until its flag reaches this call's epoch
           const int src = (mb * BM) / p.gate_rows;
@@ -245,23 +265,42 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
           if (!ok) break;
-          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           uint32_t sa = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
           uint32_t sb = sa + Cfg::A_BYTES;
           int k0 = kb * Cfg::BK;
-          if constexpr (!A_MN) {
-            tma_load_4d(sa, &tmapA, &full_bar[stage], k0, mb * BM, bh, bb);
-          } else {
+          if constexpr (CTA2) {
+            // both CTAs' loads are counted on the even CTA's barrier, which expects the bytes of the whole pair
+            if (pair_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+            const uint32_t fb = mapa_u32(smem_u32(&full_bar[stage]), 0);
+            if constexpr (!A_MN) {
+              tma_load_4d_pair(sa, &tmapA, fb, k0, a_row, bh, bb);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM / Cfg::ROW_ELEMS; ++c)
-              tma_load_4d(sa + c * Cfg::BK * 128, &tmapA, &full_bar[stage], mb * BM + c * Cfg::ROW_ELEMS, k0, bh, bb);
-          }
-          if constexpr (!B_MN) {
-            tma_load_4d(sb, &tmapB, &full_bar[stage], k0, nb_ * BN, bh, bb);
-          } else {
+              for (int c = 0; c < BM / Cfg::ROW_ELEMS; ++c) tma_load_4d_pair(sa + c * Cfg::BK * 128, &tmapA, fb, a_row + c * Cfg::ROW_ELEMS, k0, bh, bb);
+            }
+            if constexpr (!B_MN) {
+              tma_load_4d_pair(sb, &tmapB, fb, k0, b_row, bh, bb);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN / Cfg::ROW_ELEMS; ++c)
-              tma_load_4d(sb + c * Cfg::BK * 128, &tmapB, &full_bar[stage], nb_ * BN + c * Cfg::ROW_ELEMS, k0, bh, bb);
+              for (int c = 0; c < Cfg::BN_CTA / Cfg::ROW_ELEMS; ++c)
+                tma_load_4d_pair(sb + c * Cfg::BK * 128, &tmapB, fb, b_row + c * Cfg::ROW_ELEMS, k0, bh, bb);
+            }
+          } else {
+            mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+            if constexpr (!A_MN) {
+              tma_load_4d(sa, &tmapA, &full_bar[stage], k0, a_row, bh, bb);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / Cfg::ROW_ELEMS; ++c)
+                tma_load_4d(sa + c * Cfg::BK * 128, &tmapA, &full_bar[stage], a_row + c * Cfg::ROW_ELEMS, k0, bh, bb);
+            }
+            if constexpr (!B_MN) {
+              tma_load_4d(sb, &tmapB, &full_bar[stage], k0, b_row, bh, bb);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / Cfg::ROW_ELEMS; ++c)
+                tma_load_4d(sb + c * Cfg::BK * 128, &tmapB, &full_bar[stage], b_row + c * Cfg::ROW_ELEMS, k0, bh, bb);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -276,13 +315,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && pair_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      for (long long item = worker; item < num_items && ok; item += num_workers) {
         const int kb0 = (int)(item / p.num_tiles) * p.kb_per_split;
         const int kb1 = kb0 + p.kb_per_split < num_kb ? kb0 + p.kb_per_split : num_kb;
         ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
@@ -299,14 +338,21 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
           uint64_t bdesc = make_smem_desc(sb, Cfg::B_LBO, Cfg::SBO);
 #pragma unroll
           for (int k = 0; k < Cfg::BK / Cfg::UMMA_K; ++k) {
-            tc_mma<ES == 4>(d_tmem, adesc + (uint64_t)((k * Cfg::A_KADV) >> 4), bdesc + (uint64_t)((k * Cfg::B_KADV) >> 4),
-                            Cfg::IDESC, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            if constexpr (CTA2)
+              tc_mma_pair_bf16(d_tmem, adesc + (uint64_t)((k * Cfg::A_KADV) >> 4), bdesc + (uint64_t)((k * Cfg::B_KADV) >> 4), Cfg::IDESC,
+                               ((kb - kb0) | k) != 0 ? 1u : 0u);
+            else
+              tc_mma<ES == 4>(d_tmem, adesc + (uint64_t)((k * Cfg::A_KADV) >> 4), bdesc + (uint64_t)((k * Cfg::B_KADV) >> 4),
+                              Cfg::IDESC, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          // frees the smem stage (in both CTAs of a pair) once these MMAs retire
+          if constexpr (CTA2) tc_commit_pair(&empty_bar[stage]);
+          else tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tmem_full[acc]);
+        if constexpr (CTA2) tc_commit_pair(&tmem_full[acc]);
+        else tc_commit(&tmem_full[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -374,7 +420,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
     uint32_t acc_phase = 0;
     uint32_t store_it = 0;  // TMA-store chunks issued by this warp (selects the staging buffer)
     bool ok = true;
-    for (long long item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+    for (long long item = worker; item < num_items && ok; item += num_workers) {
       const long long tile = item % p.num_tiles;
       const bool first_split = item < p.num_tiles;  // the bias is added once
       int mb, nb_, bh, bb;
@@ -391,7 +437,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
         c_base = (long long)(p.scatter_src - owner) * p.scatter_rows * p.ldc;
       }
       const long long a_base = (long long)bh * p.add_sh + (long long)bb * p.add_sb;
-      const int row0 = mb * BM + q * 32;          // first row of this warp's quarter
+      const int row0 = mb * TILE_M + (int)pair_rank * BM + q * 32;  // first row of this warp's quarter
       const int rows_left = p.M - row0 - rsub;     // iteration i is valid iff 4*i < rows_left
       const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * HALF_COLS);
       uint32_t r[32];
@@ -448,7 +494,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (lane == 0) {
+          if constexpr (CTA2) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+          else mbar_arrive(&tmem_empty[acc]);
+        }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
@@ -565,7 +614,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+          if constexpr (CTA2) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[acc]), 0));
+          else mbar_arrive(&tmem_empty[acc]);
+        }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     // every bulk store this warp issued must have completed before the CTA's shared memory goes away
@@ -574,10 +626,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTA2) cluster_sync_all();  // neither CTA's shared or tensor memory goes away while its partner may still use it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
-                 : "memory");
+    if constexpr (CTA2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                   : "memory");
   }
   if (p.gate_sync && threadIdx.x == 0) {
     // the last CTA to leave advances the epoch the next call will wait for
@@ -837,12 +893,48 @@ int make_store_map(CUtensorMap *map, void *ptr, long long cols, long long rows, 
 
 __device__ int g_gemm_err = 0;
 
+// The CTA-pair kernel: same arguments; the grid is a whole number of clusters of 2 and tiles are 256 rows tall.
+template <int BN, bool A_MN, bool B_MN>
+int launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const ScatterMaps &sm, GemmArgs &args, int max_ctas,
+                cudaStream_t stream) {
+  using Cfg = GemmCfg<2, BN, A_MN, B_MN, true>;
+  static bool attr_done = false;
+  auto kern = gemm_sm100_kernel<2, BN, A_MN, B_MN, true>;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  args.tiles_m = (args.M + 2 * BM - 1) / (2 * BM);
+  args.tiles_n = (args.N + BN - 1) / BN;
+  args.num_tiles = (long long)args.tiles_m * args.tiles_n * args.nh * args.nb;
+  args.split_k = 1;
+  args.kb_per_split = (args.K + Cfg::BK - 1) / Cfg::BK;
+  long long pairs = max_ctas / 2;
+  if (args.num_tiles < pairs) pairs = args.num_tiles;
+  if (pairs < 1) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, sm, args);
+  return (int)e;
+}
+
 template <int ES, int BN, bool A_MN, bool B_MN>
 int launch_cfg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const ScatterMaps &sm, GemmArgs &args, int max_ctas,
                cudaStream_t stream) {
   using Cfg = GemmCfg<ES, BN, A_MN, B_MN>;
   static bool attr_done = false;
-  auto kern = gemm_sm100_kernel<ES, BN, A_MN, B_MN>;
+  auto kern = gemm_sm100_kernel<ES, BN, A_MN, B_MN, false>;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
@@ -883,6 +975,14 @@ int launch_major(bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap 
   if (!a_mn && b_mn) return launch_cfg<ES, BN, false, true>(ta, tb, tc, sm, args, max_ctas, stream);
   if (a_mn && !b_mn) return launch_cfg<ES, BN, true, false>(ta, tb, tc, sm, args, max_ctas, stream);
   return launch_cfg<ES, BN, true, true>(ta, tb, tc, sm, args, max_ctas, stream);
+}
+
+int launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, const ScatterMaps &sm,
+                      GemmArgs &args, int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_pair<256, false, false>(ta, tb, tc, sm, args, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_pair<256, false, true>(ta, tb, tc, sm, args, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_pair<256, true, false>(ta, tb, tc, sm, args, max_ctas, stream);
+  return launch_pair<256, true, true>(ta, tb, tc, sm, args, max_ctas, stream);
 }
 
 int sm_count() {
@@ -943,6 +1043,9 @@ struct FfkGemmDesc {
   const void *drop_seed_ptr;
 };
 
+static int g_pair_mode = 1;  // 1: CTA pairs where they apply, 0: never
+// CTA-pair (tcgen05 cta_group::2) kernel on (1) or off (0) process-wide; for A/B measurements.
+FFK_API void ffk_gemm_set_cta_pairs(int enabled) { g_pair_mode = enabled ? 1 : 0; }
 static int g_disable_tma_store = 0;
 static int g_disable_scatter_tma = 0;
 // Scatter epilogue (GEMM -> reduce-scatter) through TMA stores into the peers' stages (1) or per-lane stores (0).
@@ -1018,13 +1121,20 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
     else bn = 64;
     if (es == 4 && bn == 256) bn = 128;
   }
+  // A CTA pair per 256 x 256 tile when the problem has at least one such tile per pair of SMs and none of the fused-collective
+  // or split-K machinery is involved (those stay on the single-CTA kernel).
+  bool pair = false;
+  if (g_pair_mode && es == 2 && bn == 256 && !fused && d->M >= 256) {
+    const long long t = (long long)((d->M + 255) / 256) * ((d->N + 255) / 256) * nbatch;
+    pair = t >= sm_count() / 2;
+  }
   const int BK = 128 / es;
   CUtensorMap ta, tb;
   int r;
   if (!d->a_mn) r = make_operand_map(&ta, d->A, es, d->K, d->M, d->lda, d->nh, d->a_sh, d->nb, d->a_sb, BM);
   else r = make_operand_map(&ta, d->A, es, d->M, d->K, d->lda, d->nh, d->a_sh, d->nb, d->a_sb, BK);
   if (r) return r;
-  if (!d->b_mn) r = make_operand_map(&tb, d->B, es, d->K, d->N, d->ldb, d->nh, d->b_sh, d->nb, d->b_sb, bn);
+  if (!d->b_mn) r = make_operand_map(&tb, d->B, es, d->K, d->N, d->ldb, d->nh, d->b_sh, d->nb, d->b_sb, pair ? bn / 2 : bn);
   else r = make_operand_map(&tb, d->B, es, d->N, d->K, d->ldb, d->nh, d->b_sh, d->nb, d->b_sb, BK);
   if (r) return r;
 
@@ -1072,6 +1182,7 @@ FFK_API int ffk_gemm(const FfkGemmDesc *d, cudaStream_t stream) {
            make_store_map(&sm.m[o], d->scatter[o], d->N, (long long)owners * d->scatter_rows, d->ldc, 1, 0, 1, 0) == 0;
     if (ok) a.tma_store = 1;
   }
+  if (pair) return launch_pair_major(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
   if (es == 2) {
     if (bn == 256) return launch_major<2, 256>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);
     if (bn == 128) return launch_major<2, 128>(d->a_mn, d->b_mn, ta, tb, tc, sm, a, max_ctas, stream);

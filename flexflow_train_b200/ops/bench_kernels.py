@@ -147,7 +147,45 @@ def bench_im2col(a):
     return {"op": "im2col_3x3_bf16", "n": n, "c": c, "hw": h, **roofline(ms, hbm_bytes=2.0 * (x.numel() + col.numel()))}
 
 
-OPS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "layernorm_bwd": bench_layernorm_bwd, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
+def bench_attention(a):
+    """Fused attention forward and backward on a packed QKV buffer: --batch, --heads, --seq, --head-dim, --dropout, --causal.
+    FLOPs counted: 4 B H Sq Sk D forward, 10 B H Sq Sk D backward (halved when causal).  --compare also times the
+    library attention (torch scaled_dot_product_attention, forward and its autograd backward) on the same data."""
+    import math
+    B, H, S, D = a.batch, a.heads, a.seq, a.head_dim
+    qkv = (torch.randn(B * S, 3 * H * D, device="cuda") * 0.5).to(torch.bfloat16)
+    q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
+    out = torch.empty(B * S, H * D, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn_like(out)
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = dqkv[:, :H * D], dqkv[:, H * D:2 * H * D], dqkv[:, 2 * H * D:]
+    lse = torch.empty(B, H, S, device="cuda")
+    delta = torch.empty(B * H * S, device="cuda")
+    seed = torch.tensor([1], dtype=torch.int64, device="cuda")
+    drop = (a.dropout, 7, seed) if a.dropout > 0 else None
+    scale = 1.0 / math.sqrt(D)
+    kw = dict(B=B, H=H, Sq=S, Sk=S, D=D, scale=scale, causal=a.causal, dropout=drop)
+    f = (0.5 if a.causal else 1.0) * B * H * S * S * D
+    res = {"op": "attention_bf16", "batch": B, "heads": H, "seq": S, "head_dim": D, "dropout": a.dropout, "causal": a.causal}
+    ms = _time(lambda: K.attention_fwd(q, k, v, out, lse, **kw), a.warmup, a.iters, a.flush)
+    res["fwd"] = roofline(ms, flops=4.0 * f, hbm_bytes=2.0 * 4 * B * S * H * D)
+    if K.attention_supported(D, backward=True):
+        acc = torch.empty(K.attention_bwd_scratch_floats(B, H, S, D), device="cuda")
+        ms = _time(lambda: K.attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, **kw), a.warmup, a.iters, a.flush)
+        res["bwd"] = roofline(ms, flops=10.0 * f, hbm_bytes=2.0 * 8 * B * S * H * D)
+    if a.compare:
+        import torch.nn.functional as F
+        q4, k4, v4 = (t.reshape(B, S, H, D).transpose(1, 2).contiguous().requires_grad_(True) for t in (q, k, v))
+        do4 = dout.reshape(B, S, H, D).transpose(1, 2).contiguous()
+        fwd = lambda: F.scaled_dot_product_attention(q4, k4, v4, dropout_p=a.dropout, is_causal=a.causal)  # noqa: E731
+        res["torch_sdpa_fwd_ms"] = _time(fwd, a.warmup, a.iters, a.flush)
+        o4 = fwd()
+        res["torch_sdpa_bwd_ms"] = _time(lambda: torch.autograd.grad(o4, (q4, k4, v4), do4, retain_graph=True), a.warmup, a.iters, a.flush)
+    res["attention_error"] = K.attention_last_error()
+    return res
+
+
+OPS = {"attention": bench_attention, "gemm": bench_gemm, "layernorm": bench_layernorm, "layernorm_bwd": bench_layernorm_bwd, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
        "im2col": bench_im2col}
 
 
@@ -162,6 +200,11 @@ def main(argv=None):
     p.add_argument("--batch", type=int, default=32)
     p.add_argument("--channels", type=int, default=192)
     p.add_argument("--size", type=int, default=35)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--seq", type=int, default=1024)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--dropout", type=float, default=0.0)
+    p.add_argument("--causal", action="store_true")
     p.add_argument("--bias", action="store_true")
     p.add_argument("--relu", action="store_true")
     p.add_argument("--compare", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")

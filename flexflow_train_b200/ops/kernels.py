@@ -89,6 +89,8 @@ def lib():
         _lib = ctypes.CDLL(_LIB_PATH)
         _declare(_lib)
         # epilogue through TMA stores: FFK_TMA_STORE=1/0 overrides the library default
+        if os.environ.get("FFK_CTA_PAIRS") in ("0", "1"):
+            _lib.ffk_gemm_set_cta_pairs(int(os.environ["FFK_CTA_PAIRS"]))
         if os.environ.get("FFK_TMA_STORE") in ("0", "1"):
             _lib.ffk_gemm_set_tma_store(int(os.environ["FFK_TMA_STORE"]))
     return _lib
