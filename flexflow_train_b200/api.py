@@ -30,6 +30,8 @@ class FFConfig:
     enable_profiling: bool = False
     search_budget: int = 0
     search_alpha: float = 1.05
+    search_time_limit_s: float = 60.0   # wall-clock bound of the Unity search (it also stops when the budget is used up)
+    search_start: str = "best_template"  # or "serial": begin the search at the unparallelised graph
     search_algorithm: str = "unity"  # "unity" | "mcmc" | "data_parallel" | "tensor_parallel" | "table_parallel"
     only_data_parallel: bool = False
     enable_parameter_parallel: bool = True

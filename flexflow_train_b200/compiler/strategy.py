@@ -242,11 +242,34 @@ def shard_replicated_operators(g, world: int, rules):
     return core.apply_rules_exhaustively(g, cancellation_rules(rules), 100000, world)
 
 
+def rule_families(rules, world: int) -> List[List[int]]:
+    """Groups of rule indices that the Unity search may apply as one move: for every degree that divides the machine,
+    all rules that shard the sample dimension that many ways."""
+    names = [r.name for r in rules]
+    fams = []
+    d = 2
+    while d <= world:
+        if world % d == 0:
+            members = {r.name for r in data_parallel_rules(rules, d)}
+            fam = [i for i, n in enumerate(names) if n in members]
+            if fam:
+                fams.append(fam)
+        d *= 2
+    return fams
+
+
 def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = "unity", budget: int = 0, alpha: float = 1.05,
-             estimator=None, rules=None, seed: int = 0, mcmc_iterations: int = 200, mcmc_temperature: float = 1.0,
+             estimator=None, rules=None, seed: int = 0, mcmc_iterations: int = 200, mcmc_temperature: float = 0.02,
              substitution_frequency: float = 0.2, time_limit_s: float = 120.0, only_data_parallel: bool = False,
-             enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True, score_hybrid: bool = False) -> dict:
-    """Search a strategy.  Returns ``{"pcg", "mapped_pcg", "runtime_ms", "memory_bytes", "stats", "candidates"}``."""
+             enable_parameter_parallel: bool = True, enable_attribute_parallel: bool = True, score_hybrid: bool = False,
+             start: str = "best_template") -> dict:
+    """Search a strategy.  Returns ``{"pcg", "mapped_pcg", "runtime_ms", "memory_bytes", "stats", "candidates"}``.
+
+    The hand-built templates (single device, data parallel, tensor parallel, table parallel) are always scored.  With
+    ``budget > 0`` the Unity (or MCMC) search then runs from ``start``: ``"best_template"`` (the cheapest template) or
+    ``"serial"`` (the unparallelised graph, as the reference's search starts,
+    lib/compiler/src/compiler/unity_algorithm/unity_algorithm.cc:51-146); the cheaper of the search's result and the best
+    template is returned.  ``mcmc_temperature`` is a fraction of the starting cost."""
     if machine is None:
         machine = machine_for(world or 1)
     W = machine.num_devices
@@ -289,17 +312,20 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
     stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
     if hybrid_scores:
         stats["hybrid_candidates_not_executable"] = hybrid_scores
+    origin = scored["single_device"] if start == "serial" else best
+    stats["search_start"] = "serial" if start == "serial" else best_name
     if algorithm == "unity" and budget > 0 and W > 1:
         use = rules if not only_data_parallel else data_parallel_rules(rules, W) + cancellation_rules(rules)
         use = filter_rules(use, enable_parameter_parallel, enable_attribute_parallel)
-        r = core.unity_search(best["pcg"], machine, estimator, use, alpha, budget, 100000, time_limit_s)
-        stats["unity"] = r["stats"]
+        r = core.unity_search(origin["pcg"], machine, estimator, use, alpha, budget, 100000, time_limit_s, True, True,
+                              rule_families(use, W))
+        stats["unity"] = dict(r["stats"], runtime_ms=r["runtime_ms"])
         if r["runtime_ms"] < best["runtime_ms"]:
             best = r
-            stats["seed_strategy"] += "+unity"
+            stats["seed_strategy"] = ("serial" if start == "serial" else stats["seed_strategy"]) + "+unity"
     elif algorithm == "mcmc" and W > 1:
-        r = core.mcmc_search(best["pcg"], machine, estimator, filter_rules(rules, enable_parameter_parallel, enable_attribute_parallel),
-                             mcmc_temperature, mcmc_iterations, substitution_frequency, seed)
+        r = core.mcmc_search(origin["pcg"], machine, estimator, filter_rules(rules, enable_parameter_parallel, enable_attribute_parallel),
+                             mcmc_temperature, mcmc_iterations, substitution_frequency, seed, True)
         stats["mcmc"] = r["stats"]
         # MCMC scores with the simulator; re-score with the mapping DP for a comparable number
         rescored = core.evaluate_pcg(r["pcg"], machine, estimator)
@@ -329,6 +355,7 @@ def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
         extra = {"substitution_json": {"path": path, "rules_in_file": st["num_rules"], "rules_loaded": st["num_converted"]}}
     r = optimize(cg, world=world, algorithm=algo, budget=getattr(config, "search_budget", 0),
                  alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
+                 time_limit_s=getattr(config, "search_time_limit_s", 60.0), start=getattr(config, "search_start", "best_template"),
                  only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules,
                  enable_parameter_parallel=getattr(config, "enable_parameter_parallel", True),
                  enable_attribute_parallel=getattr(config, "enable_attribute_parallel", True),

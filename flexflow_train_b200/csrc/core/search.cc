@@ -778,13 +778,14 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
   struct State {
     double cost;
     Graph g;
+    bool exempt;  // produced by a compound move: expanded even when outside the alpha band
     bool operator<(const State &o) const { return cost > o.cost; }  // min-heap
   };
   std::priority_queue<State> queue;
   std::set<std::string> seen;
   MachineMappingCache cache;  // shared by every candidate: only the sub-problems around a rewritten region are solved anew
   SearchResult best = evaluate_pcg(start, m, est, &cache);
-  queue.push({best.runtime_ms, start});
+  queue.push({best.runtime_ms, start, true});
   seen.insert(start.signature());
   long long evaluated = 1, generated = 0;
   int iterations = 0;
@@ -792,7 +793,7 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
     if (elapsed() > cfg.time_limit_s) break;
     State cur = queue.top();
     queue.pop();
-    if (cur.cost > cfg.alpha * best.runtime_ms) continue;
+    if (!cur.exempt && cur.cost > cfg.alpha * best.runtime_ms) continue;
     int candidates = 0;
     auto consider = [&](const Graph &ng, bool keep_anyway) {
       ++generated;
@@ -802,8 +803,22 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
       SearchResult r = evaluate_pcg(ng, m, est, &cache);
       ++evaluated;
       if (r.runtime_ms < best.runtime_ms) best = r;
-      if (keep_anyway ? std::isfinite(r.runtime_ms) : r.runtime_ms <= cfg.alpha * best.runtime_ms) queue.push({r.runtime_ms, ng});
+      if (keep_anyway ? std::isfinite(r.runtime_ms) : r.runtime_ms <= cfg.alpha * best.runtime_ms) queue.push({r.runtime_ms, ng, keep_anyway});
     };
+    auto cleanup = [&](Graph g) {
+      if (!cfg.cancel_after_compound || cfg.cleanup_rules.empty()) return g;
+      std::vector<Substitution> cl;
+      for (int ci : cfg.cleanup_rules) cl.push_back(rules.at((size_t)ci));
+      return apply_rules_exhaustively(g, cl, 100000, m.num_devices());
+    };
+    // Rule families (for instance every sample-dimension partition rule of one degree): all of a family's rules applied
+    // wherever they match, as one move.
+    for (auto &fam : cfg.families) {
+      if (elapsed() > cfg.time_limit_s) break;
+      std::vector<Substitution> rs;
+      for (int ri : fam) rs.push_back(rules.at((size_t)ri));
+      consider(cleanup(apply_rules_exhaustively(cur.g, rs, 100000, m.num_devices())), true);
+    }
     for (auto &rule : rules) {
       if (candidates >= cfg.max_candidates_per_step || elapsed() > cfg.time_limit_s) break;
       auto matches = find_pattern_matches(rule.pattern, cur.g);
@@ -815,13 +830,7 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
       // outside the alpha band: its value shows only after the cancellation rules have been applied to it.
       if (cfg.compound_moves && matches.size() > 1) {
         std::vector<Substitution> one{rule};
-        Graph all = apply_rules_exhaustively(cur.g, one, 100000, m.num_devices());
-        if (cfg.cancel_after_compound && !cfg.cleanup_rules.empty()) {
-          std::vector<Substitution> cl;
-          for (int ci : cfg.cleanup_rules) cl.push_back(rules.at((size_t)ci));
-          all = apply_rules_exhaustively(all, cl, 100000, m.num_devices());
-        }
-        consider(all, true);
+        consider(cleanup(apply_rules_exhaustively(cur.g, one, 100000, m.num_devices())), true);
       }
       if (cfg.single_moves)
         for (auto &mt : matches) {
@@ -1065,8 +1074,10 @@ void bind_search(py::module &m) {
     return apply_rules_exhaustively(g, rules, max_app, max_deg);
   }, py::arg("graph"), py::arg("rules"), py::arg("max_applications") = 100000, py::arg("max_total_degree") = 0);
   m.def("unity_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double alpha,
-                           int budget, int max_num_ops, double time_limit_s, bool compound_moves, bool single_moves) {
+                           int budget, int max_num_ops, double time_limit_s, bool compound_moves, bool single_moves,
+                           std::vector<std::vector<int>> families) {
     UnityConfig c;
+    c.families = families;
     c.alpha = alpha; c.budget = budget; c.max_num_ops = max_num_ops; c.time_limit_s = time_limit_s;
     c.compound_moves = compound_moves; c.single_moves = single_moves;
     // rules that only remove parallel operators (a Combine meeting a Repartition and the like) tidy up after a compound move
@@ -1077,7 +1088,8 @@ void bind_search(py::module &m) {
     py::gil_scoped_acquire acq;
     return result_to_py(r);
   }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("alpha") = 1.05, py::arg("budget") = 10,
-        py::arg("max_num_ops") = 100000, py::arg("time_limit_s") = 120.0, py::arg("compound_moves") = true, py::arg("single_moves") = true);
+        py::arg("max_num_ops") = 100000, py::arg("time_limit_s") = 120.0, py::arg("compound_moves") = true, py::arg("single_moves") = true,
+        py::arg("families") = std::vector<std::vector<int>>());
   m.def("mcmc_search", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est, std::vector<Substitution> rules, double temperature,
                           int iters, double sub_freq, unsigned seed, bool relative) {
     MCMCConfig c;

@@ -122,6 +122,7 @@ struct UnityConfig {
   bool single_moves = true;     // one candidate per (rule, match), as the reference does
   bool compound_moves = true;   // plus one candidate per rule: that rule applied wherever it matches
   bool cancel_after_compound = true;
+  std::vector<std::vector<int>> families;  // groups of rule indices, each applied exhaustively as one move
   std::vector<int> cleanup_rules;  // indices (into the rule list) of the rules applied exhaustively after a compound move
 };
 SearchResult evaluate_pcg(const Graph &pcg, const MachineSpec &m, const CostEstimator &est, MachineMappingCache *cache = nullptr);

@@ -19,16 +19,18 @@
 // Forward CTA (320 threads) = one 128-query block of one (batch, head):
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through a two-stage ring
 //   warp 1      MMA issuer:   S[t] = Q K_j^T   (TMEM, two stages)   and   Opart[t] = P_j V_j   (TMEM, two stages)
-//   warps 2-5   softmax:      thread = query row; running max / sum, P_j -> shared memory (bf16, 128-byte swizzle)
-//   warps 6-9   accumulate:   thread = query row; O = O * alpha_j + Opart[t] in registers, final scale and store
+//   warps 2-9   softmax and output: thread = query row x half of the tile's keys (and half of the output columns);
+//               running max / sum, P_j -> shared memory (bf16, 128-byte swizzle), O = O * alpha_j + Opart[t] in registers
 //
-// Backward CTA (320 threads) = one 128-query block of one (batch, head), looping over tiles of 64 keys:
-//   S = Q K_j^T, dP = dO V_j^T (TMEM, two stages) -> thread per query row computes P and dS = P o (dP - delta)
-//   -> shared memory -> dV_j^T = dO^T P, dK_j^T = Q^T dS (TMEM, read out and added to fp32 accumulators in
-//   global memory by four read-out warps) and dQ += dS K_j (TMEM accumulator, stored once at the end).
+// Backward CTA (448 threads) = one 128-query block of one (batch, head), looping over tiles of 64 keys:
+//   S = Q K_j^T, dP = dO V_j^T (TMEM, two stages) -> eight warps (thread = query row x 32 keys) compute P and
+//   dS = P o (dP - delta) -> shared memory -> dV_j^T = dO^T P, dK_j^T = Q^T dS (TMEM, read out and added to fp32
+//   accumulators in global memory by four read-out warps) and dQ += dS K_j (TMEM accumulator, stored once at the end).
 //
 // Every mbarrier wait is bounded (tcgen05.cuh); on expiry the CTA records a code in the library's error word,
 // frees its TMEM and returns.
+#include <cstdlib>
+
 #include "tcgen05.cuh"
 
 namespace {
@@ -55,7 +57,18 @@ struct AttnArgs {
   long long lddq;
   float *dK_acc, *dV_acc; // [B, H, Sk, D] fp32, zeroed by the caller
   int *err;
+  int dbg;                // experiment switches (FFK_ATTN_DBG): parts of the kernel left out to time the rest
 };
+
+// Timeline of one CTA (experiment switch 4096): (event, step, SM clock) triples written by the roles' first lanes.
+__device__ unsigned int g_attn_trace_n = 0;
+__device__ long long g_attn_trace[3 * 2048];
+__device__ __forceinline__ void attn_trace(const AttnArgs &p, int ev, int j) {
+  if ((p.dbg & 4096) && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+    const unsigned int i = atomicAdd(&g_attn_trace_n, 1u);
+    if (i < 2048) { g_attn_trace[3 * i] = ev; g_attn_trace[3 * i + 1] = j; g_attn_trace[3 * i + 2] = clock64(); }
+  }
+}
 
 __device__ __forceinline__ unsigned long long attn_seed(const AttnArgs &p) {
   return p.drop_seed_ptr ? p.drop_salt * 0x9E3779B97F4A7C15ull + *p.drop_seed_ptr : p.drop_salt;
@@ -84,46 +97,53 @@ struct FwdCfg {
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int KV_BYTES = BKF * D * 2;       // one K or one V tile
   static constexpr int P_BYTES = BQ * BKF * 2;       // 32 KB
-  static constexpr int STAGES = 2;
+  // A K tile is free again once the scores of its step are computed, a V tile only at the end of its step: the V ring
+  // is one stage deeper so that its loads also run a full step ahead.
+  static constexpr int NK = 2, NV = 3;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
-  static constexpr int OFF_V = OFF_K + STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + STAGES * KV_BYTES;
-  static constexpr int OFF_SCALE = OFF_P + P_BYTES;          // [2][128] floats alpha, then [128] final factors
-  static constexpr int OFF_BAR = OFF_SCALE + 3 * 128 * 4;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;    // barriers + alignment slack
+  static constexpr int OFF_V = OFF_K + NK * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + NV * KV_BYTES;
+  static constexpr int OFF_XCHG = OFF_P + P_BYTES;           // [2 tile parities][2 column halves][128 rows] floats
+  static constexpr int OFF_BAR = OFF_XCHG + 4 * 128 * 4;
+  static constexpr int SLACK = D == 128 ? 768 : 1024;        // room to align the base to 1024 bytes (checked in the kernel)
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + SLACK;
   static constexpr int TMEM_S = 0;                           // S[t] at columns t * 128
   static constexpr int TMEM_O = 256;                         // Opart[t] at columns 256 + t * D
   static constexpr uint32_t IDESC_S = attn_idesc(128, BKF, 0, 0);
   static constexpr uint32_t IDESC_PV = attn_idesc(128, D, 0, 1);
 };
 
+// named barrier of the two warps that share a TMEM lane quarter (ids 1..4; 0 is __syncthreads)
+__device__ __forceinline__ void pair_sync(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory"); }
+
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnArgs p) {
   using C = FwdCfg<D>;
+  constexpr int DH = D / 2;                          // output columns owned by one thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float *alpha_s = (float *)(smem + C::OFF_SCALE);   // [2][128]
-  float *final_s = alpha_s + 256;                    // [128]
+  float *xchg = (float *)(smem + C::OFF_XCHG);       // [2][2][128]
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
   uint64_t *q_full = bars;            // 1
   uint64_t *k_full = bars + 1;        // [2]
-  uint64_t *v_full = bars + 3;        // [2]
   uint64_t *k_empty = bars + 5;       // [2]
-  uint64_t *v_empty = bars + 7;       // [2]
+  uint64_t *v_full = bars + 19;       // [NV]
+  uint64_t *v_empty = bars + 22;      // [NV]
   uint64_t *s_full = bars + 9;        // [2]
-  uint64_t *s_empty = bars + 11;      // [2] 4 warps
-  uint64_t *p_full = bars + 13;       // 4 warps
+  uint64_t *s_empty = bars + 11;      // [2] 8 warps
+  uint64_t *p_full = bars + 13;       // 8 warps
   uint64_t *p_empty = bars + 14;      // commit
   uint64_t *o_full = bars + 15;       // [2] commit
-  uint64_t *o_empty = bars + 17;      // [2] 4 warps
-  uint64_t *a_full = bars + 19;       // [2] 4 warps (alpha written)
-  uint64_t *a_empty = bars + 21;      // [2] 4 warps (alpha read)
-  uint64_t *fin = bars + 23;          // 4 warps (final factors written)
-  uint32_t *tmem_slot = (uint32_t *)(bars + 24);
+  uint64_t *o_empty = bars + 17;      // [2] 8 warps
+  uint32_t *tmem_slot = (uint32_t *)(bars + 25);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  if ((uintptr_t)(smem - smem_raw) > (uintptr_t)C::SLACK) {  // the launch did not leave room to align the tiles: refuse
+    if (threadIdx.x == 0 && p.err) atomicCAS(p.err, 0, (int)FFK_ERR_BAD_ARG);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.Sq + BQ - 1) / BQ;
@@ -140,11 +160,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 4);
-      mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 4);
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 8);
     }
-    mbar_init(p_full, 4); mbar_init(p_empty, 1); mbar_init(fin, 4);
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    mbar_init(p_full, 8); mbar_init(p_empty, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -163,22 +183,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_expect_tx(q_full, C::Q_BYTES);
 #pragma unroll
       for (int c = 0; c < C::PANELS; ++c) tma_load_4d(smem_u32(smem + C::OFF_Q + c * BQ * 128), &tmQ, q_full, c * 64, q0, h, b);
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        ok = mbar_wait(&k_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
-        if (!ok) break;
-        mbar_expect_tx(&k_full[t], C::KV_BYTES);
+      // the K and V rings advance independently; the wait for progress on either is bounded
+      int kj = 0, vj = 0;
+      uint64_t t0 = ffk_globaltimer();
+      uint32_t spins = 0;
+      while (kj < n_tiles || vj < n_tiles) {
+        bool progress = false;
+        if (kj < n_tiles) {
+          const int t = kj % C::NK;
+          if (mbar_try_wait(&k_empty[t], ((uint32_t)(kj / C::NK) & 1u) ^ 1u)) {
+            mbar_expect_tx(&k_full[t], C::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < C::PANELS; ++c)
-          tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKF * 128), &tmK, &k_full[t], c * 64, j * BKF, h, b);
-        ok = mbar_wait(&v_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
-        if (!ok) break;
-        mbar_expect_tx(&v_full[t], C::KV_BYTES);
+            for (int c = 0; c < C::PANELS; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKF * 128), &tmK, &k_full[t], c * 64, kj * BKF, h, b);
+            ++kj;
+            progress = true;
+          }
+        }
+        if (vj < n_tiles) {
+          const int t = vj % C::NV;
+          if (mbar_try_wait(&v_empty[t], ((uint32_t)(vj / C::NV) & 1u) ^ 1u)) {
+            mbar_expect_tx(&v_full[t], C::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < C::PANELS; ++c)
-          tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKF * 128), &tmV, &v_full[t], c * 64, j * BKF, h, b);
+            for (int c = 0; c < C::PANELS; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKF * 128), &tmV, &v_full[t], c * 64, vj * BKF, h, b);
+            ++vj;
+            progress = true;
+          }
+        }
+        if (progress) {
+          t0 = ffk_globaltimer();
+        } else if ((++spins & 63u) == 0) {
+          if (*abort_flag) break;
+          if (ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (p.err) atomicCAS(p.err, 0, (int)FFK_ERR_TIMEOUT_PRODUCER);
+            break;
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -194,10 +236,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES);
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
+        if (!(p.dbg & 16)) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);   // panel, then 32 bytes per k-step
           tc_mma<false>(d_tmem, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
         }
         tc_commit(&s_full[t]);
         tc_commit(&k_empty[t]);
@@ -208,14 +252,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int t = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-        ok = mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
+        const int vt = j % C::NV;
+        ok = mbar_wait(&v_full[vt], (uint32_t)(j / C::NV) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
              mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
              mbar_wait(&o_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
         const uint32_t sp = smem_u32(smem + C::OFF_P);
-        const uint32_t sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
+        const uint32_t sv = smem_u32(smem + C::OFF_V + vt * C::KV_BYTES);
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
+        if (!(p.dbg & 2))
 #pragma unroll
         for (int ks = 0; ks < BKF / 16; ++ks) {
           // A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
@@ -225,13 +271,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         ks != 0 ? 1u : 0u);
         }
         tc_commit(&o_full[t]);
-        tc_commit(&v_empty[t]);
+        tc_commit(&v_empty[vt]);
         tc_commit(p_empty);
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax: thread = query row
+  } else {
+    // ------------------------------------------------------------------ softmax + output accumulation
+    // Eight warps: warp w works on TMEM lane quarter w % 4 (a hardware rule) and on column half (w - 2) / 4, so a thread is
+    // one query row and 64 of the tile's 128 keys (and D / 2 of the output columns).  Two warps per scheduler hide each
+    // other's TMEM-load and special-function latencies; the row maximum is the only thing the two halves must agree on
+    // per tile and goes through a two-float exchange in shared memory.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int q = q0 + r;
     const float sl2 = p.scale * LOG2E;
@@ -241,8 +292,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
     const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
     const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
-    uint8_t *prow = smem + C::OFF_P + r * 128;
+    const uint32_t prow = smem_u32(smem + C::OFF_P + half * (BQ * 128) + r * 128);   // this row in this half's 64-key panel
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    float alpha_pending = 1.f;
     bool ok = true;
+    // O += Opart of tile jj (rescaled by the factor that tile's softmax produced)
+    auto accumulate = [&](int jj, float alpha) -> bool {
+      const int t = jj & 1;
+      bool k_ = mbar_wait(&o_full[t], (uint32_t)(jj >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      k_ = __all_sync(0xffffffffu, k_);
+      if (!k_) return false;
+      tc_fence_after();
+      const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
+      uint32_t ra[32];
+      if (p.dbg & 8) { tc_fence_before(); warp_arrive(&o_empty[t], lane); return true; }
+      tmem_ld32(t_o, ra);
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        tmem_ld_wait();
+        uint32_t rb[32];
+        if (c + 1 < DH / 32) tmem_ld32(t_o + (uint32_t)((c + 1) * 32), rb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(ra[i]));
+        if (c + 1 < DH / 32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ra[i] = rb[i];
+        }
+      }
+      tc_fence_before();
+      warp_arrive(&o_empty[t], lane);
+      return true;
+    };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int t = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
@@ -250,133 +333,95 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_S + t * 128);
-      const int k0 = j * BKF;
-      // columns of this tile that exist / are visible to this row
-      int kmax = p.Sk - k0;                       // columns >= kmax are padding
+      const uint32_t t_s = lane_base + (uint32_t)(C::TMEM_S + t * 128 + half * 64);
+      uint32_t rs[64];
+      tmem_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+      tmem_ld32(t_s + 32u, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      warp_arrive(&s_empty[t], lane);     // the scores are in registers: the next-but-one tile may overwrite them
+      const int k0 = j * BKF + half * 64;
+      // columns of this half that exist / are visible to this row
+      int kmax = p.Sk - k0;
       if (p.causal) kmax = min(kmax, q - k0 + 1);
-      const bool full = kmax >= BKF;
-      uint32_t rr[32];
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_s + (uint32_t)(c * 32), rr);
-        tmem_ld_wait();
-        if (full) {
+      const bool full = kmax >= 64;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(rr[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i < kmax) ? __uint_as_float(rr[i]) : -INFINITY);
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(rs[i])); mx1 = fmaxf(mx1, __uint_as_float(rs[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(rs[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(rs[i + 3]));
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx0 = fmaxf(mx0, i < kmax ? __uint_as_float(rs[i]) : -INFINITY);
       }
-      float m_new = fmaxf(m, mx * sl2);
-      if (m_new == -INFINITY) m_new = 0.f;        // a row with nothing visible yet (only padding rows get here)
+      const float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      xchg[(t * 2 + half) * 128 + r] = mine;
+      pair_sync(quarter);
+      const float other = xchg[(t * 2 + (half ^ 1)) * 128 + r];
+      float m_new = fmaxf(m, fmaxf(mine, other) * sl2);
+      if (m_new == -INFINITY) m_new = 0.f;        // nothing visible yet (padding rows only)
       const float alpha = exp2f(m - m_new);
-      ok = mbar_wait(&a_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      alpha_s[t * 128 + r] = alpha;
-      __threadfence_block();
-      warp_arrive(&a_full[t], lane);
+      float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+      if (!(p.dbg & 1))
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        float e0 = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
+        float e2 = exp2f(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = exp2f(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
+        if (!full) {
+          if (i >= kmax) e0 = 0.f;
+          if (i + 1 >= kmax) e1 = 0.f;
+          if (i + 2 >= kmax) e2 = 0.f;
+          if (i + 3 >= kmax) e3 = 0.f;
+        }
+        ls0 += e0; ls1 += e1; ls2 += e2; ls3 += e3;
+        if (drop) {
+          const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
+          if ((uint32_t)(z & 0xFFFFu) < thr) e0 = 0.f;
+          if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) e1 = 0.f;
+          if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) e2 = 0.f;
+          if ((uint32_t)(z >> 48) < thr) e3 = 0.f;
+        }
+        rs[i >> 1] = pack_bf162(e0, e1);            // probabilities packed in place (pair i/2, i/2 + 1 are already consumed)
+        rs[(i >> 1) + 1] = pack_bf162(e2, e3);
+      }
       ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      float lsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_s + (uint32_t)(c * 32), rr);
-        tmem_ld_wait();
-        float pv[32];
+      // 64 probabilities = 128 bytes = the eight 16-byte chunks of this row in this half's panel; chunk index XOR (row % 8)
+      // is the 128-byte swizzle the MMA descriptor expects
+      if (!(p.dbg & 4))
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(fmaf(__uint_as_float(rr[i]), sl2, -m_new));
-          if (!full && c * 32 + i >= kmax) e = 0.f;
-          lsum += e;
-          pv[i] = e;
-        }
-        if (drop) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint64_t z = attn_rand4(seed, row_base, (k0 >> 2) + c * 8 + g);
-            if ((uint32_t)(z & 0xFFFFu) < thr) pv[4 * g] = 0.f;
-            if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) pv[4 * g + 1] = 0.f;
-            if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) pv[4 * g + 2] = 0.f;
-            if ((uint32_t)(z >> 48) < thr) pv[4 * g + 3] = 0.f;
-          }
-        }
-        // 32 probabilities = 64 bytes = four 16-byte chunks 4c .. 4c+3 of this row; chunk index XOR (row % 8) within
-        // its 64-key panel is the 128-byte swizzle the MMA descriptor expects
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int chunk = c * 4 + u;
-          const uint32_t addr = smem_u32(prow + (chunk >> 3) * (BQ * 128)) + (uint32_t)((((chunk & 7) ^ (r & 7))) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf162(pv[8 * u], pv[8 * u + 1])),
-                       "r"(pack_bf162(pv[8 * u + 2], pv[8 * u + 3])), "r"(pack_bf162(pv[8 * u + 4], pv[8 * u + 5])),
-                       "r"(pack_bf162(pv[8 * u + 6], pv[8 * u + 7]))
-                       : "memory");
-        }
-      }
-      tc_fence_before();
-      warp_arrive(&s_empty[t], lane);
+      for (int u = 0; u < 8; ++u)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)((u ^ (r & 7)) << 4)), "r"(rs[4 * u]), "r"(rs[4 * u + 1]),
+                     "r"(rs[4 * u + 2]), "r"(rs[4 * u + 3])
+                     : "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(p_full, lane);
-      l = l * alpha + lsum;
+      l = l * alpha + ((ls0 + ls1) + (ls2 + ls3));
       m = m_new;
+      // the previous tile's P.V has had this tile's softmax to finish under
+      if (j > 0) ok = accumulate(j - 1, alpha_pending);
+      alpha_pending = alpha;
     }
+    if (ok && n_tiles > 0) ok = accumulate(n_tiles - 1, alpha_pending);
     if (ok) {
-      // final factor of this row: 1 / (sum * keep probability); log-sum-exp for backward
+      // row sum over both halves, then out = O / (sum * keep probability); the half-0 thread stores the log-sum-exp
+      xchg[half * 128 + r] = l;
+      pair_sync(quarter);
+      const float lt = l + xchg[(half ^ 1) * 128 + r];
       const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
-      final_s[r] = l > 0.f ? inv_keep / l : 0.f;
-      if (q < p.Sq && p.lse) p.lse[((long long)(b * p.H + h)) * p.Sq + q] = l > 0.f ? m + log2f(l) : INFINITY;
-      __threadfence_block();
-      warp_arrive(fin, lane);
-    }
-  } else {
-    // ------------------------------------------------------------------ accumulate: thread = query row
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
-    const int q = q0 + r;
-    float o[D];
+      const float f = lt > 0.f ? inv_keep / lt : 0.f;
+      if (q < p.Sq) {
+        if (half == 0 && p.lse) p.lse[((long long)(b * p.H + h)) * p.Sq + q] = lt > 0.f ? m + log2f(lt) : INFINITY;
+        bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D + half * DH;
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int t = j & 1;
-      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      ok = mbar_wait(&a_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const float alpha = alpha_s[t * 128 + r];
-      warp_arrive(&a_empty[t], lane);
-      ok = mbar_wait(&o_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t t_o = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_O + t * D);
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(t_o + (uint32_t)(c * 32), rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(rr[i]));
-      }
-      tc_fence_before();
-      warp_arrive(&o_empty[t], lane);
-    }
-    if (ok) {
-      ok = mbar_wait(fin, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok && q < p.Sq) {
-      const float f = final_s[r];
-      bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D;
-#pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        uint4 v = make_uint4(pack_bf162(o[8 * c] * f, o[8 * c + 1] * f), pack_bf162(o[8 * c + 2] * f, o[8 * c + 3] * f),
-                             pack_bf162(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf162(o[8 * c + 6] * f, o[8 * c + 7] * f));
-        *reinterpret_cast<uint4 *>(orow + 8 * c) = v;
+        for (int c = 0; c < DH / 8; ++c) {
+          uint4 v = make_uint4(pack_bf162(o[8 * c] * f, o[8 * c + 1] * f), pack_bf162(o[8 * c + 2] * f, o[8 * c + 3] * f),
+                               pack_bf162(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf162(o[8 * c + 6] * f, o[8 * c + 7] * f));
+          *reinterpret_cast<uint4 *>(orow + 8 * c) = v;
+        }
       }
     }
   }
@@ -442,9 +487,13 @@ struct BwdCfg {
   static constexpr int PS_BYTES = BQ * BKB * 2;       // 16 KB: P or dS tile, [128 rows x 128 B]
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + Q_BYTES;
-  static constexpr int OFF_K = OFF_DO + Q_BYTES;      // [2]
-  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;  // [2]
-  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;  // [2]
+  // A K tile is needed from the first MMA of its step (S) to the last (dQ), a V tile only by the second (dP): with the
+  // step's shared-memory budget the K ring gets four stages and the V ring two, so that a K load is issued three steps
+  // before its first use and the load latency stays off the critical path.
+  static constexpr int NK = 4, NV = 2;
+  static constexpr int OFF_K = OFF_DO + Q_BYTES;       // [NK]
+  static constexpr int OFF_V = OFF_K + NK * KV_BYTES;  // [NV]
+  static constexpr int OFF_P = OFF_V + NV * KV_BYTES;  // [2]
   static constexpr int OFF_DS = OFF_P + 2 * PS_BYTES; // [2]
   static constexpr int OFF_BAR = OFF_DS + 2 * PS_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
@@ -458,7 +507,9 @@ struct BwdCfg {
   static constexpr uint32_t IDESC_DQ = attn_idesc(128, D, 0, 1);      // dS K
 };
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+constexpr int BWD_THREADS = 448;  // TMA warp, MMA warp, 8 dS warps, 4 read-out warps
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
   using C = BwdCfg;
@@ -467,9 +518,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
   uint64_t *q_full = bars;            // Q and dO
-  uint64_t *k_full = bars + 1;        // [2]
+  uint64_t *k_full = bars + 20;       // [NK]
+  uint64_t *k_empty = bars + 24;      // [NK] commit
   uint64_t *v_full = bars + 3;        // [2]
-  uint64_t *k_empty = bars + 5;       // [2] commit
   uint64_t *v_empty = bars + 7;       // [2] commit
   uint64_t *sdp_full = bars + 9;      // [2] commit
   uint64_t *sdp_empty = bars + 11;    // [2] 4 warps
@@ -478,7 +529,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t *dkv_full = bars + 17;     // commit
   uint64_t *dkv_empty = bars + 18;    // 4 warps
   uint64_t *dq_full = bars + 19;      // commit
-  uint32_t *tmem_slot = (uint32_t *)(bars + 20);
+  uint32_t *tmem_slot = (uint32_t *)(bars + 28);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -493,9 +544,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&sdp_empty[s], 4); mbar_init(&pds_full[s], 4); mbar_init(&pds_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&sdp_empty[s], 8); mbar_init(&pds_full[s], 8); mbar_init(&pds_empty[s], 1);
     }
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     mbar_init(dkv_full, 1); mbar_init(dkv_empty, 4); mbar_init(dq_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -518,22 +570,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_load_4d(smem_u32(smem + C::OFF_Q + c * BQ * 128), &tmQ, q_full, c * 64, q0, h, b);
         tma_load_4d(smem_u32(smem + C::OFF_DO + c * BQ * 128), &tmDO, q_full, c * 64, q0, h, b);
       }
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        ok = mbar_wait(&k_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
-        if (!ok) break;
-        mbar_expect_tx(&k_full[t], C::KV_BYTES);
+      // the K and V rings advance independently: whichever has a free stage gets its next tile; the wait for progress
+      // on either is bounded like every other wait
+      int kj = 0, vj = 0;
+      uint64_t t0 = ffk_globaltimer();
+      uint32_t spins = 0;
+      while (kj < n_tiles || vj < n_tiles) {
+        bool progress = false;
+        if (kj < n_tiles) {
+          const int t = kj % C::NK;
+          if (mbar_try_wait(&k_empty[t], ((uint32_t)(kj / C::NK) & 1u) ^ 1u)) {
+            mbar_expect_tx(&k_full[t], C::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKB * 128), &tmK, &k_full[t], c * 64, j * BKB, h, b);
-        ok = mbar_wait(&v_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_PRODUCER);
-        if (!ok) break;
-        mbar_expect_tx(&v_full[t], C::KV_BYTES);
+            for (int c = 0; c < 2; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKB * 128), &tmK, &k_full[t], c * 64, kj * BKB, h, b);
+            ++kj;
+            progress = true;
+          }
+        }
+        if (vj < n_tiles) {
+          const int t = vj % C::NV;
+          if (mbar_try_wait(&v_empty[t], ((uint32_t)(vj / C::NV) & 1u) ^ 1u)) {
+            mbar_expect_tx(&v_full[t], C::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKB * 128), &tmV, &v_full[t], c * 64, j * BKB, h, b);
+            for (int c = 0; c < 2; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKB * 128), &tmV, &v_full[t], c * 64, vj * BKB, h, b);
+            ++vj;
+            progress = true;
+          }
+        }
+        if (progress) {
+          t0 = ffk_globaltimer();
+        } else if ((++spins & 63u) == 0) {
+          if (*abort_flag) break;
+          if (ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (p.err) atomicCAS(p.err, 0, (int)FFK_ERR_TIMEOUT_PRODUCER);
+            break;
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -545,10 +620,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_sdp = [&](int j) -> bool {
         const int t = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(&k_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        const int kt = j % C::NK;
+        if (!mbar_wait(&k_full[kt], (uint32_t)(j / C::NK) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         if (!mbar_wait(&sdp_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES), sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
+        const uint32_t sk = smem_u32(smem + C::OFF_K + kt * C::KV_BYTES), sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
+        if (!(p.dbg & 32))
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
@@ -557,6 +634,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         C::IDESC_S, ks != 0 ? 1u : 0u);
         }
         if (!mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!(p.dbg & 32))
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
@@ -572,21 +650,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int t = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        attn_trace(p, 0, j);
         if (j + 1 < n_tiles) { ok = issue_sdp(j + 1); if (!ok) break; }
-        ok = mbar_wait(&pds_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
-             mbar_wait(dkv_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        attn_trace(p, 1, j);
+        ok = mbar_wait(&pds_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        attn_trace(p, 2, j);
+        ok = ok && mbar_wait(dkv_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        attn_trace(p, 3, j);
         if (!ok) break;
         tc_fence_after();
         const uint32_t sp = smem_u32(smem + C::OFF_P + t * C::PS_BYTES), sds = smem_u32(smem + C::OFF_DS + t * C::PS_BYTES);
-        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES);
+        const uint32_t sk = smem_u32(smem + C::OFF_K + (j % C::NK) * C::KV_BYTES);
         // dV_j^T [D x 64] = dO^T P and dK_j^T = Q^T dS: A = dO / Q read M-major (M = head dim: two 64-column panels, LBO = panel
         // stride), B = P / dS read N-major (N = 64 keys, one panel); every k-step is 16 query rows = 2048 bytes
+        if (!(p.dbg & 64))
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
           const uint32_t off = (uint32_t)(ks * 16 * 128);
           tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DVT, make_smem_desc(sdo + off, BQ * 128, 1024), make_smem_desc(sp + off, BQ * 128, 1024),
                         C::IDESC_T, ks != 0 ? 1u : 0u);
         }
+        if (!(p.dbg & 64))
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
           const uint32_t off = (uint32_t)(ks * 16 * 128);
@@ -595,19 +679,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_commit(dkv_full);
         // dQ += dS K_j: A = dS K-major (64 keys = one panel, 32 bytes per k-step), B = K_j N-major (N = head dim, 16 key rows per step)
+        if (!(p.dbg & 128))
 #pragma unroll
         for (int ks = 0; ks < BKB / 16; ++ks) {
           tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DQ, make_smem_desc(sds + (uint32_t)(ks * 32), 16, 1024),
                         make_smem_desc(sk + (uint32_t)(ks * 16 * 128), BKB * 128, 1024), C::IDESC_DQ, (j | ks) != 0 ? 1u : 0u);
         }
-        tc_commit(&k_empty[t]);
+        tc_commit(&k_empty[j % C::NK]);
         tc_commit(&pds_empty[t]);
+        attn_trace(p, 4, j);
       }
       if (ok) tc_commit(dq_full);
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax / dS: thread = query row
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ P and dS: thread = query row x 32 of the tile's 64 keys
+    // Eight warps, two per TMEM lane quarter (w % 4), each on one half of the key columns, so that every scheduler has two
+    // warps to switch between while tensor-memory loads and exponentials are in flight.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int q = q0 + r;
     const float sl2 = p.scale * LOG2E;
@@ -621,91 +710,90 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
     const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
     const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int t = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      ok = mbar_wait(&sdp_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
-           mbar_wait(&pds_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = mbar_wait(&sdp_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (warp == 2) attn_trace(p, 10, j);
       tc_fence_after();
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      const int k0 = j * BKB;
+      uint32_t rs[32], rd[32];
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + t * 64 + half * 32), rs);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + t * 64 + half * 32), rd);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (warp == 2) attn_trace(p, 11, j);
+      warp_arrive(&sdp_empty[t], lane);   // scores and dP are in registers
+      const int k0 = j * BKB + half * 32;
       int kmax = p.Sk - k0;
       if (p.causal) kmax = min(kmax, q - k0 + 1);
-      uint8_t *prow = smem + C::OFF_P + t * C::PS_BYTES + r * 128;
-      uint8_t *dsrow = smem + C::OFF_DS + t * C::PS_BYTES + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + t * 64 + c * 32), rs);
-        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + t * 64 + c * 32), rd);
-        tmem_ld_wait();
-        float pv[32], ds[32];
+      const bool full = kmax >= 32;
+      // rs <- packed P (dropped entries zeroed: the operand of dV), rd <- packed dS = P o (dP o mask / keep - delta)
+      if (!(p.dbg & 256))
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -lse));
-          if (c * 32 + i >= kmax) e = 0.f;
-          pv[i] = e;
-          ds[i] = __uint_as_float(rd[i]) * inv_keep;
-        }
-        if (drop) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint64_t z = attn_rand4(seed, row_base, (k0 >> 2) + c * 8 + g);
-            const bool d0 = (uint32_t)(z & 0xFFFFu) < thr, d1 = (uint32_t)((z >> 16) & 0xFFFFu) < thr;
-            const bool d2 = (uint32_t)((z >> 32) & 0xFFFFu) < thr, d3 = (uint32_t)(z >> 48) < thr;
-            // dropped: contributes nothing to dV, and its dP is zero
-            if (d0) ds[4 * g] = 0.f;
-            if (d1) ds[4 * g + 1] = 0.f;
-            if (d2) ds[4 * g + 2] = 0.f;
-            if (d3) ds[4 * g + 3] = 0.f;
-            const float p0 = pv[4 * g], p1 = pv[4 * g + 1], p2 = pv[4 * g + 2], p3 = pv[4 * g + 3];
-            ds[4 * g] = p0 * (ds[4 * g] - dlt);
-            ds[4 * g + 1] = p1 * (ds[4 * g + 1] - dlt);
-            ds[4 * g + 2] = p2 * (ds[4 * g + 2] - dlt);
-            ds[4 * g + 3] = p3 * (ds[4 * g + 3] - dlt);
-            if (d0) pv[4 * g] = 0.f;
-            if (d1) pv[4 * g + 1] = 0.f;
-            if (d2) pv[4 * g + 2] = 0.f;
-            if (d3) pv[4 * g + 3] = 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ds[i] = pv[i] * (ds[i] - dlt);
-        }
+      for (int i = 0; i < 32; i += 4) {
+        float e[4], g[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int chunk = c * 4 + u;   // 0..7 within the single 64-key panel
-          const uint32_t sw = (uint32_t)((chunk ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(prow) + sw), "r"(pack_bf162(pv[8 * u], pv[8 * u + 1])),
-                       "r"(pack_bf162(pv[8 * u + 2], pv[8 * u + 3])), "r"(pack_bf162(pv[8 * u + 4], pv[8 * u + 5])),
-                       "r"(pack_bf162(pv[8 * u + 6], pv[8 * u + 7]))
-                       : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(dsrow) + sw), "r"(pack_bf162(ds[8 * u], ds[8 * u + 1])),
-                       "r"(pack_bf162(ds[8 * u + 2], ds[8 * u + 3])), "r"(pack_bf162(ds[8 * u + 4], ds[8 * u + 5])),
-                       "r"(pack_bf162(ds[8 * u + 6], ds[8 * u + 7]))
-                       : "memory");
+          e[u] = exp2f(fmaf(__uint_as_float(rs[i + u]), sl2, -lse));
+          if (!full && i + u >= kmax) e[u] = 0.f;
+          g[u] = __uint_as_float(rd[i + u]) * inv_keep;
         }
+        if (drop) {
+          const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
+          const bool d0 = (uint32_t)(z & 0xFFFFu) < thr, d1 = (uint32_t)((z >> 16) & 0xFFFFu) < thr;
+          const bool d2 = (uint32_t)((z >> 32) & 0xFFFFu) < thr, d3 = (uint32_t)(z >> 48) < thr;
+          g[0] = e[0] * ((d0 ? 0.f : g[0]) - dlt); g[1] = e[1] * ((d1 ? 0.f : g[1]) - dlt);
+          g[2] = e[2] * ((d2 ? 0.f : g[2]) - dlt); g[3] = e[3] * ((d3 ? 0.f : g[3]) - dlt);
+          if (d0) e[0] = 0.f;
+          if (d1) e[1] = 0.f;
+          if (d2) e[2] = 0.f;
+          if (d3) e[3] = 0.f;
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) g[u] = e[u] * (g[u] - dlt);
+        }
+        rs[i >> 1] = pack_bf162(e[0], e[1]); rs[(i >> 1) + 1] = pack_bf162(e[2], e[3]);
+        rd[i >> 1] = pack_bf162(g[0], g[1]); rd[(i >> 1) + 1] = pack_bf162(g[2], g[3]);
       }
-      tc_fence_before();
-      warp_arrive(&sdp_empty[t], lane);
+      if (warp == 2) attn_trace(p, 12, j);
+      ok = mbar_wait(&pds_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (warp == 2) attn_trace(p, 13, j);
+      const uint32_t prow = smem_u32(smem + C::OFF_P + t * C::PS_BYTES + r * 128);
+      const uint32_t dsrow = smem_u32(smem + C::OFF_DS + t * C::PS_BYTES + r * 128);
+      if (!(p.dbg & 512))
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t sw = (uint32_t)(((half * 4 + u) ^ (r & 7)) << 4);   // 16-byte chunk index XOR row % 8: the 128-byte swizzle
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + sw), "r"(rs[4 * u]), "r"(rs[4 * u + 1]), "r"(rs[4 * u + 2]),
+                     "r"(rs[4 * u + 3])
+                     : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dsrow + sw), "r"(rd[4 * u]), "r"(rd[4 * u + 1]), "r"(rd[4 * u + 2]),
+                     "r"(rd[4 * u + 3])
+                     : "memory");
+      }
+      if (warp == 2) attn_trace(p, 14, j);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(&pds_full[t], lane);
+      if (warp == 2) attn_trace(p, 15, j);
     }
-    // dQ of this block: scale * accumulator -> bf16
+    // dQ of this block: scale * accumulator -> bf16; each half stores 64 of the 128 columns
     if (ok) {
       ok = mbar_wait(dq_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
-      bf16 *dqrow = p.dQ + ((long long)b * p.Sq + q) * p.lddq + (long long)h * D;
+      bf16 *dqrow = p.dQ + ((long long)b * p.Sq + q) * p.lddq + (long long)h * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t rr[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(C::TMEM_DQ + c * 32), rr);
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DQ + half * (D / 2) + c * 32), rr);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -726,34 +814,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
     float *dv_base = p.dV_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
     float *dk_base = p.dK_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       ok = mbar_wait(dkv_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (warp == 10) attn_trace(p, 20, j);
       tc_fence_after();
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
       const int k0 = j * BKB;
-      uint32_t rv[2][32], rk[2][32];
-      tmem_ld32(lane_base + (uint32_t)C::TMEM_DVT, rv[0]);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + 32), rv[1]);
-      tmem_ld32(lane_base + (uint32_t)C::TMEM_DKT, rk[0]);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + 32), rk[1]);
+      const int kn = (p.dbg & 1024) ? 0 : min(BKB, p.Sk - k0);
+      uint32_t ra[32], rb[32];
+      // dV^T first (adds issued while the dK^T columns are being fetched), then dK^T; the accumulators are released as soon
+      // as the last of them is in registers
+      tmem_ld32(lane_base + (uint32_t)C::TMEM_DVT, ra);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + 32), rb);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < kn) atomicAdd(dv_base + (long long)(k0 + i) * D, __uint_as_float(ra[i]) * inv_keep);
+      tmem_ld32(lane_base + (uint32_t)C::TMEM_DKT, ra);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (32 + i < kn) atomicAdd(dv_base + (long long)(k0 + 32 + i) * D, __uint_as_float(rb[i]) * inv_keep);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + 32), rb);
       tmem_ld_wait();
       tc_fence_before();
       warp_arrive(dkv_empty, lane);
-      const int kn = min(BKB, p.Sk - k0);
+      if (warp == 10) attn_trace(p, 21, j);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int i = 0; i < 32; ++i)
+        if (i < kn) atomicAdd(dk_base + (long long)(k0 + i) * D, __uint_as_float(ra[i]) * p.scale);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kk = c * 32 + i;
-          if (kk < kn) {
-            atomicAdd(dv_base + (long long)(k0 + kk) * D, __uint_as_float(rv[c][i]) * inv_keep);
-            atomicAdd(dk_base + (long long)(k0 + kk) * D, __uint_as_float(rk[c][i]) * p.scale);
-          }
-        }
-      }
+      for (int i = 0; i < 32; ++i)
+        if (32 + i < kn) atomicAdd(dk_base + (long long)(k0 + 32 + i) * D, __uint_as_float(rb[i]) * p.scale);
     }
   }
 
@@ -828,6 +922,7 @@ FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
+  { const char *e = getenv("FFK_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
   const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
   if (grid > 0x7fffffffll) return -2;
   if (d->D == 128) {
@@ -882,6 +977,7 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
+  { const char *e = getenv("FFK_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
   static bool attr = false;
   if (!attr) {
     e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::SMEM_BYTES);
@@ -890,11 +986,23 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   }
   const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
   if (grid > 0x7fffffffll) return -2;
-  attn_bwd_kernel<<<(unsigned)grid, ATT_THREADS, BwdCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<(unsigned)grid, BWD_THREADS, BwdCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
   const int cblocks = ffk_blocks(n_acc / 4, 256);
   attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dK_acc, (bf16 *)d->dK, d->lddk, d->B, d->H, d->Sk);
   attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dV_acc, (bf16 *)d->dV, d->lddv, d->B, d->H, d->Sk);
   return (int)cudaGetLastError();
+}
+
+// Copies out (and clears) the timeline recorded under experiment switch 4096: up to 2048 (event, step, clock) triples.
+// Returns the number of events.  Synchronises the device.
+FFK_API int ffk_attention_trace(long long *host_out) {
+  unsigned int n = 0, z = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  cudaMemcpyFromSymbol(&n, g_attn_trace_n, sizeof(n));
+  if (n > 2048) n = 2048;
+  cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * 3 * n);
+  cudaMemcpyToSymbol(g_attn_trace_n, &z, sizeof(z));
+  return (int)n;
 }
 
 // Reads (and clears) the error word of the attention kernels' bounded waits.  Synchronises the device.

@@ -143,6 +143,35 @@ def test_run_model_ignores_runtime_resource_flags_and_their_values(tmp_path, cap
         run_model.main(args + ["--no-such-flag"])
 
 
+def test_search_model_emits_strategy_estimate_and_cpu_step(tmp_path, capsys):
+    """CPU-only compile + Unity search from the unparallelised graph on a small Transformer for 4 simulated GPUs: writes the
+    strategy, prints the estimated step time and trains one step on the host."""
+    import json
+
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.bin import search_model
+
+    cfg = '{"num_encoder_layers": 1, "num_decoder_layers": 1, "num_features": 256, "sequence_length": 128, "batch_size": 64, ' \
+          '"dim_feedforward": 1024, "vocab_size": 64}'
+    out = tmp_path / "strategy.json"
+    args = ["--model", "transformer", "--model-config", cfg, "--heads", "4", "--gpus", "4", "--budget", "3", "--time-limit", "60",
+            "--seed", "0", "--out", str(out), "--cpu-step"]
+    assert search_model.main(args) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    c = rec["search"]["candidates"]
+    # the search started at the serial graph and found a plan at least as good as the hand-built data-parallel template
+    assert rec["search"]["search_start"] == "serial" and rec["search"]["unity"]["evaluated"] > 10
+    assert rec["estimated_step_ms"] <= min(c.values()) * 1.0001 and rec["search"]["unity"]["runtime_ms"] <= c["dp4"] * 1.0001
+    assert rec["estimated_step_ms"] < c["single_device"]
+    g = core.Graph.from_v1(out.read_text())
+    assert g.is_mapped() and any(core.is_parallel_op(n["type"]) for n in g.nodes())
+    assert rec["cpu_step"]["loss_after_one_update"] < rec["cpu_step"]["loss"]
+    # the same seed gives the same answer
+    assert search_model.main(args[:-1]) == 0
+    again = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert again["estimated_step_ms"] == rec["estimated_step_ms"]
+
+
 def test_bench_contract_pieces_that_need_no_gpu():
     """`bench.py --impl reference` prints the one-line unavailable record and exits 0; the clock sampler degrades to a
     record with no samples when neither NVML nor nvidia-smi can be read."""
