@@ -169,75 +169,147 @@ def reference_arm(args):
 
 
 def torch_arm(args):
-    """Library baseline on one GPU: the same computation graph evaluated with stock PyTorch operators (cuBLAS /
-    cuDNN / the library attention kernel) under bf16 autocast with fp32 master weights and torch.optim, fed and
-    timed the same way.  None of this repository's kernels or executors are on this path."""
+    """Library baseline (B1): the same model, data and step contents in stock PyTorch -- cuBLAS / cuDNN / the library
+    attention kernel under bf16 autocast with fp32 parameters and torch.optim, one process per GPU with gradients
+    averaged across ranks (DistributedDataParallel for the module-based Transformer, one flat all-reduce for the
+    graph-interpreted models).  None of this repository's kernels or executors are on this path."""
     import torch
-    from flexflow_train_b200 import _ffcore as core
-    from flexflow_train_b200.bin.run_model import synthetic_batch
-    from flexflow_train_b200.runtime.torch_oracle import TorchOracle
+    import torch.distributed as dist
 
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
-        print(json.dumps({"impl": "torch", "unavailable": "the PyTorch library baseline is single-GPU"}))
-        return 0
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     model_name, mcfg = MODEL_CONFIGS[args.model]
+    mcfg = dict(mcfg)
     opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
-    g = core.build_model(model_name, dict(mcfg))
+    if global_batch % world:
+        raise SystemExit(f"global batch {global_batch} does not divide over {world} ranks")
+    local_batch = global_batch // world
+    warmup = max(args.warmup, 3)
+    gen = torch.Generator().manual_seed(1234 + rank)
     try:
-        orc = TorchOracle(g, loss=loss_kind, seed=0, device="cuda", dropout=True)
-        orc.use_sdpa = True
-        params = list(orc.params.values())
+        if model_name == "transformer_lm":
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import torch_models
+            torch.manual_seed(0)
+            net = torch_models.build_transformer_lm(mcfg).cuda()
+            params = list(net.parameters())
+            mod = torch.nn.parallel.DistributedDataParallel(net, device_ids=[local_rank], gradient_as_bucket_view=True) if world > 1 else net
+            vocab = mcfg["vocab_size"]
+            host = [(torch.randint(0, vocab, (local_batch, seq), generator=gen, dtype=torch.int64).pin_memory(),
+                     torch.randint(0, vocab, (local_batch, seq), generator=gen, dtype=torch.int64).pin_memory()) for _ in range(4)]
+
+            def fwd_bwd(ids, lab):
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = mod(ids, lab)
+                loss.backward()
+                return loss
+        else:
+            from flexflow_train_b200 import _ffcore as core
+            from flexflow_train_b200.bin.run_model import synthetic_batch
+            from flexflow_train_b200.runtime.torch_oracle import TorchOracle
+            g = core.build_model(model_name, dict(mcfg, batch_size=local_batch))
+            orc = TorchOracle(g, loss=loss_kind, seed=0, device="cuda", dropout=True)
+            orc.use_sdpa = True
+            params = list(orc.params.values())
+            channels_last = model_name == "inception_v3"
+            if channels_last:  # what a PyTorch user does for convolution networks on tensor cores
+                for prm in params:
+                    if prm.dim() == 4:
+                        prm.data = prm.data.contiguous(memory_format=torch.channels_last)
+
+            class _Shape:  # the batch generator only needs the loss value of the graph
+                loss_value = orc.loss_value
+                graph = g
+            host = [synthetic_batch(g, _Shape, loss_kind, seed=1234 + 17 * rank + i) for i in range(4)]
+            if "vocab_size" in mcfg:
+                for ins, lab in host:
+                    lab.copy_(torch.randint(0, mcfg["vocab_size"], lab.shape, generator=gen, dtype=lab.dtype))
+
+            def fwd_bwd(ins, lab):
+                if channels_last:
+                    ins = {k: (v.contiguous(memory_format=torch.channels_last) if v.dim() == 4 else v) for k, v in ins.items()}
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    pred = orc.forward(ins)
+                loss = orc.loss(pred.float(), lab).mean()
+                loss.backward()
+                if world > 1:  # data parallel: one flat all-reduce of the gradients
+                    grads = [prm.grad for prm in params if prm.grad is not None]
+                    flat = torch._utils._flatten_dense_tensors(grads)
+                    dist.all_reduce(flat)
+                    flat.div_(world)
+                    for gr, fl in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                        gr.copy_(fl)
+                return loss
         opt = torch.optim.Adam(params, lr=lr, fused=True) if opt_kind == "adam" else torch.optim.SGD(params, lr=lr, momentum=momentum)
 
-        class _Shape:  # the batch generator only needs the loss value of the graph
-            loss_value = orc.loss_value
-        host = [synthetic_batch(g, _Shape, loss_kind, seed=1234 + i) for i in range(4)]
-        if "vocab_size" in mcfg:
-            gen = torch.Generator().manual_seed(1234)
-            for i, (ins, lab) in enumerate(host):
-                lab.copy_(torch.randint(0, mcfg["vocab_size"], lab.shape, generator=gen, dtype=lab.dtype))
-        dev = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host]
+        def to_dev(batch):
+            a, b_ = batch
+            if isinstance(a, dict):
+                return {k: v.cuda(non_blocking=True) for k, v in a.items()}, b_.cuda(non_blocking=True)
+            return a.cuda(non_blocking=True), b_.cuda(non_blocking=True)
 
-        def step(ins, lab):
+        def step(batch):
             opt.zero_grad(set_to_none=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                pred = orc.forward(ins)
-            loss = orc.loss(pred.float(), lab).mean()
-            loss.backward()
+            loss = fwd_bwd(*batch)
             opt.step()
             return loss
 
-        for i in range(max(args.warmup, 3)):
-            step(*dev[i % 4])
-        torch.cuda.synchronize()
-        sampler = ClockSampler(0)
-        sampler.start()
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        dev = [to_dev(hb) for hb in host]
+        for i in range(warmup):
+            step(dev[i % 4])
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
         e0.record()
         for i in range(args.steps):
-            step(*dev[i % 4])
+            step(dev[i % 4])
         e1.record()
-        torch.cuda.synchronize()
+        barrier()
         ms = e0.elapsed_time(e1) / args.steps
-        clocks = sampler.stop()
+        clocks = sampler.stop() if rank == 0 else None
+        # end to end: pinned host batch -> device and loss -> host every step
+        barrier()
         t0 = time.perf_counter()
         for i in range(args.steps):
-            ins, lab = host[i % 4]
-            loss = step({k: v.cuda(non_blocking=True) for k, v in ins.items()}, lab.cuda(non_blocking=True))
+            loss = step(to_dev(host[i % 4]))
             float(loss)
-        torch.cuda.synchronize()
+        barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        h2d = sum(t.numel() * t.element_size() for t in (list(host[0][0].values()) if isinstance(host[0][0], dict) else [host[0][0]])) + \
+            host[0][1].numel() * host[0][1].element_size()
     except torch.OutOfMemoryError as e:
         print(json.dumps({"impl": "torch", "unavailable": f"out of memory on this config: {str(e)[:120]}"}))
         return 0
-    print(json.dumps({"metric": "train samples/s (searched strategy)", "value": global_batch / (ms / 1e3), "unit": "samples/s",
-                      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast", "data": "synthetic", "impl": "torch",
-                      "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "parallelism": "single",
-                                 "optimizer": opt_kind, "lr": lr}, "clocks": clocks,
-                      "e2e": {"value": global_batch / (e2e_ms / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms},
-                      "gpu_launches": 0, "final_loss": float(loss)}))
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        print(json.dumps({"metric": "train samples/s (searched strategy)", "value": global_batch / (ms / 1e3), "unit": "samples/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast", "data": "synthetic", "impl": "torch",
+                          "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq,
+                                     "parallelism": f"ddp{world}" if world > 1 else "single", "optimizer": opt_kind, "lr": lr},
+                          "clocks": clocks,
+                          "e2e": {"value": global_batch / (e2e_ms / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+                          "gpu_launches": 0, "final_loss": float(loss)}))
+    if world > 1:
+        dist.destroy_process_group()
     return 0
 
 
@@ -312,6 +384,16 @@ def main():
         host_batches = [synthetic_batch(model.graph, ex, loss_kind, seed=1234 + i) for i in range(n_host)]
         if model_name == "dlrm":  # binary labels
             host_batches = [(i, (l > 0.5).to(l.dtype).pin_memory()) for i, l in host_batches]
+    # Inputs that the strategy splits over the sample dimension are handed to each rank as its own piece (every rank
+    # draws the same global batch from the same seed and keeps its rows), so the host-to-device traffic per rank shrinks
+    # with the number of ranks; anything else (an input a tensor-parallel plan replicates) is passed whole.
+    direct = set(getattr(ex, "direct_inputs", {}))
+    if world > 1 and direct:
+        lb = global_batch // world
+
+        def rows(t):
+            return t[rank * lb:(rank + 1) * lb].contiguous().pin_memory()
+        host_batches = [({k: (rows(v) if k in direct else v) for k, v in i.items()}, rows(l.reshape(global_batch, -1))) for i, l in host_batches]
     dev_batches = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host_batches]
 
     def barrier():

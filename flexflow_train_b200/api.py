@@ -44,6 +44,7 @@ class FFConfig:
     compute_dtype: str = "bf16"
     use_cuda_graph: bool = True
     fuse_collectives: bool = True  # run all-gather / reduce-scatter inside the neighbouring GEMMs (else NCCL)
+    shard_inputs: bool = True      # several ranks: an input split over the sample dim may be fed as each rank's own piece
     seed: int = 0
 
 
@@ -130,7 +131,7 @@ def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None
         from .compiler.strategy import choose_strategy
         strategy, stats = choose_strategy(cg, world, config)
         from .parallel.dist_executor import DistExecutable
-        ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives)
+        ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives, shard_inputs=config.shard_inputs)
     else:
         if config.import_strategy_file:
             with open(config.import_strategy_file) as f:

@@ -204,8 +204,7 @@ def hybrid_strategy(cg, dp: int, tp: int, rules=None):
     so that it meets the next operator's Repartition(0, dp) and cancels; what remains is one Repartition of the
     inputs, one Combine of the output and the tensor-parallel collectives inside each data-parallel replica.
 
-    The single-axis SPMD executor does not run such a graph; the strategy can be scored, searched from, exported and
-    imported."""
+    The distributed executor runs such a graph on a dp x tp device mesh (rank = i_dp * tp + i_tp)."""
     world = dp * tp
     ms = machine_for(world)
     rules = rules or core.get_substitution_set(ms)
@@ -287,19 +286,17 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
                 pass
             if has_stacked_embeddings(cg):
                 cands[f"dp{W}+tables_mp{W}"] = table_parallel_strategy(cg, W, rules)
-    scored = {k: core.evaluate_pcg(g, machine, estimator) for k, g in cands.items()}
-    # data x tensor parallel meshes: scored for the report (and exportable through hybrid_strategy), never chosen,
-    # because the single-axis executor cannot run them
-    hybrid_scores = {}
-    if score_hybrid and W >= 4 and f"tp{W}" in cands:
+    # data x tensor parallel meshes (the executor runs them on a dp x tp device mesh)
+    if W >= 4 and f"tp{W}" in cands and not only_data_parallel and algorithm in ("unity", "mcmc"):
         tp = 2
         while tp < W:
             if W % tp == 0:
                 try:
-                    hybrid_scores[f"dp{W // tp}xtp{tp}"] = core.evaluate_pcg(hybrid_strategy(cg, W // tp, tp, rules), machine, estimator)["runtime_ms"]
+                    cands[f"dp{W // tp}xtp{tp}"] = hybrid_strategy(cg, W // tp, tp, rules)
                 except Exception:
                     pass
             tp *= 2
+    scored = {k: core.evaluate_pcg(g, machine, estimator) for k, g in cands.items()}
     if algorithm == "data_parallel" or only_data_parallel:
         best_name = f"dp{W}" if W > 1 else "single_device"
     elif algorithm == "tensor_parallel":
@@ -310,8 +307,6 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
         best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
     best = scored[best_name]
     stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
-    if hybrid_scores:
-        stats["hybrid_candidates_not_executable"] = hybrid_scores
     origin = scored["single_device"] if start == "serial" else best
     stats["search_start"] = "serial" if start == "serial" else best_name
     if algorithm == "unity" and budget > 0 and W > 1:

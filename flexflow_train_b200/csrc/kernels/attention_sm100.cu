@@ -60,14 +60,11 @@ struct AttnArgs {
   int dbg;                // experiment switches (FFK_ATTN_DBG): parts of the kernel left out to time the rest
 };
 
-// Timeline of one CTA (experiment switch 4096): (event, step, SM clock) triples written by the roles' first lanes.
-__device__ unsigned int g_attn_trace_n = 0;
-__device__ long long g_attn_trace[3 * 2048];
+// Timeline of one CTA (experiment switch 4096): SM clock at event `ev` (0..31) of step `j` (0..63), one slot each, written
+// with a plain store by the roles' first lanes.
+__device__ long long g_attn_trace[32 * 64];
 __device__ __forceinline__ void attn_trace(const AttnArgs &p, int ev, int j) {
-  if ((p.dbg & 4096) && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
-    const unsigned int i = atomicAdd(&g_attn_trace_n, 1u);
-    if (i < 2048) { g_attn_trace[3 * i] = ev; g_attn_trace[3 * i + 1] = j; g_attn_trace[3 * i + 2] = clock64(); }
-  }
+  if ((p.dbg & 4096) && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && j < 64) g_attn_trace[ev * 64 + j] = clock64();
 }
 
 __device__ __forceinline__ unsigned long long attn_seed(const AttnArgs &p) {
@@ -227,21 +224,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
-      const uint32_t sq = smem_u32(smem + C::OFF_Q);
+      // descriptors are built once; an MMA then costs two adds
+      const uint64_t dq = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024);
+      const uint64_t dp = make_smem_desc(smem_u32(smem + C::OFF_P), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(smem + C::OFF_V), BKF * 128, 1024);
       auto issue_s = [&](int j) -> bool {
         const int t = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         if (!mbar_wait(&k_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         if (!mbar_wait(&s_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + C::OFF_K + t * C::KV_BYTES);
+        const uint64_t dk = desc_advance(dk0, (uint32_t)(t * C::KV_BYTES));
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
         if (!(p.dbg & 16)) {
+          tc_mma_bf16<false>(d_tmem, dq, dk, C::IDESC_S);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);   // panel, then 32 bytes per k-step
-          tc_mma<false>(d_tmem, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), C::IDESC_S, ks != 0 ? 1u : 0u);
-        }
+          for (int ks = 1; ks < D / 16; ++ks) {
+            const uint32_t off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);   // panel, then 32 bytes per k-step
+            tc_mma_bf16<true>(d_tmem, desc_advance(dq, off), desc_advance(dk, off), C::IDESC_S);
+          }
         }
         tc_commit(&s_full[t]);
         tc_commit(&k_empty[t]);
@@ -258,17 +260,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
              mbar_wait(&o_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sp = smem_u32(smem + C::OFF_P);
-        const uint32_t sv = smem_u32(smem + C::OFF_V + vt * C::KV_BYTES);
+        const uint64_t dv = desc_advance(dv0, (uint32_t)(vt * C::KV_BYTES));
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
-        if (!(p.dbg & 2))
-#pragma unroll
-        for (int ks = 0; ks < BKF / 16; ++ks) {
+        if (!(p.dbg & 2)) {
           // A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
-          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-          const uint32_t b_off = (uint32_t)(ks * 16 * 128);
-          tc_mma<false>(d_tmem, make_smem_desc(sp + a_off, 16, 1024), make_smem_desc(sv + b_off, BKF * 128, 1024), C::IDESC_PV,
-                        ks != 0 ? 1u : 0u);
+          tc_mma_bf16<false>(d_tmem, dp, dv, C::IDESC_PV);
+#pragma unroll
+          for (int ks = 1; ks < BKF / 16; ++ks) {
+            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+            const uint32_t b_off = (uint32_t)(ks * 16 * 128);
+            tc_mma_bf16<true>(d_tmem, desc_advance(dp, a_off), desc_advance(dv, b_off), C::IDESC_PV);
+          }
         }
         tc_commit(&o_full[t]);
         tc_commit(&v_empty[vt]);
@@ -497,17 +499,20 @@ struct BwdCfg {
   static constexpr int OFF_DS = OFF_P + 2 * PS_BYTES; // [2]
   static constexpr int OFF_BAR = OFF_DS + 2 * PS_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int TMEM_S = 0;      // S[t] at t*64
-  static constexpr int TMEM_DP = 128;   // dP[t] at 128 + t*64
-  static constexpr int TMEM_DVT = 256;  // 64 columns
-  static constexpr int TMEM_DKT = 320;  // 64 columns
+  // Tensor memory.  S and dP are copied into registers the moment they are complete, so one stage each is enough; dV^T and
+  // dK^T stay until four warps have added them to global memory, so they get two stages and the tensor core never waits
+  // for that read-out.
+  static constexpr int TMEM_S = 0;      // 64 columns
+  static constexpr int TMEM_DP = 64;    // 64 columns
+  static constexpr int TMEM_DVT = 128;  // dV^T[u] at 128 + u * 128 (64 columns)
+  static constexpr int TMEM_DKT = 192;  // dK^T[u] at 192 + u * 128 (64 columns)
   static constexpr int TMEM_DQ = 384;   // 128 columns
   static constexpr uint32_t IDESC_S = attn_idesc(128, BKB, 0, 0);     // Q K^T, dO V^T
   static constexpr uint32_t IDESC_T = attn_idesc(128, BKB, 1, 1);     // dO^T P, Q^T dS   (both operands MN-major)
   static constexpr uint32_t IDESC_DQ = attn_idesc(128, D, 0, 1);      // dS K
 };
 
-constexpr int BWD_THREADS = 448;  // TMA warp, MMA warp, 8 dS warps, 4 read-out warps
+constexpr int BWD_THREADS = 576;  // TMA warp, MMA warp, 8 dS warps, 8 read-out warps
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -518,18 +523,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
   uint64_t *q_full = bars;            // Q and dO
-  uint64_t *k_full = bars + 20;       // [NK]
-  uint64_t *k_empty = bars + 24;      // [NK] commit
-  uint64_t *v_full = bars + 3;        // [2]
-  uint64_t *v_empty = bars + 7;       // [2] commit
-  uint64_t *sdp_full = bars + 9;      // [2] commit
-  uint64_t *sdp_empty = bars + 11;    // [2] 4 warps
-  uint64_t *pds_full = bars + 13;     // [2] 4 warps
-  uint64_t *pds_empty = bars + 15;    // [2] commit
-  uint64_t *dkv_full = bars + 17;     // commit
-  uint64_t *dkv_empty = bars + 18;    // 4 warps
-  uint64_t *dq_full = bars + 19;      // commit
-  uint32_t *tmem_slot = (uint32_t *)(bars + 28);
+  uint64_t *v_full = bars + 1;        // [2]
+  uint64_t *v_empty = bars + 3;       // [2] commit
+  uint64_t *sdp_full = bars + 5;      // commit
+  uint64_t *sdp_empty = bars + 6;     // 8 warps
+  uint64_t *pds_full = bars + 7;      // [2] 8 warps
+  uint64_t *pds_empty = bars + 9;     // [2] commit
+  uint64_t *dkv_full = bars + 11;     // [2] commit
+  uint64_t *dkv_empty = bars + 13;    // [2] 4 warps
+  uint64_t *dq_full = bars + 15;      // commit
+  uint64_t *k_full = bars + 16;       // [NK]
+  uint64_t *k_empty = bars + 20;      // [NK] commit
+  uint32_t *tmem_slot = (uint32_t *)(bars + 24);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -545,10 +550,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&sdp_empty[s], 8); mbar_init(&pds_full[s], 8); mbar_init(&pds_empty[s], 1);
+      mbar_init(&pds_full[s], 8); mbar_init(&pds_empty[s], 1); mbar_init(&dkv_full[s], 1); mbar_init(&dkv_empty[s], 8);
     }
     for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    mbar_init(dkv_full, 1); mbar_init(dkv_empty, 4); mbar_init(dq_full, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(dq_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -615,34 +620,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
-      const uint32_t sq = smem_u32(smem + C::OFF_Q), sdo = smem_u32(smem + C::OFF_DO);
-      // S[t] = Q K_j^T and dP[t] = dO V_j^T : K-major operands, k-steps of 16 head-dim columns
+      // descriptors are built once; an MMA then costs two adds
+      const uint64_t dqA = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024), ddoA = make_smem_desc(smem_u32(smem + C::OFF_DO), 16, 1024);
+      const uint64_t dqT = make_smem_desc(smem_u32(smem + C::OFF_Q), BQ * 128, 1024), ddoT = make_smem_desc(smem_u32(smem + C::OFF_DO), BQ * 128, 1024);
+      const uint64_t dkB0 = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024), dkN0 = make_smem_desc(smem_u32(smem + C::OFF_K), BKB * 128, 1024);
+      const uint64_t dvB0 = make_smem_desc(smem_u32(smem + C::OFF_V), 16, 1024);
+      const uint64_t dpN0 = make_smem_desc(smem_u32(smem + C::OFF_P), BQ * 128, 1024), ddsN0 = make_smem_desc(smem_u32(smem + C::OFF_DS), BQ * 128, 1024);
+      const uint64_t ddsA0 = make_smem_desc(smem_u32(smem + C::OFF_DS), 16, 1024);
+      // S = Q K_j^T and dP = dO V_j^T : K-major operands, k-steps of 16 head-dim columns
       auto issue_sdp = [&](int j) -> bool {
         const int t = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const int kt = j % C::NK;
         if (!mbar_wait(&k_full[kt], (uint32_t)(j / C::NK) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
-        if (!mbar_wait(&sdp_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(sdp_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + C::OFF_K + kt * C::KV_BYTES), sv = smem_u32(smem + C::OFF_V + t * C::KV_BYTES);
-        if (!(p.dbg & 32))
+        const uint64_t dkB = desc_advance(dkB0, (uint32_t)(kt * C::KV_BYTES)), dvB = desc_advance(dvB0, (uint32_t)(t * C::KV_BYTES));
+        if (!(p.dbg & 32)) {
+          tc_mma_bf16<false>(tmem_base + (uint32_t)C::TMEM_S, dqA, dkB, C::IDESC_S);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-          const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
-          tc_mma<false>(tmem_base + (uint32_t)(C::TMEM_S + t * 64), make_smem_desc(sq + a_off, 16, 1024), make_smem_desc(sk + b_off, 16, 1024),
-                        C::IDESC_S, ks != 0 ? 1u : 0u);
+          for (int ks = 1; ks < D / 16; ++ks) {
+            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+            const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
+            tc_mma_bf16<true>(tmem_base + (uint32_t)C::TMEM_S, desc_advance(dqA, a_off), desc_advance(dkB, b_off), C::IDESC_S);
+          }
         }
         if (!mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
-        if (!(p.dbg & 32))
+        if (!(p.dbg & 32)) {
+          tc_mma_bf16<false>(tmem_base + (uint32_t)C::TMEM_DP, ddoA, dvB, C::IDESC_S);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-          const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
-          tc_mma<false>(tmem_base + (uint32_t)(C::TMEM_DP + t * 64), make_smem_desc(sdo + a_off, 16, 1024), make_smem_desc(sv + b_off, 16, 1024),
-                        C::IDESC_S, ks != 0 ? 1u : 0u);
+          for (int ks = 1; ks < D / 16; ++ks) {
+            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
+            const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
+            tc_mma_bf16<true>(tmem_base + (uint32_t)C::TMEM_DP, desc_advance(ddoA, a_off), desc_advance(dvB, b_off), C::IDESC_S);
+          }
         }
-        tc_commit(&sdp_full[t]);
+        tc_commit(sdp_full);
         tc_commit(&v_empty[t]);
         return true;
       };
@@ -655,35 +668,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         attn_trace(p, 1, j);
         ok = mbar_wait(&pds_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         attn_trace(p, 2, j);
-        ok = ok && mbar_wait(dkv_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        ok = ok && mbar_wait(&dkv_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         attn_trace(p, 3, j);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sp = smem_u32(smem + C::OFF_P + t * C::PS_BYTES), sds = smem_u32(smem + C::OFF_DS + t * C::PS_BYTES);
-        const uint32_t sk = smem_u32(smem + C::OFF_K + (j % C::NK) * C::KV_BYTES);
+        const uint64_t dpN = desc_advance(dpN0, (uint32_t)(t * C::PS_BYTES)), ddsN = desc_advance(ddsN0, (uint32_t)(t * C::PS_BYTES));
+        const uint64_t ddsA = desc_advance(ddsA0, (uint32_t)(t * C::PS_BYTES));
+        const uint64_t dkN = desc_advance(dkN0, (uint32_t)((j % C::NK) * C::KV_BYTES));
         // dV_j^T [D x 64] = dO^T P and dK_j^T = Q^T dS: A = dO / Q read M-major (M = head dim: two 64-column panels, LBO = panel
         // stride), B = P / dS read N-major (N = 64 keys, one panel); every k-step is 16 query rows = 2048 bytes
-        if (!(p.dbg & 64))
+        if (!(p.dbg & 64)) {
+          const uint32_t dvt = tmem_base + (uint32_t)(C::TMEM_DVT + t * 128), dkt = tmem_base + (uint32_t)(C::TMEM_DKT + t * 128);
+          tc_mma_bf16<false>(dvt, ddoT, dpN, C::IDESC_T);
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {
-          const uint32_t off = (uint32_t)(ks * 16 * 128);
-          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DVT, make_smem_desc(sdo + off, BQ * 128, 1024), make_smem_desc(sp + off, BQ * 128, 1024),
-                        C::IDESC_T, ks != 0 ? 1u : 0u);
-        }
-        if (!(p.dbg & 64))
+          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(dvt, desc_advance(ddoT, ks * 2048u), desc_advance(dpN, ks * 2048u), C::IDESC_T);
+          tc_mma_bf16<false>(dkt, dqT, ddsN, C::IDESC_T);
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {
-          const uint32_t off = (uint32_t)(ks * 16 * 128);
-          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DKT, make_smem_desc(sq + off, BQ * 128, 1024), make_smem_desc(sds + off, BQ * 128, 1024),
-                        C::IDESC_T, ks != 0 ? 1u : 0u);
+          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(dkt, desc_advance(dqT, ks * 2048u), desc_advance(ddsN, ks * 2048u), C::IDESC_T);
         }
-        tc_commit(dkv_full);
+        tc_commit(&dkv_full[t]);
         // dQ += dS K_j: A = dS K-major (64 keys = one panel, 32 bytes per k-step), B = K_j N-major (N = head dim, 16 key rows per step)
-        if (!(p.dbg & 128))
+        if (!(p.dbg & 128)) {
+          const uint32_t dqt = tmem_base + (uint32_t)C::TMEM_DQ;
+          if (j == 0) tc_mma_bf16<false>(dqt, ddsA, dkN, C::IDESC_DQ);
+          else tc_mma_bf16<true>(dqt, ddsA, dkN, C::IDESC_DQ);
 #pragma unroll
-        for (int ks = 0; ks < BKB / 16; ++ks) {
-          tc_mma<false>(tmem_base + (uint32_t)C::TMEM_DQ, make_smem_desc(sds + (uint32_t)(ks * 32), 16, 1024),
-                        make_smem_desc(sk + (uint32_t)(ks * 16 * 128), BKB * 128, 1024), C::IDESC_DQ, (j | ks) != 0 ? 1u : 0u);
+          for (int ks = 1; ks < BKB / 16; ++ks) tc_mma_bf16<true>(dqt, desc_advance(ddsA, ks * 32u), desc_advance(dkN, ks * 2048u), C::IDESC_DQ);
         }
         tc_commit(&k_empty[j % C::NK]);
         tc_commit(&pds_empty[t]);
@@ -715,18 +725,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int t = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      ok = mbar_wait(&sdp_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = mbar_wait(sdp_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (warp == 2) attn_trace(p, 10, j);
       tc_fence_after();
       uint32_t rs[32], rd[32];
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + t * 64 + half * 32), rs);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + t * 64 + half * 32), rd);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + half * 32), rs);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + half * 32), rd);
       tmem_ld_wait();
       tc_fence_before();
       if (warp == 2) attn_trace(p, 11, j);
-      warp_arrive(&sdp_empty[t], lane);   // scores and dP are in registers
+      warp_arrive(sdp_empty, lane);       // scores and dP are in registers
       const int k0 = j * BKB + half * 32;
       int kmax = p.Sk - k0;
       if (p.causal) kmax = min(kmax, q - k0 + 1);
@@ -809,7 +819,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------------ read-out of dV_j^T / dK_j^T: thread = head-dim index
+    // Eight warps: TMEM lane quarter w % 4 (= 32 head-dim indices) and 32 of the tile's 64 keys each.  A warp-wide add
+    // covers 32 consecutive floats of one key's row in the fp32 accumulators.
     const int quarter = warp & 3;
+    const int half = (warp - 10) >> 2;
     const int dcol = quarter * 32 + lane;
     const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
     float *dv_base = p.dV_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
@@ -817,37 +830,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = mbar_wait(dkv_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      const int t = j & 1;
+      ok = mbar_wait(&dkv_full[t], (uint32_t)(j >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (warp == 10) attn_trace(p, 20, j);
       tc_fence_after();
-      const int k0 = j * BKB;
-      const int kn = (p.dbg & 1024) ? 0 : min(BKB, p.Sk - k0);
+      const int k0 = j * BKB + half * 32;
+      const int kn = (p.dbg & 1024) ? 0 : min(32, p.Sk - k0);
       uint32_t ra[32], rb[32];
-      // dV^T first (adds issued while the dK^T columns are being fetched), then dK^T; the accumulators are released as soon
-      // as the last of them is in registers
-      tmem_ld32(lane_base + (uint32_t)C::TMEM_DVT, ra);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + 32), rb);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < kn) atomicAdd(dv_base + (long long)(k0 + i) * D, __uint_as_float(ra[i]) * inv_keep);
-      tmem_ld32(lane_base + (uint32_t)C::TMEM_DKT, ra);
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (32 + i < kn) atomicAdd(dv_base + (long long)(k0 + 32 + i) * D, __uint_as_float(rb[i]) * inv_keep);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + 32), rb);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + t * 128 + half * 32), ra);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + t * 128 + half * 32), rb);
       tmem_ld_wait();
       tc_fence_before();
-      warp_arrive(dkv_empty, lane);
+      warp_arrive(&dkv_empty[t], lane);
       if (warp == 10) attn_trace(p, 21, j);
+      float *dvp = dv_base + (long long)k0 * D, *dkp = dk_base + (long long)k0 * D;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (i < kn) atomicAdd(dk_base + (long long)(k0 + i) * D, __uint_as_float(ra[i]) * p.scale);
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (32 + i < kn) atomicAdd(dk_base + (long long)(k0 + 32 + i) * D, __uint_as_float(rb[i]) * p.scale);
+        if (i < kn) {
+          atomicAdd(dvp + i * D, __uint_as_float(ra[i]) * inv_keep);
+          atomicAdd(dkp + i * D, __uint_as_float(rb[i]) * p.scale);
+        }
+      if (warp == 10) attn_trace(p, 22, j);
     }
   }
 
@@ -993,16 +998,14 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
-// Copies out (and clears) the timeline recorded under experiment switch 4096: up to 2048 (event, step, clock) triples.
-// Returns the number of events.  Synchronises the device.
+// Copies out the timeline recorded under experiment switch 4096: 32 events x 64 steps of SM clock values (0 = not reached).
+// Synchronises the device.
 FFK_API int ffk_attention_trace(long long *host_out) {
-  unsigned int n = 0, z = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  cudaMemcpyFromSymbol(&n, g_attn_trace_n, sizeof(n));
-  if (n > 2048) n = 2048;
-  cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * 3 * n);
-  cudaMemcpyToSymbol(g_attn_trace_n, &z, sizeof(z));
-  return (int)n;
+  static long long zeros[32 * 64] = {};
+  cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(long long) * 32 * 64);
+  cudaMemcpyToSymbol(g_attn_trace, zeros, sizeof(zeros));
+  return 32 * 64;
 }
 
 // Reads (and clears) the error word of the attention kernels' bounded waits.  Synchronises the device.

@@ -130,6 +130,25 @@ static __device__ __forceinline__ void tc_mma_pair_bf16(uint32_t tmem_d, uint64_
       : "memory");
 }
 
+// The same MMA with the accumulate flag as a compile-time constant (no predicate to set up per call).  With descriptors
+// that were built once and are advanced by adding a constant, issuing one MMA is a couple of integer adds and the MMA
+// itself; a single thread issues every MMA of a CTA, so its instruction count per MMA bounds the tensor-core rate of
+// small tiles.
+template <bool ACC>
+static __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  if constexpr (ACC)
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 1;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), "l"(adesc),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+  else
+    asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, 1, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), "l"(adesc),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+}
+// descriptor of the same tile `bytes` further on (the start-address field counts 16-byte units and cannot carry out of
+// its 14 bits for offsets inside shared memory)
+static __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+
 static __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "

@@ -116,6 +116,38 @@ class DistContext:
             self._subgroups[key] = dist.new_group(list(key))
         return self._subgroups[key]
 
+    def sub(self, ranks: Sequence[int]) -> "GroupContext":
+        """The same resources seen by a subset of the ranks (one axis of a device mesh): kernels and fused operators given
+        this object address only the members' memory and count only the members.  Every rank of the job must call this
+        with the group *it* belongs to at the same point of the program (allocations behind it exchange handles across the
+        whole job)."""
+        ranks = tuple(int(r) for r in ranks)
+        if ranks == tuple(range(self.world_size)):
+            return self
+        key = ("sub",) + ranks
+        if key not in self._subgroups:
+            self._subgroups[key] = GroupContext(self, ranks)
+        return self._subgroups[key]
+
+    def make_mesh_groups(self, outer: int, inner: int):
+        """Rank r = o * inner + i of an outer x inner mesh: returns (group of the ranks that share r's inner index, i.e. the
+        outer axis; group of the ranks that share r's outer index, i.e. the inner axis).  The library process groups of
+        every row and column are created on every rank, as torch.distributed requires."""
+        if outer * inner != self.world_size:
+            raise ValueError(f"a {outer} x {inner} mesh does not cover {self.world_size} ranks")
+        mine_outer = mine_inner = None
+        for i in range(inner):
+            members = [o * inner + i for o in range(outer)]
+            g = self.subgroup(members) if outer > 1 else None
+            if self.rank in members:
+                mine_outer = (members, g)
+        for o in range(outer):
+            members = [o * inner + i for i in range(inner)]
+            g = self.subgroup(members) if inner > 1 else None
+            if self.rank in members:
+                mine_inner = (members, g)
+        return self.sub(mine_outer[0]), self.sub(mine_inner[0])
+
     def check_status(self):
         """Raise if a device-side bounded wait on a peer ran out (reads one int from the device)."""
         code = int(self.status.item())
@@ -123,3 +155,56 @@ class DistContext:
             self.status.zero_()
             from ..utils.failure import CommTimeoutError
             raise CommTimeoutError(f"rank {self.rank}: a peer did not answer within the device-side wait limit (code {code})")
+
+
+class _GroupBuffer:
+    """A symmetric buffer as one rank group sees it: pointers of the members only, in group order."""
+
+    def __init__(self, base: SymmetricBuffer, g: "GroupContext"):
+        self.base, self.ctx = base, g
+        self.nbytes = base.nbytes
+        self.local_ptr = base.local_ptr
+        self.local = base.local
+        self.peer_ptrs = [base.peer_ptrs[r] for r in g.members]
+        self.ptr_array = (ctypes.c_void_p * g.world_size)(*self.peer_ptrs)
+
+    def view(self, dtype, shape=None, byte_offset: int = 0, numel: Optional[int] = None) -> torch.Tensor:
+        return self.base.view(dtype, shape, byte_offset, numel)
+
+    def peer_ptr_array(self, byte_offset: int = 0):
+        return (ctypes.c_void_p * self.ctx.world_size)(*[p + byte_offset for p in self.peer_ptrs])
+
+
+class GroupContext:
+    """A DistContext restricted to `members` (global ranks): ``rank`` is the position inside the group and ``world_size``
+    the group's size, so the peer-memory collectives and fused operators run unchanged on one axis of a mesh.  Flags,
+    status word and call-site state are the parent's; symmetric allocations go through the parent (every rank of the job
+    allocates at the same time, each for its own group) and expose the members' addresses only."""
+
+    def __init__(self, parent: DistContext, members: Sequence[int]):
+        if parent.rank not in members:
+            raise ValueError("a rank can only hold the groups it belongs to")
+        self.parent = parent
+        self.members = tuple(members)
+        self.rank = self.members.index(parent.rank)
+        self.world_size = len(self.members)
+        self.local_rank = parent.local_rank
+        self.device = parent.device
+        self.group = parent.subgroup(self.members) if self.world_size > 1 else None
+        self.flags = _GroupBuffer(parent.flags, self)
+        self.status = parent.status
+
+    def alloc_flags(self, n: int) -> int:
+        return self.parent.alloc_flags(n)
+
+    def new_sync(self) -> torch.Tensor:
+        return self.parent.new_sync()
+
+    def symmetric(self, nbytes: int) -> _GroupBuffer:
+        return _GroupBuffer(self.parent.symmetric(nbytes), self)
+
+    def subgroup(self, ranks: Sequence[int]):
+        return self.parent.subgroup(ranks)
+
+    def check_status(self):
+        self.parent.check_status()

@@ -15,7 +15,10 @@ operators at all.  Here
 
 Supported strategies: one mesh axis (every parallel degree equals the world size), which covers pure data
 parallelism, pure tensor parallelism, per-operator mixtures of the two, and model-parallel embedding tables
-under a data-parallel model (``AllToAllEmbeddingOp``).
+under a data-parallel model (``AllToAllEmbeddingOp``); and two mesh axes, data parallel of degree dp around tensor
+parallel of degree tp (``compiler.strategy.hybrid_strategy``): rank r = i_dp * tp + i_tp, sample-dimension operators
+work inside the group of ranks that share i_tp, Replicate / Reduction and weight shards inside the group that shares
+i_dp, and the gradients of every weight are summed over the data-parallel group by the fused bucket kernel.
 """
 from __future__ import annotations
 
@@ -57,8 +60,8 @@ class _ParallelOp(OpImpl):
             return False
         if self.type == "REPARTITION" and self.pair is None:
             return self.buf("INPUT").requires_grad  # forward is a local slice; backward all-gathers
-        if self.type == "COMBINE" and self.pair is not None:
-            return True
+        if self.type in ("REPLICATE", "REDUCTION") and self.pair is None and self.ex.peer_allreduce:
+            return False  # summed in place by the peer-memory all-reduce kernel
         return True
 
     def is_alias(self) -> bool:
@@ -69,10 +72,26 @@ class _ParallelOp(OpImpl):
         self.out().data = self.x()
         self.ex.alias(self.nid, self.inputs["INPUT"])
 
+    @property
+    def gctx(self):
+        """The ranks this operator's collective spans: the whole job on a one-axis plan; on a dp x tp mesh the
+        data-parallel group for Repartition / Combine of the sample dimension and the tensor-parallel group for
+        everything else."""
+        ex = self.ex
+        mesh = getattr(ex, "mesh", None)
+        if mesh is None:
+            return ex.dist
+        if self.type in ("REPARTITION", "COMBINE"):
+            dim = int(self.attrs["repartition_dim" if self.type == "REPARTITION" else "combine_dim"])
+            if dim == 0:
+                return ex.ctx_dp
+        return ex.ctx_tp
+
     def check_degree(self):
         d = _degree(self.attrs)
-        if d != self.ex.dist.world_size:
-            raise NotImplementedError(f"{self.type} of degree {d} on {self.ex.dist.world_size} ranks: only one mesh axis is supported")
+        if d != self.gctx.world_size:
+            raise NotImplementedError(f"{self.type} of degree {d} on a group of {self.gctx.world_size} ranks "
+                                      f"({self.ex.dist.world_size} in the job): the strategy does not fit the device mesh")
 
 
 @register("REPARTITION")
@@ -84,14 +103,23 @@ class RepartitionOp(_ParallelOp):
         y = self.alloc_out()
         self.dim = int(self.attrs["repartition_dim"]) % y.dim()
         self.piece = y.shape[self.dim]
+        # A graph input that is only read through this Repartition can be fed shard by shard: with
+        # `DistExecutable.shard_inputs` the caller hands each rank its own piece, which is copied straight into this
+        # operator's output and the whole-tensor copy disappears from the step (host-to-device traffic per rank then
+        # shrinks with the number of ranks).
+        src = self.ex.nodes[self.inputs["INPUT"][0]]
+        self.direct = bool(getattr(self.ex, "shard_inputs", False) and src["type"] == "INPUT" and not src["outputs"][0][2]
+                           and len(self.ex.graph.consumers(self.inputs["INPUT"])) == 1)
+        if self.direct:
+            self.ex.direct_inputs[src["name"] or f"input{src['id']}"] = self
 
     def forward(self):
-        if self.is_alias() or self.absorbed:
+        if self.is_alias() or self.absorbed or getattr(self, "direct", False):
             return
         if self.pair is not None:  # Reduction -> Repartition(0): one reduce-scatter of the partial sums
-            dist.reduce_scatter_tensor(self.out().data.view(-1), self.pair.x().view(-1), group=self.ex.dist.group)
+            dist.reduce_scatter_tensor(self.out().data.view(-1), self.pair.x().view(-1), group=self.gctx.group)
             return
-        r = self.ex.dist.rank
+        r = self.gctx.rank
         self.out().data.copy_(self.x().narrow(self.dim, r * self.piece, self.piece))
 
     def backward(self):
@@ -100,12 +128,12 @@ class RepartitionOp(_ParallelOp):
         if self.pair is not None:
             b = self.pair.buf("INPUT")
             if b.requires_grad:
-                g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), 0, self.ex.dist.world_size, self.ex.dist.group)
+                g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), 0, self.gctx.world_size, self.gctx.group)
                 self.ex.write_grad(b, g, self.pair.acc["INPUT"])
             return
         b = self.buf("INPUT")
         if b.requires_grad:
-            g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), self.dim, self.ex.dist.world_size, self.ex.dist.group)
+            g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), self.dim, self.gctx.world_size, self.gctx.group)
             self.ex.write_grad(b, g, self.acc["INPUT"])
 
 
@@ -124,7 +152,7 @@ class CombineOp(_ParallelOp):
     def forward(self):
         if self.is_alias() or self.absorbed:
             return
-        comm.nccl_all_gather_dim(self.x(), self.dim, self.ex.dist.world_size, self.ex.dist.group, out=self.out().data)
+        comm.nccl_all_gather_dim(self.x(), self.dim, self.gctx.world_size, self.gctx.group, out=self.out().data)
 
     def backward(self):
         if self.is_alias() or self.absorbed or self.pair is not None:
@@ -132,7 +160,7 @@ class CombineOp(_ParallelOp):
         b = self.buf("INPUT")
         if b.requires_grad:
             piece = self.x().shape[self.dim]
-            g = self.out().grad.view_as(self.out().data).narrow(self.dim, self.ex.dist.rank * piece, piece)
+            g = self.out().grad.view_as(self.out().data).narrow(self.dim, self.gctx.rank * piece, piece)
             self.ex.write_grad(b, g.contiguous(), self.acc["INPUT"])
 
 
@@ -155,16 +183,16 @@ class ReplicateOp(_ParallelOp):
             if cb.requires_grad:
                 full = self.out().grad.view(-1)
                 if self.pair.acc["INPUT"]:
-                    t = torch.empty(full.numel() // self.ex.dist.world_size, dtype=full.dtype, device=full.device)
-                    dist.reduce_scatter_tensor(t, full, group=self.ex.dist.group)
+                    t = torch.empty(full.numel() // self.gctx.world_size, dtype=full.dtype, device=full.device)
+                    dist.reduce_scatter_tensor(t, full, group=self.gctx.group)
                     self.ex.write_grad(cb, t, True)
                 else:
-                    dist.reduce_scatter_tensor(cb.grad.view(-1), full, group=self.ex.dist.group)
+                    dist.reduce_scatter_tensor(cb.grad.view(-1), full, group=self.gctx.group)
             return
         b = self.buf("INPUT")
         if b.requires_grad:
             g = self.out().grad
-            dist.all_reduce(g, group=self.ex.dist.group)  # the replicas' gradients add up
+            self.ex.all_reduce_activation(g, self.gctx)  # the replicas' gradients add up
             self.ex.write_grad(b, g, self.acc["INPUT"])
 
 
@@ -186,7 +214,7 @@ class ReductionOp(_ParallelOp):
             return
         if self.absorbed or self.pair is not None:
             return
-        dist.all_reduce(self.x(), group=self.ex.dist.group)
+        self.ex.all_reduce_activation(self.x(), self.gctx)
 
 
 class AllToAllEmbeddingOp(_ParallelOp):
@@ -284,8 +312,10 @@ class FuseOut:
 
 class DistExecutable(Executable):
     def __init__(self, pcg, cfg: Optional[ExecConfig], ctx: DistContext, bucket_mb: int = 128, overlap: bool = True,
-                 fuse_collectives: bool = True, fuse_optimizer: bool = True):
+                 fuse_collectives: bool = True, fuse_optimizer: bool = True, shard_inputs: bool = False):
         self.ctx = ctx
+        self.shard_inputs = shard_inputs
+        self.direct_inputs: Dict[str, "RepartitionOp"] = {}
         self.fuse_collectives = fuse_collectives
         self.fuse_optimizer = fuse_optimizer
         self._rs_shared: Dict[tuple, GemmReduceScatter] = {}
@@ -295,6 +325,10 @@ class DistExecutable(Executable):
         self.fused_out: List[int] = []
         self.bucket_bytes = bucket_mb << 20
         self.overlap = overlap
+        self._ar_stage: Dict[tuple, object] = {}
+        # activations are summed over ranks (Replicate backward, Reduction forward) by the peer-memory all-reduce kernel
+        # through a symmetric staging buffer, so that a plan with such operators is still one CUDA graph
+        self.peer_allreduce = fuse_collectives
         self._pre_analyse(pcg, ctx)
         super().__init__(pcg, cfg, dist=ctx)
         # NCCL collectives are issued eagerly: a plan that still contains one (a parallel operator that is neither
@@ -497,6 +531,61 @@ class DistExecutable(Executable):
             self.weight_replicated[nid] = replicated
         self._nodes_pre = nodes
         self._g_pre = g
+        self._infer_mesh(g, nodes, ctx)
+
+    def _infer_mesh(self, g, nodes, ctx):
+        """One axis when every parallel operator spans the whole job.  Otherwise dp x tp: dp is the degree the sample
+        dimension of the inputs is cut into, tp the degree of the Replicate / Reduction operators on activations and of
+        the weight shards; rank r sits at (r // tp, r % tp)."""
+        W = ctx.world_size
+        self.mesh = None
+        self.ctx_dp = self.ctx_tp = ctx
+        self.tp_size, self.tp_idx, self.dp_size, self.dp_idx = W, ctx.rank, W, ctx.rank
+        degrees = {_degree(n["attrs"]) for n in nodes.values() if n["type"] in PARALLEL}
+        if W == 1 or not degrees or degrees <= {W, 1}:
+            return
+        dp = tp = None
+        for nid, n in nodes.items():
+            if n["type"] not in PARALLEL or nid in self.weight_chain_nodes:
+                continue
+            d = _degree(n["attrs"])
+            dim0 = (n["type"] == "REPARTITION" and int(n["attrs"]["repartition_dim"]) == 0) or \
+                   (n["type"] == "COMBINE" and int(n["attrs"]["combine_dim"]) == 0)
+            if dim0:
+                dp = d if dp is None else dp
+                if d != dp:
+                    raise NotImplementedError(f"sample-dimension operators of degrees {dp} and {d} in one strategy")
+            else:
+                tp = d if tp is None else tp
+                if d != tp:
+                    raise NotImplementedError(f"tensor-parallel operators of degrees {tp} and {d} in one strategy")
+        dp = dp or (W // tp if tp else W)
+        tp = tp or W // dp
+        if dp * tp != W:
+            raise NotImplementedError(f"strategy of degrees {sorted(degrees)} does not form a dp x tp mesh over {W} ranks")
+        self.mesh = (dp, tp)
+        self.dp_size, self.tp_size = dp, tp
+        self.dp_idx, self.tp_idx = ctx.rank // tp, ctx.rank % tp
+        self.ctx_dp, self.ctx_tp = ctx.make_mesh_groups(dp, tp)
+
+    def all_reduce_activation(self, t: torch.Tensor, gctx):
+        """Sum `t` over the ranks of `gctx`, in place."""
+        if gctx.world_size == 1:
+            return
+        n = t.numel()
+        if not (self.peer_allreduce and t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous() and n % 8 == 0):
+            dist.all_reduce(t, group=gctx.group)
+            return
+        key = (id(gctx), t.dtype)
+        ar = self._ar_stage.get(key)
+        if ar is None or ar.numel < n:
+            # grown at set-up time only (operators run once eagerly before a step is captured)
+            ar = GradAllReduce(gctx, max(n, ar.numel if ar is not None else 0), t.dtype)
+            self._ar_stage[key] = ar
+        stage = ar.tensor[:n]
+        stage.copy_(t.view(-1))
+        ar.run(scale=1.0, offset=0, n=n)
+        t.view(-1).copy_(stage)
 
     def _final_shape(self, nid):
         return self._g_pre.shape(self.weight_final[nid])
@@ -506,7 +595,7 @@ class DistExecutable(Executable):
 
     def shard_weight(self, nid, full):
         sh = self._final_shape(nid)
-        r = self.ctx.rank
+        r = self.tp_idx if self.mesh is not None else self.ctx.rank
         cons = self.weight_consumer.get(nid)
         if cons is not None and self._nodes_pre[cons[0]]["type"] == "MULTIHEAD_ATTENTION" and any(d > 1 for d in sh.degrees):
             return self._shard_attention_weight(nid, full, cons)
@@ -522,7 +611,7 @@ class DistExecutable(Executable):
         a = self._nodes_pre[cons[0]]["attrs"]
         node = self._nodes_pre[cons[0]]
         H, kd, vd, E_ = int(a["num_heads"]), int(a["kdim"]), int(a["vdim"]), int(a["embed_dim"])
-        W, r = self.ctx.world_size, self.ctx.rank
+        W, r = (self.tp_size, self.tp_idx) if self.mesh is not None else (self.ctx.world_size, self.ctx.rank)
         Hl = H // W
         ins = {s: tuple(v) for s, v in node["inputs"]}
         dq = self._g_pre.shape(ins["QUERY"]).sizes[-1]
@@ -551,12 +640,13 @@ class DistExecutable(Executable):
         return rep + rest
 
     def alloc_grad_arena(self, numel, dtype):
-        self.grad_ar = GradAllReduce(self.ctx, numel, dtype)
+        # gradients are summed over the ranks that hold the same weight shard: the data-parallel group
+        self.grad_ar = GradAllReduce(self.ctx_dp, numel, dtype)
         return self.grad_ar.tensor
 
     def alloc_shadow_arena(self, numel):
         # peers write the updated weights of the slices they own straight into this arena
-        self.shadow_buf = self.ctx.symmetric(numel * 2)
+        self.shadow_buf = self.ctx_dp.symmetric(numel * 2)
         t = self.shadow_buf.view(torch.bfloat16, numel=numel)
         t.zero_()
         return t
@@ -572,7 +662,7 @@ class DistExecutable(Executable):
         if v is None:
             return False
         out_sum = self.graph.shape((op.nid, op.outputs[0][0])).sum_degree
-        return out_sum == 1 or self.ctx.rank == 0
+        return out_sum == 1 or (self.tp_idx if self.mesh is not None else self.ctx.rank) == 0
 
     # ------------------------------------------------------------------ loss on the local shard
     def resolve_loss_value(self, v: Value) -> Value:
@@ -589,11 +679,27 @@ class DistExecutable(Executable):
             n *= d
         return n
 
+    def set_inputs(self, inputs, labels=None):
+        """As the single-device executor, plus: with `shard_inputs`, an input that is consumed through a sample-dimension
+        Repartition may be given as this rank's piece only (or still as the whole tensor, of which the piece is taken)."""
+        rest = dict(inputs)
+        for name, op in self.direct_inputs.items():
+            if name not in rest:
+                continue
+            src = rest.pop(name)
+            dst = op.out().data
+            if src.numel() != dst.numel():  # the whole tensor: keep this rank's piece
+                full = list(dst.shape)
+                full[op.dim] *= op.gctx.world_size
+                src = src.reshape(full).narrow(op.dim, op.gctx.rank * op.piece, op.piece)
+            dst.copy_(src.reshape(dst.shape) if src.numel() == dst.numel() and src.shape != dst.shape else src, non_blocking=True)
+        super().set_inputs(rest, labels)
+
     def local_label_rows(self, labels, rows):
         flat = labels.reshape(-1) if self.cfg.loss == "sparse_categorical_crossentropy" else labels.reshape(-1, labels.shape[-1])
         if flat.shape[0] == rows:
             return flat
-        r = self.ctx.rank
+        r = self.dp_idx if self.mesh is not None else self.ctx.rank
         return flat[r * rows:(r + 1) * rows]
 
     # ------------------------------------------------------------------ gradient synchronisation (F3)
@@ -682,7 +788,7 @@ class DistExecutable(Executable):
             for s, e in self.buckets:
                 a, b = self.grad_ar.owned_ranges(s, e - s)
                 keep[a:b] = t[a:b]
-            dist.all_reduce(keep, group=self.ctx.group)
+            dist.all_reduce(keep, group=self.ctx_dp.group)
             t[:self.rep_numel].copy_(keep)
 
     def state_dict(self):
@@ -702,6 +808,8 @@ class DistExecutable(Executable):
 
     def _describe(self) -> str:
         W = self.ctx.world_size
+        if self.mesh is not None:
+            return f"dp{self.mesh[0]}xtp{self.mesh[1]}"
         kinds = set()
         for n in self.nodes.values():
             if n["type"] in ("LINEAR", "MULTIHEAD_ATTENTION", "CONV2D", "EMBEDDING"):
@@ -720,6 +828,6 @@ class DistExecutable(Executable):
         """Mean loss over the global batch (sums the local rows over ranks when the loss is batch-sharded)."""
         s = self.loss_rows.sum().reshape(1).to(torch.float64)
         sharded = self.global_loss_rows(1, self.graph.shape(self.loss_value)) > 1
-        if sharded:
-            dist.all_reduce(s, group=self.ctx.group)
+        if sharded:  # on a mesh the rows are split over the data-parallel group only
+            dist.all_reduce(s, group=self.ctx_dp.group)
         return float(s.item() * self.loss_scale)

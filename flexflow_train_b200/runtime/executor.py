@@ -1545,6 +1545,20 @@ class Executable:
             if getattr(op, "has_grad", False):
                 op.backward()
 
+    def step_plan(self):
+        """The training step as the list of (task, node) this executor runs, in its stream order: FWD of every operator,
+        LOSS on the loss value, BWD of the operators that have a backward in reverse order, UPD of every parameter.
+        `runtime.lowering.check_plan` compares this with the lowered step (pass expansion, loss and update insertion)
+        and its reader / writer dependencies."""
+        plan = [("FWD", nid) for nid in self.order]
+        if self.loss_value is not None:
+            plan.append(("LOSS", self.loss_value[0]))
+        if self.cfg.training:
+            plan += [("BWD", nid) for nid in reversed(self.order) if getattr(self.ops[nid], "has_grad", False)]
+            plan += [("UPD", nid) for nid in self.param_nodes]
+            plan += [("UPD", nid) for nid, t in self.sparse_tables.items() if t is not None and nid not in self.param_nodes]
+        return plan
+
     def profile_step(self, update: bool = False):
         """Run one eager forward + backward with CUDA events around every operator's forward and backward.
 

@@ -83,6 +83,71 @@ def test_two_rank_training_matches_single_gpu(which):
         assert out["multi"][-1] < out["multi"][0]
 
 
+def w_mesh(ctx):
+    """dp x tp on a two-axis device mesh (4 ranks: 2 x 2; 8 ranks: 4 x 2) against one GPU: same losses over four Adam
+    steps, same first-step gradients of every weight shard, inputs fed as each data-parallel group's own rows."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.compiler import strategy as S
+    from flexflow_train_b200.parallel.dist_executor import DistExecutable
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+
+    cfg = dict(CFG, sequence_length=64)
+    cg = core.build_model("transformer_lm", cfg)
+    W = ctx.world_size
+    tp = 2
+    dp = W // tp
+    pcg = S.hybrid_strategy(cg, dp, tp)
+    opt = OptimizerConfig(kind="adam", lr=1e-3)
+    single = Executable(cg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"))
+    multi = DistExecutable(pcg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"), ctx,
+                           shard_inputs=True, fuse_optimizer=False)   # plain all-reduce: the summed gradients stay readable
+    torch.manual_seed(0)
+    ids = torch.randint(0, 512, (8, 64, 1), dtype=torch.int32, device=ctx.device)
+    labels = torch.randint(0, 512, (8, 64), dtype=torch.int32, device=ctx.device)
+    lb = 8 // dp
+    i_dp = ctx.rank // tp
+    my_ids, my_labels = ids[i_dp * lb:(i_dp + 1) * lb].contiguous(), labels[i_dp * lb:(i_dp + 1) * lb].contiguous()
+    # first step by hand: gradients before any update
+    single.set_inputs({"input_ids": ids}, labels)
+    single.forward(); single.compute_loss(); single.backward()
+    multi.set_inputs({"input_ids": my_ids}, my_labels)
+    multi.forward(); multi.compute_loss(); multi.backward(); multi.sync_gradients()
+    torch.cuda.synchronize()
+    ref = dict(single.named_gradients())
+    worst = 0.0
+    for nid, (name, g) in zip(multi.param_nodes, multi.named_gradients()):
+        full = ref[name].float()
+        shard = multi.shard_weight(nid, full.view(list(multi.nodes[nid]["outputs"][0][1].sizes))).reshape(-1)
+        # the bucket kernel leaves the data-parallel sum in the gradient arena when the update is not fused into it
+        err = float((g.float().reshape(-1) - shard).norm() / (shard.norm() + 1e-9))
+        worst = max(worst, err)
+    a, b = [], []
+    single2 = Executable(cg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}"))
+    multi2 = DistExecutable(pcg, ExecConfig(compute_dtype="bf16", seed=4, optimizer=opt, device=f"cuda:{ctx.rank}", use_cuda_graph=True), ctx,
+                            shard_inputs=True)
+    for _ in range(4):
+        single2.train_step({"input_ids": ids}, labels)
+        a.append(single2.mean_loss())
+        multi2.train_step({"input_ids": my_ids}, my_labels)
+        b.append(multi2.mean_loss())
+    ctx.check_status()
+    return {"single": a, "multi": b, "parallelism": multi2.parallelism, "worst_grad_err": worst, "nccl_ops": len(multi2.nccl_ops),
+            "graph": bool(multi2.cfg.use_cuda_graph), "direct": sorted(multi2.direct_inputs)}
+
+
+def test_mesh_dp_x_tp_matches_single_gpu():
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else 4
+    res = _run("test_dist_executor_gpu:w_mesh", world=world)
+    for r, out in res.items():
+        assert out["parallelism"] == f"dp{world // 2}xtp2" and out["direct"] == ["input_ids"], out
+        assert out["nccl_ops"] == 0 and out["graph"], out   # the step is one captured graph: no library collective in it
+        assert out["worst_grad_err"] < 5e-2, out
+        for x, y in zip(out["single"], out["multi"]):
+            assert abs(x - y) < 3e-2 * abs(x), out
+        assert out["multi"][-1] < out["multi"][0]
+
+
 def _train_graph(ctx, build, loss, inputs_fn, steps=4):
     """Single-GPU vs data-parallel training of an arbitrary graph on the same global batch."""
     from flexflow_train_b200.compiler import strategy as S

@@ -180,3 +180,44 @@ def test_optimizer_attrs_and_adam_bias_correction_schedule():
     cg = core.build_model("mlp", {})
     l = core.perform_update_insertion(cg, core.perform_pass_expansion(cg, core.make_dynamic_graph(cg)), a)
     assert any(i["task"] == "UPD" and any(v["role"] == "OPT:m" for v in i["inputs"]) for i in l)
+
+
+SMALL_MODELS = {
+    "mlp": {"batch_size": 8},
+    "transformer": {"num_features": 32, "sequence_length": 8, "batch_size": 4, "dim_feedforward": 64, "num_heads": 2,
+                    "num_encoder_layers": 1, "num_decoder_layers": 1, "vocab_size": 16},
+    "transformer_lm": {"num_features": 32, "sequence_length": 8, "batch_size": 4, "dim_feedforward": 64, "num_heads": 2,
+                       "num_decoder_layers": 2, "vocab_size": 16},
+    "bert": {"token_ids": True, "batch_size": 4, "sequence_length": 8, "vocab_size": 32, "hidden_size": 32, "num_encoder_layers": 1,
+             "num_heads": 2, "dim_feedforward": 64},
+    "dlrm": {"batch_size": 8, "embedding_size": [50, 50], "embedding_dim": 8, "dense_arch_layer_sizes": [4, 8],
+             "over_arch_layer_sizes": [16, 1]},
+    "split_test": {"batch_size": 8},
+    "candle_uno": {"batch_size": 4},
+    "inception_v3": {"batch_size": 2, "num_classes": 10},
+}
+
+
+@pytest.mark.parametrize("model", sorted(SMALL_MODELS))
+def test_executor_plan_agrees_with_the_lowered_step(model):
+    """The kernel-library executor builds its step straight from the graph; the lowering passes build theirs through pass
+    expansion, loss and update insertion.  For every model of the zoo the two must describe the same step: same
+    invocations, every reader / writer dependency of the lowered step respected by the executor's stream order, same
+    operands per operator.  (Planning needs no GPU: the executor is constructed with device='cpu'.)"""
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable, OptimizerConfig
+    from flexflow_train_b200.runtime.lowering import check_plan, lower
+
+    cg = core.build_model(model, SMALL_MODELS[model])
+    loss = "mean_squared_error_avg_reduce" if model in ("dlrm", "candle_uno") else "sparse_categorical_crossentropy"
+    ex = Executable(cg, ExecConfig(device="cpu", compute_dtype="bf16" if model == "inception_v3" else "fp32", loss=loss,
+                                   optimizer=OptimizerConfig(kind="sgd", lr=0.1)))
+    inv = lower(cg, logit=ex.loss_value, loss=loss, optimizer={"type": "sgd"})
+    assert len(inv) >= len(ex.step_plan()) - 1
+    assert check_plan(ex, inv) == []
+    # and the check does notice a wrong order: run the first Linear-like operator's backward before the loss
+    plan = ex.step_plan()
+    first_bwd = next(i for i, (t, _) in enumerate(plan) if t == "BWD")
+    broken = plan[:]
+    broken.insert(0, broken.pop(first_bwd))
+    ex.step_plan = lambda: broken
+    assert any("before its dependency" in p for p in check_plan(ex, inv))

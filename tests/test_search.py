@@ -115,7 +115,7 @@ def test_optimize_picks_data_parallel_for_large_transformer_and_exports():
     g = c.build_model("transformer_lm", cfg)
     r = S.optimize(g, world=8, algorithm="unity", budget=0)
     assert r["stats"]["seed_strategy"].startswith("dp8")
-    assert set(r["stats"]["candidates"]) == {"single_device", "dp8", "tp8"}
+    assert set(r["stats"]["candidates"]) == {"single_device", "dp8", "tp8", "dp4xtp2", "dp2xtp4"}
     text = r["mapped_pcg"].to_v1_string(parallel=True)
     back = c.Graph.from_v1(text)
     assert back.signature() == r["mapped_pcg"].signature()
@@ -260,11 +260,12 @@ def test_hybrid_data_x_tensor_parallel_strategy_is_clean_and_scored():
     assert max(n["outputs"][0][1].total_degree for n in nodes.values()) == 8
     text = g.to_v1_string(parallel=True)
     assert c.Graph.from_v1(text).signature() == g.signature()
-    r = S.optimize(cg, world=8, score_hybrid=True)
-    hy = r["stats"]["hybrid_candidates_not_executable"]
-    assert set(hy) == {"dp4xtp2", "dp2xtp4"} and all(v > 0 for v in hy.values())
-    assert "x" not in r["stats"]["seed_strategy"]
-    assert "hybrid_candidates_not_executable" not in S.optimize(cg, world=8)["stats"]
+    # the mesh strategies are candidates of the search like the one-axis templates (the executor runs them)
+    r = S.optimize(cg, world=8)
+    cands = r["stats"]["candidates"]
+    assert {"dp4xtp2", "dp2xtp4", "dp8", "tp8", "single_device"} <= set(cands) and all(v > 0 for v in cands.values())
+    assert r["runtime_ms"] == min(cands.values())
+    assert "dp4xtp2" not in S.optimize(cg, world=8, only_data_parallel=True)["stats"]["candidates"]
 
 
 def test_every_strategy_template_computes_the_function_of_the_computation_graph():
