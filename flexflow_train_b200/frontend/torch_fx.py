@@ -104,6 +104,7 @@ _FUNCTIONS = {
     torch.pow: "POW", operator.pow: "POW", torch.mean: "MEAN", torch.rsqrt: "RSQRT", torch.unsqueeze: "UNSQUEEZE",
     F.dropout: "DROPOUT", torch.tanh: "TANH", F.gelu: "GELU", torch.sigmoid: "SIGMOID", F.sigmoid: "SIGMOID", torch.exp: "EXP",
     torch.sin: "SIN", torch.cos: "COS", F.elu: "ELU", F.layer_norm: "F_LAYERNORM", torch.sum: "SUM", torch.squeeze: "SQUEEZE",
+    F.linear: "F_LINEAR", torch._C._nn.linear: "F_LINEAR",
 }
 _METHODS = {
     "add": "ADD", "sub": "SUB", "mul": "MUL", "div": "TRUEDIV", "true_divide": "TRUEDIV", "floor_divide": "FLOORDIV", "split": "SPLIT",
@@ -374,6 +375,18 @@ def emit_ir(records: List[dict], ff: FFModel, input_tensors: List[Tensor], verbo
                 raise NotImplementedError(f"getattr({attr})")
         elif op == "SIZE":
             r = tuple(x.dims) if len(a) == 1 else x.dims[a[1]]
+        elif op == "F_LINEAR":
+            # the functional form (what torch.compile's graphs contain): weight and bias are tensors of the graph, not
+            # parameters owned by a layer, so this is a product with the transposed weight plus a broadcast bias
+            w = a[1]
+            b = a[2] if len(a) > 2 else kw.get("bias")
+            rows = _numel(x) // x.dims[-1]
+            x3 = ff.reshape(x, [1, rows, x.dims[-1]], name=name + ".x3")
+            wt = ff.transpose(ff.reshape(w, [1, w.dims[0], w.dims[1]], name=name + ".w3"), [0, 2, 1], name=name + ".wt")
+            y = ff.reshape(ff.batch_matmul(x3, wt, name=name + ".mm"), list(x.dims[:-1]) + [w.dims[0]], name=name + ".y")
+            if isinstance(b, Tensor):
+                y = ff.add(y, ff._t(ff.builder.broadcast(b.value, list(y.dims), name + ".bias")), name=name)
+            r = y
         elif op == "MATMUL":
             r = ff.batch_matmul(a[0], a[1], name=name)
         elif op == "TRANSPOSE":
@@ -407,3 +420,112 @@ def emit_ir(records: List[dict], ff: FFModel, input_tensors: List[Tensor], verbo
             raise NotImplementedError(f"importer op {op}")
         env[name] = r
     return outputs
+
+
+# ------------------------------------------------------------------------------------------ one-call entry points
+class CompiledModule:
+    """An ``nn.Module`` compiled for this framework's executors: ``train_step`` / ``forward`` on tensors named after the
+    module's ``forward`` arguments.  Returned by :func:`compile_module`; also what the ``torch.compile`` backend wraps."""
+
+    def __init__(self, module: nn.Module, ffmodel: FFModel, importer: "PyTorchModel", input_names: List[str]):
+        self.module, self.ffmodel, self.importer, self.input_names = module, ffmodel, importer, input_names
+        self.compiled = ffmodel.compiled
+        self.executable = ffmodel.executable
+        self.graph = ffmodel.graph
+        self.search_stats = getattr(self.compiled, "search_stats", {})
+
+    def _named(self, args):
+        if len(args) == 1 and isinstance(args[0], dict):
+            return args[0]
+        if len(args) != len(self.input_names):
+            raise ValueError(f"the module takes {len(self.input_names)} inputs ({self.input_names}), got {len(args)}")
+        return dict(zip(self.input_names, args))
+
+    def train_step(self, *inputs, labels=None, return_loss: bool = True):
+        return self.compiled.train_step(self._named(inputs), labels, return_loss=return_loss)
+
+    def forward(self, *inputs):
+        return self.executable.infer(self._named(inputs))
+
+    __call__ = forward
+
+    def sync_parameters_to_module(self):
+        """Write the trained weights back into the ``nn.Module`` (fp32 master copies, matched by layer name)."""
+        trained = dict(self.executable.named_parameters())
+        n = 0
+        with torch.no_grad():
+            for rec in self.importer.to_ir():
+                mod = rec["params"].get("module")
+                if mod is None:
+                    continue
+                sub = self.module.get_submodule(mod)
+                for slot, key in (("weight", "weight"), ("filter", "weight"), ("bias", "bias"), ("gamma", "weight"), ("beta", "bias")):
+                    src = trained.get(f"{rec['name']}.{slot}")
+                    dst = getattr(sub, key, None)
+                    if src is not None and dst is not None and tuple(dst.shape) == tuple(src.shape):
+                        dst.copy_(src.to(dst.dtype))
+                        n += 1
+        return n
+
+
+def compile_module(module: nn.Module, example_inputs, *, optimizer=None, loss_type=None, metrics=None, config=None, algorithm: Optional[str] = None,
+                   search_budget: Optional[int] = None, device: Optional[str] = None, dist=None, is_hf_model: bool = False,
+                   copy_weights: bool = True) -> CompiledModule:
+    """``nn.Module`` -> traced graph -> computation graph -> strategy search -> executor, in one call: the flow the
+    reference draws for its PyTorch frontend (docs/plantuml/figures/pytorch-tracing.puml: ``model.compile(algorithm=...,
+    optimizer=...)`` returning a compiled model with forward / backward / update).
+
+    `example_inputs`: one tensor per ``forward`` argument (only shapes and dtypes are used).  `algorithm`: the search
+    algorithm ("unity", "mcmc", "data_parallel", ...) when several ranks are present (`dist`); `search_budget` its budget.
+    The module's current parameter values are copied into the executor unless ``copy_weights=False``."""
+    from ..api import FFConfig as ApiConfig
+
+    import inspect
+
+    if isinstance(example_inputs, torch.Tensor):
+        example_inputs = [example_inputs]
+    example_inputs = list(example_inputs)
+    names = [p for p in inspect.signature(module.forward).parameters][:len(example_inputs)]
+    cfg = config or ApiConfig(batch_size=int(example_inputs[0].shape[0]))
+    if algorithm is not None:
+        cfg.search_algorithm = algorithm
+    if search_budget is not None:
+        cfg.search_budget = search_budget
+    ff = FFModel(cfg)
+    dt = {torch.float32: DataType.DT_FLOAT, torch.int32: DataType.DT_INT32, torch.int64: DataType.DT_INT64, torch.bfloat16: DataType.DT_FLOAT,
+          torch.float16: DataType.DT_FLOAT}
+    tensors = [ff.create_tensor(list(t.shape), dt.get(t.dtype, DataType.DT_FLOAT), create_grad=t.dtype.is_floating_point, name=n)
+               for n, t in zip(names, example_inputs)]
+    importer = PyTorchModel(module, is_hf_model=is_hf_model, input_names=names if is_hf_model else None)
+    importer.torch_to_ff(ff, tensors)
+    ff.compile(optimizer, loss_type, metrics, device=device, dist=dist)
+    if copy_weights:
+        importer.copy_parameters(ff)
+    return CompiledModule(module, ff, importer, names)
+
+
+def flexflow_backend(gm, example_inputs, **options):
+    """``torch.compile(model, backend=flexflow_backend)``: the graph module dynamo hands over is imported and compiled for
+    inference on this framework's executor; the returned callable has the calling convention dynamo expects (positional
+    tensors in, tuple of tensors out).  Training through ``torch.compile`` is not offered -- autograd would have to call
+    back into the executor per operator; use :func:`compile_module` and its ``train_step`` for that."""
+    from .types import CompMode
+
+    names = [n.name for n in gm.graph.nodes if n.op == "placeholder"]
+    cfg_device = options.get("device")
+    from ..api import FFConfig as ApiConfig
+
+    ff = FFModel(ApiConfig(batch_size=int(example_inputs[0].shape[0]) if len(example_inputs) and example_inputs[0].dim() else 1))
+    tensors = [ff.create_tensor(list(t.shape), DataType.DT_FLOAT if t.dtype.is_floating_point else DataType.DT_INT32,
+                                create_grad=False, name=n) for n, t in zip(names, example_inputs)]
+    importer = PyTorchModel(gm)
+    importer._traced = gm
+    importer.torch_to_ff(ff, tensors)
+    ff.compile(None, None, None, comp_mode=CompMode.INFERENCE, device=cfg_device)
+    importer.copy_parameters(ff)
+
+    def run(*args):
+        out = ff.executable.infer(dict(zip(names, args)))
+        return (out,) if isinstance(out, torch.Tensor) else tuple(out)
+
+    return run

@@ -197,3 +197,42 @@ def test_keras_sequential_and_functional_models_train():
     assert hist[-1] < hist[0]
     assert fm.predict([X, X]).shape == (128, 4)
     assert fm.evaluate([X, X], Y)["samples"] == 128
+
+
+class _SmallMlp(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.f1 = nn.Linear(16, 32)
+        self.f2 = nn.Linear(32, 5)
+
+    def forward(self, x):
+        return torch.softmax(self.f2(torch.relu(self.f1(x))), -1)
+
+
+def test_compile_module_is_a_one_call_path_from_nn_module_to_a_trainable_model():
+    """nn.Module -> trace -> computation graph -> (search) -> executor in one call, as the reference's PyTorch frontend is
+    drawn (docs/plantuml/figures/pytorch-tracing.puml): same outputs as the module, the loss goes down, and the trained
+    weights can be written back into the module."""
+    from flexflow_train_b200.frontend.torch_fx import compile_module
+
+    torch.manual_seed(0)
+    net = _SmallMlp()
+    x, y = torch.randn(8, 16), torch.randint(0, 5, (8,), dtype=torch.int32)
+    cm = compile_module(net, [x], optimizer=SGDOptimizer(lr=0.1), loss_type=LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY, device="cpu")
+    assert cm.input_names == ["x"] and torch.allclose(cm(x), net(x), atol=1e-5)
+    losses = [cm.train_step(x, labels=y) for _ in range(6)]
+    assert losses[-1] < losses[0]
+    before = net.f1.weight.detach().clone()
+    assert cm.sync_parameters_to_module() == 4 and not torch.equal(before, net.f1.weight)
+    assert torch.allclose(cm(x), net(x), atol=1e-5)
+
+
+def test_torch_compile_backend_runs_the_dynamo_graph_on_the_executor():
+    from flexflow_train_b200.frontend.torch_fx import flexflow_backend
+
+    torch.manual_seed(1)
+    net = _SmallMlp()
+    x = torch.randn(8, 16)
+    compiled = torch.compile(net, backend=lambda gm, example_inputs: flexflow_backend(gm, example_inputs, device="cpu"))
+    with torch.no_grad():
+        assert torch.allclose(compiled(x), net(x), atol=1e-5)
