@@ -322,6 +322,8 @@ def main():
     ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--strategy", default="search", help="search | dp | tp | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
+    ap.add_argument("--timeline", action="store_true",
+                    help="after the timed runs, print rank 0's per-phase and per-bucket timeline of two eager steps (stderr)")
     ap.add_argument("--no-fused-collectives", action="store_true",
                     help="tensor-parallel collectives through NCCL instead of inside the GEMM kernels (baseline)")
     args = ap.parse_args()
@@ -437,6 +439,17 @@ def main():
     e2e_ms = max(e2.elapsed_time(e3), (time.perf_counter() - t0) * 1e3) / args.steps
     h2d, d2h = model.h2d_bytes_last_step, model.d2h_bytes_last_step
 
+    if args.timeline and hasattr(ex, "enable_timeline"):
+        # every rank runs the same two eager steps (collectives inside); rank 0 reports
+        was = ex.cfg.use_cuda_graph
+        ex.cfg.use_cuda_graph = False
+        ex.enable_timeline()
+        for i in range(2):
+            ex.train_step(*dev_batches[i % n_host])
+        tl = ex.timeline()
+        ex.cfg.use_cuda_graph = was
+        if rank == 0:
+            print(json.dumps({"timeline_ms": tl}), file=sys.stderr)
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -742,9 +742,48 @@ class DistExecutable(Executable):
         self.fused_update = bool(self.fuse_optimizer and self.buckets and self.shadow is not None and o.kind in ("adam", "sgd")
                                  and all((e - s) % 8 == 0 and s % 8 == 0 for s, e in self.buckets))
 
+    # ------------------------------------------------------------------ step timeline (CUDA events, eager steps only)
+    def enable_timeline(self):
+        """Record CUDA events at the phase boundaries of the following eager steps and around every gradient bucket kernel;
+        `timeline()` turns them into milliseconds.  Use with ``use_cuda_graph=False``."""
+        self._tl = {"marks": [], "buckets": []}
+
+    def _mark(self, name):
+        tl = getattr(self, "_tl", None)
+        if tl is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            tl["marks"].append((name, e))
+
+    def timeline(self) -> dict:
+        """Milliseconds, relative to the start of the last recorded step: phase boundaries on the main stream and
+        (start, end, elements) of every bucket kernel on the side stream."""
+        tl = getattr(self, "_tl", None)
+        if not tl or not tl["marks"]:
+            return {}
+        torch.cuda.synchronize()
+        starts = [i for i, (n, _) in enumerate(tl["marks"]) if n == "step_start"]
+        marks = tl["marks"][starts[-1]:]
+        t0 = marks[0][1]
+        out = {"marks": [(n, t0.elapsed_time(e)) for n, e in marks]}
+        out["buckets"] = [(t0.elapsed_time(a), t0.elapsed_time(b), n) for a, b, n in tl["buckets"] if t0.elapsed_time(a) >= 0]
+        return out
+
+    def forward(self):
+        self._mark("step_start")
+        super().forward()
+        self._mark("forward_end")
+
+    def compute_loss(self):
+        r = super().compute_loss()
+        self._mark("loss_end")
+        return r
+
     def backward(self):
         if not getattr(self, "buckets", None):
-            return super().backward()
+            r = super().backward()
+            self._mark("backward_end")
+            return r
         main = torch.cuda.current_stream()
         for nid in reversed(self.order):
             op = self.ops[nid]
@@ -754,6 +793,7 @@ class DistExecutable(Executable):
                     self._launch_bucket(bi, main)
         for bi in self._launch_after.get(-1, ()):
             self._launch_bucket(bi, main)
+        self._mark("backward_end")
 
     def _reduce_bucket(self, s, e):
         if self.fused_update:
@@ -767,7 +807,14 @@ class DistExecutable(Executable):
         if self.side is not None:
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
+                tl = getattr(self, "_tl", None)
+                if tl is not None:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
                 self._reduce_bucket(s, e)
+                if tl is not None:
+                    b.record()
+                    tl["buckets"].append((a, b, e - s))
             self._pending = True
         else:
             self._reduce_bucket(s, e)
@@ -775,6 +822,7 @@ class DistExecutable(Executable):
     def update(self, start: int = 0):
         # replicated parameters were updated (sharded over ranks) by the bucket kernels
         super().update(self.rep_numel if getattr(self, "fused_update", False) else start)
+        self._mark("update_end")
 
     def consolidate_state(self):
         """With the sharded update every rank holds current fp32 master weights and moments only for the slices it
@@ -805,6 +853,7 @@ class DistExecutable(Executable):
         if self.side is not None and self._pending:
             torch.cuda.current_stream().wait_stream(self.side)
             self._pending = False
+        self._mark("gradients_synced")
 
     def _describe(self) -> str:
         W = self.ctx.world_size
