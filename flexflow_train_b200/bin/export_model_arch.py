@@ -10,7 +10,6 @@ three switches, JSON with the keys ``computation_graph`` and, when asked, ``sp_d
 """
 from __future__ import annotations
 
-import argparse
 import json
 import sys
 
@@ -43,16 +42,44 @@ def export(model: str, sp_decomposition: bool = False, dot: bool = False, prepro
     return json.dumps(out, indent=2)
 
 
+def cli_spec():
+    """The tool's command line as a declarative spec of the native core (flags are switches, positionals may carry a set of
+    choices), the form the reference declares its tools in (lib/utils/include/utils/cli/cli_spec.h,
+    bin/export-model-arch/src/export-model-arch/export_model_arch.cc main)."""
+    d = core.dataflow
+    spec = d.empty_cli_spec()
+    keys = {
+        "help": d.cli_add_help_flag(spec),
+        "sp_decomposition": d.cli_add_flag(spec, "sp-decomposition", None, "also output a series-parallel decomposition of the graph"),
+        "dot": d.cli_add_flag(spec, "dot", None, "output a DOT drawing instead of JSON"),
+        "preprocessed_dot": d.cli_add_flag(spec, "preprocessed-dot", None, "DOT of the graph without inputs and weights"),
+        "model": d.cli_add_positional_argument(spec, "model", sorted(core.model_names()), "name of the model to export"),
+    }
+    return spec, keys
+
+
 def main(argv=None) -> int:
-    p = argparse.ArgumentParser(prog="export-model-arch", description=__doc__.split("\n")[0])
-    p.add_argument("model", choices=sorted(core.model_names()))
-    p.add_argument("--sp-decomposition", action="store_true", help="also output a series-parallel decomposition of the graph")
-    p.add_argument("--dot", action="store_true", help="output a DOT drawing instead of JSON")
-    p.add_argument("--preprocessed-dot", action="store_true", help="DOT of the graph without inputs and weights")
-    p.add_argument("--config", help="JSON object overriding fields of the model's default config")
-    a = p.parse_args(argv)
-    cfg = json.loads(a.config) if a.config else None
-    sys.stdout.write(export(a.model, a.sp_decomposition, a.dot, a.preprocessed_dot, cfg) + "\n")
+    d = core.dataflow
+    argv = list(sys.argv[1:] if argv is None else argv)
+    cfg = None
+    if "--config" in argv:  # the one valued option: a JSON object overriding fields of the model's default config
+        i = argv.index("--config")
+        if i + 1 >= len(argv):
+            sys.stderr.write("error: --config needs a JSON object\n")
+            return 2
+        cfg = json.loads(argv[i + 1])
+        del argv[i:i + 2]
+    spec, keys = cli_spec()
+    try:
+        r = d.cli_parse(spec, ["export-model-arch"] + argv)
+    except ValueError as e:
+        sys.stderr.write(f"error: {e}\n\n{d.cli_get_help_message('export-model-arch', spec)}")
+        return 2
+    if d.cli_get_flag(r, keys["help"]):
+        sys.stdout.write(d.cli_get_help_message("export-model-arch", spec))
+        return 0
+    sys.stdout.write(export(d.cli_get_argument(r, keys["model"]), d.cli_get_flag(r, keys["sp_decomposition"]),
+                            d.cli_get_flag(r, keys["dot"]), d.cli_get_flag(r, keys["preprocessed_dot"]), cfg) + "\n")
     return 0
 
 

@@ -8,6 +8,7 @@ void bind_substitutions(py::module &m);
 void bind_search(py::module &m);
 void bind_lowering(py::module &m);
 void bind_utils(py::module &m);
+void bind_dataflow(py::module &m);
 }  // namespace ff
 
 using namespace ff;
@@ -396,4 +397,5 @@ PYBIND11_MODULE(_ffcore, m) {
   bind_search(m);
   bind_lowering(m);
   bind_utils(m);
+  bind_dataflow(m);
 }
