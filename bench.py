@@ -322,6 +322,8 @@ def main():
     ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--strategy", default="search", help="search | dp | tp | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
+    ap.add_argument("--search-budget", type=int, default=10, help="Unity search budget on top of the scored templates (0 = templates only)")
+    ap.add_argument("--search-time-limit", type=float, default=30.0)
     ap.add_argument("--timeline", action="store_true",
                     help="after the timed runs, print rank 0's per-phase and per-bucket timeline of two eager steps (stderr)")
     ap.add_argument("--no-fused-collectives", action="store_true",
@@ -358,7 +360,8 @@ def main():
     global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
     opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
-                         fuse_collectives=not args.no_fused_collectives,
+                         fuse_collectives=not args.no_fused_collectives, search_budget=args.search_budget,
+                         search_time_limit_s=args.search_time_limit,
                          search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel", "tables": "table_parallel"}.get(args.strategy, "unity"),
                          import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
     model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind=opt_kind, lr=lr, momentum=momentum),

@@ -45,6 +45,12 @@ class FFConfig:
     use_cuda_graph: bool = True
     fuse_collectives: bool = True  # run all-gather / reduce-scatter inside the neighbouring GEMMs (else NCCL)
     shard_inputs: bool = True      # several ranks: an input split over the sample dim may be fed as each rank's own piece
+    # Search on measured operator costs (the reference's LocalCostEstimator): rank 0 profiles one step of the model on its
+    # GPU at every per-device batch a data-parallel degree of this machine would give, the table is sent to all ranks,
+    # and the estimator answers from it (analytic model for shapes that were not seen).  `cost_table_file` is the disk
+    # cache: read when it exists, written after a measurement.
+    measure_costs: bool = False
+    cost_table_file: Optional[str] = None
     seed: int = 0
 
 
@@ -111,6 +117,64 @@ def _as_graph(model, model_config):
     return model
 
 
+def _search_estimator(model, model_config, cg, world: int, config: "FFConfig", dist, exec_cfg):
+    """The cost estimator the strategy search runs on: analytic, or filled with measured operator costs when the config
+    asks for them (local_cost_estimator.cc:84-179 measures per query; here one profiled step per candidate shard size
+    fills the table up front).  Returns (estimator or None, info for the search statistics)."""
+    if not (config.measure_costs or config.cost_table_file):
+        return None, None
+    import os
+
+    from .compiler.strategy import machine_for
+    from .runtime import cost_measure
+    est = core.CostEstimator(machine_for(world))
+    path = config.cost_table_file
+    if path and os.path.exists(path):
+        return est, {"source": path, "entries": cost_measure.load_table(est, path)}
+    if not (config.measure_costs and torch.cuda.is_available() and exec_cfg.device != "cpu"):
+        return est, {"source": "analytic", "entries": 0}
+    table = None
+    rank = dist.rank if dist is not None else 0
+    if rank == 0:
+        table = {}
+        graphs = [(1, cg)]
+        if isinstance(model, str):
+            # the zoo rebuilds the same model at the per-device batch of every data-parallel degree of this machine
+            base = dict(model_config or {})
+            full = int(cg.shape(_first_input(cg)).sizes[0])
+            for d in range(2, world + 1):
+                if world % d == 0 and full % d == 0:
+                    graphs.append((d, core.build_model(model, dict(base, batch_size=full // d))))
+        for d, g in graphs:
+            import dataclasses
+            ex = Executable(g, dataclasses.replace(exec_cfg, use_cuda_graph=False))
+            from .bin.run_model import synthetic_batch   # late: that module imports this one
+            inputs, labels = synthetic_batch(g, ex, exec_cfg.loss, seed=config.seed, pinned=False)
+            ex.set_inputs(inputs, labels)
+            ex.profile_step()                    # warm-up: first-use allocations and kernel loading
+            table.update(cost_measure.measure_into(est, ex, steps=2))
+            del ex
+            torch.cuda.empty_cache()
+    if dist is not None and dist.world_size > 1:
+        import torch.distributed as td
+        box = [table]
+        td.broadcast_object_list(box, src=0, group=dist.group)
+        table = box[0]
+        if rank != 0:
+            for k, v in table.items():
+                est.set_measured(k, v["fwd_ms"], v["bwd_ms"], v.get("memory_bytes", 0.0))
+    if path and rank == 0:
+        cost_measure.save_table(table, path)
+    return est, {"source": "measured", "entries": len(table)}
+
+
+def _first_input(g):
+    for n in g.nodes():
+        if n["type"] == "INPUT":
+            return (n["id"], "OUTPUT")
+    raise ValueError("the graph has no input")
+
+
 def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None, *, config: Optional[FFConfig] = None,
             optimizer: Optional[OptimizerConfig] = None, loss: Optional[str] = "sparse_categorical_crossentropy",
             dist=None, training: bool = True, device: str = "cuda") -> CompiledModel:
@@ -129,9 +193,23 @@ def compile(model: Union[str, "core.Graph"], model_config: Optional[dict] = None
     strategy, stats = cg, {}
     if world > 1:
         from .compiler.strategy import choose_strategy
-        strategy, stats = choose_strategy(cg, world, config)
+        estimator, cost_info = _search_estimator(model, model_config, cg, world, config, dist, exec_cfg)
+        strategy, stats = choose_strategy(cg, world, config, estimator=estimator)
+        if cost_info:
+            stats["measured_costs"] = cost_info
         from .parallel.dist_executor import DistExecutable
-        ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives, shard_inputs=config.shard_inputs)
+        template = stats.pop("_template_strategy", None)
+        try:
+            ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives, shard_inputs=config.shard_inputs)
+        except (NotImplementedError, ValueError, KeyError) as e:
+            # a strategy the search composed from substitutions may use a placement the executor has no lowering for: every
+            # rank sees the same exception at the same point (lowering is deterministic and happens before any collective),
+            # so all of them fall back to the best hand-built template together
+            if template is None:
+                raise
+            stats["strategy_fallback"] = f"{type(e).__name__}: {e}"
+            strategy = template
+            ex = DistExecutable(strategy, exec_cfg, dist, fuse_collectives=config.fuse_collectives, shard_inputs=config.shard_inputs)
     else:
         if config.import_strategy_file:
             with open(config.import_strategy_file) as f:

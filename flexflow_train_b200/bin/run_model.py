@@ -99,6 +99,9 @@ def main(argv=None) -> int:
     p.add_argument("--optimizer", choices=["sgd", "adam"], default=None, help="default adam; sgd with momentum 0.9 for a graph file")
     p.add_argument("--search-budget", type=int, default=0)
     p.add_argument("--search-alpha", type=float, default=1.05)
+    p.add_argument("--search-time-limit", type=float, default=60.0, help="wall-clock bound of the strategy search in seconds")
+    p.add_argument("--measure-costs", action="store_true", help="search on operator costs measured on this GPU")
+    p.add_argument("--cost-table", help="file of measured operator costs: read when present, written after measuring")
     p.add_argument("--search-algorithm", choices=["unity", "mcmc", "data_parallel", "tensor_parallel", "table_parallel"], default="unity")
     p.add_argument("--only-data-parallel", action="store_true")
     p.add_argument("--enable-parameter-parallel", action="store_true")
@@ -147,7 +150,8 @@ def main(argv=None) -> int:
                        only_data_parallel=a.only_data_parallel, enable_parameter_parallel=a.enable_parameter_parallel,
                        enable_attribute_parallel=a.enable_attribute_parallel, substitution_json_path=a.substitution_json,
                        export_strategy_file=a.export_strategy, import_strategy_file=a.import_strategy, compute_dtype=a.compute_dtype,
-                       use_cuda_graph=not a.no_cuda_graph, seed=a.seed)
+                       use_cuda_graph=not a.no_cuda_graph, seed=a.seed, search_time_limit_s=a.search_time_limit,
+                       measure_costs=a.measure_costs, cost_table_file=a.cost_table)
     model = a.model
     if a.graph_json:
         with open(a.graph_json) as f:

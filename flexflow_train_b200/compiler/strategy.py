@@ -306,6 +306,7 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
     else:
         best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
     best = scored[best_name]
+    template_best = best
     stats = {"candidates": {k: v["runtime_ms"] for k, v in scored.items()}, "seed_strategy": best_name}
     origin = scored["single_device"] if start == "serial" else best
     stats["search_start"] = "serial" if start == "serial" else best_name
@@ -330,10 +331,12 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
     stats["search_seconds"] = time.time() - t0
     out = dict(best)
     out["stats"] = stats
+    # what to run if the executor cannot lower a strategy the search composed itself
+    out["template_mapped_pcg"] = template_best["mapped_pcg"] if best is not template_best else None
     return out
 
 
-def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
+def choose_strategy(cg, world: int, config, estimator=None) -> Tuple[object, dict]:
     """Strategy for `world` ranks under an FFConfig: imported from a file if given, searched otherwise."""
     if getattr(config, "import_strategy_file", None):
         with open(config.import_strategy_file) as f:
@@ -351,10 +354,12 @@ def choose_strategy(cg, world: int, config) -> Tuple[object, dict]:
     r = optimize(cg, world=world, algorithm=algo, budget=getattr(config, "search_budget", 0),
                  alpha=getattr(config, "search_alpha", 1.05), seed=getattr(config, "seed", 0),
                  time_limit_s=getattr(config, "search_time_limit_s", 60.0), start=getattr(config, "search_start", "best_template"),
-                 only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules,
+                 only_data_parallel=getattr(config, "only_data_parallel", False), rules=rules, estimator=estimator,
                  enable_parameter_parallel=getattr(config, "enable_parameter_parallel", True),
                  enable_attribute_parallel=getattr(config, "enable_attribute_parallel", True),
                  score_hybrid=getattr(config, "score_hybrid_strategies", False))
     stats = dict(r["stats"])
     stats.update(extra)
+    if r.get("template_mapped_pcg") is not None:
+        stats["_template_strategy"] = r["template_mapped_pcg"]
     return r["mapped_pcg"], stats

@@ -75,6 +75,15 @@ class AttnDesc(ctypes.Structure):
     ]
 
 
+class ConvDesc(ctypes.Structure):
+    _fields_ = [
+        ("N", c_int), ("H", c_int), ("W", c_int), ("C", c_int), ("OC", c_int), ("KH", c_int), ("KW", c_int),
+        ("pad_h", c_int), ("pad_w", c_int), ("OH", c_int), ("OW", c_int),
+        ("x", c_void_p), ("wp", c_void_p), ("ldw", c_longlong), ("y", c_void_p), ("pre", c_void_p), ("bias", c_void_p), ("act", c_int),
+        ("dy", c_void_p), ("dx", c_void_p), ("accumulate", c_int), ("dwp", c_void_p),
+    ]
+
+
 def available() -> bool:
     return os.path.exists(_LIB_PATH)
 
@@ -105,6 +114,11 @@ def _declare(l):
         "ffk_attention_bwd": [ctypes.POINTER(AttnDesc), S],
         "ffk_attention_last_error": [],
         "ffk_attention_supported": [I, I],
+        "ffk_conv_fprop": [ctypes.POINTER(ConvDesc), S],
+        "ffk_conv_dgrad": [ctypes.POINTER(ConvDesc), S],
+        "ffk_conv_wgrad": [ctypes.POINTER(ConvDesc), S],
+        "ffk_conv_implicit_supported": [I, I, I, I],
+        "ffk_conv_last_error": [],
         "ffk_unary_fwd": [I, P, P, L, F, I, S],
         "ffk_unary_bwd": [I, P, P, P, P, L, F, I, I, S],
         "ffk_binary_fwd": [I, P, P, P, L, L, I, S],
@@ -949,6 +963,54 @@ def col2im(dcol, dx, geom: ConvGeometry, accumulate=False):
     _cuda_contig(dcol, dx)
     _check(_clib().ffk_col2im(dcol.data_ptr(), dx.data_ptr(), geom._geom, geom._strides, _dt(dx), int(accumulate), _stream()),
            "ffk_col2im")
+
+
+def conv_implicit_supported(geom: "ConvGeometry", oc: int) -> bool:
+    """Whether the implicit-GEMM kernel (no im2col matrix) takes this convolution: stride 1, channel counts that are
+    multiples of 8, channels-last bf16 data."""
+    if geom.sh != 1 or geom.sw != 1 or geom.kp != geom.kh * geom.kw * geom.c:
+        return False
+    return bool(_clib().ffk_conv_implicit_supported(geom.c, oc, geom.kh, geom.kw))
+
+
+def _conv_desc(geom: "ConvGeometry", oc: int, wp) -> ConvDesc:
+    d = ConvDesc()
+    d.N, d.H, d.W, d.C, d.OC, d.KH, d.KW = geom.n, geom.h, geom.w, geom.c, oc, geom.kh, geom.kw
+    d.pad_h, d.pad_w, d.OH, d.OW = geom.ph, geom.pw, geom.oh, geom.ow
+    d.wp, d.ldw = wp.data_ptr(), wp.stride(0)
+    return d
+
+
+def conv_fprop(x, wp, y, geom: "ConvGeometry", oc: int, bias=None, act=None, pre_act_out=None):
+    """y[N, OH, OW, OC] = act(conv(x[N, H, W, C], filter) + bias) over channels-last bf16 data; `wp` is the packed filter
+    [OC, KH*KW*C]."""
+    _cuda_contig(x, wp, y)
+    d = _conv_desc(geom, oc, wp)
+    d.x, d.y = x.data_ptr(), y.data_ptr()
+    d.bias = bias.data_ptr() if bias is not None else None
+    d.pre = pre_act_out.data_ptr() if pre_act_out is not None else None
+    d.act = ACT_CODES[act]
+    _check(_clib().ffk_conv_fprop(ctypes.byref(d), _stream()), "ffk_conv_fprop")
+
+
+def conv_dgrad(dy, wp, dx, geom: "ConvGeometry", oc: int, accumulate=False):
+    """dx[N, H, W, C] (+)= the data gradient of the convolution from dy[N, OH, OW, OC]."""
+    _cuda_contig(dy, wp, dx)
+    d = _conv_desc(geom, oc, wp)
+    d.dy, d.dx, d.accumulate = dy.data_ptr(), dx.data_ptr(), int(accumulate)
+    _check(_clib().ffk_conv_dgrad(ctypes.byref(d), _stream()), "ffk_conv_dgrad")
+
+
+def conv_wgrad(x, dy, dwp, geom: "ConvGeometry", oc: int, accumulate=False):
+    """dwp[OC, KH*KW*C] (fp32, packed layout) (+)= the filter gradient."""
+    _cuda_contig(x, dy, dwp)
+    d = _conv_desc(geom, oc, dwp)
+    d.x, d.dy, d.dwp, d.accumulate = x.data_ptr(), dy.data_ptr(), dwp.data_ptr(), int(accumulate)
+    _check(_clib().ffk_conv_wgrad(ctypes.byref(d), _stream()), "ffk_conv_wgrad")
+
+
+def conv_last_error() -> int:
+    return int(_clib().ffk_conv_last_error())
 
 
 def filter_pack(w, wp, oc, c, kh, kw, kp):

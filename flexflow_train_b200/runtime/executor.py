@@ -83,6 +83,9 @@ class ExecConfig:
     # it in backward (it is KH*KW times the activation, so this trades memory for one im2col pass per convolution
     # and step).  Value: total bytes that may be kept, claimed by the convolutions in graph order; 0 = recompute.
     keep_im2col_bytes: int = 48 << 30
+    # stride-1 convolutions over channels-last data as an implicit GEMM (shifted TMA boxes of the activation, no im2col
+    # matrix); off = every K x K convolution goes through im2col + GEMM
+    implicit_conv: bool = True
 
 
 class _Buf:

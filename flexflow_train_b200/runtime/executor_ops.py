@@ -64,11 +64,14 @@ class Conv2dOp(OpImpl):
         # the activation itself is the GEMM operand of a 1x1 stride-1 convolution over channels-last data
         self.direct = pointwise and g.sh == 1 and g.sw == 1 and g.ph == 0 and g.pw == 0 and (self.in_nhwc or h * w == 1)
         self.packed = not pointwise  # a 1x1 filter [OC, C, 1, 1] already is the K-major matrix [OC, C]
+        # stride-1 convolutions over channels-last data run as an implicit GEMM: the kernel loads shifted boxes of the
+        # activation itself, so there is no im2col / col2im matrix to write, keep or read back
+        self.implicit = (not self.direct and self.in_nhwc and self.ex.cfg.implicit_conv and K.conv_implicit_supported(g, oc))
         w_ = self.x("FILTER")
         self.wp = torch.empty(oc, g.kp, dtype=torch.bfloat16, device=x.device) if self.packed else w_.view(oc, g.kp)
         self.bias = self.x("BIAS") if "BIAS" in self.inputs else None
         self.pre = torch.empty_like(self.y2d) if (self.act == "gelu" and self.ex.cfg.training) else None
-        if not self.direct:
+        if not self.direct and not self.implicit:
             self.ex.need_big_scratch(g.rows * g.kp * 2, 2)  # slot 0: col, slot 1: dcol
         # slot 2: filter gradient in GEMM layout, fp32 (the weight-gradient GEMM has few output tiles and a very long
         # reduction over N*OH*OW rows; with an fp32 output the kernel splits that reduction over the SMs)
@@ -78,7 +81,7 @@ class Conv2dOp(OpImpl):
         self._kept = None
         col_bytes = g.rows * g.kp * 2
         claimed = getattr(self.ex, "_im2col_kept_bytes", 0)
-        if not self.direct and self.ex.cfg.training and self.buf("FILTER").requires_grad and \
+        if not self.direct and not self.implicit and self.ex.cfg.training and self.buf("FILTER").requires_grad and \
                 claimed + col_bytes <= self.ex.cfg.keep_im2col_bytes:
             free = torch.cuda.mem_get_info(x.device)[0] if x.is_cuda else 0
             if col_bytes * 4 < free:  # never take more than a quarter of what is left
@@ -166,6 +169,9 @@ class Conv2dOp(OpImpl):
         if self.packed:
             g = self.g
             K.filter_pack(self.x("FILTER"), self.wp, self.oc, g.c, g.kh, g.kw, g.kp)
+        if self.implicit:
+            K.conv_fprop(self.x(), self.wp, self.out().data, self.g, self.oc, bias=self.bias, act=self.act, pre_act_out=self.pre)
+            return
         K.matmul_nt(self._operand(), self.wp, out=self.y2d, bias=self.bias, act=self.act, pre_act_out=self.pre)
 
     def backward(self):
@@ -179,6 +185,16 @@ class Conv2dOp(OpImpl):
         if self.groups != 1:
             return self._backward_grouped(dy)
         wb = self.buf("FILTER")
+        if self.implicit:
+            if wb.requires_grad:
+                if self._dwp is None:
+                    self._dwp = _scratch_view(self.ex, 2, (self.oc, g.kp), torch.float32)
+                K.conv_wgrad(self.x(), dy, self._dwp, g, self.oc)
+                K.filter_unpack(self._dwp, wb.grad, self.oc, g.c, g.kh, g.kw, g.kp, accumulate=self.acc["FILTER"])
+            xb = self.buf("INPUT")
+            if xb.requires_grad:
+                K.conv_dgrad(dy, self.wp, xb.grad, g, self.oc, accumulate=self.acc["INPUT"])
+            return
         if wb.requires_grad:
             # the forward pass's matrix when it was kept, else recomputed (it is KH*KW times the activation)
             col = self._kept if self._kept is not None else self._operand()

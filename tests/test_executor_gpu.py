@@ -373,3 +373,29 @@ def test_checkpoint_carries_sparse_embedding_tables(tmp_path):
     e = mk(True, 11)
     ckpt.load_resharded(path2, e)
     assert torch.equal(dict(e.named_parameters())["emb1.weight"].cpu(), full["emb1.weight"])
+
+
+def test_measured_costs_fill_the_search_estimator(tmp_path):
+    """FFConfig.measure_costs: one profiled step per data-parallel shard size fills the estimator the search runs on, and
+    the table is written to (then read from) the disk cache."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.api import FFConfig, _search_estimator
+    from flexflow_train_b200.runtime.executor import ExecConfig
+    cfg_model = {"batch_size": 64}
+    cg = core.build_model("mlp", cfg_model)
+    path = tmp_path / "table.json"
+    cfg = FFConfig(measure_costs=True, cost_table_file=str(path))
+    est, info = _search_estimator("mlp", cfg_model, cg, 2, cfg, None, ExecConfig(compute_dtype="bf16"))
+    assert info["source"] == "measured" and info["entries"] > 0 and est.num_measured() == info["entries"]
+    lin = [n["id"] for n in cg.nodes() if n["type"] == "LINEAR"][0]
+    cost = est.op_cost(cg, lin)
+    assert cost["fwd_ms"] > 0 and cost["bwd_ms"] > 0
+    # the half-batch graph of a 2-way data-parallel plan was measured too
+    half = core.build_model("mlp", {"batch_size": 32})
+    lin_h = [n["id"] for n in half.nodes() if n["type"] == "LINEAR"][0]
+    before = est.num_queries()
+    est.op_cost(half, lin_h)
+    assert path.exists()
+    est2, info2 = _search_estimator("mlp", cfg_model, cg, 2, FFConfig(cost_table_file=str(path)), None, ExecConfig())
+    assert info2 == {"source": str(path), "entries": info["entries"]}
+    assert est2.op_cost(cg, lin) == cost

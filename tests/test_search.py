@@ -304,3 +304,29 @@ def test_every_strategy_template_computes_the_function_of_the_computation_graph(
     a = TorchOracle(dcg, seed=1, loss="mean_squared_error_avg_reduce").loss_and_grads(ins, y)
     b = TorchOracle(S.table_parallel_strategy(dcg, 4), seed=1, loss="mean_squared_error_avg_reduce").loss_and_grads(ins, y)
     assert torch.equal(a[0], b[0]) and all(torch.equal(a[1][k], b[1][k]) for k in a[1])
+
+
+def test_cost_table_file_feeds_the_search_estimator(tmp_path):
+    """A table of measured operator costs on disk is what the search's estimator answers from (the reference's
+    LocalCostEstimator answers from measurements); shapes that were not measured keep the analytic estimate."""
+    import json
+
+    from flexflow_train_b200.api import FFConfig, _search_estimator
+    from flexflow_train_b200.compiler.strategy import choose_strategy, machine_for
+    from flexflow_train_b200.runtime.executor import ExecConfig
+    cg = c.build_model("mlp", {"batch_size": 8})
+    probe = c.CostEstimator(machine_for(2))
+    lin = [n["id"] for n in cg.nodes() if n["type"] == "LINEAR"][0]
+    key = probe.op_cost_key(cg, lin)
+    analytic = probe.op_cost(cg, lin)
+    path = tmp_path / "costs.json"
+    path.write_text(json.dumps({key: {"fwd_ms": 123.0, "bwd_ms": 456.0, "memory_bytes": 10.0}}))
+    cfg = FFConfig(cost_table_file=str(path))
+    est, info = _search_estimator("mlp", {"batch_size": 8}, cg, 2, cfg, None, ExecConfig())
+    assert info == {"source": str(path), "entries": 1}
+    measured = est.op_cost(cg, lin)
+    assert measured != analytic and abs(measured["fwd_ms"] - 123.0) < 1e-6 and abs(measured["bwd_ms"] - 456.0) < 1e-6
+    strategy, stats = choose_strategy(cg, 2, cfg, estimator=est)
+    assert strategy is not None and "candidates" in stats
+    # no table and no measurement asked for: the search builds its own analytic estimator
+    assert _search_estimator("mlp", None, cg, 2, FFConfig(), None, ExecConfig()) == (None, None)
