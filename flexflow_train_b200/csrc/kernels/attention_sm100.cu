@@ -22,10 +22,9 @@
 //   warps 2-9   softmax and output: thread = query row x half of the tile's keys (and half of the output columns);
 //               running max / sum, P_j -> shared memory (bf16, 128-byte swizzle), O = O * alpha_j + Opart[t] in registers
 //
-// Backward CTA (448 threads) = one 128-query block of one (batch, head), looping over tiles of 64 keys:
-//   S = Q K_j^T, dP = dO V_j^T (TMEM, two stages) -> eight warps (thread = query row x 32 keys) compute P and
-//   dS = P o (dP - delta) -> shared memory -> dV_j^T = dO^T P, dK_j^T = Q^T dS (TMEM, read out and added to fp32
-//   accumulators in global memory by four read-out warps) and dQ += dS K_j (TMEM accumulator, stored once at the end).
+// Backward CTA (576 threads) = one 128-key block of one (batch, head), walking over the query blocks that see it (see the
+// comment at the backward kernel): dK and dV accumulate in tensor memory and are written once; the dQ contributions of the
+// key blocks are added into an fp32 accumulator in global memory and converted to bf16 by a last small kernel.
 //
 // Every mbarrier wait is bounded (tcgen05.cuh); on expiry the CTA records a code in the library's error word,
 // frees its TMEM and returns.
@@ -38,7 +37,6 @@ namespace {
 constexpr int ATT_THREADS = 320;
 constexpr int BQ = 128;    // query rows per CTA
 constexpr int BKF = 128;   // keys per forward tile
-constexpr int BKB = 64;    // keys per backward tile
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnArgs {
@@ -53,9 +51,9 @@ struct AttnArgs {
   float *lse;             // [B, H, Sq] log2-domain log-sum-exp of the scaled scores
   // backward only
   const float *delta;     // [B, H, Sq] rowsum(dO o O)
-  bf16 *dQ;
-  long long lddq;
-  float *dK_acc, *dV_acc; // [B, H, Sk, D] fp32, zeroed by the caller
+  bf16 *dK, *dV;          // [B*Sk, ld] outputs, written once per key block
+  long long lddk, lddv;
+  float *dQ_acc;          // [B, H, Sq, D] fp32, zeroed by the caller: the key blocks of a head add into it
   int *err;
   int dbg;                // experiment switches (FFK_ATTN_DBG): parts of the kernel left out to time the rest
 };
@@ -482,37 +480,42 @@ __global__ void attn_acc_to_bf16_kernel(const float *__restrict__ acc, bf16 *__r
   }
 }
 
+// Backward main kernel.  One CTA owns a block of 128 keys of one (batch, head) and walks over the blocks of 128 queries
+// that can see it.  K and V stay in shared memory; dK and dV accumulate in tensor memory for the whole walk and are
+// written once, as bf16, at the end.  Per query block i:
+//   S = Q_i K^T, dP = dO_i V^T                      (tensor memory; S and dP one stage each)
+//   P = exp2(S * scale * log2 e - lse), dS = P o (dP o keep / keep_prob - delta)   (eight warps, thread = query row x 64 keys)
+//   dV += P^T dO_i, dK += dS^T Q_i                  (A operand = P / dS in shared memory read M-major)
+//   dQ_i^T = K^T dS^T                               (into the columns dP just left; eight warps add it to the fp32 dQ
+//                                                    accumulator in global memory: lanes = head-dim index, so one warp-wide
+//                                                    add covers 128 contiguous bytes of one query's row)
+// The tensor core sees the five products of a step in the order dV, dQ^T, dK, S(next), dP(next): the read-out of dQ^T
+// overlaps the dK and S products, and the next step's softmax overlaps the dP product.
 struct BwdCfg {
   static constexpr int D = 128;
-  static constexpr int Q_BYTES = BQ * D * 2;          // 32 KB (also dO)
-  static constexpr int KV_BYTES = BKB * D * 2;        // 16 KB: two panels of [64 keys x 128 B]
-  static constexpr int PS_BYTES = BQ * BKB * 2;       // 16 KB: P or dS tile, [128 rows x 128 B]
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_DO = OFF_Q + Q_BYTES;
-  // A K tile is needed from the first MMA of its step (S) to the last (dQ), a V tile only by the second (dP): with the
-  // step's shared-memory budget the K ring gets four stages and the V ring two, so that a K load is issued three steps
-  // before its first use and the load latency stays off the critical path.
-  static constexpr int NK = 4, NV = 2;
-  static constexpr int OFF_K = OFF_DO + Q_BYTES;       // [NK]
-  static constexpr int OFF_V = OFF_K + NK * KV_BYTES;  // [NV]
-  static constexpr int OFF_P = OFF_V + NV * KV_BYTES;  // [2]
-  static constexpr int OFF_DS = OFF_P + 2 * PS_BYTES; // [2]
-  static constexpr int OFF_BAR = OFF_DS + 2 * PS_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  // Tensor memory.  S and dP are copied into registers the moment they are complete, so one stage each is enough; dV^T and
-  // dK^T stay until four warps have added them to global memory, so they get two stages and the tensor core never waits
-  // for that read-out.
-  static constexpr int TMEM_S = 0;      // 64 columns
-  static constexpr int TMEM_DP = 64;    // 64 columns
-  static constexpr int TMEM_DVT = 128;  // dV^T[u] at 128 + u * 128 (64 columns)
-  static constexpr int TMEM_DKT = 192;  // dK^T[u] at 192 + u * 128 (64 columns)
-  static constexpr int TMEM_DQ = 384;   // 128 columns
-  static constexpr uint32_t IDESC_S = attn_idesc(128, BKB, 0, 0);     // Q K^T, dO V^T
-  static constexpr uint32_t IDESC_T = attn_idesc(128, BKB, 1, 1);     // dO^T P, Q^T dS   (both operands MN-major)
-  static constexpr uint32_t IDESC_DQ = attn_idesc(128, D, 0, 1);      // dS K
+  static constexpr int BK = 128;                          // keys per CTA
+  static constexpr int TILE_BYTES = 128 * D * 2;          // a [128 x 128] bf16 tile = two panels of [128 rows x 128 B]
+  static constexpr int PANEL = 128 * 128;                 // bytes between the two 64-column panels of a tile
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  static constexpr int OFF_Q = OFF_V + TILE_BYTES;        // [2]
+  static constexpr int OFF_DO = OFF_Q + 2 * TILE_BYTES;   // one stage: free again after the step's second product
+  static constexpr int OFF_P = OFF_DO + TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + TILE_BYTES;     // 224 KB of tiles
+  static constexpr int SLACK = 1024;                      // room to align the base to 1024 bytes (checked in the kernel)
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + SLACK;
+  static constexpr int TMEM_S = 0;
+  static constexpr int TMEM_DPQ = 128;                    // dP, then dQ^T of the same step
+  static constexpr int TMEM_DK = 256;
+  static constexpr int TMEM_DV = 384;
+  static constexpr uint32_t IDESC_SS = attn_idesc(128, 128, 0, 0);    // Q K^T, dO V^T
+  static constexpr uint32_t IDESC_T = attn_idesc(128, 128, 1, 1);     // P^T dO, dS^T Q
+  static constexpr uint32_t IDESC_DQT = attn_idesc(128, 128, 1, 0);   // K^T dS^T
 };
+static_assert(BwdCfg::SMEM_BYTES <= 232448, "backward tiles exceed the shared memory of one CTA");
 
-constexpr int BWD_THREADS = 576;  // TMA warp, MMA warp, 8 dS warps, 8 read-out warps
+constexpr int BWD_THREADS = 576;  // TMA warp, MMA warp, 8 softmax / dS warps, 8 dQ read-out warps
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -522,38 +525,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
-  uint64_t *q_full = bars;            // Q and dO
-  uint64_t *v_full = bars + 1;        // [2]
-  uint64_t *v_empty = bars + 3;       // [2] commit
-  uint64_t *sdp_full = bars + 5;      // commit
-  uint64_t *sdp_empty = bars + 6;     // 8 warps
-  uint64_t *pds_full = bars + 7;      // [2] 8 warps
-  uint64_t *pds_empty = bars + 9;     // [2] commit
-  uint64_t *dkv_full = bars + 11;     // [2] commit
-  uint64_t *dkv_empty = bars + 13;    // [2] 4 warps
-  uint64_t *dq_full = bars + 15;      // commit
-  uint64_t *k_full = bars + 16;       // [NK]
-  uint64_t *k_empty = bars + 20;      // [NK] commit
-  uint32_t *tmem_slot = (uint32_t *)(bars + 24);
+  uint64_t *kv_full = bars;
+  uint64_t *q_full = bars + 1;        // [2]
+  uint64_t *q_empty = bars + 3;       // [2] commit
+  uint64_t *do_full = bars + 5;
+  uint64_t *do_empty = bars + 6;      // commit
+  uint64_t *s_full = bars + 7;        // commit
+  uint64_t *s_empty = bars + 8;       // 8 warps
+  uint64_t *dp_full = bars + 9;       // commit
+  uint64_t *p_full = bars + 10;       // 8 warps
+  uint64_t *p_empty = bars + 11;      // commit
+  uint64_t *ds_full = bars + 12;      // 8 warps
+  uint64_t *ds_empty = bars + 13;     // commit
+  uint64_t *dq_full = bars + 14;      // commit
+  uint64_t *dq_empty = bars + 15;     // 8 warps
+  uint64_t *dkv_full = bars + 16;     // commit
+  uint32_t *tmem_slot = (uint32_t *)(bars + 17);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  if ((uintptr_t)(smem - smem_raw) > (uintptr_t)C::SLACK) {  // the launch did not leave room to align the tiles: refuse
+    if (threadIdx.x == 0 && p.err) atomicCAS(p.err, 0, (int)FFK_ERR_BAD_ARG);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nqb = (p.Sq + BQ - 1) / BQ;
-  const int qb = blockIdx.x % nqb;
-  const int bh = blockIdx.x / nqb;
+  const int nkb = (p.Sk + C::BK - 1) / C::BK;
+  const int kb = blockIdx.x % nkb;
+  const int bh = blockIdx.x / nkb;
   const int h = bh % p.H, b = bh / p.H;
-  const int q0 = qb * BQ;
-  int n_tiles = (p.Sk + BKB - 1) / BKB;
-  if (p.causal) n_tiles = min(n_tiles, (min(q0 + BQ, p.Sq) - 1) / BKB + 1);
+  const int k0 = kb * C::BK;
+  const int nqb = (p.Sq + BQ - 1) / BQ;
+  const int i0 = p.causal ? k0 / BQ : 0;     // first query block with a row that sees a key of this block (Sq == Sk)
+  const int n_it = nqb - i0;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&pds_full[s], 8); mbar_init(&pds_empty[s], 1); mbar_init(&dkv_full[s], 1); mbar_init(&dkv_empty[s], 8);
-    }
-    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(dq_full, 1);
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    mbar_init(do_full, 1); mbar_init(do_empty, 1);
+    mbar_init(s_full, 1); mbar_init(s_empty, 8); mbar_init(dp_full, 1);
+    mbar_init(p_full, 8); mbar_init(p_empty, 1); mbar_init(ds_full, 8); mbar_init(ds_empty, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_empty, 8); mbar_init(dkv_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -569,38 +579,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * C::Q_BYTES);
+      mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        tma_load_4d(smem_u32(smem + C::OFF_Q + c * BQ * 128), &tmQ, q_full, c * 64, q0, h, b);
-        tma_load_4d(smem_u32(smem + C::OFF_DO + c * BQ * 128), &tmDO, q_full, c * 64, q0, h, b);
+        tma_load_4d(smem_u32(smem + C::OFF_K + c * C::PANEL), &tmK, kv_full, c * 64, k0, h, b);
+        tma_load_4d(smem_u32(smem + C::OFF_V + c * C::PANEL), &tmV, kv_full, c * 64, k0, h, b);
       }
-      // the K and V rings advance independently: whichever has a free stage gets its next tile; the wait for progress
-      // on either is bounded like every other wait
-      int kj = 0, vj = 0;
+      // the Q ring (two stages) and the dO stage advance independently; the wait for progress on either is bounded
+      int qi = 0, di = 0;
       uint64_t t0 = ffk_globaltimer();
       uint32_t spins = 0;
-      while (kj < n_tiles || vj < n_tiles) {
+      while (qi < n_it || di < n_it) {
         bool progress = false;
-        if (kj < n_tiles) {
-          const int t = kj % C::NK;
-          if (mbar_try_wait(&k_empty[t], ((uint32_t)(kj / C::NK) & 1u) ^ 1u)) {
-            mbar_expect_tx(&k_full[t], C::KV_BYTES);
+        if (qi < n_it) {
+          const int s = qi & 1;
+          if (mbar_try_wait(&q_empty[s], ((uint32_t)(qi >> 1) & 1u) ^ 1u)) {
+            mbar_expect_tx(&q_full[s], C::TILE_BYTES);
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tma_load_4d(smem_u32(smem + C::OFF_K + t * C::KV_BYTES + c * BKB * 128), &tmK, &k_full[t], c * 64, kj * BKB, h, b);
-            ++kj;
+              tma_load_4d(smem_u32(smem + C::OFF_Q + s * C::TILE_BYTES + c * C::PANEL), &tmQ, &q_full[s], c * 64, (i0 + qi) * BQ, h, b);
+            ++qi;
             progress = true;
           }
         }
-        if (vj < n_tiles) {
-          const int t = vj % C::NV;
-          if (mbar_try_wait(&v_empty[t], ((uint32_t)(vj / C::NV) & 1u) ^ 1u)) {
-            mbar_expect_tx(&v_full[t], C::KV_BYTES);
+        if (di < n_it) {
+          if (mbar_try_wait(do_empty, ((uint32_t)di & 1u) ^ 1u)) {
+            mbar_expect_tx(do_full, C::TILE_BYTES);
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
-              tma_load_4d(smem_u32(smem + C::OFF_V + t * C::KV_BYTES + c * BKB * 128), &tmV, &v_full[t], c * 64, vj * BKB, h, b);
-            ++vj;
+            for (int c = 0; c < 2; ++c) tma_load_4d(smem_u32(smem + C::OFF_DO + c * C::PANEL), &tmDO, do_full, c * 64, (i0 + di) * BQ, h, b);
+            ++di;
             progress = true;
           }
         }
@@ -619,240 +626,262 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
-      // descriptors are built once; an MMA then costs two adds
-      const uint64_t dqA = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024), ddoA = make_smem_desc(smem_u32(smem + C::OFF_DO), 16, 1024);
-      const uint64_t dqT = make_smem_desc(smem_u32(smem + C::OFF_Q), BQ * 128, 1024), ddoT = make_smem_desc(smem_u32(smem + C::OFF_DO), BQ * 128, 1024);
-      const uint64_t dkB0 = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024), dkN0 = make_smem_desc(smem_u32(smem + C::OFF_K), BKB * 128, 1024);
-      const uint64_t dvB0 = make_smem_desc(smem_u32(smem + C::OFF_V), 16, 1024);
-      const uint64_t dpN0 = make_smem_desc(smem_u32(smem + C::OFF_P), BQ * 128, 1024), ddsN0 = make_smem_desc(smem_u32(smem + C::OFF_DS), BQ * 128, 1024);
-      const uint64_t ddsA0 = make_smem_desc(smem_u32(smem + C::OFF_DS), 16, 1024);
-      // S = Q K_j^T and dP = dO V_j^T : K-major operands, k-steps of 16 head-dim columns
-      auto issue_sdp = [&](int j) -> bool {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        const int kt = j % C::NK;
-        if (!mbar_wait(&k_full[kt], (uint32_t)(j / C::NK) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
-        if (!mbar_wait(sdp_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+      // descriptors are built once; "K-major" = the reduction runs along a row (16 / 1024), "M-major" or "N-major" = the
+      // reduction runs down the rows of the two 64-column panels (panel stride / 1024, 2048 bytes per step of 16 rows)
+      const uint64_t dK_kmaj = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024);
+      const uint64_t dK_mmaj = make_smem_desc(smem_u32(smem + C::OFF_K), C::PANEL, 1024);
+      const uint64_t dV_kmaj = make_smem_desc(smem_u32(smem + C::OFF_V), 16, 1024);
+      const uint64_t dQ_kmaj0 = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024);
+      const uint64_t dQ_nmaj0 = make_smem_desc(smem_u32(smem + C::OFF_Q), C::PANEL, 1024);
+      const uint64_t dDO_kmaj = make_smem_desc(smem_u32(smem + C::OFF_DO), 16, 1024);
+      const uint64_t dDO_nmaj = make_smem_desc(smem_u32(smem + C::OFF_DO), C::PANEL, 1024);
+      const uint64_t dP_mmaj = make_smem_desc(smem_u32(smem + C::OFF_P), C::PANEL, 1024);
+      const uint64_t dDS_mmaj = make_smem_desc(smem_u32(smem + C::OFF_DS), C::PANEL, 1024);
+      const uint64_t dDS_kmaj = make_smem_desc(smem_u32(smem + C::OFF_DS), 16, 1024);
+      // byte offset of k-step ks inside a K-major tile: 64-column panel, then 32 bytes per step
+      auto koff = [](int ks) -> uint32_t { return (uint32_t)((ks >> 2) * C::PANEL + (ks & 3) * 32); };
+      auto issue_s = [&](int it) -> bool {      // S = Q_it K^T
+        const int s = it & 1;
+        if (!mbar_wait(&q_full[s], (uint32_t)(it >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(s_empty, ((uint32_t)it & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint64_t dkB = desc_advance(dkB0, (uint32_t)(kt * C::KV_BYTES)), dvB = desc_advance(dvB0, (uint32_t)(t * C::KV_BYTES));
-        if (!(p.dbg & 32)) {
-          tc_mma_bf16<false>(tmem_base + (uint32_t)C::TMEM_S, dqA, dkB, C::IDESC_S);
+        const uint64_t a = desc_advance(dQ_kmaj0, (uint32_t)(s * C::TILE_BYTES));
+        const uint32_t d = tmem_base + (uint32_t)C::TMEM_S;
+        tc_mma_bf16<false>(d, a, dK_kmaj, C::IDESC_SS);
 #pragma unroll
-          for (int ks = 1; ks < D / 16; ++ks) {
-            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-            const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
-            tc_mma_bf16<true>(tmem_base + (uint32_t)C::TMEM_S, desc_advance(dqA, a_off), desc_advance(dkB, b_off), C::IDESC_S);
-          }
-        }
-        if (!mbar_wait(&v_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
-        if (!(p.dbg & 32)) {
-          tc_mma_bf16<false>(tmem_base + (uint32_t)C::TMEM_DP, ddoA, dvB, C::IDESC_S);
-#pragma unroll
-          for (int ks = 1; ks < D / 16; ++ks) {
-            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-            const uint32_t b_off = (uint32_t)((ks >> 2) * (BKB * 128) + (ks & 3) * 32);
-            tc_mma_bf16<true>(tmem_base + (uint32_t)C::TMEM_DP, desc_advance(ddoA, a_off), desc_advance(dvB, b_off), C::IDESC_S);
-          }
-        }
-        tc_commit(sdp_full);
-        tc_commit(&v_empty[t]);
+        for (int ks = 1; ks < D / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(a, koff(ks)), desc_advance(dK_kmaj, koff(ks)), C::IDESC_SS);
+        tc_commit(s_full);
         return true;
       };
-      if (ok && n_tiles > 0) ok = issue_sdp(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        attn_trace(p, 0, j);
-        if (j + 1 < n_tiles) { ok = issue_sdp(j + 1); if (!ok) break; }
-        attn_trace(p, 1, j);
-        ok = mbar_wait(&pds_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
-        attn_trace(p, 2, j);
-        ok = ok && mbar_wait(&dkv_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
-        attn_trace(p, 3, j);
+      auto issue_dp = [&](int it) -> bool {     // dP = dO_it V^T, into the columns the previous step's dQ^T has left
+        if (!mbar_wait(do_full, (uint32_t)it & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(dq_empty, ((uint32_t)it & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)C::TMEM_DPQ;
+        tc_mma_bf16<false>(d, dDO_kmaj, dV_kmaj, C::IDESC_SS);
+#pragma unroll
+        for (int ks = 1; ks < D / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dDO_kmaj, koff(ks)), desc_advance(dV_kmaj, koff(ks)), C::IDESC_SS);
+        tc_commit(dp_full);
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_s(0) && issue_dp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t ph = (uint32_t)it & 1u;
+        // dV += P^T dO_it
+        ok = mbar_wait(p_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t dpN = desc_advance(dpN0, (uint32_t)(t * C::PS_BYTES)), ddsN = desc_advance(ddsN0, (uint32_t)(t * C::PS_BYTES));
-        const uint64_t ddsA = desc_advance(ddsA0, (uint32_t)(t * C::PS_BYTES));
-        const uint64_t dkN = desc_advance(dkN0, (uint32_t)((j % C::NK) * C::KV_BYTES));
-        // dV_j^T [D x 64] = dO^T P and dK_j^T = Q^T dS: A = dO / Q read M-major (M = head dim: two 64-column panels, LBO = panel
-        // stride), B = P / dS read N-major (N = 64 keys, one panel); every k-step is 16 query rows = 2048 bytes
-        if (!(p.dbg & 64)) {
-          const uint32_t dvt = tmem_base + (uint32_t)(C::TMEM_DVT + t * 128), dkt = tmem_base + (uint32_t)(C::TMEM_DKT + t * 128);
-          tc_mma_bf16<false>(dvt, ddoT, dpN, C::IDESC_T);
+        {
+          const uint32_t d = tmem_base + (uint32_t)C::TMEM_DV;
+          if (it == 0) tc_mma_bf16<false>(d, dP_mmaj, dDO_nmaj, C::IDESC_T);
+          else tc_mma_bf16<true>(d, dP_mmaj, dDO_nmaj, C::IDESC_T);
 #pragma unroll
-          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(dvt, desc_advance(ddoT, ks * 2048u), desc_advance(dpN, ks * 2048u), C::IDESC_T);
-          tc_mma_bf16<false>(dkt, dqT, ddsN, C::IDESC_T);
-#pragma unroll
-          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(dkt, desc_advance(dqT, ks * 2048u), desc_advance(ddsN, ks * 2048u), C::IDESC_T);
+          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dP_mmaj, ks * 2048u), desc_advance(dDO_nmaj, ks * 2048u), C::IDESC_T);
         }
-        tc_commit(&dkv_full[t]);
-        // dQ += dS K_j: A = dS K-major (64 keys = one panel, 32 bytes per k-step), B = K_j N-major (N = head dim, 16 key rows per step)
-        if (!(p.dbg & 128)) {
-          const uint32_t dqt = tmem_base + (uint32_t)C::TMEM_DQ;
-          if (j == 0) tc_mma_bf16<false>(dqt, ddsA, dkN, C::IDESC_DQ);
-          else tc_mma_bf16<true>(dqt, ddsA, dkN, C::IDESC_DQ);
+        tc_commit(p_empty);
+        tc_commit(do_empty);
+        // dQ_it^T = K^T dS^T (the dS warps have read dP out of these columns before they wrote dS)
+        ok = mbar_wait(ds_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint32_t d = tmem_base + (uint32_t)C::TMEM_DPQ;
+          tc_mma_bf16<false>(d, dK_mmaj, dDS_kmaj, C::IDESC_DQT);
 #pragma unroll
-          for (int ks = 1; ks < BKB / 16; ++ks) tc_mma_bf16<true>(dqt, desc_advance(ddsA, ks * 32u), desc_advance(dkN, ks * 2048u), C::IDESC_DQ);
+          for (int ks = 1; ks < C::BK / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dK_mmaj, ks * 2048u), desc_advance(dDS_kmaj, koff(ks)), C::IDESC_DQT);
         }
-        tc_commit(&k_empty[j % C::NK]);
-        tc_commit(&pds_empty[t]);
-        attn_trace(p, 4, j);
+        tc_commit(dq_full);
+        // dK += dS^T Q_it
+        {
+          const uint32_t d = tmem_base + (uint32_t)C::TMEM_DK;
+          const uint64_t bq = desc_advance(dQ_nmaj0, (uint32_t)((it & 1) * C::TILE_BYTES));
+          if (it == 0) tc_mma_bf16<false>(d, dDS_mmaj, bq, C::IDESC_T);
+          else tc_mma_bf16<true>(d, dDS_mmaj, bq, C::IDESC_T);
+#pragma unroll
+          for (int ks = 1; ks < BQ / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dDS_mmaj, ks * 2048u), desc_advance(bq, ks * 2048u), C::IDESC_T);
+        }
+        tc_commit(ds_empty);
+        tc_commit(&q_empty[it & 1]);
+        if (it + 1 < n_it) ok = issue_s(it + 1) && issue_dp(it + 1);
       }
-      if (ok) tc_commit(dq_full);
+      if (ok) tc_commit(dkv_full);
     }
   } else if (warp < 10) {
-    // ------------------------------------------------------------------ P and dS: thread = query row x 32 of the tile's 64 keys
-    // Eight warps, two per TMEM lane quarter (w % 4), each on one half of the key columns, so that every scheduler has two
-    // warps to switch between while tensor-memory loads and exponentials are in flight.
+    // ------------------------------------------------------------------ P and dS: thread = query row x 64 of the block's 128 keys
+    // Eight warps, two per TMEM lane quarter (w % 4), each on one half of the key columns.
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const int q = q0 + r;
     const float sl2 = p.scale * LOG2E;
-    const bool row_ok = q < p.Sq;
-    const long long stat = ((long long)(b * p.H + h)) * p.Sq + q;
-    const float lse = row_ok ? p.lse[stat] : INFINITY;
-    const float dlt = row_ok ? p.delta[stat] : 0.f;
     const bool drop = p.drop_p > 0.f;
     const float inv_keep = drop ? 1.f / (1.f - p.drop_p) : 1.f;
     const uint32_t thr = ffk_drop_threshold(p.drop_p);
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
     const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
-    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t prow = smem_u32(smem + C::OFF_P + half * C::PANEL + r * 128);     // this row in this half's 64-key panel
+    const uint32_t dsrow = smem_u32(smem + C::OFF_DS + half * C::PANEL + r * 128);
+    const int kbase = k0 + half * 64;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int t = j & 1;
-      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      ok = mbar_wait(sdp_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const uint32_t ph = (uint32_t)it & 1u;
+      const int q = (i0 + it) * BQ + r;
+      const bool row_ok = q < p.Sq;
+      const long long stat = ((long long)(b * p.H + h)) * p.Sq + q;
+      const float lse = row_ok ? p.lse[stat] : INFINITY;
+      const float dlt = row_ok ? p.delta[stat] : 0.f;
+      const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+      int kmax = p.Sk - kbase;
+      if (p.causal) kmax = min(kmax, q - kbase + 1);
+      ok = mbar_wait(s_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
+           mbar_wait(p_empty, ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (warp == 2) attn_trace(p, 10, j);
       tc_fence_after();
-      uint32_t rs[32], rd[32];
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + half * 32), rs);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DP + half * 32), rd);
-      tmem_ld_wait();
-      tc_fence_before();
-      if (warp == 2) attn_trace(p, 11, j);
-      warp_arrive(sdp_empty, lane);       // scores and dP are in registers
-      const int k0 = j * BKB + half * 32;
-      int kmax = p.Sk - k0;
-      if (p.causal) kmax = min(kmax, q - k0 + 1);
-      const bool full = kmax >= 32;
-      // rs <- packed P (dropped entries zeroed: the operand of dV), rd <- packed dS = P o (dP o mask / keep - delta)
-      if (!(p.dbg & 256))
+      uint32_t pe[32];          // the row's 64 probabilities before dropout, packed bf16 (dS needs them again)
+      uint32_t dropped[2] = {0u, 0u};
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        float e[4], g[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          e[u] = exp2f(fmaf(__uint_as_float(rs[i + u]), sl2, -lse));
-          if (!full && i + u >= kmax) e[u] = 0.f;
-          g[u] = __uint_as_float(rd[i + u]) * inv_keep;
-        }
-        if (drop) {
-          const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
-          const bool d0 = (uint32_t)(z & 0xFFFFu) < thr, d1 = (uint32_t)((z >> 16) & 0xFFFFu) < thr;
-          const bool d2 = (uint32_t)((z >> 32) & 0xFFFFu) < thr, d3 = (uint32_t)(z >> 48) < thr;
-          g[0] = e[0] * ((d0 ? 0.f : g[0]) - dlt); g[1] = e[1] * ((d1 ? 0.f : g[1]) - dlt);
-          g[2] = e[2] * ((d2 ? 0.f : g[2]) - dlt); g[3] = e[3] * ((d3 ? 0.f : g[3]) - dlt);
-          if (d0) e[0] = 0.f;
-          if (d1) e[1] = 0.f;
-          if (d2) e[2] = 0.f;
-          if (d3) e[3] = 0.f;
-        } else {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) g[u] = e[u] * (g[u] - dlt);
-        }
-        rs[i >> 1] = pack_bf162(e[0], e[1]); rs[(i >> 1) + 1] = pack_bf162(e[2], e[3]);
-        rd[i >> 1] = pack_bf162(g[0], g[1]); rd[(i >> 1) + 1] = pack_bf162(g[2], g[3]);
-      }
-      if (warp == 2) attn_trace(p, 12, j);
-      ok = mbar_wait(&pds_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (warp == 2) attn_trace(p, 13, j);
-      const uint32_t prow = smem_u32(smem + C::OFF_P + t * C::PS_BYTES + r * 128);
-      const uint32_t dsrow = smem_u32(smem + C::OFF_DS + t * C::PS_BYTES + r * 128);
-      if (!(p.dbg & 512))
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const uint32_t sw = (uint32_t)(((half * 4 + u) ^ (r & 7)) << 4);   // 16-byte chunk index XOR row % 8: the 128-byte swizzle
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + sw), "r"(rs[4 * u]), "r"(rs[4 * u + 1]), "r"(rs[4 * u + 2]),
-                     "r"(rs[4 * u + 3])
-                     : "memory");
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dsrow + sw), "r"(rd[4 * u]), "r"(rd[4 * u + 1]), "r"(rd[4 * u + 2]),
-                     "r"(rd[4 * u + 3])
-                     : "memory");
-      }
-      if (warp == 2) attn_trace(p, 14, j);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      warp_arrive(&pds_full[t], lane);
-      if (warp == 2) attn_trace(p, 15, j);
-    }
-    // dQ of this block: scale * accumulator -> bf16; each half stores 64 of the 128 columns
-    if (ok) {
-      ok = mbar_wait(dq_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
-      bf16 *dqrow = p.dQ + ((long long)b * p.Sq + q) * p.lddq + (long long)h * D + half * (D / 2);
-#pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DQ + half * (D / 2) + c * 32), rr);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32];
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_S + half * 64 + c * 32), rs);
         tmem_ld_wait();
-        if (row_ok) {
+        if (c == 1) {           // the scores are in registers: the next step's S may overwrite them
+          tc_fence_before();
+          warp_arrive(s_empty, lane);
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          float e[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            uint4 v = make_uint4(pack_bf162(__uint_as_float(rr[8 * u]) * p.scale, __uint_as_float(rr[8 * u + 1]) * p.scale),
-                                 pack_bf162(__uint_as_float(rr[8 * u + 2]) * p.scale, __uint_as_float(rr[8 * u + 3]) * p.scale),
-                                 pack_bf162(__uint_as_float(rr[8 * u + 4]) * p.scale, __uint_as_float(rr[8 * u + 5]) * p.scale),
-                                 pack_bf162(__uint_as_float(rr[8 * u + 6]) * p.scale, __uint_as_float(rr[8 * u + 7]) * p.scale));
-            *reinterpret_cast<uint4 *>(dqrow + c * 32 + 8 * u) = v;
+            e[u] = exp2f(fmaf(__uint_as_float(rs[i + u]), sl2, -lse));
+            if (c * 32 + i + u >= kmax) e[u] = 0.f;
+          }
+          pe[c * 16 + (i >> 1)] = pack_bf162(e[0], e[1]);
+          pe[c * 16 + (i >> 1) + 1] = pack_bf162(e[2], e[3]);
+          if (drop) {
+            const uint64_t z = attn_rand4(seed, row_base, (kbase + c * 32 + i) >> 2);
+            const uint32_t m = ((uint32_t)(z & 0xFFFFu) < thr ? 1u : 0u) | ((uint32_t)((z >> 16) & 0xFFFFu) < thr ? 2u : 0u) |
+                               ((uint32_t)((z >> 32) & 0xFFFFu) < thr ? 4u : 0u) | ((uint32_t)(z >> 48) < thr ? 8u : 0u);
+            dropped[c] |= m << i;
+            if (m & 1u) e[0] = 0.f;
+            if (m & 2u) e[1] = 0.f;
+            if (m & 4u) e[2] = 0.f;
+            if (m & 8u) e[3] = 0.f;
+          }
+          pk[i >> 1] = pack_bf162(e[0], e[1]);
+          pk[(i >> 1) + 1] = pack_bf162(e[2], e[3]);
+        }
+        // 32 probabilities = 64 bytes = four 16-byte chunks; chunk index XOR (row % 8) is the 128-byte swizzle
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)(((c * 4 + u) ^ (r & 7)) << 4)), "r"(pk[4 * u]),
+                       "r"(pk[4 * u + 1]), "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
+                       : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      warp_arrive(p_full, lane);
+      // dS = P o (dP o keep / keep_prob - delta)
+      ok = mbar_wait(dp_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
+           mbar_wait(ds_empty, ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rd[32];
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + half * 64 + c * 32), rd);
+        tmem_ld_wait();
+        if (c == 1) tc_fence_before();   // ordered before the arrival below, which lets dQ^T overwrite these columns
+        uint32_t gk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 e = unpack_bf162(pe[c * 16 + (i >> 1)]);
+          float g0 = __uint_as_float(rd[i]) * inv_keep, g1 = __uint_as_float(rd[i + 1]) * inv_keep;
+          if (drop) {
+            if ((dropped[c] >> i) & 1u) g0 = 0.f;
+            if ((dropped[c] >> (i + 1)) & 1u) g1 = 0.f;
+          }
+          gk[i >> 1] = pack_bf162(e.x * (g0 - dlt), e.y * (g1 - dlt));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dsrow + (uint32_t)(((c * 4 + u) ^ (r & 7)) << 4)), "r"(gk[4 * u]),
+                       "r"(gk[4 * u + 1]), "r"(gk[4 * u + 2]), "r"(gk[4 * u + 3])
+                       : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      warp_arrive(ds_full, lane);
+    }
+    // dK and dV of this key block: thread = key row x 64 of the 128 head-dim columns
+    if (ok && n_it > 0) {
+      ok = mbar_wait(dkv_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const int key = k0 + r;
+      bf16 *dkrow = p.dK + ((long long)b * p.Sk + key) * p.lddk + (long long)h * D + half * 64;
+      bf16 *dvrow = p.dV + ((long long)b * p.Sk + key) * p.lddv + (long long)h * D + half * 64;
+#pragma unroll 1
+      for (int w = 0; w < 2; ++w) {            // 0: dK (times the score scale), 1: dV (times 1 / keep_prob)
+        const float f = w == 0 ? p.scale : inv_keep;
+        bf16 *orow = w == 0 ? dkrow : dvrow;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rr[32];
+          if (n_it > 0) {
+            tmem_ld32(lane_base + (uint32_t)((w == 0 ? C::TMEM_DK : C::TMEM_DV) + half * 64 + c * 32), rr);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rr[i] = 0u;
+          }
+          if (key < p.Sk) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 v = make_uint4(pack_bf162(__uint_as_float(rr[8 * u]) * f, __uint_as_float(rr[8 * u + 1]) * f),
+                                   pack_bf162(__uint_as_float(rr[8 * u + 2]) * f, __uint_as_float(rr[8 * u + 3]) * f),
+                                   pack_bf162(__uint_as_float(rr[8 * u + 4]) * f, __uint_as_float(rr[8 * u + 5]) * f),
+                                   pack_bf162(__uint_as_float(rr[8 * u + 6]) * f, __uint_as_float(rr[8 * u + 7]) * f));
+              *reinterpret_cast<uint4 *>(orow + c * 32 + 8 * u) = v;
+            }
           }
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ read-out of dV_j^T / dK_j^T: thread = head-dim index
-    // Eight warps: TMEM lane quarter w % 4 (= 32 head-dim indices) and 32 of the tile's 64 keys each.  A warp-wide add
-    // covers 32 consecutive floats of one key's row in the fp32 accumulators.
+    // ------------------------------------------------------------------ read-out of dQ_it^T: thread = head-dim index x 64 queries
+    // Eight warps: TMEM lane quarter w % 4 (= 32 head-dim indices) and 64 of the block's 128 queries each.  A warp-wide add
+    // covers 32 consecutive floats of one query's row in the fp32 accumulator.
     const int quarter = warp & 3;
-    const int half = (warp - 10) >> 2;
+    const int qhalf = (warp - 10) >> 2;
     const int dcol = quarter * 32 + lane;
-    const float inv_keep = p.drop_p > 0.f ? 1.f / (1.f - p.drop_p) : 1.f;
-    float *dv_base = p.dV_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
-    float *dk_base = p.dK_acc + ((long long)(b * p.H + h) * p.Sk) * D + dcol;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float *acc_base = p.dQ_acc + ((long long)(b * p.H + h) * p.Sq) * D + dcol;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int t = j & 1;
-      ok = mbar_wait(&dkv_full[t], (uint32_t)(j >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+    for (int it = 0; it < n_it && ok; ++it) {
+      ok = mbar_wait(dq_full, (uint32_t)it & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (warp == 10) attn_trace(p, 20, j);
       tc_fence_after();
-      const int k0 = j * BKB + half * 32;
-      const int kn = (p.dbg & 1024) ? 0 : min(32, p.Sk - k0);
       uint32_t ra[32], rb[32];
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DVT + t * 128 + half * 32), ra);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DKT + t * 128 + half * 32), rb);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64), ra);
+      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64 + 32), rb);
       tmem_ld_wait();
       tc_fence_before();
-      warp_arrive(&dkv_empty[t], lane);
-      if (warp == 10) attn_trace(p, 21, j);
-      float *dvp = dv_base + (long long)k0 * D, *dkp = dk_base + (long long)k0 * D;
+      warp_arrive(dq_empty, lane);
+      const int qb0 = (i0 + it) * BQ + qhalf * 64;
+      const int qn = p.Sq - qb0;               // queries of this half that exist
+      float *dst = acc_base + (long long)qb0 * D;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (i < kn) {
-          atomicAdd(dvp + i * D, __uint_as_float(ra[i]) * inv_keep);
-          atomicAdd(dkp + i * D, __uint_as_float(rb[i]) * p.scale);
-        }
-      if (warp == 10) attn_trace(p, 22, j);
+        if (i < qn) atomicAdd(dst + i * D, __uint_as_float(ra[i]) * p.scale);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (32 + i < qn) atomicAdd(dst + (32 + i) * D, __uint_as_float(rb[i]) * p.scale);
     }
   }
 
@@ -863,6 +892,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
+
 
 // ------------------------------------------------------------------------------------------------ host side
 // 4-D map {head-dim column, row within the sequence, head, batch} of a [B*S, ld] matrix; box = 64 columns x box_rows rows
@@ -903,12 +933,12 @@ struct FfkAttnDesc {
   void *dQ; long long lddq;
   void *dK; long long lddk;
   void *dV; long long lddv;
-  void *acc;                   // 2 * B*H*Sk*D floats of scratch (dK and dV accumulators)
+  void *acc;                   // B*H*Sq*D floats of scratch (the dQ accumulator the key blocks add into)
 };
 
 // 1 when the fused kernels cover this head dimension / direction
 FFK_API int ffk_attention_supported(int D, int backward) { return backward ? (D == 128) : (D == 64 || D == 128); }
-FFK_API long long ffk_attention_bwd_scratch_floats(int B, int H, int Sk, int D) { return 2ll * B * H * Sk * D; }
+FFK_API long long ffk_attention_bwd_scratch_floats(int B, int H, int Sq, int D) { return 1ll * B * H * Sq * D; }
 
 FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
   if (d->D != 64 && d->D != 128) return -2;
@@ -963,10 +993,10 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   int r;
   if ((r = make_head_map(&tq, d->Q, D, d->Sq, d->ldq, d->H, d->B, BQ))) return r;
   if ((r = make_head_map(&tdo, d->dO, D, d->Sq, d->lddo, d->H, d->B, BQ))) return r;
-  if ((r = make_head_map(&tk, d->K, D, d->Sk, d->ldk, d->H, d->B, BKB))) return r;
-  if ((r = make_head_map(&tv, d->V, D, d->Sk, d->ldv, d->H, d->B, BKB))) return r;
-  const long long n_acc = (long long)d->B * d->H * d->Sk * D;
-  cudaError_t e = cudaMemsetAsync(d->acc, 0, (size_t)(2 * n_acc) * sizeof(float), stream);
+  if ((r = make_head_map(&tk, d->K, D, d->Sk, d->ldk, d->H, d->B, BwdCfg::BK))) return r;
+  if ((r = make_head_map(&tv, d->V, D, d->Sk, d->ldv, d->H, d->B, BwdCfg::BK))) return r;
+  const long long n_acc = (long long)d->B * d->H * d->Sq * D;
+  cudaError_t e = cudaMemsetAsync(d->acc, 0, (size_t)n_acc * sizeof(float), stream);
   if (e != cudaSuccess) return (int)e;
   {
     const long long warps = (long long)d->B * d->Sq * d->H;
@@ -977,24 +1007,21 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   a.B = d->B; a.H = d->H; a.Sq = d->Sq; a.Sk = d->Sk; a.scale = d->scale; a.causal = d->causal;
   a.drop_p = d->drop_p; a.drop_salt = d->drop_salt; a.drop_seed_ptr = (const unsigned long long *)d->drop_seed_ptr;
   a.lse = (float *)d->lse; a.delta = (const float *)d->delta;
-  a.dQ = (bf16 *)d->dQ; a.lddq = d->lddq;
-  a.dK_acc = (float *)d->acc; a.dV_acc = (float *)d->acc + n_acc;
+  a.dK = (bf16 *)d->dK; a.lddk = d->lddk; a.dV = (bf16 *)d->dV; a.lddv = d->lddv;
+  a.dQ_acc = (float *)d->acc;
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
-  { const char *e = getenv("FFK_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
   static bool attr = false;
   if (!attr) {
     e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
-  const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
+  const long long grid = (long long)((d->Sk + BwdCfg::BK - 1) / BwdCfg::BK) * d->H * d->B;
   if (grid > 0x7fffffffll) return -2;
   attn_bwd_kernel<<<(unsigned)grid, BWD_THREADS, BwdCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
-  const int cblocks = ffk_blocks(n_acc / 4, 256);
-  attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dK_acc, (bf16 *)d->dK, d->lddk, d->B, d->H, d->Sk);
-  attn_acc_to_bf16_kernel<D><<<cblocks, 256, 0, stream>>>(a.dV_acc, (bf16 *)d->dV, d->lddv, d->B, d->H, d->Sk);
+  attn_acc_to_bf16_kernel<D><<<ffk_blocks(n_acc / 4, 256), 256, 0, stream>>>(a.dQ_acc, (bf16 *)d->dQ, d->lddq, d->B, d->H, d->Sq);
   return (int)cudaGetLastError();
 }
 

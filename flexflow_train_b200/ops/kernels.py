@@ -285,8 +285,9 @@ def attention_supported(head_dim: int, backward: bool = True) -> bool:
     return bool(lib().ffk_attention_supported(int(head_dim), int(backward)))
 
 
-def attention_bwd_scratch_floats(B, H, Sk, D) -> int:
-    return int(lib().ffk_attention_bwd_scratch_floats(B, H, Sk, D))
+def attention_bwd_scratch_floats(B, H, Sq, D) -> int:
+    """fp32 elements of scratch `attention_bwd` needs (the dQ accumulator)."""
+    return int(lib().ffk_attention_bwd_scratch_floats(B, H, Sq, D))
 
 
 def attention_last_error() -> int:
@@ -328,7 +329,7 @@ def attention_fwd(q, k, v, out, lse, *, B, H, Sq, Sk, D, scale, causal=False, dr
 
 def attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, *, B, H, Sq, Sk, D, scale, causal=False, dropout=None):
     """Gradients of `attention_fwd` with respect to q, k, v (same layouts).  delta: fp32 scratch of B*H*Sq elements;
-    acc: fp32 scratch of attention_bwd_scratch_floats(B, H, Sk, D) elements."""
+    acc: fp32 scratch of attention_bwd_scratch_floats(B, H, Sq, D) elements."""
     d = _attn_desc(B, H, Sq, Sk, D, scale, causal, dropout)
     d.Q, d.ldq = _attn_view(q, D, H)
     d.K, d.ldk = _attn_view(k, D, H)
@@ -338,7 +339,7 @@ def attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, *, B, H, Sq, 
     d.dQ, d.lddq = _attn_view(dq, D, H)
     d.dK, d.lddk = _attn_view(dk, D, H)
     d.dV, d.lddv = _attn_view(dv, D, H)
-    if delta.dtype != torch.float32 or delta.numel() < B * H * Sq or acc.dtype != torch.float32 or acc.numel() < 2 * B * H * Sk * D:
+    if delta.dtype != torch.float32 or delta.numel() < B * H * Sq or acc.dtype != torch.float32 or acc.numel() < B * H * Sq * D:
         raise KernelError("attention_bwd scratch too small")
     d.lse, d.delta, d.acc = lse.data_ptr(), delta.data_ptr(), acc.data_ptr()
     _check(lib().ffk_attention_bwd(ctypes.byref(d), _stream()), "ffk_attention_bwd")

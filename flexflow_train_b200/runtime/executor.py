@@ -421,7 +421,7 @@ class AttentionOp(OpImpl):
         if self.fused:
             self.lse = torch.empty(self.B, H, self.Sq, dtype=torch.float32, device=dev)
             if ex.cfg.training:   # delta [B, H, Sq] followed by the fp32 dK / dV accumulators
-                ex.need_scratch(4 * (self.B * H * self.Sq + 4 + K.attention_bwd_scratch_floats(self.B, H, self.Sk, kd)))
+                ex.need_scratch(4 * (self.B * H * self.Sq + 4 + K.attention_bwd_scratch_floats(self.B, H, self.Sq, kd)))
         elif ex.on_gpu and blk > 0 and self.B * per_batch > 2 * blk:
             if per_batch <= blk:
                 self.cb = max(1, min(self.B, blk // per_batch))

@@ -99,6 +99,27 @@ def test_attention_backward_matches_fp32_autograd(S, causal, p):
     assert rel(dq, qf.grad) < 1.5e-2
 
 
+def test_attention_backward_cross_lengths():
+    """Query and key lengths that differ and are not multiples of the block sizes; separate q / k / v / gradient matrices."""
+    B, H, D, Sq, Sk = 2, 3, 128, 200, 333
+    torch.manual_seed(11)
+    q, k, v = (torch.randn(B * n, H * D, device="cuda").mul(0.7).to(torch.bfloat16) for n in (Sq, Sk, Sk))
+    out = torch.zeros(B * Sq, H * D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, H, Sq, device="cuda")
+    scale = 1.0 / math.sqrt(D)
+    K.attention_fwd(q, k, v, out, lse, B=B, H=H, Sq=Sq, Sk=Sk, D=D, scale=scale)
+    dout = (torch.randn(B * Sq, H * D, device="cuda") * 0.5).to(torch.bfloat16)
+    dq, dk, dv = torch.full_like(q, 3.0), torch.full_like(k, 3.0), torch.full_like(v, 3.0)
+    delta = torch.empty(B * H * Sq, device="cuda")
+    acc = torch.empty(K.attention_bwd_scratch_floats(B, H, Sq, D), device="cuda")
+    K.attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, B=B, H=H, Sq=Sq, Sk=Sk, D=D, scale=scale)
+    assert K.attention_last_error() == 0
+    qf, kf, vf = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    ref = _reference(qf, kf, vf, B, H, Sq, Sk, D, scale, False, None, 0.0)
+    ref.backward(dout.float())
+    assert rel(dv, vf.grad) < 1.5e-2 and rel(dk, kf.grad) < 1.5e-2 and rel(dq, qf.grad) < 1.5e-2
+
+
 def test_attention_mask_changes_with_the_step_seed():
     B, H, D, S = 1, 2, 128, 256
     qkv, q, k, v = _packed_qkv(B, S, H, D, seed=3)
