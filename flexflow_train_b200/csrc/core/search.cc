@@ -183,12 +183,36 @@ OpCost CostEstimator::op_cost(const Node &n, const Graph &g) const {
 }
 
 // ---------------------------------------------------------------- machine views
-std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m) {
+std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m, bool strided) {
   int count = 1;
   for (int d : task_degrees) count *= d;
   std::vector<MachineView> out;
   if (count > r.count) return out;
   const int per_node = m.num_gpus_per_node;
+  if (strided && count > 1) {
+    // Strided placements inside one node (the reference's MachineView stride, allowed_machine_views.cc:51-162): the
+    // tasks sit on every s-th device, s a power of two, so that s interleaved groups tile a block of count * s devices.
+    // s = 1 gives the contiguous views below.  On an NVSwitch node all of them cost the same, which is why the mapping
+    // search does not ask for them; a machine with a ring or a mesh between its GPUs would.
+    for (int s = 2; count * s <= r.count && r.start % per_node + r.count <= per_node; s *= 2) {
+      for (int block = r.start; block + count * s <= r.start + r.count; block += count * s) {
+        for (int off = 0; off < s; ++off) {
+          MachineView v;
+          v.start_node = (block + off) / per_node;
+          v.start_device = (block + off) % per_node;
+          int stride = s;
+          std::vector<MachineViewDim> dims(task_degrees.size());
+          for (int i = (int)task_degrees.size() - 1; i >= 0; --i) {
+            dims[i] = {stride, false};
+            stride *= task_degrees[i];
+          }
+          v.dims = dims;
+          out.push_back(v);
+        }
+      }
+    }
+  }
+  std::vector<MachineView> contiguous;
   for (int start = r.start; start + count <= r.start + r.count; start += count) {
     MachineView v;
     v.start_node = start / per_node;
@@ -202,9 +226,10 @@ std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degr
       stride *= task_degrees[i];
     }
     v.dims = dims;
-    out.push_back(v);
+    contiguous.push_back(v);
   }
-  return out;
+  contiguous.insert(contiguous.end(), out.begin(), out.end());   // contiguous views first, then the strided ones
+  return contiguous;
 }
 std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task_degrees, const MachineSpec &m) {
   std::vector<int> devs;
@@ -1023,11 +1048,11 @@ void bind_search(py::module &m) {
       .def("num_measured", [](const CostEstimator &e) { return e.measured.size(); })
       .def("movement_cost_ms", &CostEstimator::movement_cost_ms)
       .def_readonly("num_queries", &CostEstimator::num_queries);
-  m.def("allowed_machine_views", [](std::vector<int> task, int start, int count, const MachineSpec &ms) {
+  m.def("allowed_machine_views", [](std::vector<int> task, int start, int count, const MachineSpec &ms, bool strided) {
     py::list l;
-    for (auto &v : allowed_machine_views(task, Resources{start, count}, ms)) l.append(json_to_py(v.to_json()));
+    for (auto &v : allowed_machine_views(task, Resources{start, count}, ms, strided)) l.append(json_to_py(v.to_json()));
     return l;
-  });
+  }, py::arg("task_degrees"), py::arg("start"), py::arg("count"), py::arg("machine"), py::arg("strided") = false);
   m.def("get_tensor_set_movement", [](const Graph &g, NodeId src, py::object vs, NodeId dst, py::object vd, const MachineSpec &ms) {
     py::list out;
     for (auto &e : get_tensor_set_movement(g, src, MachineView::from_json(json_from_py(vs)), dst, MachineView::from_json(json_from_py(vd)), ms)) {

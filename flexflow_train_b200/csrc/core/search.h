@@ -64,7 +64,8 @@ struct Resources {
   int count = 1;
   bool operator<(const Resources &o) const { return std::tie(start, count) < std::tie(o.start, o.count); }
 };
-std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m);
+std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degrees, const Resources &r, const MachineSpec &m,
+                                               bool strided = false);
 std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task_degrees, const MachineSpec &m);
 // one tensor piece that has to travel between two devices
 struct CommunicationEdge {

@@ -434,6 +434,387 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ================================================================================================ forward, two query tiles per CTA
+// One CTA = 256 queries of one (batch, head) as two independent 128-row tiles that share every K and V tile brought into
+// shared memory (half the L2 -> shared-memory traffic of one tile per CTA, which bounded the one-tile kernel).  The
+// output accumulates in tensor memory: O_t += P_t V_j.  The running maximum a row's exponentials are taken against is
+// only moved when the true maximum has grown past it by more than 8 (a factor 256, harmless in fp32 / bf16); then the
+// row's softmax threads rescale their columns of O_t in tensor memory before they publish P_t, so the common step has no
+// correction pass at all.  While one tile's softmax runs, the tensor core works on the other tile.
+//   warp 0       TMA: Q (both tiles) once, then K / V tiles through rings
+//   warp 1       MMA: S_t = Q_t K_j^T; O_t += P_t V_j
+//   warps 2-17   softmax: tile t = (w - 2) / 8; thread = query row x 64 of the 128 keys
+// P_TMEM: the probabilities go back into the first 64 columns of S_t (bf16 pairs) and the second product reads its A
+// operand from tensor memory; otherwise they go through shared memory.
+template <int D, bool P_TMEM>
+struct Fwd2Cfg {
+  static constexpr int PANELS = D / 64;
+  static constexpr int QT_BYTES = 128 * D * 2;
+  static constexpr int KV_BYTES = BKF * D * 2;
+  static constexpr int P_BYTES = 128 * BKF * 2;
+  static constexpr int NK = P_TMEM ? 3 : 2;
+  static constexpr int NV = P_TMEM ? 2 : 1;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * QT_BYTES;
+  static constexpr int OFF_V = OFF_K + NK * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + NV * KV_BYTES;
+  static constexpr int OFF_XCHG = OFF_P + (P_TMEM ? 0 : 2 * P_BYTES);   // [2 tiles][2 halves][128 rows] floats
+  static constexpr int OFF_BAR = OFF_XCHG + 2 * 2 * 128 * 4;
+  static constexpr int SLACK = 512;                                     // room to align the base (checked in the kernel)
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + SLACK;
+  static constexpr int TMEM_S = 0;      // S_t at t * 128
+  static constexpr int TMEM_O = 256;    // O_t at 256 + t * D
+  static constexpr uint32_t IDESC_S = attn_idesc(128, BKF, 0, 0);
+  static constexpr uint32_t IDESC_PV = attn_idesc(128, D, 0, 1);
+  static_assert(SMEM_BYTES <= 232448, "forward tiles exceed the shared memory of one CTA");
+};
+
+constexpr int FWD2_THREADS = 576;
+constexpr float RESCALE_GAP = 8.f;      // log2 units the true row maximum may exceed the one in use
+
+template <int D, bool P_TMEM>
+__global__ void __launch_bounds__(FWD2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs p) {
+  using C = Fwd2Cfg<D, P_TMEM>;
+  constexpr int DH = D / 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float *xchg = (float *)(smem + C::OFF_XCHG);
+  uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
+  uint64_t *q_full = bars;
+  uint64_t *k_full = bars + 1;        // [NK]
+  uint64_t *k_empty = bars + 4;       // [NK] commit
+  uint64_t *v_full = bars + 7;        // [NV]
+  uint64_t *v_empty = bars + 9;       // [NV] commit
+  uint64_t *s_full = bars + 11;       // [2] commit
+  uint64_t *p_full = bars + 13;       // [2] 8 warps
+  uint64_t *pv_done = bars + 15;      // [2] commit
+  uint32_t *tmem_slot = (uint32_t *)(bars + 17);
+  volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  if ((uintptr_t)(smem - smem_raw) > (uintptr_t)C::SLACK) {
+    if (threadIdx.x == 0 && p.err) atomicCAS(p.err, 0, (int)FFK_ERR_BAD_ARG);
+    return;
+  }
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.Sq + 255) / 256;
+  const int qb = blockIdx.x % nqb;
+  const int bh = blockIdx.x / nqb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int q0 = qb * 256;
+  // key tiles each query tile needs: all of them, or under the causal mask those with a key <= the tile's last query
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int first = q0 + t * 128;
+    int n = first < p.Sq ? (p.Sk + BKF - 1) / BKF : 0;
+    if (p.causal && n > 0) n = min(n, (min(first + 128, p.Sq) - 1) / BKF + 1);
+    n_t[t] = n;
+  }
+  const int n_tiles = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&pv_done[t], 1); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * C::QT_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int c = 0; c < C::PANELS; ++c)
+          tma_load_4d(smem_u32(smem + C::OFF_Q + t * C::QT_BYTES + c * 128 * 128), &tmQ, q_full, c * 64, q0 + t * 128, h, b);
+      int kj = 0, vj = 0;
+      uint64_t t0 = ffk_globaltimer();
+      uint32_t spins = 0;
+      while (kj < n_tiles || vj < n_tiles) {
+        bool progress = false;
+        if (kj < n_tiles) {
+          const int s = kj % C::NK;
+          if (mbar_try_wait(&k_empty[s], ((uint32_t)(kj / C::NK) & 1u) ^ 1u)) {
+            mbar_expect_tx(&k_full[s], C::KV_BYTES);
+#pragma unroll
+            for (int c = 0; c < C::PANELS; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_K + s * C::KV_BYTES + c * BKF * 128), &tmK, &k_full[s], c * 64, kj * BKF, h, b);
+            ++kj;
+            progress = true;
+          }
+        }
+        if (vj < n_tiles) {
+          const int s = vj % C::NV;
+          if (mbar_try_wait(&v_empty[s], ((uint32_t)(vj / C::NV) & 1u) ^ 1u)) {
+            mbar_expect_tx(&v_full[s], C::KV_BYTES);
+#pragma unroll
+            for (int c = 0; c < C::PANELS; ++c)
+              tma_load_4d(smem_u32(smem + C::OFF_V + s * C::KV_BYTES + c * BKF * 128), &tmV, &v_full[s], c * 64, vj * BKF, h, b);
+            ++vj;
+            progress = true;
+          }
+        }
+        if (progress) {
+          t0 = ffk_globaltimer();
+        } else if ((++spins & 63u) == 0) {
+          if (*abort_flag) break;
+          if (ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (p.err) atomicCAS(p.err, 0, (int)FFK_ERR_TIMEOUT_PRODUCER);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+      const uint64_t dq0 = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(smem + C::OFF_V), BKF * 128, 1024);
+      const uint64_t dp0 = make_smem_desc(smem_u32(smem + C::OFF_P), 16, 1024);
+      auto issue_s = [&](int t, int j) {        // S_t = Q_t K_j^T (the caller has waited for K_j)
+        const uint64_t dq = desc_advance(dq0, (uint32_t)(t * C::QT_BYTES));
+        const uint64_t dk = desc_advance(dk0, (uint32_t)((j % C::NK) * C::KV_BYTES));
+        const uint32_t d = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
+        tc_mma_bf16<false>(d, dq, dk, C::IDESC_S);
+#pragma unroll
+        for (int ks = 1; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)((ks >> 2) * (128 * 128) + (ks & 3) * 32);
+          tc_mma_bf16<true>(d, desc_advance(dq, off), desc_advance(dk, off), C::IDESC_S);
+        }
+        tc_commit(&s_full[t]);
+      };
+      if (ok && n_tiles > 0) {
+        ok = mbar_wait(&k_full[0], 0, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (ok) {
+          tc_fence_after();
+          for (int t = 0; t < 2; ++t)
+            if (n_t[t] > 0) issue_s(t, 0);
+          tc_commit(&k_empty[0]);
+        }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        const int vs = j % C::NV;
+        ok = mbar_wait(&v_full[vs], (uint32_t)(j / C::NV) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        if (!ok) break;
+        const uint64_t dv = desc_advance(dv0, (uint32_t)(vs * C::KV_BYTES));
+        bool k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < n_t[t]) {
+            ok = mbar_wait(&p_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d = tmem_base + (uint32_t)(C::TMEM_O + t * D);
+            if constexpr (P_TMEM) {
+              const uint32_t a = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
+              if (j == 0) tc_mma_ts_bf16<false>(d, a, dv, C::IDESC_PV);
+              else tc_mma_ts_bf16<true>(d, a, dv, C::IDESC_PV);
+#pragma unroll
+              for (int ks = 1; ks < BKF / 16; ++ks) tc_mma_ts_bf16<true>(d, a + (uint32_t)(ks * 8), desc_advance(dv, (uint32_t)(ks * 2048)), C::IDESC_PV);
+            } else {
+              const uint64_t dp = desc_advance(dp0, (uint32_t)(t * C::P_BYTES));
+              if (j == 0) tc_mma_bf16<false>(d, dp, dv, C::IDESC_PV);
+              else tc_mma_bf16<true>(d, dp, dv, C::IDESC_PV);
+#pragma unroll
+              for (int ks = 1; ks < BKF / 16; ++ks) {
+                const uint32_t a_off = (uint32_t)((ks >> 2) * (128 * 128) + (ks & 3) * 32);
+                tc_mma_bf16<true>(d, desc_advance(dp, a_off), desc_advance(dv, (uint32_t)(ks * 2048)), C::IDESC_PV);
+              }
+            }
+            tc_commit(&pv_done[t]);
+          }
+          if (j + 1 < n_t[t]) {
+            if (!k_ready) {
+              ok = mbar_wait(&k_full[(j + 1) % C::NK], (uint32_t)((j + 1) / C::NK) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+              if (!ok) break;
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[vs]);
+        if (j + 1 < n_tiles) tc_commit(&k_empty[(j + 1) % C::NK]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: tile t, thread = query row x 64 keys
+    const int t = (warp - 2) >> 3;
+    const int quarter = warp & 3;
+    const int half = ((warp - 2) >> 2) & 1;
+    const int r = quarter * 32 + lane;
+    const int q = q0 + t * 128 + r;
+    const int n_mine = n_t[t];
+    const float sl2 = p.scale * LOG2E;
+    const bool drop = p.drop_p > 0.f;
+    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const unsigned long long seed = drop ? attn_seed(p) : 0ull;
+    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
+    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t t_s = lane_base + (uint32_t)(C::TMEM_S + t * 128);
+    const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
+    const uint32_t prow = smem_u32(smem + C::OFF_P + t * C::P_BYTES + half * (128 * 128) + r * 128);
+    float *my_x = xchg + (t * 2 + half) * 128 + r, *other_x = xchg + (t * 2 + (half ^ 1)) * 128 + r;
+    const int pair_bar = 1 + t * 4 + quarter;     // named barrier of the two warps that share these 32 rows
+    float m_ref = 0.f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine && ok; ++j) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      ok = mbar_wait(&s_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t rs[64];
+      tmem_ld32(t_s + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+      tmem_ld32(t_s + (uint32_t)(half * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
+      tmem_ld_wait();
+      const int k0 = j * BKF + half * 64;
+      int kmax = p.Sk - k0;
+      if (p.causal) kmax = min(kmax, q - k0 + 1);
+      const bool full = kmax >= 64;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (full) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(rs[i])); mx1 = fmaxf(mx1, __uint_as_float(rs[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(rs[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(rs[i + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx0 = fmaxf(mx0, i < kmax ? __uint_as_float(rs[i]) : -INFINITY);
+      }
+      *my_x = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // both halves hold their scores in registers from here on
+      const float m_row = fmaxf(*my_x, *other_x) * sl2;
+      bool need = false;
+      if (j == 0) m_ref = m_row == -INFINITY ? 0.f : m_row;
+      else need = m_row > m_ref + RESCALE_GAP;
+      const bool any = __any_sync(0xffffffffu, need);
+      bool waited = false;
+      if (any) {
+        // O_t (complete up to tile j - 1) and the row sum move to the new reference maximum
+        ok = mbar_wait(&pv_done[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        waited = true;
+        tc_fence_after();
+        const float alpha = need ? exp2f(m_ref - m_row) : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t ro[32];
+          tmem_ld32(t_o + (uint32_t)(c * 32), ro);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+          tmem_st32(t_o + (uint32_t)(c * 32), ro);
+        }
+        tmem_st_wait();
+        l *= alpha;
+        if (need) m_ref = m_row;
+      }
+      float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        float e0 = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -m_ref)), e1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_ref));
+        float e2 = exp2f(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_ref)), e3 = exp2f(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_ref));
+        if (!full) {
+          if (i >= kmax) e0 = 0.f;
+          if (i + 1 >= kmax) e1 = 0.f;
+          if (i + 2 >= kmax) e2 = 0.f;
+          if (i + 3 >= kmax) e3 = 0.f;
+        }
+        ls0 += e0; ls1 += e1; ls2 += e2; ls3 += e3;
+        if (drop) {
+          const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
+          if ((uint32_t)(z & 0xFFFFu) < thr) e0 = 0.f;
+          if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) e1 = 0.f;
+          if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) e2 = 0.f;
+          if ((uint32_t)(z >> 48) < thr) e3 = 0.f;
+        }
+        rs[i >> 1] = pack_bf162(e0, e1);          // packed in place (registers i / 2, i / 2 + 1 are already consumed)
+        rs[(i >> 1) + 1] = pack_bf162(e2, e3);
+      }
+      l += (ls0 + ls1) + (ls2 + ls3);
+      if constexpr (P_TMEM) {
+        // 64 probabilities = 32 columns of bf16 pairs at the start of S_t (this half's own scores or the other half's,
+        // all of which are in registers since the barrier above)
+        tmem_st32(t_s + (uint32_t)(half * 32), *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        if (j > 0 && !waited) {   // the previous product has finished reading this tile's P buffer
+          ok = mbar_wait(&pv_done[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)((u ^ (r & 7)) << 4)), "r"(rs[4 * u]), "r"(rs[4 * u + 1]),
+                       "r"(rs[4 * u + 2]), "r"(rs[4 * u + 3])
+                       : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();   // orders the tensor-memory traffic of a rescale before the arrival
+      }
+      warp_arrive(&p_full[t], lane);
+    }
+    if (ok && n_mine > 0) {
+      ok = mbar_wait(&pv_done[t], (uint32_t)(n_mine - 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && n_mine > 0) {
+      tc_fence_after();
+      *my_x = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      const float lt = l + *other_x;
+      const float inv_keep = drop ? 1.f / (1.f - p.drop_p) : 1.f;
+      const float f = lt > 0.f ? inv_keep / lt : 0.f;
+      if (q < p.Sq && half == 0 && p.lse) p.lse[((long long)(b * p.H + h)) * p.Sq + q] = lt > 0.f ? m_ref + log2f(lt) : INFINITY;
+      bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D + half * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t ro[32];
+        tmem_ld32(t_o + (uint32_t)(c * 32), ro);
+        tmem_ld_wait();
+        if (q < p.Sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 v = make_uint4(pack_bf162(__uint_as_float(ro[8 * u]) * f, __uint_as_float(ro[8 * u + 1]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 2]) * f, __uint_as_float(ro[8 * u + 3]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 4]) * f, __uint_as_float(ro[8 * u + 5]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 6]) * f, __uint_as_float(ro[8 * u + 7]) * f));
+            *reinterpret_cast<uint4 *>(orow + c * 32 + 8 * u) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // ================================================================================================ backward
 // delta[b, h, q] = sum_c dO[b, q, h, c] * O[b, q, h, c]; one warp per (row, head)
 template <int D>
@@ -912,6 +1293,31 @@ __device__ int g_attn_err = 0;
 
 bool aligned16(const void *p, long long ld) { return (((uintptr_t)p) & 15) == 0 && (ld * 2) % 16 == 0; }
 
+template <int D, bool P_TMEM>
+int launch_fwd2(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnArgs &a, long long grid, cudaStream_t stream) {
+  using C = Fwd2Cfg<D, P_TMEM>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<D, P_TMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  attn_fwd2_kernel<D, P_TMEM><<<(unsigned)grid, FWD2_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, a);
+  return (int)cudaGetLastError();
+}
+
+// forward kernel in use: 1 = one query tile per CTA, 2 = two tiles per CTA with P through shared memory, 3 = two tiles with
+// P through tensor memory (FFK_ATTN_FWD overrides the default)
+int fwd_variant() {
+  static int v = 0;
+  if (!v) {
+    const char *e = getenv("FFK_ATTN_FWD");
+    v = e ? atoi(e) : 1;
+    if (v < 1 || v > 3) v = 1;
+  }
+  return v;
+}
+
 }  // namespace
 
 // One attention call.  Plain C struct so ctypes can fill it.
@@ -958,6 +1364,13 @@ FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
   { const char *e = getenv("FFK_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
+  const int variant = fwd_variant();
+  if (variant >= 2) {
+    const long long grid2 = (long long)((d->Sq + 255) / 256) * d->H * d->B;
+    if (grid2 > 0x7fffffffll) return -2;
+    if (d->D == 128) return variant == 3 ? launch_fwd2<128, true>(tq, tk, tv, a, grid2, stream) : launch_fwd2<128, false>(tq, tk, tv, a, grid2, stream);
+    return variant == 3 ? launch_fwd2<64, true>(tq, tk, tv, a, grid2, stream) : launch_fwd2<64, false>(tq, tk, tv, a, grid2, stream);
+  }
   const long long grid = (long long)((d->Sq + BQ - 1) / BQ) * d->H * d->B;
   if (grid > 0x7fffffffll) return -2;
   if (d->D == 128) {

@@ -330,3 +330,19 @@ def test_cost_table_file_feeds_the_search_estimator(tmp_path):
     assert strategy is not None and "candidates" in stats
     # no table and no measurement asked for: the search builds its own analytic estimator
     assert _search_estimator("mlp", None, cg, 2, FFConfig(), None, ExecConfig()) == (None, None)
+
+
+def test_strided_machine_views_interleave_inside_a_node():
+    """With strided=True the tasks may sit on every s-th device (the reference's MachineView stride); the contiguous views
+    come first and are all the mapping search asks for on a uniform NVSwitch node."""
+    ms = c.MachineSpecification(1, 8)
+    views = c.allowed_machine_views([4], 0, 8, ms, strided=True)
+    devs = [c.view_devices(v, [4], ms) for v in views]
+    assert devs == [[0, 1, 2, 3], [4, 5, 6, 7], [0, 2, 4, 6], [1, 3, 5, 7]]
+    assert [v["dimensions"][0]["stride"] for v in views] == [1, 1, 2, 2]
+    two = [c.view_devices(v, [2, 2], ms) for v in c.allowed_machine_views([2, 2], 0, 8, ms, strided=True)]
+    assert [0, 1, 2, 3] in two and [0, 2, 4, 6] in two and [1, 3, 5, 7] in two
+    for d in two:
+        assert len(set(d)) == 4 and all(0 <= x < 8 for x in d)
+    # a strided view round-trips through the strategy file format like any other
+    assert c.allowed_machine_views([4], 0, 8, ms) == views[:2]
