@@ -75,6 +75,14 @@ __host__ __device__ constexpr uint32_t attn_idesc(int M, int N, int a_mn, int b_
          ((uint32_t)(M >> 4) << 24);
 }
 
+// 2^x on the special-function unit, one instruction (exp2f() adds range handling for results below the normal range,
+// which a probability does not need: those flush to zero)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
@@ -362,13 +370,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float other = xchg[(t * 2 + (half ^ 1)) * 128 + r];
       float m_new = fmaxf(m, fmaxf(mine, other) * sl2);
       if (m_new == -INFINITY) m_new = 0.f;        // nothing visible yet (padding rows only)
-      const float alpha = exp2f(m - m_new);
+      const float alpha = fast_exp2(m - m_new);
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
       if (!(p.dbg & 1))
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
-        float e0 = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
-        float e2 = exp2f(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = exp2f(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
+        float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
+        float e2 = fast_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = fast_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
         if (!full) {
           if (i >= kmax) e0 = 0.f;
           if (i + 1 >= kmax) e1 = 0.f;
@@ -716,7 +724,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!ok) break;
         waited = true;
         tc_fence_after();
-        const float alpha = need ? exp2f(m_ref - m_row) : 1.f;
+        const float alpha = need ? fast_exp2(m_ref - m_row) : 1.f;
 #pragma unroll 1
         for (int c = 0; c < DH / 32; ++c) {
           uint32_t ro[32];
@@ -733,8 +741,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
-        float e0 = exp2f(fmaf(__uint_as_float(rs[i]), sl2, -m_ref)), e1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_ref));
-        float e2 = exp2f(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_ref)), e3 = exp2f(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_ref));
+        float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_ref));
+        float e2 = fast_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_ref));
         if (!full) {
           if (i >= kmax) e0 = 0.f;
           if (i + 1 >= kmax) e1 = 0.f;
@@ -1115,6 +1123,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
       int kmax = p.Sk - kbase;
       if (p.causal) kmax = min(kmax, q - kbase + 1);
+      const bool full = kmax >= 64;     // every key of this half exists and is visible to this row
       ok = mbar_wait(s_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
            mbar_wait(p_empty, ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
@@ -1137,8 +1146,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           float e[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            e[u] = exp2f(fmaf(__uint_as_float(rs[i + u]), sl2, -lse));
-            if (c * 32 + i + u >= kmax) e[u] = 0.f;
+            e[u] = fast_exp2(fmaf(__uint_as_float(rs[i + u]), sl2, -lse));
+            if (!full && c * 32 + i + u >= kmax) e[u] = 0.f;
           }
           pe[c * 16 + (i >> 1)] = pack_bf162(e[0], e[1]);
           pe[c * 16 + (i >> 1) + 1] = pack_bf162(e[2], e[3]);
@@ -1180,12 +1189,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float2 e = unpack_bf162(pe[c * 16 + (i >> 1)]);
-          float g0 = __uint_as_float(rd[i]) * inv_keep, g1 = __uint_as_float(rd[i + 1]) * inv_keep;
+          float g0 = fmaf(__uint_as_float(rd[i]), inv_keep, -dlt), g1 = fmaf(__uint_as_float(rd[i + 1]), inv_keep, -dlt);
           if (drop) {
-            if ((dropped[c] >> i) & 1u) g0 = 0.f;
-            if ((dropped[c] >> (i + 1)) & 1u) g1 = 0.f;
+            if ((dropped[c] >> i) & 1u) g0 = -dlt;
+            if ((dropped[c] >> (i + 1)) & 1u) g1 = -dlt;
           }
-          gk[i >> 1] = pack_bf162(e.x * (g0 - dlt), e.y * (g1 - dlt));
+          gk[i >> 1] = pack_bf162(e.x * g0, e.y * g1);
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -1307,15 +1316,17 @@ int launch_fwd2(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap 
 }
 
 // forward kernel in use: 1 = one query tile per CTA, 2 = two tiles per CTA with P through shared memory, 3 = two tiles with
-// P through tensor memory (FFK_ATTN_FWD overrides the default)
+// P through tensor memory.  All three give the same results; on B200 they also take the same time (the softmax warps, not
+// the tensor core or the K / V traffic, bound them), so 1 stays the default.  FFK_ATTN_FWD or ffk_attention_set_fwd_variant
+// choose another.
+int g_fwd_variant = 0;
 int fwd_variant() {
-  static int v = 0;
-  if (!v) {
+  if (!g_fwd_variant) {
     const char *e = getenv("FFK_ATTN_FWD");
-    v = e ? atoi(e) : 1;
-    if (v < 1 || v > 3) v = 1;
+    g_fwd_variant = e ? atoi(e) : 1;
+    if (g_fwd_variant < 1 || g_fwd_variant > 3) g_fwd_variant = 1;
   }
-  return v;
+  return g_fwd_variant;
 }
 
 }  // namespace
@@ -1343,6 +1354,7 @@ struct FfkAttnDesc {
 };
 
 // 1 when the fused kernels cover this head dimension / direction
+FFK_API void ffk_attention_set_fwd_variant(int v) { g_fwd_variant = (v >= 1 && v <= 3) ? v : 1; }
 FFK_API int ffk_attention_supported(int D, int backward) { return backward ? (D == 128) : (D == 64 || D == 128); }
 FFK_API long long ffk_attention_bwd_scratch_floats(int B, int H, int Sq, int D) { return 1ll * B * H * Sq * D; }
 

@@ -323,6 +323,37 @@ __global__ void push_rows_kernel(const uint4 *__restrict__ src, PeerPtrs dst, lo
   }
 }
 
+// ---------------------------------------------------------------- reduce-scatter, sending half
+// src holds `world` consecutive pieces of nvec vectors; piece p goes into slot `rank` of peer p's staging buffer
+// [world][nvec] (the layout reduce_partials_kernel sums), then flag[flag_base + rank] is raised on every peer.
+__global__ void scatter_pieces_kernel(const uint4 *__restrict__ src, PeerPtrs dst, long long nvec, PeerPtrs flags, int flag_base, int rank, int world,
+                                      unsigned long long *epoch_ctr, unsigned int *blocks_done) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k < world) {
+        const int peer = (rank + k) % world;
+        ((uint4 *)dst.p[peer])[(long long)rank * nvec + i] = src[(long long)peer * nvec + i];
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) last = (atomicAdd(blocks_done, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) {
+    unsigned long long epoch = *epoch_ctr + 1;
+    if ((int)threadIdx.x < world) st_release_sys((unsigned long long *)flags.p[threadIdx.x] + flag_base + rank, epoch);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *epoch_ctr = epoch;
+      *blocks_done = 0;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- reduce staged partials (F1 consumer side)
 // stage holds `nsrc` partial copies [nsrc][n] written by the peers' GEMM epilogues; out = sum (+ residual).
 // Waits for flag[flag_base + s] >= *epoch_ctr + 1 for every source first.
@@ -413,6 +444,70 @@ __global__ void alltoall_embedding_bwd_kernel(float *const *__restrict__ tables,
   }
 }
 
+// The same two kernels for dim % 4 == 0 (every table and staging row then starts on a 16-byte boundary): one thread
+// moves four consecutive elements of a row -- one 16-byte table read, one 8- or 16-byte remote store; backward adds with
+// one 16-byte vector atomic -- and the flat index is split with 32-bit arithmetic (the launcher checks that it fits).
+template <typename T>
+__device__ __forceinline__ void st4(T *dst, float4 v);
+template <>
+__device__ __forceinline__ void st4<float>(float *dst, float4 v) { *reinterpret_cast<float4 *>(dst) = v; }
+template <>
+__device__ __forceinline__ void st4<bf16>(bf16 *dst, float4 v) { *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_bf162(v.x, v.y), pack_bf162(v.z, v.w)); }
+template <typename T>
+__device__ __forceinline__ float4 ld4(const T *src);
+template <>
+__device__ __forceinline__ float4 ld4<float>(const float *src) { return *reinterpret_cast<const float4 *>(src); }
+template <>
+__device__ __forceinline__ float4 ld4<bf16>(const bf16 *src) {
+  const uint2 u = *reinterpret_cast<const uint2 *>(src);
+  const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T, typename I>
+__global__ void alltoall_embedding_fwd_vec_kernel(const float *const *__restrict__ tables, const long long *__restrict__ entries,
+                                                  const I *__restrict__ idx, PeerPtrs out, int global_batch, int local_batch, int num_tables, int dim,
+                                                  int rank, int world, unsigned total_vec) {
+  const unsigned dv = (unsigned)dim >> 2;
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += stride) {
+    const unsigned c4 = i % dv;
+    const unsigned rest = i / dv;
+    const unsigned b = rest % (unsigned)global_batch;
+    const unsigned lt = rest / (unsigned)global_batch;
+    const int t = (int)lt * world + rank;
+    const long long e = (long long)idx[(long long)b * num_tables + t];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e >= 0 && e < entries[lt]) v = *reinterpret_cast<const float4 *>(tables[lt] + e * dim + c4 * 4);
+    const unsigned owner = b / (unsigned)local_batch;
+    st4<T>((T *)out.p[owner] + ((long long)(b - owner * (unsigned)local_batch) * num_tables + t) * dim + c4 * 4, v);
+  }
+}
+template <typename T, typename I>
+__global__ void alltoall_embedding_bwd_vec_kernel(float *const *__restrict__ tables, float *const *__restrict__ dgrad, const long long *__restrict__ entries,
+                                                  const I *__restrict__ idx, PeerPtrs dout, int global_batch, int local_batch, int num_tables,
+                                                  int dim, int rank, int world, float lr, unsigned total_vec) {
+  const unsigned dv = (unsigned)dim >> 2;
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += stride) {
+    const unsigned c4 = i % dv;
+    const unsigned rest = i / dv;
+    const unsigned b = rest % (unsigned)global_batch;
+    const unsigned lt = rest / (unsigned)global_batch;
+    const int t = (int)lt * world + rank;
+    const long long e = (long long)idx[(long long)b * num_tables + t];
+    if (e < 0 || e >= entries[lt]) continue;
+    const unsigned owner = b / (unsigned)local_batch;
+    float4 g = ld4<T>((const T *)dout.p[owner] + ((long long)(b - owner * (unsigned)local_batch) * num_tables + t) * dim + c4 * 4);
+    if (dgrad) {
+      atomicAdd(reinterpret_cast<float4 *>(dgrad[lt] + e * dim + c4 * 4), g);
+    } else {
+      g.x *= -lr; g.y *= -lr; g.z *= -lr; g.w *= -lr;
+      atomicAdd(reinterpret_cast<float4 *>(tables[lt] + e * dim + c4 * 4), g);
+    }
+  }
+}
+
 PeerPtrs make_ptrs(void *const *p, int world) {
   PeerPtrs r;
   for (int i = 0; i < MAX_RANKS; ++i) r.p[i] = i < world ? p[i] : nullptr;
@@ -485,6 +580,17 @@ FFK_API int ffk_push_rows(const void *src, void *const *dst_peers, long long dst
   return (int)cudaGetLastError();
 }
 
+// Piece p (piece_bytes each) of src goes into slot `rank` of peer p's staging buffer; then this rank's flag is raised on
+// every peer.  Together with ffk_reduce_partials on the receiving side this is a reduce-scatter over peer memory.
+FFK_API int ffk_scatter_pieces(const void *src, void *const *dst_peers, long long piece_bytes, void *const *flag_peers, int flag_base, int rank,
+                               int world, void *sync_words, int blocks, cudaStream_t st) {
+  if (world > MAX_RANKS || (piece_bytes & 15) || (((uintptr_t)src) & 15)) return -2;
+  if (blocks <= 0) blocks = 32;
+  scatter_pieces_kernel<<<blocks, 512, 0, st>>>((const uint4 *)src, make_ptrs(dst_peers, world), piece_bytes / 16, make_ptrs(flag_peers, world),
+                                                flag_base, rank, world, (unsigned long long *)sync_words, (unsigned int *)sync_words + 3);
+  return (int)cudaGetLastError();
+}
+
 // out[n] = sum_{s<nsrc} stage[s][n] (+ residual); waits for the nsrc source flags of the next epoch first.
 FFK_API int ffk_reduce_partials(const void *stage, const void *residual, void *out, long long n, int nsrc, const void *flags_local, int flag_base,
                                 void *sync_words, int *status, int dt, int blocks, cudaStream_t st) {
@@ -510,8 +616,21 @@ FFK_API int ffk_alltoall_embedding_fwd(const void *tables, const void *entries, 
   int tl = (num_tables - rank + world - 1) / world;
   long long total = (long long)tl * global_batch * dim;
   if (total <= 0) return 0;
-  int grid = ffk_blocks(total, 256);
   PeerPtrs o = make_ptrs(out_peers, world);
+  if (dim % 4 == 0 && total / 4 < 0x7fffffffll) {
+    // rows start on 16-byte boundaries (tables and staging buffers come from cudaMalloc / the symmetric allocator)
+    const unsigned tv = (unsigned)(total / 4);
+    const int gridv = ffk_blocks(tv, 256);
+#define A2A_FWDV(T, I) alltoall_embedding_fwd_vec_kernel<T, I><<<gridv, 256, 0, st>>>((const float *const *)tables, (const long long *)entries, (const I *)idx, o, global_batch, local_batch, num_tables, dim, rank, world, tv)
+    if (out_dt == 1 && idx_dt == 3) A2A_FWDV(bf16, long long);
+    else if (out_dt == 1 && idx_dt == 2) A2A_FWDV(bf16, int);
+    else if (out_dt == 0 && idx_dt == 3) A2A_FWDV(float, long long);
+    else if (out_dt == 0 && idx_dt == 2) A2A_FWDV(float, int);
+    else return -2;
+#undef A2A_FWDV
+    return (int)cudaGetLastError();
+  }
+  int grid = ffk_blocks(total, 256);
 #define A2A_FWD(T, I) alltoall_embedding_fwd_kernel<float, T, I><<<grid, 256, 0, st>>>((const float *const *)tables, (const long long *)entries, (const I *)idx, o, global_batch, local_batch, num_tables, dim, rank, world)
   if (out_dt == 1 && idx_dt == 3) A2A_FWD(bf16, long long);
   else if (out_dt == 1 && idx_dt == 2) A2A_FWD(bf16, int);
@@ -528,8 +647,20 @@ FFK_API int ffk_alltoall_embedding_bwd(const void *tables, const void *dgrad, co
   int tl = (num_tables - rank + world - 1) / world;
   long long total = (long long)tl * global_batch * dim;
   if (total <= 0) return 0;
-  int grid = ffk_blocks(total, 256);
   PeerPtrs o = make_ptrs(dout_peers, world);
+  if (dim % 4 == 0 && total / 4 < 0x7fffffffll) {
+    const unsigned tv = (unsigned)(total / 4);
+    const int gridv = ffk_blocks(tv, 256);
+#define A2A_BWDV(T, I) alltoall_embedding_bwd_vec_kernel<T, I><<<gridv, 256, 0, st>>>((float *const *)tables, (float *const *)dgrad, (const long long *)entries, (const I *)idx, o, global_batch, local_batch, num_tables, dim, rank, world, lr, tv)
+    if (out_dt == 1 && idx_dt == 3) A2A_BWDV(bf16, long long);
+    else if (out_dt == 1 && idx_dt == 2) A2A_BWDV(bf16, int);
+    else if (out_dt == 0 && idx_dt == 3) A2A_BWDV(float, long long);
+    else if (out_dt == 0 && idx_dt == 2) A2A_BWDV(float, int);
+    else return -2;
+#undef A2A_BWDV
+    return (int)cudaGetLastError();
+  }
+  int grid = ffk_blocks(total, 256);
 #define A2A_BWD(T, I) alltoall_embedding_bwd_kernel<T, I><<<grid, 256, 0, st>>>((float *const *)tables, (float *const *)dgrad, (const long long *)entries, (const I *)idx, o, global_batch, local_batch, num_tables, dim, rank, world, lr)
   if (out_dt == 1 && idx_dt == 3) A2A_BWD(bf16, long long);
   else if (out_dt == 1 && idx_dt == 2) A2A_BWD(bf16, int);

@@ -290,6 +290,12 @@ def attention_bwd_scratch_floats(B, H, Sq, D) -> int:
     return int(lib().ffk_attention_bwd_scratch_floats(B, H, Sq, D))
 
 
+def attention_set_forward_variant(v: int):
+    """Which forward kernel `attention_fwd` launches: 1 = one 128-query tile per CTA (default), 2 / 3 = two tiles per CTA
+    sharing the K / V tiles, probabilities passed to the second product through shared (2) or tensor (3) memory."""
+    lib().ffk_attention_set_fwd_variant(int(v))
+
+
 def attention_last_error() -> int:
     return lib().ffk_attention_last_error()
 

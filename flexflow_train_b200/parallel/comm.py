@@ -27,6 +27,7 @@ def _lib():
             "ffk_grad_allreduce_scale": [PP, PP, I, L, L, F, I, I, P, P, I, I, P],
             "ffk_grad_allreduce_update": [PP, PP, P, P, P, PP, I, L, L, F, I, I, P, P, I, F, P, F, F, F, F, F, I, I, P],
             "ffk_push_rows": [P, PP, L, L, PP, I, I, I, P, I, I, P],
+            "ffk_scatter_pieces": [P, PP, L, PP, I, I, I, P, I, P],
             "ffk_reduce_partials": [P, P, P, L, I, P, I, P, P, I, I, P],
             "ffk_alltoall_embedding_fwd": [P, P, P, PP, I, I, I, I, I, I, I, I, P],
             "ffk_alltoall_embedding_bwd": [P, P, P, P, PP, I, I, I, I, I, I, F, I, I, P],
@@ -83,6 +84,14 @@ def push_rows(ctx: DistContext, src: torch.Tensor, dst: SymmetricBuffer, dst_byt
     nb = src.numel() * src.element_size() if nbytes is None else nbytes
     _chk(_lib().ffk_push_rows(src.data_ptr(), dst.ptr_array, dst_byte_offset, nb, ctx.flags.ptr_array, flag_base, ctx.rank,
                               ctx.world_size, sync.data_ptr(), int(skip_self), blocks, _stream()), "ffk_push_rows")
+
+
+def scatter_pieces(ctx: DistContext, src: torch.Tensor, dst: SymmetricBuffer, piece_bytes: int, flag_base: int, sync: torch.Tensor,
+                   blocks: int = 32):
+    """Piece p of `src` (world pieces of piece_bytes) goes into slot `rank` of peer p's `dst` ([world][piece]); then
+    flag[flag_base + rank] is raised on every peer."""
+    _chk(_lib().ffk_scatter_pieces(src.data_ptr(), dst.ptr_array, piece_bytes, ctx.flags.ptr_array, flag_base, ctx.rank, ctx.world_size,
+                                   sync.data_ptr(), blocks, _stream()), "ffk_scatter_pieces")
 
 
 def signal(ctx: DistContext, dst: SymmetricBuffer, flag_base: int, sync: torch.Tensor):

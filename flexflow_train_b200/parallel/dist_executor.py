@@ -32,7 +32,7 @@ from ..runtime import executor as E
 from ..runtime.executor import ExecConfig, Executable, OpImpl, Value, register
 from . import comm
 from .context import DistContext
-from .fused_ops import AllGatherGemm, AllToAllEmbedding, GemmReduceScatter, GradAllReduce
+from .fused_ops import PeerAllGather, PeerReduceScatter, AllGatherGemm, AllToAllEmbedding, GemmReduceScatter, GradAllReduce
 
 PARALLEL = ("REPARTITION", "COMBINE", "REPLICATE", "REDUCTION")
 
@@ -58,15 +58,72 @@ class _ParallelOp(OpImpl):
         """Does this operator call NCCL in forward or backward?"""
         if self.is_alias() or self.absorbed or isinstance(self, E.SkippedOp):
             return False
-        if self.type == "REPARTITION" and self.pair is None:
-            return self.buf("INPUT").requires_grad  # forward is a local slice; backward all-gathers
         if self.type in ("REPLICATE", "REDUCTION") and self.pair is None and self.ex.peer_allreduce:
             return False  # summed in place by the peer-memory all-reduce kernel
+        if self.type == "REPARTITION":
+            if self.pair is None:  # forward is a local slice; backward all-gathers
+                return self.buf("INPUT").requires_grad and self.peer_ag is None
+            return self.peer_rs is None or (self.pair.buf("INPUT").requires_grad and self.peer_ag is None)
+        if self.type == "COMBINE":
+            return self.peer_ag is None
+        if self.type == "REPLICATE" and self.pair is not None:
+            return self.pair.buf("INPUT").requires_grad and self.peer_rs is None
         return True
 
     def is_alias(self) -> bool:
         ex = self.ex
         return ex.dist is None or ex.dist.world_size == 1 or self.nid in getattr(ex, "weight_chain_nodes", ())
+
+    # ---- stand-alone collectives over peer memory (NCCL when the executable was built without them or the piece does not
+    # fit the kernels' 16-byte vectors).  The buffers are symmetric allocations, so they are made in setup(), where every
+    # rank passes in the same order.
+    peer_ag = None
+    peer_rs = None
+
+    def _peer_fits(self, numel: int, dtype) -> bool:
+        if not getattr(self.ex, "peer_collectives", False) or dtype not in (torch.bfloat16, torch.float32):
+            return False
+        es = 2 if dtype == torch.bfloat16 else 4
+        return numel % 8 == 0 and (numel * es) % 16 == 0
+
+    def make_peer_all_gather(self, shard: torch.Tensor):
+        if self._peer_fits(shard.numel(), shard.dtype):
+            self.peer_ag = PeerAllGather(self.gctx, shard.numel(), shard.dtype)
+
+    def make_peer_reduce_scatter(self, piece: torch.Tensor):
+        if self._peer_fits(piece.numel(), piece.dtype):
+            self.peer_rs = PeerReduceScatter(self.gctx, piece.numel(), piece.dtype)
+
+    def all_gather_dim(self, t: torch.Tensor, dim: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """All ranks' `t` concatenated along `dim` (materialised contiguously, into `out` when given)."""
+        W = self.gctx.world_size
+        if self.peer_ag is None:
+            return comm.nccl_all_gather_dim(t, dim, W, self.gctx.group, out=out)
+        parts = self.peer_ag(t.contiguous().view(-1)).view((W,) + tuple(t.shape))
+        if dim == 0:
+            res = parts.view((W * t.shape[0],) + tuple(t.shape[1:]))
+        else:
+            perm = list(range(1, dim + 1)) + [0] + list(range(dim + 1, t.dim() + 1))
+            res = K.permute(parts, perm).view(tuple(t.shape[:dim]) + (W * t.shape[dim],) + tuple(t.shape[dim + 1:]))
+        if out is not None:
+            out.copy_(res)
+            return out
+        # the staging buffer is overwritten by this operator's next call: hand out a copy unless the caller consumes it now
+        return res
+
+    def reduce_scatter(self, out_flat: torch.Tensor, full_flat: torch.Tensor, accumulate: bool = False):
+        """out (+)= this rank's piece of the sum of `full` over the group."""
+        if self.peer_rs is not None:
+            self.peer_rs(full_flat, out_flat, accumulate=accumulate)
+        elif accumulate:
+            t = torch.empty_like(out_flat)
+            dist.reduce_scatter_tensor(t, full_flat, group=self.gctx.group)
+            out_flat.add_(t)
+        else:
+            dist.reduce_scatter_tensor(out_flat, full_flat, group=self.gctx.group)
+
+    def uses_library_collectives(self, needs_gather: bool, needs_scatter: bool) -> bool:
+        return (needs_gather and self.peer_ag is None) or (needs_scatter and self.peer_rs is None)
 
     def alias_setup(self):
         self.out().data = self.x()
@@ -112,12 +169,17 @@ class RepartitionOp(_ParallelOp):
                            and len(self.ex.graph.consumers(self.inputs["INPUT"])) == 1)
         if self.direct:
             self.ex.direct_inputs[src["name"] or f"input{src['id']}"] = self
+        if not self.absorbed:
+            if self.pair is not None:
+                self.make_peer_reduce_scatter(y)
+            if self.ex.cfg.training and (self.pair.buf("INPUT") if self.pair is not None else self.buf("INPUT")).requires_grad:
+                self.make_peer_all_gather(y)
 
     def forward(self):
         if self.is_alias() or self.absorbed or getattr(self, "direct", False):
             return
         if self.pair is not None:  # Reduction -> Repartition(0): one reduce-scatter of the partial sums
-            dist.reduce_scatter_tensor(self.out().data.view(-1), self.pair.x().view(-1), group=self.gctx.group)
+            self.reduce_scatter(self.out().data.view(-1), self.pair.x().view(-1))
             return
         r = self.gctx.rank
         self.out().data.copy_(self.x().narrow(self.dim, r * self.piece, self.piece))
@@ -128,12 +190,12 @@ class RepartitionOp(_ParallelOp):
         if self.pair is not None:
             b = self.pair.buf("INPUT")
             if b.requires_grad:
-                g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), 0, self.gctx.world_size, self.gctx.group)
+                g = self.all_gather_dim(self.out().grad.view_as(self.out().data), 0)
                 self.ex.write_grad(b, g, self.pair.acc["INPUT"])
             return
         b = self.buf("INPUT")
         if b.requires_grad:
-            g = comm.nccl_all_gather_dim(self.out().grad.view_as(self.out().data), self.dim, self.gctx.world_size, self.gctx.group)
+            g = self.all_gather_dim(self.out().grad.view_as(self.out().data), self.dim)
             self.ex.write_grad(b, g, self.acc["INPUT"])
 
 
@@ -148,11 +210,12 @@ class CombineOp(_ParallelOp):
             self.out().data = self.fuse.bind_gathered(self)  # the staging buffer of the fused all-gather
             return
         self.alloc_out()
+        self.make_peer_all_gather(self.x())
 
     def forward(self):
         if self.is_alias() or self.absorbed:
             return
-        comm.nccl_all_gather_dim(self.x(), self.dim, self.gctx.world_size, self.gctx.group, out=self.out().data)
+        self.all_gather_dim(self.x(), self.dim, out=self.out().data)
 
     def backward(self):
         if self.is_alias() or self.absorbed or self.pair is not None:
@@ -171,6 +234,8 @@ class ReplicateOp(_ParallelOp):
             return self.alias_setup()
         self.check_degree()
         self.out().data = self.x()  # already present on every rank
+        if self.pair is not None and not self.absorbed and self.ex.cfg.training and self.pair.buf("INPUT").requires_grad:
+            self.make_peer_reduce_scatter(self.pair.x())
 
     def forward(self):
         pass
@@ -181,13 +246,7 @@ class ReplicateOp(_ParallelOp):
         if self.pair is not None:  # Combine(0) -> Replicate: sum over ranks and keep the own rows = reduce-scatter
             cb = self.pair.buf("INPUT")
             if cb.requires_grad:
-                full = self.out().grad.view(-1)
-                if self.pair.acc["INPUT"]:
-                    t = torch.empty(full.numel() // self.gctx.world_size, dtype=full.dtype, device=full.device)
-                    dist.reduce_scatter_tensor(t, full, group=self.gctx.group)
-                    self.ex.write_grad(cb, t, True)
-                else:
-                    dist.reduce_scatter_tensor(cb.grad.view(-1), full, group=self.gctx.group)
+                self.reduce_scatter(cb.grad.view(-1), self.out().grad.view(-1), accumulate=self.pair.acc["INPUT"])
             return
         b = self.buf("INPUT")
         if b.requires_grad:
@@ -329,6 +388,8 @@ class DistExecutable(Executable):
         # activations are summed over ranks (Replicate backward, Reduction forward) by the peer-memory all-reduce kernel
         # through a symmetric staging buffer, so that a plan with such operators is still one CUDA graph
         self.peer_allreduce = fuse_collectives
+        # the same for the stand-alone all-gathers and reduce-scatters of Combine / Repartition / Replicate
+        self.peer_collectives = fuse_collectives
         self._pre_analyse(pcg, ctx)
         super().__init__(pcg, cfg, dist=ctx)
         # NCCL collectives are issued eagerly: a plan that still contains one (a parallel operator that is neither

@@ -63,6 +63,63 @@ class GradAllReduce:
         return offset + v0 * 8, offset + max(v1, v0) * 8
 
 
+class PeerAllGather:
+    """All-gather of equal shards over peer memory (the stand-alone Combine, and Repartition's backward): every rank
+    copies its shard into slot `rank` of every peer's staging buffer with plain stores over NVLink.  The result
+    ``gathered`` ([world, shard elements]) lives in the staging buffer until the next call.  Two flag barriers frame the
+    copy: the first keeps a fast rank from overwriting a buffer a peer is still reading from the previous call, the second
+    tells every rank that all shards have landed.  No library call, so a plan built from these stays one CUDA graph."""
+
+    def __init__(self, ctx: DistContext, shard_numel: int, dtype=torch.bfloat16):
+        es = torch.empty((), dtype=dtype).element_size()
+        if (shard_numel * es) % 16 != 0:
+            raise ValueError("a shard must be a multiple of 16 bytes")
+        self.ctx, self.n, self.dtype = ctx, shard_numel, dtype
+        self.shard_bytes = shard_numel * es
+        self.stage = ctx.symmetric(ctx.world_size * self.shard_bytes)
+        self.gathered = self.stage.view(dtype, shape=(ctx.world_size, shard_numel), numel=ctx.world_size * shard_numel)
+        self.flag_base = ctx.alloc_flags(ctx.world_size)
+        self.bar_pre, self.bar_post = ctx.alloc_flags(ctx.world_size), ctx.alloc_flags(ctx.world_size)
+        self.sync_push, self.sync_pre, self.sync_post = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
+
+    def __call__(self, shard: torch.Tensor) -> torch.Tensor:
+        ctx = self.ctx
+        if shard.numel() != self.n or shard.dtype != self.dtype or not shard.is_contiguous():
+            raise ValueError("shard does not match the buffer this all-gather was built for")
+        comm.barrier(ctx, self.bar_pre, self.sync_pre)
+        comm.push_rows(ctx, shard, self.stage, ctx.rank * self.shard_bytes, self.flag_base, self.sync_push)
+        comm.barrier(ctx, self.bar_post, self.sync_post)
+        return self.gathered
+
+
+class PeerReduceScatter:
+    """Reduce-scatter over peer memory (Reduction -> Repartition without a GEMM to fuse into, and the backward of
+    Combine -> Replicate): piece p of this rank's partial sums goes into slot `rank` of peer p's staging buffer; every
+    rank then sums the `world` slots it received (the kernel waits for the senders' flags itself)."""
+
+    def __init__(self, ctx: DistContext, piece_numel: int, dtype=torch.bfloat16):
+        es = torch.empty((), dtype=dtype).element_size()
+        if (piece_numel * es) % 16 != 0 or piece_numel % 8 != 0:
+            raise ValueError("a piece must be a multiple of 8 elements and of 16 bytes")
+        self.ctx, self.n, self.dtype = ctx, piece_numel, dtype
+        self.piece_bytes = piece_numel * es
+        self.stage = ctx.symmetric(ctx.world_size * self.piece_bytes)
+        self.stage_t = self.stage.view(dtype, numel=ctx.world_size * piece_numel)
+        self.flag_base = ctx.alloc_flags(ctx.world_size)
+        self.bar_base = ctx.alloc_flags(ctx.world_size)
+        self.sync_send, self.sync_red, self.sync_bar = ctx.new_sync(), ctx.new_sync(), ctx.new_sync()
+
+    def __call__(self, full: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+        """out[piece] (+)= sum over ranks of their full[rank * piece : (rank + 1) * piece]."""
+        ctx = self.ctx
+        if full.numel() != ctx.world_size * self.n or out.numel() != self.n or full.dtype != self.dtype or out.dtype != self.dtype:
+            raise ValueError("operands do not match the buffer this reduce-scatter was built for")
+        comm.barrier(ctx, self.bar_base, self.sync_bar)   # peers may still be summing the previous call's pieces
+        comm.scatter_pieces(ctx, full, self.stage, self.piece_bytes, self.flag_base, self.sync_send)
+        comm.reduce_partials(ctx, self.stage_t, out, ctx.world_size, self.flag_base, self.sync_red, residual=out if accumulate else None)
+        return out
+
+
 class GemmReduceScatter:
     """F1.  y_shard[rows/world, N] = sum_over_ranks( x_r[rows, K_r] @ w_r[N, K_r]^T )  (+ residual shard)."""
 

@@ -14,6 +14,15 @@ def rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+@pytest.fixture(params=[1, 2, 3], ids=["one_tile", "two_tiles_smem_p", "two_tiles_tmem_p"])
+def fwd_variant(request):
+    """Every forward test runs on the three forward kernels (one query tile per CTA; two tiles per CTA with the
+    probabilities handed to the second product through shared or through tensor memory)."""
+    K.attention_set_forward_variant(request.param)
+    yield request.param
+    K.attention_set_forward_variant(1)
+
+
 def _reference(q, k, v, B, H, S_q, S_k, D, scale, causal, keep, p):
     """q/k/v: [B*S, H*D] fp32 leaves.  Returns the [B*Sq, H*D] context."""
     qh = q.view(B, S_q, H, D).permute(0, 2, 1, 3)
@@ -37,7 +46,7 @@ def _packed_qkv(B, S, H, D, seed):
 @pytest.mark.parametrize("S", [128, 1000, 1024])
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("causal,p", [(False, 0.0), (True, 0.0), (False, 0.1)])
-def test_attention_forward_matches_fp32_reference(S, D, causal, p):
+def test_attention_forward_matches_fp32_reference(S, D, causal, p, fwd_variant):
     B, H = 2, 3
     qkv, q, k, v = _packed_qkv(B, S, H, D, seed=S + D)
     out = torch.zeros(B * S, H * D, device="cuda", dtype=torch.bfloat16)
@@ -56,7 +65,7 @@ def test_attention_forward_matches_fp32_reference(S, D, causal, p):
     assert (lse - torch.logsumexp(s, -1) * math.log2(math.e)).abs().max() < 2e-2
 
 
-def test_attention_forward_cross_lengths():
+def test_attention_forward_cross_lengths(fwd_variant):
     """Different query and key lengths (neither a multiple of the tile sizes), separate q / k / v matrices."""
     B, H, D, Sq, Sk = 2, 2, 128, 200, 333
     torch.manual_seed(5)

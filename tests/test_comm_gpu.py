@@ -168,6 +168,47 @@ def w_alltoall_embedding(ctx):
 
 
 # ------------------------------------------------------------------ tests
+def w_peer_collectives(ctx):
+    """Stand-alone all-gather and reduce-scatter over peer memory against NCCL, called repeatedly on the same buffers (the
+    barriers around the copies are what makes reuse safe), on the whole job and on a sub-group view of it."""
+    import torch.distributed as dist
+    from flexflow_train_b200.parallel.fused_ops import PeerAllGather, PeerReduceScatter
+
+    W, r = ctx.world_size, ctx.rank
+    out = {}
+    for dtype in (torch.bfloat16, torch.float32):
+        n = 3 * 1024 + 8
+        ag = PeerAllGather(ctx, n, dtype)
+        rs = PeerReduceScatter(ctx, n, dtype)
+        worst_ag = worst_rs = 0.0
+        for it in range(4):
+            torch.manual_seed(100 * it + r)
+            shard = torch.randn(n, device="cuda").to(dtype)
+            got = ag(shard).clone()
+            ref = torch.empty(W, n, device="cuda", dtype=dtype)
+            dist.all_gather_into_tensor(ref.view(-1), shard)
+            worst_ag = max(worst_ag, float((got.float() - ref.float()).abs().max()))
+            full = torch.randn(W * n, device="cuda").to(dtype)
+            base = torch.randn(n, device="cuda").to(dtype)
+            mine = base.clone()
+            rs(full, mine, accumulate=(it % 2 == 1))
+            ref_rs = torch.empty(n, device="cuda", dtype=torch.float32)
+            dist.reduce_scatter_tensor(ref_rs, full.float())
+            if it % 2 == 1:
+                ref_rs += base.float()
+            worst_rs = max(worst_rs, _rel(mine, ref_rs))
+        out[str(dtype)] = (worst_ag, worst_rs)
+    return out
+
+
+def test_peer_all_gather_and_reduce_scatter_match_nccl():
+    res = _run("w_peer_collectives")
+    for rank, by_dtype in res.items():
+        for dt, (e_ag, e_rs) in by_dtype.items():
+            assert e_ag == 0.0, (rank, dt, e_ag)
+            assert e_rs < (1e-2 if "bfloat16" in dt else 1e-5), (rank, dt, e_rs)
+
+
 def test_grad_allreduce_scale_matches_nccl():
     res = _run("w_allreduce")
     for r, errs in res.items():

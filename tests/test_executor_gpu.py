@@ -386,7 +386,7 @@ def test_measured_costs_fill_the_search_estimator(tmp_path):
     path = tmp_path / "table.json"
     cfg = FFConfig(measure_costs=True, cost_table_file=str(path))
     est, info = _search_estimator("mlp", cfg_model, cg, 2, cfg, None, ExecConfig(compute_dtype="bf16"))
-    assert info["source"] == "measured" and info["entries"] > 0 and est.num_measured == info["entries"]
+    assert info["source"] == "measured" and info["entries"] > 0 and est.num_measured() == info["entries"]
     lin = [n["id"] for n in cg.nodes() if n["type"] == "LINEAR"][0]
     cost = est.op_cost(cg, lin)
     assert cost["fwd_ms"] > 0 and cost["bwd_ms"] > 0
