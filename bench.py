@@ -321,7 +321,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--model", default="transformer_large", choices=sorted(MODEL_CONFIGS))
     ap.add_argument("--no-cuda-graph", action="store_true")
-    ap.add_argument("--strategy", default="search", help="search | dp | tp | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
+    ap.add_argument("--strategy", default="search", help="search | dp | tp | dp<a>xtp<b> (device mesh) | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
     ap.add_argument("--search-budget", type=int, default=10, help="Unity search budget on top of the scored templates (0 = templates only)")
     ap.add_argument("--search-time-limit", type=float, default=30.0)
     ap.add_argument("--timeline", action="store_true",
@@ -362,7 +362,8 @@ def main():
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
                          fuse_collectives=not args.no_fused_collectives, search_budget=args.search_budget,
                          search_time_limit_s=args.search_time_limit,
-                         search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel", "tables": "table_parallel"}.get(args.strategy, "unity"),
+                         search_algorithm={"search": "unity", "dp": "data_parallel", "tp": "tensor_parallel", "tables": "table_parallel"}.get(
+                             args.strategy, args.strategy if "xtp" in args.strategy else "unity"),
                          import_strategy_file=args.strategy if os.path.exists(args.strategy) else None)
     model = api.compile(model_name, mcfg, config=ffcfg, optimizer=OptimizerConfig(kind=opt_kind, lr=lr, momentum=momentum),
                         loss=loss_kind, dist=dctx)
@@ -394,10 +395,12 @@ def main():
     # with the number of ranks; anything else (an input a tensor-parallel plan replicates) is passed whole.
     direct = set(getattr(ex, "direct_inputs", {}))
     if world > 1 and direct:
-        lb = global_batch // world
+        # the sample dimension is cut over the data-parallel axis: all ranks on a one-axis plan, the rows of the mesh otherwise
+        grp = next(iter(ex.direct_inputs.values())).gctx
+        lb = global_batch // grp.world_size
 
         def rows(t):
-            return t[rank * lb:(rank + 1) * lb].contiguous().pin_memory()
+            return t[grp.rank * lb:(grp.rank + 1) * lb].contiguous().pin_memory()
         host_batches = [({k: (rows(v) if k in direct else v) for k, v in i.items()}, rows(l.reshape(global_batch, -1))) for i, l in host_batches]
     dev_batches = [({k: v.cuda() for k, v in i.items()}, l.cuda()) for i, l in host_batches]
 

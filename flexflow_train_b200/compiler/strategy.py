@@ -287,7 +287,7 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
             if has_stacked_embeddings(cg):
                 cands[f"dp{W}+tables_mp{W}"] = table_parallel_strategy(cg, W, rules)
     # data x tensor parallel meshes (the executor runs them on a dp x tp device mesh)
-    if W >= 4 and f"tp{W}" in cands and not only_data_parallel and algorithm in ("unity", "mcmc"):
+    if W >= 4 and f"tp{W}" in cands and not only_data_parallel and (algorithm in ("unity", "mcmc") or "xtp" in algorithm):
         tp = 2
         while tp < W:
             if W % tp == 0:
@@ -303,6 +303,8 @@ def optimize(cg, machine=None, *, world: Optional[int] = None, algorithm: str = 
         best_name = f"tp{W}" if f"tp{W}" in scored else min(scored, key=lambda k: scored[k]["runtime_ms"])
     elif algorithm == "table_parallel":
         best_name = f"dp{W}+tables_mp{W}" if f"dp{W}+tables_mp{W}" in scored else min(scored, key=lambda k: scored[k]["runtime_ms"])
+    elif algorithm in scored:   # a template by name, e.g. "dp2xtp2": the mesh strategy as it is
+        best_name = algorithm
     else:
         best_name = min(scored, key=lambda k: scored[k]["runtime_ms"])
     best = scored[best_name]

@@ -725,6 +725,12 @@ class DistExecutable(Executable):
         out_sum = self.graph.shape((op.nid, op.outputs[0][0])).sum_degree
         return out_sum == 1 or (self.tp_idx if self.mesh is not None else self.ctx.rank) == 0
 
+    def bias_grad_without_use(self, op, slot: str) -> bool:
+        # On one axis the gradient reduction spans all ranks, so the zero gradients of the ranks that do not add the bias
+        # and the full gradient of the one that does sum to the right value.  On a mesh, gradients are summed over the
+        # data-parallel group only: the tensor-parallel peers never see each other's bias gradient, and each computes it.
+        return self.mesh is not None and op.inputs.get(slot) is not None and not self.use_bias(op, slot)
+
     # ------------------------------------------------------------------ loss on the local shard
     def resolve_loss_value(self, v: Value) -> Value:
         skip = getattr(self, "_skip_nodes", set())

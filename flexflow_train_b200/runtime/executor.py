@@ -265,6 +265,8 @@ class LinearOp(OpImpl):
         self.x2d = x.view(-1, x.shape[-1])
         self.w = self.x("WEIGHT")
         self.bias = self.x("BIAS") if ("BIAS" in self.inputs and self.ex.use_bias(self, "BIAS")) else None
+        # a bias this rank holds but does not add (row-parallel shard): its gradient is still the column sum of dY
+        self.bias_grad = self.bias is not None or ("BIAS" in self.inputs and self.ex.bias_grad_without_use(self, "BIAS"))
         rows, cols = self.x2d.shape[0], self.w.shape[0]
         self.pre = torch.empty(rows, cols, dtype=x.dtype, device=x.device) if (self.act == "gelu" and self.ex.cfg.training) else None
         self.ex.need_scratch(4 * K.bias_act_bwd_scratch(rows, cols) if K.available() and self.ex.on_gpu else 0)
@@ -294,12 +296,12 @@ class LinearOp(OpImpl):
             d = self.bwd_dropout
             src = d.out().grad.view_as(self.y2d)  # gradient w.r.t. the dropped output; masked and passed on in one pass
             saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
-            bb = self.buf("BIAS") if self.bias is not None else None
+            bb = self.buf("BIAS") if self.bias_grad else None
             K.bias_act_bwd(src, saved, dy, bb.grad if bb is not None else None, self.ex.scratch_f32(), self.act,
                            accumulate=self.acc.get("BIAS", False), dropout=(d.p, d.salt, self.ex.seed_tensor))
-        elif self.act is not None or self.bias is not None or self.fused_dropout is not None:
+        elif self.act is not None or self.bias_grad or self.fused_dropout is not None:
             saved = self.pre if self.act == "gelu" else (self.y2d if self.act else None)
-            bb = self.buf("BIAS") if self.bias is not None else None
+            bb = self.buf("BIAS") if self.bias_grad else None
             rewrite = self.act is not None or self.fused_dropout is not None
             K.bias_act_bwd(dy, saved, dy if rewrite else None, bb.grad if bb is not None else None,
                            self.ex.scratch_f32(), self.act, accumulate=self.acc.get("BIAS", False), dropout=self._drop())
@@ -438,6 +440,7 @@ class AttentionOp(OpImpl):
             self.alloc_out()
         self.bias_in = self.x("INPUT_BIAS") if "INPUT_BIAS" in self.inputs else None
         self.bias_out = self.x("OUTPUT_BIAS") if ("OUTPUT_BIAS" in self.inputs and ex.use_bias(self, "OUTPUT_BIAS")) else None
+        self.bias_out_grad = self.bias_out is not None or ("OUTPUT_BIAS" in self.inputs and ex.bias_grad_without_use(self, "OUTPUT_BIAS"))
         self.alpha = 1.0 / math.sqrt(kd)
         nbytes = self.probs.numel() * self.probs.element_size()
         if self.cb:
@@ -612,7 +615,7 @@ class AttentionOp(OpImpl):
         accw = self.acc["WEIGHT"]
         n_q, n_k, n_v = H * kd * self.dq, H * kd * self.dk, H * vd * self.dv
         g_wo = wg[n_q + n_k + n_v:].view(self.embed, H * vd)
-        if self.bias_out is not None:
+        if self.bias_out_grad:
             K.bias_act_bwd(dy, None, None, self.buf("OUTPUT_BIAS").grad, ex.scratch_f32(), None,
                            accumulate=self.acc.get("OUTPUT_BIAS", False))
         self.ex.wgrad_gemm(dy, self.ctx, g_wo, accw)
@@ -1078,6 +1081,11 @@ class Executable:
         """False when `slot` is the bias of an operator that produces partial sums and this rank is not the one
         that contributes it (a row-parallel Linear adds its bias once, not once per shard)."""
         return True
+
+    def bias_grad_without_use(self, op, slot: str) -> bool:
+        """True when this rank keeps a copy of a bias it does not add in forward (see use_bias) and still has to compute
+        that bias's gradient itself, because the gradient reduction does not reach the rank that adds it."""
+        return False
 
     # ---- physical layout: 4-D activations produced by convolution-stack operators are kept channels-last
     def is_nhwc(self, v: Value) -> bool:
