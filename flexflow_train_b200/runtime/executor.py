@@ -146,7 +146,7 @@ class OpImpl:
         sh = dict(self.outputs)[slot]
         shape = list(sh.piece_sizes) if shape is None else shape
         dt = self.ex.torch_dtype(sh.dtype) if dtype is None else dtype
-        t = torch.empty(shape, dtype=dt, device=self.ex.device)
+        t = self.ex.allocator.allocate(shape, dt)
         self.out(slot).data = t
         return t
 
@@ -1050,6 +1050,12 @@ class Executable:
         self.on_gpu = self.device.type == "cuda"
         if self.on_gpu:
             K.lib()  # fail loudly if the kernel library is missing
+        # every long-lived device buffer of the plan (parameter / gradient / optimizer arenas, activations, scratch) comes
+        # from this allocator, which counts bytes (the reference's per-device Allocator behind a tracking wrapper,
+        # lib/kernels/include/kernels/allocation.h, lib/local-execution/.../tracked_allocator.h); symmetric peer-memory
+        # arenas of the multi-GPU executor are the exception: they come from the peer-memory context
+        from .allocator import LocalCPUAllocator, LocalCudaAllocator, TrackedAllocator
+        self.allocator = TrackedAllocator(LocalCudaAllocator(self.device.index or 0) if self.on_gpu else LocalCPUAllocator())
         self.values: Dict[Value, _Buf] = {}
         self.layout: Dict[Value, str] = {}
         self.ops: Dict[int, OpImpl] = {}
@@ -1187,9 +1193,8 @@ class Executable:
         # 5. gradient buffers + accumulate flags
         if self.cfg.training:
             self._plan_gradients()
-        self._scratch = torch.empty(max(self._scratch_bytes // 4, 1), dtype=torch.float32, device=self.device)
-        self._big = [torch.empty(max(self._big_scratch_bytes, 1), dtype=torch.uint8, device=self.device)
-                     for _ in range(max(self._big_scratch_slots, 1))]
+        self._scratch = self.allocator.allocate([max(self._scratch_bytes // 4, 1)], torch.float32)
+        self._big = [self.allocator.allocate([max(self._big_scratch_bytes, 1)], torch.uint8) for _ in range(max(self._big_scratch_slots, 1))]
 
     def sparse_weight_nodes(self) -> List[int]:
         """Weights that are the table of exactly one Embedding and can take the sparse SGD update."""
@@ -1231,13 +1236,13 @@ class Executable:
         self.param_offsets = offs
         self.num_params = total
         mixed = self.cfg.compute_dtype == "bf16"
-        self.master = torch.zeros(max(total, 1), dtype=torch.float32, device=dev)
+        self.master = self.allocator.allocate([max(total, 1)], torch.float32).zero_()
         self.shadow = self.alloc_shadow_arena(max(total, 1)) if mixed else None
         if self.cfg.training:
             self.grads = self.alloc_grad_arena(max(total, 1), torch.bfloat16 if mixed else torch.float32)
-            self.opt_m = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) \
+            self.opt_m = self.allocator.allocate([max(total, 1)], torch.float32).zero_() \
                 if (self.cfg.optimizer.kind == "adam" or self.cfg.optimizer.momentum > 0) else None
-            self.opt_v = torch.zeros(max(total, 1), dtype=torch.float32, device=dev) if self.cfg.optimizer.kind == "adam" else None
+            self.opt_v = self.allocator.allocate([max(total, 1)], torch.float32).zero_() if self.cfg.optimizer.kind == "adam" else None
         for i, nid in enumerate(self.param_nodes):
             o, n = offs[nid]
             shape = self.local_weight_shape(nid)
@@ -1278,11 +1283,16 @@ class Executable:
         return param_nodes
 
     def alloc_grad_arena(self, numel, dtype):
-        return torch.zeros(numel, dtype=dtype, device=self.device)
+        return self.allocator.allocate([numel], dtype).zero_()
+
+    def memory_report(self) -> dict:
+        """Bytes the plan's buffers hold, as counted by the executor's allocator."""
+        a = self.allocator
+        return {"current_bytes": a.current_bytes, "peak_bytes": a.peak_bytes, "total_allocated_bytes": a.total_allocated_bytes}
 
     def alloc_shadow_arena(self, numel):
         """The bf16 copy of the weights that the kernels read (the fp32 master arena is only touched by the update)."""
-        return torch.zeros(numel, dtype=torch.bfloat16, device=self.device)
+        return self.allocator.allocate([numel], torch.bfloat16).zero_()
 
     def resolve_loss_value(self, v: Value) -> Value:
         """The value the loss is computed on; the distributed executable steps back over a trailing Combine."""

@@ -400,3 +400,18 @@ def test_measured_costs_fill_the_search_estimator(tmp_path):
     est2, info2 = _search_estimator("mlp", cfg_model, cg, 2, FFConfig(cost_table_file=str(path)), None, ExecConfig())
     assert info2 == {"source": str(path), "entries": info["entries"]}
     assert est2.op_cost(cg, lin) == cost
+
+
+def test_executor_buffers_come_from_the_tracked_allocator():
+    """Arenas, activations and scratch are handed out by the executor's allocator, which counts them."""
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable
+    cg = core.build_model("mlp", {"batch_size": 32})
+    ex = Executable(cg, ExecConfig(compute_dtype="bf16"))
+    rep = ex.memory_report()
+    params = sum(n for _, n in ex.param_offsets.values())
+    # fp32 master + bf16 shadow + bf16 gradients at least
+    assert rep["current_bytes"] >= params * (4 + 2 + 2) and rep["peak_bytes"] >= rep["current_bytes"]
+    assert ex.allocator.inner.num_live > 4
+    small = Executable(core.build_model("mlp", {"batch_size": 8}), ExecConfig(compute_dtype="bf16"))
+    assert small.memory_report()["current_bytes"] < rep["current_bytes"]
