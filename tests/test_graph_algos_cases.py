@@ -1,0 +1,137 @@
+"""Digraph algorithms on the hand-worked cases of lib/utils/test/src/utils/graph/digraph/algorithms/*.cc (transitive
+reduction / closure, dominators, post-dominators, longest paths, components, lowest common ancestors) and against a brute-force
+oracle on random DAGs."""
+import itertools
+import random
+
+import pytest
+
+from flexflow_train_b200 import _ffcore as c
+
+
+def G(edges, n=None):
+    ns = sorted(set(x for e in edges for x in e) | set(range(n or 0)))
+    return c.DiGraph(ns, edges)
+
+
+@pytest.mark.parametrize("n,edges,kept", [
+    (3, [(0, 1), (1, 2), (0, 2)], [(0, 1), (1, 2)]),
+    (6, [(0, 1), (1, 2), (2, 3), (0, 3)], [(0, 1), (1, 2), (2, 3)]),
+    (6, [(0, 1), (1, 2), (2, 3), (3, 4), (0, 3), (1, 4)], [(0, 1), (1, 2), (2, 3), (3, 4)]),
+    (4, [(0, 1), (0, 2), (1, 3), (2, 3)], [(0, 1), (0, 2), (1, 3), (2, 3)]),            # a diamond has nothing to remove
+    (5, [(0, 1), (0, 2), (1, 3), (2, 3), (0, 3), (3, 4), (0, 4), (1, 4)], [(0, 1), (0, 2), (1, 3), (2, 3), (3, 4)]),
+    (4, [], []),
+])
+def test_transitive_reduction_cases(n, edges, kept):
+    r = c.transitive_reduction(G(edges, n))
+    assert sorted(r.edges()) == sorted(kept) and sorted(r.nodes()) == list(range(n))
+
+
+@pytest.mark.parametrize("edges,closure", [
+    ([(0, 1), (1, 2), (2, 3)], [(0, 1), (0, 2), (0, 3), (1, 2), (1, 3), (2, 3)]),
+    ([(0, 1), (0, 2)], [(0, 1), (0, 2)]),
+    ([(0, 2), (1, 2), (2, 3), (2, 4)], [(0, 2), (0, 3), (0, 4), (1, 2), (1, 3), (1, 4), (2, 3), (2, 4)]),
+])
+def test_transitive_closure_cases(edges, closure):
+    assert sorted(c.transitive_closure(G(edges)).edges()) == sorted(closure)
+
+
+def test_dominators_on_a_graph_with_a_join_and_a_side_entrance():
+    #      0 -> 1 -> 3 -> 4
+    #      0 -> 2 -> 3        5 -> 4   (a second source: only 4 and 5 itself are reachable from it)
+    g = G([(0, 1), (0, 2), (1, 3), (2, 3), (3, 4), (5, 4)])
+    dom = c.get_dominators(g)
+    assert dom[0] == {0} and dom[1] == {0, 1} and dom[2] == {0, 2} and dom[3] == {0, 3}
+    assert dom[4] == {4}      # reachable from two sources: no other node lies on every path
+    pdom = c.get_post_dominators(g)
+    assert pdom[0] == {0, 3, 4} and pdom[1] == {1, 3, 4} and pdom[5] == {5, 4} and pdom[4] == {4}
+    assert c.get_imm_dominator(g, 3) == 0 and c.get_imm_dominator(g, 1) == 0 and c.get_imm_dominator(g, 4) is None
+
+
+@pytest.mark.parametrize("edges,lengths", [
+    ([(0, 1), (1, 2), (0, 2)], {0: 0, 1: 1, 2: 2}),
+    ([(0, 1), (0, 2), (1, 3), (2, 3), (3, 4), (0, 4)], {0: 0, 1: 1, 2: 1, 3: 2, 4: 3}),
+    ([(0, 1), (1, 2), (2, 3), (0, 3), (3, 4), (1, 4)], {0: 0, 1: 1, 2: 2, 3: 3, 4: 4}),
+])
+def test_longest_path_lengths_from_root_cases(edges, lengths):
+    assert c.get_longest_path_lengths_from_root(G(edges)) == lengths
+
+
+@pytest.mark.parametrize("edges,n,components", [
+    ([(0, 1), (1, 2), (3, 4)], 6, [[0, 1, 2], [3, 4], [5]]),
+    ([(0, 2), (1, 2)], 3, [[0, 1, 2]]),
+    ([], 3, [[0], [1], [2]]),
+])
+def test_weakly_connected_components_cases(edges, n, components):
+    got = sorted(sorted(s) for s in c.get_weakly_connected_components(G(edges, n)))
+    assert got == components
+
+
+def test_lowest_common_ancestor_cases():
+    #        0
+    #       / \
+    #      1   2
+    #     / \   \
+    #    3   4   5
+    tree = G([(0, 1), (0, 2), (1, 3), (1, 4), (2, 5)])
+    assert c.get_lowest_common_ancestor(tree, {3, 4}) == 1
+    assert c.get_lowest_common_ancestor(tree, {3, 5}) == 0
+    assert c.get_lowest_common_ancestor(tree, {3}) == 3
+    assert c.get_lowest_common_ancestor(tree, {1, 4}) == 1
+
+
+# ------------------------------------------------------------------------------------------ random DAGs vs brute force
+def random_dag(rng, n, p):
+    return [(i, j) for i in range(n) for j in range(i + 1, n) if rng.random() < p]
+
+
+def reach(n, edges):
+    adj = {i: set() for i in range(n)}
+    for a, b in edges:
+        adj[a].add(b)
+    r = {i: set() for i in range(n)}
+    for i in reversed(range(n)):
+        for j in adj[i]:
+            r[i] |= {j} | r[j]
+    return r
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_closure_reduction_descendants_against_brute_force(seed):
+    rng = random.Random(seed)
+    n = rng.randint(4, 11)
+    edges = random_dag(rng, n, rng.choice([0.2, 0.4, 0.7]))
+    g = G(edges, n)
+    r = reach(n, edges)
+    assert sorted(c.transitive_closure(g).edges()) == sorted((i, j) for i in range(n) for j in r[i])
+    red = sorted(c.transitive_reduction(g).edges())
+    # an edge survives iff no longer path connects its ends; the reduction keeps reachability
+    want = sorted((a, b) for a, b in set(edges) if not any(b in r[k] for k in range(n) if k != b and (a, k) in set(edges)))
+    assert red == want
+    assert reach(n, red) == r
+    for v in range(n):
+        assert c.get_descendants(g, v) == r[v]
+        assert c.get_ancestors(g, v) == {u for u in range(n) if v in r[u]}
+    order = c.topological_ordering(g)
+    pos = {v: i for i, v in enumerate(order)}
+    assert all(pos[a] < pos[b] for a, b in edges)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_dominators_against_path_enumeration(seed):
+    rng = random.Random(100 + seed)
+    n = rng.randint(4, 8)
+    edges = [(0, j) for j in range(1, n) if rng.random() < 0.4] + random_dag(rng, n, 0.35)
+    edges = sorted(set(edges) | {(0, j) for j in range(1, n) if not any(b == j for _, b in edges)})   # single source 0
+    g = G(edges, n)
+    adj = {i: [b for a, b in edges if a == i] for i in range(n)}
+
+    def paths(u, v):
+        if u == v:
+            return [[v]]
+        return [[u] + p for w in adj[u] for p in paths(w, v)]
+
+    dom = c.get_dominators(g)
+    for v in range(n):
+        ps = paths(0, v)
+        assert dom[v] == set.intersection(*[set(p) for p in ps]), (edges, v)
