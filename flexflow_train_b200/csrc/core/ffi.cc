@@ -6,6 +6,7 @@
 #include <string>
 
 #include "builder.h"
+#include "graph_algos.h"
 #include "ir.h"
 #include "models.h"
 #include "search.h"
@@ -118,6 +119,116 @@ FFC_EXPORT int ffc_builder_binary(ffc_builder_t *b, const char *op, ffc_value_t 
 FFC_EXPORT int ffc_builder_softmax(ffc_builder_t *b, ffc_value_t x, int dim, const char *name, ffc_value_t *out) {
   return guarded([&] { *out = val(b->b.softmax(ref(x), dim, str(name))); });
 }
+FFC_EXPORT int ffc_builder_pool2d(ffc_builder_t *b, ffc_value_t x, int kernel_h, int kernel_w, int stride_h, int stride_w, int padding_h,
+                                  int padding_w, const char *pool_type, const char *activation, const char *name, ffc_value_t *out) {
+  return guarded([&] {
+    *out = val(b->b.pool2d(ref(x), kernel_h, kernel_w, stride_h, stride_w, padding_h, padding_w, str(pool_type).empty() ? "MAX" : str(pool_type),
+                           opt(activation), str(name)));
+  });
+}
+FFC_EXPORT int ffc_builder_batch_norm(ffc_builder_t *b, ffc_value_t x, int affine, const char *activation, double eps, double momentum,
+                                      const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.batch_norm(ref(x), affine != 0, opt(activation), eps, momentum, str(name))); });
+}
+FFC_EXPORT int ffc_builder_layer_norm(ffc_builder_t *b, ffc_value_t x, const int *axes, int num_axes, int affine, double eps, const char *name,
+                                      ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.layer_norm(ref(x), std::vector<int>(axes, axes + num_axes), affine != 0, eps, str(name))); });
+}
+FFC_EXPORT int ffc_builder_embedding(ffc_builder_t *b, ffc_value_t ids, int64_t num_entries, int64_t out_dim, const char *aggr, const char *dtype,
+                                     const char *name, ffc_value_t *out) {
+  return guarded([&] {
+    *out = val(b->b.embedding(ref(ids), num_entries, out_dim, str(aggr).empty() ? "SUM" : str(aggr),
+                              datatype_from_string(dtype && *dtype ? dtype : "FLOAT"), std::nullopt, str(name)));
+  });
+}
+FFC_EXPORT int ffc_builder_multihead_attention(ffc_builder_t *b, ffc_value_t q, ffc_value_t k, ffc_value_t v, int64_t embed_dim,
+                                               int64_t num_heads, int64_t kdim, int64_t vdim, double dropout, int bias, int add_bias_kv,
+                                               int add_zero_attn, const char *name, ffc_value_t *out) {
+  return guarded([&] {
+    *out = val(b->b.multihead_attention(ref(q), ref(k), ref(v), embed_dim, num_heads, kdim > 0 ? std::optional<int64_t>(kdim) : std::nullopt,
+                                        vdim > 0 ? std::optional<int64_t>(vdim) : std::nullopt, dropout, bias != 0, add_bias_kv != 0,
+                                        add_zero_attn != 0, std::nullopt, str(name)));
+  });
+}
+FFC_EXPORT int ffc_builder_batch_matmul(ffc_builder_t *b, ffc_value_t a, ffc_value_t bb, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.batch_matmul(ref(a), ref(bb), str(name))); });
+}
+FFC_EXPORT int ffc_builder_dropout(ffc_builder_t *b, ffc_value_t x, double rate, uint64_t seed, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.dropout(ref(x), rate, seed, str(name))); });
+}
+FFC_EXPORT int ffc_builder_cast(ffc_builder_t *b, ffc_value_t x, const char *dtype, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.cast(ref(x), datatype_from_string(str(dtype)), str(name))); });
+}
+FFC_EXPORT int ffc_builder_concat(ffc_builder_t *b, const ffc_value_t *xs, int num, int axis, const char *name, ffc_value_t *out) {
+  return guarded([&] {
+    std::vector<ValueRef> v;
+    for (int i = 0; i < num; ++i) v.push_back(ref(xs[i]));
+    *out = val(b->b.concat(v, axis, str(name)));
+  });
+}
+FFC_EXPORT int ffc_builder_split(ffc_builder_t *b, ffc_value_t x, const int64_t *sizes, int num, int axis, const char *name, ffc_value_t *outs) {
+  return guarded([&] {
+    auto r = b->b.split(ref(x), std::vector<int64_t>(sizes, sizes + num), axis, str(name));
+    for (size_t i = 0; i < r.size(); ++i) outs[i] = val(r[i]);
+  });
+}
+FFC_EXPORT int ffc_builder_flat(ffc_builder_t *b, ffc_value_t x, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.flat(ref(x), 1, -1, str(name))); });
+}
+FFC_EXPORT int ffc_builder_transpose(ffc_builder_t *b, ffc_value_t x, const int *perm, int num, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.transpose(ref(x), std::vector<int>(perm, perm + num), str(name))); });
+}
+FFC_EXPORT int ffc_builder_reshape(ffc_builder_t *b, ffc_value_t x, const int64_t *dims, int num, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.reshape(ref(x), std::vector<int64_t>(dims, dims + num), str(name))); });
+}
+FFC_EXPORT int ffc_builder_reverse(ffc_builder_t *b, ffc_value_t x, int axis, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.reverse(ref(x), axis, str(name))); });
+}
+FFC_EXPORT int ffc_builder_gather(ffc_builder_t *b, ffc_value_t x, ffc_value_t index, int dim, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.gather(ref(x), ref(index), dim, str(name))); });
+}
+FFC_EXPORT int ffc_builder_top_k(ffc_builder_t *b, ffc_value_t x, int k, int sorted, const char *name, ffc_value_t *values,
+                                 ffc_value_t *indices) {
+  return guarded([&] {
+    auto r = b->b.top_k(ref(x), k, sorted != 0, str(name));
+    *values = val(r.at(0));
+    *indices = val(r.at(1));
+  });
+}
+FFC_EXPORT int ffc_builder_reduce(ffc_builder_t *b, const char *op, ffc_value_t x, const int *axes, int num_axes, int keepdims,
+                                  const char *name, ffc_value_t *out) {
+  return guarded([&] {
+    *out = val(b->b.reduce(optype_from_string(str(op)), ref(x), std::vector<int>(axes, axes + num_axes), keepdims != 0, str(name)));
+  });
+}
+FFC_EXPORT int ffc_builder_broadcast(ffc_builder_t *b, ffc_value_t x, const int64_t *target, int num, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.broadcast(ref(x), std::vector<int64_t>(target, target + num), str(name))); });
+}
+FFC_EXPORT ffc_builder_t *ffc_builder_create_parallel(void) { return new ffc_builder{GraphBuilder(true)}; }
+FFC_EXPORT int ffc_builder_parallel_partition(ffc_builder_t *b, ffc_value_t x, int dim, int degree, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.parallel_partition(ref(x), dim, degree, str(name))); });
+}
+FFC_EXPORT int ffc_builder_parallel_combine(ffc_builder_t *b, ffc_value_t x, int dim, int degree, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.parallel_combine(ref(x), dim, degree, str(name))); });
+}
+FFC_EXPORT int ffc_builder_parallel_replicate(ffc_builder_t *b, ffc_value_t x, int degree, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.parallel_replicate(ref(x), degree, str(name))); });
+}
+FFC_EXPORT int ffc_builder_parallel_reduce(ffc_builder_t *b, ffc_value_t x, int degree, const char *name, ffc_value_t *out) {
+  return guarded([&] { *out = val(b->b.parallel_reduce(ref(x), degree, str(name))); });
+}
+FFC_EXPORT int ffc_builder_value_degrees(const ffc_builder_t *b, ffc_value_t v, int *degrees, int max_dims, int *ndims, int *sum_degree,
+                                         int *copy_degree) {
+  return guarded([&] {
+    const PShape &sh = b->b.graph.shape(ref(v));
+    auto d = sh.degrees();
+    if ((int)d.size() > max_dims) throw Error("ffc_builder_value_degrees: max_dims too small");
+    for (size_t i = 0; i < d.size(); ++i) degrees[i] = (int)d[i];
+    *ndims = (int)d.size();
+    if (sum_degree) *sum_degree = (int)sh.sum_degree;
+    if (copy_degree) *copy_degree = (int)sh.discard_copy_degree;
+  });
+}
 FFC_EXPORT int ffc_builder_value_shape(const ffc_builder_t *b, ffc_value_t v, int64_t *dims, int max_dims, int *ndims) {
   return guarded([&] {
     auto sizes = b->b.graph.shape(ref(v)).sizes();
@@ -146,6 +257,27 @@ FFC_EXPORT char *ffc_graph_to_json(const ffc_graph_t *g, int parallel, int inden
 FFC_EXPORT char *ffc_graph_to_dot(const ffc_graph_t *g) {
   char *r = nullptr;
   guarded([&] { r = dup_string(g->g.as_dot()); });
+  return r;
+}
+FFC_EXPORT int ffc_graph_estimate(const ffc_graph_t *pcg, int num_nodes, int gpus_per_node, double *runtime_ms) {
+  return guarded([&] {
+    MachineSpec ms;
+    ms.num_nodes = num_nodes;
+    ms.num_gpus_per_node = gpus_per_node;
+    CostParams cp;
+    cp.nvlink_gbs = ms.intra_node_bandwidth;
+    CostEstimator est(cp, ms);
+    const double t = evaluate_pcg(pcg->g, ms, est).runtime_ms;
+    if (!(t < 1e300)) throw Error("no machine mapping of this graph fits " + std::to_string(num_nodes * gpus_per_node) + " devices");
+    *runtime_ms = t;
+  });
+}
+FFC_EXPORT char *ffc_graph_sp_decomposition(const ffc_graph_t *g) {
+  char *r = nullptr;
+  guarded([&] {
+    // exact when the graph is series-parallel, from SP-ization otherwise; JSON of the left-associative binary tree
+    r = dup_string(sp_to_json(left_associative_binary_sp_tree(get_graph_sp_decomposition(g->g))).dump());
+  });
   return r;
 }
 FFC_EXPORT int ffc_graph_num_nodes(const ffc_graph_t *g) { return (int)g->g.num_nodes(); }

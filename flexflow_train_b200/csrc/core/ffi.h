@@ -45,6 +45,43 @@ int ffc_builder_unary(ffc_builder_t *b, const char *op, ffc_value_t x, int has_s
 int ffc_builder_binary(ffc_builder_t *b, const char *op, ffc_value_t x, ffc_value_t y, const char *name, ffc_value_t *out);
 int ffc_builder_softmax(ffc_builder_t *b, ffc_value_t x, int dim, const char *name, ffc_value_t *out);
 int ffc_builder_value_shape(const ffc_builder_t *b, ffc_value_t v, int64_t *dims, int max_dims, int *ndims);
+/* One function per layer of the builder (the reference's flexflow_model_add_* family, lib/ffi/include/flexflow/ffi.h).
+ * Optional strings may be NULL; initializers are the defaults of the layer. */
+int ffc_builder_pool2d(ffc_builder_t *b, ffc_value_t x, int kernel_h, int kernel_w, int stride_h, int stride_w, int padding_h, int padding_w,
+                       const char *pool_type, const char *activation, const char *name, ffc_value_t *out);
+int ffc_builder_batch_norm(ffc_builder_t *b, ffc_value_t x, int affine, const char *activation, double eps, double momentum, const char *name,
+                           ffc_value_t *out);
+int ffc_builder_layer_norm(ffc_builder_t *b, ffc_value_t x, const int *axes, int num_axes, int affine, double eps, const char *name,
+                           ffc_value_t *out);
+int ffc_builder_embedding(ffc_builder_t *b, ffc_value_t ids, int64_t num_entries, int64_t out_dim, const char *aggr, const char *dtype,
+                          const char *name, ffc_value_t *out);
+int ffc_builder_multihead_attention(ffc_builder_t *b, ffc_value_t q, ffc_value_t k, ffc_value_t v, int64_t embed_dim, int64_t num_heads,
+                                    int64_t kdim, int64_t vdim, double dropout, int bias, int add_bias_kv, int add_zero_attn, const char *name,
+                                    ffc_value_t *out);
+int ffc_builder_batch_matmul(ffc_builder_t *b, ffc_value_t a, ffc_value_t bb, const char *name, ffc_value_t *out);
+int ffc_builder_dropout(ffc_builder_t *b, ffc_value_t x, double rate, uint64_t seed, const char *name, ffc_value_t *out);
+int ffc_builder_cast(ffc_builder_t *b, ffc_value_t x, const char *dtype, const char *name, ffc_value_t *out);
+int ffc_builder_concat(ffc_builder_t *b, const ffc_value_t *xs, int num, int axis, const char *name, ffc_value_t *out);
+int ffc_builder_split(ffc_builder_t *b, ffc_value_t x, const int64_t *sizes, int num, int axis, const char *name, ffc_value_t *outs);
+int ffc_builder_flat(ffc_builder_t *b, ffc_value_t x, const char *name, ffc_value_t *out);
+int ffc_builder_transpose(ffc_builder_t *b, ffc_value_t x, const int *perm, int num, const char *name, ffc_value_t *out);
+int ffc_builder_reshape(ffc_builder_t *b, ffc_value_t x, const int64_t *dims, int num, const char *name, ffc_value_t *out);
+int ffc_builder_reverse(ffc_builder_t *b, ffc_value_t x, int axis, const char *name, ffc_value_t *out);
+int ffc_builder_gather(ffc_builder_t *b, ffc_value_t x, ffc_value_t index, int dim, const char *name, ffc_value_t *out);
+int ffc_builder_top_k(ffc_builder_t *b, ffc_value_t x, int k, int sorted, const char *name, ffc_value_t *values, ffc_value_t *indices);
+/* op: "REDUCE_SUM" or "REDUCE_MEAN" (also MAX / MIN / PROD) */
+int ffc_builder_reduce(ffc_builder_t *b, const char *op, ffc_value_t x, const int *axes, int num_axes, int keepdims, const char *name,
+                       ffc_value_t *out);
+int ffc_builder_broadcast(ffc_builder_t *b, ffc_value_t x, const int64_t *target, int num, const char *name, ffc_value_t *out);
+/* Parallel builder: the four parallel operators are available and implicit weights get their Repartition / Replicate chains. */
+ffc_builder_t *ffc_builder_create_parallel(void);
+int ffc_builder_parallel_partition(ffc_builder_t *b, ffc_value_t x, int dim, int degree, const char *name, ffc_value_t *out);
+int ffc_builder_parallel_combine(ffc_builder_t *b, ffc_value_t x, int dim, int degree, const char *name, ffc_value_t *out);
+int ffc_builder_parallel_replicate(ffc_builder_t *b, ffc_value_t x, int degree, const char *name, ffc_value_t *out);
+int ffc_builder_parallel_reduce(ffc_builder_t *b, ffc_value_t x, int degree, const char *name, ffc_value_t *out);
+/* Parallel shape of a value: per-dim degrees, sum degree and discard-copy degree (degrees has room for max_dims entries). */
+int ffc_builder_value_degrees(const ffc_builder_t *b, ffc_value_t v, int *degrees, int max_dims, int *ndims, int *sum_degree, int *copy_degree);
+
 /* A copy of the graph built so far */
 ffc_graph_t *ffc_builder_graph(const ffc_builder_t *b);
 
@@ -54,6 +91,12 @@ ffc_graph_t *ffc_graph_from_json(const char *v1_json);
 char *ffc_graph_to_json(const ffc_graph_t *g, int parallel, int indent);
 char *ffc_graph_to_dot(const ffc_graph_t *g);
 int ffc_graph_num_nodes(const ffc_graph_t *g);
+/* Estimated step time (ms) of a parallel computation graph on num_nodes x gpus_per_node devices under the analytic cost
+ * model, with the machine mapping the dynamic program finds. */
+int ffc_graph_estimate(const ffc_graph_t *pcg, int num_nodes, int gpus_per_node, double *runtime_ms);
+/* Series-parallel decomposition of the graph's operators as JSON (malloc'd; NULL with an error when there is none). */
+char *ffc_graph_sp_decomposition(const ffc_graph_t *g);
+
 void ffc_graph_destroy(ffc_graph_t *g);
 
 /* ---- strategy search.  algorithm: "unity", "mcmc" or "data_parallel".  On success *out is the mapped parallel
