@@ -880,37 +880,41 @@ __global__ void attn_acc_to_bf16_kernel(const float *__restrict__ acc, bf16 *__r
 //                                                    add covers 128 contiguous bytes of one query's row)
 // The tensor core sees the five products of a step in the order dV, dQ^T, dK, S(next), dP(next): the read-out of dQ^T
 // overlaps the dK and S products, and the next step's softmax overlaps the dP product.
+template <int D_>
 struct BwdCfg {
-  static constexpr int D = 128;
+  static constexpr int D = D_;                            // head dim: 128, or 64 (then dQ is produced untransposed, see the kernel)
   static constexpr int BK = 128;                          // keys per CTA
-  static constexpr int TILE_BYTES = 128 * D * 2;          // a [128 x 128] bf16 tile = two panels of [128 rows x 128 B]
-  static constexpr int PANEL = 128 * 128;                 // bytes between the two 64-column panels of a tile
+  static constexpr int PANEL = 128 * 128;                 // bytes of one 64-column panel: [128 rows x 128 B]
+  static constexpr int TILE_BYTES = 128 * D * 2;          // a [128 x D] bf16 tile = D / 64 panels
+  static constexpr int PS_BYTES = 128 * 128 * 2;          // P or dS: [128 queries x 128 keys] = two panels
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TILE_BYTES;
   static constexpr int OFF_Q = OFF_V + TILE_BYTES;        // [2]
   static constexpr int OFF_DO = OFF_Q + 2 * TILE_BYTES;   // one stage: free again after the step's second product
   static constexpr int OFF_P = OFF_DO + TILE_BYTES;
-  static constexpr int OFF_DS = OFF_P + TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + TILE_BYTES;     // 224 KB of tiles
+  static constexpr int OFF_DS = OFF_P + PS_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + PS_BYTES;       // 224 KB of tiles at head dim 128
   static constexpr int SLACK = 1024;                      // room to align the base to 1024 bytes (checked in the kernel)
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + SLACK;
   static constexpr int TMEM_S = 0;
   static constexpr int TMEM_DPQ = 128;                    // dP, then dQ^T of the same step
-  static constexpr int TMEM_DK = 256;
-  static constexpr int TMEM_DV = 384;
+  static constexpr int TMEM_DK = 256;                     // D columns
+  static constexpr int TMEM_DV = 256 + D;
   static constexpr uint32_t IDESC_SS = attn_idesc(128, 128, 0, 0);    // Q K^T, dO V^T
-  static constexpr uint32_t IDESC_T = attn_idesc(128, 128, 1, 1);     // P^T dO, dS^T Q
-  static constexpr uint32_t IDESC_DQT = attn_idesc(128, 128, 1, 0);   // K^T dS^T
+  static constexpr uint32_t IDESC_T = attn_idesc(128, D, 1, 1);       // P^T dO, dS^T Q
+  static constexpr uint32_t IDESC_DQT = attn_idesc(128, 128, 1, 0);   // K^T dS^T (head dim 128)
+  static constexpr uint32_t IDESC_DQ = attn_idesc(128, D, 0, 1);      // dS K (head dim 64)
+  static_assert(SMEM_BYTES <= 232448, "backward tiles exceed the shared memory of one CTA");
 };
-static_assert(BwdCfg::SMEM_BYTES <= 232448, "backward tiles exceed the shared memory of one CTA");
 
 constexpr int BWD_THREADS = 576;  // TMA warp, MMA warp, 8 softmax / dS warps, 8 dQ read-out warps
 
+template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const AttnArgs p) {
-  using C = BwdCfg;
-  constexpr int D = C::D;
+  using C = BwdCfg<D>;
+  constexpr int PANELS = D / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
@@ -970,7 +974,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < PANELS; ++c) {
         tma_load_4d(smem_u32(smem + C::OFF_K + c * C::PANEL), &tmK, kv_full, c * 64, k0, h, b);
         tma_load_4d(smem_u32(smem + C::OFF_V + c * C::PANEL), &tmV, kv_full, c * 64, k0, h, b);
       }
@@ -985,7 +989,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (mbar_try_wait(&q_empty[s], ((uint32_t)(qi >> 1) & 1u) ^ 1u)) {
             mbar_expect_tx(&q_full[s], C::TILE_BYTES);
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < PANELS; ++c)
               tma_load_4d(smem_u32(smem + C::OFF_Q + s * C::TILE_BYTES + c * C::PANEL), &tmQ, &q_full[s], c * 64, (i0 + qi) * BQ, h, b);
             ++qi;
             progress = true;
@@ -995,7 +999,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (mbar_try_wait(do_empty, ((uint32_t)di & 1u) ^ 1u)) {
             mbar_expect_tx(do_full, C::TILE_BYTES);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_4d(smem_u32(smem + C::OFF_DO + c * C::PANEL), &tmDO, do_full, c * 64, (i0 + di) * BQ, h, b);
+            for (int c = 0; c < PANELS; ++c) tma_load_4d(smem_u32(smem + C::OFF_DO + c * C::PANEL), &tmDO, do_full, c * 64, (i0 + di) * BQ, h, b);
             ++di;
             progress = true;
           }
@@ -1076,9 +1080,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         {
           const uint32_t d = tmem_base + (uint32_t)C::TMEM_DPQ;
-          tc_mma_bf16<false>(d, dK_mmaj, dDS_kmaj, C::IDESC_DQT);
+          if constexpr (D == 128) {   // transposed: lanes = head-dim index
+            tc_mma_bf16<false>(d, dK_mmaj, dDS_kmaj, C::IDESC_DQT);
 #pragma unroll
-          for (int ks = 1; ks < C::BK / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dK_mmaj, ks * 2048u), desc_advance(dDS_kmaj, koff(ks)), C::IDESC_DQT);
+            for (int ks = 1; ks < C::BK / 16; ++ks)
+              tc_mma_bf16<true>(d, desc_advance(dK_mmaj, ks * 2048u), desc_advance(dDS_kmaj, koff(ks)), C::IDESC_DQT);
+          } else {                    // dQ_it = dS K: lanes = query rows, 64 columns (a 64-row product would not fill the tensor core)
+            tc_mma_bf16<false>(d, dDS_kmaj, dK_mmaj, C::IDESC_DQ);
+#pragma unroll
+            for (int ks = 1; ks < C::BK / 16; ++ks)
+              tc_mma_bf16<true>(d, desc_advance(dDS_kmaj, koff(ks)), desc_advance(dK_mmaj, ks * 2048u), C::IDESC_DQ);
+          }
         }
         tc_commit(dq_full);
         // dK += dS^T Q_it
@@ -1213,17 +1225,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) {
       tc_fence_after();
       const int key = k0 + r;
-      bf16 *dkrow = p.dK + ((long long)b * p.Sk + key) * p.lddk + (long long)h * D + half * 64;
-      bf16 *dvrow = p.dV + ((long long)b * p.Sk + key) * p.lddv + (long long)h * D + half * 64;
+      constexpr int DH = D / 2;               // head-dim columns per thread
+      bf16 *dkrow = p.dK + ((long long)b * p.Sk + key) * p.lddk + (long long)h * D + half * DH;
+      bf16 *dvrow = p.dV + ((long long)b * p.Sk + key) * p.lddv + (long long)h * D + half * DH;
 #pragma unroll 1
       for (int w = 0; w < 2; ++w) {            // 0: dK (times the score scale), 1: dV (times 1 / keep_prob)
         const float f = w == 0 ? p.scale : inv_keep;
         bf16 *orow = w == 0 ? dkrow : dvrow;
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < DH / 32; ++c) {
           uint32_t rr[32];
           if (n_it > 0) {
-            tmem_ld32(lane_base + (uint32_t)((w == 0 ? C::TMEM_DK : C::TMEM_DV) + half * 64 + c * 32), rr);
+            tmem_ld32(lane_base + (uint32_t)((w == 0 ? C::TMEM_DK : C::TMEM_DV) + half * DH + c * 32), rr);
             tmem_ld_wait();
           } else {
 #pragma unroll
@@ -1243,35 +1256,52 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------------------------ read-out of dQ_it^T: thread = head-dim index x 64 queries
-    // Eight warps: TMEM lane quarter w % 4 (= 32 head-dim indices) and 64 of the block's 128 queries each.  A warp-wide add
-    // covers 32 consecutive floats of one query's row in the fp32 accumulator.
+    // ------------------------------------------------------------------ read-out of dQ_it
+    // Eight warps.  Head dim 128: dQ_it^T, thread = head-dim index (TMEM lane quarter w % 4) x 64 of the block's 128 queries; a
+    // warp-wide add covers 32 consecutive floats of one query's row in the fp32 accumulator.  Head dim 64: dQ_it, thread =
+    // query row x 32 of the 64 columns, added with 16-byte vector atomics.
     const int quarter = warp & 3;
     const int qhalf = (warp - 10) >> 2;
-    const int dcol = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    float *acc_base = p.dQ_acc + ((long long)(b * p.H + h) * p.Sq) * D + dcol;
+    float *acc_head = p.dQ_acc + ((long long)(b * p.H + h) * p.Sq) * D;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       ok = mbar_wait(dq_full, (uint32_t)it & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t ra[32], rb[32];
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64), ra);
-      tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64 + 32), rb);
-      tmem_ld_wait();
-      tc_fence_before();
-      warp_arrive(dq_empty, lane);
-      const int qb0 = (i0 + it) * BQ + qhalf * 64;
-      const int qn = p.Sq - qb0;               // queries of this half that exist
-      float *dst = acc_base + (long long)qb0 * D;
+      if constexpr (D == 128) {
+        const int dcol = quarter * 32 + lane;
+        uint32_t ra[32], rb[32];
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64), ra);
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 64 + 32), rb);
+        tmem_ld_wait();
+        tc_fence_before();
+        warp_arrive(dq_empty, lane);
+        const int qb0 = (i0 + it) * BQ + qhalf * 64;
+        const int qn = p.Sq - qb0;               // queries of this half that exist
+        float *dst = acc_head + (long long)qb0 * D + dcol;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < qn) atomicAdd(dst + i * D, __uint_as_float(ra[i]) * p.scale);
+        for (int i = 0; i < 32; ++i)
+          if (i < qn) atomicAdd(dst + i * D, __uint_as_float(ra[i]) * p.scale);
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (32 + i < qn) atomicAdd(dst + (32 + i) * D, __uint_as_float(rb[i]) * p.scale);
+        for (int i = 0; i < 32; ++i)
+          if (32 + i < qn) atomicAdd(dst + (32 + i) * D, __uint_as_float(rb[i]) * p.scale);
+      } else {
+        uint32_t ra[32];
+        tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 32), ra);
+        tmem_ld_wait();
+        tc_fence_before();
+        warp_arrive(dq_empty, lane);
+        const int q = (i0 + it) * BQ + quarter * 32 + lane;
+        if (q < p.Sq) {
+          float4 *dst = reinterpret_cast<float4 *>(acc_head + (long long)q * D + qhalf * 32);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            atomicAdd(dst + u, make_float4(__uint_as_float(ra[4 * u]) * p.scale, __uint_as_float(ra[4 * u + 1]) * p.scale,
+                                           __uint_as_float(ra[4 * u + 2]) * p.scale, __uint_as_float(ra[4 * u + 3]) * p.scale));
+        }
+      }
     }
   }
 
@@ -1355,7 +1385,7 @@ struct FfkAttnDesc {
 
 // 1 when the fused kernels cover this head dimension / direction
 FFK_API void ffk_attention_set_fwd_variant(int v) { g_fwd_variant = (v >= 1 && v <= 3) ? v : 1; }
-FFK_API int ffk_attention_supported(int D, int backward) { return backward ? (D == 128) : (D == 64 || D == 128); }
+FFK_API int ffk_attention_supported(int D, int backward) { (void)backward; return D == 64 || D == 128; }
 FFK_API long long ffk_attention_bwd_scratch_floats(int B, int H, int Sq, int D) { return 1ll * B * H * Sq * D; }
 
 FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
@@ -1405,21 +1435,15 @@ FFK_API int ffk_attention_fwd(const FfkAttnDesc *d, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
-FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
-  if (d->D != 128) return -2;
-  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Sk <= 0) return 0;
-  if (!aligned16(d->Q, d->ldq) || !aligned16(d->K, d->ldk) || !aligned16(d->V, d->ldv) || !aligned16(d->O, d->ldo) ||
-      !aligned16(d->dO, d->lddo) || !aligned16(d->dQ, d->lddq) || !aligned16(d->dK, d->lddk) || !aligned16(d->dV, d->lddv) ||
-      (((uintptr_t)d->acc) & 15))
-    return -2;
-  if (d->causal && d->Sq != d->Sk) return -2;
-  constexpr int D = 128;
+template <int D>
+static int launch_bwd(const FfkAttnDesc *d, AttnArgs &a, cudaStream_t stream) {
+  using C = BwdCfg<D>;
   CUtensorMap tq, tk, tv, tdo;
   int r;
   if ((r = make_head_map(&tq, d->Q, D, d->Sq, d->ldq, d->H, d->B, BQ))) return r;
   if ((r = make_head_map(&tdo, d->dO, D, d->Sq, d->lddo, d->H, d->B, BQ))) return r;
-  if ((r = make_head_map(&tk, d->K, D, d->Sk, d->ldk, d->H, d->B, BwdCfg::BK))) return r;
-  if ((r = make_head_map(&tv, d->V, D, d->Sk, d->ldv, d->H, d->B, BwdCfg::BK))) return r;
+  if ((r = make_head_map(&tk, d->K, D, d->Sk, d->ldk, d->H, d->B, C::BK))) return r;
+  if ((r = make_head_map(&tv, d->V, D, d->Sk, d->ldv, d->H, d->B, C::BK))) return r;
   const long long n_acc = (long long)d->B * d->H * d->Sq * D;
   cudaError_t e = cudaMemsetAsync(d->acc, 0, (size_t)n_acc * sizeof(float), stream);
   if (e != cudaSuccess) return (int)e;
@@ -1428,6 +1452,27 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
     attn_delta_kernel<D><<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>((const bf16 *)d->dO, d->lddo, (const bf16 *)d->O, d->ldo,
                                                                            (float *)d->delta, d->B, d->H, d->Sq);
   }
+  static bool attr = false;
+  if (!attr) {
+    e = cudaFuncSetAttribute(attn_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  const long long grid = (long long)((d->Sk + C::BK - 1) / C::BK) * d->H * d->B;
+  if (grid > 0x7fffffffll) return -2;
+  attn_bwd_kernel<D><<<(unsigned)grid, BWD_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  attn_acc_to_bf16_kernel<D><<<ffk_blocks(n_acc / 4, 256), 256, 0, stream>>>(a.dQ_acc, (bf16 *)d->dQ, d->lddq, d->B, d->H, d->Sq);
+  return (int)cudaGetLastError();
+}
+
+FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
+  if (d->D != 128 && d->D != 64) return -2;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Sk <= 0) return 0;
+  if (!aligned16(d->Q, d->ldq) || !aligned16(d->K, d->ldk) || !aligned16(d->V, d->ldv) || !aligned16(d->O, d->ldo) ||
+      !aligned16(d->dO, d->lddo) || !aligned16(d->dQ, d->lddq) || !aligned16(d->dK, d->lddk) || !aligned16(d->dV, d->lddv) ||
+      (((uintptr_t)d->acc) & 15))
+    return -2;
+  if (d->causal && d->Sq != d->Sk) return -2;
   AttnArgs a = {};
   a.B = d->B; a.H = d->H; a.Sq = d->Sq; a.Sk = d->Sk; a.scale = d->scale; a.causal = d->causal;
   a.drop_p = d->drop_p; a.drop_salt = d->drop_salt; a.drop_seed_ptr = (const unsigned long long *)d->drop_seed_ptr;
@@ -1437,17 +1482,7 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
-  static bool attr = false;
-  if (!attr) {
-    e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    attr = true;
-  }
-  const long long grid = (long long)((d->Sk + BwdCfg::BK - 1) / BwdCfg::BK) * d->H * d->B;
-  if (grid > 0x7fffffffll) return -2;
-  attn_bwd_kernel<<<(unsigned)grid, BWD_THREADS, BwdCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
-  attn_acc_to_bf16_kernel<D><<<ffk_blocks(n_acc / 4, 256), 256, 0, stream>>>(a.dQ_acc, (bf16 *)d->dQ, d->lddq, d->B, d->H, d->Sq);
-  return (int)cudaGetLastError();
+  return d->D == 128 ? launch_bwd<128>(d, a, stream) : launch_bwd<64>(d, a, stream);
 }
 
 // Copies out the timeline recorded under experiment switch 4096: 32 events x 64 steps of SM clock values (0 = not reached).

@@ -147,6 +147,41 @@ def bench_im2col(a):
     return {"op": "im2col_3x3_bf16", "n": n, "c": c, "hw": h, **roofline(ms, hbm_bytes=2.0 * (x.numel() + col.numel()))}
 
 
+def bench_conv(a):
+    """Implicit-GEMM convolution (forward, data gradient, weight gradient) on channels-last bf16 data: --batch, --channels
+    (input), --n (output channels), --size (height = width), --k (square filter, stride 1, "same" padding).  --compare also
+    times torch's convolution (cuDNN, channels-last) forward and its two gradients."""
+    n, c, h, w, oc, kk = a.batch, a.channels, a.size, a.size, a.n, a.k
+    pad = kk // 2
+    x = torch.randn(n, h, w, c, device="cuda").to(torch.bfloat16)
+    wt = (torch.randn(oc, c, kk, kk, device="cuda") / (c * kk * kk) ** 0.5).to(torch.bfloat16)
+    g = K.ConvGeometry(n, c, h, w, kk, kk, 1, 1, pad, pad, K.nhwc_strides(n, c, h, w))
+    wp = torch.empty(oc, g.kp, device="cuda", dtype=torch.bfloat16)
+    K.filter_pack(wt, wp, oc, c, kk, kk, g.kp)
+    y = torch.empty(n, g.oh, g.ow, oc, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn_like(y)
+    dx = torch.empty_like(x)
+    dwp = torch.empty(oc, g.kp, device="cuda", dtype=torch.float32)
+    flops = 2.0 * n * g.oh * g.ow * oc * c * kk * kk
+    act_bytes = 2.0 * (x.numel() + y.numel())
+    res = {"op": "conv2d_implicit_bf16", "n": n, "c": c, "hw": h, "oc": oc, "k": kk}
+    res["fprop"] = roofline(_time(lambda: K.conv_fprop(x, wp, y, g, oc), a.warmup, a.iters, a.flush), flops=flops, hbm_bytes=act_bytes)
+    res["dgrad"] = roofline(_time(lambda: K.conv_dgrad(dy, wp, dx, g, oc), a.warmup, a.iters, a.flush), flops=flops, hbm_bytes=act_bytes)
+    res["wgrad"] = roofline(_time(lambda: K.conv_wgrad(x, dy, dwp, g, oc), a.warmup, a.iters, a.flush), flops=flops, hbm_bytes=act_bytes)
+    if a.compare:
+        import torch.nn.functional as F
+        xt = x.permute(0, 3, 1, 2).requires_grad_(True)          # NCHW view of channels-last storage
+        wl = wt.contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        fwd = lambda: F.conv2d(xt, wl, None, padding=pad)         # noqa: E731
+        res["torch_fprop_ms"] = _time(fwd, a.warmup, a.iters, a.flush)
+        yt = fwd()
+        dyt = dy.permute(0, 3, 1, 2)
+        res["torch_dgrad_ms"] = _time(lambda: torch.autograd.grad(yt, xt, dyt, retain_graph=True), a.warmup, a.iters, a.flush)
+        res["torch_wgrad_ms"] = _time(lambda: torch.autograd.grad(yt, wl, dyt, retain_graph=True), a.warmup, a.iters, a.flush)
+    res["conv_error"] = K.conv_last_error()
+    return res
+
+
 def bench_attention(a):
     """Fused attention forward and backward on a packed QKV buffer: --batch, --heads, --seq, --head-dim, --dropout, --causal.
     FLOPs counted: 4 B H Sq Sk D forward, 10 B H Sq Sk D backward (halved when causal).  --compare also times the
@@ -186,7 +221,7 @@ def bench_attention(a):
 
 
 OPS = {"attention": bench_attention, "gemm": bench_gemm, "layernorm": bench_layernorm, "layernorm_bwd": bench_layernorm_bwd, "softmax": bench_softmax, "batchnorm": bench_batchnorm,
-       "im2col": bench_im2col}
+       "im2col": bench_im2col, "conv": bench_conv}
 
 
 def main(argv=None):
