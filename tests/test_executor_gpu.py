@@ -232,7 +232,7 @@ def test_blocked_attention_core_matches_oracle(block_bytes):
     """The L2-blocked attention core (blocks of batch elements, or of head groups of one batch element, with the
     probabilities recomputed in backward) computes the same loss and gradients as the whole-batch core."""
     g = core.build_model("transformer_lm", SMALL_LM)
-    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=3, attention_block_bytes=block_bytes))
+    ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=3, attention_block_bytes=block_bytes, fused_attention=False))
     att = [op for op in ex.ops.values() if op.type == "MULTIHEAD_ATTENTION"][0]
     assert (att.cb > 0) == (block_bytes > 0)
     if block_bytes == 8192:
@@ -260,7 +260,7 @@ def test_blocked_attention_with_dropout_is_consistent_between_forward_and_backwa
     out = []
     for use_graph in (False, True):
         g = core.build_model("transformer_lm", cfg)
-        ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, use_cuda_graph=use_graph, attention_block_bytes=16384,
+        ex = Executable(g, ExecConfig(compute_dtype="bf16", seed=5, use_cuda_graph=use_graph, attention_block_bytes=16384, fused_attention=False,
                                       optimizer=OptimizerConfig(kind="adam", lr=1e-3)))
         ls = []
         for _ in range(6):
