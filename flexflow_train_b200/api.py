@@ -17,41 +17,7 @@ from . import _ffcore as core
 from .runtime.executor import ExecConfig, Executable, OptimizerConfig
 
 
-@dataclass
-class FFConfig:
-    """Run configuration; field names follow the reference's FFConfig / CLI flags (README.md:58-81)."""
-    epochs: int = 1
-    batch_size: int = 64
-    num_nodes: int = 1
-    gpus_per_node: int = 0  # 0 = use WORLD_SIZE / visible devices
-    learning_rate: float = 0.01
-    weight_decay: float = 0.0001
-    workspace_size: int = 1 << 30
-    enable_profiling: bool = False
-    search_budget: int = 0
-    search_alpha: float = 1.05
-    search_time_limit_s: float = 60.0   # wall-clock bound of the Unity search (it also stops when the budget is used up)
-    search_start: str = "best_template"  # or "serial": begin the search at the unparallelised graph
-    search_algorithm: str = "unity"  # "unity" | "mcmc" | "data_parallel" | "tensor_parallel" | "table_parallel"
-    only_data_parallel: bool = False
-    enable_parameter_parallel: bool = True
-    enable_attribute_parallel: bool = True
-    score_hybrid_strategies: bool = False  # also estimate data x tensor parallel meshes (reported, not executed)
-    substitution_json_path: Optional[str] = None
-    export_strategy_file: Optional[str] = None
-    import_strategy_file: Optional[str] = None
-    export_strategy_computation_graph_file: Optional[str] = None
-    compute_dtype: str = "bf16"
-    use_cuda_graph: bool = True
-    fuse_collectives: bool = True  # run all-gather / reduce-scatter inside the neighbouring GEMMs (else NCCL)
-    shard_inputs: bool = True      # several ranks: an input split over the sample dim may be fed as each rank's own piece
-    # Search on measured operator costs (the reference's LocalCostEstimator): rank 0 profiles one step of the model on its
-    # GPU at every per-device batch a data-parallel degree of this machine would give, the table is sent to all ranks,
-    # and the estimator answers from it (analytic model for shapes that were not seen).  `cost_table_file` is the disk
-    # cache: read when it exists, written after a measurement.
-    measure_costs: bool = False
-    cost_table_file: Optional[str] = None
-    seed: int = 0
+from .config_schema import FFConfig  # noqa: E402  (the dataclass is generated from the one field table)
 
 
 class CompiledModel:

@@ -23,6 +23,7 @@ import torch
 
 from .. import _ffcore as core
 from .. import api
+from .. import config_schema as schema
 from ..runtime.executor import OptimizerConfig
 from ..utils import checkpoint as ckpt
 from ..utils.metrics import StepLogger
@@ -90,33 +91,20 @@ def main(argv=None) -> int:
     p.add_argument("--device", choices=["cuda", "cpu"], default=None, help="cpu: host executor (fp32); default: the GPU")
     p.add_argument("--model", default="transformer", choices=sorted(core.model_names()))
     p.add_argument("--model-config", help="JSON object overriding fields of the model's default config")
-    p.add_argument("-e", "--epochs", type=int, default=1)
-    p.add_argument("-b", "--batch-size", type=int, default=None)
     p.add_argument("-p", "--print-freq", type=int, default=10)
     p.add_argument("-d", "--dataset", default=None, help="ignored: data is synthetic")
     p.add_argument("--iterations", type=int, default=None, help="steps per epoch (default 20; 5 for a graph file)")
-    p.add_argument("--learning-rate", type=float, default=1e-3)
     p.add_argument("--optimizer", choices=["sgd", "adam"], default=None, help="default adam; sgd with momentum 0.9 for a graph file")
-    p.add_argument("--search-budget", type=int, default=0)
-    p.add_argument("--search-alpha", type=float, default=1.05)
-    p.add_argument("--search-time-limit", type=float, default=60.0, help="wall-clock bound of the strategy search in seconds")
-    p.add_argument("--measure-costs", action="store_true", help="search on operator costs measured on this GPU")
-    p.add_argument("--cost-table", help="file of measured operator costs: read when present, written after measuring")
-    p.add_argument("--search-algorithm", choices=["unity", "mcmc", "data_parallel", "tensor_parallel", "table_parallel"], default="unity")
-    p.add_argument("--only-data-parallel", action="store_true")
-    p.add_argument("--enable-parameter-parallel", action="store_true")
-    p.add_argument("--enable-attribute-parallel", action="store_true")
-    p.add_argument("--export-strategy", dest="export_strategy")
-    p.add_argument("--import-strategy", dest="import_strategy")
-    p.add_argument("--substitution-json", dest="substitution_json")
-    p.add_argument("--compute-dtype", choices=["bf16", "fp32"], default="bf16")
-    p.add_argument("--no-cuda-graph", action="store_true")
+    # every FFConfig field that has a flag (epochs, batch size, the search and strategy options, dtype, seed ...) comes from
+    # the one field table
+    schema.add_cli_arguments(p, skip=("batch_size", "enable_profiling", "learning_rate"))
+    p.add_argument("-b", "--batch-size", type=int, default=None, help="global batch size (default: the model's own)")
+    p.add_argument("--learning-rate", type=float, default=1e-3)
     p.add_argument("--profiling", action="store_true", help="print a per-operator time table after training")
     p.add_argument("--checkpoint-dir")
     p.add_argument("--checkpoint-every", type=int, default=0)
     p.add_argument("--resume", action="store_true")
     p.add_argument("--log-file")
-    p.add_argument("--seed", type=int, default=0)
     a = p.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -145,13 +133,8 @@ def main(argv=None) -> int:
     if a.batch_size:
         mcfg["batch_size"] = a.batch_size
     loss = "mean_squared_error_avg_reduce" if a.model in REGRESSION_MODELS else "sparse_categorical_crossentropy"
-    cfg = api.FFConfig(epochs=a.epochs, batch_size=mcfg.get("batch_size", 64), learning_rate=a.learning_rate, search_budget=a.search_budget,
-                       search_alpha=a.search_alpha, search_algorithm="data_parallel" if a.only_data_parallel else a.search_algorithm,
-                       only_data_parallel=a.only_data_parallel, enable_parameter_parallel=a.enable_parameter_parallel,
-                       enable_attribute_parallel=a.enable_attribute_parallel, substitution_json_path=a.substitution_json,
-                       export_strategy_file=a.export_strategy, import_strategy_file=a.import_strategy, compute_dtype=a.compute_dtype,
-                       use_cuda_graph=not a.no_cuda_graph, seed=a.seed, search_time_limit_s=a.search_time_limit,
-                       measure_costs=a.measure_costs, cost_table_file=a.cost_table)
+    cfg = schema.config_from_args(a, batch_size=mcfg.get("batch_size", 64), enable_profiling=False, learning_rate=a.learning_rate,
+                                  search_algorithm="data_parallel" if a.only_data_parallel else a.search_algorithm)
     model = a.model
     if a.graph_json:
         with open(a.graph_json) as f:

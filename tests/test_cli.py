@@ -195,3 +195,30 @@ def test_bench_contract_pieces_that_need_no_gpu():
     s.start()
     out = s.stop()
     assert "sm_mhz" in out and "reasons" in out
+
+
+def test_config_fields_flags_and_docs_come_from_one_table():
+    """FFConfig, the tools' flags and the field documentation are generated from config_schema.FIELDS."""
+    import argparse
+    import dataclasses
+
+    from flexflow_train_b200 import api, config_schema as cs
+    assert api.FFConfig is cs.FFConfig
+    names = [f.name for f in dataclasses.fields(cs.FFConfig)]
+    assert names == [f.name for f in cs.FIELDS] and len(set(names)) == len(names)
+    cfg = cs.FFConfig()
+    for f in cs.FIELDS:
+        assert getattr(cfg, f.name) == f.default
+    p = argparse.ArgumentParser()
+    cs.add_cli_arguments(p)
+    flags = {a.dest for a in p._actions}
+    assert {f.name for f in cs.FIELDS if f.flag} <= flags
+    ns = p.parse_args(["--search-budget", "7", "--no-cuda-graph", "--export-strategy", "s.json", "-e", "3", "--measure-costs"])
+    c = cs.config_from_args(ns, seed=5)
+    assert (c.search_budget, c.use_cuda_graph, c.export_strategy_file, c.epochs, c.measure_costs, c.seed) == (7, False, "s.json", 3, True, 5)
+    # the reference's opt-in switches: off on the command line unless given, on for library users
+    assert c.enable_parameter_parallel is False and cs.FFConfig().enable_parameter_parallel is True
+    table = cs.describe()
+    assert all(f"`{f.name}`" in table for f in cs.FIELDS)
+    with __import__("pytest").raises(SystemExit):
+        p.parse_args(["--compute-dtype", "fp8"])
