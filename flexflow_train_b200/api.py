@@ -87,13 +87,26 @@ def _search_estimator(model, model_config, cg, world: int, config: "FFConfig", d
     """The cost estimator the strategy search runs on: analytic, or filled with measured operator costs when the config
     asks for them (local_cost_estimator.cc:84-179 measures per query; here one profiled step per candidate shard size
     fills the table up front).  Returns (estimator or None, info for the search statistics)."""
-    if not (config.measure_costs or config.cost_table_file):
+    if not (config.measure_costs or config.cost_table_file or config.cost_params_file):
         return None, None
+    import json
     import os
 
     from .compiler.strategy import machine_for
     from .runtime import cost_measure
-    est = core.CostEstimator(machine_for(world))
+    params = None
+    if config.cost_params_file:
+        # overrides of the analytic model's constants, merged over the defaults
+        with open(config.cost_params_file) as f:
+            overrides = json.load(f)
+        params = core.CostEstimator(machine_for(world)).params()
+        table = dict(params.get("measured_gbs", {}))
+        table.update(overrides.pop("measured_gbs", {}))
+        params.update(overrides)
+        params["measured_gbs"] = table
+    est = core.CostEstimator(machine_for(world), params)
+    if not (config.measure_costs or config.cost_table_file):
+        return est, {"source": "analytic", "cost_params": config.cost_params_file, "entries": 0}
     path = config.cost_table_file
     if path and os.path.exists(path):
         return est, {"source": path, "entries": cost_measure.load_table(est, path)}

@@ -51,6 +51,8 @@ FIELDS: List[Field] = [
     Field("shard_inputs", bool, True, "several ranks: an input cut over the sample dim may be fed as each rank's own piece"),
     Field("measure_costs", bool, False, "search on operator costs measured on this GPU (rank 0 measures, all ranks get the table)", "--measure-costs"),
     Field("cost_table_file", Optional[str], None, "measured operator costs: read when the file exists, written after measuring", "--cost-table"),
+    Field("cost_params_file", Optional[str], None, "JSON overrides of the analytic cost model, e.g. the measured_gbs table that "
+          "parallel.bench_fused --write-cost-params produces", "--cost-params"),
     Field("seed", int, 0, "seed of initializers, dropout and the search", "--seed"),
 ]
 

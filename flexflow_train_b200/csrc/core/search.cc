@@ -19,7 +19,24 @@ Json CostParams::to_json() const {
   j["nvlink_gbs"] = nvlink_gbs; j["allreduce_bus_gbs"] = allreduce_bus_gbs; j["launch_us"] = launch_us;
   j["collective_latency_us"] = collective_latency_us; j["inter_node_gbs"] = inter_node_gbs;
   j["fused_overlap"] = fused_overlap; j["bytes_per_float"] = bytes_per_float;
+  Json mg = Json::object();
+  for (auto &kv : measured_gbs) mg[kv.first] = kv.second;
+  j["measured_gbs"] = mg;
   return j;
+}
+double CostParams::collective_gbs(const std::string &kind, int group, double nominal) const {
+  double best = nominal;
+  int best_size = 0;
+  for (auto &kv : measured_gbs) {
+    auto at = kv.first.find('@');
+    if (at == std::string::npos || kv.first.compare(0, at, kind) != 0) continue;
+    int size = std::atoi(kv.first.c_str() + at + 1);
+    if (size <= group && size > best_size) {
+      best_size = size;
+      best = kv.second;
+    }
+  }
+  return best;
 }
 CostParams CostParams::from_json(const Json &j) {
   CostParams p;
@@ -33,6 +50,10 @@ CostParams CostParams::from_json(const Json &j) {
   p.inter_node_gbs = j.get_float("inter_node_gbs", p.inter_node_gbs);
   p.fused_overlap = j.get_float("fused_overlap", p.fused_overlap);
   p.bytes_per_float = (int)j.get_int("bytes_per_float", p.bytes_per_float);
+  if (j.contains("measured_gbs")) {
+    p.measured_gbs.clear();
+    for (auto &kv : j.at("measured_gbs").fields()) p.measured_gbs[kv.first] = kv.second.as_float();
+  }
   return p;
 }
 
@@ -139,13 +160,13 @@ OpCost CostEstimator::op_cost(const Node &n, const Graph &g) const {
       int k = (int)n.attrs.at("repartition_degree").as_int();
       // forward: every rank keeps its slice of data it already holds; backward: all-gather of the gradient
       c.fwd_ms = launch;
-      c.bwd_ms = coll_lat + in_bytes * (k - 1.0) / k / (p.nvlink_gbs * 1e6);
+      c.bwd_ms = coll_lat + in_bytes * (k - 1.0) / k / (p.collective_gbs("allgather", k, p.nvlink_gbs) * 1e6);
       c.memory_bytes = out_bytes;
       return c;
     }
     case OpType::COMBINE: {
       int k = (int)n.attrs.at("combine_degree").as_int();
-      c.fwd_ms = coll_lat + out_bytes * (k - 1.0) / k / (p.nvlink_gbs * 1e6);
+      c.fwd_ms = coll_lat + out_bytes * (k - 1.0) / k / (p.collective_gbs("allgather", k, p.nvlink_gbs) * 1e6);
       c.bwd_ms = launch;
       return c;
     }
@@ -153,7 +174,7 @@ OpCost CostEstimator::op_cost(const Node &n, const Graph &g) const {
       int k = (int)n.attrs.at("replicate_degree").as_int();
       // forward is free in SPMD execution (the tensor already lives on every rank); backward sums the
       // replicas' gradients: an all-reduce, overlapped with the rest of backward when it is a weight gradient
-      double ar = coll_lat + 2.0 * in_bytes * (k - 1.0) / k / (p.allreduce_bus_gbs * 1e6);
+      double ar = coll_lat + 2.0 * in_bytes * (k - 1.0) / k / (p.collective_gbs("allreduce", k, p.allreduce_bus_gbs) * 1e6);
       bool weight_grad = g.node(n.inputs[0].src.node).type == OpType::WEIGHT ||
                          (is_parallel_op(g.node(n.inputs[0].src.node).type) && !g.node(n.inputs[0].src.node).inputs.empty() &&
                           g.node(g.node(n.inputs[0].src.node).inputs[0].src.node).type == OpType::WEIGHT);
@@ -164,7 +185,7 @@ OpCost CostEstimator::op_cost(const Node &n, const Graph &g) const {
     }
     case OpType::REDUCTION: {
       int k = (int)n.attrs.at("reduction_degree").as_int();
-      double ar = coll_lat + 2.0 * out_bytes * (k - 1.0) / k / (p.allreduce_bus_gbs * 1e6);
+      double ar = coll_lat + 2.0 * out_bytes * (k - 1.0) / k / (p.collective_gbs("allreduce", k, p.allreduce_bus_gbs) * 1e6);
       // fused with the producing GEMM (GEMM -> reduce-scatter kernel) most of the transfer hides under the math
       const Node &prod = g.node(n.inputs[0].src.node);
       bool fused = prod.type == OpType::LINEAR || prod.type == OpType::BATCHMATMUL || prod.type == OpType::MULTIHEAD_ATTENTION;

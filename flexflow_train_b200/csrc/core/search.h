@@ -39,6 +39,13 @@ struct CostParams {
   double inter_node_gbs = 25.0;
   double fused_overlap = 0.85;      // fraction of a collective hidden when it is fused with its GEMM
   int bytes_per_float = 2;          // activations/weights are bf16 at run time
+  // Achieved bandwidth (GB/s, in the units the formulas use: bus bandwidth for an all-reduce, bytes received or sent per
+  // rank for an all-gather / reduce-scatter) of this library's collective kernels as measured on this machine, by kind and
+  // group size: "allreduce@8" -> 513.  A collective of a size that was not measured takes the entry of the nearest smaller
+  // measured size, else the nominal figures above.  The defaults are the 2- and 8-GPU measurements of the peer-memory
+  // kernels (gradient all-reduce, all-gather into a GEMM, GEMM into reduce-scatter).
+  std::map<std::string, double> measured_gbs = {{"allreduce@2", 457.0}, {"allreduce@8", 513.0}, {"allgather@8", 342.0}, {"reducescatter@8", 172.0}};
+  double collective_gbs(const std::string &kind, int group, double nominal) const;
   Json to_json() const;
   static CostParams from_json(const Json &);
 };

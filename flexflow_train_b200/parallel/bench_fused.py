@@ -56,6 +56,9 @@ def main(argv=None):
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--only", default="f1,f2,f3,f4")
+    p.add_argument("--write-cost-params", metavar="FILE",
+                   help="merge the bandwidths measured here into FILE as the cost model's measured_gbs table (key kind@world): the "
+                        "search reads it through FFConfig.cost_params_file")
     p.add_argument("--no-scatter-tma", action="store_true", help="F1: per-lane stores into the peers' stages instead of TMA stores")
     a = p.parse_args(argv)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
@@ -68,6 +71,8 @@ def main(argv=None):
         from ..ops import kernels as K
         K.lib().ffk_gemm_set_scatter_tma_store(0)
     es = 2
+
+    measured = {}   # collective kind -> achieved GB/s at this world size, in the units of the cost model
 
     def emit(d):
         ctx.check_status()
@@ -88,6 +93,8 @@ def main(argv=None):
             dist.reduce_scatter_tensor(out, full)
         ms_lib = _timed(lib, a.warmup, a.iters)
         r = roofline(ms, flops=2.0 * rows * n * k, nvlink_bytes=(W - 1) / W * rows * n * es, sustained=True)
+        if r["nvlink_gbs"] > 0 and r["bound"] != "compute":   # a compute-bound run says nothing about the link
+            measured["reducescatter"] = r["nvlink_gbs"]
         emit({"kernel": "F1 gemm->reduce_scatter", "world": W, "rows": rows, "n": n, "k_local": k, "library_ms": ms_lib,
               "speedup_vs_library": ms_lib / ms, **r})
         del op, full
@@ -106,6 +113,8 @@ def main(argv=None):
             torch.matmul(gathered, w.t(), out=out)
         ms_lib = _timed(lib, a.warmup, a.iters)
         r = roofline(ms, flops=2.0 * a.rows * n * k, nvlink_bytes=(W - 1) * rows_local * k * es, sustained=True)
+        if r["nvlink_gbs"] > 0 and r["bound"] != "compute":
+            measured["allgather"] = r["nvlink_gbs"]
         emit({"kernel": "F2 all_gather->gemm", "world": W, "rows": a.rows, "n_local": n, "k": k, "library_ms": ms_lib,
               "speedup_vs_library": ms_lib / ms, **r})
         del op, gathered
@@ -123,6 +132,8 @@ def main(argv=None):
         ms_lib = _timed(lib, a.warmup, a.iters)
         sent = 2.0 * (W - 1) / W * n * es
         r = roofline(ms, hbm_bytes=3.0 * n * es, nvlink_bytes=sent)
+        if W > 1:
+            measured["allreduce"] = sent / ms / 1e6
         emit({"kernel": "F3 grad all_reduce+scale", "world": W, "elements": n, "library_ms": ms_lib, "speedup_vs_library": ms_lib / ms,
               "bus_gbs": sent / ms / 1e6, **r})
         del ar, t
@@ -141,6 +152,16 @@ def main(argv=None):
         emit({"kernel": "F4 all_to_all+embedding fwd", "world": W, "tables": T, "batch": a.batch, "dim": dim, **rf})
         emit({"kernel": "F4 all_to_all+embedding sparse-SGD bwd", "world": W, "tables": T, "batch": a.batch, "dim": dim, **rb})
 
+    if a.write_cost_params and rank == 0 and W > 1:
+        doc = {}
+        if os.path.exists(a.write_cost_params):
+            with open(a.write_cost_params) as f:
+                doc = json.load(f)
+        table = doc.setdefault("measured_gbs", {})
+        for kind, gbs in measured.items():
+            table[f"{kind}@{W}"] = round(gbs, 1)
+        with open(a.write_cost_params, "w") as f:
+            json.dump(doc, f, indent=1)
     dist.destroy_process_group()
 
 

@@ -346,3 +346,41 @@ def test_strided_machine_views_interleave_inside_a_node():
         assert len(set(d)) == 4 and all(0 <= x < 8 for x in d)
     # a strided view round-trips through the strategy file format like any other
     assert c.allowed_machine_views([4], 0, 8, ms) == views[:2]
+
+
+def test_measured_collective_bandwidths_price_the_parallel_operators():
+    """The cost of a collective comes from the bandwidth measured for its kind at (the nearest smaller measured) group size;
+    kinds and sizes that were not measured keep the nominal NVLink figures."""
+    ms = S.machine_for(8)
+    base = c.CostEstimator(ms).params()
+    assert base["measured_gbs"]["allreduce@8"] == 513.0 and base["measured_gbs"]["reducescatter@8"] == 172.0
+    b = c.GraphBuilder(True)
+    x = b.create_input([64, 4096], "FLOAT", False, "x")
+    r = b.parallel_replicate(x, 8)
+    y = b.parallel_partition(x, 0, 4)
+    g = b.graph
+    rep = [n["id"] for n in g.nodes() if n["type"] == "REPLICATE"][0]
+    part = [n["id"] for n in g.nodes() if n["type"] == "REPARTITION"][0]
+    slow = c.CostEstimator(ms, dict(base, measured_gbs={"allreduce@8": 51.3, "allgather@2": 77.0}))
+    fast = c.CostEstimator(ms, dict(base, measured_gbs={}))
+    lat = base["collective_latency_us"] / 1000.0
+    t_meas, t_slow, t_nom = (e.op_cost(g, rep)["bwd_ms"] - lat for e in (c.CostEstimator(ms), slow, fast))
+    assert abs(t_slow / t_meas - 10.0) < 1e-6                      # a tenth of the bandwidth, ten times the transfer time
+    assert abs(t_nom / t_meas - 513.0 / base["allreduce_bus_gbs"]) < 1e-6
+    # a 4-way all-gather: priced with the 2-way measurement when that is the nearest smaller one, nominal otherwise
+    g4_slow, g4_nom = (e.op_cost(g, part)["bwd_ms"] - lat for e in (slow, fast))
+    assert abs(g4_slow / g4_nom - base["nvlink_gbs"] / 77.0) < 1e-6
+
+
+def test_cost_params_file_overrides_the_analytic_model(tmp_path):
+    import json
+
+    from flexflow_train_b200.api import FFConfig, _search_estimator
+    from flexflow_train_b200.runtime.executor import ExecConfig
+    path = tmp_path / "params.json"
+    path.write_text(json.dumps({"measured_gbs": {"allreduce@4": 333.0}, "launch_us": 9.0}))
+    cg = c.build_model("mlp", {"batch_size": 8})
+    est, info = _search_estimator("mlp", None, cg, 4, FFConfig(cost_params_file=str(path)), None, ExecConfig())
+    p = est.params()
+    assert p["launch_us"] == 9.0 and p["measured_gbs"]["allreduce@4"] == 333.0 and p["measured_gbs"]["allreduce@8"] == 513.0
+    assert info["source"] == "analytic" and info["cost_params"] == str(path)
