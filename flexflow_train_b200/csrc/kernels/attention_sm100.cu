@@ -625,8 +625,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         bool k_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j < n_t[t]) {
+            attn_trace(p, 20 + 4 * t, j);
             ok = mbar_wait(&p_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
             if (!ok) break;
+            attn_trace(p, 21 + 4 * t, j);
             tc_fence_after();
             const uint32_t d = tmem_base + (uint32_t)(C::TMEM_O + t * D);
             if constexpr (P_TMEM) {
@@ -646,6 +648,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               }
             }
             tc_commit(&pv_done[t]);
+            attn_trace(p, 22 + 4 * t, j);
           }
           if (j + 1 < n_t[t]) {
             if (!k_ready) {
@@ -655,6 +658,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               k_ready = true;
             }
             issue_s(t, j + 1);
+            attn_trace(p, 23 + 4 * t, j);
           }
         }
         if (!ok) break;
@@ -686,14 +690,18 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
     for (int j = 0; j < n_mine && ok; ++j) {
       const uint32_t ph = (uint32_t)j & 1u;
+      const bool tr = warp == 2 || warp == 10;
+      const int te = t * 6;
       ok = mbar_wait(&s_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (tr) attn_trace(p, te + 0, j);
       tc_fence_after();
       uint32_t rs[64];
       tmem_ld32(t_s + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
       tmem_ld32(t_s + (uint32_t)(half * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
       tmem_ld_wait();
+      if (tr) attn_trace(p, te + 1, j);
       const int k0 = j * BKF + half * 64;
       int kmax = p.Sk - k0;
       if (p.causal) kmax = min(kmax, q - k0 + 1);
@@ -711,6 +719,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       *my_x = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // both halves hold their scores in registers from here on
+      if (tr) attn_trace(p, te + 2, j);
       const float m_row = fmaxf(*my_x, *other_x) * sl2;
       bool need = false;
       if (j == 0) m_ref = m_row == -INFINITY ? 0.f : m_row;
@@ -761,6 +770,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         rs[(i >> 1) + 1] = pack_bf162(e2, e3);
       }
       l += (ls0 + ls1) + (ls2 + ls3);
+      if (tr) attn_trace(p, te + 3, j);
       if constexpr (P_TMEM) {
         // 64 probabilities = 32 columns of bf16 pairs at the start of S_t (this half's own scores or the other half's,
         // all of which are in registers since the barrier above)
@@ -782,6 +792,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before();   // orders the tensor-memory traffic of a rescale before the arrival
       }
       warp_arrive(&p_full[t], lane);
+      if (tr) attn_trace(p, te + 4, j);
     }
     if (ok && n_mine > 0) {
       ok = mbar_wait(&pv_done[t], (uint32_t)(n_mine - 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
