@@ -725,6 +725,7 @@ def _decl_tensor_ops(l):
         "ffk_topk": [P, P, P, I, I, I, I, S],
         "ffk_topk_bwd": [P, P, P, I, I, I, I, I, S],
         "ffk_reverse": [P, P, L, L, L, I, S],
+        "ffk_load_rows": [P, P, P, L, L, L, L, S],
     }
     for name, args in sig.items():
         fn = getattr(l, name)
@@ -801,6 +802,25 @@ def reduce_select_bwd(x, y, dy, dx, outer, red, inner, op, accumulate=False):
     _cuda_contig(x, y, dy, dx)
     _check(_tlib().ffk_reduce_select_bwd(x.data_ptr(), y.data_ptr(), dy.data_ptr(), dx.data_ptr(), outer, red, inner, REDUCE_OPS[op],
                                          _dt(x), int(accumulate), _stream()), "ffk_reduce_select_bwd")
+
+
+def load_rows(dataset, out, indices=None, first=0):
+    """out[i] = dataset[indices[i]] (or dataset[first + i] without indices).  `dataset` is a contiguous [num_samples, ...]
+    tensor in page-locked host memory (read by the GPU in place) or on the device; `indices` an int64 device tensor."""
+    if not (dataset.is_contiguous() and out.is_contiguous() and out.is_cuda):
+        raise KernelError("load_rows: contiguous data set and a contiguous device batch expected")
+    if not (dataset.is_cuda or dataset.is_pinned()):
+        raise KernelError("load_rows: the data set must be in page-locked host memory (tensor.pin_memory()) or on the device")
+    n = out.shape[0]
+    row_bytes = (dataset.numel() // max(dataset.shape[0], 1)) * dataset.element_size()
+    if out.numel() * out.element_size() != n * row_bytes or out.dtype != dataset.dtype:
+        raise KernelError("load_rows: batch rows do not match the data set's rows")
+    if indices is not None:
+        if indices.dtype != torch.int64 or not indices.is_cuda or indices.numel() < n:
+            raise KernelError("load_rows: indices must be an int64 device tensor with one entry per batch row")
+    _check(_tlib().ffk_load_rows(dataset.data_ptr(), None if indices is None else indices.data_ptr(), out.data_ptr(), n, row_bytes, int(first),
+                                 dataset.shape[0], _stream()), "ffk_load_rows")
+    return out
 
 
 def gather(x, idx, out, dim):
