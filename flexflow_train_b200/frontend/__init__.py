@@ -2,5 +2,6 @@
 and the Keras-compatible classes."""
 from .ffmodel import (AdamOptimizer, FFModel, GlorotUniformInitializer, NormInitializer, SGDOptimizer, SingleDataLoader,  # noqa: F401
                       Tensor, UniformInitializer, ZeroInitializer)
+from .dataloader import DataLoader  # noqa: F401
 from .types import (ActiMode, AggrMode, CompMode, DataType, LossType, MetricsType, OpType, ParameterSyncType, PoolType,  # noqa: F401
                     RegularizerMode)
