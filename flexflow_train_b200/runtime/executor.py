@@ -1055,7 +1055,9 @@ class Executable:
         # lib/kernels/include/kernels/allocation.h, lib/local-execution/.../tracked_allocator.h); symmetric peer-memory
         # arenas of the multi-GPU executor are the exception: they come from the peer-memory context
         from .allocator import LocalCPUAllocator, LocalCudaAllocator, TrackedAllocator
-        self.allocator = TrackedAllocator(LocalCudaAllocator(self.device.index or 0) if self.on_gpu else LocalCPUAllocator())
+        # "cuda" without an index means the process's current device (one process per GPU sets it before compiling)
+        dev_idx = self.device.index if self.device.index is not None else (torch.cuda.current_device() if self.on_gpu else 0)
+        self.allocator = TrackedAllocator(LocalCudaAllocator(dev_idx) if self.on_gpu else LocalCPUAllocator())
         self.values: Dict[Value, _Buf] = {}
         self.layout: Dict[Value, str] = {}
         self.ops: Dict[int, OpImpl] = {}
