@@ -83,22 +83,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// 2^x for x <= 0 on the FMA pipe: x = n + f with n the nearest integer (magic-number rounding), 2^f for f in [-0.5, 0.5]
-// by a degree-4 polynomial (relative error < 5e-5, far below bf16 resolution), then n added to the exponent bits.  Ten
-// instructions on a pipe with eight times the special-function unit's throughput; the forward softmax evaluates every
-// other pair of probabilities this way because the special-function unit bounds it.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;
-  const float n = t - 12582912.f;
-  const float f = x - n;
-  float p = fmaf(f, 0.00961813f, 0.05550411f);
-  p = fmaf(p, f, 0.24022651f);
-  p = fmaf(p, f, 0.69314718f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 __device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
@@ -392,7 +376,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
-        float e2 = poly_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = poly_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
+        float e2 = fast_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = fast_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
         if (!full) {
           if (i >= kmax) e0 = 0.f;
           if (i + 1 >= kmax) e1 = 0.f;
@@ -767,7 +751,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_ref));
-        float e2 = poly_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_ref)), e3 = poly_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_ref));
+        float e2 = fast_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_ref));
         if (!full) {
           if (i >= kmax) e0 = 0.f;
           if (i + 1 >= kmax) e1 = 0.f;
