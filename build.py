@@ -60,7 +60,9 @@ def build_kernels(force=False, verbose=False, ptxas_info=False):
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         list(ex.map(lambda c: _run(c, verbose or ptxas_info), jobs))
     if jobs or force or _stale(out, objs):
-        _run([NVCC, "-shared", "-o", out] + objs + ["-lcudart"], verbose)
+        # link beside the target and rename: a reader (an import, a copy of the tree) never sees a half-written library
+        _run([NVCC, "-shared", "-o", out + ".tmp"] + objs + ["-lcudart"], verbose)
+        os.replace(out + ".tmp", out)
     return out
 
 
@@ -88,7 +90,8 @@ def build_core(force=False, verbose=False, sanitize=False):
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         list(ex.map(lambda c: _run(c, verbose), jobs))
     if jobs or force or _stale(out, objs):
-        _run(["g++", "-shared", "-o", out] + objs + (["-fsanitize=undefined"] if sanitize else []), verbose)
+        _run(["g++", "-shared", "-o", out + ".tmp"] + objs + (["-fsanitize=undefined"] if sanitize else []), verbose)
+        os.replace(out + ".tmp", out)
     return out
 
 

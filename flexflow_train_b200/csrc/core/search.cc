@@ -690,15 +690,6 @@ MachineMappingResult get_optimal_machine_mapping(const Graph &pcg, const SPTree 
   return r;
 }
 
-std::vector<std::pair<uint64_t, int>> debug_sub_hashes(const Graph &pcg, const MachineSpec &m, const CostEstimator &est) {
-  MachineMappingCache local;
-  DP dp{pcg, m, est, 1, local};
-  dp.annotate(normalize_sp(get_graph_sp_decomposition(pcg)));
-  std::vector<std::pair<uint64_t, int>> out;
-  for (auto &s : dp.subs) out.push_back({s.hash, (int)s.leaves.size()});
-  return out;
-}
-
 Graph mapped_pcg_from_pcg_and_mapping(const Graph &pcg, const std::map<NodeId, MachineView> &mapping) {
   Graph g = pcg;
   for (auto &kv : mapping)
@@ -1114,7 +1105,6 @@ void bind_search(py::module &m) {
     return pts;
   }, py::arg("pcg"), py::arg("tree") = py::none(), py::arg("machine") = MachineSpec(), py::arg("estimator") = CostEstimator(),
         py::arg("max_front") = 1);
-  m.def("debug_sub_hashes", &debug_sub_hashes);
   m.def("evaluate_pcg", [](const Graph &g, const MachineSpec &ms, const CostEstimator &est) { return result_to_py(evaluate_pcg(g, ms, est)); });
   m.def("apply_rules_exhaustively", [](const Graph &g, std::vector<Substitution> rules, int max_app, int max_deg) {
     return apply_rules_exhaustively(g, rules, max_app, max_deg);

@@ -55,7 +55,7 @@ struct AttnArgs {
   long long lddk, lddv;
   float *dQ_acc;          // [B, H, Sq, D] fp32, zeroed by the caller: the key blocks of a head add into it
   int *err;
-  int dbg;                // experiment switches (FFK_ATTN_DBG): parts of the kernel left out to time the rest
+  int dbg;                // FFK_ATTN_DBG: 4096 records the timeline of one CTA (ffk_attention_trace)
 };
 
 // Timeline of one CTA (experiment switch 4096): SM clock at event `ev` (0..31) of step `j` (0..63), one slot each, written
@@ -243,7 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         const uint64_t dk = desc_advance(dk0, (uint32_t)(t * C::KV_BYTES));
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_S + t * 128);
-        if (!(p.dbg & 16)) {
+        {
           tc_mma_bf16<false>(d_tmem, dq, dk, C::IDESC_S);
 #pragma unroll
           for (int ks = 1; ks < D / 16; ++ks) {
@@ -268,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         const uint64_t dv = desc_advance(dv0, (uint32_t)(vt * C::KV_BYTES));
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
-        if (!(p.dbg & 2)) {
+        {
           // A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
           tc_mma_bf16<false>(d_tmem, dp, dv, C::IDESC_PV);
 #pragma unroll
@@ -316,7 +316,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
       uint32_t ra[32];
-      if (p.dbg & 8) { tc_fence_before(); warp_arrive(&o_empty[t], lane); return true; }
       tmem_ld32(t_o, ra);
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
@@ -372,7 +371,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (m_new == -INFINITY) m_new = 0.f;        // nothing visible yet (padding rows only)
       const float alpha = fast_exp2(m - m_new);
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-      if (!(p.dbg & 1))
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
@@ -399,7 +397,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
       // 64 probabilities = 128 bytes = the eight 16-byte chunks of this row in this half's panel; chunk index XOR (row % 8)
       // is the 128-byte swizzle the MMA descriptor expects
-      if (!(p.dbg & 4))
 #pragma unroll
       for (int u = 0; u < 8; ++u)
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)((u ^ (r & 7)) << 4)), "r"(rs[4 * u]), "r"(rs[4 * u + 1]),
