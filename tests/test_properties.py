@@ -172,3 +172,78 @@ def test_v1_reader_accepts_a_hand_written_file_with_the_reference_field_names():
     assert list(g.shape((2, "OUTPUT")).sizes) == [4, 3]
     # and the writer emits the same document (key for key) for this graph
     assert json.loads(g.to_v1_string()) == GOLDEN_V1
+
+
+# ------------------------------------------------------------------------------------------ dataflow graphs
+def _random_dataflow(data, n_inputs, n_nodes):
+    """Builds an open dataflow graph from hypothesis draws; returns (graph, recipe) where recipe lets the same graph be
+    rebuilt with its nodes added in another order."""
+    d = core.dataflow
+    g = d.OpenDataflowGraph()
+    values = [g.add_input() for _ in range(n_inputs)]
+    recipe = []
+    for _ in range(n_nodes):
+        k = data.draw(st.integers(0, min(3, len(values))))
+        ins = [values[data.draw(st.integers(0, len(values) - 1))] for _ in range(k)]
+        n_out = data.draw(st.integers(1, 2))
+        node, outs = g.add_node(ins, n_out)
+        recipe.append((ins, n_out, node))
+        values.extend(outs)
+    return g, recipe
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.data())
+def test_dataflow_graph_invariants(data):
+    d = core.dataflow
+    n_inputs = data.draw(st.integers(0, 3))
+    g, recipe = _random_dataflow(data, n_inputs, data.draw(st.integers(1, 7)))
+    nodes = sorted(g.get_nodes())
+    assert len(nodes) == len(recipe)
+    # every operand is an earlier value; uses and inputs mirror each other
+    order = g.topological_ordering()
+    pos = {n: i for i, n in enumerate(order)}
+    for ins, n_out, node in recipe:
+        assert g.get_inputs(node) == ins and len(g.get_outputs(node)) == n_out
+        for slot, v in enumerate(ins):
+            assert (node, slot) in g.get_uses(v)
+            if v[0] != "input":
+                assert pos[v[0]] < pos[node]
+    used = {tuple(v) for ins, _, _ in recipe for v in ins}
+    assert sorted(g.get_unused_outputs()) == sorted(o for _, _, node in recipe for o in g.get_outputs(node) if tuple(o) not in used)
+    # a graph is isomorphic to itself, and the map is the identity when every node is distinguishable by position
+    m = d.find_dataflow_isomorphism(g, g)
+    assert m is not None and sorted(m) == nodes and sorted(m.values()) == nodes
+    # copies are independent
+    h = g.copy()
+    h.add_node([], 1)
+    assert len(h.get_nodes()) == len(nodes) + 1 and len(g.get_nodes()) == len(nodes)
+    assert d.find_dataflow_isomorphism(g, h) is None
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.data())
+def test_open_subgraph_keeps_structure_and_cuts_the_rest_into_inputs(data):
+    d = core.dataflow
+    g, recipe = _random_dataflow(data, data.draw(st.integers(0, 2)), data.draw(st.integers(2, 7)))
+    nodes = sorted(g.get_nodes())
+    keep = {n for n in nodes if data.draw(st.booleans())} or {nodes[0]}
+    sub, node_of, input_of = d.get_open_subgraph(g, keep)
+    assert set(node_of) == keep and len(sub.get_nodes()) == len(keep)
+    outside = {}
+    for gi, v in input_of:
+        outside[tuple(gi)] = tuple(v) if not isinstance(v, tuple) else v
+    # distinct outside values get distinct graph inputs
+    assert len(set(outside.values())) == len(outside)
+    for n in keep:
+        ins_full = g.get_inputs(n)
+        ins_sub = sub.get_inputs(node_of[n])
+        assert len(ins_full) == len(ins_sub)
+        for vf, vs in zip(ins_full, ins_sub):
+            if vf[0] != "input" and vf[0] in keep:
+                assert vs == (node_of[vf[0]], vf[1])           # an edge inside the set stays an edge
+            else:
+                assert vs[0] == "input" and outside[tuple(vs)] == tuple(vf)   # a cut value became this graph input
+    # taking everything changes nothing but the numbering
+    whole, _, ins = d.get_open_subgraph(g, set(nodes))
+    assert d.find_dataflow_isomorphism(g, whole) is not None or len(g.get_graph_inputs()) != len(whole.get_graph_inputs())
