@@ -324,6 +324,8 @@ def main():
     ap.add_argument("--strategy", default="search", help="search | dp | tp | dp<a>xtp<b> (device mesh) | tables (model-parallel embedding tables under a data-parallel model) | <path to strategy json>")
     ap.add_argument("--search-budget", type=int, default=10, help="Unity search budget on top of the scored templates (0 = templates only)")
     ap.add_argument("--search-time-limit", type=float, default=30.0)
+    ap.add_argument("--global-batch", type=int, default=None, help="override the model configuration's global batch (experiments; the "
+                    "headline configuration is the default)")
     ap.add_argument("--timeline", action="store_true",
                     help="after the timed runs, print rank 0's per-phase and per-bucket timeline of two eager steps (stderr)")
     ap.add_argument("--no-fused-collectives", action="store_true",
@@ -357,6 +359,8 @@ def main():
 
     model_name, mcfg = MODEL_CONFIGS[args.model]
     mcfg = dict(mcfg)
+    if args.global_batch:
+        mcfg["batch_size"] = args.global_batch
     global_batch, seq = mcfg["batch_size"], mcfg.get("sequence_length", 1)
     opt_kind, lr, momentum, loss_kind = TRAINING[args.model]
     ffcfg = api.FFConfig(batch_size=global_batch, compute_dtype="bf16", use_cuda_graph=not args.no_cuda_graph, seed=0,
