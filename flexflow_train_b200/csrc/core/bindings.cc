@@ -9,6 +9,7 @@ void bind_search(py::module &m);
 void bind_lowering(py::module &m);
 void bind_utils(py::module &m);
 void bind_dataflow(py::module &m);
+void bind_containers(py::module &m);
 }  // namespace ff
 
 using namespace ff;
@@ -398,4 +399,5 @@ PYBIND11_MODULE(_ffcore, m) {
   bind_lowering(m);
   bind_utils(m);
   bind_dataflow(m);
+  bind_containers(m);
 }
