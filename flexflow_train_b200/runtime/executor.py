@@ -1051,18 +1051,20 @@ class Executable:
         if self.on_gpu:
             K.lib()  # fail loudly if the kernel library is missing
         # every long-lived device buffer of the plan (parameter / gradient / optimizer arenas, activations, scratch) comes
-        # from this allocator, which counts bytes (the reference's per-device Allocator behind a tracking wrapper,
+        # from the handle's allocator, which counts bytes (the reference's per-device Allocator behind a tracking wrapper,
         # lib/kernels/include/kernels/allocation.h, lib/local-execution/.../tracked_allocator.h); symmetric peer-memory
-        # arenas of the multi-GPU executor are the exception: they come from the peer-memory context
-        from .allocator import LocalCPUAllocator, LocalCudaAllocator, TrackedAllocator
-        # "cuda" without an index means the process's current device (one process per GPU sets it before compiling)
-        dev_idx = self.device.index if self.device.index is not None else (torch.cuda.current_device() if self.on_gpu else 0)
-        self.allocator = TrackedAllocator(LocalCudaAllocator(dev_idx) if self.on_gpu else LocalCPUAllocator())
+        # arenas of the multi-GPU executor are the exception: they come from the peer-memory context.  The handle also
+        # owns the one workspace the operators' scratch needs are folded into.
+        from .device_handle import create_local_handle_for_device, create_multi_gpu_handle
+        if dist is not None and self.on_gpu:
+            self.handle = create_multi_gpu_handle(dist)
+        else:
+            self.handle = create_local_handle_for_device(self.device)
+        self.allocator = self.handle.allocator
         self.values: Dict[Value, _Buf] = {}
         self.layout: Dict[Value, str] = {}
         self.ops: Dict[int, OpImpl] = {}
         self.order: List[int] = list(graph.topological_order())
-        self._scratch_bytes = 0
         self._big_scratch_bytes = 0
         self._big_scratch_slots = 0
         self._salt = 0
@@ -1118,7 +1120,11 @@ class Executable:
         return self._salt * 0x1000003
 
     def need_scratch(self, nbytes: int):
-        self._scratch_bytes = max(self._scratch_bytes, int(nbytes))
+        self.handle.reserve_workspace(nbytes)
+
+    @property
+    def _scratch(self) -> torch.Tensor:
+        return self.handle.workspace
 
     def need_big_scratch(self, nbytes: int, slots: int):
         self._big_scratch_bytes = max(self._big_scratch_bytes, int(nbytes))
@@ -1195,7 +1201,7 @@ class Executable:
         # 5. gradient buffers + accumulate flags
         if self.cfg.training:
             self._plan_gradients()
-        self._scratch = self.allocator.allocate([max(self._scratch_bytes // 4, 1)], torch.float32)
+        self.handle.materialize_workspace()
         self._big = [self.allocator.allocate([max(self._big_scratch_bytes, 1)], torch.uint8) for _ in range(max(self._big_scratch_slots, 1))]
 
     def sparse_weight_nodes(self) -> List[int]:

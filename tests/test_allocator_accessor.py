@@ -73,3 +73,30 @@ def test_task_bodies_allocate_through_a_tracked_allocator():
 
     table = run_invocations(inv, {("FWD", "*"): body}, allocate=tracked)
     assert tracked.peak_bytes == 256 and table[(0, "OUTPUT", "FWD", None)].shape == (8, 8)
+
+
+def test_device_handle_folds_workspace_requests_and_counts_its_bytes():
+    # the per-device handle (lib/kernels/include/kernels/ff_handle.h, managed_per_device_ff_handle.h): one workspace sized
+    # by the largest request, allocated once through the tracked allocator; the CPU handle has no stream
+    from flexflow_train_b200.runtime.device_handle import create_local_handle_for_device
+    h = create_local_handle_for_device("cpu", workspace_bytes=64)
+    assert not h.is_gpu and not h.stream().is_gpu and h.num_ranks == 1 and h.my_rank == 0
+    h.reserve_workspace(1000)
+    h.reserve_workspace(10)
+    assert h.workspace_bytes == 1000 and h.workspace is None
+    before = h.allocator.current_bytes
+    ws = h.materialize_workspace()
+    assert ws.dtype == torch.float32 and ws.numel() * 4 >= 1000 and h.materialize_workspace() is ws
+    assert h.allocator.current_bytes - before == ws.numel() * 4
+    h.reserve_workspace(500)       # fits: fine
+    with pytest.raises(RuntimeError):
+        h.reserve_workspace(1 << 20)   # the workspace is already allocated and too small
+    assert "workspace 1000 bytes" in h.describe()
+
+
+def test_cpu_executable_plans_its_workspace_through_the_handle():
+    from flexflow_train_b200 import _ffcore as core
+    from flexflow_train_b200.runtime.executor import ExecConfig, Executable
+    g = core.build_model("mlp", {"batch_size": 8, "input_dim": 16, "hidden": [32], "num_classes": 4})
+    ex = Executable(g, ExecConfig(device="cpu", compute_dtype="fp32"))
+    assert ex.handle.allocator is ex.allocator and ex.handle.workspace is ex.scratch_f32() and ex.handle.workspace is not None
