@@ -3,6 +3,8 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
+#include <sstream>
 #include <string>
 
 #include "builder.h"
@@ -281,6 +283,82 @@ FFC_EXPORT char *ffc_graph_sp_decomposition(const ffc_graph_t *g) {
   return r;
 }
 FFC_EXPORT int ffc_graph_num_nodes(const ffc_graph_t *g) { return (int)g->g.num_nodes(); }
+FFC_EXPORT int ffc_graph_save_file(const ffc_graph_t *g, const char *path, int parallel, int indent) {
+  return guarded([&] {
+    std::ofstream f(str(path));
+    if (!f) throw Error("cannot open " + str(path) + " for writing");
+    f << graph_to_v1(g->g, parallel != 0).dump(indent);
+    if (!f.flush()) throw Error("write to " + str(path) + " failed");
+  });
+}
+FFC_EXPORT ffc_graph_t *ffc_graph_load_file(const char *path) {
+  ffc_graph_t *g = nullptr;
+  guarded([&] {
+    std::ifstream f(str(path));
+    if (!f) throw Error("cannot open " + str(path));
+    std::stringstream ss;
+    ss << f.rdbuf();
+    g = new ffc_graph{graph_from_v1(Json::parse(ss.str()))};
+  });
+  return g;
+}
+FFC_EXPORT int ffc_graph_node_ids(const ffc_graph_t *g, int *ids, int max_ids, int *num) {
+  return guarded([&] {
+    auto order = g->g.topological_order();
+    *num = (int)order.size();
+    for (int i = 0; i < (int)order.size() && i < max_ids; ++i) ids[i] = (int)order[i];
+  });
+}
+FFC_EXPORT char *ffc_graph_node_op_type(const ffc_graph_t *g, int node) {
+  char *r = nullptr;
+  guarded([&] { r = dup_string(to_string(g->g.node(node).type)); });
+  return r;
+}
+FFC_EXPORT char *ffc_graph_node_name(const ffc_graph_t *g, int node) {
+  char *r = nullptr;
+  guarded([&] { r = dup_string(g->g.node(node).name); });
+  return r;
+}
+FFC_EXPORT char *ffc_graph_node_attrs_json(const ffc_graph_t *g, int node) {
+  char *r = nullptr;
+  guarded([&] { r = dup_string(g->g.node(node).attrs.dump()); });
+  return r;
+}
+FFC_EXPORT char *ffc_graph_node_view_json(const ffc_graph_t *g, int node) {
+  char *r = nullptr;
+  guarded([&] {
+    const Node &n = g->g.node(node);
+    if (!n.view) throw Error("node " + std::to_string(node) + " has no machine view (the graph is not mapped)");
+    r = dup_string(n.view->to_json().dump());
+  });
+  return r;
+}
+FFC_EXPORT int ffc_graph_value_shape(const ffc_graph_t *g, ffc_value_t v, int64_t *dims, int max_dims, int *ndims) {
+  return guarded([&] {
+    auto sizes = g->g.shape(ref(v)).sizes();
+    if ((int)sizes.size() > max_dims) throw Error("ffc_graph_value_shape: max_dims too small");
+    for (size_t i = 0; i < sizes.size(); ++i) dims[i] = sizes[i];
+    *ndims = (int)sizes.size();
+  });
+}
+FFC_EXPORT const char *ffc_graph_value_dtype(const ffc_graph_t *g, ffc_value_t v) {
+  static thread_local std::string s;
+  if (guarded([&] { s = to_string(g->g.shape(ref(v)).dtype); })) return nullptr;
+  return s.c_str();
+}
+FFC_EXPORT int ffc_graph_value_create_grad(const ffc_graph_t *g, ffc_value_t v, int *create_grad) {
+  return guarded([&] { *create_grad = g->g.node(v.node).out((Slot)v.slot).create_grad ? 1 : 0; });
+}
+FFC_EXPORT int ffc_datatype_size(const char *dtype) {
+  int n = -1;
+  guarded([&] { n = dtype_bytes(datatype_from_string(str(dtype))); });
+  return n;
+}
+FFC_EXPORT const char *ffc_builder_value_dtype(const ffc_builder_t *b, ffc_value_t v) {
+  static thread_local std::string s;
+  if (guarded([&] { s = to_string(b->b.graph.shape(ref(v)).dtype); })) return nullptr;
+  return s.c_str();
+}
 FFC_EXPORT void ffc_graph_destroy(ffc_graph_t *g) { delete g; }
 
 FFC_EXPORT int ffc_graph_optimize(const ffc_graph_t *cg, int num_nodes, int gpus_per_node, const char *algorithm, int budget, double alpha,

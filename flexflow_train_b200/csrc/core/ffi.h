@@ -45,6 +45,7 @@ int ffc_builder_unary(ffc_builder_t *b, const char *op, ffc_value_t x, int has_s
 int ffc_builder_binary(ffc_builder_t *b, const char *op, ffc_value_t x, ffc_value_t y, const char *name, ffc_value_t *out);
 int ffc_builder_softmax(ffc_builder_t *b, ffc_value_t x, int dim, const char *name, ffc_value_t *out);
 int ffc_builder_value_shape(const ffc_builder_t *b, ffc_value_t v, int64_t *dims, int max_dims, int *ndims);
+const char *ffc_builder_value_dtype(const ffc_builder_t *b, ffc_value_t v);
 /* One function per layer of the builder (the reference's flexflow_model_add_* family, lib/ffi/include/flexflow/ffi.h).
  * Optional strings may be NULL; initializers are the defaults of the layer. */
 int ffc_builder_pool2d(ffc_builder_t *b, ffc_value_t x, int kernel_h, int kernel_w, int stride_h, int stride_w, int padding_h, int padding_w,
@@ -91,6 +92,24 @@ ffc_graph_t *ffc_graph_from_json(const char *v1_json);
 char *ffc_graph_to_json(const ffc_graph_t *g, int parallel, int indent);
 char *ffc_graph_to_dot(const ffc_graph_t *g);
 int ffc_graph_num_nodes(const ffc_graph_t *g);
+/* The same serialisation to and from a file (parallel != 0 writes the parallel / mapped variant). */
+int ffc_graph_save_file(const ffc_graph_t *g, const char *path, int parallel, int indent);
+ffc_graph_t *ffc_graph_load_file(const char *path);
+/* Node ids in topological order (ids has room for max_ids entries; *num is the node count either way). */
+int ffc_graph_node_ids(const ffc_graph_t *g, int *ids, int max_ids, int *num);
+/* Operator type name ("LINEAR", ...), layer name and attribute object of a node; malloc'd strings. */
+char *ffc_graph_node_op_type(const ffc_graph_t *g, int node);
+char *ffc_graph_node_name(const ffc_graph_t *g, int node);
+char *ffc_graph_node_attrs_json(const ffc_graph_t *g, int node);
+/* Machine view of a node of a mapped graph as JSON ({"start": {"node_idx", "device_idx"}, "dimensions": [...]}); NULL with an
+ * error when the node has none. */
+char *ffc_graph_node_view_json(const ffc_graph_t *g, int node);
+/* Shape, data type name and gradient flag of a node's output value. */
+int ffc_graph_value_shape(const ffc_graph_t *g, ffc_value_t v, int64_t *dims, int max_dims, int *ndims);
+const char *ffc_graph_value_dtype(const ffc_graph_t *g, ffc_value_t v);
+int ffc_graph_value_create_grad(const ffc_graph_t *g, ffc_value_t v, int *create_grad);
+/* Bytes of one element of a data type given by name; -1 with an error for an unknown name. */
+int ffc_datatype_size(const char *dtype);
 /* Estimated step time (ms) of a parallel computation graph on num_nodes x gpus_per_node devices under the analytic cost
  * model, with the machine mapping the dynamic program finds. */
 int ffc_graph_estimate(const ffc_graph_t *pcg, int num_nodes, int gpus_per_node, double *runtime_ms);

@@ -200,3 +200,77 @@ def test_parallel_builder_through_the_c_api():
     assert l.ffc_builder_create_input(b2, (c_int64 * 2)(16, 32), 2, b"FLOAT", b"x", byref(x)) == 0
     assert l.ffc_builder_parallel_replicate(b2, x, 2, b"r", byref(y)) != 0
     l.ffc_builder_destroy(b2)
+
+
+def test_graph_inspection_and_files_through_the_c_api(tmp_path):
+    l = _lib()
+    I, L = c_int, c_int64
+    l.ffc_graph_save_file.argtypes = [c_void_p, c_char_p, I, I]
+    l.ffc_graph_load_file.restype = c_void_p
+    l.ffc_graph_load_file.argtypes = [c_char_p]
+    l.ffc_graph_node_ids.argtypes = [c_void_p, POINTER(I), I, POINTER(I)]
+    for f in ("ffc_graph_node_op_type", "ffc_graph_node_name", "ffc_graph_node_attrs_json", "ffc_graph_node_view_json"):
+        getattr(l, f).restype = c_void_p
+        getattr(l, f).argtypes = [c_void_p, I]
+    l.ffc_graph_value_shape.argtypes = [c_void_p, Value, POINTER(L), I, POINTER(I)]
+    l.ffc_graph_value_dtype.restype = c_char_p
+    l.ffc_graph_value_dtype.argtypes = [c_void_p, Value]
+    l.ffc_graph_value_create_grad.argtypes = [c_void_p, Value, POINTER(I)]
+    l.ffc_datatype_size.argtypes = [c_char_p]
+    l.ffc_builder_value_dtype.restype = c_char_p
+    l.ffc_builder_value_dtype.argtypes = [c_void_p, Value]
+
+    def text(p):
+        assert p, l.ffc_last_error()
+        s = ctypes.string_at(p).decode()
+        l.ffc_string_free(p)
+        return s
+
+    assert [l.ffc_datatype_size(n) for n in (b"BOOL", b"INT32", b"INT64", b"HALF", b"BFLOAT16", b"FLOAT", b"DOUBLE")] == [1, 4, 8, 2, 2, 4, 8]
+    assert l.ffc_datatype_size(b"QUADRUPLE") == -1 and l.ffc_last_error()
+
+    ref = core.build_model("mlp", {"batch_size": 8})
+    g = l.ffc_model_build(b"mlp", b'{"batch_size": 8}')
+    n = c_int()
+    assert l.ffc_graph_node_ids(g, None, 0, byref(n)) == 0 and n.value == len(ref.nodes())
+    ids = (I * n.value)()
+    assert l.ffc_graph_node_ids(g, ids, n.value, byref(n)) == 0 and list(ids) == list(ref.topological_order())
+    by_id = {nd["id"]: nd for nd in ref.nodes()}
+    slot_out = l.ffc_slot_from_name(b"OUTPUT")
+    for nid in ids:
+        nd = by_id[nid]
+        assert text(l.ffc_graph_node_op_type(g, nid)) == nd["type"] and text(l.ffc_graph_node_name(g, nid)) == nd["name"]
+        assert json.loads(text(l.ffc_graph_node_attrs_json(g, nid))) == nd["attrs"]
+        dims, nd_ = (L * 8)(), c_int()
+        v = Value(nid, slot_out)
+        assert l.ffc_graph_value_shape(g, v, dims, 8, byref(nd_)) == 0
+        sh = ref.shape((nid, "OUTPUT"))
+        assert list(dims[:nd_.value]) == list(sh.sizes) and l.ffc_graph_value_dtype(g, v).decode() == sh.dtype
+        cg = c_int(-1)
+        assert l.ffc_graph_value_create_grad(g, v, byref(cg)) == 0 and cg.value in (0, 1)
+    assert l.ffc_graph_node_op_type(g, 10 ** 6) is None and l.ffc_last_error()
+    assert l.ffc_graph_node_view_json(g, ids[0]) is None and b"view" in l.ffc_last_error()
+
+    # a mapped graph: every node has a view; the file round trip keeps it
+    mapped, ms = c_void_p(), c_double()
+    l.ffc_graph_optimize.argtypes = [c_void_p, c_int, c_int, c_char_p, c_int, c_double, c_uint, POINTER(c_void_p), POINTER(c_double)]
+    assert l.ffc_graph_optimize(g, 1, 2, b"data_parallel", 0, 1.05, 0, byref(mapped), byref(ms)) == 0, l.ffc_last_error()
+    path = str(tmp_path / "strategy.json").encode()
+    assert l.ffc_graph_save_file(mapped, path, 1, 1) == 0, l.ffc_last_error()
+    back = l.ffc_graph_load_file(path)
+    assert back and l.ffc_graph_num_nodes(back) == l.ffc_graph_num_nodes(mapped)
+    assert l.ffc_graph_node_ids(back, None, 0, byref(n)) == 0
+    ids2 = (I * n.value)()
+    l.ffc_graph_node_ids(back, ids2, n.value, byref(n))
+    views = [json.loads(text(l.ffc_graph_node_view_json(back, i))) for i in ids2]
+    assert all("start" in v and "dimensions" in v for v in views)
+    assert any(len(v["dimensions"]) == 1 for v in views)        # the batch-parallel operators run over a 1-d view of 2 devices
+    assert l.ffc_graph_load_file(str(tmp_path / "missing.json").encode()) is None and b"cannot open" in l.ffc_last_error()
+    assert l.ffc_graph_save_file(mapped, str(tmp_path / "no_dir" / "x.json").encode(), 1, 1) != 0
+    for h in (g, mapped, back):
+        l.ffc_graph_destroy(h)
+    b = l.ffc_builder_create()
+    x = Value()
+    assert l.ffc_builder_create_input(b, (c_int64 * 2)(4, 4), 2, b"INT32", b"ids", byref(x)) == 0
+    assert l.ffc_builder_value_dtype(b, x) == b"INT32"
+    l.ffc_builder_destroy(b)
