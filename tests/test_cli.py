@@ -222,3 +222,22 @@ def test_config_fields_flags_and_docs_come_from_one_table():
     assert all(f"`{f.name}`" in table for f in cs.FIELDS)
     with __import__("pytest").raises(SystemExit):
         p.parse_args(["--compute-dtype", "fp8"])
+
+
+def test_documentation_pages_are_current():
+    # the configuration page is generated from the schema; the index lists every page; tools named in the docs exist
+    import importlib
+    import os
+    import re
+    from flexflow_train_b200 import config_schema
+    docs = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "docs")
+    assert config_schema.describe() in open(os.path.join(docs, "configuration.md")).read()
+    index = open(os.path.join(docs, "index.md")).read()
+    pages = sorted(f for f in os.listdir(docs) if f.endswith(".md") and f != "index.md")
+    assert pages and all(f"({p})" in index for p in pages)
+    text = "\n".join(open(os.path.join(docs, p)).read() for p in pages)
+    for mod in set(re.findall(r"python -m (flexflow_train_b200\.[a-z_.]+)", text)):
+        if not mod.endswith("<tool>"):
+            assert importlib.util.find_spec(mod.rstrip(".")) is not None, mod
+    for path in set(re.findall(r"`((?:csrc|runtime|frontend|parallel|utils|ops|compiler|bin)/[A-Za-z0-9_/.]+\.(?:py|cc|cu|cuh|h))`", text)):
+        assert os.path.exists(os.path.join(os.path.dirname(docs), "flexflow_train_b200", path)), path
