@@ -88,11 +88,23 @@ __device__ __forceinline__ void warp_arrive(uint64_t *bar, int lane) {
   if (lane == 0) mbar_arrive(bar);
 }
 
-// keep bits of the four keys 4*g4 .. 4*g4+3 of one row
-__device__ __forceinline__ uint64_t attn_rand4(unsigned long long seed, unsigned long long row_groups_base, int g4) {
-  return ffk_rand16x4(seed, row_groups_base + (unsigned long long)g4);
+// Dropout draws of the attention kernels: one 32-bit word per (query row, group of four keys) from two multiply-fold steps,
+// then one odd multiplier per key of the group; key j is dropped iff word * ATT_RC[j] (mod 2^32) < p * 2^32.  Sixteen
+// instructions per four keys (the generic 64-bit generator of the element-wise kernels costs about forty); the forward and
+// the backward kernel and ops/kernels.py::attention_keep_mask (the host restatement the tests use) share this definition.
+__device__ __forceinline__ uint32_t attn_row_mix(unsigned long long seed, unsigned long long row) {
+  return (uint32_t)seed + (uint32_t)row * 0x9E3779B9u;
 }
-
+__device__ __forceinline__ uint32_t attn_group_word(uint32_t row_mix, uint32_t seed_hi, uint32_t group) {
+  const uint32_t a = group * 0xB5297A4Du + row_mix;
+  const uint64_t m = (uint64_t)a * 0xCC9E2D51u;
+  return (uint32_t)m ^ (uint32_t)(m >> 32) ^ seed_hi;
+}
+constexpr uint32_t ATT_RC0 = 0x9E3779B1u, ATT_RC1 = 0x85EBCA6Bu, ATT_RC2 = 0xC2B2AE35u, ATT_RC3 = 0x27D4EB2Fu;
+__device__ __forceinline__ uint32_t attn_drop_threshold(float p) {
+  const float t = p * 4294967296.0f;
+  return t >= 4294967040.0f ? 0xFFFFFF00u : (uint32_t)t;
+}
 
 // Probabilities of one thread's 64 scores when there is no dropout: rs[i] (raw fp32 bits of s_i) becomes the bf16 pair
 // (p_2i, p_2i+1) in rs[0..31], p_i = 2^(s_i * sl2 - m), zero from column kmax on; returns the sum of the p_i.  The work goes
@@ -291,6 +303,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_commit(&s_full[t]);
         tc_commit(&k_empty[t]);
+        attn_trace(p, 20, j);
         return true;
       };
       if (ok && n_tiles > 0) ok = issue_s(0);
@@ -303,6 +316,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
              mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
              mbar_wait(&o_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
+        attn_trace(p, 21, j);
         tc_fence_after();
         const uint64_t dv = desc_advance(dv0, (uint32_t)(vt * C::KV_BYTES));
         const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
@@ -319,6 +333,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_commit(&o_full[t]);
         tc_commit(&v_empty[vt]);
         tc_commit(p_empty);
+        attn_trace(p, 22, j);
       }
     }
   } else {
@@ -334,10 +349,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float sl2 = p.scale * LOG2E;
     float m = -INFINITY, l = 0.f;
     const bool drop = p.drop_p > 0.f;   // kept a run-time value: as a compile-time constant the mask arithmetic is hoisted and spills
-    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const uint32_t thr = attn_drop_threshold(p.drop_p);
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
-    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
-    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    const uint32_t seed_hi = (uint32_t)(seed >> 32);
+    const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
     const uint32_t prow = smem_u32(smem + C::OFF_P + half * (BQ * 128) + r * 128);   // this row in this half's 64-key panel
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     float o[DH];
@@ -351,6 +366,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool k_ = mbar_wait(&o_full[t], (uint32_t)(jj >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       k_ = __all_sync(0xffffffffu, k_);
       if (!k_) return false;
+      if (warp == 2) attn_trace(p, 6, jj + 1);
       tc_fence_after();
       const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
       uint32_t ra[32];
@@ -377,6 +393,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(&s_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      const bool tr = warp == 2;
+      if (tr) attn_trace(p, 0, j);
       tc_fence_after();
       const uint32_t t_s = lane_base + (uint32_t)(C::TMEM_S + t * 128 + half * 64);
       uint32_t rs[64];
@@ -384,7 +402,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld32(t_s + 32u, *reinterpret_cast<uint32_t(*)[32]>(&rs[32]));
       tmem_ld_wait();
       tc_fence_before();
-      warp_arrive(&s_empty[t], lane);     // the scores are in registers: the next-but-one tile may overwrite them
+      warp_arrive(&s_empty[t], lane);
+      if (tr) attn_trace(p, 1, j);     // the scores are in registers: the next-but-one tile may overwrite them
       const int k0 = j * BKF + half * 64;
       // columns of this half that exist / are visible to this row
       int kmax = p.Sk - k0;
@@ -405,6 +424,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       xchg[(t * 2 + half) * 128 + r] = mine;
       pair_sync(quarter);
       const float other = xchg[(t * 2 + (half ^ 1)) * 128 + r];
+      if (tr) attn_trace(p, 2, j);
       float m_new = fmaxf(m, fmaxf(mine, other) * sl2);
       if (m_new == -INFINITY) m_new = 0.f;        // nothing visible yet (padding rows only)
       const float alpha = fast_exp2(m - m_new);
@@ -423,11 +443,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           ls0 += e0; ls1 += e1; ls2 += e2; ls3 += e3;
           if (drop) {
-            const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
-            if ((uint32_t)(z & 0xFFFFu) < thr) e0 = 0.f;
-            if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) e1 = 0.f;
-            if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) e2 = 0.f;
-            if ((uint32_t)(z >> 48) < thr) e3 = 0.f;
+            const uint32_t z = attn_group_word(row_mix, seed_hi, (uint32_t)((k0 + i) >> 2));
+            if (z * ATT_RC0 < thr) e0 = 0.f;
+            if (z * ATT_RC1 < thr) e1 = 0.f;
+            if (z * ATT_RC2 < thr) e2 = 0.f;
+            if (z * ATT_RC3 < thr) e3 = 0.f;
           }
           rs[i >> 1] = pack_bf162(e0, e1);            // probabilities packed in place (pair i/2, i/2 + 1 are already consumed)
           rs[(i >> 1) + 1] = pack_bf162(e2, e3);
@@ -436,9 +456,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         lsum = softmax_exp64(rs, sl2, m_new, full, kmax);
       }
+      if (tr) attn_trace(p, 3, j);
       ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (tr) attn_trace(p, 4, j);
       // 64 probabilities = 128 bytes = the eight 16-byte chunks of this row in this half's panel; chunk index XOR (row % 8)
       // is the 128-byte swizzle the MMA descriptor expects
 #pragma unroll
@@ -448,10 +470,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                      : "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(p_full, lane);
+      if (tr) attn_trace(p, 5, j);
       l = l * alpha + lsum;
       m = m_new;
       // the previous tile's P.V has had this tile's softmax to finish under
       if (j > 0) ok = accumulate(j - 1, alpha_pending);
+      if (tr) attn_trace(p, 7, j);
       alpha_pending = alpha;
     }
     if (ok && n_tiles > 0) ok = accumulate(n_tiles - 1, alpha_pending);
@@ -717,10 +741,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int n_mine = n_t[t];
     const float sl2 = p.scale * LOG2E;
     const bool drop = p.drop_p > 0.f;
-    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const uint32_t thr = attn_drop_threshold(p.drop_p);
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
-    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
-    const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+    const uint32_t seed_hi = (uint32_t)(seed >> 32);
+    const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t t_s = lane_base + (uint32_t)(C::TMEM_S + t * 128);
     const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
@@ -801,11 +825,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         ls0 += e0; ls1 += e1; ls2 += e2; ls3 += e3;
         if (drop) {
-          const uint64_t z = attn_rand4(seed, row_base, (k0 + i) >> 2);
-          if ((uint32_t)(z & 0xFFFFu) < thr) e0 = 0.f;
-          if ((uint32_t)((z >> 16) & 0xFFFFu) < thr) e1 = 0.f;
-          if ((uint32_t)((z >> 32) & 0xFFFFu) < thr) e2 = 0.f;
-          if ((uint32_t)(z >> 48) < thr) e3 = 0.f;
+          const uint32_t z = attn_group_word(row_mix, seed_hi, (uint32_t)((k0 + i) >> 2));
+          if (z * ATT_RC0 < thr) e0 = 0.f;
+          if (z * ATT_RC1 < thr) e1 = 0.f;
+          if (z * ATT_RC2 < thr) e2 = 0.f;
+          if (z * ATT_RC3 < thr) e3 = 0.f;
         }
         rs[i >> 1] = pack_bf162(e0, e1);          // packed in place (registers i / 2, i / 2 + 1 are already consumed)
         rs[(i >> 1) + 1] = pack_bf162(e2, e3);
@@ -1169,9 +1193,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float sl2 = p.scale * LOG2E;
     const bool drop = p.drop_p > 0.f;
     const float inv_keep = drop ? 1.f / (1.f - p.drop_p) : 1.f;
-    const uint32_t thr = ffk_drop_threshold(p.drop_p);
+    const uint32_t thr = attn_drop_threshold(p.drop_p);
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
-    const unsigned long long groups_per_row = (unsigned long long)((p.Sk + 3) >> 2);
+    const uint32_t seed_hi = (uint32_t)(seed >> 32);
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t prow = smem_u32(smem + C::OFF_P + half * C::PANEL + r * 128);     // this row in this half's 64-key panel
     const uint32_t dsrow = smem_u32(smem + C::OFF_DS + half * C::PANEL + r * 128);
@@ -1184,7 +1208,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const long long stat = ((long long)(b * p.H + h)) * p.Sq + q;
       const float lse = row_ok ? p.lse[stat] : INFINITY;
       const float dlt = row_ok ? p.delta[stat] : 0.f;
-      const unsigned long long row_base = ((unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q) * groups_per_row;
+      const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
       int kmax = p.Sk - kbase;
       if (p.causal) kmax = min(kmax, q - kbase + 1);
       const bool full = kmax >= 64;     // every key of this half exists and is visible to this row
@@ -1216,9 +1240,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           pe[c * 16 + (i >> 1)] = pack_bf162(e[0], e[1]);
           pe[c * 16 + (i >> 1) + 1] = pack_bf162(e[2], e[3]);
           if (drop) {
-            const uint64_t z = attn_rand4(seed, row_base, (kbase + c * 32 + i) >> 2);
-            const uint32_t m = ((uint32_t)(z & 0xFFFFu) < thr ? 1u : 0u) | ((uint32_t)((z >> 16) & 0xFFFFu) < thr ? 2u : 0u) |
-                               ((uint32_t)((z >> 32) & 0xFFFFu) < thr ? 4u : 0u) | ((uint32_t)(z >> 48) < thr ? 8u : 0u);
+            const uint32_t z = attn_group_word(row_mix, seed_hi, (uint32_t)((kbase + c * 32 + i) >> 2));
+            const uint32_t m = (z * ATT_RC0 < thr ? 1u : 0u) | (z * ATT_RC1 < thr ? 2u : 0u) | (z * ATT_RC2 < thr ? 4u : 0u) |
+                               (z * ATT_RC3 < thr ? 8u : 0u);
             dropped[c] |= m << i;
             if (m & 1u) e[0] = 0.f;
             if (m & 2u) e[1] = 0.f;

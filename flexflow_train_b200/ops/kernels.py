@@ -352,30 +352,23 @@ def attention_bwd(q, k, v, out, lse, dout, dq, dk, dv, delta, acc, *, B, H, Sq, 
 
 
 def attention_keep_mask(B, H, Sq, Sk, p, salt, seed=None, device="cpu"):
-    """The dropout keep mask [B, H, Sq, Sk] (bool) the fused attention kernels draw: a host restatement of the
-    counter-based generator, for tests and debugging."""
-    M = (1 << 64) - 1
-
-    def u64(x):  # python int (mod 2^64) -> int64 tensor value
-        x &= M
-        return x - (1 << 64) if x >= (1 << 63) else x
-
-    sd = int(salt) & M
+    """The dropout keep mask [B, H, Sq, Sk] (bool) the fused attention kernels draw: a host restatement of their
+    counter-based generator (csrc/kernels/attention_sm100.cu: attn_row_mix / attn_group_word), for tests and debugging."""
+    M64, M32 = (1 << 64) - 1, (1 << 32) - 1
+    sd = int(salt) & M64
     if seed is not None:
-        sd = (sd * 0x9E3779B97F4A7C15 + int(seed)) & M
+        sd = (sd * 0x9E3779B97F4A7C15 + int(seed)) & M64
+    s0, s1 = sd & M32, sd >> 32
     groups = (Sk + 3) // 4
     rows = torch.arange(B * H * Sq, dtype=torch.int64, device=device)[:, None]
     g = torch.arange(groups, dtype=torch.int64, device=device)[None, :]
-    z = (rows * groups + g) * u64(0x9E3779B97F4A7C15) + u64(sd)
-
-    def lsr(x, n):  # logical shift right on int64
-        return (x >> n) & ((1 << (64 - n)) - 1)
-
-    z = (z ^ lsr(z, 30)) * u64(0xBF58476D1CE4E5B9)
-    z = (z ^ lsr(z, 27)) * u64(0x94D049BB133111EB)
-    z = z ^ lsr(z, 31)
-    thr = int(p * 65536.0)
-    fields = torch.stack([lsr(z, 16 * i) & 0xFFFF if i else z & 0xFFFF for i in range(4)], dim=-1)  # [rows, groups, 4]
+    row_mix = (s0 + (rows & M32) * 0x9E3779B9) & M32
+    a = (g * 0xB5297A4D + row_mix) & M32
+    m = a * 0xCC9E2D51                       # below 2^64: the int64 product wraps, the two 32-bit halves are still right
+    word = ((m & M32) ^ ((m >> 32) & M32) ^ s1) & M32
+    t = torch.tensor(float(p), dtype=torch.float32).item() * 4294967296.0   # the kernel scales the fp32 value of p (exact: a power of two)
+    thr = 0xFFFFFF00 if t >= 4294967040.0 else int(t)
+    fields = torch.stack([(word * c) & M32 for c in (0x9E3779B1, 0x85EBCA6B, 0xC2B2AE35, 0x27D4EB2F)], dim=-1)  # [rows, groups, 4]
     keep = (fields >= thr).reshape(B * H * Sq, groups * 4)[:, :Sk]
     return keep.reshape(B, H, Sq, Sk)
 
