@@ -144,6 +144,7 @@ __device__ __forceinline__ float softmax_exp64(uint32_t (&rs)[64], float sl2, fl
 }
 
 // ================================================================================================ forward
+constexpr float RESCALE_GAP = 8.f;      // log2 units the true row maximum may exceed the one in use
 template <int D>
 struct FwdCfg {
   static constexpr int PANELS = D / 64;              // 64-column (128-byte) panels per row of Q / K / V
@@ -308,21 +309,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
       if (ok && n_tiles > 0) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
         const int vt = j % C::NV;
         ok = mbar_wait(&v_full[vt], (uint32_t)(j / C::NV) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
-             mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
-             mbar_wait(&o_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+             mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         attn_trace(p, 21, j);
         tc_fence_after();
         const uint64_t dv = desc_advance(dv0, (uint32_t)(vt * C::KV_BYTES));
-        const uint32_t d_tmem = tmem_base + (uint32_t)(C::TMEM_O + t * D);
+        const uint32_t d_tmem = tmem_base + (uint32_t)C::TMEM_O;
         {
-          // A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
-          tc_mma_bf16<false>(d_tmem, dp, dv, C::IDESC_PV);
+          // O += P V.  A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
+          if (j == 0) tc_mma_bf16<false>(d_tmem, dp, dv, C::IDESC_PV);
+          else tc_mma_bf16<true>(d_tmem, dp, dv, C::IDESC_PV);
 #pragma unroll
           for (int ks = 1; ks < BKF / 16; ++ks) {
             const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
@@ -330,9 +329,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_mma_bf16<true>(d_tmem, desc_advance(dp, a_off), desc_advance(dv, b_off), C::IDESC_PV);
           }
         }
-        tc_commit(&o_full[t]);
         tc_commit(&v_empty[vt]);
-        tc_commit(p_empty);
+        tc_commit(p_empty);        // P(j) has been read and O holds tiles 0..j
         attn_trace(p, 22, j);
       }
     }
@@ -347,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quarter * 32 + lane;
     const int q = q0 + r;
     const float sl2 = p.scale * LOG2E;
-    float m = -INFINITY, l = 0.f;
+    float m = 0.f, l = 0.f;     // m: the maximum the row's exponentials are taken against (see RESCALE_GAP)
     const bool drop = p.drop_p > 0.f;   // kept a run-time value: as a compile-time constant the mask arithmetic is hoisted and spills
     const uint32_t thr = attn_drop_threshold(p.drop_p);
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
@@ -355,38 +353,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
     const uint32_t prow = smem_u32(smem + C::OFF_P + half * (BQ * 128) + r * 128);   // this row in this half's 64-key panel
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    float o[DH];
-#pragma unroll
-    for (int i = 0; i < DH; ++i) o[i] = 0.f;
-    float alpha_pending = 1.f;
+    const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + half * DH);   // this thread's half of its row of O
     bool ok = true;
-    // O += Opart of tile jj (rescaled by the factor that tile's softmax produced)
-    auto accumulate = [&](int jj, float alpha) -> bool {
-      const int t = jj & 1;
-      bool k_ = mbar_wait(&o_full[t], (uint32_t)(jj >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      k_ = __all_sync(0xffffffffu, k_);
-      if (!k_) return false;
-      if (warp == 2) attn_trace(p, 6, jj + 1);
-      tc_fence_after();
-      const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + t * D + half * DH);
-      uint32_t ra[32];
-      tmem_ld32(t_o, ra);
-#pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        tmem_ld_wait();
-        uint32_t rb[32];
-        if (c + 1 < DH / 32) tmem_ld32(t_o + (uint32_t)((c + 1) * 32), rb);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(ra[i]));
-        if (c + 1 < DH / 32) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ra[i] = rb[i];
-        }
-      }
-      tc_fence_before();
-      warp_arrive(&o_empty[t], lane);
-      return true;
-    };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int t = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
@@ -425,9 +393,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       pair_sync(quarter);
       const float other = xchg[(t * 2 + (half ^ 1)) * 128 + r];
       if (tr) attn_trace(p, 2, j);
-      float m_new = fmaxf(m, fmaxf(mine, other) * sl2);
-      if (m_new == -INFINITY) m_new = 0.f;        // nothing visible yet (padding rows only)
-      const float alpha = fast_exp2(m - m_new);
+      // The reference maximum only moves when the true maximum has grown past it by more than RESCALE_GAP (a factor 256,
+      // harmless in fp32 / bf16); then this thread rescales its columns of O in tensor memory before it publishes P, so the
+      // common step has no correction pass.  Both threads of a row see the same two maxima and take the same decision.
+      const float m_row = fmaxf(mine, other) * sl2;
+      bool need = false;
+      if (j == 0) m = m_row == -INFINITY ? 0.f : m_row;
+      else need = m_row > m + RESCALE_GAP;
+      bool waited = false;
+      if (__any_sync(0xffffffffu, need)) {
+        // O is complete up to tile j - 1 once the previous product has finished (the same event that frees the P buffer)
+        ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        waited = true;
+        tc_fence_after();
+        const float alpha = need ? fast_exp2(m - m_row) : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t ro[32];
+          tmem_ld32(t_o + (uint32_t)(c * 32), ro);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+          tmem_st32(t_o + (uint32_t)(c * 32), ro);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        l *= alpha;
+        if (need) m = m_row;
+      }
+      const float m_new = m;
       float lsum;
       if constexpr (DROP) {
         float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
@@ -457,9 +453,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         lsum = softmax_exp64(rs, sl2, m_new, full, kmax);
       }
       if (tr) attn_trace(p, 3, j);
-      ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!waited) {
+        ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
       if (tr) attn_trace(p, 4, j);
       // 64 probabilities = 128 bytes = the eight 16-byte chunks of this row in this half's panel; chunk index XOR (row % 8)
       // is the 128-byte swizzle the MMA descriptor expects
@@ -471,14 +469,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(p_full, lane);
       if (tr) attn_trace(p, 5, j);
-      l = l * alpha + lsum;
-      m = m_new;
-      // the previous tile's P.V has had this tile's softmax to finish under
-      if (j > 0) ok = accumulate(j - 1, alpha_pending);
-      if (tr) attn_trace(p, 7, j);
-      alpha_pending = alpha;
+      l += lsum;
     }
-    if (ok && n_tiles > 0) ok = accumulate(n_tiles - 1, alpha_pending);
+    if (ok && n_tiles > 0) {     // the last product has finished: O is complete
+      ok = mbar_wait(p_empty, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+    }
     if (ok) {
       // row sum over both halves, then out = O / (sum * keep probability); the half-0 thread stores the log-sum-exp
       xchg[half * 128 + r] = l;
@@ -488,14 +485,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float f = lt > 0.f ? inv_keep / lt : 0.f;
       if (q < p.Sq) {
         if (half == 0 && p.lse) p.lse[((long long)(b * p.H + h)) * p.Sq + q] = lt > 0.f ? m + log2f(lt) : INFINITY;
-        bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D + half * DH;
+      }
+      bf16 *orow = p.O + ((long long)b * p.Sq + q) * p.ldo + (long long)h * D + half * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t ro[32];
+        if (n_tiles > 0) {
+          tmem_ld32(t_o + (uint32_t)(c * 32), ro);     // warp-wide: rows past the end read too and store nothing
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int c = 0; c < DH / 8; ++c) {
-          uint4 v = make_uint4(pack_bf162(o[8 * c] * f, o[8 * c + 1] * f), pack_bf162(o[8 * c + 2] * f, o[8 * c + 3] * f),
-                               pack_bf162(o[8 * c + 4] * f, o[8 * c + 5] * f), pack_bf162(o[8 * c + 6] * f, o[8 * c + 7] * f));
-          *reinterpret_cast<uint4 *>(orow + 8 * c) = v;
+          for (int i = 0; i < 32; ++i) ro[i] = 0u;
+        }
+        if (q < p.Sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 v = make_uint4(pack_bf162(__uint_as_float(ro[8 * u]) * f, __uint_as_float(ro[8 * u + 1]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 2]) * f, __uint_as_float(ro[8 * u + 3]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 4]) * f, __uint_as_float(ro[8 * u + 5]) * f),
+                                 pack_bf162(__uint_as_float(ro[8 * u + 6]) * f, __uint_as_float(ro[8 * u + 7]) * f));
+            *reinterpret_cast<uint4 *>(orow + c * 32 + 8 * u) = v;
+          }
         }
       }
+      tc_fence_before();
     }
   }
 
@@ -543,7 +556,6 @@ struct Fwd2Cfg {
 };
 
 constexpr int FWD2_THREADS = 576;
-constexpr float RESCALE_GAP = 8.f;      // log2 units the true row maximum may exceed the one in use
 
 template <int D, bool P_TMEM>
 __global__ void __launch_bounds__(FWD2_THREADS, 1)
