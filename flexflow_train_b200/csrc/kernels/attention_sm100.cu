@@ -12,9 +12,8 @@
 // Layouts.  Q, K, V, O, dO, dQ, dK, dV are [batch * seq, ld] bf16 matrices in which head h occupies the D
 // columns starting at h * D (so the packed output of one QKV projection GEMM is used as it lies); D is 64 or 128.
 //
-// Dropout is counter based: element (b, h, q, k) is kept when 16 bits of hash(seed, row * ceil(Sk / 4) + k / 4),
-// row = (b * H + h) * Sq + q, selected by k % 4, are >= p * 65536 (common.cuh: ffk_rand16x4), so backward
-// regenerates the mask.  The 1 / (1 - p) factor is applied once per output row / gradient tile.
+// Dropout is counter based: element (b, h, q, k) is kept when word(seed, row, k / 4) * RC[k % 4] (mod 2^32) is at least
+// p * 2^32, row = (b * H + h) * Sq + q (attn_group_word below), so backward regenerates the mask.  The 1 / (1 - p) factor is applied once per output row / gradient tile.
 //
 // Forward CTA (320 threads) = one 128-query block of one (batch, head):
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through a two-stage ring
