@@ -1121,10 +1121,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint64_t dDS_kmaj = make_smem_desc(smem_u32(smem + C::OFF_DS), 16, 1024);
       // byte offset of k-step ks inside a K-major tile: 64-column panel, then 32 bytes per step
       auto koff = [](int ks) -> uint32_t { return (uint32_t)((ks >> 2) * C::PANEL + (ks & 3) * 32); };
-      auto issue_s = [&](int it) -> bool {      // S = Q_it K^T
+      // S = Q_it K^T.  `try_only`: issue only if the Q tile has arrived and the previous scores have been read, without waiting.
+      auto issue_s = [&](int it, bool try_only) -> int {      // 1 issued, 0 not yet (try_only), -1 a wait ran out
         const int s = it & 1;
-        if (!mbar_wait(&q_full[s], (uint32_t)(it >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
-        if (!mbar_wait(s_empty, ((uint32_t)it & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
+        if (try_only) {
+          if (!mbar_try_wait(&q_full[s], (uint32_t)(it >> 1) & 1u) || !mbar_try_wait(s_empty, ((uint32_t)it & 1u) ^ 1u)) return 0;
+        } else {
+          if (!mbar_wait(&q_full[s], (uint32_t)(it >> 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return -1;
+          if (!mbar_wait(s_empty, ((uint32_t)it & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return -1;
+        }
         tc_fence_after();
         const uint64_t a = desc_advance(dQ_kmaj0, (uint32_t)(s * C::TILE_BYTES));
         const uint32_t d = tmem_base + (uint32_t)C::TMEM_S;
@@ -1132,7 +1137,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int ks = 1; ks < D / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(a, koff(ks)), desc_advance(dK_kmaj, koff(ks)), C::IDESC_SS);
         tc_commit(s_full);
-        return true;
+        attn_trace(p, 23, it);
+        return 1;
+      };
+      // Waits for `bar` like mbar_wait; while it waits, the next step's S is issued as soon as it can be (pending_s is then
+      // cleared): the probability warps can work on step it + 1 while the tensor core still runs the products of step it.
+      bool pending_s = false;
+      int next_it = 0;
+      auto wait_issuing_s = [&](uint64_t *bar, uint32_t parity) -> bool {
+        uint64_t t0 = ffk_globaltimer();
+        uint32_t spins = 0;
+        while (true) {
+          if (pending_s) {
+            const int r = issue_s(next_it, true);
+            if (r > 0) pending_s = false;
+          }
+          if (mbar_try_wait(bar, parity)) return true;
+          if ((++spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (ffk_globaltimer() - t0 > WAIT_LIMIT_NS) {
+              *abort_flag = 1;
+              if (p.err) atomicCAS(p.err, 0, (int)FFK_ERR_TIMEOUT_MMA);
+              return false;
+            }
+          }
+        }
       };
       auto issue_dp = [&](int it) -> bool {     // dP = dO_it V^T, into the columns the previous step's dQ^T has left
         if (!mbar_wait(do_full, (uint32_t)it & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
@@ -1143,13 +1172,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int ks = 1; ks < D / 16; ++ks) tc_mma_bf16<true>(d, desc_advance(dDO_kmaj, koff(ks)), desc_advance(dV_kmaj, koff(ks)), C::IDESC_SS);
         tc_commit(dp_full);
+        attn_trace(p, 24, it);
         return true;
       };
-      if (ok && n_it > 0) ok = issue_s(0) && issue_dp(0);
+      if (ok && n_it > 0) ok = issue_s(0, false) > 0 && issue_dp(0);
       for (int it = 0; it < n_it && ok; ++it) {
         const uint32_t ph = (uint32_t)it & 1u;
+        pending_s = it + 1 < n_it;
+        next_it = it + 1;
         // dV += P^T dO_it
-        ok = mbar_wait(p_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        ok = wait_issuing_s(p_full, ph);
         if (!ok) break;
         tc_fence_after();
         {
@@ -1161,9 +1193,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_commit(p_empty);
         tc_commit(do_empty);
+        attn_trace(p, 20, it);
         // dQ_it^T = K^T dS^T (the dS warps have read dP out of these columns before they wrote dS)
-        ok = mbar_wait(ds_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+        ok = wait_issuing_s(ds_full, ph);
         if (!ok) break;
+        attn_trace(p, 21, it);
         tc_fence_after();
         {
           const uint32_t d = tmem_base + (uint32_t)C::TMEM_DPQ;
@@ -1191,7 +1225,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_commit(ds_empty);
         tc_commit(&q_empty[it & 1]);
-        if (it + 1 < n_it) ok = issue_s(it + 1) && issue_dp(it + 1);
+        attn_trace(p, 22, it);
+        if (it + 1 < n_it) ok = (!pending_s || issue_s(it + 1, false) > 0) && issue_dp(it + 1);
       }
       if (ok) tc_commit(dkv_full);
     }
@@ -1227,6 +1262,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
            mbar_wait(p_empty, ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (warp == 2) attn_trace(p, 0, it);
       tc_fence_after();
       uint32_t pe[32];          // the row's 64 probabilities before dropout, packed bf16 (dS needs them again)
       uint32_t dropped[2] = {0u, 0u};
@@ -1272,11 +1308,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(p_full, lane);
+      if (warp == 2) attn_trace(p, 1, it);
       // dS = P o (dP o keep / keep_prob - delta)
       ok = mbar_wait(dp_full, ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE) &&
            mbar_wait(ds_empty, ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (warp == 2) attn_trace(p, 2, it);
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -1303,6 +1341,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       warp_arrive(ds_full, lane);
+      if (warp == 2) attn_trace(p, 3, it);
     }
     // dK and dV of this key block: thread = key row x 64 of the 128 head-dim columns
     if (ok && n_it > 0) {
@@ -1356,6 +1395,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(dq_full, (uint32_t)it & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (warp == 10) attn_trace(p, 10, it);
       tc_fence_after();
       if constexpr (D == 128) {
         const int dcol = quarter * 32 + lane;
@@ -1365,6 +1405,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
         tc_fence_before();
         warp_arrive(dq_empty, lane);
+        if (warp == 10) attn_trace(p, 11, it);
         const int qb0 = (i0 + it) * BQ + qhalf * 64;
         const int qn = p.Sq - qb0;               // queries of this half that exist
         float *dst = acc_head + (long long)qb0 * D + dcol;
@@ -1374,6 +1415,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; ++i)
           if (32 + i < qn) atomicAdd(dst + (32 + i) * D, __uint_as_float(rb[i]) * p.scale);
+        if (warp == 10) attn_trace(p, 12, it);
       } else {
         uint32_t ra[32];
         tmem_ld32(lane_base + (uint32_t)(C::TMEM_DPQ + qhalf * 32), ra);
@@ -1566,6 +1608,7 @@ FFK_API int ffk_attention_bwd(const FfkAttnDesc *d, cudaStream_t stream) {
   void *errp = nullptr;
   cudaGetSymbolAddress(&errp, g_attn_err);
   a.err = (int *)errp;
+  { const char *e = getenv("FFK_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
   return d->D == 128 ? launch_bwd<128>(d, a, stream) : launch_bwd<64>(d, a, stream);
 }
 
