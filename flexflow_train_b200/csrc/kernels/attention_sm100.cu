@@ -334,14 +334,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d_tmem = tmem_base + (uint32_t)C::TMEM_O;
         {
           // O += P V.  A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
-          if (j == 0) tc_mma_bf16<false>(d_tmem, dp, dv, C::IDESC_PV);
-          else tc_mma_bf16<true>(d_tmem, dp, dv, C::IDESC_PV);
+          // P(j) lies in the first 64 columns of the tensor-memory buffer its scores came from (bf16 pairs, 8 columns per
+          // step of 16 keys); S(j + 2), which overwrites that buffer, is issued after this product and runs after it
+          const uint32_t a_tmem = tmem_base + (uint32_t)(C::TMEM_S + (j & 1) * 128);
+          if (j == 0) tc_mma_ts_bf16<false>(d_tmem, a_tmem, dv, C::IDESC_PV);
+          else tc_mma_ts_bf16<true>(d_tmem, a_tmem, dv, C::IDESC_PV);
 #pragma unroll
-          for (int ks = 1; ks < BKF / 16; ++ks) {
-            const uint32_t a_off = (uint32_t)((ks >> 2) * (BQ * 128) + (ks & 3) * 32);
-            const uint32_t b_off = (uint32_t)(ks * 16 * 128);
-            tc_mma_bf16<true>(d_tmem, desc_advance(dp, a_off), desc_advance(dv, b_off), C::IDESC_PV);
-          }
+          for (int ks = 1; ks < BKF / 16; ++ks)
+            tc_mma_ts_bf16<true>(d_tmem, a_tmem + (uint32_t)(ks * 8), desc_advance(dv, (uint32_t)(ks * 16 * 128)), C::IDESC_PV);
         }
         tc_commit(&v_empty[vt]);
         tc_commit(p_empty);        // P(j) has been read and O holds tiles 0..j
@@ -467,20 +467,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         lsum = softmax_exp64(rs, sl2, m_new, full, kmax);
       }
       if (tr) attn_trace(p, 3, j);
-      if (!waited) {
-        ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
       if (tr) attn_trace(p, 4, j);
-      // 64 probabilities = 128 bytes = the eight 16-byte chunks of this row in this half's panel; chunk index XOR (row % 8)
-      // is the 128-byte swizzle the MMA descriptor expects
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)((u ^ (r & 7)) << 4)), "r"(rs[4 * u]), "r"(rs[4 * u + 1]),
-                     "r"(rs[4 * u + 2]), "r"(rs[4 * u + 3])
-                     : "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // 64 probabilities = 32 columns of bf16 pairs: half 0 writes columns 0-31, half 1 columns 32-63 of this row of S(j)'s
+      // buffer.  Those columns held half 0's scores, which are in registers since the exchange above.
+      tmem_st32(lane_base + (uint32_t)(C::TMEM_S + t * 128 + half * 32), *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
+      tmem_st_wait();
+      tc_fence_before();
       warp_arrive(p_full, lane);
       if (tr) attn_trace(p, 5, j);
       l += lsum;
