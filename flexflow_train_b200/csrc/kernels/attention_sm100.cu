@@ -164,20 +164,19 @@ struct FwdCfg {
   static constexpr int PANELS = D / 64;              // 64-column (128-byte) panels per row of Q / K / V
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int KV_BYTES = BKF * D * 2;       // one K or one V tile
-  static constexpr int P_BYTES = BQ * BKF * 2;       // 32 KB
-  // A K tile is free again once the scores of its step are computed, a V tile only at the end of its step: the V ring
-  // is one stage deeper so that its loads also run a full step ahead.
-  static constexpr int NK = 2, NV = 3;
+  // Three stages each: the score product runs two key tiles ahead of the softmax, a V tile is needed one step after its K tile
+  static constexpr int NK = 3, NV = 3;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + NK * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + NV * KV_BYTES;
-  static constexpr int OFF_XCHG = OFF_P + P_BYTES;           // [2 tile parities][2 column halves][128 rows] floats
+  static constexpr int OFF_XCHG = OFF_V + NV * KV_BYTES;     // [2 tile parities][2 column halves][128 rows] floats
   static constexpr int OFF_BAR = OFF_XCHG + 4 * 128 * 4;
   static constexpr int SLACK = D == 128 ? 768 : 1024;        // room to align the base to 1024 bytes (checked in the kernel)
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + SLACK;
-  static constexpr int TMEM_S = 0;                           // S[t] at columns t * 128
-  static constexpr int TMEM_O = 256;                         // Opart[t] at columns 256 + t * D
+  static constexpr int NS = 3;                               // score buffers S[j % 3] at tensor-memory columns (j % 3) * 128;
+  static constexpr int TMEM_S = 0;                           // P(j) overwrites the first 64 columns of its own buffer
+  static constexpr int TMEM_O = 384;                         // O, D columns
+  static_assert(SMEM_BYTES <= 232448, "forward tiles exceed the shared memory of one CTA");
   static constexpr uint32_t IDESC_S = attn_idesc(128, BKF, 0, 0);
   static constexpr uint32_t IDESC_PV = attn_idesc(128, D, 0, 1);
 };
@@ -196,16 +195,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float *xchg = (float *)(smem + C::OFF_XCHG);       // [2][2][128]
   uint64_t *bars = (uint64_t *)(smem + C::OFF_BAR);
   uint64_t *q_full = bars;            // 1
-  uint64_t *k_full = bars + 1;        // [2]
-  uint64_t *k_empty = bars + 5;       // [2]
+  uint64_t *k_full = bars + 1;        // [NK]
+  uint64_t *k_empty = bars + 5;       // [NK]
   uint64_t *v_full = bars + 19;       // [NV]
   uint64_t *v_empty = bars + 22;      // [NV]
-  uint64_t *s_full = bars + 9;        // [2]
-  uint64_t *s_empty = bars + 11;      // [2] 8 warps
-  uint64_t *p_full = bars + 13;       // 8 warps
-  uint64_t *p_empty = bars + 14;      // commit
-  uint64_t *o_full = bars + 15;       // [2] commit
-  uint64_t *o_empty = bars + 17;      // [2] 8 warps
+  uint64_t *s_full = bars + 9;        // [NS]
+  uint64_t *s_empty = bars + 15;      // [NS] 8 warps
+  // The softmax warps may run up to two key tiles apart (the score products are issued two tiles ahead), so the barriers
+  // they arrive on or wait for by parity exist once per score buffer: a single one could count an early arrival into the
+  // previous phase, or answer a wait for product j - 1 with the completion of product j - 3.
+  uint64_t *p_full = bars + 26;       // [NS] 8 warps: P(j) is in tensor memory
+  uint64_t *pv_done = bars + 29;      // [NS] commit: P(j) has been read and O holds key tiles 0..j
   uint32_t *tmem_slot = (uint32_t *)(bars + 25);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
   if ((uintptr_t)(smem - smem_raw) > (uintptr_t)C::SLACK) {  // the launch did not leave room to align the tiles: refuse
@@ -227,12 +227,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 8);
-    }
+    for (int s = 0; s < C::NK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < C::NS; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); }
     for (int s = 0; s < C::NV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    mbar_init(p_full, 8); mbar_init(p_empty, 1);
+    for (int s = 0; s < C::NS; ++s) { mbar_init(&p_full[s], 8); mbar_init(&pv_done[s], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -298,11 +296,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // descriptors are built once; an MMA then costs two adds
       const uint64_t dq = make_smem_desc(smem_u32(smem + C::OFF_Q), 16, 1024);
       const uint64_t dk0 = make_smem_desc(smem_u32(smem + C::OFF_K), 16, 1024);
-      const uint64_t dp = make_smem_desc(smem_u32(smem + C::OFF_P), 16, 1024);
       const uint64_t dv0 = make_smem_desc(smem_u32(smem + C::OFF_V), BKF * 128, 1024);
+      // S(j) = Q K_j^T into buffer j % 3.  That buffer held S(j - 3) and then P(j - 3): the softmax warps have read the former
+      // (s_empty) and the product that reads the latter was issued before this one, and products run in issue order.
       auto issue_s = [&](int j) -> bool {
-        const int t = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const int t = j % C::NS;
+        const uint32_t ph = (uint32_t)(j / C::NS) & 1u;
         if (!mbar_wait(&k_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         if (!mbar_wait(&s_empty[t], ph ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
@@ -321,12 +320,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         attn_trace(p, 20, j);
         return true;
       };
+      // the score products run two key tiles ahead, so the softmax of tile j + 1 never waits for the tensor core
       if (ok && n_tiles > 0) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+        if (j + 2 < n_tiles) { ok = issue_s(j + 2); if (!ok) break; }
         const int vt = j % C::NV;
         ok = mbar_wait(&v_full[vt], (uint32_t)(j / C::NV) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA) &&
-             mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
+             mbar_wait(&p_full[j % C::NS], (uint32_t)(j / C::NS) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_MMA);
         if (!ok) break;
         attn_trace(p, 21, j);
         tc_fence_after();
@@ -335,8 +336,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         {
           // O += P V.  A = P (K-major, two panels of 64 keys); B = V (N = head dim contiguous: MN-major, 16 key rows per step)
           // P(j) lies in the first 64 columns of the tensor-memory buffer its scores came from (bf16 pairs, 8 columns per
-          // step of 16 keys); S(j + 2), which overwrites that buffer, is issued after this product and runs after it
-          const uint32_t a_tmem = tmem_base + (uint32_t)(C::TMEM_S + (j & 1) * 128);
+          // step of 16 keys)
+          const uint32_t a_tmem = tmem_base + (uint32_t)(C::TMEM_S + (j % C::NS) * 128);
           if (j == 0) tc_mma_ts_bf16<false>(d_tmem, a_tmem, dv, C::IDESC_PV);
           else tc_mma_ts_bf16<true>(d_tmem, a_tmem, dv, C::IDESC_PV);
 #pragma unroll
@@ -344,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_mma_ts_bf16<true>(d_tmem, a_tmem + (uint32_t)(ks * 8), desc_advance(dv, (uint32_t)(ks * 16 * 128)), C::IDESC_PV);
         }
         tc_commit(&v_empty[vt]);
-        tc_commit(p_empty);        // P(j) has been read and O holds tiles 0..j
+        tc_commit(&pv_done[j % C::NS]);
         attn_trace(p, 22, j);
       }
     }
@@ -365,13 +366,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const unsigned long long seed = drop ? attn_seed(p) : 0ull;
     const uint32_t seed_hi = (uint32_t)(seed >> 32);
     const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
-    const uint32_t prow = smem_u32(smem + C::OFF_P + half * (BQ * 128) + r * 128);   // this row in this half's 64-key panel
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t t_o = lane_base + (uint32_t)(C::TMEM_O + half * DH);   // this thread's half of its row of O
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int t = j & 1;
-      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      const int t = j % C::NS;
+      const uint32_t ph = (uint32_t)(j / C::NS) & 1u;
+      const int xp = j & 1;              // parity of the exchange slots
       ok = mbar_wait(&s_full[t], ph, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -403,9 +404,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 64; ++i) mx0 = fmaxf(mx0, i < kmax ? __uint_as_float(rs[i]) : -INFINITY);
       }
       const float mine = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      xchg[(t * 2 + half) * 128 + r] = mine;
+      xchg[(xp * 2 + half) * 128 + r] = mine;
       pair_sync(quarter);
-      const float other = xchg[(t * 2 + (half ^ 1)) * 128 + r];
+      const float other = xchg[(xp * 2 + (half ^ 1)) * 128 + r];
       if (tr) attn_trace(p, 2, j);
       // The reference maximum only moves when the true maximum has grown past it by more than RESCALE_GAP (a factor 256,
       // harmless in fp32 / bf16); then this thread rescales its columns of O in tensor memory before it publishes P, so the
@@ -414,13 +415,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool need = false;
       if (j == 0) m = m_row == -INFINITY ? 0.f : m_row;
       else need = m_row > m + RESCALE_GAP;
-      bool waited = false;
       if (__any_sync(0xffffffffu, need)) {
         // O is complete up to tile j - 1 once the previous product has finished (the same event that frees the P buffer)
-        ok = mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+        ok = mbar_wait(&pv_done[(j - 1) % C::NS], (uint32_t)((j - 1) / C::NS) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        waited = true;
         tc_fence_after();
         const float alpha = need ? fast_exp2(m - m_row) : 1.f;
 #pragma unroll 1
@@ -473,12 +472,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_st32(lane_base + (uint32_t)(C::TMEM_S + t * 128 + half * 32), *reinterpret_cast<uint32_t(*)[32]>(&rs[0]));
       tmem_st_wait();
       tc_fence_before();
-      warp_arrive(p_full, lane);
+      warp_arrive(&p_full[t], lane);
       if (tr) attn_trace(p, 5, j);
       l += lsum;
     }
     if (ok && n_tiles > 0) {     // the last product has finished: O is complete
-      ok = mbar_wait(p_empty, (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
+      ok = mbar_wait(&pv_done[(n_tiles - 1) % C::NS], (uint32_t)((n_tiles - 1) / C::NS) & 1u, abort_flag, p.err, FFK_ERR_TIMEOUT_EPILOGUE);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
     }
