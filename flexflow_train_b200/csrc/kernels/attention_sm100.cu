@@ -6,20 +6,24 @@
 // (lib/kernels/src/cuda/ops/attention_kernels.cu:224-285: cudnnMultiHeadAttnForward / BackwardData /
 // BackwardWeights) for the score / softmax / context part; the projections stay GEMMs.  The [Sq, Sk] score
 // matrix never exists in global memory: scores are produced by tcgen05.mma into tensor memory (TMEM), turned into
-// probabilities by one thread per query row, written as bf16 into shared memory and multiplied with V by the
-// tensor core again.  Only the row log-sum-exp is kept for backward, which recomputes the scores tile by tile.
+// probabilities by two threads per query row and multiplied with V by the tensor core again (forward: the bf16
+// probabilities go back into tensor memory and are the A operand of the second product from there; backward: through
+// shared memory).  Only the row log-sum-exp is kept for backward, which recomputes the scores tile by tile.
 //
 // Layouts.  Q, K, V, O, dO, dQ, dK, dV are [batch * seq, ld] bf16 matrices in which head h occupies the D
 // columns starting at h * D (so the packed output of one QKV projection GEMM is used as it lies); D is 64 or 128.
 //
 // Dropout is counter based: element (b, h, q, k) is kept when word(seed, row, k / 4) * RC[k % 4] (mod 2^32) is at least
-// p * 2^32, row = (b * H + h) * Sq + q (attn_group_word below), so backward regenerates the mask.  The 1 / (1 - p) factor is applied once per output row / gradient tile.
+// p * 2^32, row = (b * H + h) * Sq + q (attn_group_word below), so backward regenerates the mask.  The 1 / (1 - p) factor is
+// applied once per output row / gradient tile.
 //
 // Forward CTA (320 threads) = one 128-query block of one (batch, head):
-//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through a two-stage ring
-//   warp 1      MMA issuer:   S[t] = Q K_j^T   (TMEM, two stages)   and   Opart[t] = P_j V_j   (TMEM, two stages)
-//   warps 2-9   softmax and output: thread = query row x half of the tile's keys (and half of the output columns);
-//               running max / sum, P_j -> shared memory (bf16, 128-byte swizzle), O = O * alpha_j + Opart[t] in registers
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through three-stage rings
+//   warp 1      MMA issuer:   S[j % 3] = Q K_j^T, issued two key tiles ahead (TMEM, three buffers), and O += P_j V_j (TMEM)
+//   warps 2-9   softmax: thread = query row x half of the tile's keys; the row maximum is exchanged between the two halves,
+//               P_j (bf16) overwrites the first 64 columns of S[j % 3]; the exponentials are taken against a reference
+//               maximum that only moves when the true maximum has grown by more than 2^8, in which case the thread rescales
+//               its half of the row of O in tensor memory; at the end O / sum is written out
 //
 // Backward CTA (576 threads) = one 128-key block of one (batch, head), walking over the query blocks that see it (see the
 // comment at the backward kernel): dK and dV accumulate in tensor memory and are written once; the dQ contributions of the
@@ -350,7 +354,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + output accumulation
+    // ------------------------------------------------------------------ softmax, rescale and read-out of O
     // Eight warps: warp w works on TMEM lane quarter w % 4 (a hardware rule) and on column half (w - 2) / 4, so a thread is
     // one query row and 64 of the tile's 128 keys (and D / 2 of the output columns).  Two warps per scheduler hide each
     // other's TMEM-load and special-function latencies; the row maximum is the only thing the two halves must agree on
