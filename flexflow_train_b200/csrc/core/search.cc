@@ -8,6 +8,8 @@
 #include <queue>
 #include <set>
 
+#include <pybind11/functional.h>
+
 #include "pyjson.h"
 
 namespace ff {
@@ -891,11 +893,50 @@ SearchResult unity_search(const Graph &start, const MachineSpec &m, const CostEs
 }
 
 // ---------------------------------------------------------------- simulator
+std::vector<TaskProfile> simulate_task_graph_execution(int n, const std::vector<std::pair<int, int>> &edges, const std::vector<double> &cost,
+                                                       const TaskConstraint &allowed) {
+  if ((int)cost.size() != n) throw Error("simulate_task_graph_execution: one cost per task is needed");
+  std::vector<std::vector<int>> succ(n);
+  std::vector<int> missing(n, 0);
+  for (auto &e : edges) {
+    if (e.first < 0 || e.first >= n || e.second < 0 || e.second >= n) throw Error("simulate_task_graph_execution: edge endpoint out of range");
+    succ[e.first].push_back(e.second);
+    ++missing[e.second];
+  }
+  std::set<int> ready, in_progress, finished;
+  for (int t = 0; t < n; ++t)
+    if (missing[t] == 0) ready.insert(t);
+  std::vector<TaskProfile> trace(n, TaskProfile{-1, 0, 0});
+  std::multimap<double, int> running;   // end time -> task
+  double now = 0;
+  while ((int)finished.size() < n) {
+    // offer the ready tasks in index order; a start changes what the constraint sees, so go round until nothing starts
+    for (bool started = true; started;) {
+      started = false;
+      for (int t : std::vector<int>(ready.begin(), ready.end())) {
+        if (!allowed(t, in_progress, finished)) continue;
+        ready.erase(t);
+        in_progress.insert(t);
+        trace[t] = TaskProfile{t, now, now + cost[t]};
+        running.emplace(now + cost[t], t);
+        started = true;
+      }
+    }
+    if (running.empty()) throw Error("simulate_task_graph_execution: " + std::to_string(n - (int)finished.size()) + " tasks can never start (cycle, or the constraint refuses them with nothing running)");
+    now = running.begin()->first;
+    while (!running.empty() && running.begin()->first == now) {
+      const int t = running.begin()->second;
+      running.erase(running.begin());
+      in_progress.erase(t);
+      finished.insert(t);
+      for (int s2 : succ[t])
+        if (--missing[s2] == 0) ready.insert(s2);
+    }
+  }
+  return trace;
+}
+
 double simulate_task_graph(const Graph &g, const MachineSpec &m, const CostEstimator &est, bool include_backward) {
-  // forward tasks in topological order; list scheduling: a task starts when its producers (plus the
-  // transfers between differing device sets) are done and all of its devices are free
-  std::map<NodeId, double> finish;
-  std::map<int, double> device_free;
   auto devices_of = [&](NodeId n) {
     const Node &nd = g.node(n);
     auto ts = operator_task_space(nd, g);
@@ -904,45 +945,69 @@ double simulate_task_graph(const Graph &g, const MachineSpec &m, const CostEstim
       auto vs = allowed_machine_views(ts, Resources{0, m.num_devices()}, m);
       if (!vs.empty()) v = vs.front();
     }
-    return view_devices(v, ts, m);
+    auto d = view_devices(v, ts, m);
+    std::sort(d.begin(), d.end());
+    return d;
   };
   auto order = g.topological_order();
   std::map<NodeId, std::vector<int>> devs;
   for (NodeId n : order) devs[n] = devices_of(n);
-  auto run = [&](NodeId n, double ready, double dur) {
-    double start = ready;
-    for (int d : devs[n]) start = std::max(start, device_free[d]);
-    double end = start + dur;
-    for (int d : devs[n]) device_free[d] = end;
-    return end;
-  };
-  auto comm = [&](NodeId a, NodeId b) {
-    auto da = devs[a], db = devs[b];
-    std::sort(da.begin(), da.end());
-    std::sort(db.begin(), db.end());
+  auto comm_ms = [&](NodeId a, NodeId b) {   // movement of a's outputs that b consumes, 0 when b's devices already hold them
+    const auto &da = devs[a], &db = devs[b];
     if (da == db || std::includes(da.begin(), da.end(), db.begin(), db.end())) return 0.0;
     double bytes = 0;
     for (auto &e : g.node(b).inputs) if (e.src.node == a) bytes += (double)g.shape(e.src).piece_bytes();
     return est.movement_cost_ms(bytes, da.front() / m.num_gpus_per_node != db.front() / m.num_gpus_per_node);
   };
+  // tasks: forward operator tasks in topological order, then (optionally) backward operator tasks, then movement tasks
+  std::vector<double> cost;
+  std::vector<std::vector<int>> task_devs;   // empty = unconstrained (movement)
+  std::vector<std::pair<int, int>> edges;
+  std::map<NodeId, int> fwd, bwd;
   for (NodeId n : order) {
-    double ready = 0;
-    for (auto &e : g.node(n).inputs) ready = std::max(ready, finish[e.src.node] + comm(e.src.node, n));
-    finish[n] = run(n, ready, est.op_cost(g.node(n), g).fwd_ms);
+    fwd[n] = (int)cost.size();
+    cost.push_back(est.op_cost(g.node(n), g).fwd_ms);
+    task_devs.push_back(devs[n]);
   }
+  if (include_backward)
+    for (NodeId n : order) {
+      bwd[n] = (int)cost.size();
+      cost.push_back(est.op_cost(g.node(n), g).bwd_ms);
+      task_devs.push_back(devs[n]);
+    }
+  auto link = [&](int from, int to, double ms) {
+    if (ms <= 0) { edges.push_back({from, to}); return; }
+    const int c = (int)cost.size();
+    cost.push_back(ms);
+    task_devs.push_back({});
+    edges.push_back({from, c});
+    edges.push_back({c, to});
+  };
+  std::vector<int> sinks;
+  for (NodeId n : order) {
+    std::set<NodeId> producers;
+    for (auto &e : g.node(n).inputs) producers.insert(e.src.node);
+    for (NodeId a : producers) {
+      const double ms = comm_ms(a, n);
+      link(fwd[a], fwd[n], ms);
+      if (include_backward) link(bwd[n], bwd[a], ms);   // the gradient goes back over the same pieces
+    }
+    if (g.successors(n).empty()) sinks.push_back(fwd[n]);
+  }
+  if (include_backward)   // backward starts when the whole forward pass has finished (the loss needs every output)
+    for (NodeId n : order)
+      if (g.successors(n).empty())
+        for (int s2 : sinks) edges.push_back({s2, bwd[n]});
+  auto allowed = [&](int t, const std::set<int> &in_progress, const std::set<int> &) {
+    if (task_devs[t].empty()) return true;
+    for (int r : in_progress)
+      for (int d : task_devs[r])
+        if (std::binary_search(task_devs[t].begin(), task_devs[t].end(), d)) return false;
+    return true;
+  };
   double makespan = 0;
-  for (auto &kv : finish) makespan = std::max(makespan, kv.second);
-  if (!include_backward) return makespan;
-  std::map<NodeId, double> bfinish;
-  for (auto it = order.rbegin(); it != order.rend(); ++it) {
-    NodeId n = *it;
-    double ready = makespan;
-    for (NodeId s : g.successors(n)) ready = std::max(ready, bfinish[s] + comm(n, s));
-    bfinish[n] = run(n, ready, est.op_cost(g.node(n), g).bwd_ms);
-  }
-  double total = makespan;
-  for (auto &kv : bfinish) total = std::max(total, kv.second);
-  return total;
+  for (auto &tp : simulate_task_graph_execution((int)cost.size(), edges, cost, allowed)) makespan = std::max(makespan, tp.end);
+  return makespan;
 }
 
 // ---------------------------------------------------------------- MCMC
@@ -1134,6 +1199,14 @@ void bind_search(py::module &m) {
     return result_to_py(mcmc_search(g, ms, est, rules, c));
   }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("temperature") = 1.0, py::arg("num_iterations") = 100,
         py::arg("substitution_frequency") = 0.2, py::arg("seed") = 0, py::arg("relative_temperature") = false);
+  m.def("simulate_task_graph_execution",
+        [](int n, const std::vector<std::pair<int, int>> &edges, const std::vector<double> &cost, const TaskConstraint &allowed) {
+          std::vector<std::tuple<int, double, double>> out;
+          for (auto &tp : simulate_task_graph_execution(n, edges, cost, allowed)) out.emplace_back(tp.task, tp.start, tp.end);
+          return out;
+        },
+        py::arg("num_tasks"), py::arg("edges"), py::arg("cost"), py::arg("allowed"),
+        "event-driven execution of a task graph; allowed(task, in_progress, finished) -> bool; returns [(task, start, end)]");
   m.def("simulate_task_graph", &simulate_task_graph, py::arg("mapped_pcg"), py::arg("machine"), py::arg("estimator"),
         py::arg("include_backward") = false);
   m.def("mapped_pcg_from_pcg_and_mapping", [](const Graph &g, py::dict mapping) {

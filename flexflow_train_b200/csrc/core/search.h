@@ -6,6 +6,8 @@
 // unity_algorithm/unity_algorithm.cc:51-146, mcmc/mcmc_over_mapped_pcg.cc:18-66,
 // task_graph_simulator/task_simulator.cc:23-75, cost_estimator/cost_estimator.h:14-41.
 #pragma once
+#include <functional>
+#include <set>
 #include <map>
 #include <memory>
 #include <optional>
@@ -150,8 +152,21 @@ struct MCMCConfig {
 SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
                          const MCMCConfig &cfg);
 
-// Event-driven simulation of a mapped PCG: operator tasks occupy their devices exclusively, communication
-// tasks run unconstrained.  include_backward also schedules the mirrored backward tasks and the weight updates.
+// Event-driven execution of a task graph (reference: compiler/task_graph_simulator/simulate_task_graph_execution.cc).  Tasks
+// 0..n-1 with durations `cost`, precedence `edges` (before, after).  A task whose predecessors have finished starts as soon
+// as `allowed(task, in_progress, finished)` says so; ready tasks are offered in index order, again after every start and every
+// completion; tasks that end at the same time complete together.  Throws when tasks remain that may never start.
+struct TaskProfile {
+  int task;
+  double start, end;
+};
+using TaskConstraint = std::function<bool(int, const std::set<int> &, const std::set<int> &)>;
+std::vector<TaskProfile> simulate_task_graph_execution(int n, const std::vector<std::pair<int, int>> &edges, const std::vector<double> &cost,
+                                                       const TaskConstraint &allowed);
+
+// Simulation of a mapped PCG on that engine: one task per operator (forward; with include_backward also the mirrored backward
+// task) that occupies its devices exclusively, one unconstrained task per tensor movement between differing device sets.
+// Returns the makespan in ms.
 double simulate_task_graph(const Graph &mapped_pcg, const MachineSpec &m, const CostEstimator &est, bool include_backward = false);
 
 }  // namespace ff

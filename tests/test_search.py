@@ -384,3 +384,67 @@ def test_cost_params_file_overrides_the_analytic_model(tmp_path):
     p = est.params()
     assert p["launch_us"] == 9.0 and p["measured_gbs"]["allreduce@4"] == 333.0 and p["measured_gbs"]["allreduce@8"] == 513.0
     assert info["source"] == "analytic" and info["cost_params"] == str(path)
+
+
+# ------------------------------------------------------------------ generic event-driven task-graph execution
+# cases and expected traces of the reference's test (lib/compiler/test/src/compiler/task_graph_simulator/
+# simulate_task_graph_execution.cc)
+def _trace(n, edges, cost, allowed):
+    return sorted(c.simulate_task_graph_execution(n, edges, [float(x) for x in cost], allowed))
+
+
+ALWAYS = lambda t, running, done: True            # noqa: E731
+ONE_AT_A_TIME = lambda t, running, done: len(running) == 0   # noqa: E731
+
+
+def test_task_graph_execution_linear():
+    assert _trace(4, [(0, 1), (1, 2), (2, 3)], [1, 10, 100, 1000], ALWAYS) == [(0, 0, 1), (1, 1, 11), (2, 11, 111), (3, 111, 1111)]
+
+
+def test_task_graph_execution_rhombus():
+    edges, cost = [(0, 1), (0, 2), (1, 3), (2, 3)], [10, 15, 20, 25]
+    assert _trace(4, edges, cost, ALWAYS) == [(0, 0, 10), (1, 10, 25), (2, 10, 30), (3, 30, 55)]
+    assert _trace(4, edges, cost, ONE_AT_A_TIME) == [(0, 0, 10), (1, 10, 25), (2, 25, 45), (3, 45, 70)]
+
+
+def test_task_graph_execution_diamond_with_crossing():
+    edges = [(0, 1), (0, 2), (1, 3), (2, 3), (2, 4), (3, 5), (4, 5)]
+    cost = [10, 15, 20, 25, 30, 35]
+    assert _trace(6, edges, cost, ALWAYS) == [(0, 0, 10), (1, 10, 25), (2, 10, 30), (3, 30, 55), (4, 30, 60), (5, 60, 95)]
+    assert _trace(6, edges, cost, ONE_AT_A_TIME) == [(0, 0, 10), (1, 10, 25), (2, 25, 45), (3, 45, 70), (4, 70, 100), (5, 100, 135)]
+
+
+def test_task_graph_execution_all_to_all_with_two_slots():
+    edges = [(0, 1), (0, 2), (0, 3), (1, 4), (2, 4), (3, 4)]
+    at_most_two = lambda t, running, done: len(running) < 2   # noqa: E731
+    assert _trace(5, edges, [10, 100, 100, 100, 20], at_most_two) == [(0, 0, 10), (1, 10, 110), (2, 10, 110), (3, 110, 210), (4, 210, 230)]
+
+
+def test_task_graph_execution_constraint_sees_finished_tasks_and_stuck_graphs_are_errors():
+    seen = []
+    def allowed(t, running, done):
+        seen.append((t, frozenset(running), frozenset(done)))
+        return True
+    _trace(3, [(0, 2), (1, 2)], [5, 7, 1], allowed)
+    assert (2, frozenset(), frozenset({0, 1})) in seen          # task 2 is offered once both producers have finished
+    with pytest.raises(Exception):
+        _trace(2, [(0, 1), (1, 0)], [1, 1], ALWAYS)              # a cycle: nothing can ever start
+    with pytest.raises(Exception):
+        _trace(2, [], [1, 1], lambda t, running, done: t == 0)   # task 1 is refused for ever
+    with pytest.raises(Exception):
+        _trace(2, [(0, 5)], [1, 1], ALWAYS)
+
+
+def test_pcg_simulation_of_a_branching_graph_is_deterministic_and_grows_with_backward():
+    # the split_test model has parallel branches; on one device every task serialises: the simulated forward time of the
+    # mapped graph equals the sum of its operators' forward costs, and backward adds to it
+    g = c.build_model("split_test", {"batch_size": 8})
+    ms = c.MachineSpecification(1, 1)
+    est = c.CostEstimator(ms)
+    m = c.evaluate_pcg(c.pcg_from_computation_graph(g), ms, est)["mapped_pcg"]
+    f = c.simulate_task_graph(m, ms, est, False)
+    fb = c.simulate_task_graph(m, ms, est, True)
+    assert 0 < f < fb and f == c.simulate_task_graph(m, ms, est, False)
+    total = sum(est.op_cost(m, n["id"])["fwd_ms"] for n in m.nodes()) if hasattr(est, "op_cost") else None
+    if total is not None:
+        assert abs(f - total) < 1e-6 * max(1.0, total)
