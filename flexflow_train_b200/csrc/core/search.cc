@@ -272,6 +272,66 @@ std::vector<int> view_devices(const MachineView &v, const std::vector<int> &task
   return devs;
 }
 
+// ---------------------------------------------------------------- machine views, reference stride semantics
+namespace {
+// weight of task dim k among the dims that share its projection: product of (degree * stride) of the earlier ones
+std::vector<long long> reference_dim_weights(const MachineView &v, const std::vector<int> &deg) {
+  if (v.dims.size() != deg.size()) throw Error("machine view has " + std::to_string(v.dims.size()) + " dims, the task space " + std::to_string(deg.size()));
+  std::vector<long long> w(deg.size(), 1);
+  long long acc[2] = {1, 1};
+  for (size_t k = 0; k < deg.size(); ++k) {
+    const int p = v.dims[k].inter_node ? 1 : 0;
+    w[k] = acc[p] * v.dims[k].stride;
+    acc[p] *= (long long)deg[k] * v.dims[k].stride;
+  }
+  return w;
+}
+}  // namespace
+std::pair<int, int> reference_machine_coordinate(const MachineView &v, const std::vector<int> &deg, const std::vector<int> &coord) {
+  if (coord.size() != deg.size()) throw Error("task coordinate and task space differ in rank");
+  auto w = reference_dim_weights(v, deg);
+  long long node = v.start_node, dev = v.start_device;
+  for (size_t k = 0; k < deg.size(); ++k) {
+    if (coord[k] < 0 || coord[k] >= deg[k]) throw Error("task coordinate outside the task space");
+    (v.dims[k].inter_node ? node : dev) += w[k] * coord[k];
+  }
+  return {(int)node, (int)dev};
+}
+std::vector<MachineView> reference_allowed_machine_views(const std::vector<int> &deg, int num_nodes, int gpus_per_node) {
+  long long full = 1;
+  for (int d : deg) full *= std::max(d - 1, 0);
+  full = std::max(full, 1ll);
+  const int total = num_nodes * gpus_per_node;
+  const int max_stride = (int)((total + full - 1) / full);
+  std::vector<int> last;
+  for (int d : deg) last.push_back(d - 1);
+  std::vector<MachineView> out;
+  const size_t nd = deg.size();
+  std::vector<int> stride(nd, 1);
+  for (;;) {   // every stride vector in [1, max_stride]^nd
+    for (unsigned proj = 0; proj < (1u << nd); ++proj)
+      for (int node = 0; node < num_nodes; ++node)
+        for (int dev = 0; dev < gpus_per_node; ++dev) {
+          MachineView v;
+          v.start_node = node;
+          v.start_device = dev;
+          for (size_t k = 0; k < nd; ++k) v.dims.push_back({stride[k], ((proj >> k) & 1u) != 0});
+          auto mx = reference_machine_coordinate(v, deg, last);
+          if (mx.first < num_nodes && mx.second < gpus_per_node) out.push_back(v);
+        }
+    size_t k = 0;
+    while (k < nd && ++stride[k] > max_stride) stride[k++] = 1;
+    if (k == nd) break;
+  }
+  return out;
+}
+MachineView absolute_view_from_reference(const MachineView &v, const std::vector<int> &deg) {
+  auto w = reference_dim_weights(v, deg);
+  MachineView a = v;
+  for (size_t k = 0; k < deg.size(); ++k) a.dims[k].stride = (int)w[k];
+  return a;
+}
+
 // ---------------------------------------------------------------- tensor set movement
 // Which pieces travel between which devices when `src` (placed by view `vs`) feeds `dst` (placed by `vd`): for every
 // task of the consumer, the shard of the tensor it reads (operator_tensor_coord) is looked up among the producer's
@@ -1145,6 +1205,17 @@ void bind_search(py::module &m) {
                                           const CostEstimator &est) {
     return tensor_set_movement_cost_ms(get_tensor_set_movement(g, src, MachineView::from_json(json_from_py(vs)), dst,
                                                                MachineView::from_json(json_from_py(vd)), ms), ms, est);
+  });
+  m.def("reference_machine_coordinate", [](py::object view, std::vector<int> task, std::vector<int> coord) {
+    return reference_machine_coordinate(MachineView::from_json(json_from_py(view)), task, coord);
+  }, py::arg("view"), py::arg("task_degrees"), py::arg("coord"), "(node, device) of a task under the reference's relative-stride view semantics");
+  m.def("reference_allowed_machine_views", [](std::vector<int> task, int num_nodes, int gpus_per_node) {
+    py::list l;
+    for (auto &v : reference_allowed_machine_views(task, num_nodes, gpus_per_node)) l.append(json_to_py(v.to_json()));
+    return l;
+  }, py::arg("task_degrees"), py::arg("num_nodes"), py::arg("gpus_per_node"));
+  m.def("absolute_view_from_reference", [](py::object view, std::vector<int> task) {
+    return json_to_py(absolute_view_from_reference(MachineView::from_json(json_from_py(view)), task).to_json());
   });
   m.def("view_devices", [](py::object view, std::vector<int> task, const MachineSpec &ms) {
     return view_devices(MachineView::from_json(json_from_py(view)), task, ms);

@@ -152,6 +152,17 @@ struct MCMCConfig {
 SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
                          const MCMCConfig &cfg);
 
+// Machine views with the reference's stride semantics (compiler/machine_mapping/machine_view.cc:65-135,
+// allowed_machine_views.cc:51-162), next to the absolute-stride views the mapping search uses (allowed_machine_views above).
+// Here a view's stride is relative: the task dims projected onto the same machine dimension (inter-node / intra-node) are
+// combined first-dim-fastest, dim k weighing prod_{i<k}(degree_i * stride_i) * stride_k.  `reference_machine_coordinate` maps a
+// task coordinate to (node, device); `reference_allowed_machine_views` enumerates every (start, strides, projections) whose
+// last task stays inside a machine of num_nodes x gpus_per_node, strides up to ceil(devices / prod(degree_i - 1));
+// `absolute_view_from_reference` rewrites such a view with absolute strides so that view_devices resolves it.
+std::pair<int, int> reference_machine_coordinate(const MachineView &v, const std::vector<int> &task_degrees, const std::vector<int> &coord);
+std::vector<MachineView> reference_allowed_machine_views(const std::vector<int> &task_degrees, int num_nodes, int gpus_per_node);
+MachineView absolute_view_from_reference(const MachineView &v, const std::vector<int> &task_degrees);
+
 // Event-driven execution of a task graph (reference: compiler/task_graph_simulator/simulate_task_graph_execution.cc).  Tasks
 // 0..n-1 with durations `cost`, precedence `edges` (before, after).  A task whose predecessors have finished starts as soon
 // as `allowed(task, in_progress, finished)` says so; ready tasks are offered in index order, again after every start and every

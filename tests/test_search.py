@@ -448,3 +448,61 @@ def test_pcg_simulation_of_a_branching_graph_is_deterministic_and_grows_with_bac
     total = sum(est.op_cost(m, n["id"])["fwd_ms"] for n in m.nodes()) if hasattr(est, "op_cost") else None
     if total is not None:
         assert abs(f - total) < 1e-6 * max(1.0, total)
+
+
+# ------------------------------------------------------------------ machine views with the reference's stride semantics
+# golden values of lib/compiler/test/src/compiler/machine_mapping/{machine_view,allowed_machine_views}.cc
+def _view(node, dev, *dims):
+    return {"start": {"node_idx": node, "device_idx": dev, "device_type": "GPU"},
+            "dimensions": [{"stride": s, "projection": p} for s, p in dims]}
+
+
+INTRA, INTER = "INTRA_NODE", "INTER_NODE"
+
+
+@pytest.mark.parametrize("view,degrees,expected", [
+    (_view(0, 1, (2, INTRA)), [3], {(0,): (0, 1), (1,): (0, 3), (2,): (0, 5)}),
+    (_view(1, 2, (1, INTER), (2, INTRA)), [2, 2], {(0, 0): (1, 2), (0, 1): (1, 4), (1, 0): (2, 2), (1, 1): (2, 4)}),
+    (_view(1, 0, (1, INTRA), (2, INTRA)), [2, 2], {(0, 0): (1, 0), (0, 1): (1, 4), (1, 0): (1, 1), (1, 1): (1, 5)}),
+    (_view(0, 1, (1, INTER), (2, INTRA), (1, INTRA)), [2, 2, 2], {(0, 1, 0): (0, 3), (1, 0, 1): (1, 5), (1, 1, 1): (1, 7)}),
+])
+def test_reference_machine_coordinates(view, degrees, expected):
+    for coord, where in expected.items():
+        assert c.reference_machine_coordinate(view, degrees, list(coord)) == where
+    with pytest.raises(Exception):
+        c.reference_machine_coordinate(view, degrees, [d + 1 for d in degrees])     # outside the task space
+    with pytest.raises(Exception):
+        c.reference_machine_coordinate(view, degrees + [2], [0] * (len(degrees) + 1))  # rank mismatch
+
+
+def _key(v):
+    return (v["start"]["node_idx"], v["start"]["device_idx"], tuple((d["stride"], d["projection"]) for d in v["dimensions"]))
+
+
+@pytest.mark.parametrize("degrees,nodes,gpus,expected", [
+    ([3], 1, 5, [_view(0, 0, (1, INTRA)), _view(0, 1, (1, INTRA)), _view(0, 2, (1, INTRA)), _view(0, 0, (2, INTRA))]),
+    ([2, 3], 3, 3, [_view(0, 0, (1, INTER), (1, INTRA)), _view(1, 0, (1, INTER), (1, INTRA)), _view(0, 0, (2, INTER), (1, INTRA)),
+                    _view(0, 0, (1, INTRA), (1, INTER)), _view(0, 1, (1, INTRA), (1, INTER)), _view(0, 0, (2, INTRA), (1, INTER))]),
+    ([], 2, 1, [_view(0, 0), _view(1, 0)]),
+    ([2], 2, 2, [_view(0, 0, (1, INTRA)), _view(0, 0, (1, INTER)), _view(1, 0, (1, INTRA)), _view(0, 1, (1, INTER))]),
+])
+def test_reference_allowed_machine_views(degrees, nodes, gpus, expected):
+    got = c.reference_allowed_machine_views(degrees, nodes, gpus)
+    assert sorted(map(_key, got)) == sorted(map(_key, expected))
+
+
+def test_reference_views_resolve_to_devices_through_absolute_strides():
+    # every enumerated view, rewritten with absolute strides, resolves to distinct devices inside the machine, and task
+    # by task to the device the reference's coordinate rule gives
+    ms = c.MachineSpecification(2, 4)
+    degrees = [2, 2]
+    views = c.reference_allowed_machine_views(degrees, 2, 4)
+    assert len(views) > 8
+    for v in views:
+        devs = c.view_devices(c.absolute_view_from_reference(v, degrees), degrees, ms)
+        expect = []
+        for i, j in itertools.product(range(2), range(2)):
+            node, dev = c.reference_machine_coordinate(v, degrees, [i, j])
+            assert 0 <= node < 2 and 0 <= dev < 4
+            expect.append(node * 4 + dev)
+        assert devs == expect and len(set(devs)) == 4
