@@ -1087,63 +1087,57 @@ SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEst
   auto score = [&](const Graph &g, const std::map<NodeId, MachineView> &mv) {
     return simulate_task_graph(mapped_pcg_from_pcg_and_mapping(g, mv), m, est, true);
   };
-  Graph cur = start;
-  auto cur_map = random_views(cur);
-  double cur_cost = score(cur, cur_map);
-  SearchResult best;
-  best.pcg = cur;
-  best.mapping = cur_map;
-  best.runtime_ms = cur_cost;
-  int accepted = 0, substitutions = 0;
+  struct State {
+    Graph g;
+    std::map<NodeId, MachineView> views;
+  };
+  State init{start, random_views(start)};
+  const double start_cost = score(init.g, init.views);
+  int substitutions = 0;
   // relative: the temperature is a fraction of the starting cost, so that "a candidate 1 % worse" means the same
-  // whether a step takes 3 ms or 300 ms; absolute: the reference's exp(-delta / temperature) with delta in ms
-  const double temperature = cfg.relative_temperature ? cfg.temperature * std::max(cur_cost, 1e-9) : cfg.temperature;
-  for (int it = 0; it < cfg.num_iterations; ++it) {
-    Graph cand = cur;
-    auto cand_map = cur_map;
+  // whether a step takes 3 ms or 300 ms; absolute: exp(-delta / temperature) with delta in ms
+  const double temperature = cfg.relative_temperature ? cfg.temperature * std::max(start_cost, 1e-9) : cfg.temperature;
+  auto propose = [&](const State &cur, std::mt19937 &) -> std::optional<State> {
+    State cand = cur;
     bool changed = false;
     if (uni(rng) < cfg.substitution_frequency && !rules.empty()) {
       // a random rule at a random match; new layers take a random allowed view
       for (int attempt = 0; attempt < 8 && !changed; ++attempt) {
         const Substitution &rule = rules[rng() % rules.size()];
-        auto ms = find_pattern_matches(rule.pattern, cur);
+        auto ms = find_pattern_matches(rule.pattern, cur.g);
         if (ms.empty()) continue;
-        auto ng = apply_substitution(cur, rule, ms[rng() % ms.size()]);
+        auto ng = apply_substitution(cur.g, rule, ms[rng() % ms.size()]);
         if (!ng) continue;
-        cand = *ng;
-        for (auto &kv : cand.nodes())
-          if (!cand_map.count(kv.first)) {
-            auto vs = allowed_machine_views(operator_task_space(kv.second, cand), Resources{0, m.num_devices()}, m);
-            if (!vs.empty()) cand_map[kv.first] = vs[rng() % vs.size()];
+        cand.g = *ng;
+        for (auto &kv : cand.g.nodes())
+          if (!cand.views.count(kv.first)) {
+            auto vs = allowed_machine_views(operator_task_space(kv.second, cand.g), Resources{0, m.num_devices()}, m);
+            if (!vs.empty()) cand.views[kv.first] = vs[rng() % vs.size()];
           }
-        for (auto itv = cand_map.begin(); itv != cand_map.end();)
-          itv = cand.has_node(itv->first) ? std::next(itv) : cand_map.erase(itv);
+        for (auto itv = cand.views.begin(); itv != cand.views.end();)
+          itv = cand.g.has_node(itv->first) ? std::next(itv) : cand.views.erase(itv);
         changed = true;
         ++substitutions;
       }
     }
     if (!changed) {
       // mutate the view of one layer
-      auto ids = cand.node_ids();
+      auto ids = cand.g.node_ids();
       NodeId n = ids[rng() % ids.size()];
-      auto vs = allowed_machine_views(operator_task_space(cand.node(n), cand), Resources{0, m.num_devices()}, m);
-      if (vs.empty()) continue;
-      cand_map[n] = vs[rng() % vs.size()];
+      auto vs = allowed_machine_views(operator_task_space(cand.g.node(n), cand.g), Resources{0, m.num_devices()}, m);
+      if (vs.empty()) return std::nullopt;
+      cand.views[n] = vs[rng() % vs.size()];
     }
-    double c = score(cand, cand_map);
-    double accept_p = c <= cur_cost ? 1.0 : std::exp(-(c - cur_cost) / std::max(1e-12, temperature));
-    if (uni(rng) < accept_p) {
-      cur = cand;
-      cur_map = cand_map;
-      cur_cost = c;
-      ++accepted;
-      if (c < best.runtime_ms) {
-        best.pcg = cur;
-        best.mapping = cur_map;
-        best.runtime_ms = c;
-      }
-    }
-  }
+    return cand;
+  };
+  int accepted = 0;
+  double best_cost = start_cost;
+  State found = run_mcmc(init, propose, [&](const State &st) { return score(st.g, st.views); }, temperature, cfg.num_iterations, rng, &accepted,
+                         &best_cost);
+  SearchResult best;
+  best.pcg = found.g;
+  best.mapping = found.views;
+  best.runtime_ms = best_cost;
   best.stats = Json::object();
   best.stats["iterations"] = cfg.num_iterations;
   best.stats["accepted"] = accepted;
@@ -1270,6 +1264,24 @@ void bind_search(py::module &m) {
     return result_to_py(mcmc_search(g, ms, est, rules, c));
   }, py::arg("pcg"), py::arg("machine"), py::arg("estimator"), py::arg("rules"), py::arg("temperature") = 1.0, py::arg("num_iterations") = 100,
         py::arg("substitution_frequency") = 0.2, py::arg("seed") = 0, py::arg("relative_temperature") = false);
+  m.def("run_mcmc",
+        [](py::object start, std::function<py::object(py::object, double)> sampler, std::function<double(py::object)> cost, double temperature,
+           int num_iterations, unsigned seed) {
+          std::mt19937 rng(seed);
+          std::uniform_real_distribution<double> uni(0.0, 1.0);
+          int accepted = 0;
+          double best_cost = 0;
+          auto propose = [&](const py::object &st, std::mt19937 &r) -> std::optional<py::object> {
+            py::object o = sampler(st, uni(r));
+            if (o.is_none()) return std::nullopt;
+            return o;
+          };
+          py::object best = run_mcmc(start, propose, cost, temperature, num_iterations, rng, &accepted, &best_cost);
+          return py::make_tuple(best, best_cost, accepted);
+        },
+        py::arg("start"), py::arg("sampler"), py::arg("cost"), py::arg("temperature") = 1.0, py::arg("num_iterations") = 100, py::arg("seed") = 0,
+        "Metropolis search over Python states: sampler(state, u) -> state or None (u uniform in [0, 1) from the seeded generator), "
+        "cost(state) -> float; returns (best state, its cost, proposals accepted)");
   m.def("simulate_task_graph_execution",
         [](int n, const std::vector<std::pair<int, int>> &edges, const std::vector<double> &cost, const TaskConstraint &allowed) {
           std::vector<std::tuple<int, double, double>> out;

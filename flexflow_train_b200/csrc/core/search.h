@@ -6,6 +6,7 @@
 // unity_algorithm/unity_algorithm.cc:51-146, mcmc/mcmc_over_mapped_pcg.cc:18-66,
 // task_graph_simulator/task_simulator.cc:23-75, cost_estimator/cost_estimator.h:14-41.
 #pragma once
+#include <cmath>
 #include <functional>
 #include <set>
 #include <map>
@@ -151,6 +152,38 @@ struct MCMCConfig {
 };
 SearchResult mcmc_search(const Graph &start, const MachineSpec &m, const CostEstimator &est, const std::vector<Substitution> &rules,
                          const MCMCConfig &cfg);
+
+// Metropolis search over any state type (reference: compiler/mcmc/generic_mcmc_algorithm.h).  `sampler(state, rng)` proposes
+// a neighbour or nothing; a proposal that costs less is taken, one that costs more with probability
+// exp(-(cost - current cost) / temperature); the cheapest state seen is returned.  (The reference measures the increase
+// against the best state instead of the current one; against the current one the chain can leave a local minimum and
+// still come back.)  One cost evaluation per proposal; `accepted` counts the proposals taken.
+template <typename State, typename Sampler, typename Cost, typename Rng>
+State run_mcmc(const State &start, Sampler sampler, Cost cost, double temperature, int num_iterations, Rng &rng, int *accepted = nullptr,
+               double *best_cost_out = nullptr) {
+  std::uniform_real_distribution<double> uni(0.0, 1.0);
+  State cur = start, best = start;
+  double cur_cost = cost(cur), best_cost = cur_cost;
+  int taken = 0;
+  for (int it = 0; it < num_iterations; ++it) {
+    std::optional<State> cand = sampler(cur, rng);
+    if (!cand) continue;
+    const double c = cost(*cand);
+    const double accept_p = c <= cur_cost ? 1.0 : std::exp(-(c - cur_cost) / std::max(1e-12, temperature));
+    if (uni(rng) < accept_p) {
+      cur = std::move(*cand);
+      cur_cost = c;
+      ++taken;
+      if (c < best_cost) {
+        best = cur;
+        best_cost = c;
+      }
+    }
+  }
+  if (accepted) *accepted = taken;
+  if (best_cost_out) *best_cost_out = best_cost;
+  return best;
+}
 
 // Machine views with the reference's stride semantics (compiler/machine_mapping/machine_view.cc:65-135,
 // allowed_machine_views.cc:51-162), next to the absolute-stride views the mapping search uses (allowed_machine_views above).

@@ -506,3 +506,28 @@ def test_reference_views_resolve_to_devices_through_absolute_strides():
             assert 0 <= node < 2 and 0 <= dev < 4
             expect.append(node * 4 + dev)
         assert devs == expect and len(set(devs)) == 4
+
+
+# ------------------------------------------------------------------ generic Metropolis search
+def test_generic_mcmc_finds_the_minimum_of_a_parabola():
+    # the reference's case (lib/compiler/test/src/compiler/mcmc/generic_mcmc_algorithm.cc): walk on [0, 1] with steps of
+    # +-0.5, cost (x - 0.5)^2, start 0.1; a low temperature relative to the cost scale keeps what it finds
+    def sampler(x, u):
+        y = x + (u - 0.5)
+        return y if 0.0 <= y <= 1.0 else None
+    cost = lambda x: (x - 0.5) ** 2   # noqa: E731
+    best, best_cost, accepted = c.run_mcmc(0.1, sampler, cost, temperature=0.01, num_iterations=400, seed=0)
+    assert 0.47 < best < 0.53 and 0 <= best_cost < 0.001 and best_cost == cost(best) and 0 < accepted <= 400
+    # the seed fixes the walk
+    assert c.run_mcmc(0.1, sampler, cost, temperature=0.01, num_iterations=400, seed=0)[0] == best
+    assert c.run_mcmc(0.1, sampler, cost, temperature=0.01, num_iterations=400, seed=1)[0] != best
+
+
+def test_generic_mcmc_temperature_controls_acceptance_of_worse_states():
+    sampler = lambda x, u: x + (1 if u < 0.5 else -1)   # noqa: E731
+    cost = lambda x: float(abs(x))                      # noqa: E731
+    cold = c.run_mcmc(0, sampler, cost, temperature=1e-6, num_iterations=300, seed=3)
+    hot = c.run_mcmc(0, sampler, cost, temperature=1e6, num_iterations=300, seed=3)
+    assert cold[0] == 0 and cold[2] == 0          # every proposal is worse than the start and a cold chain refuses them all
+    assert hot[0] == 0 and hot[2] > 250           # a hot chain takes nearly everything and still reports the best state seen
+    assert c.run_mcmc(5, lambda x, u: None, cost, 1.0, 10, 0) == (5, 5.0, 0)   # a sampler that proposes nothing
