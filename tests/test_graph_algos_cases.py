@@ -135,3 +135,83 @@ def test_dominators_against_path_enumeration(seed):
     for v in range(n):
         ps = paths(0, v)
         assert dom[v] == set.intersection(*[set(p) for p in ps]), (edges, v)
+
+
+# ------------------------------------------------------------------ series-parallel decomposition of computation graphs
+# cases of lib/compiler/test/src/compiler/series_parallel/computation_graph/get_computation_graph_series_parallel_decomposition.cc
+from flexflow_train_b200 import _ffcore as core  # noqa: E402
+def _norm(t):
+    """SP tree with the children of parallel splits as frozensets (their order carries no meaning)."""
+    if isinstance(t, int):
+        return t
+    kind, kids = t
+    kids = [_norm(k) for k in kids]
+    return (kind, frozenset(kids)) if kind == "P" else (kind, tuple(kids))
+
+
+def _decompose(b):
+    tree, exact = core.get_graph_sp_decomposition(b.graph)
+    return _norm(tree), exact
+
+
+def test_cg_sp_decomposition_empty_graph_and_single_input():
+    tree, exact = core.get_graph_sp_decomposition(core.GraphBuilder().graph)
+    assert core.sp_nodes(tree) == [] and not exact          # an empty graph has no series-parallel decomposition
+    b = core.GraphBuilder()
+    x = b.create_input([10, 12], "FLOAT", name="x")
+    assert _decompose(b) == (x[0], True)
+
+
+def test_cg_sp_decomposition_single_operator_with_input_and_weights():
+    b = core.GraphBuilder()
+    x = b.create_input([10, 12], "FLOAT", name="x")
+    y = b.dense(x, 14, None, True)
+    ids = {n["id"]: n["type"] for n in b.graph.nodes()}
+    weights = [i for i, t in ids.items() if t == "WEIGHT"]
+    assert len(weights) == 2
+    assert _decompose(b) == (("S", (("P", frozenset([x[0]] + weights)), y[0])), True)
+
+
+def test_cg_sp_decomposition_shared_input_with_private_weights():
+    #   w1   input   w2        series-parallel without the weights, not with them as they stand: inputs and weights are
+    #    \   /   \   /         gathered into one parallel stage in front (the decomposition's preprocessing)
+    #     op1     op2
+    b = core.GraphBuilder()
+    x = b.create_input([10, 12], "FLOAT", name="x")
+    y1 = b.dense(x, 14, None, False, name="op1")
+    y2 = b.dense(x, 14, None, False, name="op2")
+    weights = [n["id"] for n in b.graph.nodes() if n["type"] == "WEIGHT"]
+    assert len(weights) == 2
+    assert _decompose(b) == (("S", (("P", frozenset([x[0]] + weights)), ("P", frozenset([y1[0], y2[0]])))), True)
+
+
+def test_cg_sp_decomposition_keeps_independent_chains_apart_when_no_preprocessing_is_needed():
+    #   input1   input2
+    #     |        |
+    #    op1      op2
+    b = core.GraphBuilder()
+    x1 = b.create_input([10, 12], "FLOAT", name="x1")
+    x2 = b.create_input([10, 12], "FLOAT", name="x2")
+    r1 = b.unary("RELU", x1)
+    r2 = b.unary("RELU", x2)
+    assert _decompose(b) == (("P", frozenset([("S", (x1[0], r1[0])), ("S", (x2[0], r2[0]))])), True)
+
+
+def test_cg_sp_decomposition_of_an_n_shaped_graph_is_not_exact():
+    #      input            op4 reads op1 and op2, op3 reads op1 only: not series-parallel with or without weights.  The
+    #      /   \            reference answers "none" here; this implementation SP-izes and says that it did (exact = False),
+    #    op1   op2          and the result still orders every producer before its consumers
+    #     | \   |
+    #    op3  op4
+    b = core.GraphBuilder()
+    x = b.create_input([10, 12], "FLOAT", name="x")
+    o1 = b.unary("RELU", x)
+    o2 = b.unary("RELU", x)
+    o3 = b.unary("RELU", o1)
+    o4 = b.binary("EW_ADD", o1, o2)
+    tree, exact = core.get_graph_sp_decomposition(b.graph)
+    assert not exact and set(core.sp_nodes(tree)) >= {x[0], o1[0], o2[0], o3[0], o4[0]}
+    order = core.sp_nodes(tree)                      # leaves in series order: every producer comes before its consumers
+    first = {n: order.index(n) for n in set(order)}
+    for a_, b_ in ((x[0], o1[0]), (x[0], o2[0]), (o1[0], o3[0]), (o1[0], o4[0]), (o2[0], o4[0])):
+        assert first[a_] < max(i for i, n in enumerate(order) if n == b_)
