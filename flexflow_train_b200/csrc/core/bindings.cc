@@ -1,4 +1,6 @@
 // bindings.cc -- the pybind11 module `_ffcore`: Python surface of the C++ compiler core.
+#include <pybind11/functional.h>
+
 #include "builder.h"
 #include "models.h"
 #include "pyjson.h"
@@ -333,6 +335,11 @@ PYBIND11_MODULE(_ffcore, m) {
   // ---- models
   m.def("model_names", &model_names);
   m.def("default_model_config", [](const std::string &n) { return json_to_py(default_model_config(n)); });
+  m.def("tensor_dims_has_dim", &tensor_dims_has_dim);
+  m.def("tensor_dims_is_broadcastable_to", &tensor_dims_is_broadcastable_to, py::arg("curr"), py::arg("goal"));
+  m.def("get_broadcast_target_dims", &get_broadcast_target_dims);
+  m.def("get_tensor_dims_coord_set", &get_tensor_dims_coord_set);
+  m.def("tensor_dims_drop_dims", &tensor_dims_drop_dims, py::arg("dims"), py::arg("should_drop"));
   m.def("build_model", [](const std::string &n, py::object cfg) { return build_model(n, json_from_py(cfg)); }, py::arg("name"),
         py::arg("config") = py::none());
 

@@ -33,6 +33,43 @@ int dtype_bytes(DataType d) {
   }
   return 4;
 }
+
+bool tensor_dims_has_dim(const std::vector<int64_t> &dims, int idx) { return idx >= 0 && idx < (int)dims.size(); }
+bool tensor_dims_is_broadcastable_to(const std::vector<int64_t> &curr, const std::vector<int64_t> &goal) {
+  if (goal.size() < curr.size()) return false;
+  const size_t off = goal.size() - curr.size();
+  for (size_t i = 0; i < curr.size(); ++i)
+    if (curr[i] != goal[off + i] && curr[i] != 1) return false;
+  return true;
+}
+std::optional<std::vector<int64_t>> get_broadcast_target_dims(const std::vector<std::vector<int64_t>> &inputs) {
+  for (auto &goal : inputs) {
+    bool all = true;
+    for (auto &d : inputs) all = all && tensor_dims_is_broadcastable_to(d, goal);
+    if (all) return goal;
+  }
+  return std::nullopt;
+}
+std::vector<std::vector<int64_t>> get_tensor_dims_coord_set(const std::vector<int64_t> &dims) {
+  std::vector<std::vector<int64_t>> out = {{}};
+  for (int64_t d : dims) {
+    std::vector<std::vector<int64_t>> next;
+    for (auto &prefix : out)
+      for (int64_t c = 0; c < d; ++c) {
+        auto p = prefix;
+        p.push_back(c);
+        next.push_back(std::move(p));
+      }
+    out = std::move(next);
+  }
+  return out;
+}
+std::vector<int64_t> tensor_dims_drop_dims(const std::vector<int64_t> &dims, const std::function<bool(int)> &should_drop) {
+  std::vector<int64_t> out;
+  for (int i = 0; i < (int)dims.size(); ++i)
+    if (!should_drop(i)) out.push_back(dims[i]);
+  return out;
+}
 std::string to_string(OpType t) {
   switch (t) {
 #define X(n) case OpType::n: return #n;

@@ -39,6 +39,16 @@ std::string to_string(DataType);
 DataType datatype_from_string(const std::string &);
 int dtype_bytes(DataType);
 
+// Plain tensor dims (lib/op-attrs/include/op-attrs/tensor_dims.h): broadcasting follows numpy -- a tensor reaches a goal of at
+// least its rank when, aligned at the trailing dim, each of its dims equals the goal's or is 1.
+bool tensor_dims_has_dim(const std::vector<int64_t> &dims, int idx);
+bool tensor_dims_is_broadcastable_to(const std::vector<int64_t> &curr, const std::vector<int64_t> &goal);
+// the one of `inputs` that all of them broadcast to, if there is one (a target that is not among the inputs does not count)
+std::optional<std::vector<int64_t>> get_broadcast_target_dims(const std::vector<std::vector<int64_t>> &inputs);
+// every coordinate of a tensor of these dims, last dim fastest (one empty coordinate for a zero-dimensional tensor)
+std::vector<std::vector<int64_t>> get_tensor_dims_coord_set(const std::vector<int64_t> &dims);
+std::vector<int64_t> tensor_dims_drop_dims(const std::vector<int64_t> &dims, const std::function<bool(int)> &should_drop);
+
 // Operator types, same set and order as lib/op-attrs/include/op-attrs/operator_type.dtg.toml
 #define FF_OPTYPES(X)                                                                                               \
   X(NOOP) X(INPUT) X(WEIGHT) X(CONV2D) X(DROPOUT) X(LINEAR) X(BATCHMATMUL) X(POOL2D) X(SCALAR_MULTIPLY)            \

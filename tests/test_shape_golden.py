@@ -180,3 +180,41 @@ def test_flat_cast_dropout_shapes():
     assert sig(o["OUTPUT"]) == ([12, 4], [2, 2], 1, 1)
     with pytest.raises(c.CoreError):   # a mask over partial sums would not commute with the reduction
         infer("DROPOUT", {"rate": 0.5, "seed": 1}, [("INPUT", par([12, 4], [1, 1], 2, 1))])
+
+
+# ------------------------------------------------------------------ plain tensor dims (lib/op-attrs/test/src/op-attrs/tensor_dims.cc)
+def test_tensor_dims_has_dim():
+    assert all(c.tensor_dims_has_dim([6, 9, 8], i) for i in (0, 1, 2))
+    assert not c.tensor_dims_has_dim([6, 9, 8], 3) and not c.tensor_dims_has_dim([], 0)
+
+
+@pytest.mark.parametrize("curr,ok", [
+    ([1, 1, 4, 3], True),          # dims match
+    ([4, 3], True),                # rank promotion only
+    ([1, 1, 1, 3], True),          # dim expansion only
+    ([1, 3], True),                # both
+    ([1, 1, 2, 3], False),         # 2 does not expand to 4
+    ([1, 1, 10, 4, 3], False),     # the goal has fewer dims
+])
+def test_tensor_dims_is_broadcastable_to(curr, ok):
+    assert c.tensor_dims_is_broadcastable_to(curr, [1, 1, 4, 3]) is ok
+
+
+def test_get_broadcast_target_dims():
+    d1, d2 = [1, 10, 4, 3], [10, 4, 1]
+    assert c.get_broadcast_target_dims([d1, d2, [1, 1, 4, 3]]) == d1
+    assert c.get_broadcast_target_dims([d1, d2, [1, 1, 1, 4]]) is None
+    d3, possible = [1, 1, 1, 4, 3], [1, 1, 10, 4, 3]
+    assert all(c.tensor_dims_is_broadcastable_to(d, possible) for d in (d1, d2, d3))
+    assert c.get_broadcast_target_dims([d1, d2, d3]) is None          # a target outside the inputs does not count
+    assert c.get_broadcast_target_dims([]) is None
+    assert c.get_broadcast_target_dims([d1] * 5) == d1
+
+
+def test_tensor_dims_coord_set_and_drop_dims():
+    assert c.get_tensor_dims_coord_set([3, 1, 2]) == [[0, 0, 0], [0, 0, 1], [1, 0, 0], [1, 0, 1], [2, 0, 0], [2, 0, 1]]
+    assert c.get_tensor_dims_coord_set([]) == [[]]
+    dims = [3, 5, 1, 2]
+    assert c.tensor_dims_drop_dims(dims, lambda i: i in (0, 2)) == [5, 2]
+    assert c.tensor_dims_drop_dims(dims, lambda i: False) == dims
+    assert c.tensor_dims_drop_dims(dims, lambda i: True) == []
