@@ -147,3 +147,95 @@ def test_legacy_rule_inline_and_dot():
     rules, st = c.load_legacy_rules({"_t": "RuleCollection", "rule": [rule]})
     assert st["num_converted"] == 1
     assert "digraph" in rules[0].as_dot() and "OP_PARTITION" in c.legacy_rule_as_dot(rule)
+
+
+# ------------------------------------------------------------------ one rule at a time on a hand-built graph
+# (the structure the reference's lib/substitutions/test/src/substitutions/unity_substitution_set.cc builds by hand)
+def _rule(name):
+    return {r.name: r for r in c.get_substitution_set(MS)}[name]
+
+
+def _apply_once(g, rule):
+    ms = c.find_pattern_matches(rule, g)
+    assert len(ms) == 1, len(ms)
+    g2 = c.apply_substitution(g, rule, ms[0])
+    assert g2 is not None
+    return g2
+
+
+def _producer(g, node, slot):
+    ins = dict((s, tuple(v)) for s, v in node["inputs"])
+    return g.node(ins[slot][0])
+
+
+def _only(g, typ):
+    ns = [n for n in g.nodes() if n["type"] == typ]
+    assert len(ns) == 1, (typ, len(ns))
+    return ns[0]
+
+
+def test_partition_conv2d_combine_rule():
+    b = c.GraphBuilder()
+    x = b.create_input([8, 4, 16, 16], "FLOAT", name="image")
+    b.conv2d(x, 6, 3, 3, 1, 1, 1, 1, None, 1, True, name="conv")
+    g2 = _apply_once(b.graph, _rule("partition_conv2d_combine_2_bias"))
+    conv = _only(g2, "CONV2D")
+    rp = _producer(g2, conv, "INPUT")
+    assert rp["type"] == "REPARTITION" and rp["attrs"]["repartition_dim"] == 0 and rp["attrs"]["repartition_degree"] == 2
+    for slot in ("FILTER", "BIAS"):
+        w = _producer(g2, conv, slot)
+        assert w["type"] == "REPLICATE" and w["attrs"]["replicate_degree"] == 2 and g2.node(dict((s, tuple(v)) for s, v in w["inputs"])["INPUT"][0])["type"] == "WEIGHT"
+    assert conv["outputs"][0][1].degrees == [2, 1, 1, 1]
+    cons = g2.consumers((conv["id"], "OUTPUT"))
+    comb = g2.node(cons[0][0])
+    assert len(cons) == 1 and comb["type"] == "COMBINE" and comb["attrs"]["combine_dim"] == 0 and comb["attrs"]["combine_degree"] == 2
+    assert comb["outputs"][0][1].degrees == [1, 1, 1, 1] and comb["outputs"][0][1].sizes == [8, 6, 16, 16]
+
+
+def test_partition_softmax_combine_rule_cuts_a_dim_other_than_the_softmax_dim():
+    b = c.GraphBuilder()
+    x = b.create_input([8, 10], "FLOAT", name="logits")
+    b.softmax(x, 1, name="prob")
+    g = b.graph
+    g2 = _apply_once(g, _rule("partition_softmax_combine_1_0_2"))       # softmax over dim 1, cut dim 0 in two
+    sm = _only(g2, "SOFTMAX")
+    rp = _producer(g2, sm, "INPUT")
+    assert rp["type"] == "REPARTITION" and rp["attrs"]["repartition_dim"] == 0 and sm["outputs"][0][1].degrees == [2, 1]
+    comb = g2.node(g2.consumers((sm["id"], "OUTPUT"))[0][0])
+    assert comb["type"] == "COMBINE" and comb["attrs"]["combine_dim"] == 0
+    # the rule that would cut the softmax dim itself does not exist, and one written for another softmax dim does not match
+    names = {r.name for r in c.get_substitution_set(MS)}
+    assert "partition_softmax_combine_1_1_2" not in names
+    assert c.find_pattern_matches(_rule("partition_softmax_combine_0_1_2"), g) == []
+
+
+def test_partition_add_combine_rule_cuts_both_operands():
+    b = c.GraphBuilder()
+    x = b.create_input([8, 10], "FLOAT", name="a")
+    y = b.create_input([8, 10], "FLOAT", name="b")
+    b.binary("EW_ADD", x, y, name="sum")
+    g2 = _apply_once(b.graph, _rule("partition_EW_ADD_combine_1_2"))
+    add = _only(g2, "EW_ADD")
+    for slot in ("LHS_INPUT", "RHS_INPUT"):
+        rp = _producer(g2, add, slot)
+        assert rp["type"] == "REPARTITION" and rp["attrs"]["repartition_dim"] == 1 and rp["attrs"]["repartition_degree"] == 2
+    assert add["outputs"][0][1].degrees == [1, 2]
+    assert g2.node(g2.consumers((add["id"], "OUTPUT"))[0][0])["type"] == "COMBINE"
+
+
+def test_partition_relu_combine_rule_and_its_cancellation_with_a_neighbour():
+    b = c.GraphBuilder()
+    x = b.create_input([8, 10], "FLOAT", name="x")
+    r1 = b.unary("RELU", x, name="r1")
+    b.unary("RELU", r1, name="r2")
+    g = b.graph
+    rule = _rule("partition_RELU_combine_0_2")
+    assert len(c.find_pattern_matches(rule, g)) == 2
+    both = c.apply_rules_exhaustively(g, [rule], 100, 4)
+    k = kinds(both)
+    assert k["REPARTITION"] == 2 and k["COMBINE"] == 2
+    # Combine(0, 2) followed by Repartition(0, 2) between the two ReLUs cancels: one cut region remains
+    merged = c.apply_rules_exhaustively(both, [r for r in c.get_substitution_set(MS) if r.name.startswith("cancel")], 100, 4)
+    k = kinds(merged)
+    assert k["REPARTITION"] == 1 and k["COMBINE"] == 1
+    assert all(n["outputs"][0][1].degrees == [2, 1] for n in merged.nodes() if n["type"] == "RELU")
