@@ -771,5 +771,125 @@ std::multiset<T> multiset_union(const std::multiset<T> &a, const std::multiset<T
   return out;
 }
 
+
+// ------------------------------------------------------------------ strings
+template <typename C, typename F>
+std::string join_strings(const C &c, const std::string &delimiter, F f) {
+  std::string out;
+  bool first = true;
+  for (auto &&x : c) {
+    if (!first) out += delimiter;
+    out += f(x);
+    first = false;
+  }
+  return out;
+}
+template <typename C>
+std::string join_strings(const C &c, const std::string &delimiter) {
+  return join_strings(c, delimiter, [](const std::string &x) { return x; });
+}
+// every line, the first and an empty last one included, moved right by indent_size spaces
+inline std::string indent(const std::string &text, int indent_size = 2) {
+  const std::string pad((size_t)indent_size, ' ');
+  std::string out = pad;
+  for (char ch : text) {
+    out += ch;
+    if (ch == '\n') out += pad;
+  }
+  return out;
+}
+
+// ------------------------------------------------------------------ small value types
+// an unordered pair: (a, b) == (b, a); ordered by (max, min)
+template <typename T>
+class commutative_pair {
+public:
+  commutative_pair(const T &a, const T &b) : hi_(a < b ? b : a), lo_(a < b ? a : b) {}
+  const T &max() const { return hi_; }
+  const T &min() const { return lo_; }
+  bool operator==(const commutative_pair &o) const { return hi_ == o.hi_ && lo_ == o.lo_; }
+  bool operator!=(const commutative_pair &o) const { return !(*this == o); }
+  bool operator<(const commutative_pair &o) const { return std::tie(hi_, lo_) < std::tie(o.hi_, o.lo_); }
+
+private:
+  T hi_, lo_;
+};
+// a query over values: everything, nothing, or a set of allowed values (utils/graph/query_set.h)
+template <typename T>
+class query_set {
+public:
+  static query_set matchall() { return query_set(std::nullopt); }
+  static query_set match_none() { return query_set(std::set<T>{}); }
+  static query_set match_values_in(const std::set<T> &v) { return query_set(v); }
+  static query_set match_single_value(const T &v) { return query_set(std::set<T>{v}); }
+  bool is_matchall() const { return !allowed_.has_value(); }
+  bool includes(const T &v) const { return !allowed_ || allowed_->count(v) > 0; }
+  const std::set<T> &allowed_values() const {
+    detail::require(allowed_.has_value(), "allowed_values of a match-all query");
+    return *allowed_;
+  }
+  std::set<T> apply(const std::set<T> &universe) const { return allowed_ ? intersection(universe, *allowed_) : universe; }
+  query_set intersect(const query_set &o) const {
+    if (is_matchall()) return o;
+    if (o.is_matchall()) return *this;
+    return query_set(intersection(*allowed_, *o.allowed_));
+  }
+  bool operator==(const query_set &o) const { return allowed_ == o.allowed_; }
+
+private:
+  explicit query_set(std::optional<std::set<T>> a) : allowed_(std::move(a)) {}
+  std::optional<std::set<T>> allowed_;
+};
+// fixed-capacity string and map without heap allocation (utils/stack_string.h, stack_map.h), over stack_vector
+template <size_t MAXSIZE>
+class stack_string {
+public:
+  stack_string() = default;
+  stack_string(const char *s) {   // NOLINT: converting on purpose, like the reference's
+    for (; *s; ++s) chars_.push_back(*s);
+  }
+  stack_string(const std::string &s) : stack_string(s.c_str()) {}   // NOLINT
+  size_t size() const { return chars_.size(); }
+  size_t length() const { return chars_.size(); }
+  char operator[](size_t i) const { return chars_[i]; }
+  void push_back(char ch) { chars_.push_back(ch); }
+  operator std::string() const { return std::string(chars_.begin(), chars_.end()); }   // NOLINT
+  bool operator==(const stack_string &o) const { return (std::string)*this == (std::string)o; }
+  bool operator<(const stack_string &o) const { return (std::string)*this < (std::string)o; }
+
+private:
+  stack_vector<char, MAXSIZE> chars_;
+};
+template <typename K, typename V, size_t MAXSIZE>
+class stack_map {
+public:
+  V &operator[](const K &k) {
+    for (auto &kv : items_)
+      if (kv.first == k) return kv.second;
+    items_.push_back({k, V{}});
+    return items_.back().second;
+  }
+  void insert(const K &k, const V &v) { (*this)[k] = v; }
+  const V &at(const K &k) const {
+    for (auto &kv : items_)
+      if (kv.first == k) return kv.second;
+    throw std::out_of_range("stack_map::at: no such key");
+  }
+  bool contains(const K &k) const {
+    for (auto &kv : items_)
+      if (kv.first == k) return true;
+    return false;
+  }
+  size_t size() const { return items_.size(); }
+  std::vector<std::pair<K, V>> sorted_items() const {   // in key order
+    std::vector<std::pair<K, V>> out(items_.begin(), items_.end());
+    std::sort(out.begin(), out.end(), [](const std::pair<K, V> &a, const std::pair<K, V> &b) { return a.first < b.first; });
+    return out;
+  }
+
+private:
+  stack_vector<std::pair<K, V>, MAXSIZE> items_;
+};
+
 }  // namespace utils
 }  // namespace ff

@@ -148,6 +148,47 @@ void bind_containers(py::module &root) {
   m.def("merge_disjoint_maps", [](const std::vector<MSI> &ms) { return merge_disjoint_maps(ms); });
   m.def("merge_maps_with_right_dominating", [](const std::vector<MSI> &ms) { return merge_maps_with_right_dominating(ms); });
   m.def("try_merge_nondisjoint_maps", [](const MSI &a, const MSI &b) { return try_merge_nondisjoint_maps(a, b); });
+  // strings and small value types
+  m.def("join_strings", [](const std::vector<std::string> &v, const std::string &d) { return join_strings(v, d); });
+  m.def("join_ints", [](const VI &v, const std::string &d) { return join_strings(v, d, [](int x) { return std::to_string(x); }); });
+  m.def("indent", &indent, py::arg("text"), py::arg("indent_size") = 2);
+  m.def("commutative_pair", [](int a, int b) {
+    commutative_pair<int> p(a, b);
+    return std::make_pair(p.max(), p.min());
+  });
+  m.def("commutative_pair_compare", [](int a, int b, int c2, int d) {
+    commutative_pair<int> p(a, b), q(c2, d);
+    return py::make_tuple(p == q, p != q, p < q);
+  });
+  m.def("query_set_apply", [](std::optional<SI> allowed, const SI &universe) {
+    auto q = allowed ? query_set<int>::match_values_in(*allowed) : query_set<int>::matchall();
+    return q.apply(universe);
+  }, py::arg("allowed"), py::arg("universe"), "None = match everything");
+  m.def("query_set_intersect", [](std::optional<SI> a, std::optional<SI> b) -> std::optional<SI> {
+    auto qa = a ? query_set<int>::match_values_in(*a) : query_set<int>::matchall();
+    auto qb = b ? query_set<int>::match_values_in(*b) : query_set<int>::matchall();
+    auto q = qa.intersect(qb);
+    if (q.is_matchall()) return std::nullopt;
+    return q.allowed_values();
+  });
+  m.def("query_set_includes", [](std::optional<SI> a, int v) {
+    return (a ? query_set<int>::match_values_in(*a) : query_set<int>::matchall()).includes(v);
+  });
+  m.def("stack_string_roundtrip", [](const std::string &s2) {
+    stack_string<16> t(s2);
+    t.push_back('!');
+    return py::make_tuple((std::string)t, t.size(), t.length());
+  });
+  m.def("stack_map_items", [](const std::vector<std::pair<int, int>> &writes) {
+    stack_map<int, int, 4> mp;
+    for (auto &kv : writes) mp[kv.first] = kv.second;
+    return mp.sorted_items();
+  });
+  m.def("stack_map_at", [](const std::vector<std::pair<int, int>> &writes, int key) {
+    stack_map<int, int, 4> mp;
+    for (auto &kv : writes) mp.insert(kv.first, kv.second);
+    return mp.at(key);
+  });
   // sets
   m.def("set_minus", [](const SI &a, const SI &b) { return set_minus(a, b); });
   m.def("set_difference", [](const SI &a, const SI &b) { return set_difference(a, b); });

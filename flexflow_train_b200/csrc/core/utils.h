@@ -382,6 +382,11 @@ public:
   static constexpr size_t capacity() { return MAXSIZE; }
   const T *begin() const { return data_.data(); }
   const T *end() const { return data_.data() + n_; }
+  T *begin() { return data_.data(); }
+  T *end() { return data_.data() + n_; }
+  T &operator[](size_t i) { return data_[i]; }
+  const T &operator[](size_t i) const { return data_[i]; }
+  T &back() { return at(n_ - 1); }
 
 private:
   std::array<T, MAXSIZE> data_{};

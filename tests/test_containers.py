@@ -286,3 +286,56 @@ def test_map_merges_match_python(a, b):
     assert C.is_submapeq_of(a, {**b, **a}) and C.is_submapeq_of(a, b) == all(k in b and b[k] == v for k, v in a.items())
     inv = C.invert_map(a)
     assert sorted(k for ks in inv.values() for k in ks) == sorted(a) and all(a[k] == v for v, ks in inv.items() for k in ks)
+
+
+# ------------------------------------------------------------------ strings and small value types
+def test_join_strings_and_indent():
+    assert C.join_strings(["a", "b", "c"], ", ") == "a, b, c" and C.join_strings([], ", ") == "" and C.join_strings(["x"], "-") == "x"
+    assert C.join_ints([1, 2, 3], "x") == "1x2x3"
+    # the reference's cases (lib/utils/test/src/utils/indent.cc)
+    assert C.indent("") == "  "
+    assert C.indent("hello world") == "  hello world"
+    assert C.indent("\na b\nc d\ne f\ng\n") == "  \n  a b\n  c d\n  e f\n  g\n  "
+    assert C.indent("   a b  \nc   d e\n     ") == "     a b  \n  c   d e\n       "
+    assert C.indent("a\nb", 4) == "    a\n    b"
+
+
+def test_commutative_pair():
+    assert C.commutative_pair(1, 2) == (2, 1) == C.commutative_pair(2, 1)
+    assert C.commutative_pair_compare(1, 2, 2, 1) == (True, False, False)
+    assert C.commutative_pair_compare(1, 2, 1, 3) == (False, True, True)      # ordered by (max, min)
+    assert C.commutative_pair_compare(1, 3, 2, 2) == (False, True, False)
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.integers(-20, 20), st.integers(-20, 20), st.integers(-20, 20), st.integers(-20, 20))
+def test_commutative_pair_properties(a, b, c2, d):
+    hi, lo = C.commutative_pair(a, b)
+    assert hi >= lo and {hi, lo} == {a, b}
+    eq, ne, lt = C.commutative_pair_compare(a, b, c2, d)
+    assert eq == (sorted((a, b)) == sorted((c2, d))) and ne == (not eq)
+    assert lt == ((max(a, b), min(a, b)) < (max(c2, d), min(c2, d)))
+    assert C.commutative_pair_compare(a, b, b, a) == (True, False, False)
+
+
+def test_query_set():
+    universe = {1, 2, 3, 4}
+    assert C.query_set_apply(None, universe) == universe                   # match-all
+    assert C.query_set_apply(set(), universe) == set()                     # match-none
+    assert C.query_set_apply({2, 9}, universe) == {2}
+    assert C.query_set_includes(None, 7) and C.query_set_includes({7}, 7) and not C.query_set_includes({1}, 7)
+    assert C.query_set_intersect(None, None) is None
+    assert C.query_set_intersect(None, {1, 2}) == {1, 2} == C.query_set_intersect({1, 2}, None)
+    assert C.query_set_intersect({1, 2}, {2, 3}) == {2}
+
+
+def test_stack_string_and_stack_map():
+    assert C.stack_string_roundtrip("Hello") == ("Hello!", 6, 6) and C.stack_string_roundtrip("") == ("!", 1, 1)
+    with pytest.raises(Exception):
+        C.stack_string_roundtrip("x" * 16)                                  # capacity 16, one more character is pushed
+    assert C.stack_map_items([(2, 20), (1, 10), (2, 21)]) == [(1, 10), (2, 21)]
+    assert C.stack_map_at([(1, 10), (2, 20)], 2) == 20
+    with pytest.raises(IndexError):
+        C.stack_map_at([(1, 10)], 3)
+    with pytest.raises(Exception):
+        C.stack_map_items([(i, i) for i in range(5)])                       # capacity 4
