@@ -610,6 +610,25 @@ Graph graph_from_v1(const Json &j) {
     tmp.at(dst).ins.push_back({slot_from_string(e.at("dstSlot").as_string()),
                                {(int)e.at("srcNode").as_int(), slot_from_string(e.at("srcSlot").as_string())}});
   }
+  // the file must be closed under its own references: every value an edge reads and every value the graph lists as an
+  // output has a label (shape), and every endpoint is a labelled node
+  auto has_output = [&](int node, Slot slot) {
+    auto it = tmp.find(node);
+    if (it == tmp.end()) return false;
+    for (auto &o : it->second.outs)
+      if (o.slot == slot) return true;
+    return false;
+  };
+  for (auto &kv : tmp)
+    for (auto &in : kv.second.ins)
+      if (!has_output(in.second.first, in.second.second))
+        throw Error("v1 graph: node " + std::to_string(kv.first) + " reads output " + to_string(in.second.second) + " of node " +
+                    std::to_string(in.second.first) + ", which has no output label");
+  if (raw.at("graph").contains("outputs"))
+    for (auto &o : raw.at("graph").at("outputs").items())
+      if (!has_output((int)o.at("node").as_int(), slot_from_string(o.at("slot_name").as_string())))
+        throw Error("v1 graph: output " + o.at("slot_name").as_string() + " of node " + std::to_string((int)o.at("node").as_int()) +
+                    " is listed by the graph but has no output label");
   // insert in dependency order, remembering the id translation
   std::map<int, NodeId> remap;
   Graph g;

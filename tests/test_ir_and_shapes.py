@@ -157,3 +157,45 @@ def test_json_optional_is_null_and_parser_round_trip():
     assert lin["attrs"]["activation"] is None and lin["attrs"]["regularizer"] is None
     assert json.loads(c.json_roundtrip('{"a": [1, 2.5, null, true, "x\\n"], "b": {"c": -3}}')) == \
         {"a": [1, 2.5, None, True, "x\n"], "b": {"c": -3}}
+
+
+# ------------------------------------------------------------------ v1 files against hand-written golden files
+def _golden(name):
+    import os
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name)) as f:
+        return json.load(f)
+
+
+def test_v1_computation_graph_matches_the_golden_file():
+    # field names, variant tags ({"type", "value"}), [key, value] pairs for maps with non-string keys, null for empty
+    # optionals and enum value names are pinned by a file written by hand from the format description
+    b = c.GraphBuilder()
+    x = b.create_input([4, 6], "FLOAT", name="x")
+    b.dense(x, 3, "RELU", False, name="fc")
+    gold = _golden("v1_computation_graph_linear_relu.json")
+    assert b.graph.to_v1() == gold
+    back = c.Graph.from_v1(gold)
+    assert back.signature() == b.graph.signature() and back.to_v1() == gold
+    lin = [n for n in back.nodes() if n["type"] == "LINEAR"][0]
+    assert lin["attrs"]["activation"] == "RELU" and lin["attrs"]["use_bias"] is False and lin["name"] == "fc"
+
+
+def test_v1_mapped_parallel_graph_matches_the_golden_file():
+    pb = c.GraphBuilder(parallel=True)
+    x = pb.create_input([8, 16], "FLOAT", name="x")
+    pb.dense(pb.parallel_partition(x, 0, 2, name="cut"), 4, None, False, name="fc")
+    ms = c.MachineSpecification(1, 2)
+    mapped = c.evaluate_pcg(pb.graph, ms, c.CostEstimator(ms))["mapped_pcg"]
+    gold = _golden("v1_mapped_pcg_partitioned_linear.json")
+    assert mapped.to_v1(parallel=True) == gold
+    back = c.Graph.from_v1(gold)
+    assert back.is_mapped() and back.signature() == mapped.signature()
+    # a file that names an unknown operator tag or lacks a label is refused with a message, not half-read
+    bad = json.loads(json.dumps(gold))
+    bad["raw_graph"]["node_labels"][4][1]["op_attrs"]["type"] = "no_such_operator"
+    with pytest.raises(Exception):
+        c.Graph.from_v1(bad)
+    bad = json.loads(json.dumps(gold))
+    del bad["raw_graph"]["output_labels"][4]
+    with pytest.raises(Exception):
+        c.Graph.from_v1(bad)
