@@ -199,3 +199,24 @@ def test_v1_mapped_parallel_graph_matches_the_golden_file():
     del bad["raw_graph"]["output_labels"][4]
     with pytest.raises(Exception):
         c.Graph.from_v1(bad)
+
+
+def test_sp_decomposition_json_form():
+    # {"type": "series" | "parallel", "left_child", "right_child"} / {"type": "leaf", "value": n}, binary and left-associative
+    # (lib/pcg/src/pcg/file_format/v1/v1_binary_sp_decomposition/json.cc)
+    b = c.GraphBuilder()
+    x = b.create_input([4, 6], "FLOAT", name="x")
+    y = b.dense(x, 3, "RELU", True, name="fc")
+    tree, exact = c.get_graph_sp_decomposition(b.graph)
+    assert exact
+    j = c.sp_to_json(c.sp_left_associative_binary(tree))     # the n-ary tree has a three-way parallel stage
+    leaf = lambda n: {"type": "leaf", "value": n}   # noqa: E731
+    assert j["type"] == "series" and j["right_child"] == leaf(y[0])
+    par = j["left_child"]                            # ((input | weight) | bias), left-associative
+    assert par["type"] == "parallel" and par["left_child"]["type"] == "parallel" and par["right_child"]["type"] == "leaf"
+    leaves = {par["right_child"]["value"], par["left_child"]["left_child"]["value"], par["left_child"]["right_child"]["value"]}
+    assert leaves == {n["id"] for n in b.graph.nodes() if n["type"] in ("INPUT", "WEIGHT")}
+    assert c.sp_nodes(c.sp_from_json(j)) == c.sp_nodes(tree)
+    for bad in ({"type": "leaf"}, {"type": "series", "left_child": leaf(0)}, {"type": "tree", "value": 1}):
+        with pytest.raises(Exception):
+            c.sp_from_json(bad)
