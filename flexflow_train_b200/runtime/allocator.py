@@ -199,3 +199,149 @@ def tensor_accessor_matmul(a: TensorAccessor, b: TensorAccessor, allocator: Opti
                 s += A[i][k] * B[k][j]
             out.tensor[i, j] = s
     return out
+
+
+# ------------------------------------------------------------------------------------------ accessor utilities
+# Host-side helpers over accessors, the vocabulary the reference's kernel tests are written in
+# (lib/kernels/include/kernels/{map_tensor_accessors,compare_tensor_accessors,tensor_accessor_reductions,
+# tensor_accessor_unary_ops,reduce_tensor_accessor,create_accessor_with_contents}.h).  They work on CPU and GPU accessors
+# alike (the work runs as torch operators on the accessor's device); functions given as Python callables are applied
+# element by element on the host.
+def _out(alloc: Optional[Allocator], shape, dtype, like: torch.Tensor) -> TensorAccessor:
+    if alloc is None:
+        return TensorAccessor(torch.empty(list(shape), dtype=dtype, device=like.device), True)
+    return TensorAccessor(alloc.allocate(list(shape), dtype), True)
+
+
+def _need_writable(a: TensorAccessor):
+    if not a.writable:
+        raise PermissionError("read-only accessor")
+
+
+def create_accessor_with_contents(contents, dtype: torch.dtype = torch.float32, allocator: Optional[Allocator] = None,
+                                  writable: bool = True) -> TensorAccessor:
+    """An accessor holding the nested list `contents` (1-d to 4-d in the reference; any rank here).  Ragged input is an error."""
+    try:
+        t = torch.tensor(contents, dtype=dtype)
+    except (ValueError, TypeError) as e:
+        raise ValueError(f"contents are not a rectangular nested list: {e}") from None
+    out = _out(allocator, t.shape, dtype, t)
+    out.tensor.copy_(t)
+    return TensorAccessor(out.tensor, writable)
+
+
+def map_tensor_accessor(a: TensorAccessor, f, allocator: Optional[Allocator] = None, out_dtype: Optional[torch.dtype] = None) -> TensorAccessor:
+    """A new accessor with f applied to every element."""
+    flat = a.tensor.detach().cpu().reshape(-1).tolist()
+    vals = [f(v) for v in flat]
+    dt = out_dtype or a.dtype
+    out = _out(allocator, a.shape, dt, a.tensor)
+    out.tensor.copy_(torch.tensor(vals, dtype=dt).reshape(a.shape))
+    return out
+
+
+def map_tensor_accessor_inplace(a: TensorAccessor, f) -> None:
+    _need_writable(a)
+    a.tensor.copy_(map_tensor_accessor(a, f).tensor)
+
+
+def map_tensor_accessors2(lhs: TensorAccessor, rhs: TensorAccessor, f, allocator: Optional[Allocator] = None,
+                          out_dtype: Optional[torch.dtype] = None) -> TensorAccessor:
+    """f(l, r) element by element over two accessors of the same shape."""
+    if lhs.shape != rhs.shape:
+        raise ValueError(f"map over accessors of different shapes: {lhs.shape} and {rhs.shape}")
+    lv, rv = lhs.tensor.detach().cpu().reshape(-1).tolist(), rhs.tensor.detach().cpu().reshape(-1).tolist()
+    dt = out_dtype or lhs.dtype
+    out = _out(allocator, lhs.shape, dt, lhs.tensor)
+    out.tensor.copy_(torch.tensor([f(x, y) for x, y in zip(lv, rv)], dtype=dt).reshape(lhs.shape))
+    return out
+
+
+def _compare(op):
+    def run(lhs: TensorAccessor, rhs: TensorAccessor, allocator: Optional[Allocator] = None) -> TensorAccessor:
+        if lhs.shape != rhs.shape or lhs.dtype != rhs.dtype:
+            raise ValueError(f"comparison of accessors of different shape or dtype: {lhs.shape} {lhs.dtype} and {rhs.shape} {rhs.dtype}")
+        out = _out(allocator, lhs.shape, torch.bool, lhs.tensor)
+        out.tensor.copy_(op(lhs.tensor, rhs.tensor.to(lhs.tensor.device)))
+        return out
+    return run
+
+
+compare_tensor_accessors_lt = _compare(torch.lt)
+compare_tensor_accessors_le = _compare(torch.le)
+compare_tensor_accessors_gt = _compare(torch.gt)
+compare_tensor_accessors_ge = _compare(torch.ge)
+compare_tensor_accessors_eq = _compare(torch.eq)
+compare_tensor_accessors_ne = _compare(torch.ne)
+
+
+def tensor_accessor_all(a: TensorAccessor) -> bool:
+    if a.dtype != torch.bool:
+        raise TypeError("tensor_accessor_all wants a BOOL accessor")
+    return bool(a.tensor.all().item())
+
+
+def tensor_accessor_any(a: TensorAccessor) -> bool:
+    if a.dtype != torch.bool:
+        raise TypeError("tensor_accessor_any wants a BOOL accessor")
+    return bool(a.tensor.any().item())
+
+
+def tensor_accessor_scale_by_constant(a: TensorAccessor, constant: float, allocator: Optional[Allocator] = None) -> TensorAccessor:
+    out = _out(allocator, a.shape, a.dtype, a.tensor)
+    out.tensor.copy_(a.tensor * constant)
+    return out
+
+
+def tensor_accessor_scale_by_constant_inplace(a: TensorAccessor, constant: float) -> None:
+    _need_writable(a)
+    a.tensor.mul_(constant)
+
+
+def tensor_accessor_relu(a: TensorAccessor, allocator: Optional[Allocator] = None) -> TensorAccessor:
+    out = _out(allocator, a.shape, a.dtype, a.tensor)
+    out.tensor.copy_(torch.relu(a.tensor))
+    return out
+
+
+def tensor_accessor_broadcast(a: TensorAccessor, target_shape: Sequence[int], allocator: Optional[Allocator] = None) -> TensorAccessor:
+    """numpy broadcasting to `target_shape` (rank promotion at the front, size-1 dims expanded)."""
+    try:
+        b = a.tensor.expand(list(target_shape))
+    except RuntimeError:
+        raise ValueError(f"{a.shape} does not broadcast to {list(target_shape)}") from None
+    out = _out(allocator, target_shape, a.dtype, a.tensor)
+    out.tensor.copy_(b)
+    return out
+
+
+def tensor_accessor_transpose(a: TensorAccessor, allocator: Optional[Allocator] = None) -> TensorAccessor:
+    if a.tensor.dim() != 2:
+        raise ValueError("transpose of a 2-d accessor")
+    out = _out(allocator, [a.shape[1], a.shape[0]], a.dtype, a.tensor)
+    out.tensor.copy_(a.tensor.t())
+    return out
+
+
+def reduce_tensor_accessor_in_dims(a: TensorAccessor, dims: Sequence[int], f, allocator: Optional[Allocator] = None) -> TensorAccessor:
+    """Folds f(acc, element) over the given dims (which disappear from the shape); the first element seeds acc."""
+    dims = sorted(set(int(d) for d in dims))
+    if any(d < 0 or d >= a.tensor.dim() for d in dims):
+        raise ValueError(f"reduce dims {dims} outside a {a.tensor.dim()}-d accessor")
+    keep = [d for d in range(a.tensor.dim()) if d not in dims]
+    moved = a.tensor.detach().cpu().permute(keep + dims).reshape([a.shape[d] for d in keep] + [-1])
+    rows = moved.reshape(-1, moved.shape[-1]).tolist()
+    vals = []
+    for row in rows:
+        acc = row[0]
+        for v in row[1:]:
+            acc = f(acc, v)
+        vals.append(acc)
+    out = _out(allocator, [a.shape[d] for d in keep], a.dtype, a.tensor)
+    out.tensor.copy_(torch.tensor(vals, dtype=a.dtype).reshape([a.shape[d] for d in keep]))
+    return out
+
+
+def tensor_accessor_reduce(a: TensorAccessor, dim: int, allocator: Optional[Allocator] = None) -> TensorAccessor:
+    """Sum over one dim."""
+    return reduce_tensor_accessor_in_dims(a, [dim], lambda x, y: x + y, allocator)

@@ -100,3 +100,70 @@ def test_cpu_executable_plans_its_workspace_through_the_handle():
     g = core.build_model("mlp", {"batch_size": 8, "input_dim": 16, "hidden": [32], "num_classes": 4})
     ex = Executable(g, ExecConfig(device="cpu", compute_dtype="fp32"))
     assert ex.handle.allocator is ex.allocator and ex.handle.workspace is ex.scratch_f32() and ex.handle.workspace is not None
+
+
+# ------------------------------------------------------------------ accessor utilities
+# cases after lib/kernels/test/src/kernels/{map_tensor_accessors,compare_tensor_accessors,tensor_accessor_reductions,
+# tensor_accessor_unary_ops,reduce_tensor_accessor,create_accessor_with_contents}.cc
+def test_create_accessor_with_contents():
+    a = A.create_accessor_with_contents([[1, 2, 3], [4, 5, 6]], torch.float32)
+    assert a.shape == [2, 3] and a.at(1, 2) == 6.0 and a.writable
+    r = A.create_accessor_with_contents([[[1], [2]]], torch.int32, writable=False)
+    assert r.shape == [1, 2, 1] and r.dtype == torch.int32 and not r.writable
+    alloc = A.TrackedAllocator(A.LocalCPUAllocator())
+    A.create_accessor_with_contents([1.0, 2.0], allocator=alloc)
+    assert alloc.current_bytes == 8
+    with pytest.raises(ValueError):
+        A.create_accessor_with_contents([[1, 2], [3]])
+
+
+def test_map_tensor_accessors():
+    a = A.create_accessor_with_contents([[1, 3, 2], [2, 1, 5]], torch.float32)
+    assert A.map_tensor_accessor(a, lambda v: v + 1).tensor.tolist() == [[2, 4, 3], [3, 2, 6]]
+    assert A.map_tensor_accessor(a, lambda v: v > 2, out_dtype=torch.bool).tensor.tolist() == [[False, True, False], [False, False, True]]
+    b = A.create_accessor_with_contents([[0, 2, 5], [3, 3, 8]], torch.float32)
+    assert A.map_tensor_accessors2(a, b, lambda x, y: x + 2 * y).tensor.tolist() == [[1, 7, 12], [8, 7, 21]]
+    A.map_tensor_accessor_inplace(a, lambda v: v * v)
+    assert a.tensor.tolist() == [[1, 9, 4], [4, 1, 25]]
+    with pytest.raises(ValueError):
+        A.map_tensor_accessors2(a, A.create_accessor_with_contents([1.0]), lambda x, y: x)
+    with pytest.raises(PermissionError):
+        A.map_tensor_accessor_inplace(A.read_only(a), lambda v: v)
+
+
+def test_compare_tensor_accessors_and_reductions():
+    lhs = A.create_accessor_with_contents([[1, 3, 2], [2, 1, 5]], torch.float32)
+    rhs = A.create_accessor_with_contents([[2, 3, 1], [2, 0, 9]], torch.float32)
+    assert A.compare_tensor_accessors_lt(lhs, rhs).tensor.tolist() == [[True, False, False], [False, False, True]]
+    assert A.compare_tensor_accessors_le(lhs, rhs).tensor.tolist() == [[True, True, False], [True, False, True]]
+    assert A.compare_tensor_accessors_gt(lhs, rhs).tensor.tolist() == [[False, False, True], [False, True, False]]
+    assert A.compare_tensor_accessors_ge(lhs, rhs).tensor.tolist() == [[False, True, True], [True, True, False]]
+    assert A.compare_tensor_accessors_eq(lhs, rhs).tensor.tolist() == [[False, True, False], [True, False, False]]
+    ne = A.compare_tensor_accessors_ne(lhs, rhs)
+    assert ne.dtype == torch.bool and A.tensor_accessor_any(ne) and not A.tensor_accessor_all(ne)
+    assert A.tensor_accessor_all(A.compare_tensor_accessors_eq(lhs, lhs)) and not A.tensor_accessor_any(A.compare_tensor_accessors_ne(lhs, lhs))
+    with pytest.raises(TypeError):
+        A.tensor_accessor_all(lhs)
+    with pytest.raises(ValueError):
+        A.compare_tensor_accessors_lt(lhs, A.create_accessor_with_contents([[1, 2, 3]], torch.float32))
+
+
+def test_tensor_accessor_unary_ops_and_reduce():
+    a = A.create_accessor_with_contents([[1, -3, 2], [-2, 1, 5]], torch.float32)
+    assert A.tensor_accessor_scale_by_constant(a, 2.0).tensor.tolist() == [[2, -6, 4], [-4, 2, 10]]
+    assert A.tensor_accessor_relu(a).tensor.tolist() == [[1, 0, 2], [0, 1, 5]]
+    assert A.tensor_accessor_transpose(a).tensor.tolist() == [[1, -2], [-3, 1], [2, 5]]
+    assert A.tensor_accessor_broadcast(A.create_accessor_with_contents([[1], [2]], torch.float32), [3, 2, 2]).tensor.tolist() == [[[1, 1], [2, 2]]] * 3
+    with pytest.raises(ValueError):
+        A.tensor_accessor_broadcast(a, [2, 4])
+    assert A.tensor_accessor_reduce(a, 0).tensor.tolist() == [-1, -2, 7] and A.tensor_accessor_reduce(a, 1).tensor.tolist() == [0, 4]
+    t = A.create_accessor_with_contents([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], torch.float32)
+    assert A.reduce_tensor_accessor_in_dims(t, [0, 2], max).tensor.tolist() == [6, 8]
+    assert A.reduce_tensor_accessor_in_dims(t, [1], lambda x, y: x - y).tensor.tolist() == [[-2, -2], [-2, -2]]
+    with pytest.raises(ValueError):
+        A.reduce_tensor_accessor_in_dims(t, [3], max)
+    w = A.create_accessor_with_contents([1.0, 2.0])
+    A.tensor_accessor_scale_by_constant_inplace(w, 3.0)
+    assert w.tensor.tolist() == [3.0, 6.0]
+    with pytest.raises(PermissionError):
+        A.tensor_accessor_scale_by_constant_inplace(A.read_only(w), 3.0)
