@@ -232,6 +232,42 @@ Json perform_copy_insertion(const Graph &g, const Json &list, const MachineSpec 
         cp["outputs"].push_back(o);
         out.push_back(cp);
       }
+    } else if (task == "BWD") {
+      // the mirror image: the gradient of one of this operator's outputs is produced by a consumer's backward task on
+      // the consumer's devices and has to reach this operator's devices first
+      NodeId n = (NodeId)inv.at("node").as_int();
+      auto dn = devices_of(g, n, m);
+      std::sort(dn.begin(), dn.end());
+      std::set<std::pair<NodeId, int>> done;   // (consumer, output slot): one copy per consumer and value
+      for (auto &in : inv.at("inputs").items()) {
+        if (in.at("role").as_string() != "GRAD") continue;
+        const Slot slot = slot_from_string(in.at("slot").as_string());
+        for (NodeId cons : g.successors(n)) {
+          bool reads = false;
+          for (auto &e : g.node(cons).inputs) reads = reads || (e.src.node == n && e.src.slot == slot);
+          if (!reads || !done.insert({cons, (int)slot}).second) continue;
+          auto dc = devices_of(g, cons, m);
+          std::sort(dc.begin(), dc.end());
+          if (dc == dn || std::includes(dc.begin(), dc.end(), dn.begin(), dn.end())) continue;
+          Json cp = Json::object();
+          cp["task"] = "COPY";
+          cp["node"] = n;
+          cp["op_type"] = "COPY";
+          cp["name"] = "";
+          cp["shard"] = Json();
+          cp["device"] = Json();
+          cp["src_devices"] = Json::from_ints(dc);
+          cp["dst_devices"] = Json::from_ints(dn);
+          cp["inputs"] = Json::array();
+          cp["outputs"] = Json::array();
+          cp["inputs"].push_back(value_ref(n, slot, "GRAD"));
+          Json o = value_ref(n, slot, "GRAD");
+          o["copy_for"] = n;
+          o["copy_from"] = cons;
+          cp["outputs"].push_back(o);
+          out.push_back(cp);
+        }
+      }
     }
     out.push_back(inv);
   }

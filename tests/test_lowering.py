@@ -221,3 +221,47 @@ def test_executor_plan_agrees_with_the_lowered_step(model):
     broken.insert(0, broken.pop(first_bwd))
     ex.step_plan = lambda: broken
     assert any("before its dependency" in p for p in check_plan(ex, inv))
+
+
+def _two_relus_on(dev_first: int, dev_second: int):
+    """x -> dense -> relu on a two-GPU machine: input, weight and dense on one device, the relu on the other."""
+    b = core.GraphBuilder(parallel=True)
+    x = b.create_input([4, 8], "FLOAT", name="x")
+    r1 = b.dense(x, 8, None, False, name="fc")
+    r2 = b.unary("RELU", r1, name="r2")
+    view = lambda d: {"start": {"node_idx": 0, "device_idx": d, "device_type": "GPU"}, "dimensions": []}   # noqa: E731
+    placement = {n["id"]: view(dev_first) for n in b.graph.nodes()}
+    placement[r2[0]] = view(dev_second)
+    return core.mapped_pcg_from_pcg_and_mapping(b.graph, placement), r1[0], r2[0]
+
+
+def test_copy_insertion_same_placement_needs_no_copies():
+    # the cases of lib/task-spec/test/src/task-spec/dynamic_graph/copy_insertion.cc: same mapping, no copies ...
+    ms = core.MachineSpecification(1, 2)
+    g, _, _ = _two_relus_on(0, 0)
+    inv = core.perform_copy_insertion(g, core.perform_pass_expansion(g, core.make_dynamic_graph(g)), ms)
+    assert [i for i in inv if i["task"] == "COPY"] == []
+
+
+def test_copy_insertion_moves_a_tensor_between_differently_placed_operators():
+    # ... and one tensor that has to move: forward from the producer's device to the consumer's, its gradient back
+    ms = core.MachineSpecification(1, 2)
+    g, r1, r2 = _two_relus_on(0, 1)
+    before = core.perform_pass_expansion(g, core.make_dynamic_graph(g))
+    inv = core.perform_copy_insertion(g, before, ms)
+    copies = [i for i in inv if i["task"] == "COPY"]
+    assert len(copies) == 2 and len(inv) == len(before) + 2
+    roles = sorted((cp["inputs"][0]["role"], cp["src_devices"], cp["dst_devices"]) for cp in copies)
+    assert roles == [("FWD", [0], [1]), ("GRAD", [1], [0])]
+    # the forward copy sits right before the consumer's forward task, the gradient copy right before the producer's backward task
+    pos = {(i["task"], i["node"], i["inputs"][0]["role"] if i["task"] == "COPY" else ""): k for k, i in enumerate(inv)}
+    assert pos[("COPY", r2, "FWD")] + 1 == pos[("FWD", r2, "")] and pos[("COPY", r1, "GRAD")] + 1 == pos[("BWD", r1, "")]
+    shard = core.perform_shard_expansion(g, inv, ms)
+    placed = [(i["device"], i["op_type"]) for i in shard if i["task"] == "COPY"]
+    assert len(placed) == 2
+    on = {i["node"]: i["device"] for i in shard if i["task"] == "FWD" and i["node"] in (r1, r2)}
+    assert on == {r1: 0, r2: 1}
+    # each device's slice holds its own operator's forward and backward tasks
+    for dev, node in ((0, r1), (1, r2)):
+        sl = core.perform_machine_slicing(shard, dev)
+        assert {i["task"] for i in sl if i.get("node") == node} >= {"FWD", "BWD"}
