@@ -367,6 +367,23 @@ PYBIND11_MODULE(_ffcore, m) {
   m.def("get_dominators", &get_dominators);
   m.def("get_post_dominators", &get_post_dominators);
   m.def("get_imm_dominator", &get_imm_dominator);
+  m.def("flipped", &flipped);
+  m.def("get_strict_dominators", &get_strict_dominators);
+  m.def("get_imm_dominators_map", &get_imm_dominators_map);
+  m.def("get_imm_post_dominator", &get_imm_post_dominator);
+  m.def("get_imm_post_dominators_map", &get_imm_post_dominators_map);
+  m.def("calculate_topo_rank", &calculate_topo_rank);
+  m.def("get_node_with_greatest_topo_rank", &get_node_with_greatest_topo_rank);
+  m.def("get_topological_ordering_from_starting_node", &get_topological_ordering_from_starting_node);
+  m.def("get_edge_topological_ordering", &get_edge_topological_ordering);
+  m.def("is_tree", &is_tree);
+  m.def("get_edges_from_subgraph_to_subgraph", &get_edges_from_subgraph_to_subgraph);
+  m.def("get_subgraph_outgoing_edges", &get_subgraph_outgoing_edges);
+  m.def("get_subgraph_successors", &get_subgraph_successors);
+  m.def("apply_contraction", &apply_contraction);
+  m.def("contract_node", &contract_node);
+  m.def("is_complete_bipartite_digraph", &is_complete_bipartite_digraph);
+  m.def("digraph_as_dot", &digraph_as_dot);
   m.def("get_weakly_connected_components", &get_weakly_connected_components);
   m.def("get_longest_path_lengths_from_root", &get_longest_path_lengths_from_root);
   m.def("get_descendants", &get_descendants);

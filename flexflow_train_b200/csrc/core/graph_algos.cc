@@ -227,6 +227,113 @@ bool SPTree::operator==(const SPTree &o) const {
   }
   return true;
 }
+
+DiGraph flipped(const DiGraph &g) {
+  DiGraph r;
+  for (int n : g.nodes()) r.add_node(n);
+  for (auto &e : g.edges()) r.add_edge(e.second, e.first);
+  return r;
+}
+std::map<int, std::set<int>> get_strict_dominators(const DiGraph &g) {
+  auto d = get_dominators(g);
+  for (auto &kv : d) kv.second.erase(kv.first);
+  return d;
+}
+std::map<int, std::optional<int>> get_imm_dominators_map(const DiGraph &g) {
+  std::map<int, std::optional<int>> out;
+  for (int n : g.nodes()) out[n] = get_imm_dominator(g, n);
+  return out;
+}
+std::optional<int> get_imm_post_dominator(const DiGraph &g, int n) { return get_imm_dominator(flipped(g), n); }
+std::map<int, std::optional<int>> get_imm_post_dominators_map(const DiGraph &g) { return get_imm_dominators_map(flipped(g)); }
+std::map<int, int> calculate_topo_rank(const DiGraph &g) {
+  std::map<int, int> rank;
+  int i = 0;
+  for (int n : topological_ordering(g)) rank[n] = i++;
+  return rank;
+}
+std::optional<int> get_node_with_greatest_topo_rank(const std::set<int> &nodes, const DiGraph &g) {
+  auto rank = calculate_topo_rank(g);
+  std::optional<int> best;
+  for (int n : nodes)
+    if (!best || rank.at(n) > rank.at(*best)) best = n;
+  return best;
+}
+std::vector<int> get_topological_ordering_from_starting_node(const DiGraph &g, int start) {
+  if (!is_acyclic(g)) throw std::runtime_error("topological ordering of a graph with a cycle");
+  std::set<int> keep = get_descendants(g, start);
+  keep.insert(start);
+  std::vector<int> out;
+  for (int n : topological_ordering(g))
+    if (keep.count(n)) out.push_back(n);
+  return out;
+}
+std::vector<std::pair<int, int>> get_edge_topological_ordering(const DiGraph &g) {
+  std::vector<std::pair<int, int>> out;
+  for (int n : topological_ordering(g))
+    for (int s2 : g.successors(n)) out.push_back({n, s2});
+  return out;
+}
+bool is_tree(const DiGraph &g) {
+  if (g.num_nodes() == 0) throw std::runtime_error("is_tree of an empty graph");
+  return g.sources().size() == 1 && get_weakly_connected_components(g).size() == 1 && g.num_edges() == g.num_nodes() - 1;
+}
+std::set<std::pair<int, int>> get_edges_from_subgraph_to_subgraph(const DiGraph &g, const std::set<int> &src, const std::set<int> &dst) {
+  for (int n : src)
+    if (dst.count(n)) throw std::runtime_error("the two node sets overlap");
+  std::set<std::pair<int, int>> out;
+  for (int a : src)
+    if (g.has_node(a))
+      for (int b : g.successors(a))
+        if (dst.count(b)) out.insert({a, b});
+  return out;
+}
+std::set<std::pair<int, int>> get_subgraph_outgoing_edges(const DiGraph &g, const std::set<int> &sub) {
+  std::set<std::pair<int, int>> out;
+  for (int a : sub)
+    if (g.has_node(a))
+      for (int b : g.successors(a))
+        if (!sub.count(b)) out.insert({a, b});
+  return out;
+}
+std::set<int> get_subgraph_successors(const DiGraph &g, const std::set<int> &sub) {
+  std::set<int> out;
+  for (auto &e : get_subgraph_outgoing_edges(g, sub)) out.insert(e.second);
+  return out;
+}
+DiGraph apply_contraction(const DiGraph &g, const std::map<int, int> &into) {
+  auto final_of = [&](int n) {
+    std::set<int> seen;
+    while (true) {
+      auto it = into.find(n);
+      if (it == into.end() || it->second == n) return n;
+      if (!seen.insert(n).second) throw std::runtime_error("contraction map has a cycle");
+      n = it->second;
+    }
+  };
+  DiGraph r;
+  for (int n : g.nodes()) r.add_node(final_of(n));
+  for (auto &e : g.edges()) r.add_edge(final_of(e.first), final_of(e.second));
+  return r;
+}
+DiGraph contract_node(const DiGraph &g, int from, int into) { return apply_contraction(g, {{from, into}}); }
+bool is_complete_bipartite_digraph(const DiGraph &g) {
+  auto src = g.sources(), snk = g.sinks();
+  std::set<int> s(src.begin(), src.end()), t(snk.begin(), snk.end());
+  if (s.size() + t.size() != g.num_nodes()) return false;
+  for (int n : s)
+    if (t.count(n)) return false;          // an isolated node is a source and a sink at once
+  for (int a : s)
+    for (int b : t)
+      if (!g.has_edge(a, b)) return false;
+  return g.num_edges() == s.size() * t.size();
+}
+std::string digraph_as_dot(const DiGraph &g) {
+  std::string out = "digraph {\n";
+  for (int n : g.nodes()) out += "  n" + std::to_string(n) + " [label=\"" + std::to_string(n) + "\"];\n";
+  for (auto &e : g.edges()) out += "  n" + std::to_string(e.first) + " -> n" + std::to_string(e.second) + ";\n";
+  return out + "}\n";
+}
 std::string SPTree::str() const {
   if (kind == Leaf) return std::to_string(node);
   std::string s = kind == Series ? "S(" : "P(";

@@ -49,6 +49,26 @@ std::set<int> get_descendants(const DiGraph &g, int n);
 std::set<int> get_ancestors(const DiGraph &g, int n);
 std::optional<int> get_lowest_common_ancestor(const DiGraph &g, const std::set<int> &nodes);
 bool is_2_terminal_dag(const DiGraph &g);
+// more of lib/utils/include/utils/graph/digraph/algorithms/*.h
+DiGraph flipped(const DiGraph &g);                                       // every edge reversed
+std::map<int, std::set<int>> get_strict_dominators(const DiGraph &g);    // dominators without the node itself
+std::map<int, std::optional<int>> get_imm_dominators_map(const DiGraph &g);
+std::optional<int> get_imm_post_dominator(const DiGraph &g, int n);
+std::map<int, std::optional<int>> get_imm_post_dominators_map(const DiGraph &g);
+std::map<int, int> calculate_topo_rank(const DiGraph &g);                // position in the topological order
+std::optional<int> get_node_with_greatest_topo_rank(const std::set<int> &nodes, const DiGraph &g);
+std::vector<int> get_topological_ordering_from_starting_node(const DiGraph &g, int start);   // start and its descendants
+std::vector<std::pair<int, int>> get_edge_topological_ordering(const DiGraph &g);           // by source in topological order
+bool is_tree(const DiGraph &g);                                          // one root, connected, |E| = |V| - 1
+std::set<std::pair<int, int>> get_edges_from_subgraph_to_subgraph(const DiGraph &g, const std::set<int> &src, const std::set<int> &dst);
+std::set<std::pair<int, int>> get_subgraph_outgoing_edges(const DiGraph &g, const std::set<int> &sub);   // edges leaving the node set
+std::set<int> get_subgraph_successors(const DiGraph &g, const std::set<int> &sub);                       // their heads
+// Nodes merged along `into` (node -> node it is merged into, chains followed to their end); edges follow their endpoints,
+// so an edge inside a merged group becomes a self loop.
+DiGraph apply_contraction(const DiGraph &g, const std::map<int, int> &into);
+DiGraph contract_node(const DiGraph &g, int from, int into);
+bool is_complete_bipartite_digraph(const DiGraph &g);                    // every source has an edge to every sink and nothing else
+std::string digraph_as_dot(const DiGraph &g);
 
 // Series-parallel decomposition tree.  N-ary after normalisation; binary variants keep exactly two children.
 struct SPTree {

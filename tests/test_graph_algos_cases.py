@@ -215,3 +215,90 @@ def test_cg_sp_decomposition_of_an_n_shaped_graph_is_not_exact():
     first = {n: order.index(n) for n in set(order)}
     for a_, b_ in ((x[0], o1[0]), (x[0], o2[0]), (o1[0], o3[0]), (o1[0], o4[0]), (o2[0], o4[0])):
         assert first[a_] < max(i for i, n in enumerate(order) if n == b_)
+
+
+# ------------------------------------------------------------------ more digraph algorithms
+from hypothesis import given, settings, strategies as st  # noqa: E402
+def _dg(edges, nodes=()):
+    g = c.DiGraph()
+    for n in nodes:
+        g.add_node(n)
+    for a, b in edges:
+        g.add_edge(a, b)
+    return g
+
+
+def test_apply_contraction_reference_case():
+    # lib/utils/test/src/utils/graph/digraph/algorithms/apply_contraction.cc
+    g = _dg([(0, 1), (0, 2), (0, 4), (1, 3), (2, 4), (3, 0), (3, 4), (3, 5), (4, 5)])
+    r = c.apply_contraction(g, {0: 3, 3: 2, 2: 2, 1: 4})
+    assert sorted(r.nodes()) == [2, 4, 5]
+    assert sorted(r.edges()) == [(2, 2), (2, 4), (2, 5), (4, 2), (4, 5)]
+    one = c.contract_node(_dg([(0, 1), (1, 2)]), 1, 0)
+    assert sorted(one.nodes()) == [0, 2] and sorted(one.edges()) == [(0, 0), (0, 2)]
+    with pytest.raises(Exception):
+        c.apply_contraction(g, {0: 1, 1: 0})
+
+
+def test_flipped_and_dominator_variants():
+    g = _dg([(0, 1), (0, 2), (1, 3), (2, 3), (3, 4)])
+    assert sorted(c.flipped(g).edges()) == [(1, 0), (2, 0), (3, 1), (3, 2), (4, 3)]
+    strict = c.get_strict_dominators(g)
+    assert strict[0] == set() and strict[3] == {0} and strict[4] == {0, 3}
+    assert c.get_imm_dominators_map(g) == {0: None, 1: 0, 2: 0, 3: 0, 4: 3}
+    assert c.get_imm_post_dominator(g, 0) == 3 and c.get_imm_post_dominator(g, 4) is None
+    assert c.get_imm_post_dominators_map(g) == {0: 3, 1: 3, 2: 3, 3: 4, 4: None}
+
+
+def test_topological_rank_and_orderings():
+    g = _dg([(0, 1), (0, 2), (1, 3), (2, 3), (3, 4), (5, 4)])
+    rank = c.calculate_topo_rank(g)
+    assert sorted(rank.values()) == list(range(6)) and all(rank[a] < rank[b] for a, b in g.edges())
+    assert c.get_node_with_greatest_topo_rank({0, 1, 3}, g) == 3 and c.get_node_with_greatest_topo_rank(set(), g) is None
+    assert c.get_topological_ordering_from_starting_node(g, 1) == [1, 3, 4]
+    assert c.get_topological_ordering_from_starting_node(g, 4) == [4]
+    order = c.get_edge_topological_ordering(g)
+    assert sorted(order) == sorted(g.edges()) and [rank[a] for a, _ in order] == sorted(rank[a] for a, _ in order)
+    with pytest.raises(Exception):
+        c.get_topological_ordering_from_starting_node(_dg([(0, 1), (1, 0)]), 0)
+
+
+def test_is_tree_and_complete_bipartite():
+    assert c.is_tree(_dg([(0, 1), (0, 2), (2, 3)])) and c.is_tree(_dg([], nodes=[7]))
+    assert not c.is_tree(_dg([(0, 1), (0, 2), (1, 3), (2, 3)]))          # a diamond: |E| = |V|
+    assert not c.is_tree(_dg([(0, 1), (2, 3)]))                          # two roots
+    with pytest.raises(Exception):
+        c.is_tree(c.DiGraph())
+    assert c.is_complete_bipartite_digraph(_dg([(0, 2), (0, 3), (1, 2), (1, 3)]))
+    assert not c.is_complete_bipartite_digraph(_dg([(0, 2), (0, 3), (1, 2)]))            # 1 -> 3 is missing
+    assert not c.is_complete_bipartite_digraph(_dg([(0, 1), (1, 2)]))                    # a middle node
+    assert not c.is_complete_bipartite_digraph(_dg([(0, 1)], nodes=[5]))                 # an isolated node
+
+
+def test_subgraph_edge_queries_and_dot():
+    g = _dg([(0, 1), (0, 2), (1, 3), (2, 3), (3, 4)])
+    assert c.get_edges_from_subgraph_to_subgraph(g, {0, 1}, {2, 3}) == {(0, 2), (1, 3)}
+    assert c.get_edges_from_subgraph_to_subgraph(g, {4}, {0}) == set()
+    with pytest.raises(Exception):
+        c.get_edges_from_subgraph_to_subgraph(g, {0, 1}, {1, 2})
+    assert c.get_subgraph_outgoing_edges(g, {0, 1}) == {(0, 2), (1, 3)} and c.get_subgraph_successors(g, {0, 1}) == {2, 3}
+    assert c.get_subgraph_outgoing_edges(g, {0, 1, 2, 3, 4}) == set()
+    dot = c.digraph_as_dot(g)
+    assert dot.startswith("digraph {") and dot.count("->") == 5 and 'n3 [label="3"]' in dot
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(2, 9), st.integers(0, 10 ** 6))
+def test_dominator_variants_agree_on_random_dags(n, seed):
+    rng = random.Random(seed)
+    g = _dg([(a, b) for a in range(n) for b in range(a + 1, n) if rng.random() < 0.35] + [(0, k) for k in range(1, n)])
+    dom, strict, imm = c.get_dominators(g), c.get_strict_dominators(g), c.get_imm_dominators_map(g)
+    for v in g.nodes():
+        assert strict[v] == dom[v] - {v}
+        if v == 0:
+            assert imm[v] is None
+        else:
+            # the immediate dominator is the strict dominator that every other strict dominator dominates
+            assert imm[v] in strict[v] and all(d in dom[imm[v]] for d in strict[v])
+    f = c.flipped(c.flipped(g))
+    assert sorted(f.edges()) == sorted(g.edges())
