@@ -114,8 +114,8 @@ __device__ __forceinline__ uint32_t attn_drop_threshold(float p) {
 // in chunks of 16 scores whose sixteen special-function instructions are issued back to back (volatile keeps them in source
 // order).  A warp issues in order: an exponential followed directly by the add that consumes it stalls the warp for the
 // unit's latency each time, which held this phase at 0.4 of the unit's rate (0.641 -> 0.573 ms at batch 32 x 16 heads x 1024
-// x 128).  With dropout the mask arithmetic of the neighbouring scores already fills that latency, and the chunked form is
-// slower there (0.823 -> 0.850 ms); in the backward kernel, which has 96 registers per thread, it spills.
+// x 128; with dropout, after the mask generator became cheap, 0.604 -> 0.551 ms).  In the backward kernel, which has 96
+// registers per thread, the chunked form spills and is slower.
 __device__ __forceinline__ float fast_exp2_ordered(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -157,6 +157,44 @@ __device__ __forceinline__ float softmax_exp64(uint32_t (&rs)[64], float sl2, fl
     }
 #pragma unroll
     for (int i = 0; i < 16; i += 2) rs[(c + i) >> 1] = pack_bf162(e[i], e[i + 1]);   // registers (c + i) / 2 are already consumed
+  }
+  return (ls0 + ls1) + (ls2 + ls3);
+}
+
+// The same with dropout: the four group words of a chunk are drawn before its exponentials are issued (integer work that
+// runs under the special-function unit's latency), the mask is applied after the row sum has taken the undropped values.
+__device__ __forceinline__ float softmax_exp64_drop(uint32_t (&rs)[64], float sl2, float m, bool full, int kmax, uint32_t thr, uint32_t row_mix,
+                                                    uint32_t seed_hi, int k0) {
+  float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+  const float neg_m = -m;
+#pragma unroll
+  for (int c = 0; c < 64; c += 16) {
+    float e[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) e[i] = fmaf(__uint_as_float(rs[c + i]), sl2, neg_m);
+    uint32_t z[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) z[g] = attn_group_word(row_mix, seed_hi, (uint32_t)((k0 + c + 4 * g) >> 2));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) e[i] = fast_exp2_ordered(e[i]);
+    if (!full) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (c + i >= kmax) e[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      ls0 += e[i]; ls1 += e[i + 1]; ls2 += e[i + 2]; ls3 += e[i + 3];
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (z[g] * ATT_RC0 < thr) e[4 * g] = 0.f;
+      if (z[g] * ATT_RC1 < thr) e[4 * g + 1] = 0.f;
+      if (z[g] * ATT_RC2 < thr) e[4 * g + 2] = 0.f;
+      if (z[g] * ATT_RC3 < thr) e[4 * g + 3] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) rs[(c + i) >> 1] = pack_bf162(e[i], e[i + 1]);
   }
   return (ls0 + ls1) + (ls2 + ls3);
 }
@@ -365,9 +403,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q = q0 + r;
     const float sl2 = p.scale * LOG2E;
     float m = 0.f, l = 0.f;     // m: the maximum the row's exponentials are taken against (see RESCALE_GAP)
-    const bool drop = p.drop_p > 0.f;   // kept a run-time value: as a compile-time constant the mask arithmetic is hoisted and spills
     const uint32_t thr = attn_drop_threshold(p.drop_p);
-    const unsigned long long seed = drop ? attn_seed(p) : 0ull;
+    const unsigned long long seed = DROP ? attn_seed(p) : 0ull;
     const uint32_t seed_hi = (uint32_t)(seed >> 32);
     const uint32_t row_mix = attn_row_mix(seed, (unsigned long long)(b * p.H + h) * p.Sq + (unsigned long long)q);
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -442,33 +479,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float m_new = m;
       float lsum;
-      if constexpr (DROP) {
-        float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -m_new)), e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -m_new));
-          float e2 = fast_exp2(fmaf(__uint_as_float(rs[i + 2]), sl2, -m_new)), e3 = fast_exp2(fmaf(__uint_as_float(rs[i + 3]), sl2, -m_new));
-          if (!full) {
-            if (i >= kmax) e0 = 0.f;
-            if (i + 1 >= kmax) e1 = 0.f;
-            if (i + 2 >= kmax) e2 = 0.f;
-            if (i + 3 >= kmax) e3 = 0.f;
-          }
-          ls0 += e0; ls1 += e1; ls2 += e2; ls3 += e3;
-          if (drop) {
-            const uint32_t z = attn_group_word(row_mix, seed_hi, (uint32_t)((k0 + i) >> 2));
-            if (z * ATT_RC0 < thr) e0 = 0.f;
-            if (z * ATT_RC1 < thr) e1 = 0.f;
-            if (z * ATT_RC2 < thr) e2 = 0.f;
-            if (z * ATT_RC3 < thr) e3 = 0.f;
-          }
-          rs[i >> 1] = pack_bf162(e0, e1);            // probabilities packed in place (pair i/2, i/2 + 1 are already consumed)
-          rs[(i >> 1) + 1] = pack_bf162(e2, e3);
-        }
-        lsum = (ls0 + ls1) + (ls2 + ls3);
-      } else {
-        lsum = softmax_exp64(rs, sl2, m_new, full, kmax);
-      }
+      if constexpr (DROP) lsum = softmax_exp64_drop(rs, sl2, m_new, full, kmax, thr, row_mix, seed_hi, k0);
+      else lsum = softmax_exp64(rs, sl2, m_new, full, kmax);
       if (tr) attn_trace(p, 3, j);
       if (tr) attn_trace(p, 4, j);
       // 64 probabilities = 32 columns of bf16 pairs: half 0 writes columns 0-31, half 1 columns 32-63 of this row of S(j)'s
