@@ -10,6 +10,108 @@ namespace py = pybind11;
 namespace ff {
 
 // ---------------------------------------------------------------------------------------------- isomorphism
+// A graph cannot be given chosen node ids (add_node numbers them), so a permutation is realised by inserting the nodes in an
+// order in which the ids come out right where that is possible; where it is not (the new ids would break "producers first"),
+// the nodes are inserted in topological order and `assigned` reports the ids they got.
+OpenDataflowGraph permute_node_ids(const OpenDataflowGraphView &g, const std::map<int, int> &new_of_old, std::map<int, int> *assigned) {
+  std::set<int> seen;
+  for (int n : g.get_nodes()) {
+    auto it = new_of_old.find(n);
+    if (it == new_of_old.end()) throw std::invalid_argument("permute_node_ids: node " + std::to_string(n) + " has no new id");
+    if (!seen.insert(it->second).second) throw std::invalid_argument("permute_node_ids: two nodes map to the same id");
+  }
+  OpenDataflowGraph out;
+  std::map<int, int> in_map;
+  for (auto &gi : g.get_graph_inputs()) in_map[gi.idx] = out.add_input().idx;
+  std::map<int, int> got;
+  for (int n : g.topological_ordering()) {
+    std::vector<OpenDataflowValue> ins;
+    for (auto &v : g.get_inputs(n)) {
+      if (std::holds_alternative<DataflowOutput>(v)) {
+        const DataflowOutput &o = std::get<DataflowOutput>(v);
+        ins.push_back(DataflowOutput{got.at(o.node), o.idx});
+      } else {
+        ins.push_back(DataflowGraphInput{in_map.at(std::get<DataflowGraphInput>(v).idx)});
+      }
+    }
+    got[n] = out.add_node(ins, (int)g.get_outputs(n).size()).node;
+  }
+  if (assigned) *assigned = got;
+  return out;
+}
+OpenDataflowGraph permute_input_ids(const OpenDataflowGraphView &g, const std::map<int, int> &new_of_old) {
+  std::vector<std::pair<int, int>> by_new;   // (new id, old id)
+  std::set<int> seen;
+  for (auto &gi : g.get_graph_inputs()) {
+    auto it = new_of_old.find(gi.idx);
+    if (it == new_of_old.end()) throw std::invalid_argument("permute_input_ids: input " + std::to_string(gi.idx) + " has no new id");
+    if (!seen.insert(it->second).second) throw std::invalid_argument("permute_input_ids: two inputs map to the same id");
+    by_new.push_back({it->second, gi.idx});
+  }
+  std::sort(by_new.begin(), by_new.end());
+  OpenDataflowGraph out;
+  std::map<int, int> in_map;   // old id -> id in `out` (inputs are created in the order of their new ids)
+  for (auto &p : by_new) in_map[p.second] = out.add_input().idx;
+  std::map<int, int> got;
+  for (int n : g.topological_ordering()) {
+    std::vector<OpenDataflowValue> ins;
+    for (auto &v : g.get_inputs(n)) {
+      if (std::holds_alternative<DataflowOutput>(v)) {
+        const DataflowOutput &o = std::get<DataflowOutput>(v);
+        ins.push_back(DataflowOutput{got.at(o.node), o.idx});
+      } else {
+        ins.push_back(DataflowGraphInput{in_map.at(std::get<DataflowGraphInput>(v).idx)});
+      }
+    }
+    got[n] = out.add_node(ins, (int)g.get_outputs(n).size()).node;
+  }
+  return out;
+}
+bool is_isomorphic_under(const OpenDataflowGraphView &a, const OpenDataflowGraphView &b, const std::map<int, int> &node_map,
+                         const std::map<int, int> &input_map) {
+  if (a.get_nodes().size() != b.get_nodes().size() || a.get_graph_inputs().size() != b.get_graph_inputs().size()) return false;
+  std::set<int> img;
+  for (int n : a.get_nodes()) {
+    auto it = node_map.find(n);
+    if (it == node_map.end() || !b.has_node(it->second) || !img.insert(it->second).second) return false;
+    if (a.get_outputs(n).size() != b.get_outputs(it->second).size()) return false;
+    const auto &ia = a.get_inputs(n);
+    const auto &ib = b.get_inputs(it->second);
+    if (ia.size() != ib.size()) return false;
+    for (size_t i = 0; i < ia.size(); ++i) {
+      if (ia[i].index() != ib[i].index()) return false;
+      if (std::holds_alternative<DataflowOutput>(ia[i])) {
+        const DataflowOutput &x = std::get<DataflowOutput>(ia[i]), &y = std::get<DataflowOutput>(ib[i]);
+        auto m = node_map.find(x.node);
+        if (m == node_map.end() || m->second != y.node || x.idx != y.idx) return false;
+      } else {
+        auto m = input_map.find(std::get<DataflowGraphInput>(ia[i]).idx);
+        if (m == input_map.end() || m->second != std::get<DataflowGraphInput>(ib[i]).idx) return false;
+      }
+    }
+  }
+  return true;
+}
+std::string open_dataflow_graph_as_dot(const OpenDataflowGraphView &g) {
+  std::ostringstream o;
+  o << "digraph {\n";
+  for (auto &gi : g.get_graph_inputs()) o << "  i" << gi.idx << " [shape=box, label=\"input " << gi.idx << "\"];\n";
+  for (int n : g.get_nodes()) o << "  n" << n << " [label=\"" << n << "\"];\n";
+  for (int n : g.get_nodes()) {
+    const auto &ins = g.get_inputs(n);
+    for (size_t i = 0; i < ins.size(); ++i) {
+      if (std::holds_alternative<DataflowOutput>(ins[i])) {
+        const DataflowOutput &x = std::get<DataflowOutput>(ins[i]);
+        o << "  n" << x.node << " -> n" << n << " [label=\"" << x.idx << " -> " << i << "\"];\n";
+      } else {
+        o << "  i" << std::get<DataflowGraphInput>(ins[i]).idx << " -> n" << n << " [label=\"-> " << i << "\"];\n";
+      }
+    }
+  }
+  o << "}\n";
+  return o.str();
+}
+
 std::optional<std::map<int, int>> find_dataflow_isomorphism(const OpenDataflowGraphView &a, const OpenDataflowGraphView &b) {
   const std::vector<int> na = a.topological_ordering(), nb = b.topological_ordering();
   if (na.size() != nb.size() || a.get_graph_inputs().size() != b.get_graph_inputs().size()) return std::nullopt;
@@ -235,6 +337,33 @@ void bind_dataflow(py::module &root) {
     return py::make_tuple(r.graph, r.node_of, ins);
   });
   m.def("find_dataflow_isomorphism", &find_dataflow_isomorphism);
+  auto edges_to_py = [](const std::set<DataflowEdge> &es) {
+    py::list l;
+    for (auto &e : es) l.append(py::make_tuple(py::make_tuple(e.src.node, e.src.idx), py::make_tuple(e.dst.node, e.dst.idx)));
+    return l;
+  };
+  m.def("get_source_nodes", &get_source_nodes);
+  m.def("get_unused_open_dataflow_graph_inputs", [](const OpenDataflowGraphView &g) {
+    std::set<int> r;
+    for (auto &gi : get_unused_open_dataflow_graph_inputs(g)) r.insert(gi.idx);
+    return r;
+  });
+  m.def("get_dataflow_edges_from_node_to_node", [=](const OpenDataflowGraphView &g, int a, int b) { return edges_to_py(get_dataflow_edges_from_node_to_node(g, a, b)); });
+  m.def("get_subgraph_inputs", [](const OpenDataflowGraphView &g, std::set<int> nodes) {
+    py::list l;
+    for (auto &v : get_subgraph_inputs(g, nodes)) l.append(value_to_py(v));
+    return l;
+  });
+  m.def("get_subgraph_incoming_edges", [=](const OpenDataflowGraphView &g, std::set<int> nodes) { return edges_to_py(get_subgraph_incoming_edges(g, nodes)); });
+  m.def("get_subgraph_outgoing_edges", [=](const OpenDataflowGraphView &g, std::set<int> nodes) { return edges_to_py(get_subgraph_outgoing_dataflow_edges(g, nodes)); });
+  m.def("permute_node_ids", [](const OpenDataflowGraphView &g, std::map<int, int> new_of_old) {
+    std::map<int, int> got;
+    OpenDataflowGraph r = permute_node_ids(g, new_of_old, &got);
+    return py::make_tuple(r, got);
+  });
+  m.def("permute_input_ids", &permute_input_ids);
+  m.def("is_isomorphic_under", &is_isomorphic_under, py::arg("a"), py::arg("b"), py::arg("node_map"), py::arg("input_map") = std::map<int, int>{});
+  m.def("open_dataflow_graph_as_dot", &open_dataflow_graph_as_dot);
 
   // named slots and labels, instantiated for what Python can hold: string slots, object labels
   using KG = KwargDataflowGraph<std::string>;

@@ -226,6 +226,58 @@ inline OpenSubgraphResult get_open_subgraph(const OpenDataflowGraphView &g, cons
   return r;
 }
 
+// ---- algorithms over open dataflow graphs (lib/utils/include/utils/graph/{dataflow_graph,open_dataflow_graph}/algorithms/*.h)
+// nodes all of whose operands are graph inputs (or that have none)
+inline std::set<int> get_source_nodes(const OpenDataflowGraphView &g) {
+  std::set<int> r;
+  for (int n : g.get_nodes()) {
+    bool src = true;
+    for (auto &v : g.get_inputs(n)) src = src && std::holds_alternative<DataflowGraphInput>(v);
+    if (src) r.insert(n);
+  }
+  return r;
+}
+inline std::set<DataflowGraphInput> get_unused_open_dataflow_graph_inputs(const OpenDataflowGraphView &g) {
+  std::set<DataflowGraphInput> r;
+  for (auto &gi : g.get_graph_inputs())
+    if (g.get_uses(gi).empty()) r.insert(gi);
+  return r;
+}
+inline std::set<DataflowEdge> get_dataflow_edges_from_node_to_node(const OpenDataflowGraphView &g, int src, int dst) {
+  DataflowEdgeQuery q;
+  q.src_nodes = std::set<int>{src};
+  q.dst_nodes = std::set<int>{dst};
+  return g.query_edges(q);
+}
+// the values a node set reads from outside itself: outputs of other nodes and graph inputs
+inline std::set<OpenDataflowValue> get_subgraph_inputs(const OpenDataflowGraphView &g, const std::set<int> &nodes) {
+  std::set<OpenDataflowValue> r;
+  for (int n : nodes)
+    for (auto &v : g.get_inputs(n))
+      if (!(std::holds_alternative<DataflowOutput>(v) && nodes.count(std::get<DataflowOutput>(v).node))) r.insert(v);
+  return r;
+}
+// edges from nodes outside the set to nodes inside it
+inline std::set<DataflowEdge> get_subgraph_incoming_edges(const OpenDataflowGraphView &g, const std::set<int> &nodes) {
+  std::set<DataflowEdge> r;
+  for (auto &e : g.query_edges())
+    if (nodes.count(e.dst.node) && !nodes.count(e.src.node)) r.insert(e);
+  return r;
+}
+inline std::set<DataflowEdge> get_subgraph_outgoing_dataflow_edges(const OpenDataflowGraphView &g, const std::set<int> &nodes) {
+  std::set<DataflowEdge> r;
+  for (auto &e : g.query_edges())
+    if (nodes.count(e.src.node) && !nodes.count(e.dst.node)) r.insert(e);
+  return r;
+}
+// the same graph with nodes (inputs) renumbered; the maps must be injective and cover every node (input)
+OpenDataflowGraph permute_node_ids(const OpenDataflowGraphView &g, const std::map<int, int> &new_of_old, std::map<int, int> *assigned = nullptr);
+OpenDataflowGraph permute_input_ids(const OpenDataflowGraphView &g, const std::map<int, int> &new_of_old);
+// does `node_map` (nodes of a -> nodes of b) together with `input_map` carry a onto b: same operands in the same order?
+bool is_isomorphic_under(const OpenDataflowGraphView &a, const OpenDataflowGraphView &b, const std::map<int, int> &node_map,
+                         const std::map<int, int> &input_map);
+std::string open_dataflow_graph_as_dot(const OpenDataflowGraphView &g);
+
 // closed graphs: the open graph without graph inputs
 class DataflowGraphView : public OpenDataflowGraphView {};
 class DataflowGraph : public OpenDataflowGraph {

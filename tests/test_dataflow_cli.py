@@ -159,3 +159,58 @@ def test_export_model_arch_uses_the_native_spec(capsys):
     assert out.startswith("usage: export-model-arch [-h] [--sp-decomposition] [--dot] [--preprocessed-dot] {")
     assert export_model_arch.main(["no_such_model"]) == 2
     assert "Invalid option for positional argument" in capsys.readouterr().err
+
+
+# ------------------------------------------------------------------ algorithms over open dataflow graphs
+def test_source_nodes_unused_inputs_and_edges_between_nodes():
+    g, x, (a, b, c, e), (a0, a1, b0, c0, e0) = diamond()
+    assert d.get_source_nodes(g) == {a}                       # only `a` reads nothing but graph inputs
+    assert d.get_unused_open_dataflow_graph_inputs(g) == set()
+    y = g.add_input()
+    assert d.get_unused_open_dataflow_graph_inputs(g) == {y[1]}
+    assert d.get_dataflow_edges_from_node_to_node(g, a, c) == [(a1, (c, 0))]
+    assert d.get_dataflow_edges_from_node_to_node(g, a, e) == [] and d.get_dataflow_edges_from_node_to_node(g, e, a) == []
+    lone = d.OpenDataflowGraph()
+    n, _ = lone.add_node([], 1)
+    assert d.get_source_nodes(lone) == {n}
+
+
+def test_subgraph_inputs_and_crossing_edges():
+    g, x, (a, b, c, e), (a0, a1, b0, c0, e0) = diamond()
+    assert sorted(d.get_subgraph_inputs(g, {b, c}), key=str) == sorted([a0, a1, x], key=str)
+    assert d.get_subgraph_inputs(g, {a, b, c, e}) == [x]
+    assert sorted(d.get_subgraph_incoming_edges(g, {b, c})) == [(a0, (b, 0)), (a1, (c, 0))]
+    assert sorted(d.get_subgraph_outgoing_edges(g, {b, c})) == [(b0, (e, 0)), (c0, (e, 1))]
+    assert d.get_subgraph_incoming_edges(g, {a}) == [] and d.get_subgraph_outgoing_edges(g, {e}) == []
+
+
+def test_permutations_keep_the_graph_isomorphic():
+    g, x, (a, b, c, e), outs = diamond()
+    same = {n: n for n in (a, b, c, e)}
+    assert d.is_isomorphic_under(g, g, same, {x[1]: x[1]})
+    assert not d.is_isomorphic_under(g, g, {a: a, b: c, c: b, e: e}, {x[1]: x[1]})      # b and c read different operands
+    h, got = d.permute_node_ids(g, {a: 3, b: 2, c: 1, e: 0})
+    assert sorted(got) == [a, b, c, e] and d.is_isomorphic_under(g, h, got, {x[1]: h.get_graph_inputs()[0][1]})
+    assert d.find_dataflow_isomorphism(g, h) is not None
+    with pytest.raises(Exception):
+        d.permute_node_ids(g, {a: 0, b: 0, c: 1, e: 2})
+    with pytest.raises(Exception):
+        d.permute_node_ids(g, {a: 0})
+    # two inputs swapped: the graph is isomorphic to the original under the swapped input map only
+    k = d.OpenDataflowGraph()
+    p, q = k.add_input(), k.add_input()
+    n, _ = k.add_node([p, q, q], 1)
+    s = d.permute_input_ids(k, {p[1]: q[1], q[1]: p[1]})
+    sn = s.get_nodes()[0]
+    assert d.is_isomorphic_under(k, s, {n: sn}, {p[1]: q[1], q[1]: p[1]})
+    assert not d.is_isomorphic_under(k, s, {n: sn}, {p[1]: p[1], q[1]: q[1]})
+    with pytest.raises(Exception):
+        d.permute_input_ids(k, {p[1]: 0, q[1]: 0})
+
+
+def test_open_dataflow_graph_as_dot():
+    g, x, (a, b, c, e), outs = diamond()
+    dot = d.open_dataflow_graph_as_dot(g)
+    assert dot.startswith("digraph {") and dot.rstrip().endswith("}")
+    assert dot.count("[shape=box") == 1 and dot.count(" -> n") == 6          # 4 node-to-node uses + 2 uses of the input
+    assert f'n{a} -> n{c} [label="1 -> 0"]' in dot and f'i{x[1]} -> n{c} [label="-> 1"]' in dot
