@@ -148,6 +148,71 @@ PYBIND11_MODULE(_ffcore, m) {
       })
       .def("is_mapped", &Graph::is_mapped)
       .def("signature", &Graph::signature)
+      // graph queries of the reference's computation_graph.h / parallel_computation_graph.h
+      .def("get_layer_by_name", [](const Graph &g, const std::string &name) {
+        std::vector<NodeId> found;
+        for (auto &kv : g.nodes())
+          if (kv.second.name == name) found.push_back(kv.first);
+        if (found.size() != 1) throw Error("get_layer_by_name: " + std::to_string(found.size()) + " layers are named \"" + name + "\"");
+        return found[0];
+      })
+      .def("get_incoming_tensors", [](const Graph &g, NodeId n) {
+        py::list l;
+        for (auto &e : g.node(n).inputs) l.append(py::make_tuple(to_string(e.dst_slot), py::make_tuple(e.src.node, to_string(e.src.slot))));
+        return l;
+      }, "(slot, value) of every operand, in slot order")
+      .def("get_incoming_inputs", [](const Graph &g, NodeId n) {
+        py::list l;
+        for (auto &e : g.node(n).inputs)
+          if (!is_weight_slot(g.node(n).type, e.dst_slot)) l.append(py::make_tuple(e.src.node, to_string(e.src.slot)));
+        return l;
+      }, "operands that are activations (the operator's incoming tensor role INPUT)")
+      .def("get_incoming_weights", [](const Graph &g, NodeId n) {
+        py::list l;
+        for (auto &e : g.node(n).inputs)
+          if (is_weight_slot(g.node(n).type, e.dst_slot)) l.append(py::make_tuple(e.src.node, to_string(e.src.slot)));
+        return l;
+      }, "operands that are parameters (role WEIGHT)")
+      .def("get_outgoing_tensors", [](const Graph &g, NodeId n) {
+        py::list l;
+        for (auto &o : g.node(n).outputs) l.append(py::make_tuple(n, to_string(o.slot)));
+        return l;
+      })
+      .def("get_all_tensors", [](const Graph &g) {
+        py::list l;
+        for (auto &v : g.all_values()) l.append(py::make_tuple(v.node, to_string(v.slot)));
+        return l;
+      })
+      .def("get_source_layer", [](const Graph &g, py::object v) { return value_from_py(v).node; })
+      .def("without_layer_names", [](const Graph &g) {
+        Graph r = g;
+        for (NodeId n : r.node_ids()) r.node(n).name.clear();
+        return r;
+      }, "a copy whose layers have no names (names do not take part in `signature`, so it is isomorphic to the original)")
+      .def("is_isomorphic_to", [](const Graph &a, const Graph &b) { return a.num_nodes() == b.num_nodes() && a.signature() == b.signature(); },
+           "same operators with the same attributes and shapes wired the same way, whatever the node ids and names")
+      .def("get_subgraph_incoming_edges", [](const Graph &g, std::set<NodeId> sub) {
+        py::list l;
+        for (NodeId n : sub)
+          for (auto &e : g.node(n).inputs)
+            if (!sub.count(e.src.node)) l.append(py::make_tuple(py::make_tuple(e.src.node, to_string(e.src.slot)), py::make_tuple(n, to_string(e.dst_slot))));
+        return l;
+      })
+      .def("get_subgraph_outgoing_edges", [](const Graph &g, std::set<NodeId> sub) {
+        py::list l;
+        for (NodeId n : sub)
+          for (auto &o : g.node(n).outputs)
+            for (auto &c2 : g.consumers(ValueRef{n, o.slot}))
+              if (!sub.count(c2.first)) l.append(py::make_tuple(py::make_tuple(n, to_string(o.slot)), py::make_tuple(c2.first, to_string(c2.second))));
+        return l;
+      })
+      .def("get_subgraph_successors", [](const Graph &g, std::set<NodeId> sub) {
+        std::set<NodeId> r;
+        for (NodeId n : sub)
+          for (NodeId s2 : g.successors(n))
+            if (!sub.count(s2)) r.insert(s2);
+        return r;
+      })
       .def("as_dot", &Graph::as_dot)
       .def("copy", [](const Graph &g) { return Graph(g); })
       .def("to_v1", [](const Graph &g, bool parallel) { return json_to_py(graph_to_v1(g, parallel)); }, py::arg("parallel") = false)

@@ -220,3 +220,54 @@ def test_sp_decomposition_json_form():
     for bad in ({"type": "leaf"}, {"type": "series", "left_child": leaf(0)}, {"type": "tree", "value": 1}):
         with pytest.raises(Exception):
             c.sp_from_json(bad)
+
+
+# ------------------------------------------------------------------ graph queries (lib/pcg/include/pcg/computation_graph.h)
+def _two_layer():
+    b = c.GraphBuilder()
+    x = b.create_input([4, 6], "FLOAT", name="x")
+    h = b.dense(x, 5, "RELU", True, name="fc1")
+    y = b.dense(h, 3, None, False, name="fc2")
+    return b.graph, x, h, y
+
+
+def test_graph_queries_by_name_and_role():
+    g, x, h, y = _two_layer()
+    fc1 = g.get_layer_by_name("fc1")
+    assert fc1 == h[0] and g.node(fc1)["type"] == "LINEAR"
+    with pytest.raises(Exception):
+        g.get_layer_by_name("no such layer")
+    assert g.get_incoming_inputs(fc1) == [x]
+    weights = g.get_incoming_weights(fc1)
+    assert len(weights) == 2 and all(g.node(w[0])["type"] == "WEIGHT" for w in weights)
+    assert [s for s, _ in g.get_incoming_tensors(fc1)] == ["INPUT", "WEIGHT", "BIAS"]
+    assert g.get_incoming_weights(x[0]) == [] and g.get_incoming_inputs(x[0]) == []
+    assert g.get_outgoing_tensors(fc1) == [h] and g.get_source_layer(y) == y[0]
+    assert sorted(g.get_all_tensors()) == sorted((n["id"], "OUTPUT") for n in g.nodes())
+
+
+def test_graph_isomorphism_ignores_names_and_ids():
+    g, x, h, y = _two_layer()
+    bare = g.without_layer_names()
+    assert all(n["name"] == "" for n in bare.nodes()) and bare.is_isomorphic_to(g) and g.get_layer_by_name("fc2") == y[0]
+    # the same layers added in another order (weights first) get other ids and are still the same graph
+    b = c.GraphBuilder()
+    x2 = b.create_input([4, 6], "FLOAT", name="other")
+    b.dense(b.dense(x2, 5, "RELU", True), 3, None, False)
+    assert b.graph.is_isomorphic_to(g)
+    b.unary("RELU", x2)
+    assert not b.graph.is_isomorphic_to(g)
+    wider = c.GraphBuilder()
+    wider.dense(wider.dense(wider.create_input([4, 6], "FLOAT"), 7, "RELU", True), 3, None, False)
+    assert not wider.graph.is_isomorphic_to(g)
+
+
+def test_graph_subgraph_edges():
+    g, x, h, y = _two_layer()
+    sub = {h[0]}
+    inc = g.get_subgraph_incoming_edges(sub)
+    assert len(inc) == 3 and ((x[0], "OUTPUT"), (h[0], "INPUT")) in inc
+    assert g.get_subgraph_outgoing_edges(sub) == [(h, (y[0], "INPUT"))]
+    assert g.get_subgraph_successors(sub) == {y[0]} and g.get_subgraph_successors({y[0]}) == set()
+    everything = {n["id"] for n in g.nodes()}
+    assert g.get_subgraph_incoming_edges(everything) == [] and g.get_subgraph_outgoing_edges(everything) == []
