@@ -241,3 +241,25 @@ def test_documentation_pages_are_current():
             assert importlib.util.find_spec(mod.rstrip(".")) is not None, mod
     for path in set(re.findall(r"`((?:csrc|runtime|frontend|parallel|utils|ops|compiler|bin)/[A-Za-z0-9_/.]+\.(?:py|cc|cu|cuh|h))`", text)):
         assert os.path.exists(os.path.join(os.path.dirname(docs), "flexflow_train_b200", path)), path
+
+
+def test_flexflow_python_launcher(tmp_path, capsys):
+    from flexflow_train_b200.bin import flexflow_python as fp
+    script = tmp_path / "train.py"
+    script.write_text("import sys, json\nprint(json.dumps(sys.argv[1:]))\n")
+    # one rank: the script runs in this process and sees only its own arguments
+    assert fp.main([str(script), "-ll:gpu", "1", "-ll:fsize", "14000", "-ll:zsize=2048", "-b", "64", "--epochs", "2"]) == 0
+    out = capsys.readouterr()
+    assert json.loads(out.out.strip().splitlines()[-1]) == ["-b", "64", "--epochs", "2"]
+    assert "-ll:fsize 14000" in out.err and "-ll:zsize=2048" in out.err and "-ll:gpu" not in out.err
+    # several ranks: a torch.distributed.run command with one process per GPU and a loopback rendezvous
+    ranks, opts, s, args, dropped = fp.plan([str(script), "-ll:gpu", "4", "--nodes", "2", "--node-rank", "1", "--master-addr", "10.0.0.1", "-b", "8"])
+    assert (ranks, s, args, dropped) == (4, str(script), ["-b", "8"], [])
+    cmd = fp.command(ranks, opts, s, args)
+    assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes"] and cmd[cmd.index("--nproc-per-node") + 1] == "4"
+    assert cmd[cmd.index("--node-rank") + 1] == "1" and cmd[cmd.index("--master-addr") + 1] == "10.0.0.1" and cmd[-3:] == [str(script), "-b", "8"]
+    assert fp.plan([str(script), "-ll:gpu=2"])[0] == 2
+    with pytest.raises(SystemExit):
+        fp.main([str(tmp_path / "missing.py"), "-ll:gpu", "1"])
+    with pytest.raises(SystemExit):
+        fp.plan([str(script), "-ll:gpu", "0"])
