@@ -66,6 +66,49 @@ def make_config_class():
                               "config_schema.FIELDS:\n\n" + "\n".join(f"    {f.name} ({getattr(f.type, '__name__', str(f.type))}, default {f.default!r}): {f.help}"
                                                                      for f in FIELDS)})
     cls.__module__ = __name__
+
+    # the legacy FFConfig surface (bindings/python/old/flexflow/core/flexflow_cffi.py: parse_args, get_current_time,
+    # begin_trace / end_trace, workers_per_node)
+    def parse_args(self, argv=None):
+        """Fills the fields that have a command-line flag from `argv` (default: sys.argv[1:]); unknown arguments and the
+        Legion resource flags are left alone."""
+        import sys
+        parser = argparse.ArgumentParser(add_help=False, allow_abbrev=False)
+        add_cli_arguments(parser)
+        ns, _ = parser.parse_known_args(list(sys.argv[1:] if argv is None else argv))
+        given = set()
+        for tok in (sys.argv[1:] if argv is None else argv):
+            for f in FIELDS:
+                if tok in (f.flag, f.short) or (f.flag and tok.startswith(f.flag + "=")):
+                    given.add(f.name)
+        for name in given:
+            setattr(self, name, getattr(ns, name))
+        return self
+
+    def get_current_time(self) -> float:
+        """Microseconds on a monotonic clock, after the device has finished what was queued (the legacy call fenced the
+        runtime the same way before reading the clock)."""
+        import time
+        try:
+            import torch
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+        except ImportError:
+            pass
+        return time.perf_counter() * 1e6
+
+    def begin_trace(self, trace_id: int) -> None:
+        """Legion traces have no counterpart to switch on: a compiled model replays its step as one CUDA graph
+        (`use_cuda_graph`).  Kept so that training scripts run unchanged."""
+
+    def end_trace(self, trace_id: int) -> None:
+        pass
+
+    cls.parse_args = parse_args
+    cls.get_current_time = get_current_time
+    cls.begin_trace = begin_trace
+    cls.end_trace = end_trace
+    cls.workers_per_node = property(lambda self: self.gpus_per_node)
     return cls
 
 

@@ -1,5 +1,6 @@
 """User-facing model frontends: the layer API (``FFModel``), the PyTorch (torch.fx) importer, the ONNX importer
 and the Keras-compatible classes."""
+from ..config_schema import FFConfig  # noqa: F401
 from .ffmodel import (AdamOptimizer, FFModel, GlorotUniformInitializer, NormInitializer, SGDOptimizer, SingleDataLoader,  # noqa: F401
                       Tensor, UniformInitializer, ZeroInitializer)
 from .dataloader import DataLoader  # noqa: F401

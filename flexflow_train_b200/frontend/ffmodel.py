@@ -43,6 +43,59 @@ class Tensor:
     def __repr__(self):
         return f"Tensor(dims={self.dims}, dtype={self.data_type.name}, value={self.value})"
 
+    # ---- data access of the legacy Tensor / Parameter classes (flexflow_cffi.py: get_weights, set_weights, get_gradients,
+    # get_array, get_flat_array).  Valid once the model is compiled; arrays are numpy copies on the host.
+    def _parameter_name(self, ffmodel) -> str:
+        node = next(n for n in ffmodel.graph.nodes() if n["id"] == self.value[0])
+        if node["type"] != "WEIGHT":
+            raise TypeError(f"{self!r} is not a weight: only parameters can be read and written like this")
+        return node["name"] or f"weight{node['id']}"
+
+    def _lookup(self, ffmodel, pairs, what):
+        if getattr(ffmodel, "executable", None) is None:
+            raise RuntimeError(f"{what}: compile the model first")
+        name = self._parameter_name(ffmodel)
+        for k, t in pairs:
+            if k == name:
+                return t
+        raise KeyError(f"{what}: no parameter named {name!r} on this device (a sharded strategy keeps shards: use the checkpoint API)")
+
+    @staticmethod
+    def _pairs(ffmodel, what, which):
+        if getattr(ffmodel, "executable", None) is None:
+            raise RuntimeError(f"{what}: compile the model first")
+        return getattr(ffmodel.executable, which)()
+
+    def get_weights(self, ffmodel):
+        t = self._lookup(ffmodel, self._pairs(ffmodel, "get_weights", "named_parameters"), "get_weights")
+        if tuple(t.shape) != self.dims:
+            raise RuntimeError(f"get_weights: this rank holds a shard of shape {tuple(t.shape)} of a {self.dims} parameter")
+        return t.detach().float().cpu().numpy().copy()
+
+    def set_weights(self, ffmodel, np_array) -> bool:
+        t = self._lookup(ffmodel, self._pairs(ffmodel, "set_weights", "named_parameters"), "set_weights")
+        src = torch.as_tensor(np_array)
+        if tuple(src.shape) != tuple(t.shape):
+            raise ValueError(f"set_weights: array of shape {tuple(src.shape)} for a parameter of shape {tuple(t.shape)}")
+        with torch.no_grad():
+            t.copy_(src.to(device=t.device, dtype=t.dtype))
+        ex = ffmodel.executable
+        if getattr(ex, "shadow", None) is not None:      # the compute-dtype copy the kernels read
+            ex.shadow.copy_(ex.master)
+        return True
+
+    def get_gradients(self, ffmodel, comm_type=None):
+        t = self._lookup(ffmodel, self._pairs(ffmodel, "get_gradients", "named_gradients"), "get_gradients")
+        if t is None:
+            raise RuntimeError("get_gradients: no backward pass has run yet")
+        return t.detach().float().cpu().numpy().copy()
+
+    def get_array(self, ffmodel, data_type=None):
+        return self.get_weights(ffmodel)
+
+    def get_flat_array(self, ffmodel, data_type=None):
+        return self.get_weights(ffmodel).reshape(-1)
+
 
 class Initializer:
     def __init__(self, kind: str, **value):
@@ -142,6 +195,27 @@ class Layer:
     def get_output_tensor(self):
         return Tensor(self.model, (self.node_id, self._node["outputs"][0][0]))
 
+    _ACTIVATION_SLOTS = ("INPUT", "LHS_INPUT", "RHS_INPUT", "QUERY", "KEY", "VALUE", "INDEX")
+
+    def get_number_inputs(self) -> int:
+        return sum(1 for s, _ in self._node["inputs"] if s in self._ACTIVATION_SLOTS)
+
+    def get_number_parameters(self) -> int:
+        return sum(1 for s, _ in self._node["inputs"] if s not in self._ACTIVATION_SLOTS)
+
+    def get_number_outputs(self) -> int:
+        return len(self._node["outputs"])
+
+    def get_input_by_id(self, idx):
+        ins = [tuple(v) for s, v in self._node["inputs"] if s in self._ACTIVATION_SLOTS]
+        return Tensor(self.model, ins[idx])
+
+    def get_input_tensor(self):
+        return self.get_input_by_id(0)
+
+    def get_output_by_id(self, idx):
+        return Tensor(self.model, (self.node_id, self._node["outputs"][idx][0]))
+
 
 # ------------------------------------------------------------------------------------------ the model
 class FFModel:
@@ -184,6 +258,10 @@ class FFModel:
             if l.name == layer_name:
                 return l
         return None
+
+    def get_tensor_by_id(self, id):
+        """The first output of the layer with that id (legacy `FFModel.get_tensor_by_id`)."""
+        return self.get_layer_by_id(id).get_output_tensor()
 
     def print_layers(self, id=-1):
         for i, l in enumerate(self._layers):

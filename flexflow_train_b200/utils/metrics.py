@@ -121,6 +121,11 @@ class PerfMetrics:
         self.pull()
         return self.train_correct / max(self.train_all, 1)
 
+    def get_accuracy(self) -> float:
+        """Accuracy in percent, as the legacy ``PerfMetrics.get_accuracy`` reports it
+        (bindings/python/old/flexflow/core/flexflow_cffi.py)."""
+        return 100.0 * self.accuracy
+
     def throughput(self) -> float:
         self.pull()
         return self.train_all / max(self.current_time - self.start_time, 1e-9)

@@ -236,3 +236,48 @@ def test_torch_compile_backend_runs_the_dynamo_graph_on_the_executor():
     compiled = torch.compile(net, backend=lambda gm, example_inputs: flexflow_backend(gm, example_inputs, device="cpu"))
     with torch.no_grad():
         assert torch.allclose(compiled(x), net(x), atol=1e-5)
+
+
+def test_legacy_weight_access_layer_queries_and_config_helpers():
+    # the data-access surface of the legacy Tensor / Layer / FFConfig / PerfMetrics classes
+    # (bindings/python/old/flexflow/core/flexflow_cffi.py)
+    import numpy as np
+    from flexflow_train_b200.frontend import ActiMode, DataType, FFConfig, FFModel, LossType, SGDOptimizer
+    cfg = FFConfig(batch_size=4)
+    cfg.parse_args(["-b", "8", "--epochs", "3", "-ll:gpu", "1", "--unknown-flag"])
+    assert cfg.batch_size == 8 and cfg.epochs == 3 and cfg.learning_rate == FFConfig().learning_rate
+    assert cfg.workers_per_node == cfg.gpus_per_node
+    t0 = cfg.get_current_time()
+    cfg.begin_trace(111)
+    cfg.end_trace(111)
+    assert cfg.get_current_time() >= t0
+
+    ff = FFModel(cfg)
+    x = ff.create_tensor([8, 6], DataType.DT_FLOAT, name="x")
+    h = ff.dense(x, 5, ActiMode.AC_MODE_RELU, name="fc1")
+    ff.softmax(ff.dense(h, 3, name="fc2"))
+    fc1 = ff.get_layer_by_name("fc1")
+    assert (fc1.get_number_inputs(), fc1.get_number_parameters(), fc1.get_number_outputs()) == (1, 2, 1)
+    assert fc1.get_input_tensor().dims == (8, 6) and fc1.get_input_by_id(0).value == x.value
+    assert fc1.get_output_by_id(0).dims == (8, 5) and ff.get_tensor_by_id(0).dims == ff.get_layer_by_id(0).get_output_tensor().dims
+    w = fc1.get_weight_tensor()
+    with pytest.raises(RuntimeError):
+        w.get_weights(ff)                                   # not compiled yet
+    ff.compile(optimizer=SGDOptimizer(ff, 0.1), loss_type=LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY, device="cpu")
+    before = w.get_weights(ff)
+    assert before.shape == (5, 6) and before.dtype == np.float32
+    new = np.arange(30, dtype=np.float32).reshape(5, 6) / 30.0
+    assert w.set_weights(ff, new) and np.array_equal(w.get_weights(ff), new)
+    assert np.array_equal(w.get_flat_array(ff), new.reshape(-1)) and np.array_equal(w.get_array(ff), new)
+    with pytest.raises(ValueError):
+        w.set_weights(ff, np.zeros((6, 5), dtype=np.float32))
+    with pytest.raises(TypeError):
+        h.get_weights(ff)                                   # an activation, not a parameter
+    # a step with the new weights: the gradient of fc1's weight exists and the weight moves by -lr * gradient
+    xs = np.random.RandomState(0).rand(8, 6).astype(np.float32)
+    ys = np.random.RandomState(1).randint(0, 3, size=(8, 1)).astype(np.int32)
+    ff.fit(x=xs, y=ys, epochs=1)
+    g = w.get_gradients(ff)
+    assert g.shape == (5, 6) and np.abs(g).sum() > 0
+    assert np.allclose(w.get_weights(ff), new - 0.1 * g, atol=1e-6)
+    assert ff.get_perf_metrics().get_accuracy() == 100.0 * ff.get_perf_metrics().accuracy

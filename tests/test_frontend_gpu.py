@@ -88,3 +88,25 @@ def test_torch_fx_import_runs_on_gpu_and_matches_pytorch():
         m.executable.train_step({"x": xin.cuda()}, labels.cuda())
         losses.append(m.executable.mean_loss())
     assert losses[-1] < losses[0]
+
+
+def test_legacy_weight_access_on_gpu():
+    # Tensor.get_weights / set_weights / get_gradients of the legacy API against the GPU executor: a written weight is what
+    # the kernels compute with (the bf16 copy follows the fp32 master), and the gradient comes back after a step
+    m = FFModel(FFConfig(batch_size=64, use_cuda_graph=False))
+    x = m.create_tensor([64, 32], DataType.DT_FLOAT, name="x")
+    m.softmax(m.dense(x, 4, use_bias=False, name="fc"))
+    m.compile(SGDOptimizer(m, 0.0), LossType.LOSS_SPARSE_CATEGORICAL_CROSSENTROPY)
+    w = m.get_layer_by_name("fc").get_weight_tensor()
+    assert w.get_weights(m).shape == (4, 32)
+    new = np.zeros((4, 32), dtype=np.float32)
+    new[2, :] = 0.5                                           # class 2 wins for inputs with a positive sum
+    assert w.set_weights(m, new) and np.array_equal(w.get_weights(m), new)
+    xs = np.abs(np.random.RandomState(0).randn(64, 32)).astype(np.float32)
+    ys = np.full((64, 1), 2, dtype=np.int32)
+    m.fit(x=xs, y=ys, epochs=1)
+    pred = m._predictions().argmax(-1).cpu().numpy()
+    assert (pred == 2).all()
+    g = w.get_gradients(m)
+    assert g.shape == (4, 32) and np.isfinite(g).all() and np.abs(g).sum() > 0
+    assert np.array_equal(w.get_weights(m), new)              # learning rate 0: the step left the weight alone
