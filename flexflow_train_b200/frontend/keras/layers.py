@@ -44,6 +44,16 @@ def _pair(v):
     return (v, v) if isinstance(v, int) else tuple(v)
 
 
+def _init(v):
+    """A Keras initializer (object or name) or a layer-API initializer -> what the layer API takes."""
+    if v is None:
+        return None
+    from . import initializers
+    if isinstance(v, str):
+        v = initializers.get(v)
+    return v.ff() if isinstance(v, initializers.Initializer) else v
+
+
 def _padding(p, k):
     if p == "valid":
         return (0, 0)
@@ -67,7 +77,8 @@ class Dense(Layer):
     def __init__(self, units, activation=None, use_bias=True, kernel_initializer=None, bias_initializer=None, name=None, **kw):
         super().__init__(name, **kw)
         self.units, self.activation, self.use_bias = units, activation, use_bias
-        self.kernel_initializer, self.bias_initializer = kernel_initializer, bias_initializer
+        self.kernel_initializer, self.bias_initializer = _init(kernel_initializer), _init(bias_initializer)
+        self.kernel_regularizer = kw.get("kernel_regularizer")     # recorded; see keras/regularizers.py
 
     def build(self, ff, xs):
         act = self.activation
@@ -84,7 +95,7 @@ class Conv2D(Layer):
         super().__init__(name, **kw)
         self.filters, self.kernel, self.strides, self.padding = filters, _pair(kernel_size), _pair(strides), padding
         self.activation, self.groups, self.use_bias = activation, groups, use_bias
-        self.kernel_initializer, self.bias_initializer = kernel_initializer, bias_initializer
+        self.kernel_initializer, self.bias_initializer = _init(kernel_initializer), _init(bias_initializer)
 
     def build(self, ff, xs):
         p = _padding(self.padding, self.kernel)

@@ -281,3 +281,66 @@ def test_legacy_weight_access_layer_queries_and_config_helpers():
     assert g.shape == (5, 6) and np.abs(g).sum() > 0
     assert np.allclose(w.get_weights(ff), new - 0.1 * g, atol=1e-6)
     assert ff.get_perf_metrics().get_accuracy() == 100.0 * ff.get_perf_metrics().accuracy
+
+
+def test_keras_utils_preprocessing_and_datasets(tmp_path):
+    import numpy as np
+    from flexflow_train_b200.frontend import keras
+    K = keras
+    assert K.utils.to_categorical([0, 2, 1]).tolist() == [[1, 0, 0], [0, 0, 1], [0, 1, 0]]
+    assert K.utils.to_categorical([[1], [0]], num_classes=3).shape == (2, 3)
+    assert K.utils.to_categorical(np.array([[0, 1], [1, 0]])).shape == (2, 2, 2)
+    with pytest.raises(ValueError):
+        K.utils.to_categorical([3], num_classes=3)
+    n = K.utils.normalize(np.array([[3.0, 4.0], [0.0, 0.0]]))
+    assert np.allclose(n, [[0.6, 0.8], [0.0, 0.0]])
+    pad = K.preprocessing.sequence.pad_sequences
+    assert pad([[1, 2, 3], [4], []], maxlen=2).tolist() == [[2, 3], [0, 4], [0, 0]]
+    assert pad([[1, 2, 3], [4]], padding="post", truncating="post", maxlen=2).tolist() == [[1, 2], [4, 0]]
+    assert pad([[1], [2, 3]]).shape == (2, 2)
+    tok = K.preprocessing.text.Tokenizer(num_words=3, oov_token="<unk>")
+    tok.fit_on_texts(["The cat sat.", "the cat ran!"])
+    assert tok.word_index["<unk>"] == 1 and tok.word_index["the"] == 2 and tok.word_index["cat"] == 3
+    assert tok.texts_to_sequences(["the dog sat"]) == [[2, 1, 1]]            # only indices below num_words are kept
+    # data sets read local files and name the file they miss
+    with pytest.raises(FileNotFoundError, match="mnist.npz"):
+        K.datasets.mnist.load_data(str(tmp_path / "mnist.npz"))
+    np.savez(tmp_path / "mnist.npz", x_train=np.zeros((5, 28, 28), np.uint8), y_train=np.arange(5), x_test=np.zeros((2, 28, 28), np.uint8), y_test=np.arange(2))
+    (xtr, ytr), (xte, yte) = K.datasets.mnist.load_data(str(tmp_path / "mnist.npz"))
+    assert xtr.shape == (5, 28, 28) and yte.tolist() == [0, 1]
+    x = np.empty(4, dtype=object)
+    x[:] = [[1, 2], [3], [4, 5, 6], [7]]
+    np.savez(tmp_path / "reuters.npz", x=x, y=np.array([0, 1, 2, 3]))
+    (a, la), (b, lb) = K.datasets.reuters.load_data(str(tmp_path / "reuters.npz"), test_split=0.25, num_words=8)
+    assert len(a) == 3 and len(b) == 1 and all(s[0] == 1 for s in list(a) + list(b))
+    assert all(w in (1, 2) or 3 <= w < 8 for s in list(a) + list(b) for w in s)
+    with pytest.raises(FileNotFoundError):
+        K.datasets.cifar10.load_data(str(tmp_path / "nowhere"))
+
+
+def test_keras_initializers_regularizers_and_backend_functions():
+    import numpy as np
+    from flexflow_train_b200.frontend import keras
+    from flexflow_train_b200.frontend.types import RegularizerMode
+    L, B = keras.layers, keras.backend
+    assert keras.regularizers.L2(0.5)._lambda == 0.5 and keras.regularizers.L1().type == RegularizerMode.REG_MODE_L1
+    assert isinstance(keras.initializers.get("zeros"), keras.initializers.Zeros)
+    with pytest.raises(ValueError):
+        keras.initializers.get("no_such")
+    inp = keras.Input(shape=(6,))
+    h = L.Dense(5, activation="relu", kernel_initializer=keras.initializers.Zeros(), bias_initializer="zeros",
+                kernel_regularizer=keras.regularizers.L2(0.01), name="zeroed")(inp)
+    h = B.exp(h)                                     # exp(relu(0)) = 1 everywhere
+    h = B.pow(h, 2.0)
+    s = B.sum(h, axis=1, keepdims=True)              # 5 ones per sample
+    out = L.Dense(3, activation="softmax", name="head")(L.Concatenate(axis=1)([h, s]))
+    model = keras.Model(inp, out)
+    model.compile(optimizer=keras.optimizers.SGD(0.0), loss="sparse_categorical_crossentropy", metrics=["accuracy"], device="cpu")
+    xs = np.random.RandomState(0).rand(8, 6).astype(np.float32)
+    ys = np.zeros((8, 1), dtype=np.int32)
+    model.fit(xs, ys, batch_size=8, epochs=1)        # the graph is built at the first fit; learning rate 0 leaves the weights
+    ff = model.ffmodel
+    w = ff.get_layer_by_name("zeroed").get_weight_tensor()
+    assert not w.get_weights(ff).any()
+    types = [n["type"] for n in ff.graph.nodes()]
+    assert "EXP" in types and "POW" in types and "REDUCE_SUM" in types
