@@ -92,6 +92,7 @@ PYBIND11_MODULE(_ffcore, m) {
            }),
            py::arg("num_nodes") = 1, py::arg("num_gpus_per_node") = 1, py::arg("num_cpus_per_node") = 1,
            py::arg("inter_node_bandwidth") = 25.0, py::arg("intra_node_bandwidth") = 770.0)
+      .def_readwrite("view_enumeration", &MachineSpec::view_enumeration)
       .def_readwrite("num_nodes", &MachineSpec::num_nodes)
       .def_readwrite("num_gpus_per_node", &MachineSpec::num_gpus_per_node)
       .def_readwrite("num_cpus_per_node", &MachineSpec::num_cpus_per_node)

@@ -134,6 +134,10 @@ struct MachineSpec {  // lib/pcg/include/pcg/machine_specification.dtg.toml
   int num_gpus_per_node = 1;
   double inter_node_bandwidth = 25.0;   // GB/s
   double intra_node_bandwidth = 770.0;  // GB/s, NVLink 5 peer copy per direction
+  // Which machine views the mapping search may give an operator (not part of the serialised specification):
+  // 0 = contiguous, start-aligned blocks; 1 = those plus power-of-two strides inside a node; 2 = every start, stride vector
+  // and inter- / intra-node projection that fits, the reference's enumeration (allowed_machine_views.cc:51-162).
+  int view_enumeration = 0;
   int num_devices() const { return num_nodes * num_gpus_per_node; }
   Json to_json() const;
   static MachineSpec from_json(const Json &);

@@ -212,6 +212,21 @@ std::vector<MachineView> allowed_machine_views(const std::vector<int> &task_degr
   std::vector<MachineView> out;
   if (count > r.count) return out;
   const int per_node = m.num_gpus_per_node;
+  strided = strided || m.view_enumeration == 1;
+  if (m.view_enumeration == 2) {
+    // the reference's enumeration over the whole machine, kept where every task lands inside the resource range on its own
+    // device; rewritten with absolute strides, which is what view_devices and the rest of the search read
+    std::set<MachineView> seen;
+    for (auto &v : reference_allowed_machine_views(task_degrees, m.num_nodes, per_node)) {
+      MachineView a = absolute_view_from_reference(v, task_degrees);
+      auto devs = view_devices(a, task_degrees, m);
+      std::set<int> distinct(devs.begin(), devs.end());
+      bool inside = distinct.size() == devs.size();
+      for (int d : devs) inside = inside && d >= r.start && d < r.start + r.count;
+      if (inside && seen.insert(a).second) out.push_back(a);
+    }
+    return out;
+  }
   if (strided && count > 1) {
     // Strided placements inside one node (the reference's MachineView stride, allowed_machine_views.cc:51-162): the
     // tasks sit on every s-th device, s a power of two, so that s interleaved groups tile a block of count * s devices.

@@ -531,3 +531,25 @@ def test_generic_mcmc_temperature_controls_acceptance_of_worse_states():
     assert cold[0] == 0 and cold[2] == 0          # every proposal is worse than the start and a cold chain refuses them all
     assert hot[0] == 0 and hot[2] > 250           # a hot chain takes nearly everything and still reports the best state seen
     assert c.run_mcmc(5, lambda x, u: None, cost, 1.0, 10, 0) == (5, 5.0, 0)   # a sampler that proposes nothing
+
+
+def test_mapping_search_over_the_reference_view_enumeration():
+    # MachineSpecification.view_enumeration = 2: the DP chooses among every start, stride and projection that fits
+    ms = c.MachineSpecification(1, 4)
+    base = c.allowed_machine_views([2], 0, 4, ms)
+    assert sorted(c.view_devices(v, [2], ms) for v in base) == [[0, 1], [2, 3]]
+    ms.view_enumeration = 2
+    every = c.allowed_machine_views([2], 0, 4, ms)
+    assert sorted(c.view_devices(v, [2], ms) for v in every) == [[0, 1], [0, 2], [0, 3], [1, 2], [1, 3], [2, 3]]
+    assert sorted(c.view_devices(v, [2], ms) for v in c.allowed_machine_views([2], 2, 2, ms)) == [[2, 3]]     # a resource sub-range
+    two = c.MachineSpecification(2, 2)
+    two.view_enumeration = 2
+    devs = sorted(c.view_devices(v, [2], two) for v in c.allowed_machine_views([2], 0, 4, two))
+    assert [0, 2] in devs and [1, 3] in devs and [0, 1] in devs         # across the nodes and inside one
+    # on a uniform machine the richer view set finds the same optimum as the contiguous one
+    g = c.build_model("mlp", {"batch_size": 16})
+    plain = c.MachineSpecification(1, 4)
+    pcg = S.optimize(g, world=4, algorithm="data_parallel")["pcg"]
+    a = c.evaluate_pcg(pcg, plain, c.CostEstimator(plain))
+    b = c.evaluate_pcg(pcg, ms, c.CostEstimator(ms))
+    assert abs(a["runtime_ms"] - b["runtime_ms"]) < 1e-9 * max(1.0, a["runtime_ms"]) and b["mapped_pcg"].is_mapped()
