@@ -611,69 +611,354 @@ SPTree work_duplicating_sp_ization(const DiGraph &g, bool coalesce) {
   return coalesce ? coalesce_parallel(t) : t;
 }
 
-SPTree escribano_sp_ization(const DiGraph &g) {
-  // Layer-by-layer construction that synchronises only the components that a layer actually joins
-  // (after Escribano et al.).  State: a forest of SP components, each with the set of DAG nodes it
-  // contains.  For every stratum, the new nodes that (transitively through shared predecessors'
-  // components) touch the same components are grouped; the touched components are closed under a
-  // parallel node and followed by the parallel group of new nodes.
-  auto depth = get_longest_path_lengths_from_root(g);
-  std::map<int, std::vector<int>> strata;
-  for (auto &kv : depth) strata[kv.second].push_back(kv.first);
-  struct Comp { SPTree tree; std::set<int> members; };
-  std::vector<Comp> comps;
-  for (auto &kv : strata) {
-    const std::vector<int> &layer = kv.second;
-    // union-find over (components + new nodes)
-    size_t nc = comps.size();
-    std::vector<int> parent(nc + layer.size());
-    for (size_t i = 0; i < parent.size(); ++i) parent[i] = (int)i;
-    std::function<int(int)> find = [&](int x) { return parent[x] == x ? x : parent[x] = find(parent[x]); };
-    for (size_t li = 0; li < layer.size(); ++li)
-      for (int p : g.predecessors(layer[li]))
-        for (size_t ci = 0; ci < nc; ++ci)
-          if (comps[ci].members.count(p)) parent[find((int)(nc + li))] = find((int)ci);
-    std::map<int, std::pair<std::vector<size_t>, std::vector<size_t>>> groups;  // root -> (comps, layer idx)
-    for (size_t ci = 0; ci < nc; ++ci) groups[find((int)ci)].first.push_back(ci);
-    for (size_t li = 0; li < layer.size(); ++li) groups[find((int)(nc + li))].second.push_back(li);
-    std::vector<Comp> next;
-    for (auto &gkv : groups) {
-      auto &cidx = gkv.second.first;
-      auto &lidx = gkv.second.second;
-      if (lidx.empty()) {  // untouched components carry over
-        for (size_t ci : cidx) next.push_back(comps[ci]);
-        continue;
-      }
-      Comp c;
-      std::vector<SPTree> olds, news;
-      for (size_t ci : cidx) { olds.push_back(comps[ci].tree); c.members.insert(comps[ci].members.begin(), comps[ci].members.end()); }
-      for (size_t li : lidx) { news.push_back(SPTree::leaf(layer[li])); c.members.insert(layer[li]); }
-      if (olds.empty()) c.tree = normalize_sp(SPTree::parallel(news));
-      else c.tree = normalize_sp(SPTree::series({SPTree::parallel(olds), SPTree::parallel(news)}));
-      next.push_back(c);
+// Kept nodes of g with an edge a->b wherever g has a path from a to b whose inner nodes are all dropped.
+static DiGraph bridge_out_nodes(const DiGraph &g, const std::function<bool(int)> &drop) {
+  DiGraph r;
+  for (int n : g.nodes()) {
+    if (drop(n)) continue;
+    r.add_node(n);
+    std::vector<int> stack(g.successors(n).begin(), g.successors(n).end());
+    std::set<int> seen;
+    while (!stack.empty()) {
+      int x = stack.back();
+      stack.pop_back();
+      if (!seen.insert(x).second) continue;
+      if (!drop(x)) { r.add_edge(n, x); continue; }
+      for (int y : g.successors(x)) stack.push_back(y);
     }
-    comps = next;
   }
-  std::vector<SPTree> all;
-  for (auto &c : comps) all.push_back(c.tree);
-  return normalize_sp(SPTree::parallel(all));
+  return r;
 }
 
-SPTree flexible_sp_ization(const DiGraph &g, const std::function<double(int)> &cost) {
-  // Cost-aware choice: evaluate the candidate SP-izations under the given node costs and keep the one
-  // with the smallest critical path, breaking ties on total work (duplication).
-  std::vector<SPTree> cands = {escribano_sp_ization(g), naive_stratum_sync_sp_ization(g),
-                               work_duplicating_sp_ization(g, true)};
-  if (auto exact = get_series_parallel_decomposition(g)) return *exact;
-  size_t best = 0;
-  double best_cp = 0, best_w = 0;
-  for (size_t i = 0; i < cands.size(); ++i) {
-    double cp = sp_critical_path_cost(cands[i], cost), w = sp_work_cost(cands[i], cost);
-    if (i == 0 || cp < best_cp - 1e-12 || (std::abs(cp - best_cp) <= 1e-12 && w < best_w)) {
-      best = i; best_cp = cp; best_w = w;
+static SPTree sp_without_leaves(const SPTree &t, const std::set<int> &gone) {
+  if (t.kind == SPTree::Leaf) return t;
+  SPTree r;
+  r.kind = t.kind;
+  for (auto &c : t.children) {
+    if (c.kind == SPTree::Leaf && gone.count(c.node)) continue;
+    SPTree k = sp_without_leaves(c, gone);
+    if (k.kind != SPTree::Leaf && k.children.empty()) continue;
+    r.children.push_back(k);
+  }
+  return r;
+}
+
+SPTree escribano_sp_ization(const DiGraph &g0) {
+  // Local synchronisation of consecutive strata (after Escribano et al., "Mapping unstructured applications into
+  // nested parallelism"): where the naive algorithm joins ALL nodes of one stratum with ALL nodes of the next, this
+  // one joins only the nodes that the new dependencies actually tie together.
+  //   1. every edge is made to span exactly one stratum by threading it through placeholder nodes;
+  //   2. the series-parallel graph is grown one node at a time in breadth-first order.  The new node and its
+  //      predecessors, together with whatever earlier joins between the last two strata they touch, form a class;
+  //      the deepest common ancestor of the class is its handle, and every branch below the handle that reaches into
+  //      the class is closed: all of those branches' nodes in the last stratum but one ("up") are joined to all of
+  //      their nodes in the last stratum ("down") through one fresh join node;
+  //   3. placeholders and join nodes are bridged out, and what is left is series-parallel by construction.
+  // lib/utils/src/utils/graph/series_parallel/sp_ization/escribano_algo.cc:201-250 builds the same tree for
+  // two-terminal graphs; here a graph with several sources or sinks first gets a common one, taken out again at the end.
+  if (g0.num_nodes() == 0) return SPTree::parallel({});
+  if (g0.num_nodes() == 1) return SPTree::leaf(g0.nodes()[0]);
+  enum Role { Real, Placeholder, Join };
+  std::map<int, Role> role;
+  DiGraph g = g0;
+  int next_id = 0;
+  for (int n : g.nodes()) { role[n] = Real; next_id = std::max(next_id, n + 1); }
+  std::set<int> added_terminals;
+  if (g.sources().size() > 1) {
+    int r = next_id++;
+    for (int s : g.sources()) g.add_edge(r, s);
+    role[r] = Real;
+    added_terminals.insert(r);
+  }
+  if (g.sinks().size() > 1) {
+    int t = next_id++;
+    for (int s : g.sinks()) g.add_edge(s, t);
+    role[t] = Real;
+    added_terminals.insert(t);
+  }
+  std::map<int, int> depth = get_longest_path_lengths_from_root(g);
+  for (auto &e : g.edges()) {
+    int span = depth.at(e.second) - depth.at(e.first);
+    if (span <= 1) continue;
+    g.remove_edge(e.first, e.second);
+    int prev = e.first;
+    for (int i = 1; i < span; ++i) {
+      int ph = next_id++;
+      role[ph] = Placeholder;
+      depth[ph] = depth.at(e.first) + i;
+      g.add_edge(prev, ph);
+      prev = ph;
+    }
+    g.add_edge(prev, e.second);
+  }
+  // strata in order; inside a stratum, nodes in id order (placeholders after the real nodes)
+  std::map<int, std::vector<int>> strata;
+  for (int n : g.nodes()) strata[depth.at(n)].push_back(n);
+
+  // Once a stratum is closed every one of its nodes hangs below exactly one join, so the graph above the stratum
+  // being worked on never changes again.  That makes ancestor sets of the previous stratum's nodes fixed bit rows,
+  // and with bits numbered stratum by stratum (a stratum's joins before its nodes) the deepest common ancestor of a
+  // class is the highest bit that all of its rows share.  Only the rows of the previous stratum are kept.
+  std::map<int, size_t> bit, join_base;
+  size_t total = 0;
+  for (auto &layer : strata) {
+    if (layer.first > 0) { join_base[layer.first] = total; total += layer.second.size(); }
+    for (int n : layer.second) bit[n] = total++;
+  }
+  const size_t words = (total + 63) / 64;
+  using Row = std::vector<uint64_t>;
+  std::vector<int> node_at(total, -1);
+  for (auto &kv : bit) node_at[kv.second] = kv.first;
+  auto set_bit = [](Row &r, size_t i) { r[i >> 6] |= uint64_t(1) << (i & 63); };
+  auto has_bit = [](const Row &r, size_t i) { return (r[i >> 6] >> (i & 63)) & 1; };
+
+  DiGraph sp;
+  std::map<int, Row> above_prev;  // ancestors-or-self of the previous stratum's nodes
+  for (auto &layer : strata) {
+    const int d = layer.first;
+    if (d == 0) {
+      for (int n : layer.second) { sp.add_node(n); Row r(words, 0); set_bit(r, bit.at(n)); above_prev[n] = r; }
+      continue;
+    }
+    std::set<int> window;  // the last two strata and the joins between them
+    for (auto &kv : above_prev) window.insert(kv.first);
+    std::vector<int> arrived;
+    size_t joins_made = 0;
+    for (int node : layer.second) {
+      sp.add_node(node);
+      for (int p : g.predecessors(node)) sp.add_edge(p, node);
+      window.insert(node);
+      arrived.push_back(node);
+      // the class of the new node: what it is tied to inside the window
+      std::set<int> seen = {node};
+      std::vector<int> stack = {node};
+      while (!stack.empty()) {
+        int x = stack.back();
+        stack.pop_back();
+        for (const std::set<int> *side : {&sp.successors(x), &sp.predecessors(x)})
+          for (int y : *side) if (window.count(y) && seen.insert(y).second) stack.push_back(y);
+      }
+      std::vector<int> cls;
+      Row common;
+      for (int n : seen) {
+        if (role.at(n) == Join) continue;
+        cls.push_back(n);
+        auto it = above_prev.find(n);
+        if (it == above_prev.end()) continue;   // a node of this stratum adds nothing: its ancestors contain a member's
+        if (common.empty()) common = it->second;
+        else for (size_t w = 0; w < words; ++w) common[w] &= it->second[w];
+      }
+      int handle = -1;
+      for (size_t w = words; w-- > 0 && handle < 0;)
+        if (common[w]) handle = node_at[w * 64 + 63 - __builtin_clzll(common[w])];
+      // The handle's branches sit in one block of bits, so only that word range of a row is ever looked at.
+      // below: every branch bit that some member of the class has above it; those branches are the ones to close.
+      const std::set<int> &branches = sp.successors(handle);
+      size_t lo = words, hi = 0;
+      for (int b : branches) { lo = std::min(lo, bit.at(b) >> 6); hi = std::max(hi, (bit.at(b) >> 6) + 1); }
+      Row below(words, 0);
+      auto add_row = [&](const Row &r) { for (size_t w = lo; w < hi; ++w) below[w] |= r[w]; };
+      for (int m : cls) {
+        auto it = above_prev.find(m);
+        if (it != above_prev.end()) { add_row(it->second); continue; }
+        set_bit(below, bit.at(m));
+        for (int p : sp.predecessors(m)) {
+          set_bit(below, bit.at(p));
+          if (role.at(p) == Join && !above_prev.count(p)) { for (int q : sp.predecessors(p)) add_row(above_prev.at(q)); }
+          else add_row(above_prev.at(p));
+        }
+      }
+      Row closing(words, 0);
+      std::set<int> touching;
+      for (int b : branches) if (has_bit(below, bit.at(b))) { set_bit(closing, bit.at(b)); touching.insert(b); }
+      auto meets = [&](const Row &r) { for (size_t w = lo; w < hi; ++w) if (r[w] & closing[w]) return true; return false; };
+      std::set<int> up, down;
+      for (auto &kv : above_prev) if (meets(kv.second)) up.insert(kv.first);
+      for (int w : arrived) {
+        bool in = touching.count(w) > 0;
+        for (int p : sp.predecessors(w)) {
+          if (in) break;
+          if (touching.count(p) || up.count(p)) in = true;
+          else if (role.at(p) == Join) for (int q : sp.predecessors(p)) if (up.count(q)) { in = true; break; }
+        }
+        if (in) down.insert(w);
+      }
+      if (role.at(handle) != Join && depth.at(handle) + 1 == d) up.insert(handle);
+      for (int u : up) for (int x : std::set<int>(sp.successors(u))) sp.remove_edge(u, x);
+      for (int w : down) for (int p : std::set<int>(sp.predecessors(w))) sp.remove_edge(p, w);
+      int join = next_id++;
+      role[join] = Join;
+      bit[join] = join_base.at(d) + joins_made++;
+      node_at[bit[join]] = join;
+      sp.add_node(join);
+      window.insert(join);
+      for (int u : up) sp.add_edge(u, join);
+      for (int w : down) sp.add_edge(join, w);
+    }
+    std::map<int, Row> above_cur, above_join;
+    for (int n : layer.second) {
+      Row r(words, 0);
+      for (int p : sp.predecessors(n)) {
+        if (role.at(p) != Join) { for (size_t w = 0; w < words; ++w) r[w] |= above_prev.at(p)[w]; continue; }
+        auto it = above_join.find(p);
+        if (it == above_join.end()) {
+          Row jr(words, 0);
+          set_bit(jr, bit.at(p));
+          for (int u : sp.predecessors(p)) { const Row &ur = above_prev.at(u); for (size_t w = 0; w < words; ++w) jr[w] |= ur[w]; }
+          it = above_join.emplace(p, std::move(jr)).first;
+        }
+        for (size_t w = 0; w < words; ++w) r[w] |= it->second[w];
+      }
+      set_bit(r, bit.at(n));
+      above_cur[n] = std::move(r);
+    }
+    above_prev = std::move(above_cur);
+  }
+  DiGraph real = transitive_reduction(bridge_out_nodes(sp, [&](int n) { return role.at(n) != Real; }));
+  std::optional<SPTree> tree = get_series_parallel_decomposition(real);
+  if (!tree) throw std::runtime_error("escribano_sp_ization: result is not series-parallel");
+  return normalize_sp(sp_without_leaves(*tree, added_terminals));
+}
+
+static DiGraph induced_subgraph(const DiGraph &g, const std::set<int> &keep) {
+  DiGraph r;
+  for (int n : keep) {
+    r.add_node(n);
+    for (int s : g.successors(n)) if (keep.count(s)) r.add_edge(n, s);
+  }
+  return r;
+}
+
+static double longest_weighted_path(const DiGraph &g, const std::function<double(int)> &cost) {
+  double best = 0;
+  for (auto &kv : get_weighted_longest_path_lengths(g, cost)) best = std::max(best, kv.second);
+  return best;
+}
+
+SPTree flexible_sp_ization(const DiGraph &g0, const std::function<double(int)> &node_cost) {
+  // Cost-aware generalisation of escribano_sp_ization.  The graph is again grown into a series-parallel one with
+  // join nodes, but (a) nodes arrive in order of their earliest finish time instead of stratum by stratum (all ready
+  // nodes that share the cheapest one's predecessor set arrive together), and (b) the region being closed is not cut
+  // between its last two strata: every cut of the region into an upper and a lower part that keeps the new nodes
+  // below and their ancestors above is a candidate, the candidates being the prefixes of the undecided nodes ordered
+  // by finish time, and the cut with the smallest (longest path above + longest path below) wins; ties go to the
+  // cheaper, then the smaller, lower part.  lib/utils/src/utils/graph/series_parallel/sp_ization/flexible_algo.cc:254-310
+  // is the upstream statement of the algorithm (two-terminal graphs only; several sources or sinks get a common
+  // zero-cost one here, which is taken out of the result).
+  if (g0.num_nodes() == 0) return SPTree::parallel({});
+  if (g0.num_nodes() == 1) return SPTree::leaf(g0.nodes()[0]);
+  DiGraph g = transitive_reduction(g0);
+  std::set<int> joins, added_terminals;
+  int next_id = 0;
+  for (int n : g.nodes()) next_id = std::max(next_id, n + 1);
+  if (g.sources().size() > 1) {
+    int r = next_id++;
+    for (int s : g.sources()) g.add_edge(r, s);
+    added_terminals.insert(r);
+  }
+  if (g.sinks().size() > 1) {
+    int t = next_id++;
+    for (int s : g.sinks()) g.add_edge(s, t);
+    added_terminals.insert(t);
+  }
+  auto cost = [&](int n) { return joins.count(n) || added_terminals.count(n) ? 0.0 : node_cost(n); };
+  auto is_join = [&](int n) { return joins.count(n) > 0; };
+
+  DiGraph sp;
+  sp.add_node(g.sources()[0]);
+  while (sp.num_nodes() - joins.size() < g.num_nodes()) {
+    // ---- the next batch of nodes
+    std::map<int, double> finish = get_weighted_longest_path_lengths(sp, cost);
+    std::vector<int> ready;
+    for (int n : g.nodes()) {
+      if (sp.has_node(n)) continue;
+      bool ok = true;
+      for (int p : g.predecessors(n)) ok = ok && sp.has_node(p);
+      if (ok) ready.push_back(n);
+    }
+    int first = -1;
+    double first_finish = 0;
+    for (int n : ready) {
+      double start = 0;
+      for (int p : g.predecessors(n)) start = std::max(start, finish.at(p));
+      double f = start + cost(n);
+      if (first < 0 || f < first_finish) { first = n; first_finish = f; }
+    }
+    std::set<int> batch;
+    for (int n : ready) if (g.predecessors(n) == g.predecessors(first)) batch.insert(n);
+    for (int n : batch) for (int p : g.predecessors(n)) sp.add_edge(p, n);
+    sp = transitive_reduction(sp);
+
+    // ---- the region to close: what the batch's predecessors reach, and what else feeds into that
+    std::set<int> region;
+    for (int n : batch) for (int p : sp.predecessors(n)) region.insert(p);
+    std::set<int> reached;
+    for (int p : region) for (int x : get_descendants(sp, p)) reached.insert(x);
+    for (int x : reached) { region.insert(x); for (int p : sp.predecessors(x)) region.insert(p); }
+    int handle = *get_lowest_common_ancestor(sp, region);
+    std::set<int> forest;
+    for (int branch : sp.successors(handle)) {
+      std::set<int> below = get_descendants(sp, branch);
+      below.insert(branch);
+      bool touches = false;
+      for (int n : below) if (region.count(n)) { touches = true; break; }
+      if (touches) for (int n : below) if (!is_join(n)) forest.insert(n);
+    }
+    if (!is_join(handle)) forest.insert(handle);
+
+    // ---- choose the cut
+    DiGraph pure = bridge_out_nodes(sp, is_join);
+    std::set<int> fixed_up, undecided;
+    for (int n : batch) for (int a : get_ancestors(pure, n)) if (forest.count(a)) fixed_up.insert(a);
+    for (int n : forest) if (!fixed_up.count(n) && !batch.count(n)) undecided.insert(n);
+    std::map<int, double> forest_finish = get_weighted_longest_path_lengths(induced_subgraph(pure, forest), cost);
+    std::vector<std::optional<double>> limits = {std::nullopt};   // nothing undecided goes up / all up to this finish time
+    for (int n : undecided) limits.push_back(forest_finish.at(n));
+    bool have = false;
+    std::set<int> best_up, best_down;
+    std::tuple<double, double, size_t> best_key;
+    for (auto &limit : limits) {
+      std::set<int> up = fixed_up, down = batch;
+      for (int n : undecided) (limit && forest_finish.at(n) <= *limit ? up : down).insert(n);
+      bool valid = true;
+      for (int d : down) for (int s : pure.successors(d)) if (up.count(s)) valid = false;
+      if (!valid) continue;
+      double cu = longest_weighted_path(induced_subgraph(pure, up), cost);
+      double cd = longest_weighted_path(induced_subgraph(pure, down), cost);
+      std::tuple<double, double, size_t> key{cu + cd, cd, down.size()};
+      if (!have || key < best_key) { have = true; best_key = key; best_up = up; best_down = down; }
+    }
+    if (!have) throw std::runtime_error("flexible_sp_ization: no valid cut");
+
+    // ---- replace what crosses the cut by one join
+    for (int u : best_up) for (int s : std::set<int>(sp.successors(u))) if (best_down.count(s)) sp.remove_edge(u, s);
+    for (int j : joins) {
+      const std::set<int> ps = sp.predecessors(j), ss = sp.successors(j);
+      bool inside = true;
+      for (int p : ps) inside = inside && best_up.count(p);
+      for (int x : ss) inside = inside && best_down.count(x);
+      if (!inside) continue;
+      for (int p : ps) sp.remove_edge(p, j);
+      for (int x : ss) sp.remove_edge(j, x);
+    }
+    int join = next_id++;
+    joins.insert(join);
+    sp.add_node(join);
+    for (int u : best_up) {
+      bool last = true;
+      for (int s : sp.successors(u)) if (best_up.count(s)) last = false;
+      if (last) sp.add_edge(u, join);
+    }
+    for (int d : best_down) {
+      bool head = true;
+      for (int p : sp.predecessors(d)) if (best_down.count(p)) head = false;
+      if (head) sp.add_edge(join, d);
     }
   }
-  return cands[best];
+  DiGraph real = transitive_reduction(bridge_out_nodes(transitive_reduction(sp), is_join));
+  std::optional<SPTree> tree = get_series_parallel_decomposition(real);
+  if (!tree) throw std::runtime_error("flexible_sp_ization: result is not series-parallel");
+  return normalize_sp(sp_without_leaves(*tree, added_terminals));
 }
 
 bool sp_preserves_dependencies(const SPTree &t, const DiGraph &g) {

@@ -302,3 +302,161 @@ def test_dominator_variants_agree_on_random_dags(n, seed):
             assert imm[v] in strict[v] and all(d in dom[imm[v]] for d in strict[v])
     f = c.flipped(c.flipped(g))
     assert sorted(f.edges()) == sorted(g.edges())
+
+
+# ------------------------------------------------------------------ SP-ization golden cases
+def _canon(t):
+    """Order-free form of a decomposition: the children of a parallel split are a set."""
+    if not isinstance(t, tuple):
+        return t
+    kind, kids = t
+    kids = [_canon(k) for k in kids]
+    return (kind, frozenset(kids)) if kind == "P" else (kind, tuple(kids))
+
+
+def _S(*k):
+    return ("S", list(k))
+
+
+def _P(*k):
+    return ("P", list(k))
+
+
+def _graph_costs(edges, cost):
+    """Work and critical path of the graph itself."""
+    longest = {}
+    order = sorted(cost)  # the cases number their nodes in a topological order
+    for n in order:
+        longest[n] = cost[n] + max([longest[a] for a, b in edges if b == n], default=0.0)
+    return sum(cost.values()), max(longest.values())
+
+
+_STRATUM_CASES = [
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/naive_stratum_sync.cc
+    ("independent nodes", 4, [], {0: 1, 1: 5, 2: 2, 3: 3}, _P(0, 1, 2, 3), None),
+    ("chain", 5, [(0, 1), (1, 2), (2, 3), (3, 4)], {0: 1, 1: 2, 2: 3, 3: 4, 4: 5}, _S(0, 1, 2, 3, 4), None),
+    ("two layers, all to all", 5, [(0, 2), (0, 3), (0, 4), (1, 2), (1, 3), (1, 4)],
+     {0: 2, 1: 3, 2: 5, 3: 7, 4: 11}, _S(_P(0, 1), _P(2, 3, 4)), None),
+    ("barrier lengthens the critical path", 6, [(0, 1), (0, 2), (1, 3), (2, 5), (3, 4), (4, 5)],
+     {0: 1, 1: 1, 2: 10, 3: 1, 4: 1, 5: 1}, None, (12.0, 14.0)),
+    ("diamond with tail", 6, [(0, 1), (0, 2), (1, 3), (2, 4), (3, 5), (4, 5)],
+     {n: 1 for n in range(6)}, _S(0, _P(1, 2), _P(3, 4), 5), None),
+]
+
+
+@pytest.mark.parametrize("name,n,edges,cost,expected,paths", _STRATUM_CASES, ids=[k[0] for k in _STRATUM_CASES])
+def test_naive_stratum_sync_golden_cases(name, n, edges, cost, expected, paths):
+    g = _dg(edges, range(n))
+    cost = {k: float(v) for k, v in cost.items()}
+    sp = c.naive_stratum_sync_sp_ization(g)
+    if expected is not None:
+        assert _canon(sp) == _canon(expected)
+    work, critical = _graph_costs(edges, cost)
+    assert c.sp_work_cost(sp, cost) == work
+    if paths is None:
+        assert c.sp_critical_path_cost(sp, cost) == critical
+    else:
+        assert (critical, c.sp_critical_path_cost(sp, cost)) == paths
+    assert c.sp_preserves_dependencies(sp, g)
+
+
+_ESCRIBANO_CASES = [
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/escribano_algo.cc
+    ("single node", 1, [], 0),
+    ("chain", 3, [(0, 1), (1, 2)], _S(0, 1, 2)),
+    ("rhombus", 4, [(0, 1), (0, 2), (1, 3), (2, 3)], _S(0, _P(1, 2), 3)),
+    ("sample 1", 6, [(0, 1), (0, 2), (1, 2), (1, 3), (2, 4), (3, 4), (3, 5), (4, 5)], _S(0, 1, _P(2, 3), 4, 5)),
+    ("diamond without crossing", 6, [(0, 1), (0, 2), (1, 3), (2, 5), (3, 4), (4, 5)], _S(0, _P(_S(1, 3, 4), 2), 5)),
+    ("diamond", 6, [(0, 1), (0, 2), (1, 4), (1, 3), (2, 4), (3, 5), (4, 5)], _S(0, _P(1, 2), _P(3, 4), 5)),
+    ("sample 2", 10, [(0, 1), (0, 3), (1, 2), (1, 5), (1, 4), (2, 6), (3, 4), (3, 5), (3, 8), (4, 8), (5, 7), (7, 8),
+                      (6, 9), (8, 9)],
+     _S(0, _P(1, 3), _P(_S(2, 6), _S(_P(_S(5, 7), 4), 8)), 9)),
+    # lib/utils/include/utils/graph/series_parallel/sp_ization/index.dox: strata 1 and 2 are joined in two local groups
+    ("local joins", 8, [(0, 1), (0, 2), (0, 3), (1, 4), (1, 5), (2, 5), (3, 6), (4, 7), (5, 7), (6, 7)],
+     _S(0, _P(_S(_P(1, 2), _P(4, 5)), _S(3, 6)), 7)),
+    # several sources and sinks: not in the upstream cases, which want a two-terminal graph
+    ("two sources, two sinks", 4, [(0, 2), (1, 2), (1, 3)], _S(_P(0, 1), _P(2, 3))),
+    ("independent chains", 4, [(0, 1), (2, 3)], _P(_S(0, 1), _S(2, 3))),
+]
+
+
+@pytest.mark.parametrize("name,n,edges,expected", _ESCRIBANO_CASES, ids=[k[0] for k in _ESCRIBANO_CASES])
+def test_escribano_golden_cases(name, n, edges, expected):
+    g = _dg(edges, range(n))
+    sp = c.escribano_sp_ization(g)
+    assert c.sp_preserves_dependencies(sp, g)
+    assert sorted(c.sp_nodes(sp)) == list(range(n))
+    assert _canon(sp) == _canon(expected)
+
+
+_SIX_DIAMOND = [(0, 1), (0, 2), (1, 3), (1, 4), (2, 4), (3, 5), (4, 5)]
+_APPENDAGE = _SIX_DIAMOND + [(0, 6), (6, 5), (2, 7), (7, 5)]
+_PAPER = [(0, 1), (0, 2), (1, 3), (1, 4), (2, 10), (2, 11), (2, 12), (3, 5), (3, 6), (4, 6), (4, 7), (4, 10), (5, 8),
+          (6, 8), (6, 9), (7, 8), (8, 17), (9, 17), (10, 16), (11, 16), (12, 13), (12, 14), (13, 15), (14, 15),
+          (15, 16), (16, 17)]
+_FLEXIBLE_CASES = [
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/flexible_algo.cc
+    ("single node", 1, [], {}, 0),
+    ("rhombus", 4, [(0, 1), (0, 2), (1, 3), (2, 3)], {}, _S(0, _P(1, 2), 3)),
+    ("chain", 4, [(0, 1), (1, 2), (2, 3)], {}, _S(0, 1, 2, 3)),
+    ("six-node diamond, unit costs", 6, _SIX_DIAMOND, {}, _S(0, _P(1, 2), _P(3, 4), 5)),
+    ("six-node diamond, heavy 3", 6, _SIX_DIAMOND, {2: 10, 3: 1000}, _S(0, 1, _P(_S(2, 4), 3), 5)),
+    ("six-node diamond, heavy 2 and 3", 6, _SIX_DIAMOND, {2: 1000, 3: 1000}, _S(0, _P(_S(1, 3), 2), 4, 5)),
+    ("parallel strands", 8, [(0, 1), (0, 2), (1, 3), (2, 4), (3, 5), (4, 6), (5, 7), (6, 7)], {},
+     _S(0, _P(_S(1, 3, 5), _S(2, 4, 6)), 7)),
+    ("diamond beside a strand", 7, [(0, 1), (0, 2), (1, 3), (1, 4), (2, 4), (3, 6), (4, 6), (0, 5), (5, 6)],
+     {2: 100, 3: 100}, _S(0, _P(_S(_P(_S(1, 3), 2), 4), 5), 6)),
+    ("appendage, unit costs", 8, _APPENDAGE, {}, _S(0, _P(6, _S(_P(1, 2), _P(3, 4, 7))), 5)),
+    ("appendage, weighted", 8, _APPENDAGE, {1: 100, 7: 100}, _S(0, _P(6, _S(2, _P(7, _S(1, _P(3, 4))))), 5)),
+    ("cut across unequal depths", 7, [(0, 1), (0, 2), (1, 3), (1, 4), (2, 5), (3, 6), (4, 5), (5, 6)],
+     {3: 10, 5: 10}, _S(0, _P(_S(1, 4), 2), _P(3, 5), 6)),
+    ("graph from the paper, unit costs", 18, _PAPER + [(10, 9)], {},
+     _S(0, _P(_S(1, _P(3, 4)), _S(2, _P(11, 12))), _P(_S(_P(10, 5, 6, 7), _P(8, 9)), _S(_P(13, 14), 15)), 16, 17)),
+    ("graph from the paper without 10->9", 18, _PAPER, {}, None),
+    ("graph from the paper, mixed costs", 18, _PAPER,
+     {1: 3, 2: 5, 3: 3, 4: 5, 5: 3, 6: 5, 8: 5, 9: 5, 10: 3, 11: 3, 13: 3, 14: 3}, None),
+]
+
+
+@pytest.mark.parametrize("name,n,edges,heavy,expected", _FLEXIBLE_CASES, ids=[k[0] for k in _FLEXIBLE_CASES])
+def test_flexible_golden_cases(name, n, edges, heavy, expected):
+    g = _dg(edges, range(n))
+    cost = {k: float(heavy.get(k, 1)) for k in range(n)}
+    sp = c.flexible_sp_ization(g, cost)
+    assert c.sp_preserves_dependencies(sp, g)
+    assert sorted(c.sp_nodes(sp)) == list(range(n))      # no work is duplicated
+    if expected is not None:
+        assert _canon(sp) == _canon(expected)
+    # never worse than closing whole strata
+    assert c.sp_critical_path_cost(sp, cost) <= c.sp_critical_path_cost(c.naive_stratum_sync_sp_ization(g), cost)
+
+
+def test_flexible_picks_the_cut_that_suits_the_costs_on_the_n_graph():
+    # a -> c, a -> d, b -> d between a common source 9 and sink 10: each of the three ways of closing the N is best
+    # under one of these cost maps (lib/utils/include/utils/graph/series_parallel/sp_ization/index.dox)
+    a, b, cc, d = 0, 1, 2, 3
+    edges = [(9, a), (9, b), (a, cc), (a, d), (b, d), (cc, 10), (d, 10)]
+    for costs, best in (((1, 1, 1, 1), 2.0), ((1, 3, 2, 1), 4.0), ((1, 2, 3, 1), 4.0)):
+        g = _dg(edges, [a, b, cc, d, 9, 10])
+        cost = {a: costs[0], b: costs[1], cc: costs[2], d: costs[3], 9: 0.0, 10: 0.0}
+        sp = c.flexible_sp_ization(g, {k: float(v) for k, v in cost.items()})
+        assert c.sp_preserves_dependencies(sp, g)
+        assert c.sp_critical_path_cost(sp, {k: float(v) for k, v in cost.items()}) == best
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(2, 14), st.integers(0, 10 ** 6))
+def test_escribano_and_flexible_on_random_dags(n, seed):
+    # any DAG (several sources, sinks and components included): every dependency kept, every node exactly once,
+    # and the locally-joining algorithms never lengthen the critical path beyond whole-stratum barriers
+    rng = random.Random(seed)
+    edges = random_dag(rng, n, rng.choice([0.15, 0.3, 0.6]))
+    g = _dg(edges, range(n))
+    cost = {k: float(rng.choice([1, 1, 2, 5, 20])) for k in range(n)}
+    unit = {k: 1.0 for k in range(n)}
+    esc = c.escribano_sp_ization(g)
+    flex = c.flexible_sp_ization(g, cost)
+    for sp in (esc, flex):
+        assert c.sp_preserves_dependencies(sp, g)
+        assert sorted(c.sp_nodes(sp)) == list(range(n))
+    assert c.sp_critical_path_cost(esc, unit) <= c.sp_critical_path_cost(c.naive_stratum_sync_sp_ization(g), unit)
