@@ -478,6 +478,9 @@ PYBIND11_MODULE(_ffcore, m) {
   m.def("naive_stratum_sync_sp_ization", [](const DiGraph &g) { return sp_to_py(naive_stratum_sync_sp_ization(g)); });
   m.def("work_duplicating_sp_ization", [](const DiGraph &g, bool coalesce) { return sp_to_py(work_duplicating_sp_ization(g, coalesce)); },
         py::arg("g"), py::arg("coalesce") = false);
+  m.def("bridge_out_nodes", [](const DiGraph &g, std::set<int> nodes) {
+    return bridge_out_nodes(g, [&](int n) { return nodes.count(n) > 0; });
+  }, py::arg("g"), py::arg("nodes"));
   m.def("escribano_sp_ization", [](const DiGraph &g) { return sp_to_py(escribano_sp_ization(g)); });
   m.def("flexible_sp_ization", [](const DiGraph &g, std::map<int, double> cost) {
     return sp_to_py(flexible_sp_ization(g, [&](int n) { auto it = cost.find(n); return it == cost.end() ? 1.0 : it->second; }));

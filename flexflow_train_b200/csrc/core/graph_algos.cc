@@ -612,7 +612,7 @@ SPTree work_duplicating_sp_ization(const DiGraph &g, bool coalesce) {
 }
 
 // Kept nodes of g with an edge a->b wherever g has a path from a to b whose inner nodes are all dropped.
-static DiGraph bridge_out_nodes(const DiGraph &g, const std::function<bool(int)> &drop) {
+DiGraph bridge_out_nodes(const DiGraph &g, const std::function<bool(int)> &drop) {
   DiGraph r;
   for (int n : g.nodes()) {
     if (drop(n)) continue;

@@ -67,6 +67,9 @@ std::set<int> get_subgraph_successors(const DiGraph &g, const std::set<int> &sub
 // so an edge inside a merged group becomes a self loop.
 DiGraph apply_contraction(const DiGraph &g, const std::map<int, int> &into);
 DiGraph contract_node(const DiGraph &g, int from, int into);
+// The graph without the nodes that `drop` picks: a -> b wherever there was a path from a to b through dropped nodes only
+// (the auxiliary nodes of the SP-ization algorithms leave this way; sp_ization/node_role.h, contract_out_nodes_of_given_role).
+DiGraph bridge_out_nodes(const DiGraph &g, const std::function<bool(int)> &drop);
 bool is_complete_bipartite_digraph(const DiGraph &g);                    // every source has an edge to every sink and nothing else
 std::string digraph_as_dot(const DiGraph &g);
 

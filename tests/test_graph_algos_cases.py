@@ -460,3 +460,75 @@ def test_escribano_and_flexible_on_random_dags(n, seed):
         assert c.sp_preserves_dependencies(sp, g)
         assert sorted(c.sp_nodes(sp)) == list(range(n))
     assert c.sp_critical_path_cost(esc, unit) <= c.sp_critical_path_cost(c.naive_stratum_sync_sp_ization(g), unit)
+
+
+def _canon_multi(t):
+    """Like _canon but a parallel split may hold equal children more than once (duplicated work)."""
+    if not isinstance(t, tuple):
+        return t
+    kind, kids = t
+    kids = [_canon_multi(k) for k in kids]
+    return (kind, tuple(sorted(kids, key=repr))) if kind == "P" else (kind, tuple(kids))
+
+
+_LOPSIDED = [(0, 1), (0, 2), (1, 3), (2, 5), (3, 4), (4, 5)]
+_DUPLICATING_CASES = [
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/work_duplicating_sp_ization.cc
+    ("chain", False, 3, [(0, 1), (1, 2)], _S(0, 1, 2)),
+    ("rhombus", False, 4, [(0, 1), (0, 2), (1, 3), (2, 3)], _S(_P(_S(0, 1), _S(0, 2)), 3)),
+    ("paths of different lengths", False, 6, _LOPSIDED, _S(_P(_S(0, 1, 3, 4), _S(0, 2)), 5)),
+    ("rhombus, coalesced", True, 4, [(0, 1), (0, 2), (1, 3), (2, 3)], _S(0, _P(1, 2), 3)),
+    ("paths of different lengths, coalesced", True, 6, _LOPSIDED, _S(0, _P(_S(1, 3, 4), 2), 5)),
+    ("strands with cross edges, coalesced", True, 6,
+     # upstream stops at S(0, 1, P(S(P(2, 3), 4), 3), 5), with node 3 still twice; the factoring here also merges that copy
+     [(0, 1), (0, 2), (1, 2), (1, 3), (2, 4), (3, 4), (3, 5), (4, 5)], _S(0, 1, _P(2, 3), 4, 5)),
+    ("transitive edges, coalesced", True, 5,
+     [(0, 1), (0, 2), (0, 4), (1, 2), (1, 3), (1, 4), (2, 4), (3, 4)], _S(0, 1, _P(2, 3), 4)),
+]
+
+
+@pytest.mark.parametrize("name,coalesce,n,edges,expected", _DUPLICATING_CASES, ids=[k[0] for k in _DUPLICATING_CASES])
+def test_work_duplicating_golden_cases(name, coalesce, n, edges, expected):
+    g = _dg(edges, range(n))
+    sp = c.work_duplicating_sp_ization(g, coalesce)
+    assert c.sp_preserves_dependencies(sp, g)
+    assert _canon_multi(sp) == _canon_multi(expected)
+    # duplication buys an unchanged critical path
+    unit = {k: 1.0 for k in range(n)}
+    assert c.sp_critical_path_cost(sp, unit) == _graph_costs(edges, unit)[1]
+
+
+def test_dependencies_are_maintained_cases():
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/dependencies_are_maintained.cc
+    assert c.sp_preserves_dependencies(0, _dg([], [0]))
+    chain = _dg([(0, 1), (1, 2)], range(3))
+    assert c.sp_preserves_dependencies(_S(0, 1, 2), chain)
+    assert not c.sp_preserves_dependencies(_S(0, 2, 1), chain)
+    assert not c.sp_preserves_dependencies(_P(0, 1, 2), chain)
+    assert not c.sp_preserves_dependencies(_S(0, 1), chain)          # a node is missing
+    loose = _dg([], range(3))
+    assert c.sp_preserves_dependencies(_P(0, 1, 2), loose)
+    assert c.sp_preserves_dependencies(_S(0, 1, 2), loose)          # extra ordering is allowed
+    rhombus = _dg([(0, 1), (0, 2), (1, 3), (2, 3)], range(4))
+    assert c.sp_preserves_dependencies(_S(0, _P(1, 2), 3), rhombus)
+    assert c.sp_preserves_dependencies(_S(0, 1, 2, 3), rhombus)
+    assert c.sp_preserves_dependencies(_S(_P(_S(0, 1), _S(0, 2)), 3), rhombus)
+    assert not c.sp_preserves_dependencies(_S(_P(0, 1), 2, 3), rhombus)
+    diamond = _dg(_SIX_DIAMOND, range(6))
+    assert c.sp_preserves_dependencies(_S(0, _P(1, 2), _P(3, 4), 5), diamond)
+    assert c.sp_preserves_dependencies(_S(0, _P(_S(1, 3), 2), 4, 5), diamond)
+    assert not c.sp_preserves_dependencies(_S(0, _P(_S(1, 3), _S(2, 4)), 5), diamond)   # 1 -> 4 is lost
+
+
+def test_bridge_out_nodes_cases():
+    # lib/utils/test/src/utils/graph/series_parallel/sp_ization/node_role.cc
+    g = _dg([(0, 1), (1, 2), (1, 3), (2, 4), (3, 4)], range(5))
+    r = c.bridge_out_nodes(g, {1, 2})
+    assert sorted(r.nodes()) == [0, 3, 4]
+    assert sorted(r.edges()) == [(0, 3), (0, 4), (3, 4)]
+    g = _dg([(0, 1), (1, 2), (1, 3)], range(4))
+    r = c.bridge_out_nodes(g, set())
+    assert sorted(r.nodes()) == sorted(g.nodes()) and sorted(r.edges()) == sorted(g.edges())
+    # a dropped source or sink simply goes
+    r = c.bridge_out_nodes(g, {0, 3})
+    assert sorted(r.nodes()) == [1, 2] and sorted(r.edges()) == [(1, 2)]
