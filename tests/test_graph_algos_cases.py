@@ -532,3 +532,41 @@ def test_bridge_out_nodes_cases():
     # a dropped source or sink simply goes
     r = c.bridge_out_nodes(g, {0, 3})
     assert sorted(r.nodes()) == [1, 2] and sorted(r.edges()) == [(1, 2)]
+
+
+_DECOMPOSITION_CASES = [
+    # lib/utils/test/src/utils/graph/series_parallel/get_series_parallel_decomposition.cc
+    ("single node", 1, [], 0),
+    ("two loose nodes", 2, [], _P(0, 1)),
+    ("chain", 2, [(0, 1)], _S(0, 1)),
+    ("fork", 3, [(0, 1), (0, 2)], _S(0, _P(1, 2))),
+    ("two strands", 6, [(0, 1), (0, 2), (1, 3), (2, 4), (3, 5), (4, 5)], _S(0, _P(_S(1, 3), _S(2, 4)), 5)),
+    ("all to all", 4, [(0, 2), (0, 3), (1, 2), (1, 3)], _S(_P(0, 1), _P(2, 3))),
+    ("N graph", 4, [(0, 2), (1, 2), (1, 3)], None),
+    ("needs transitive reduction", 4, [(0, 1), (0, 2), (1, 2), (1, 3), (2, 3)], _S(0, 1, 2, 3)),
+]
+
+
+@pytest.mark.parametrize("name,n,edges,expected", _DECOMPOSITION_CASES, ids=[k[0] for k in _DECOMPOSITION_CASES])
+def test_series_parallel_decomposition_golden_cases(name, n, edges, expected):
+    sp = c.get_series_parallel_decomposition(_dg(edges, range(n)))
+    if expected is None:
+        assert sp is None
+    else:
+        assert _canon(sp) == _canon(expected)
+
+
+@pytest.mark.parametrize("tree,nodes,edges,sources,sinks", [
+    # lib/utils/test/src/utils/graph/series_parallel/digraph_generation.cc
+    (_S(1, 2, 3), 3, 2, 1, 1),
+    (_P(1, 2, 3), 3, 0, 3, 3),
+    (_S(1, _P(2, 3)), 3, 2, 1, 2),
+    (_P(_S(1, 2), _S(3, 4)), 4, 2, 2, 2),
+    (_S(1, _P(2, 3), 4), 4, 4, 1, 1),
+    (_S(_P(_S(_P(1, 2), _P(3, 4), 5), _S(6, 7)), 8), 8, 9, 3, 1),
+])
+def test_digraph_from_sp_cases(tree, nodes, edges, sources, sinks):
+    g = c.digraph_from_sp(tree)
+    assert (len(g.nodes()), len(g.edges()), len(g.sources()), len(g.sinks())) == (nodes, edges, sources, sinks)
+    if nodes > 1:
+        assert _canon(c.get_series_parallel_decomposition(g)) == _canon(tree)     # the two are inverses
