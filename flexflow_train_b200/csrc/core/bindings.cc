@@ -478,6 +478,7 @@ PYBIND11_MODULE(_ffcore, m) {
   m.def("naive_stratum_sync_sp_ization", [](const DiGraph &g) { return sp_to_py(naive_stratum_sync_sp_ization(g)); });
   m.def("work_duplicating_sp_ization", [](const DiGraph &g, bool coalesce) { return sp_to_py(work_duplicating_sp_ization(g, coalesce)); },
         py::arg("g"), py::arg("coalesce") = false);
+  m.def("sp_ancestors", [](py::object t, int node) { return sp_ancestors(sp_from_py(t), node); }, py::arg("tree"), py::arg("node"));
   m.def("bridge_out_nodes", [](const DiGraph &g, std::set<int> nodes) {
     return bridge_out_nodes(g, [&](int n) { return nodes.count(n) > 0; });
   }, py::arg("g"), py::arg("nodes"));

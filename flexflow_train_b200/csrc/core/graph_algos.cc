@@ -550,6 +550,32 @@ std::optional<SPTree> get_series_parallel_decomposition(const DiGraph &g_in) {
   return normalize_sp(edges[alive[0]].label);
 }
 
+// Walks down to `node`; on the way, a series split contributes all the children left of the one that holds the node.
+static bool collect_sp_ancestors(const SPTree &t, int node, std::set<int> &out) {
+  if (t.kind == SPTree::Leaf) return t.node == node;
+  bool found = false;
+  if (t.kind == SPTree::Parallel) {
+    for (auto &c : t.children) found = collect_sp_ancestors(c, node, out) || found;
+    return found;
+  }
+  std::set<int> before;
+  for (auto &c : t.children) {
+    std::set<int> inner;
+    if (collect_sp_ancestors(c, node, inner)) {
+      found = true;
+      out.insert(before.begin(), before.end());
+      out.insert(inner.begin(), inner.end());
+    }
+    for (int n : sp_nodes(c)) before.insert(n);
+  }
+  return found;
+}
+std::set<int> sp_ancestors(const SPTree &t, int node) {
+  std::set<int> out;
+  if (!collect_sp_ancestors(t, node, out)) throw std::runtime_error("sp_ancestors: node " + std::to_string(node) + " is not in the tree");
+  return out;
+}
+
 // ---------------------------------------------------------------- SP-ization
 SPTree naive_stratum_sync_sp_ization(const DiGraph &g) {
   auto depth = get_longest_path_lengths_from_root(g);

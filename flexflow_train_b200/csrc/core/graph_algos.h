@@ -92,6 +92,9 @@ SPTree right_associative_binary_sp_tree(const SPTree &nary);
 SPTree balanced_binary_sp_tree(const SPTree &nary);      // balanced_binary_sp_tree_from_nary.h
 double sp_work_cost(const SPTree &t, const std::function<double(int)> &cost);
 double sp_critical_path_cost(const SPTree &t, const std::function<double(int)> &cost);
+// Every node the tree orders before `node` (before any of its occurrences, if work was duplicated);
+// lib/utils/include/utils/graph/series_parallel/get_ancestors.h
+std::set<int> sp_ancestors(const SPTree &t, int node);
 DiGraph digraph_from_sp(const SPTree &t);                // the dependencies the tree implies
 Json sp_to_json(const SPTree &binary);                   // {"type": series|parallel|leaf, left_child, right_child, value}
 SPTree sp_from_json(const Json &j);

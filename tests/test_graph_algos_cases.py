@@ -570,3 +570,23 @@ def test_digraph_from_sp_cases(tree, nodes, edges, sources, sinks):
     assert (len(g.nodes()), len(g.edges()), len(g.sources()), len(g.sinks())) == (nodes, edges, sources, sinks)
     if nodes > 1:
         assert _canon(c.get_series_parallel_decomposition(g)) == _canon(tree)     # the two are inverses
+
+
+def test_sp_ancestors_cases():
+    # lib/utils/test/src/utils/graph/series_parallel/get_ancestors.cc
+    assert c.sp_ancestors(0, 0) == set()
+    assert c.sp_ancestors(_S(0, 1, 2), 2) == {0, 1}
+    assert c.sp_ancestors(_P(0, 1, 2), 1) == set()
+    assert c.sp_ancestors(_S(0, _P(_S(1, 2), 3)), 2) == {0, 1}
+    assert c.sp_ancestors(_S(0, _P(1, 2), 3), 3) == {0, 1, 2}
+    sp = _S(0, _P(_S(1, _P(2, 3), 4), _S(5, 6)), 7)
+    assert c.sp_ancestors(sp, 4) == {0, 1, 2, 3}
+    assert c.sp_ancestors(sp, 3) == {0, 1}
+    assert c.sp_ancestors(sp, 6) == {0, 5}
+    assert c.sp_ancestors(sp, 7) == {0, 1, 2, 3, 4, 5, 6}
+    with pytest.raises(Exception):
+        c.sp_ancestors(sp, 99)
+    # the tree's own view agrees with the graph it stands for
+    g = c.digraph_from_sp(sp)
+    for n in range(8):
+        assert c.sp_ancestors(sp, n) == set(c.get_ancestors(g, n))
