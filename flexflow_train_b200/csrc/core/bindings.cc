@@ -461,7 +461,12 @@ PYBIND11_MODULE(_ffcore, m) {
     if (!t) return py::none();
     return sp_to_py(*t);
   });
-  m.def("sp_normalize", [](py::object t) { return sp_to_py(normalize_sp(sp_from_py(t))); });
+  m.def("sp_normalize", [](py::object t) {
+    // a tree without a single node has no normal form (normalize_sp_decomposition.h refuses it as well)
+    SPTree n = normalize_sp(sp_from_py(t));
+    if (n.kind != SPTree::Leaf && n.children.empty()) throw std::runtime_error("sp_normalize: the decomposition holds no node");
+    return sp_to_py(n);
+  });
   m.def("sp_balanced_binary", [](py::object t) { return sp_to_py(balanced_binary_sp_tree(sp_from_py(t))); });
   m.def("sp_left_associative_binary", [](py::object t) { return sp_to_py(left_associative_binary_sp_tree(sp_from_py(t))); });
   m.def("sp_right_associative_binary", [](py::object t) { return sp_to_py(right_associative_binary_sp_tree(sp_from_py(t))); });

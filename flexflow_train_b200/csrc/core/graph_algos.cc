@@ -345,6 +345,7 @@ SPTree normalize_sp(const SPTree &t) {
   std::vector<SPTree> flat;
   for (auto &c : t.children) {
     SPTree n = normalize_sp(c);
+    if (n.kind != SPTree::Leaf && n.children.empty()) continue;   // a split with nothing in it goes
     if (n.kind == t.kind) flat.insert(flat.end(), n.children.begin(), n.children.end());
     else flat.push_back(n);
   }

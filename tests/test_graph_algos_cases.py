@@ -590,3 +590,16 @@ def test_sp_ancestors_cases():
     g = c.digraph_from_sp(sp)
     for n in range(8):
         assert c.sp_ancestors(sp, n) == set(c.get_ancestors(g, n))
+
+
+def test_sp_normalize_cases():
+    # lib/utils/test/src/utils/graph/series_parallel/normalize_sp_decomposition.cc
+    assert c.sp_normalize(1) == 1
+    assert c.sp_normalize(_S(1)) == 1
+    assert c.sp_normalize(_P(1)) == 1
+    assert c.sp_normalize(_S(_P(1), 2)) == _S(1, 2)
+    assert _canon(c.sp_normalize(_P(_S(1), 2))) == _canon(_P(1, 2))
+    assert _canon(c.sp_normalize(_P(_S(_P(1, 2)), 3, _S()))) == _canon(_P(1, 2, 3))
+    assert c.sp_normalize(_S(1, _S(2, _S(3, _P())), 4)) == _S(1, 2, 3, 4)
+    with pytest.raises(Exception):
+        c.sp_normalize(_S(_P(), _P()))
